@@ -1,0 +1,194 @@
+/*
+ * xg_sm100 — C ABI of the sm_100a kernel library behind xpu_graph's `cuda_sm100` target.
+ *
+ * Conventions (all entry points):
+ *   - plain pointers and sizes; the caller owns every buffer (device memory unless the
+ *     parameter is documented as a HOST array);
+ *   - work is enqueued on `stream` (a cudaStream_t passed as void*) of the caller's current
+ *     device; nothing synchronises the device, nothing allocates device memory;
+ *   - return value: XG_OK (0) or a negative XG_ERR_* code; the library never aborts or throws;
+ *     xg_last_error() returns a thread-local, human-readable message for the last failure;
+ *   - dtype codes: XG_F32 / XG_BF16 / XG_F16; element strides ("ld", "stride") are in ELEMENTS
+ *     unless the name ends in _bytes.
+ *
+ * Each declaration cites the reference interface it stands in for (paths are relative to the
+ * xpu_graph source tree, src/xpu_graph/...).
+ */
+#ifndef XG_SM100_H_
+#define XG_SM100_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define XG_OK 0
+#define XG_ERR_INVALID_ARG (-1)   /* null pointer, negative extent, bad enum */
+#define XG_ERR_UNSUPPORTED (-2)   /* shape / dtype / alignment this build has no kernel for */
+#define XG_ERR_LAUNCH (-3)        /* cudaGetLastError() after the launch was not cudaSuccess */
+#define XG_ERR_DEVICE (-4)        /* wrong architecture or no device */
+#define XG_ERR_TOO_LARGE (-5)     /* size beyond a documented fixed maximum */
+
+#define XG_F32 0
+#define XG_BF16 1
+#define XG_F16 2
+
+#define XG_ACT_NONE 0
+#define XG_ACT_GELU 1 /* erf form, aten.gelu(approximate='none') */
+#define XG_ACT_RELU 2
+#define XG_ACT_SILU 3
+#define XG_ACT_SIGMOID 4
+
+/* ---- library identity ------------------------------------------------------------------ */
+
+/* ABI version of this header (major*1000 + minor). */
+int xg_version(void);
+/* 1 if device `device` is compute capability 10.x (the only architecture the kernels are built for). */
+int xg_device_arch_ok(int device);
+/* Message of the last failing call on this thread ("" if none). */
+const char* xg_last_error(void);
+
+/*
+ * Status word of the tensor-core kernels on the current device: 0 = healthy; non-zero = a bounded
+ * wait inside a kernel expired (bit 0 producer, bit 1 MMA issuer, bit 2 epilogue, bits 4-6 the same
+ * roles of the attention kernel) and that launch's output is invalid. This is the one entry point
+ * that synchronises (it copies the word back); reset != 0 clears it. No reference counterpart.
+ */
+int xg_tc_status(unsigned int* status, int reset);
+
+/* ---- normalisation --------------------------------------------------------------------- */
+
+/*
+ * RMSNorm with optional fused residual add.
+ *   s = residual ? round_to_dtype(x + residual) : x
+ *   y = to_dtype( (float(s) * rsqrt(mean(float(s)^2) + eps)) * float(weight) )
+ *   if sum_out: sum_out = s          (the "store output before norm" second result)
+ * Replaces: passes/patterns/utils/default_replacements.py:19-25 (DefaultRMSNorm) as called by
+ * passes/patterns/structure/custom_rmsnorm.py:21-29; residual form: targets/npu/triton_kernel/
+ * fused_add_rmsnorm.py:10-36 and targets/mlu/fuse_add_norm.py:21-83 (store_output_before_norm).
+ * x, residual, y, sum_out: [rows, hidden], last dim contiguous, row strides in elements
+ * (y and sum_out are written with row stride `hidden`). weight: [hidden] of dtype w_dtype
+ * (XG_F32 or the same as dtype).
+ */
+int xg_rmsnorm(const void* x, const void* residual, const void* weight, void* y, void* sum_out,
+               int64_t rows, int64_t hidden, int64_t x_row_stride, int64_t res_row_stride,
+               float eps, int dtype, int w_dtype, void* stream);
+
+/*
+ * LayerNorm with optional fused residual add; weight and bias are both required, as in
+ * passes/patterns/structure/custom_layernorm.py:25.
+ *   s = residual ? round_to_dtype(x + residual) : x
+ *   y = to_dtype( (float(s) - mean) * rsqrt(var + eps) * float(weight) + float(bias) )
+ * Replaces: passes/patterns/utils/default_replacements.py:28-36 (DefaultLayerNorm) as called by
+ * passes/patterns/structure/custom_layernorm.py:21-29; residual form targets/mlu/fuse_add_norm.py:21-83.
+ */
+int xg_layernorm(const void* x, const void* residual, const void* weight, const void* bias, void* y,
+                 void* sum_out, int64_t rows, int64_t hidden, int64_t x_row_stride,
+                 int64_t res_row_stride, float eps, int dtype, int w_dtype, void* stream);
+
+/* ---- elementwise fusions --------------------------------------------------------------- */
+
+/*
+ * Rotate-half rotary embedding: y = x*cos + cat(-x[..., D/2:], x[..., :D/2])*sin.
+ * x: [B, H, S, D] addressed by element strides (D contiguous); cos/sin: [S, D] contiguous, same
+ * dtype as x; y: [B, H, S, D] contiguous. The reference has no RoPE op; this replaces the
+ * 2x slice + neg + cat + 2x mul + add chain that the graph carries (semantics of the aten ops).
+ */
+int xg_rope(const void* x, const void* cos, const void* sin, void* y, int64_t B, int64_t H, int64_t S,
+            int64_t D, int64_t x_stride_b, int64_t x_stride_h, int64_t x_stride_s, int dtype,
+            void* stream);
+
+/*
+ * SwiGLU: out = silu(gate) * up, row-major [rows, cols] with separate row strides (a packed
+ * [rows, 2*cols] tensor is passed as gate = base, up = base + cols, both ld = 2*cols).
+ * Replaces: targets/npu/triton_kernel/fused_silu_mul.py:10-60 (fused_silu_mul).
+ */
+int xg_swiglu(const void* gate, const void* up, void* out, int64_t rows, int64_t cols, int64_t ld_gate,
+              int64_t ld_up, int64_t ld_out, int dtype, void* stream);
+
+/* ---- dense layers ---------------------------------------------------------------------- */
+
+/*
+ * out[M,N] = act( A[M,K] @ W + bias + residual ),  W = B[K,N] (trans_b = 0) or B[N,K]^T (trans_b = 1).
+ * bias: nullable [N]; residual: nullable [M,N] with row stride ldr (the "2-D bias" / beta = 1 form);
+ * act: XG_ACT_*. dtype XG_BF16 / XG_F16: tensor-core path (tcgen05, fp32 accumulate);
+ * dtype XG_F32: true fp32 FMA path (no TF32).
+ * Replaces: targets/mlu/structure_replacements/dense_layer_modules.py:9-57 (DenseLayerModule →
+ * torch_mlu_ops.matmul) as called by passes/patterns/structure/custom_denselayer.py:80-88.
+ */
+int xg_gemm_bias_act(const void* A, const void* B, const void* bias, const void* residual, void* out,
+                     int64_t M, int64_t N, int64_t K, int64_t lda, int64_t ldb, int64_t ldc,
+                     int64_t ldr, int trans_b, int act, int dtype, void* stream);
+
+/*
+ * Batched form: out[b] = act( A[b] @ W[b] + bias[b] + residual[b] ), batch strides in elements
+ * (0 broadcasts). Replaces: dense_layer_modules.py:71-120 (BatchDenseLayerModule) as called by
+ * passes/patterns/structure/custom_denselayer.py:111-117.
+ */
+int xg_bgemm_bias_act(const void* A, const void* B, const void* bias, const void* residual, void* out,
+                      int64_t batch, int64_t M, int64_t N, int64_t K, int64_t lda, int64_t ldb,
+                      int64_t ldc, int64_t ldr, int64_t stride_a, int64_t stride_b,
+                      int64_t stride_bias, int64_t stride_r, int64_t stride_c, int trans_b, int act,
+                      int dtype, void* stream);
+
+/*
+ * Dual GEMM with SwiGLU epilogue: out = silu(A @ Wg^T) * (A @ Wu^T); Wg, Wu: [N, K] (Linear layout).
+ * Replaces the mul(silu(mm), mm) sub-graph; elementwise part as targets/npu/fuse_silu_mul.py:21-69.
+ */
+int xg_gemm_swiglu(const void* A, const void* Wg, const void* Wu, void* out, int64_t M, int64_t N,
+                   int64_t K, int64_t lda, int64_t ldw, int64_t ldc, int dtype, void* stream);
+
+/* ---- attention ------------------------------------------------------------------------- */
+
+/*
+ * out = softmax(q @ k^T * scale + mask) @ v, per (batch, head); online softmax, fp32 accumulate.
+ * q: [B,H,Sq,D], k,v: [B,H,Skv,D], out: [B,H,Sq,D]; each addressed by element strides for
+ * (batch, head, seq) with D contiguous. mask: nullable additive mask of the same dtype,
+ * addressed by element strides for (batch, head, q, kv) — 0 strides broadcast. causal != 0 applies
+ * the lower-triangular mask (query i sees keys j <= i + Skv - Sq).
+ * Replaces: aten.scaled_dot_product_attention as emitted by
+ * passes/patterns/common/fuse_scaled_dot_product_attention.py:163-238 (FusedSDPA).
+ */
+int xg_sdpa_fwd(const void* q, const void* k, const void* v, const void* mask, void* out, int64_t B,
+                int64_t H, int64_t Sq, int64_t Skv, int64_t D, const int64_t* q_strides3,
+                const int64_t* k_strides3, const int64_t* v_strides3, const int64_t* o_strides3,
+                const int64_t* mask_strides4, float scale, int causal, int dtype, void* stream);
+
+/* ---- copy fusions (bit-exact) ---------------------------------------------------------- */
+
+/*
+ * Segmented 2-D copy: for every segment k and row r < rows,
+ *   dst_k[r*dst_ld_k + 0..len_k) = zero_row(r) ? 0 : src_k[r*src_ld_k + 0..len_k)
+ * where src_k = (char*)src_ptrs[k], dst_k = (char*)dst_ptrs[k]; all lengths and strides in BYTES.
+ * zero_row(r) = row_mask && (row_mask[r] != 0) == (mask_zero_when != 0); row_mask: nullable
+ * device bytes [rows]. src_ptrs/dst_ptrs/src_ld_bytes/dst_ld_bytes/len_bytes: HOST arrays of nseg.
+ * This one entry point carries: slice+cat of one source (targets/mlu/structure_replacements/
+ * __init__.py:50-63, FuseSliceCatSameInputModule), equal-length multi-slice to [num, rows, len]
+ * (:21-47, FuseSliceModule), multi-output split (:66-144, FuseSliceCatSameInputModule_v2),
+ * where-masked slice+cat (targets/mlu/triton_kernel/fused_slice_where_cat.py:12-73), and plain
+ * cat / stack of several sources along the last dim.
+ */
+int xg_seg_copy(const void* const* src_ptrs, void* const* dst_ptrs, const int64_t* src_ld_bytes,
+                const int64_t* dst_ld_bytes, const int64_t* len_bytes, int64_t nseg, int64_t rows,
+                const uint8_t* row_mask, int mask_zero_when, void* stream);
+
+/*
+ * Multi-table row gather (embedding lookups fused with the where-mask and the stack/cat):
+ *   out[r*out_ld + f*D + j] = zero_row(r) ? 0 : tables[f][idx(r,f)*D + j],   j < D
+ * tables: HOST array of F device pointers to [table_rows[f], D] contiguous tables;
+ * idx(r,f) = idx[r*idx_row_stride + f*idx_col_stride] (int64, device); an index outside
+ * [0, table_rows[f]) writes zeros for that row. elem_size in {2,4,8}; out_ld in elements.
+ * Replaces: F fused aten.embedding lookups + where + stack; nearest reference anchors are
+ * targets/mlu/repeat_to_expand.py:25-56 and torch_mlu.emb_concat
+ * (targets/mlu/structure_replacements/__init__.py:136).
+ */
+int xg_gather_rows(const void* const* tables, const int64_t* table_rows, int64_t F, const int64_t* idx,
+                   int64_t idx_row_stride, int64_t idx_col_stride, const uint8_t* row_mask,
+                   int mask_zero_when, void* out, int64_t rows, int64_t D, int64_t out_ld,
+                   int elem_size, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* XG_SM100_H_ */

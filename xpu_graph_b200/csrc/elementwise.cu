@@ -1,0 +1,198 @@
+// Bandwidth-bound elementwise fusions: rotate-half RoPE and SwiGLU (silu(gate) * up).
+// Both read each input element once with 16-byte loads and write the result once.
+#include "common.cuh"
+
+namespace xg {
+namespace {
+
+// ---------------------------------------------------------------------------------------
+// RoPE. One thread produces the two 16-byte output vectors at column j and j + D/2 of a row,
+// because both need the same pair of input vectors.
+// ---------------------------------------------------------------------------------------
+struct RopeParams {
+    const void* x;
+    const void* cos;
+    const void* sin;
+    void* y;
+    int64_t B, H, S, D;
+    int64_t sb, sh, ss;
+};
+
+template <typename T>
+__global__ void __launch_bounds__(256) rope_vec_kernel(const RopeParams p) {
+    constexpr int EPV = Vec16<T>::N;
+    const int hv_per_row = (int)(p.D / 2 / EPV);
+    const int64_t total = p.B * p.H * p.S * hv_per_row;
+    const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= total) return;
+    const int hv = (int)(idx % hv_per_row);
+    const int64_t row = idx / hv_per_row;  // (b, h, s) flattened
+    const int64_t s = row % p.S;
+    const int64_t bh = row / p.S;
+    const int64_t h = bh % p.H;
+    const int64_t b = bh / p.H;
+    const int64_t half = p.D / 2;
+    const T* xr = reinterpret_cast<const T*>(p.x) + b * p.sb + h * p.sh + s * p.ss;
+    const T* cr = reinterpret_cast<const T*>(p.cos) + s * p.D;
+    const T* sr = reinterpret_cast<const T*>(p.sin) + s * p.D;
+    T* yr = reinterpret_cast<T*>(p.y) + row * p.D;
+    const int64_t j = (int64_t)hv * EPV;
+    const Vec16<T> x1 = ld16_stream(xr + j), x2 = ld16_stream(xr + j + half);
+    const Vec16<T> c1 = ld16(cr + j), c2 = ld16(cr + j + half);
+    const Vec16<T> s1 = ld16(sr + j), s2 = ld16(sr + j + half);
+    Vec16<T> o1, o2;
+#pragma unroll
+    for (int i = 0; i < EPV; ++i) {
+        const float a = Cvt<T>::to_f(x1.v[i]), bb = Cvt<T>::to_f(x2.v[i]);
+        o1.v[i] = Cvt<T>::from_f(a * Cvt<T>::to_f(c1.v[i]) - bb * Cvt<T>::to_f(s1.v[i]));
+        o2.v[i] = Cvt<T>::from_f(bb * Cvt<T>::to_f(c2.v[i]) + a * Cvt<T>::to_f(s2.v[i]));
+    }
+    st16(yr + j, o1);
+    st16(yr + j + half, o2);
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) rope_scalar_kernel(const RopeParams p) {
+    const int64_t half = p.D / 2;
+    const int64_t total = p.B * p.H * p.S * half;
+    const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= total) return;
+    const int64_t j = idx % half;
+    const int64_t row = idx / half;
+    const int64_t s = row % p.S;
+    const int64_t bh = row / p.S;
+    const int64_t h = bh % p.H;
+    const int64_t b = bh / p.H;
+    const T* xr = reinterpret_cast<const T*>(p.x) + b * p.sb + h * p.sh + s * p.ss;
+    const T* cr = reinterpret_cast<const T*>(p.cos) + s * p.D;
+    const T* sr = reinterpret_cast<const T*>(p.sin) + s * p.D;
+    T* yr = reinterpret_cast<T*>(p.y) + row * p.D;
+    const float a = Cvt<T>::to_f(xr[j]), bb = Cvt<T>::to_f(xr[j + half]);
+    yr[j] = Cvt<T>::from_f(a * Cvt<T>::to_f(cr[j]) - bb * Cvt<T>::to_f(sr[j]));
+    yr[j + half] = Cvt<T>::from_f(bb * Cvt<T>::to_f(cr[j + half]) + a * Cvt<T>::to_f(sr[j + half]));
+}
+
+template <typename T>
+int launch_rope(const RopeParams& p, cudaStream_t st) {
+    constexpr int EPV = Vec16<T>::N;
+    const int64_t half = p.D / 2;
+    const bool vec_ok = (half % EPV == 0) && aligned16(p.x) && aligned16(p.cos) && aligned16(p.sin) && aligned16(p.y) &&
+                        p.sb % EPV == 0 && p.sh % EPV == 0 && p.ss % EPV == 0;
+    const int64_t total = p.B * p.H * p.S * (vec_ok ? half / EPV : half);
+    const int64_t grid = (total + 255) / 256;
+    if (grid > 0x7fffffffLL) return fail(XG_ERR_TOO_LARGE, "xg_rope: tensor too large");
+    if (vec_ok) rope_vec_kernel<T><<<(unsigned)grid, 256, 0, st>>>(p);
+    else rope_scalar_kernel<T><<<(unsigned)grid, 256, 0, st>>>(p);
+    return check_launch("xg_rope");
+}
+
+// ---------------------------------------------------------------------------------------
+// SwiGLU
+// ---------------------------------------------------------------------------------------
+struct SwigluParams {
+    const void* gate;
+    const void* up;
+    void* out;
+    int64_t rows, cols, ldg, ldu, ldo;
+};
+
+// expf (not __expf): the fp32 path must stay within 1e-5 relative of aten's silu.
+__device__ __forceinline__ float silu_f(float g) { return g / (1.0f + expf(-g)); }
+
+template <typename T, int UNROLL>
+__global__ void __launch_bounds__(256) swiglu_vec_kernel(const SwigluParams p) {
+    constexpr int EPV = Vec16<T>::N;
+    const int64_t vec_per_row = p.cols / EPV;
+    const int64_t total = p.rows * vec_per_row;
+    const int64_t base = ((int64_t)blockIdx.x * UNROLL) * blockDim.x + threadIdx.x;
+    Vec16<T> g[UNROLL], u[UNROLL];
+    int64_t off_o[UNROLL];
+#pragma unroll
+    for (int k = 0; k < UNROLL; ++k) {
+        const int64_t idx = base + (int64_t)k * blockDim.x;
+        if (idx < total) {
+            const int64_t r = idx / vec_per_row;
+            const int64_t c = (idx - r * vec_per_row) * EPV;
+            g[k] = ld16_stream(reinterpret_cast<const T*>(p.gate) + r * p.ldg + c);
+            u[k] = ld16_stream(reinterpret_cast<const T*>(p.up) + r * p.ldu + c);
+            off_o[k] = r * p.ldo + c;
+        }
+    }
+#pragma unroll
+    for (int k = 0; k < UNROLL; ++k) {
+        const int64_t idx = base + (int64_t)k * blockDim.x;
+        if (idx < total) {
+            Vec16<T> o;
+#pragma unroll
+            for (int i = 0; i < EPV; ++i)
+                o.v[i] = Cvt<T>::from_f(silu_f(Cvt<T>::to_f(g[k].v[i])) * Cvt<T>::to_f(u[k].v[i]));
+            st16(reinterpret_cast<T*>(p.out) + off_o[k], o);
+        }
+    }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) swiglu_scalar_kernel(const SwigluParams p) {
+    const int64_t total = p.rows * p.cols;
+    const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= total) return;
+    const int64_t r = idx / p.cols, c = idx - r * p.cols;
+    const float g = Cvt<T>::to_f(reinterpret_cast<const T*>(p.gate)[r * p.ldg + c]);
+    const float u = Cvt<T>::to_f(reinterpret_cast<const T*>(p.up)[r * p.ldu + c]);
+    reinterpret_cast<T*>(p.out)[r * p.ldo + c] = Cvt<T>::from_f(silu_f(g) * u);
+}
+
+template <typename T>
+int launch_swiglu(const SwigluParams& p, cudaStream_t st) {
+    constexpr int EPV = Vec16<T>::N;
+    constexpr int UNROLL = 4;
+    const bool vec_ok = p.cols % EPV == 0 && p.ldg % EPV == 0 && p.ldu % EPV == 0 && p.ldo % EPV == 0 &&
+                        aligned16(p.gate) && aligned16(p.up) && aligned16(p.out);
+    if (vec_ok) {
+        const int64_t total = p.rows * (p.cols / EPV);
+        const int64_t grid = (total + 256 * UNROLL - 1) / (256 * UNROLL);
+        if (grid > 0x7fffffffLL) return fail(XG_ERR_TOO_LARGE, "xg_swiglu: tensor too large");
+        swiglu_vec_kernel<T, UNROLL><<<(unsigned)grid, 256, 0, st>>>(p);
+    } else {
+        const int64_t grid = (p.rows * p.cols + 255) / 256;
+        if (grid > 0x7fffffffLL) return fail(XG_ERR_TOO_LARGE, "xg_swiglu: tensor too large");
+        swiglu_scalar_kernel<T><<<(unsigned)grid, 256, 0, st>>>(p);
+    }
+    return check_launch("xg_swiglu");
+}
+
+}  // namespace
+}  // namespace xg
+
+extern "C" int xg_rope(const void* x, const void* cos, const void* sin, void* y, int64_t B, int64_t H, int64_t S,
+                       int64_t D, int64_t x_stride_b, int64_t x_stride_h, int64_t x_stride_s, int dtype, void* stream) {
+    using namespace xg;
+    if (!x || !cos || !sin || !y) return fail(XG_ERR_INVALID_ARG, "xg_rope: null pointer");
+    if (B < 0 || H < 0 || S < 0 || D <= 0 || (D & 1)) return fail(XG_ERR_INVALID_ARG, "xg_rope: bad extents (D must be even)");
+    if (dtype_size(dtype) == 0) return fail(XG_ERR_INVALID_ARG, "xg_rope: bad dtype %d", dtype);
+    if (B * H * S == 0) return XG_OK;
+    RopeParams p{x, cos, sin, y, B, H, S, D, x_stride_b, x_stride_h, x_stride_s};
+    cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+    switch (dtype) {
+        case XG_F32: return launch_rope<float>(p, st);
+        case XG_BF16: return launch_rope<__nv_bfloat16>(p, st);
+        default: return launch_rope<__half>(p, st);
+    }
+}
+
+extern "C" int xg_swiglu(const void* gate, const void* up, void* out, int64_t rows, int64_t cols, int64_t ld_gate,
+                         int64_t ld_up, int64_t ld_out, int dtype, void* stream) {
+    using namespace xg;
+    if (!gate || !up || !out) return fail(XG_ERR_INVALID_ARG, "xg_swiglu: null pointer");
+    if (rows < 0 || cols < 0) return fail(XG_ERR_INVALID_ARG, "xg_swiglu: negative extent");
+    if (ld_gate < cols || ld_up < cols || ld_out < cols) return fail(XG_ERR_INVALID_ARG, "xg_swiglu: row stride smaller than cols");
+    if (dtype_size(dtype) == 0) return fail(XG_ERR_INVALID_ARG, "xg_swiglu: bad dtype %d", dtype);
+    if (rows * cols == 0) return XG_OK;
+    SwigluParams p{gate, up, out, rows, cols, ld_gate, ld_up, ld_out};
+    cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+    switch (dtype) {
+        case XG_F32: return launch_swiglu<float>(p, st);
+        case XG_BF16: return launch_swiglu<__nv_bfloat16>(p, st);
+        default: return launch_swiglu<__half>(p, st);
+    }
+}

@@ -1,0 +1,74 @@
+// C-ABI front of the dense-layer kernels: argument validation and routing to the tensor-core
+// (16-bit) or FFMA (fp32) implementation.
+#include "common.cuh"
+
+namespace xg {
+int gemm_tc_entry(const void* A, const void* B, const void* bias, const void* residual, void* out, int64_t M, int64_t N,
+                  int64_t K, int64_t lda, int64_t ldb, int64_t ldc, int64_t ldr, int act, int dtype, cudaStream_t st);
+int gemm_f32_entry(const void* A, const void* B, const void* bias, const void* residual, void* out, int64_t M, int64_t N,
+                   int64_t K, int64_t lda, int64_t ldb, int64_t ldc, int64_t ldr, int trans_b, int act, cudaStream_t st);
+int gemm_swiglu_entry(const void* A, const void* Wg, const void* Wu, void* out, int64_t M, int64_t N, int64_t K,
+                      int64_t lda, int64_t ldw, int64_t ldc, int dtype, cudaStream_t st);
+int read_tc_status(unsigned int* host_out, int reset);
+
+namespace {
+int validate_gemm(const char* name, const void* A, const void* B, const void* residual, void* out, int64_t M, int64_t N,
+                  int64_t K, int64_t lda, int64_t ldb, int64_t ldc, int64_t ldr, int trans_b, int act, int dtype) {
+    if (!A || !B || !out) return fail(XG_ERR_INVALID_ARG, "%s: null A/B/out", name);
+    if (M < 0 || N < 0 || K <= 0) return fail(XG_ERR_INVALID_ARG, "%s: bad extents M=%lld N=%lld K=%lld", name, (long long)M, (long long)N, (long long)K);
+    if (dtype_size(dtype) == 0) return fail(XG_ERR_INVALID_ARG, "%s: bad dtype %d", name, dtype);
+    if (act < XG_ACT_NONE || act > XG_ACT_SIGMOID) return fail(XG_ERR_INVALID_ARG, "%s: bad activation %d", name, act);
+    if (lda < K || ldc < N || (residual && ldr < N)) return fail(XG_ERR_INVALID_ARG, "%s: leading dimension too small", name);
+    if (ldb < (trans_b ? K : N)) return fail(XG_ERR_INVALID_ARG, "%s: ldb too small", name);
+    return XG_OK;
+}
+}  // namespace
+}  // namespace xg
+
+extern "C" int xg_gemm_bias_act(const void* A, const void* B, const void* bias, const void* residual, void* out,
+                                int64_t M, int64_t N, int64_t K, int64_t lda, int64_t ldb, int64_t ldc, int64_t ldr,
+                                int trans_b, int act, int dtype, void* stream) {
+    using namespace xg;
+    int rc = validate_gemm("xg_gemm_bias_act", A, B, residual, out, M, N, K, lda, ldb, ldc, ldr, trans_b, act, dtype);
+    if (rc != XG_OK) return rc;
+    cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+    if (dtype == XG_F32) return gemm_f32_entry(A, B, bias, residual, out, M, N, K, lda, ldb, ldc, ldr, trans_b, act, st);
+    if (!trans_b)
+        return fail(XG_ERR_UNSUPPORTED, "xg_gemm_bias_act: 16-bit weights must be [N, K] (trans_b = 1); [K, N] has no kernel");
+    return gemm_tc_entry(A, B, bias, residual, out, M, N, K, lda, ldb, ldc, ldr, act, dtype, st);
+}
+
+extern "C" int xg_bgemm_bias_act(const void* A, const void* B, const void* bias, const void* residual, void* out,
+                                 int64_t batch, int64_t M, int64_t N, int64_t K, int64_t lda, int64_t ldb, int64_t ldc,
+                                 int64_t ldr, int64_t stride_a, int64_t stride_b, int64_t stride_bias, int64_t stride_r,
+                                 int64_t stride_c, int trans_b, int act, int dtype, void* stream) {
+    using namespace xg;
+    if (batch < 0) return fail(XG_ERR_INVALID_ARG, "xg_bgemm_bias_act: negative batch");
+    const int es = dtype_size(dtype);
+    if (es == 0) return fail(XG_ERR_INVALID_ARG, "xg_bgemm_bias_act: bad dtype %d", dtype);
+    for (int64_t b = 0; b < batch; ++b) {
+        const char* Ab = reinterpret_cast<const char*>(A) + b * stride_a * es;
+        const char* Bb = reinterpret_cast<const char*>(B) + b * stride_b * es;
+        const char* biasb = bias ? reinterpret_cast<const char*>(bias) + b * stride_bias * es : nullptr;
+        const char* rb = residual ? reinterpret_cast<const char*>(residual) + b * stride_r * es : nullptr;
+        char* ob = reinterpret_cast<char*>(out) + b * stride_c * es;
+        int rc = xg_gemm_bias_act(Ab, Bb, biasb, rb, ob, M, N, K, lda, ldb, ldc, ldr, trans_b, act, dtype, stream);
+        if (rc != XG_OK) return rc;
+    }
+    return XG_OK;
+}
+
+extern "C" int xg_gemm_swiglu(const void* A, const void* Wg, const void* Wu, void* out, int64_t M, int64_t N, int64_t K,
+                              int64_t lda, int64_t ldw, int64_t ldc, int dtype, void* stream) {
+    using namespace xg;
+    if (!A || !Wg || !Wu || !out) return fail(XG_ERR_INVALID_ARG, "xg_gemm_swiglu: null pointer");
+    if (M < 0 || N < 0 || K <= 0) return fail(XG_ERR_INVALID_ARG, "xg_gemm_swiglu: bad extents");
+    if (dtype != XG_BF16 && dtype != XG_F16) return fail(XG_ERR_UNSUPPORTED, "xg_gemm_swiglu: 16-bit dtypes only");
+    if (lda < K || ldw < K || ldc < N) return fail(XG_ERR_INVALID_ARG, "xg_gemm_swiglu: leading dimension too small");
+    return gemm_swiglu_entry(A, Wg, Wu, out, M, N, K, lda, ldw, ldc, dtype, reinterpret_cast<cudaStream_t>(stream));
+}
+
+extern "C" int xg_tc_status(unsigned int* status, int reset) {
+    if (!status) return xg::fail(XG_ERR_INVALID_ARG, "xg_tc_status: null output");
+    return xg::read_tc_status(status, reset);
+}

@@ -1,0 +1,155 @@
+// True-fp32 dense layer (no TF32): out = act(A @ W + bias + residual) with FFMA accumulation.
+// Shared-memory tiled SIMT kernel; used for the fp32 graphs whose tolerance (1e-5 relative) rules out
+// tensor-core TF32. W is [K, N] (trans_b = 0) or [N, K] (trans_b = 1); both tiles are stored k-major
+// in shared memory so the inner product reads float4 vectors without bank conflicts.
+#include "common.cuh"
+
+namespace xg {
+namespace {
+
+struct GemmF32Params {
+    const float* A;
+    const float* B;
+    const float* bias;
+    const float* residual;
+    float* out;
+    int64_t M, N, K, lda, ldb, ldc, ldr;
+    int trans_b;
+    int act;
+};
+
+__device__ __forceinline__ float act_f32(float v, int act) {
+    switch (act) {
+        case XG_ACT_GELU: return 0.5f * v * (1.0f + erff(v * 0.70710678118654752f));
+        case XG_ACT_RELU: return v > 0.f ? v : 0.f;
+        case XG_ACT_SILU: return v / (1.0f + expf(-v));
+        case XG_ACT_SIGMOID: return 1.0f / (1.0f + expf(-v));
+        default: return v;
+    }
+}
+
+// 256 threads; thread (ty, tx) owns a TM x TN micro-tile; BM = 16*TM, BN = 16*TN.
+template <int TM, int TN, int BK>
+__global__ void __launch_bounds__(256) gemm_f32_kernel(const GemmF32Params p) {
+    constexpr int BM = 16 * TM, BN = 16 * TN;
+    __shared__ __align__(16) float As[2][BK][BM + 4];
+    __shared__ __align__(16) float Bs[2][BK][BN + 4];
+    const int tid = threadIdx.x;
+    const int tx = tid & 15, ty = tid >> 4;
+    const int64_t m0 = (int64_t)blockIdx.y * BM, n0 = (int64_t)blockIdx.x * BN;
+
+    float acc[TM][TN];
+#pragma unroll
+    for (int i = 0; i < TM; ++i)
+#pragma unroll
+        for (int j = 0; j < TN; ++j) acc[i][j] = 0.f;
+
+    constexpr int A_ELEMS = BM * BK / 256;
+    constexpr int B_ELEMS = BN * BK / 256;
+    float a_reg[A_ELEMS], b_reg[B_ELEMS];
+
+    auto load_global = [&](int64_t k0) {
+#pragma unroll
+        for (int e = 0; e < A_ELEMS; ++e) {
+            const int idx = tid + e * 256;  // k fastest: consecutive threads read consecutive k of one row
+            const int kk = idx % BK, mm = idx / BK;
+            const int64_t gm = m0 + mm, gk = k0 + kk;
+            a_reg[e] = (gm < p.M && gk < p.K) ? p.A[gm * p.lda + gk] : 0.f;
+        }
+#pragma unroll
+        for (int e = 0; e < B_ELEMS; ++e) {
+            const int idx = tid + e * 256;
+            if (p.trans_b) {  // W[N, K]: k fastest
+                const int kk = idx % BK, nn = idx / BK;
+                const int64_t gn = n0 + nn, gk = k0 + kk;
+                b_reg[e] = (gn < p.N && gk < p.K) ? p.B[gn * p.ldb + gk] : 0.f;
+            } else {  // W[K, N]: n fastest
+                const int nn = idx % BN, kk = idx / BN;
+                const int64_t gn = n0 + nn, gk = k0 + kk;
+                b_reg[e] = (gn < p.N && gk < p.K) ? p.B[gk * p.ldb + gn] : 0.f;
+            }
+        }
+    };
+    auto store_shared = [&](int buf) {
+#pragma unroll
+        for (int e = 0; e < A_ELEMS; ++e) {
+            const int idx = tid + e * 256;
+            As[buf][idx % BK][idx / BK] = a_reg[e];
+        }
+#pragma unroll
+        for (int e = 0; e < B_ELEMS; ++e) {
+            const int idx = tid + e * 256;
+            if (p.trans_b) Bs[buf][idx % BK][idx / BK] = b_reg[e];
+            else Bs[buf][idx / BN][idx % BN] = b_reg[e];
+        }
+    };
+
+    const int64_t nk = (p.K + BK - 1) / BK;
+    load_global(0);
+    store_shared(0);
+    __syncthreads();
+    for (int64_t kt = 0; kt < nk; ++kt) {
+        const int buf = (int)(kt & 1);
+        if (kt + 1 < nk) load_global((kt + 1) * BK);
+#pragma unroll
+        for (int kk = 0; kk < BK; ++kk) {
+            float a[TM], b[TN];
+#pragma unroll
+            for (int i = 0; i < TM; i += 4) {
+                const float4 t = *reinterpret_cast<const float4*>(&As[buf][kk][ty * TM + i]);
+                a[i] = t.x; a[i + 1] = t.y; a[i + 2] = t.z; a[i + 3] = t.w;
+            }
+#pragma unroll
+            for (int j = 0; j < TN; j += 4) {
+                const float4 t = *reinterpret_cast<const float4*>(&Bs[buf][kk][tx * TN + j]);
+                b[j] = t.x; b[j + 1] = t.y; b[j + 2] = t.z; b[j + 3] = t.w;
+            }
+#pragma unroll
+            for (int i = 0; i < TM; ++i)
+#pragma unroll
+                for (int j = 0; j < TN; ++j) acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
+        }
+        if (kt + 1 < nk) {
+            store_shared(buf ^ 1);
+            __syncthreads();
+        }
+    }
+
+#pragma unroll
+    for (int i = 0; i < TM; ++i) {
+        const int64_t gm = m0 + ty * TM + i;
+        if (gm >= p.M) continue;
+#pragma unroll
+        for (int j = 0; j < TN; ++j) {
+            const int64_t gn = n0 + tx * TN + j;
+            if (gn >= p.N) continue;
+            float v = acc[i][j];
+            if (p.bias) v += p.bias[gn];
+            if (p.residual) v += p.residual[gm * p.ldr + gn];
+            p.out[gm * p.ldc + gn] = act_f32(v, p.act);
+        }
+    }
+}
+
+}  // namespace
+
+int gemm_f32_entry(const void* A, const void* B, const void* bias, const void* residual, void* out, int64_t M, int64_t N,
+                   int64_t K, int64_t lda, int64_t ldb, int64_t ldc, int64_t ldr, int trans_b, int act, cudaStream_t st) {
+    if (M * N == 0) return XG_OK;
+    GemmF32Params p{reinterpret_cast<const float*>(A), reinterpret_cast<const float*>(B), reinterpret_cast<const float*>(bias),
+                    reinterpret_cast<const float*>(residual), reinterpret_cast<float*>(out), M, N, K, lda, ldb, ldc, ldr,
+                    trans_b, act};
+    const int64_t big_tiles = ((M + 127) / 128) * ((N + 127) / 128);
+    if (big_tiles >= 2LL * num_sms()) {
+        dim3 grid((unsigned)((N + 127) / 128), (unsigned)((M + 127) / 128));
+        if ((M + 127) / 128 > 65535) return fail(XG_ERR_TOO_LARGE, "xg_gemm_bias_act(f32): M too large");
+        gemm_f32_kernel<8, 8, 16><<<grid, 256, 0, st>>>(p);
+    } else {
+        dim3 grid((unsigned)((N + 63) / 64), (unsigned)((M + 63) / 64));
+        if ((M + 63) / 64 > 65535) return fail(XG_ERR_TOO_LARGE, "xg_gemm_bias_act(f32): M too large");
+        gemm_f32_kernel<4, 4, 16><<<grid, 256, 0, st>>>(p);
+    }
+    return check_launch("xg_gemm_bias_act(f32)");
+}
+
+}  // namespace xg

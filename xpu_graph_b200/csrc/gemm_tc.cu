@@ -1,0 +1,451 @@
+// Dense layer on the 5th-generation tensor cores: out = act(A @ W^T + bias + residual), 16-bit inputs,
+// fp32 accumulation in TMEM, epilogue fused into the store.
+//
+// Persistent kernel, one CTA per SM, warp-specialised:
+//   warp 0      : TMA producer  - streams [128 x 64] A tiles and [BN x 64] W tiles (128-byte swizzle)
+//                 through a STAGES-deep shared-memory ring, one mbarrier pair (full/empty) per stage;
+//   warp 1      : MMA issuer    - one elected thread issues tcgen05.mma (128 x BN x 16) straight from
+//                 shared memory into one of two TMEM accumulator buffers; tcgen05.commit releases the
+//                 ring stage and, after the last k-block, publishes the accumulator;
+//   warps 2..5  : epilogue      - tcgen05.ld the accumulator (each warp owns its 32-lane TMEM quadrant),
+//                 add bias / residual, apply the activation, convert and store, then hand the TMEM
+//                 buffer back. The second accumulator buffer lets tile i's epilogue overlap tile i+1's
+//                 main loop.
+// Tiles are visited in groups of 16 row-blocks so that the ~148 tiles in flight share A and W tiles in L2.
+// Every TMA load is issued by the CTA that consumes it (no cluster multicast anywhere).
+#include "common.cuh"
+#include "sm100_ptx.cuh"
+
+#include <mutex>
+
+namespace xg {
+
+// ---- tensor-map helpers (host) ----------------------------------------------------------------
+PFN_encodeTiled get_encode_tiled() {
+    static PFN_encodeTiled fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, []() {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) == cudaSuccess &&
+            qres == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<PFN_encodeTiled>(p);
+        else
+            cudaGetLastError();
+    });
+    return fn;
+}
+
+bool make_tmap_2d_16bit(CUtensorMap* out, const void* base, uint64_t rows, uint64_t cols, uint64_t ld,
+                        uint32_t box_rows, uint32_t box_cols, bool is_bf16) {
+    PFN_encodeTiled enc = get_encode_tiled();
+    if (!enc) return false;
+    cuuint64_t dims[2] = {cols, rows};
+    cuuint64_t strides[1] = {ld * 2};
+    cuuint32_t box[2] = {box_cols, box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = enc(out, is_bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2,
+                     const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                     CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS;
+}
+
+// Device-side status word: non-zero after a bounded wait expired inside a tcgen05 kernel.
+__device__ unsigned int g_tc_status[4];
+
+namespace {
+
+constexpr int BM = 128;
+constexpr int BK = 64;       // 64 x 16-bit = one 128-byte swizzled row
+constexpr int UMMA_K = 16;
+constexpr int kGemmThreads = 192;
+constexpr int GROUP_M = 16;
+
+struct GemmParams {
+    void* out;
+    const void* bias;
+    const void* residual;
+    int64_t M, N, K, ldc, ldr;
+    int act;
+    int vec_ok;       // out (and residual) rows are 16-byte addressable
+    int bias_vec_ok;  // bias pointer 16-byte aligned
+    int num_m_blocks, num_n_blocks, num_k_blocks;
+};
+
+template <int BN>
+struct GemmCfg {
+    static constexpr int A_BYTES = BM * BK * 2;
+    static constexpr int B_BYTES = BN * BK * 2;
+    static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+    static constexpr int STAGES = (BN == 256) ? 4 : (BN == 128 ? 6 : 8);
+    static constexpr int TMEM_COLS = 2 * BN;  // two accumulator buffers; 128, 256 or 512 (powers of two)
+    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
+};
+
+__device__ __forceinline__ float apply_act(float v, int act) {
+    switch (act) {
+        case XG_ACT_GELU: return 0.5f * v * (1.0f + erff(v * 0.70710678118654752f));
+        case XG_ACT_RELU: return v > 0.f ? v : 0.f;
+        case XG_ACT_SILU: return v / (1.0f + __expf(-v));
+        case XG_ACT_SIGMOID: return 1.0f / (1.0f + __expf(-v));
+        default: return v;
+    }
+}
+
+__device__ __forceinline__ void tile_coords(int t, int num_m, int num_n, int& mb, int& nb) {
+    const int per_group = GROUP_M * num_n;
+    const int g = t / per_group;
+    const int first_m = g * GROUP_M;
+    const int gsz = (num_m - first_m) < GROUP_M ? (num_m - first_m) : GROUP_M;
+    const int in_g = t - g * per_group;
+    mb = first_m + in_g % gsz;
+    nb = in_g / gsz;
+}
+
+// SWIGLU: the W tile is [gate rows ; up rows] (BN/2 each, two TMA loads), so accumulator columns
+// [0, BN/2) hold A @ Wg^T and [BN/2, BN) hold A @ Wu^T; the epilogue writes silu(gate) * up, BN/2 wide.
+template <typename T, int BN, bool SWIGLU>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+               const __grid_constant__ CUtensorMap tmap_b2, const GemmParams p) {
+    constexpr int OUT_BN = SWIGLU ? BN / 2 : BN;  // output columns per tile
+    using Cfg = GemmCfg<BN>;
+    constexpr int STAGES = Cfg::STAGES;
+    extern __shared__ uint8_t smem_raw[];
+    // 1024-byte alignment: required by the 128-byte swizzle pattern shared by TMA and the MMA descriptors.
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint8_t* smem_a = smem;
+    uint8_t* smem_b = smem + STAGES * Cfg::A_BYTES;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * Cfg::STAGE_BYTES);
+    uint64_t* full_bar = bars;                    // [STAGES]
+    uint64_t* empty_bar = bars + STAGES;          // [STAGES]
+    uint64_t* tmem_full = bars + 2 * STAGES;      // [2]
+    uint64_t* tmem_empty = bars + 2 * STAGES + 2; // [2]
+    uint64_t* drain_bar = bars + 2 * STAGES + 4;  // [1]
+    uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 5);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_base_slot + 1);
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            ptx::mbar_init(&full_bar[s], 1);
+            ptx::mbar_init(&empty_bar[s], 1);
+        }
+        for (int a = 0; a < 2; ++a) {
+            ptx::mbar_init(&tmem_full[a], 1);
+            ptx::mbar_init(&tmem_empty[a], 4);
+        }
+        ptx::mbar_init(drain_bar, 1);
+        *abort_flag = 0;
+        ptx::fence_mbar_init();
+        ptx::fence_proxy_async();
+    }
+    if (warp == 1) ptx::tmem_alloc(tmem_base_slot, Cfg::TMEM_COLS);
+    ptx::tc_fence_before();
+    __syncthreads();
+    ptx::tc_fence_after();
+    const uint32_t tmem_base = *tmem_base_slot;
+
+    const int num_tiles = p.num_m_blocks * p.num_n_blocks;
+    const int nkb = p.num_k_blocks;
+
+    if (warp == 0) {
+        // ------------------------------ TMA producer ------------------------------
+        if (ptx::elect_one()) {
+            ptx::prefetch_tensormap(&tmap_a);
+            ptx::prefetch_tensormap(&tmap_b);
+            if (SWIGLU) ptx::prefetch_tensormap(&tmap_b2);
+            int stage = 0;
+            uint32_t phase = 0;
+            uint32_t armed = 0;                 // stages with a load this thread issued
+            uint32_t armed_phase = 0;           // parity of that load's phase, one bit per stage
+            bool ok = true;
+            for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+                int mb, nb;
+                tile_coords(t, p.num_m_blocks, p.num_n_blocks, mb, nb);
+                for (int kb = 0; kb < nkb; ++kb) {
+                    if (!ptx::mbar_wait_bounded(&empty_bar[stage], phase ^ 1u, abort_flag)) { ok = false; break; }
+                    ptx::mbar_arrive_expect_tx(&full_bar[stage], Cfg::STAGE_BYTES);
+                    ptx::tma_load_2d(smem_a + stage * Cfg::A_BYTES, &tmap_a, &full_bar[stage], kb * BK, mb * BM);
+                    if (SWIGLU) {
+                        ptx::tma_load_2d(smem_b + stage * Cfg::B_BYTES, &tmap_b, &full_bar[stage], kb * BK, nb * OUT_BN);
+                        ptx::tma_load_2d(smem_b + stage * Cfg::B_BYTES + Cfg::B_BYTES / 2, &tmap_b2, &full_bar[stage],
+                                         kb * BK, nb * OUT_BN);
+                    } else {
+                        ptx::tma_load_2d(smem_b + stage * Cfg::B_BYTES, &tmap_b, &full_bar[stage], kb * BK, nb * BN);
+                    }
+                    armed |= 1u << stage;
+                    armed_phase = (armed_phase & ~(1u << stage)) | (phase << stage);
+                    if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+                }
+            }
+            if (!ok) {
+                // Unwinding: let this thread's own copies land before the CTA gives up its shared memory.
+                atomicOr(&g_tc_status[0], 1u);
+                for (int s = 0; s < STAGES; ++s) {
+                    if (armed & (1u << s)) {
+                        const uint64_t t0 = ptx::globaltimer_ns();
+                        while (!ptx::mbar_try_wait(&full_bar[s], (armed_phase >> s) & 1u)) {
+                            if (ptx::globaltimer_ns() - t0 > ptx::kWaitLimitNs) break;
+                        }
+                    }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------ MMA issuer --------------------------------
+        if (ptx::elect_one()) {
+            constexpr uint32_t idesc = ptx::make_idesc_f16(sizeof(T) == 2 && std::is_same<T, __nv_bfloat16>::value ? 1 : 0, BM, BN);
+            int stage = 0;
+            uint32_t phase = 0;
+            int acc = 0;
+            uint32_t acc_phase = 0;
+            bool ok = true;
+            for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+                if (!ptx::mbar_wait_bounded(&tmem_empty[acc], acc_phase ^ 1u, abort_flag)) { ok = false; break; }
+                ptx::tc_fence_after();
+                const uint32_t tmem_d = tmem_base + (uint32_t)(acc * BN);
+                for (int kb = 0; kb < nkb; ++kb) {
+                    if (!ptx::mbar_wait_bounded(&full_bar[stage], phase, abort_flag)) { ok = false; break; }
+                    ptx::tc_fence_after();
+                    const uint32_t a_addr = ptx::smem_u32(smem_a + stage * Cfg::A_BYTES);
+                    const uint32_t b_addr = ptx::smem_u32(smem_b + stage * Cfg::B_BYTES);
+                    const uint64_t da = ptx::make_kmajor_sw128_desc(a_addr);
+                    const uint64_t db = ptx::make_kmajor_sw128_desc(b_addr);
+#pragma unroll
+                    for (int k = 0; k < BK / UMMA_K; ++k) {
+                        // +32 bytes per 16-element K step, in the descriptor's 16-byte address units
+                        ptx::mma_f16_ss(tmem_d, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc, (kb | k) != 0 ? 1u : 0u);
+                    }
+                    ptx::tc_commit(&empty_bar[stage]);  // stage reusable once these MMAs have read it
+                    if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+                }
+                if (!ok) break;
+                ptx::tc_commit(&tmem_full[acc]);  // accumulator complete
+                if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
+            }
+            if (!ok) {
+                atomicOr(&g_tc_status[0], 2u);
+                // Let the MMAs already issued finish before TMEM is released.
+                ptx::tc_commit(drain_bar);
+                const uint64_t t0 = ptx::globaltimer_ns();
+                while (!ptx::mbar_try_wait(drain_bar, 0)) {
+                    if (ptx::globaltimer_ns() - t0 > ptx::kWaitLimitNs) break;
+                }
+            }
+        }
+    } else {
+        // ------------------------------ epilogue ----------------------------------
+        const int quad = warp & 3;  // TMEM lanes [32*quad, 32*quad + 32) belong to this warp
+        int acc = 0;
+        uint32_t acc_phase = 0;
+        bool ok = true;
+        T* out = reinterpret_cast<T*>(p.out);
+        const T* bias = reinterpret_cast<const T*>(p.bias);
+        const T* resid = reinterpret_cast<const T*>(p.residual);
+        for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+            int mb, nb;
+            tile_coords(t, p.num_m_blocks, p.num_n_blocks, mb, nb);
+            if (!ptx::mbar_wait_bounded(&tmem_full[acc], acc_phase, abort_flag)) { ok = false; break; }
+            ptx::tc_fence_after();
+            const int64_t row = (int64_t)mb * BM + quad * 32 + lane;
+            const bool row_ok = row < p.M;
+#pragma unroll 1
+            for (int c = 0; c < OUT_BN / 32; ++c) {
+                const int64_t col0 = (int64_t)nb * OUT_BN + c * 32;
+                if (col0 >= p.N) break;  // warp-uniform
+                uint32_t r[32];
+                const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(acc * BN + c * 32);
+                ptx::tmem_ld_32x32(taddr, r);
+                ptx::tmem_ld_wait();
+                float v[32];
+#pragma unroll
+                for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+                if (SWIGLU) {
+                    ptx::tmem_ld_32x32(taddr + (uint32_t)(BN / 2), r);
+                    ptx::tmem_ld_wait();
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) v[i] = (v[i] / (1.0f + __expf(-v[i]))) * __uint_as_float(r[i]);
+                }
+                const bool full = (col0 + 32 <= p.N);
+                if (bias != nullptr) {
+                    if (full && p.bias_vec_ok) {
+#pragma unroll
+                        for (int i = 0; i < 32; i += 8) {
+                            const Vec16<T> bv = ld16(bias + col0 + i);
+#pragma unroll
+                            for (int j = 0; j < 8; ++j) v[i + j] += Cvt<T>::to_f(bv.v[j]);
+                        }
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < 32; ++i)
+                            if (col0 + i < p.N) v[i] += Cvt<T>::to_f(bias[col0 + i]);
+                    }
+                }
+                if (row_ok) {
+                    if (full && p.vec_ok) {
+                        if (resid != nullptr) {
+                            const T* rr = resid + row * p.ldr + col0;
+#pragma unroll
+                            for (int i = 0; i < 32; i += 8) {
+                                const Vec16<T> rv = ld16_stream(rr + i);
+#pragma unroll
+                                for (int j = 0; j < 8; ++j) v[i + j] += Cvt<T>::to_f(rv.v[j]);
+                            }
+                        }
+                        T* orow = out + row * p.ldc + col0;
+#pragma unroll
+                        for (int i = 0; i < 32; i += 8) {
+                            Vec16<T> ov;
+#pragma unroll
+                            for (int j = 0; j < 8; ++j) ov.v[j] = Cvt<T>::from_f(apply_act(v[i + j], p.act));
+                            st16(orow + i, ov);
+                        }
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) {
+                            if (col0 + i < p.N) {
+                                float a = v[i];
+                                if (resid != nullptr) a += Cvt<T>::to_f(resid[row * p.ldr + col0 + i]);
+                                out[row * p.ldc + col0 + i] = Cvt<T>::from_f(apply_act(a, p.act));
+                            }
+                        }
+                    }
+                }
+            }
+            // All of this warp's TMEM reads are complete (wait::ld above): return the buffer.
+            ptx::tc_fence_before();
+            __syncwarp();
+            if (lane == 0) ptx::mbar_arrive(&tmem_empty[acc]);
+            if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
+        }
+        if (!ok && lane == 0) atomicOr(&g_tc_status[0], 4u);
+    }
+
+    // ------------------------------ teardown --------------------------------------
+    ptx::tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        ptx::tc_fence_after();
+        ptx::tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
+    }
+}
+
+template <typename T, int BN, bool SWIGLU>
+int launch_gemm_tc(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tb2, const GemmParams& p,
+                   cudaStream_t st) {
+    using Cfg = GemmCfg<BN>;
+    auto kern = gemm_tc_kernel<T, BN, SWIGLU>;
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
+    if (e != cudaSuccess) {
+        cudaGetLastError();
+        return fail(XG_ERR_LAUNCH, "xg_gemm_bias_act: cannot reserve %d bytes of shared memory: %s", Cfg::SMEM_BYTES,
+                    cudaGetErrorString(e));
+    }
+    const int tiles = p.num_m_blocks * p.num_n_blocks;
+    const int grid = tiles < num_sms() ? tiles : num_sms();
+    kern<<<grid, kGemmThreads, Cfg::SMEM_BYTES, st>>>(ta, tb, tb2, p);
+    return check_launch("xg_gemm_bias_act");
+}
+
+template <typename T>
+int gemm_tc_dispatch(const void* A, const void* B, const void* bias, const void* residual, void* out, int64_t M,
+                     int64_t N, int64_t K, int64_t lda, int64_t ldb, int64_t ldc, int64_t ldr, int act,
+                     cudaStream_t st) {
+    constexpr bool is_bf16 = std::is_same<T, __nv_bfloat16>::value;
+    // Tile width: the widest tile that still gives every SM work.
+    const int64_t mblk = (M + BM - 1) / BM;
+    const int sms = num_sms();
+    int bn = 256;
+    if (mblk * ((N + 255) / 256) < sms) bn = 128;
+    if (bn == 128 && mblk * ((N + 127) / 128) < sms) bn = 64;
+
+    CUtensorMap ta, tb;
+    if (!make_tmap_2d_16bit(&ta, A, (uint64_t)M, (uint64_t)K, (uint64_t)lda, BM, BK, is_bf16) ||
+        !make_tmap_2d_16bit(&tb, B, (uint64_t)N, (uint64_t)K, (uint64_t)ldb, (uint32_t)bn, BK, is_bf16))
+        return fail(XG_ERR_UNSUPPORTED, "xg_gemm_bias_act: tensor-map encoding failed (M=%lld N=%lld K=%lld lda=%lld ldb=%lld)",
+                    (long long)M, (long long)N, (long long)K, (long long)lda, (long long)ldb);
+    GemmParams p;
+    p.out = out;
+    p.bias = bias;
+    p.residual = residual;
+    p.M = M; p.N = N; p.K = K; p.ldc = ldc; p.ldr = ldr;
+    p.act = act;
+    p.vec_ok = (ldc % 8 == 0) && aligned16(out) && (!residual || (ldr % 8 == 0 && aligned16(residual)));
+    p.bias_vec_ok = bias ? aligned16(bias) : 0;
+    p.num_m_blocks = (int)mblk;
+    p.num_n_blocks = (int)((N + bn - 1) / bn);
+    p.num_k_blocks = (int)((K + BK - 1) / BK);
+    switch (bn) {
+        case 256: return launch_gemm_tc<T, 256, false>(ta, tb, tb, p, st);
+        case 128: return launch_gemm_tc<T, 128, false>(ta, tb, tb, p, st);
+        default: return launch_gemm_tc<T, 64, false>(ta, tb, tb, p, st);
+    }
+}
+
+template <typename T>
+int gemm_swiglu_dispatch(const void* A, const void* Wg, const void* Wu, void* out, int64_t M, int64_t N, int64_t K,
+                         int64_t lda, int64_t ldw, int64_t ldc, cudaStream_t st) {
+    constexpr bool is_bf16 = std::is_same<T, __nv_bfloat16>::value;
+    CUtensorMap ta, tg, tu;
+    if (!make_tmap_2d_16bit(&ta, A, (uint64_t)M, (uint64_t)K, (uint64_t)lda, BM, BK, is_bf16) ||
+        !make_tmap_2d_16bit(&tg, Wg, (uint64_t)N, (uint64_t)K, (uint64_t)ldw, 128, BK, is_bf16) ||
+        !make_tmap_2d_16bit(&tu, Wu, (uint64_t)N, (uint64_t)K, (uint64_t)ldw, 128, BK, is_bf16))
+        return fail(XG_ERR_UNSUPPORTED, "xg_gemm_swiglu: tensor-map encoding failed");
+    GemmParams p;
+    p.out = out;
+    p.bias = nullptr;
+    p.residual = nullptr;
+    p.M = M; p.N = N; p.K = K; p.ldc = ldc; p.ldr = 0;
+    p.act = XG_ACT_NONE;
+    p.vec_ok = (ldc % 8 == 0) && aligned16(out);
+    p.bias_vec_ok = 0;
+    p.num_m_blocks = (int)((M + BM - 1) / BM);
+    p.num_n_blocks = (int)((N + 127) / 128);
+    p.num_k_blocks = (int)((K + BK - 1) / BK);
+    return launch_gemm_tc<T, 256, true>(ta, tg, tu, p, st);
+}
+
+}  // namespace
+
+// Entry used by xg_gemm_bias_act for 16-bit dtypes with W given as [N, K] (trans_b = 1).
+int gemm_tc_entry(const void* A, const void* B, const void* bias, const void* residual, void* out, int64_t M, int64_t N,
+                  int64_t K, int64_t lda, int64_t ldb, int64_t ldc, int64_t ldr, int act, int dtype, cudaStream_t st) {
+    if (!aligned16(A) || !aligned16(B) || lda % 8 != 0 || ldb % 8 != 0)
+        return fail(XG_ERR_UNSUPPORTED, "xg_gemm_bias_act: A/W must be 16-byte aligned with row strides multiple of 8 elements");
+    if (M * N == 0) return XG_OK;
+    if (M > (int64_t)BM * 0x7fffff || N > (int64_t)64 * 0x7fffff || K > 0x7fffffff)
+        return fail(XG_ERR_TOO_LARGE, "xg_gemm_bias_act: extent too large");
+    if (dtype == XG_BF16)
+        return gemm_tc_dispatch<__nv_bfloat16>(A, B, bias, residual, out, M, N, K, lda, ldb, ldc, ldr, act, st);
+    return gemm_tc_dispatch<__half>(A, B, bias, residual, out, M, N, K, lda, ldb, ldc, ldr, act, st);
+}
+
+int gemm_swiglu_entry(const void* A, const void* Wg, const void* Wu, void* out, int64_t M, int64_t N, int64_t K,
+                      int64_t lda, int64_t ldw, int64_t ldc, int dtype, cudaStream_t st) {
+    if (!aligned16(A) || !aligned16(Wg) || !aligned16(Wu) || lda % 8 != 0 || ldw % 8 != 0)
+        return fail(XG_ERR_UNSUPPORTED, "xg_gemm_swiglu: A/W must be 16-byte aligned with row strides multiple of 8 elements");
+    if (M * N == 0) return XG_OK;
+    if (M > (int64_t)BM * 0x7fffff || N > (int64_t)64 * 0x7fffff || K > 0x7fffffff)
+        return fail(XG_ERR_TOO_LARGE, "xg_gemm_swiglu: extent too large");
+    if (dtype == XG_BF16) return gemm_swiglu_dispatch<__nv_bfloat16>(A, Wg, Wu, out, M, N, K, lda, ldw, ldc, st);
+    return gemm_swiglu_dispatch<__half>(A, Wg, Wu, out, M, N, K, lda, ldw, ldc, st);
+}
+
+int read_tc_status(unsigned int* host_out, int reset) {
+    unsigned int v[4] = {0, 0, 0, 0};
+    if (cudaMemcpyFromSymbol(v, g_tc_status, sizeof(v)) != cudaSuccess) {
+        cudaGetLastError();
+        return fail(XG_ERR_DEVICE, "xg_tc_status: cannot read device status");
+    }
+    *host_out = v[0];
+    if (reset && v[0] != 0) {
+        unsigned int z[4] = {0, 0, 0, 0};
+        cudaMemcpyToSymbol(g_tc_status, z, sizeof(z));
+    }
+    return XG_OK;
+}
+
+}  // namespace xg

@@ -1,0 +1,294 @@
+// RMSNorm / LayerNorm with optional fused residual add (and "sum" second output).
+//
+// HBM-bound: every element of x (and residual) is read once and y (and sum) written once; the
+// row lives in registers between the reduction and the normalisation. One warp owns a row when
+// it fits (hidden <= 32 lanes x V 16-byte vectors); wider rows are split over WPR warps of one
+// CTA with a shared-memory exchange of the per-warp partial sums. All loads/stores are 16 bytes
+// and coalesced (consecutive lanes touch consecutive vectors); reductions are warp shuffles.
+#include "common.cuh"
+
+namespace xg {
+namespace {
+
+struct NormParams {
+    const void* x;
+    const void* res;
+    const void* w;
+    const void* b;
+    void* y;
+    void* sum_out;
+    int64_t rows;
+    int64_t hidden;
+    int64_t x_stride;
+    int64_t res_stride;
+    float eps;
+    int w_is_f32;
+};
+
+// Load the EPV affine coefficients that match vector `vi` as floats.
+template <typename T>
+__device__ __forceinline__ void load_coef(const void* p, int w_is_f32, int64_t elem_off, float (&out)[Vec16<T>::N]) {
+    constexpr int EPV = Vec16<T>::N;
+    if (w_is_f32 || sizeof(T) == 4) {
+        const float* fp = reinterpret_cast<const float*>(p) + elem_off;
+#pragma unroll
+        for (int i = 0; i < EPV; i += 4) {
+            float4 f = *reinterpret_cast<const float4*>(fp + i);
+            out[i] = f.x;
+            out[i + 1] = f.y;
+            out[i + 2] = f.z;
+            out[i + 3] = f.w;
+        }
+    } else {
+        Vec16<T> wv = ld16(reinterpret_cast<const T*>(p) + elem_off);
+#pragma unroll
+        for (int i = 0; i < EPV; ++i) out[i] = Cvt<T>::to_f(wv.v[i]);
+    }
+}
+
+// V = 16-byte vectors per lane, WPR = warps per row. WPR == 1: 4 independent rows per CTA.
+template <typename T, int V, int WPR, bool LN>
+__global__ void __launch_bounds__((WPR == 1 ? 4 : WPR) * 32) norm_vec_kernel(const NormParams p) {
+    constexpr int EPV = Vec16<T>::N;
+    constexpr int WARPS = (WPR == 1 ? 4 : WPR);
+    const int lane = threadIdx.x & 31;
+    const int warp = threadIdx.x >> 5;
+    int64_t row;
+    int wig;
+    if (WPR == 1) {
+        row = (int64_t)blockIdx.x * WARPS + warp;
+        wig = 0;
+        if (row >= p.rows) return;  // no block-wide barrier on this path
+    } else {
+        row = blockIdx.x;
+        wig = warp;
+    }
+    __shared__ float red_a[WARPS];
+    __shared__ float red_b[WARPS];
+
+    const int nvec = (int)(p.hidden / EPV);
+    const T* xr = reinterpret_cast<const T*>(p.x) + row * p.x_stride;
+    Vec16<T> s[V];
+#pragma unroll
+    for (int v = 0; v < V; ++v) {
+        const int vi = (v * WPR + wig) * 32 + lane;
+        if (vi < nvec) s[v] = ld16_stream(xr + (int64_t)vi * EPV);
+    }
+    if (p.res != nullptr) {
+        const T* rr = reinterpret_cast<const T*>(p.res) + row * p.res_stride;
+        Vec16<T> r[V];
+#pragma unroll
+        for (int v = 0; v < V; ++v) {
+            const int vi = (v * WPR + wig) * 32 + lane;
+            if (vi < nvec) r[v] = ld16_stream(rr + (int64_t)vi * EPV);
+        }
+#pragma unroll
+        for (int v = 0; v < V; ++v) {
+            const int vi = (v * WPR + wig) * 32 + lane;
+            if (vi < nvec) {
+#pragma unroll
+                for (int i = 0; i < EPV; ++i)
+                    s[v].v[i] = Cvt<T>::from_f(Cvt<T>::to_f(s[v].v[i]) + Cvt<T>::to_f(r[v].v[i]));
+            }
+        }
+        if (p.sum_out != nullptr) {
+            T* so = reinterpret_cast<T*>(p.sum_out) + row * p.hidden;
+#pragma unroll
+            for (int v = 0; v < V; ++v) {
+                const int vi = (v * WPR + wig) * 32 + lane;
+                if (vi < nvec) st16(so + (int64_t)vi * EPV, s[v]);
+            }
+        }
+    }
+
+    const float inv_h = 1.0f / (float)p.hidden;
+    float mean = 0.f;
+    if (LN) {
+        float a = 0.f;
+#pragma unroll
+        for (int v = 0; v < V; ++v) {
+            const int vi = (v * WPR + wig) * 32 + lane;
+            if (vi < nvec) {
+#pragma unroll
+                for (int i = 0; i < EPV; ++i) a += Cvt<T>::to_f(s[v].v[i]);
+            }
+        }
+        a = warp_sum(a);
+        if (WPR > 1) {
+            if (lane == 0) red_a[wig] = a;
+            __syncthreads();
+            a = 0.f;
+#pragma unroll
+            for (int w = 0; w < WPR; ++w) a += red_a[w];
+        }
+        mean = a * inv_h;
+    }
+    float q = 0.f;
+#pragma unroll
+    for (int v = 0; v < V; ++v) {
+        const int vi = (v * WPR + wig) * 32 + lane;
+        if (vi < nvec) {
+#pragma unroll
+            for (int i = 0; i < EPV; ++i) {
+                const float d = Cvt<T>::to_f(s[v].v[i]) - mean;
+                q += d * d;
+            }
+        }
+    }
+    q = warp_sum(q);
+    if (WPR > 1) {
+        if (lane == 0) red_b[wig] = q;
+        __syncthreads();
+        q = 0.f;
+#pragma unroll
+        for (int w = 0; w < WPR; ++w) q += red_b[w];
+    }
+    const float rstd = rsqrtf(q * inv_h + p.eps);
+
+    T* yr = reinterpret_cast<T*>(p.y) + row * p.hidden;
+#pragma unroll
+    for (int v = 0; v < V; ++v) {
+        const int vi = (v * WPR + wig) * 32 + lane;
+        if (vi < nvec) {
+            float wf[EPV];
+            load_coef<T>(p.w, p.w_is_f32, (int64_t)vi * EPV, wf);
+            Vec16<T> o;
+            if (LN) {
+                float bf[EPV];
+                load_coef<T>(p.b, p.w_is_f32, (int64_t)vi * EPV, bf);
+#pragma unroll
+                for (int i = 0; i < EPV; ++i)
+                    o.v[i] = Cvt<T>::from_f((Cvt<T>::to_f(s[v].v[i]) - mean) * rstd * wf[i] + bf[i]);
+            } else {
+#pragma unroll
+                for (int i = 0; i < EPV; ++i) o.v[i] = Cvt<T>::from_f(Cvt<T>::to_f(s[v].v[i]) * rstd * wf[i]);
+            }
+            st16(yr + (int64_t)vi * EPV, o);
+        }
+    }
+}
+
+// Any hidden size / alignment: one 128-thread CTA per row, scalar accesses, the row re-read from
+// L1/L2 for each pass. Only ragged or unaligned shapes land here.
+template <typename T, bool LN>
+__global__ void __launch_bounds__(128) norm_generic_kernel(const NormParams p) {
+    __shared__ float red[4];
+    __shared__ float bcast;
+    const int64_t row = blockIdx.x;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const T* xr = reinterpret_cast<const T*>(p.x) + row * p.x_stride;
+    const T* rr = p.res ? reinterpret_cast<const T*>(p.res) + row * p.res_stride : nullptr;
+    T* so = (p.res && p.sum_out) ? reinterpret_cast<T*>(p.sum_out) + row * p.hidden : nullptr;
+    auto sval = [&](int64_t i) -> float {
+        float a = Cvt<T>::to_f(xr[i]);
+        if (rr) a = Cvt<T>::to_f(Cvt<T>::from_f(a + Cvt<T>::to_f(rr[i])));
+        return a;
+    };
+    auto block_sum = [&](float a) -> float {
+        a = warp_sum(a);
+        __syncthreads();  // protects red/bcast reuse between the two reductions
+        if (lane == 0) red[warp] = a;
+        __syncthreads();
+        if (threadIdx.x == 0) bcast = red[0] + red[1] + red[2] + red[3];
+        __syncthreads();
+        return bcast;
+    };
+    const float inv_h = 1.0f / (float)p.hidden;
+    float mean = 0.f;
+    if (LN) {
+        float a = 0.f;
+        for (int64_t i = threadIdx.x; i < p.hidden; i += 128) a += sval(i);
+        mean = block_sum(a) * inv_h;
+    }
+    float q = 0.f;
+    for (int64_t i = threadIdx.x; i < p.hidden; i += 128) {
+        const float d = sval(i) - mean;
+        q += d * d;
+    }
+    const float rstd = rsqrtf(block_sum(q) * inv_h + p.eps);
+    T* yr = reinterpret_cast<T*>(p.y) + row * p.hidden;
+    for (int64_t i = threadIdx.x; i < p.hidden; i += 128) {
+        const float sv = sval(i);
+        if (so) so[i] = Cvt<T>::from_f(sv);
+        const float wf = (p.w_is_f32 || sizeof(T) == 4) ? reinterpret_cast<const float*>(p.w)[i]
+                                                        : Cvt<T>::to_f(reinterpret_cast<const T*>(p.w)[i]);
+        float o;
+        if (LN) {
+            const float bf = (p.w_is_f32 || sizeof(T) == 4) ? reinterpret_cast<const float*>(p.b)[i]
+                                                            : Cvt<T>::to_f(reinterpret_cast<const T*>(p.b)[i]);
+            o = (sv - mean) * rstd * wf + bf;
+        } else {
+            o = sv * rstd * wf;
+        }
+        yr[i] = Cvt<T>::from_f(o);
+    }
+}
+
+template <typename T, int V, int WPR, bool LN>
+void launch_vec(const NormParams& p, cudaStream_t st) {
+    constexpr int WARPS = (WPR == 1 ? 4 : WPR);
+    const int64_t grid = (WPR == 1) ? (p.rows + WARPS - 1) / WARPS : p.rows;
+    norm_vec_kernel<T, V, WPR, LN><<<(unsigned)grid, WARPS * 32, 0, st>>>(p);
+}
+
+template <typename T, bool LN>
+int launch_norm(const NormParams& p, cudaStream_t st, const char* name) {
+    constexpr int EPV = Vec16<T>::N;
+    if (p.rows > 0x7fffffffLL) return fail(XG_ERR_TOO_LARGE, "%s: rows %lld exceed 2^31-1", name, (long long)p.rows);
+    const bool w_f32 = p.w_is_f32 || sizeof(T) == 4;
+    bool vec_ok = (p.hidden % EPV == 0) && aligned16(p.x) && (p.x_stride % EPV == 0) && aligned16(p.y) &&
+                  aligned16(p.w) && (!LN || aligned16(p.b)) &&
+                  (!p.res || (aligned16(p.res) && p.res_stride % EPV == 0)) && (!p.sum_out || aligned16(p.sum_out));
+    (void)w_f32;
+    const int64_t nvec = p.hidden / EPV;
+    if (vec_ok && nvec <= 32 * 8 * 16) {
+        if (nvec <= 32 * 2) launch_vec<T, 2, 1, LN>(p, st);
+        else if (nvec <= 32 * 4) launch_vec<T, 4, 1, LN>(p, st);
+        else if (nvec <= 32 * 4 * 2) launch_vec<T, 4, 2, LN>(p, st);
+        else if (nvec <= 32 * 4 * 4) launch_vec<T, 4, 4, LN>(p, st);
+        else if (nvec <= 32 * 8 * 4) launch_vec<T, 8, 4, LN>(p, st);
+        else if (nvec <= 32 * 8 * 8) launch_vec<T, 8, 8, LN>(p, st);
+        else launch_vec<T, 8, 16, LN>(p, st);
+    } else {
+        norm_generic_kernel<T, LN><<<(unsigned)p.rows, 128, 0, st>>>(p);
+    }
+    return check_launch(name);
+}
+
+template <bool LN>
+int norm_entry(const char* name, const void* x, const void* residual, const void* weight, const void* bias, void* y,
+               void* sum_out, int64_t rows, int64_t hidden, int64_t x_row_stride, int64_t res_row_stride, float eps,
+               int dtype, int w_dtype, void* stream) {
+    if (!x || !weight || !y || (LN && !bias)) return fail(XG_ERR_INVALID_ARG, "%s: null x/weight/bias/y", name);
+    if (rows < 0 || hidden <= 0) return fail(XG_ERR_INVALID_ARG, "%s: bad extents rows=%lld hidden=%lld", name, (long long)rows, (long long)hidden);
+    if (x_row_stride < hidden || (residual && res_row_stride < hidden))
+        return fail(XG_ERR_INVALID_ARG, "%s: row stride smaller than hidden", name);
+    if (dtype_size(dtype) == 0) return fail(XG_ERR_INVALID_ARG, "%s: bad dtype %d", name, dtype);
+    if (w_dtype != XG_F32 && w_dtype != dtype) return fail(XG_ERR_UNSUPPORTED, "%s: weight dtype must be f32 or the input dtype", name);
+    if (sum_out && !residual) return fail(XG_ERR_INVALID_ARG, "%s: sum_out given without residual", name);
+    if (rows == 0) return XG_OK;
+    NormParams p{x, residual, weight, bias, y, sum_out, rows, hidden, x_row_stride, res_row_stride, eps, w_dtype == XG_F32 ? 1 : 0};
+    cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+    switch (dtype) {
+        case XG_F32: return launch_norm<float, LN>(p, st, name);
+        case XG_BF16: return launch_norm<__nv_bfloat16, LN>(p, st, name);
+        default: return launch_norm<__half, LN>(p, st, name);
+    }
+}
+
+}  // namespace
+}  // namespace xg
+
+extern "C" int xg_rmsnorm(const void* x, const void* residual, const void* weight, void* y, void* sum_out, int64_t rows,
+                          int64_t hidden, int64_t x_row_stride, int64_t res_row_stride, float eps, int dtype,
+                          int w_dtype, void* stream) {
+    return xg::norm_entry<false>("xg_rmsnorm", x, residual, weight, nullptr, y, sum_out, rows, hidden, x_row_stride,
+                                 res_row_stride, eps, dtype, w_dtype, stream);
+}
+
+extern "C" int xg_layernorm(const void* x, const void* residual, const void* weight, const void* bias, void* y,
+                            void* sum_out, int64_t rows, int64_t hidden, int64_t x_row_stride, int64_t res_row_stride,
+                            float eps, int dtype, int w_dtype, void* stream) {
+    return xg::norm_entry<true>("xg_layernorm", x, residual, weight, bias, y, sum_out, rows, hidden, x_row_stride,
+                                res_row_stride, eps, dtype, w_dtype, stream);
+}

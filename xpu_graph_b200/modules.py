@@ -1,0 +1,250 @@
+"""Replacement modules of the ``cuda_sm100`` target.
+
+These are the ``nn.Module`` classes that xpu_graph's structure patterns instantiate and call
+(``target_mod(...)``); names, constructor arguments, ``forward`` signatures and error behaviour mirror
+the Cambricon target's (passes/patterns/targets/mlu/structure_replacements/__init__.py:21-179,
+dense_layer_modules.py:4-128, norm_modules.py:4-21) so that the reference's structure patterns can use
+them unchanged. Every ``forward`` ends in a ``torch.ops.xg_sm100.*`` custom op; the modules hold no
+tensors and no library handles, so compiled graphs stay picklable for the compile cache
+(cache.py:113-179 of the reference).
+"""
+from __future__ import annotations
+
+from typing import List, Optional, Sequence, Tuple
+
+import torch
+
+from . import ops  # noqa: F401  (registers torch.ops.xg_sm100.*)
+
+_X = torch.ops.xg_sm100
+
+_SUPPORTED = (torch.float32, torch.bfloat16, torch.float16)
+
+
+# ---- normalisation -------------------------------------------------------------------------
+class RMSNormModule(torch.nn.Module):
+    """CustomRMSNorm target (structure/custom_rmsnorm.py:21-29): forward(inputs, weights, epsilon)."""
+
+    def forward(self, inputs, weights, epsilon):
+        return _X.rms_norm(inputs, weights, float(epsilon))
+
+
+class LayerNormModule(torch.nn.Module):
+    """CustomLayerNorm target (structure/custom_layernorm.py:21-29): forward(inputs, weights, bias, epsilon)."""
+
+    def forward(self, inputs, weights, bias, epsilon):
+        return _X.layer_norm(inputs, weights, bias, float(epsilon))
+
+
+class AddRMSNormModule(torch.nn.Module):
+    """Residual add fused into RMSNorm. ``store_sum`` mirrors store_output_before_norm of
+    targets/mlu/fuse_add_norm.py:118-121: with it the module returns (normed, x + residual)."""
+
+    def __init__(self, store_sum: bool):
+        super().__init__()
+        self.store_sum = bool(store_sum)
+
+    def forward(self, inputs, residual, weights, epsilon):
+        if self.store_sum:
+            y, s = _X.add_rms_norm(inputs, residual, weights, float(epsilon))
+            return y, s
+        return _X.add_rms_norm_y(inputs, residual, weights, float(epsilon))
+
+
+class AddLayerNormModule(torch.nn.Module):
+    """Residual add fused into LayerNorm (see AddRMSNormModule)."""
+
+    def __init__(self, store_sum: bool):
+        super().__init__()
+        self.store_sum = bool(store_sum)
+
+    def forward(self, inputs, residual, weights, bias, epsilon):
+        if self.store_sum:
+            y, s = _X.add_layer_norm(inputs, residual, weights, bias, float(epsilon))
+            return y, s
+        return _X.add_layer_norm_y(inputs, residual, weights, bias, float(epsilon))
+
+
+# ---- dense layers --------------------------------------------------------------------------
+class DenseLayerModule(torch.nn.Module):
+    """CustomDenseLayer target (structure/custom_denselayer.py:80-88):
+    ``M(fast_act)``; forward(inputs, weight, weight_trans, bias, act). Bias handling follows
+    dense_layer_modules.py:22-57: a 1-D (or [1, N]) bias is a per-column bias, anything else is a
+    full [M, N] addend."""
+
+    def __init__(self, fast_act):
+        super().__init__()
+        self.fast_act = fast_act
+
+    def forward(self, inputs, weight, weight_trans, bias, act):
+        m = inputs.shape[0]
+        n = weight.shape[-1] if not weight_trans else weight.shape[-2]
+        col_bias, full_bias = None, None
+        if bias is not None:
+            bshape = bias.shape
+            if len(bshape) == 2 and bshape[0] == 1:
+                bias = bias.view(-1)
+                bshape = bias.shape
+            if len(bshape) == 1:
+                col_bias = bias if bias.shape[0] == n else bias.broadcast_to((n,)).contiguous()
+            else:
+                full_bias = bias if bias.shape == torch.Size([m, n]) else bias.broadcast_to((m, n)).contiguous()
+        return _X.dense(inputs, weight, bool(weight_trans), col_bias, full_bias, act)
+
+
+def can_fuse_custom_denselayer(inputs, weight, weight_trans, bias, act_str):
+    """constraint_fn of CustomDenseLayer, evaluated on FakeTensors (custom_denselayer.py:86)."""
+    if act_str not in ["gelu", "relu", "silu", "sigmoid", "none"]:
+        return False
+    if inputs.dim() != 2 or weight.dim() != 2:
+        return False
+    if inputs.dtype not in _SUPPORTED or weight.dtype != inputs.dtype:
+        return False
+    if bias is not None and bias.dtype != inputs.dtype:
+        return False
+    if not inputs.is_cuda:
+        return False
+    if inputs.dtype != torch.float32:
+        # tensor-core kernel: weights in Linear layout [N, K], K a multiple of 8 (16-byte rows for TMA)
+        if not weight_trans:
+            return False
+        if inputs.shape[1] % 8 != 0:
+            return False
+    return True
+
+
+class BatchDenseLayerModule(torch.nn.Module):
+    """CustomBatchDenseLayer target (custom_denselayer.py:111-117); bias forms as
+    dense_layer_modules.py:82-93: [b, M, N] is a residual, anything else broadcasts to [b, 1, N]."""
+
+    def forward(self, inputs, weight, weight_trans, bias, act):
+        b, m, _ = inputs.shape
+        n = weight.shape[-1] if not weight_trans else weight.shape[-2]
+        col_bias, residual = None, None
+        if bias is not None:
+            if bias.shape == torch.Size([b, m, n]):
+                residual = bias
+            else:
+                col_bias = bias.broadcast_to((b, 1, n))
+        return _X.batch_dense(inputs, weight, bool(weight_trans), col_bias, residual, act)
+
+
+def can_fuse_custom_batch_denselayer(inputs, weight, weight_trans, bias, act_str):
+    if act_str not in ["gelu", "silu", "none"]:
+        return False
+    if inputs.dim() != 3 or weight.dim() != 3 or not inputs.is_cuda:
+        return False
+    if inputs.dtype not in _SUPPORTED or weight.dtype != inputs.dtype:
+        return False
+    if inputs.dtype != torch.float32 and (not weight_trans or inputs.shape[2] % 8 != 0):
+        return False
+    return True
+
+
+class DenseSwiGLUModule(torch.nn.Module):
+    """mul(silu(x @ Wg^T), x @ Wu^T) as one dual GEMM with the SwiGLU epilogue."""
+
+    def forward(self, inputs, w_gate, w_up):
+        return _X.dense_swiglu(inputs, w_gate, w_up)
+
+
+class SwiGLUModule(torch.nn.Module):
+    """silu(gate) * up (targets/npu/fuse_silu_mul.py:21-69 applies the same fusion to a packed tensor)."""
+
+    def forward(self, gate, up):
+        return _X.swiglu(gate, up)
+
+
+class RopeModule(torch.nn.Module):
+    """x*cos + rotate_half(x)*sin on [B, H, S, D]."""
+
+    def forward(self, x, cos, sin):
+        return _X.rope(x, cos, sin)
+
+
+class SDPAModule(torch.nn.Module):
+    """aten.scaled_dot_product_attention as produced by FusedSDPA
+    (common/fuse_scaled_dot_product_attention.py:230-234)."""
+
+    def forward(self, q, k, v, attn_mask, scale, is_causal):
+        if scale is None:
+            scale = q.shape[-1] ** -0.5
+        return _X.sdpa(q, k, v, attn_mask, float(scale), bool(is_causal))
+
+
+# ---- copy fusions --------------------------------------------------------------------------
+class FuseSliceModule(torch.nn.Module):
+    """FusedSlice target (structure/fuse_slice.py:96-106): ``M(start_indices)``;
+    forward(src, slice_len) -> [num, *src.shape[:-1], slice_len]."""
+
+    def __init__(self, slices_index):
+        super().__init__()
+        self.slices_index = [int(s) for s in slices_index]
+
+    def forward(self, input_tensor, slice_len):
+        return _X.multi_slice(input_tensor, self.slices_index, int(slice_len))
+
+
+class FuseSliceCatSameInputModule(torch.nn.Module):
+    """FusedCatSlice / FusedSliceStackSum target (structure/fuse_slice_cat.py:72-75):
+    forward(src_2d, [(start, end), ...]) -> [rows, sum(len)]."""
+
+    def forward(self, input_tensor, slices):
+        if len(input_tensor.shape) != 2:
+            raise NotImplementedError("input must be 2d")
+        starts = [int(s) for s, _ in slices]
+        ends = [int(e) for _, e in slices]
+        return _X.slice_cat(input_tensor, starts, ends, None, False)
+
+
+class FuseSliceCatSameInputModule_v2(torch.nn.Module):
+    """FusedMultipleSliceCat target (structure/fuse_multiple_slice_cat.py:29-39):
+    ``M(many_slices)``; forward(src, many_slices) -> list of [rows, sum(len_k)]."""
+
+    def __init__(self, many_slices):
+        super().__init__()
+        self.starts = [int(s) for group in many_slices for s, _ in group]
+        self.ends = [int(e) for group in many_slices for _, e in group]
+        self.counts = [len(group) for group in many_slices]
+
+    def forward(self, input_tensor, many_slices):
+        return _X.slice_cat_multi(input_tensor, self.starts, self.ends, self.counts)
+
+
+class MaskedSliceCatModule(torch.nn.Module):
+    """cat([where(mask[B,1], 0, x[:, s:e]) ...], -1) — the computation of the reference's
+    fuse_slice_where_cat kernel (targets/mlu/triton_kernel/fused_slice_where_cat.py:12-73)."""
+
+    def forward(self, input_tensor, mask, slices):
+        starts = [int(s) for s, _ in slices]
+        ends = [int(e) for _, e in slices]
+        return _X.slice_cat(input_tensor, starts, ends, mask, True)
+
+
+class CatLastDimModule(torch.nn.Module):
+    """cat / stack of several tensors along the last dim in one pass."""
+
+    def forward(self, tensors, row_mask=None, zero_when=True):
+        return _X.cat_lastdim(list(tensors), row_mask, bool(zero_when))
+
+
+class GatherStackModule(torch.nn.Module):
+    """F embedding lookups + where-mask + stack in one pass: forward(tables, idx[rows, F], mask)."""
+
+    def forward(self, tables, idx, row_mask=None, zero_when=True):
+        return _X.gather_stack(list(tables), idx, row_mask, bool(zero_when))
+
+
+def get_structure_replacements(config=None) -> dict:
+    """Structure-pattern name -> module (or (module, constraint_fn)), the dict that
+    passes/patterns/targets/__init__.py:13-27 normalises."""
+    return {
+        "CustomRMSNorm": RMSNormModule,
+        "CustomLayerNorm": LayerNormModule,
+        "FusedSlice": FuseSliceModule,
+        "FusedCatSlice": FuseSliceCatSameInputModule,
+        "FusedSliceStackSum": FuseSliceCatSameInputModule,
+        "FusedMultipleSliceCat": FuseSliceCatSameInputModule_v2,
+        "CustomDenseLayer": (DenseLayerModule, can_fuse_custom_denselayer),
+        "CustomBatchDenseLayer": (BatchDenseLayerModule, can_fuse_custom_batch_denselayer),
+    }

@@ -1,0 +1,507 @@
+"""torch.library custom ops of the ``cuda_sm100`` target (namespace ``xg_sm100``).
+
+PyTorch appears here only at the Python boundary: each op validates its tensors, allocates the
+outputs with ``torch.empty`` on the input's device and hands raw pointers, extents and the current
+CUDA stream to the C ABI of libxg_sm100.so. Ops are functional (``mutates_args=()``), registered for
+the ``cuda`` device only (there is no CPU implementation on purpose) and carry fake implementations
+so that the graph compiler can propagate shapes through them.
+
+Registration pattern follows passes/patterns/targets/mlu/triton_kernel/fused_slice_where_cat.py:75,132
+(``custom_op`` + ``register_fake``) of the reference.
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import List, Optional, Sequence
+
+import torch
+
+from . import lib as _lib
+
+NS = "xg_sm100"
+
+_DTYPE_CODE = {torch.float32: _lib.XG_F32, torch.bfloat16: _lib.XG_BF16, torch.float16: _lib.XG_F16}
+
+
+def _code(dtype: torch.dtype) -> int:
+    try:
+        return _DTYPE_CODE[dtype]
+    except KeyError:
+        raise TypeError(f"xg_sm100: unsupported dtype {dtype}") from None
+
+
+def _stream(t: torch.Tensor) -> int:
+    return torch.cuda.current_stream(t.device).cuda_stream
+
+
+def _ptr(t: Optional[torch.Tensor]):
+    return None if t is None else t.data_ptr()
+
+
+def _rows_view(x: torch.Tensor) -> torch.Tensor:
+    """View x as [rows, hidden] with a contiguous last dim; copies only when strides do not allow it."""
+    h = x.shape[-1]
+    if x.dim() == 2 and x.stride(1) == 1:
+        return x
+    if x.is_contiguous():
+        return x.view(-1, h)
+    return x.contiguous().view(-1, h)
+
+
+def _row_stride(x2: torch.Tensor) -> int:
+    return x2.stride(0) if x2.shape[0] > 1 else max(x2.stride(0), x2.shape[1])
+
+
+def _coef(w: torch.Tensor, dtype: torch.dtype) -> torch.Tensor:
+    """Affine coefficients are passed as fp32 or as the activation dtype."""
+    if w.dtype not in (torch.float32, dtype):
+        w = w.to(torch.float32)
+    return w.contiguous()
+
+
+# --------------------------------------------------------------------------------------------
+# normalisation
+# --------------------------------------------------------------------------------------------
+def _norm_call(kind: str, x, residual, weight, bias, eps: float, want_sum: bool):
+    L = _lib.load()
+    x2 = _rows_view(x)
+    rows, hidden = x2.shape
+    r2 = None
+    if residual is not None:
+        if residual.shape != x.shape or residual.dtype != x.dtype:
+            raise ValueError("xg_sm100 norm: residual must match x in shape and dtype")
+        r2 = _rows_view(residual)
+    w = _coef(weight, x.dtype)
+    b = _coef(bias, x.dtype).to(w.dtype) if bias is not None else None
+    y = torch.empty((rows, hidden), dtype=x.dtype, device=x.device)
+    s = torch.empty((rows, hidden), dtype=x.dtype, device=x.device) if want_sum else None
+    code, wcode = _code(x.dtype), _code(w.dtype)
+    if kind == "rms":
+        rc = L.xg_rmsnorm(_ptr(x2), _ptr(r2), _ptr(w), _ptr(y), _ptr(s), rows, hidden, _row_stride(x2),
+                          _row_stride(r2) if r2 is not None else 0, float(eps), code, wcode, _stream(x))
+        _lib.check(rc, "xg_rmsnorm")
+    else:
+        rc = L.xg_layernorm(_ptr(x2), _ptr(r2), _ptr(w), _ptr(b), _ptr(y), _ptr(s), rows, hidden, _row_stride(x2),
+                            _row_stride(r2) if r2 is not None else 0, float(eps), code, wcode, _stream(x))
+        _lib.check(rc, "xg_layernorm")
+    y = y.view(x.shape)
+    if want_sum:
+        return y, s.view(x.shape)
+    return y
+
+
+@torch.library.custom_op(f"{NS}::rms_norm", mutates_args=(), device_types="cuda")
+def rms_norm(x: torch.Tensor, weight: torch.Tensor, eps: float) -> torch.Tensor:
+    return _norm_call("rms", x, None, weight, None, eps, False)
+
+
+@rms_norm.register_fake
+def _(x, weight, eps):
+    return torch.empty(x.shape, dtype=x.dtype, device=x.device)
+
+
+@torch.library.custom_op(f"{NS}::add_rms_norm", mutates_args=(), device_types="cuda")
+def add_rms_norm(x: torch.Tensor, residual: torch.Tensor, weight: torch.Tensor, eps: float) -> List[torch.Tensor]:
+    y, s = _norm_call("rms", x, residual, weight, None, eps, True)
+    return [y, s]
+
+
+@add_rms_norm.register_fake
+def _(x, residual, weight, eps):
+    return [torch.empty(x.shape, dtype=x.dtype, device=x.device), torch.empty(x.shape, dtype=x.dtype, device=x.device)]
+
+
+@torch.library.custom_op(f"{NS}::add_rms_norm_y", mutates_args=(), device_types="cuda")
+def add_rms_norm_y(x: torch.Tensor, residual: torch.Tensor, weight: torch.Tensor, eps: float) -> torch.Tensor:
+    return _norm_call("rms", x, residual, weight, None, eps, False)
+
+
+@add_rms_norm_y.register_fake
+def _(x, residual, weight, eps):
+    return torch.empty(x.shape, dtype=x.dtype, device=x.device)
+
+
+@torch.library.custom_op(f"{NS}::layer_norm", mutates_args=(), device_types="cuda")
+def layer_norm(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor, eps: float) -> torch.Tensor:
+    return _norm_call("ln", x, None, weight, bias, eps, False)
+
+
+@layer_norm.register_fake
+def _(x, weight, bias, eps):
+    return torch.empty(x.shape, dtype=x.dtype, device=x.device)
+
+
+@torch.library.custom_op(f"{NS}::add_layer_norm", mutates_args=(), device_types="cuda")
+def add_layer_norm(x: torch.Tensor, residual: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor,
+                   eps: float) -> List[torch.Tensor]:
+    y, s = _norm_call("ln", x, residual, weight, bias, eps, True)
+    return [y, s]
+
+
+@add_layer_norm.register_fake
+def _(x, residual, weight, bias, eps):
+    return [torch.empty(x.shape, dtype=x.dtype, device=x.device), torch.empty(x.shape, dtype=x.dtype, device=x.device)]
+
+
+@torch.library.custom_op(f"{NS}::add_layer_norm_y", mutates_args=(), device_types="cuda")
+def add_layer_norm_y(x: torch.Tensor, residual: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor,
+                     eps: float) -> torch.Tensor:
+    return _norm_call("ln", x, residual, weight, bias, eps, False)
+
+
+@add_layer_norm_y.register_fake
+def _(x, residual, weight, bias, eps):
+    return torch.empty(x.shape, dtype=x.dtype, device=x.device)
+
+
+# --------------------------------------------------------------------------------------------
+# elementwise
+# --------------------------------------------------------------------------------------------
+@torch.library.custom_op(f"{NS}::rope", mutates_args=(), device_types="cuda")
+def rope(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> torch.Tensor:
+    """x: [B, H, S, D] (any strides with D contiguous); cos/sin broadcastable from [S, D]."""
+    if x.dim() != 4:
+        raise ValueError("xg_sm100::rope expects [B, H, S, D]")
+    B, H, S, D = x.shape
+    if x.stride(3) != 1:
+        x = x.contiguous()
+    cos2 = cos.reshape(S, D).to(x.dtype).contiguous()
+    sin2 = sin.reshape(S, D).to(x.dtype).contiguous()
+    y = torch.empty((B, H, S, D), dtype=x.dtype, device=x.device)
+    rc = _lib.load().xg_rope(_ptr(x), _ptr(cos2), _ptr(sin2), _ptr(y), B, H, S, D, x.stride(0), x.stride(1), x.stride(2),
+                             _code(x.dtype), _stream(x))
+    _lib.check(rc, "xg_rope")
+    return y
+
+
+@rope.register_fake
+def _(x, cos, sin):
+    return torch.empty(x.shape, dtype=x.dtype, device=x.device)
+
+
+@torch.library.custom_op(f"{NS}::swiglu", mutates_args=(), device_types="cuda")
+def swiglu(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
+    if gate.shape != up.shape or gate.dtype != up.dtype:
+        raise ValueError("xg_sm100::swiglu: gate and up must match")
+    g2, u2 = _rows_view(gate), _rows_view(up)
+    rows, cols = g2.shape
+    out = torch.empty((rows, cols), dtype=gate.dtype, device=gate.device)
+    rc = _lib.load().xg_swiglu(_ptr(g2), _ptr(u2), _ptr(out), rows, cols, _row_stride(g2), _row_stride(u2), cols,
+                               _code(gate.dtype), _stream(gate))
+    _lib.check(rc, "xg_swiglu")
+    return out.view(gate.shape)
+
+
+@swiglu.register_fake
+def _(gate, up):
+    return torch.empty(gate.shape, dtype=gate.dtype, device=gate.device)
+
+
+# --------------------------------------------------------------------------------------------
+# dense layers
+# --------------------------------------------------------------------------------------------
+def _mat(t: torch.Tensor) -> torch.Tensor:
+    return t if t.stride(-1) == 1 else t.contiguous()
+
+
+@torch.library.custom_op(f"{NS}::dense", mutates_args=(), device_types="cuda")
+def dense(x: torch.Tensor, weight: torch.Tensor, weight_trans: bool, bias: Optional[torch.Tensor],
+          residual: Optional[torch.Tensor], act: str) -> torch.Tensor:
+    """act(x @ W + bias + residual); W = weight ([K, N]) or weight^T (weight is [N, K], weight_trans)."""
+    if x.dim() != 2 or weight.dim() != 2:
+        raise ValueError("xg_sm100::dense expects 2-D x and weight")
+    x = _mat(x)
+    weight = _mat(weight)
+    M, K = x.shape
+    N = weight.shape[0] if weight_trans else weight.shape[1]
+    if (weight.shape[1] if weight_trans else weight.shape[0]) != K:
+        raise ValueError("xg_sm100::dense: inner dimensions differ")
+    if bias is not None:
+        bias = bias.to(x.dtype).contiguous()
+    ldr = 0
+    if residual is not None:
+        residual = _mat(residual.to(x.dtype))
+        ldr = _row_stride(residual)
+    out = torch.empty((M, N), dtype=x.dtype, device=x.device)
+    rc = _lib.load().xg_gemm_bias_act(_ptr(x), _ptr(weight), _ptr(bias), _ptr(residual), _ptr(out), M, N, K, _row_stride(x),
+                                      _row_stride(weight), N, ldr, 1 if weight_trans else 0, _lib.ACT_CODES[act],
+                                      _code(x.dtype), _stream(x))
+    _lib.check(rc, "xg_gemm_bias_act")
+    return out
+
+
+@dense.register_fake
+def _(x, weight, weight_trans, bias, residual, act):
+    N = weight.shape[0] if weight_trans else weight.shape[1]
+    return torch.empty((x.shape[0], N), dtype=x.dtype, device=x.device)
+
+
+@torch.library.custom_op(f"{NS}::batch_dense", mutates_args=(), device_types="cuda")
+def batch_dense(x: torch.Tensor, weight: torch.Tensor, weight_trans: bool, bias: Optional[torch.Tensor],
+                residual: Optional[torch.Tensor], act: str) -> torch.Tensor:
+    """Batched dense: x [b, M, K], weight [b, K, N] or [b, N, K]; bias [b, 1, N] / [b, N]; residual [b, M, N]."""
+    x = x.contiguous()
+    weight = weight.contiguous()
+    b, M, K = x.shape
+    N = weight.shape[1] if weight_trans else weight.shape[2]
+    sbias = 0
+    if bias is not None:
+        bias = bias.to(x.dtype).broadcast_to((b, 1, N)).contiguous()
+        sbias = N
+    sr = 0
+    if residual is not None:
+        residual = residual.to(x.dtype).broadcast_to((b, M, N)).contiguous()
+        sr = M * N
+    out = torch.empty((b, M, N), dtype=x.dtype, device=x.device)
+    rc = _lib.load().xg_bgemm_bias_act(_ptr(x), _ptr(weight), _ptr(bias), _ptr(residual), _ptr(out), b, M, N, K, K,
+                                       weight.shape[2], N, N, M * K, weight.shape[1] * weight.shape[2], sbias, sr, M * N,
+                                       1 if weight_trans else 0, _lib.ACT_CODES[act], _code(x.dtype), _stream(x))
+    _lib.check(rc, "xg_bgemm_bias_act")
+    return out
+
+
+@batch_dense.register_fake
+def _(x, weight, weight_trans, bias, residual, act):
+    N = weight.shape[1] if weight_trans else weight.shape[2]
+    return torch.empty((x.shape[0], x.shape[1], N), dtype=x.dtype, device=x.device)
+
+
+@torch.library.custom_op(f"{NS}::dense_swiglu", mutates_args=(), device_types="cuda")
+def dense_swiglu(x: torch.Tensor, w_gate: torch.Tensor, w_up: torch.Tensor) -> torch.Tensor:
+    """silu(x @ w_gate^T) * (x @ w_up^T); weights in Linear layout [N, K]."""
+    x = _mat(x)
+    w_gate, w_up = _mat(w_gate), _mat(w_up)
+    if _row_stride(w_gate) != _row_stride(w_up):
+        w_gate, w_up = w_gate.contiguous(), w_up.contiguous()
+    M, K = x.shape
+    N = w_gate.shape[0]
+    out = torch.empty((M, N), dtype=x.dtype, device=x.device)
+    rc = _lib.load().xg_gemm_swiglu(_ptr(x), _ptr(w_gate), _ptr(w_up), _ptr(out), M, N, K, _row_stride(x),
+                                    _row_stride(w_gate), N, _code(x.dtype), _stream(x))
+    _lib.check(rc, "xg_gemm_swiglu")
+    return out
+
+
+@dense_swiglu.register_fake
+def _(x, w_gate, w_up):
+    return torch.empty((x.shape[0], w_gate.shape[0]), dtype=x.dtype, device=x.device)
+
+
+# --------------------------------------------------------------------------------------------
+# attention
+# --------------------------------------------------------------------------------------------
+@torch.library.custom_op(f"{NS}::sdpa", mutates_args=(), device_types="cuda")
+def sdpa(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, attn_mask: Optional[torch.Tensor], scale: float,
+         is_causal: bool) -> torch.Tensor:
+    """q [B,H,Sq,D], k/v [B,H,Skv,D]; attn_mask: additive (same dtype) or boolean, broadcastable to [B,H,Sq,Skv]."""
+    if q.dim() != 4:
+        raise ValueError("xg_sm100::sdpa expects 4-D q/k/v")
+    B, H, Sq, D = q.shape
+    Skv = k.shape[2]
+    q, k, v = (t if t.stride(3) == 1 else t.contiguous() for t in (q, k, v))
+    mstr = None
+    if attn_mask is not None:
+        m = attn_mask
+        if m.dtype == torch.bool:
+            m = torch.zeros(m.shape, dtype=q.dtype, device=q.device).masked_fill_(~m, float("-inf"))
+        m = m.to(q.dtype)
+        while m.dim() < 4:
+            m = m.unsqueeze(0)
+        m = m.expand(B, H, Sq, Skv)
+        attn_mask = m
+        mstr = _lib.i64_array(m.stride())
+    out = torch.empty((B, H, Sq, D), dtype=q.dtype, device=q.device)
+    rc = _lib.load().xg_sdpa_fwd(_ptr(q), _ptr(k), _ptr(v), _ptr(attn_mask), _ptr(out), B, H, Sq, Skv, D,
+                                 _lib.i64_array(q.stride()[:3]), _lib.i64_array(k.stride()[:3]),
+                                 _lib.i64_array(v.stride()[:3]), _lib.i64_array(out.stride()[:3]), mstr, float(scale),
+                                 1 if is_causal else 0, _code(q.dtype), _stream(q))
+    _lib.check(rc, "xg_sdpa_fwd")
+    return out
+
+
+@sdpa.register_fake
+def _(q, k, v, attn_mask, scale, is_causal):
+    return torch.empty(q.shape, dtype=q.dtype, device=q.device)
+
+
+# --------------------------------------------------------------------------------------------
+# copy fusions (bit-exact)
+# --------------------------------------------------------------------------------------------
+def _seg_copy(srcs: Sequence[int], dsts: Sequence[int], src_ld: Sequence[int], dst_ld: Sequence[int],
+              lens: Sequence[int], rows: int, mask: Optional[torch.Tensor], zero_when: bool, ref: torch.Tensor) -> None:
+    n = len(srcs)
+    rc = _lib.load().xg_seg_copy(_lib.ptr_array(srcs), _lib.ptr_array(dsts), _lib.i64_array(src_ld), _lib.i64_array(dst_ld),
+                                 _lib.i64_array(lens), n, rows, _ptr(mask), 1 if zero_when else 0, _stream(ref))
+    _lib.check(rc, "xg_seg_copy")
+
+
+def _norm_slices(width: int, starts: Sequence[int], ends: Sequence[int]):
+    out = []
+    for s, e in zip(starts, ends):
+        s = s + width if s < 0 else s
+        e = e + width if e < 0 else e
+        s = min(max(s, 0), width)
+        e = min(max(e, s), width)
+        out.append((s, e))
+    return out
+
+
+def _mask_bytes(mask: Optional[torch.Tensor], rows: int) -> Optional[torch.Tensor]:
+    if mask is None:
+        return None
+    m = mask.reshape(-1)
+    if m.numel() != rows:
+        raise ValueError("xg_sm100: row mask must have one entry per row")
+    return m.to(torch.uint8) if m.dtype != torch.uint8 else m.contiguous()
+
+
+@torch.library.custom_op(f"{NS}::slice_cat", mutates_args=(), device_types="cuda")
+def slice_cat(src: torch.Tensor, starts: List[int], ends: List[int], row_mask: Optional[torch.Tensor],
+              zero_when: bool) -> torch.Tensor:
+    """cat([src[:, s:e] for s, e in zip(starts, ends)], -1) of a 2-D src; rows where
+    (row_mask != 0) == zero_when are written as zeros."""
+    if src.dim() != 2:
+        raise NotImplementedError("input must be 2d")
+    if src.stride(1) != 1:
+        src = src.contiguous()
+    rows, width = src.shape
+    segs = _norm_slices(width, starts, ends)
+    total = sum(e - s for s, e in segs)
+    out = torch.empty((rows, total), dtype=src.dtype, device=src.device)
+    es = src.element_size()
+    srcs, dsts, lens = [], [], []
+    off = 0
+    for s, e in segs:
+        srcs.append(src.data_ptr() + s * es)
+        dsts.append(out.data_ptr() + off * es)
+        lens.append((e - s) * es)
+        off += e - s
+    n = len(segs)
+    _seg_copy(srcs, dsts, [_row_stride(src) * es] * n, [total * es] * n, lens, rows, _mask_bytes(row_mask, rows), zero_when, src)
+    return out
+
+
+@slice_cat.register_fake
+def _(src, starts, ends, row_mask, zero_when):
+    segs = _norm_slices(src.shape[1], starts, ends)
+    return torch.empty((src.shape[0], sum(e - s for s, e in segs)), dtype=src.dtype, device=src.device)
+
+
+@torch.library.custom_op(f"{NS}::multi_slice", mutates_args=(), device_types="cuda")
+def multi_slice(src: torch.Tensor, starts: List[int], slice_len: int) -> torch.Tensor:
+    """stack([src[..., s:s+slice_len] for s in starts], 0) -> [num, *src.shape[:-1], slice_len]."""
+    lead = list(src.shape[:-1])
+    s2 = _rows_view(src)
+    rows, width = s2.shape
+    num = len(starts)
+    out = torch.empty((num, rows, slice_len), dtype=src.dtype, device=src.device)
+    es = src.element_size()
+    srcs = [s2.data_ptr() + (s + width if s < 0 else s) * es for s in starts]
+    dsts = [out.data_ptr() + k * rows * slice_len * es for k in range(num)]
+    _seg_copy(srcs, dsts, [_row_stride(s2) * es] * num, [slice_len * es] * num, [slice_len * es] * num, rows, None, False, src)
+    return out.view([num] + lead + [slice_len])
+
+
+@multi_slice.register_fake
+def _(src, starts, slice_len):
+    return torch.empty([len(starts)] + list(src.shape[:-1]) + [slice_len], dtype=src.dtype, device=src.device)
+
+
+@torch.library.custom_op(f"{NS}::slice_cat_multi", mutates_args=(), device_types="cuda")
+def slice_cat_multi(src: torch.Tensor, starts: List[int], ends: List[int], counts: List[int]) -> List[torch.Tensor]:
+    """Several slice_cat results of one 2-D src in one pass: output k concatenates the next
+    counts[k] (start, end) pairs."""
+    if src.dim() != 2:
+        raise NotImplementedError("input must be 2d")
+    if src.stride(1) != 1:
+        src = src.contiguous()
+    rows, width = src.shape
+    segs = _norm_slices(width, starts, ends)
+    es = src.element_size()
+    outs, srcs, dsts, slds, dlds, lens = [], [], [], [], [], []
+    pos = 0
+    for c in counts:
+        group = segs[pos:pos + c]
+        pos += c
+        total = sum(e - s for s, e in group)
+        o = torch.empty((rows, total), dtype=src.dtype, device=src.device)
+        outs.append(o)
+        off = 0
+        for s, e in group:
+            srcs.append(src.data_ptr() + s * es)
+            dsts.append(o.data_ptr() + off * es)
+            slds.append(_row_stride(src) * es)
+            dlds.append(total * es)
+            lens.append((e - s) * es)
+            off += e - s
+    _seg_copy(srcs, dsts, slds, dlds, lens, rows, None, False, src)
+    return outs
+
+
+@slice_cat_multi.register_fake
+def _(src, starts, ends, counts):
+    segs = _norm_slices(src.shape[1], starts, ends)
+    outs, pos = [], 0
+    for c in counts:
+        outs.append(torch.empty((src.shape[0], sum(e - s for s, e in segs[pos:pos + c])), dtype=src.dtype, device=src.device))
+        pos += c
+    return outs
+
+
+@torch.library.custom_op(f"{NS}::cat_lastdim", mutates_args=(), device_types="cuda")
+def cat_lastdim(xs: List[torch.Tensor], row_mask: Optional[torch.Tensor], zero_when: bool) -> torch.Tensor:
+    """cat(xs, -1) for tensors that agree on every leading dim (stack along a new trailing-but-one
+    dim is the same copy followed by a view)."""
+    lead = list(xs[0].shape[:-1])
+    xs2 = [_rows_view(x) for x in xs]
+    rows = xs2[0].shape[0]
+    total = sum(x.shape[1] for x in xs2)
+    out = torch.empty((rows, total), dtype=xs[0].dtype, device=xs[0].device)
+    es = out.element_size()
+    srcs, dsts, slds, lens = [], [], [], []
+    off = 0
+    for x in xs2:
+        if x.dtype != out.dtype or x.shape[0] != rows:
+            raise ValueError("xg_sm100::cat_lastdim: inputs must agree in dtype and leading dims")
+        srcs.append(x.data_ptr())
+        dsts.append(out.data_ptr() + off * es)
+        slds.append(_row_stride(x) * es)
+        lens.append(x.shape[1] * es)
+        off += x.shape[1]
+    _seg_copy(srcs, dsts, slds, [total * es] * len(xs2), lens, rows, _mask_bytes(row_mask, rows), zero_when, out)
+    return out.view(lead + [total])
+
+
+@cat_lastdim.register_fake
+def _(xs, row_mask, zero_when):
+    return torch.empty(list(xs[0].shape[:-1]) + [sum(x.shape[-1] for x in xs)], dtype=xs[0].dtype, device=xs[0].device)
+
+
+@torch.library.custom_op(f"{NS}::gather_stack", mutates_args=(), device_types="cuda")
+def gather_stack(tables: List[torch.Tensor], idx: torch.Tensor, row_mask: Optional[torch.Tensor],
+                 zero_when: bool) -> torch.Tensor:
+    """out[r, f*D:(f+1)*D] = tables[f][idx[r, f]] (zeros where the row mask says so): F embedding
+    lookups, the where-mask and the stack in one pass. idx: int64 [rows, F]."""
+    F = len(tables)
+    if idx.dim() != 2 or idx.shape[1] != F or idx.dtype != torch.int64:
+        raise ValueError("xg_sm100::gather_stack: idx must be int64 [rows, F]")
+    D = tables[0].shape[1]
+    tabs = []
+    for t in tables:
+        if t.dim() != 2 or t.shape[1] != D or t.dtype != tables[0].dtype:
+            raise ValueError("xg_sm100::gather_stack: tables must be 2-D with one embedding dim and dtype")
+        tabs.append(t if t.is_contiguous() else t.contiguous())
+    rows = idx.shape[0]
+    out = torch.empty((rows, F * D), dtype=tables[0].dtype, device=idx.device)
+    rc = _lib.load().xg_gather_rows(_lib.ptr_array([t.data_ptr() for t in tabs]), _lib.i64_array([t.shape[0] for t in tabs]),
+                                    F, _ptr(idx), idx.stride(0), idx.stride(1), _ptr(_mask_bytes(row_mask, rows)),
+                                    1 if zero_when else 0, _ptr(out), rows, D, F * D, out.element_size(), _stream(idx))
+    _lib.check(rc, "xg_gather_rows")
+    # keep the contiguous copies alive until the launch is enqueued (stream-ordered frees make this safe)
+    del tabs
+    return out
+
+
+@gather_stack.register_fake
+def _(tables, idx, row_mask, zero_when):
+    return torch.empty((idx.shape[0], len(tables) * tables[0].shape[1]), dtype=tables[0].dtype, device=idx.device)
