@@ -146,7 +146,8 @@ int xg_gemm_swiglu(const void* A, const void* Wg, const void* Wu, void* out, int
  * q: [B,H,Sq,D], k,v: [B,H,Skv,D], out: [B,H,Sq,D]; each addressed by element strides for
  * (batch, head, seq) with D contiguous. mask: nullable additive mask of the same dtype,
  * addressed by element strides for (batch, head, q, kv) — 0 strides broadcast. causal != 0 applies
- * the lower-triangular mask (query i sees keys j <= i + Skv - Sq).
+ * the lower-triangular mask aligned to the top-left corner (query i sees keys j <= i), as
+ * aten.scaled_dot_product_attention(is_causal=True) does.
  * Replaces: aten.scaled_dot_product_attention as emitted by
  * passes/patterns/common/fuse_scaled_dot_product_attention.py:163-238 (FusedSDPA).
  */

@@ -121,7 +121,7 @@ def sdpa_math(q, k, v, attn_mask=None, scale: Optional[float] = None, is_causal:
         s = s + attn_mask.float()
     if is_causal:
         sq, skv = s.shape[-2:]
-        keep = torch.ones(sq, skv, dtype=torch.bool).tril(diagonal=skv - sq)
+        keep = torch.ones(sq, skv, dtype=torch.bool).tril(diagonal=0)  # top-left aligned, as aten
         s = s.masked_fill(~keep, float("-inf"))
     return torch.matmul(torch.softmax(s, dim=-1), vf)
 

@@ -1,0 +1,106 @@
+"""GPU parity: fused scaled-dot-product attention through the C ABI vs the CPU oracle.
+
+Shapes follow the reference's SDPA tests (tests/common/test_fuse_sdpa.py:553-561: B in {1,2,4}, 32 heads,
+S=38, E=64, fp16) plus the two benchmark shapes (encoder block fp32 [1,8,128,64]; Llama prefill bf16
+[8,32,2048,128] causal). The reference's own test drops its comparison result; these pin it.
+"""
+import pytest
+import torch
+
+from oracle import ref_ops
+from tests.helpers import assert_parity, error_stats
+
+pytestmark = pytest.mark.gpu
+
+
+def _qkv(B, H, Sq, Skv, D, dtype, seed):
+    g = torch.Generator().manual_seed(seed)
+    q = torch.randn(B, H, Sq, D, generator=g).to(dtype)
+    k = torch.randn(B, H, Skv, D, generator=g).to(dtype)
+    v = torch.randn(B, H, Skv, D, generator=g).to(dtype)
+    return q, k, v
+
+
+def _run(cuda_device, q, k, v, mask, scale, causal):
+    from xpu_graph_b200 import lib
+    from xpu_graph_b200.modules import SDPAModule
+
+    out = SDPAModule()(q.to(cuda_device), k.to(cuda_device), v.to(cuda_device), mask.to(cuda_device) if mask is not None else None, scale, causal)
+    torch.cuda.synchronize()
+    assert lib.tc_status() == 0, "a bounded wait expired inside the attention kernel"
+    return out
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("causal", [False, True])
+@pytest.mark.parametrize("B,H,S,D", [(1, 1, 128, 128), (2, 3, 256, 128), (1, 2, 300, 128), (2, 2, 38, 64), (1, 4, 512, 64), (1, 1, 1, 128)])
+def test_flash_tc(cuda_device, B, H, S, D, causal, dtype):
+    q, k, v = _qkv(B, H, S, S, D, dtype, 30)
+    got = _run(cuda_device, q, k, v, None, None, causal)
+    want = ref_ops.sdpa(q, k, v, None, None, causal)
+    assert_parity(got, want, f"sdpa {B}x{H}x{S}x{D} causal={causal} {dtype}")
+    exact = ref_ops.sdpa_math(q, k, v, None, None, causal)
+    max_abs, mean_rel = error_stats(got, exact)
+    assert max_abs < 2e-2, f"max abs error vs fp32 math {max_abs}"
+
+
+def test_flash_tc_mask_and_cross_lengths(cuda_device):
+    q, k, v = _qkv(2, 2, 130, 200, 64, torch.bfloat16, 31)
+    g = torch.Generator().manual_seed(32)
+    mask = torch.randn(2, 1, 130, 200, generator=g).to(torch.bfloat16)
+    got = _run(cuda_device, q, k, v, mask, 0.2, False)
+    assert_parity(got, ref_ops.sdpa(q, k, v, mask, 0.2, False), "sdpa additive mask")
+    keep = torch.rand(1, 1, 130, 200, generator=g) > 0.3
+    keep[..., 0] = True  # no fully masked row
+    got = _run(cuda_device, q, k, v, keep, None, False)
+    assert_parity(got, ref_ops.sdpa(q, k, v, keep, None, False), "sdpa boolean mask")
+
+
+def test_flash_tc_transposed_views(cuda_device):
+    """q/k/v as they leave the projections: [B, S, H*D] viewed and transposed to [B, H, S, D]."""
+    B, S, H, D = 2, 260, 4, 128
+    g = torch.Generator().manual_seed(33)
+    base = [torch.randn(B, S, H * D, generator=g).to(torch.bfloat16) for _ in range(3)]
+    q, k, v = (t.view(B, S, H, D).transpose(1, 2) for t in base)
+    from xpu_graph_b200.modules import SDPAModule
+
+    dq, dk, dv = (t.to(cuda_device).view(B, S, H, D).transpose(1, 2) for t in base)
+    got = SDPAModule()(dq, dk, dv, None, None, True)
+    assert_parity(got, ref_ops.sdpa(q, k, v, None, None, True), "sdpa transposed views")
+
+
+@pytest.mark.parametrize("causal", [False, True])
+def test_simt_fp32_encoder_shape(cuda_device, causal):
+    q, k, v = _qkv(1, 8, 128, 128, 64, torch.float32, 34)
+    got = _run(cuda_device, q, k, v, None, 0.125, causal)
+    want = ref_ops.sdpa_math(q.double(), k.double(), v.double(), None, 0.125, causal).float()
+    assert_parity(got, want, "sdpa fp32")
+
+
+def test_simt_other_head_dims(cuda_device):
+    q, k, v = _qkv(2, 2, 77, 91, 96, torch.bfloat16, 35)
+    g = torch.Generator().manual_seed(36)
+    mask = torch.randn(77, 91, generator=g).to(torch.bfloat16)
+    got = _run(cuda_device, q, k, v, mask, None, False)
+    assert_parity(got, ref_ops.sdpa(q, k, v, mask, None, False), "sdpa D=96")
+
+
+def test_config4_prefill_shape(cuda_device):
+    """Llama prefill shape [8, 32, 2048, 128] bf16 causal: sampled (batch, head) pairs against the oracle,
+    plus the row-stochastic property (attention over an all-ones V returns ones)."""
+    B, H, S, D = 8, 32, 2048, 128
+    g = torch.Generator(device=cuda_device).manual_seed(3)
+    q = torch.randn(B, H, S, D, generator=g, device=cuda_device, dtype=torch.bfloat16)
+    k = torch.randn(B, H, S, D, generator=g, device=cuda_device, dtype=torch.bfloat16)
+    v = torch.randn(B, H, S, D, generator=g, device=cuda_device, dtype=torch.bfloat16)
+    from xpu_graph_b200 import lib
+    from xpu_graph_b200.modules import SDPAModule
+
+    got = SDPAModule()(q, k, v, None, None, True)
+    torch.cuda.synchronize()
+    assert lib.tc_status() == 0
+    for b, h in [(0, 0), (7, 31), (3, 17)]:
+        want = ref_ops.sdpa(q[b:b + 1, h:h + 1].cpu(), k[b:b + 1, h:h + 1].cpu(), v[b:b + 1, h:h + 1].cpu(), None, None, True)
+        assert_parity(got[b:b + 1, h:h + 1], want, f"prefill pair ({b},{h})")
+    ones = SDPAModule()(q, k, torch.ones_like(v), None, None, True)
+    assert (ones.float() - 1.0).abs().max().item() < 1e-2

@@ -10,6 +10,7 @@ int gemm_f32_entry(const void* A, const void* B, const void* bias, const void* r
 int gemm_swiglu_entry(const void* A, const void* Wg, const void* Wu, void* out, int64_t M, int64_t N, int64_t K,
                       int64_t lda, int64_t ldw, int64_t ldc, int dtype, cudaStream_t st);
 int read_tc_status(unsigned int* host_out, int reset);
+int read_sdpa_status(unsigned int* host_out, int reset);
 
 namespace {
 int validate_gemm(const char* name, const void* A, const void* B, const void* residual, void* out, int64_t M, int64_t N,
@@ -70,5 +71,11 @@ extern "C" int xg_gemm_swiglu(const void* A, const void* Wg, const void* Wu, voi
 
 extern "C" int xg_tc_status(unsigned int* status, int reset) {
     if (!status) return xg::fail(XG_ERR_INVALID_ARG, "xg_tc_status: null output");
-    return xg::read_tc_status(status, reset);
+    unsigned int a = 0, b = 0;
+    int rc = xg::read_tc_status(&a, reset);
+    if (rc != XG_OK) return rc;
+    rc = xg::read_sdpa_status(&b, reset);
+    if (rc != XG_OK) return rc;
+    *status = a | b;
+    return XG_OK;
 }

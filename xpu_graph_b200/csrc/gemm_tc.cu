@@ -17,6 +17,7 @@
 #include "sm100_ptx.cuh"
 
 #include <mutex>
+#include <type_traits>
 
 namespace xg {
 
@@ -45,6 +46,22 @@ bool make_tmap_2d_16bit(CUtensorMap* out, const void* base, uint64_t rows, uint6
     cuuint32_t box[2] = {box_cols, box_rows};
     cuuint32_t estr[2] = {1, 1};
     CUresult r = enc(out, is_bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2,
+                     const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                     CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS;
+}
+
+bool make_tmap_bhsd_16bit(CUtensorMap* out, const void* base, uint64_t B, uint64_t H, uint64_t S, uint64_t D,
+                          uint64_t stride_b, uint64_t stride_h, uint64_t stride_s, uint32_t box_rows, bool is_bf16) {
+    PFN_encodeTiled enc = get_encode_tiled();
+    if (!enc) return false;
+    cuuint64_t dims[4] = {D, S, H, B};
+    // A stride of a size-1 dimension is never used for addressing but must still be a valid multiple of 16 bytes.
+    auto fix = [&](uint64_t st, uint64_t extent) -> cuuint64_t { return (extent == 1 || st == 0) ? D * 2 : st * 2; };
+    cuuint64_t strides[3] = {fix(stride_s, S), fix(stride_h, H), fix(stride_b, B)};
+    cuuint32_t box[4] = {64, box_rows, 1, 1};
+    cuuint32_t estr[4] = {1, 1, 1, 1};
+    CUresult r = enc(out, is_bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4,
                      const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                      CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     return r == CUDA_SUCCESS;
@@ -248,7 +265,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
             int mb, nb;
             tile_coords(t, p.num_m_blocks, p.num_n_blocks, mb, nb);
-            if (!ptx::mbar_wait_bounded(&tmem_full[acc], acc_phase, abort_flag)) { ok = false; break; }
+            // warp-uniform result: the TMEM loads below are warp-collective
+            if (!__all_sync(0xffffffffu, ptx::mbar_wait_bounded(&tmem_full[acc], acc_phase, abort_flag))) { ok = false; break; }
             ptx::tc_fence_after();
             const int64_t row = (int64_t)mb * BM + quad * 32 + lane;
             const bool row_ok = row < p.M;

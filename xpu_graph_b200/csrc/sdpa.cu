@@ -1,9 +1,518 @@
-// Fused scaled-dot-product attention (placeholder until the flash kernel lands).
+// Fused scaled-dot-product attention: out = softmax(q k^T * scale + mask) v, online softmax.
+//
+// 16-bit inputs with head_dim 64 or 128 run on the tensor cores (flash_tc_kernel):
+//   one CTA per (batch, head, 128-query tile); warp 0 streams K/V tiles with TMA (2-stage ring),
+//   warp 1's elected thread issues tcgen05.mma for S = Q K^T (into one of two TMEM buffers, so the
+//   next block's scores are computed while the current block is in softmax) and for P V (P staged in
+//   shared memory as bf16/f16 in the 128-byte-swizzled K-major layout, V consumed MN-major exactly as
+//   TMA leaves it); warps 2..5 own one query row per thread: they read the row's scores from TMEM,
+//   keep the running max / sum, write P, and accumulate the output row in registers
+//   (O = (O + PV_prev) * alpha), so no shuffles and no TMEM read-modify-write are needed.
+//   Causal tiles beyond the diagonal are skipped.
+// Everything else (fp32, other head dims) runs a warp-per-query SIMT kernel in true fp32.
 #include "common.cuh"
+#include "sm100_ptx.cuh"
+
+#include <type_traits>
+
+namespace xg {
+
+// Status word of the attention kernel (device globals are per translation unit without -rdc).
+__device__ unsigned int g_sdpa_status[4];
+
+namespace {
+
+constexpr float kLog2e = 1.4426950408889634f;
+
+struct SdpaParams {
+    const void* q;
+    const void* k;
+    const void* v;
+    const void* mask;
+    void* out;
+    int64_t B, H, Sq, Skv, D;
+    int64_t q_sb, q_sh, q_ss;
+    int64_t k_sb, k_sh, k_ss;
+    int64_t v_sb, v_sh, v_ss;
+    int64_t o_sb, o_sh, o_ss;
+    int64_t m_sb, m_sh, m_sq, m_sk;
+    float scale;
+    int causal;
+};
+
+// ---------------------------------------------------------------------------------------
+// Tensor-core flash kernel
+// ---------------------------------------------------------------------------------------
+constexpr int FM = 128;  // query rows per CTA
+constexpr int FN = 64;   // keys per block
+constexpr int kFlashThreads = 192;
+constexpr float kRescaleThreshold = 8.0f;  // log2 units: the running max may lag by up to 2^8
+
+template <int D>
+struct FlashCfg {
+    static constexpr int DB = D / 64;                 // 64-wide head-dim blocks
+    static constexpr int Q_BYTES = FM * D * 2;
+    static constexpr int KV_BYTES = FN * D * 2;       // one K or V tile
+    static constexpr int P_BYTES = FM * FN * 2;
+    // Two CTAs share an SM (tiles 112 KiB at D = 128), so there is no alignment slack: the kernel checks
+    // that the dynamic shared-memory window starts on a 1024-byte boundary and reports if it does not.
+    static constexpr int SMEM_BYTES = Q_BYTES + 4 * KV_BYTES + P_BYTES + 256;
+    static constexpr int TMEM_COLS = 256;             // S0 [0,64) S1 [64,128) O [128, 128+D)
+    static constexpr uint32_t O_COL = 128;
+};
+
+template <typename T, int D>
+__global__ void __launch_bounds__(kFlashThreads, 2)
+flash_tc_kernel(const __grid_constant__ CUtensorMap tmq, const __grid_constant__ CUtensorMap tmk,
+                const __grid_constant__ CUtensorMap tmv, const SdpaParams p) {
+    using Cfg = FlashCfg<D>;
+    extern __shared__ __align__(1024) uint8_t smem[];
+    uint8_t* q_s = smem;
+    uint8_t* k_s = q_s + Cfg::Q_BYTES;            // [2][KV_BYTES]
+    uint8_t* v_s = k_s + 2 * Cfg::KV_BYTES;       // [2][KV_BYTES]
+    uint8_t* p_s = v_s + 2 * Cfg::KV_BYTES;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(p_s + Cfg::P_BYTES);
+    uint64_t* q_full = bars;          // 1
+    uint64_t* k_full = bars + 1;      // 2
+    uint64_t* k_empty = bars + 3;     // 2
+    uint64_t* v_full = bars + 5;      // 2
+    uint64_t* v_empty = bars + 7;     // 2
+    uint64_t* s_full = bars + 9;      // 2
+    uint64_t* s_empty = bars + 11;    // 2
+    uint64_t* p_full = bars + 13;     // 1
+    uint64_t* pv_full = bars + 14;    // 1
+    uint64_t* drain_bar = bars + 15;  // 1
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 16);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+    if ((ptx::smem_u32(smem) & 1023u) != 0) {  // uniform over the CTA: the swizzled tiles need this alignment
+        if (threadIdx.x == 0) atomicOr(&g_sdpa_status[0], 128u);
+        return;
+    }
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int q_tiles = (int)((p.Sq + FM - 1) / FM);
+    // Heavy (late) causal tiles first: the longest CTAs start earliest.
+    const int qt = p.causal ? (q_tiles - 1 - (int)(blockIdx.x % q_tiles)) : (int)(blockIdx.x % q_tiles);
+    const int bh = blockIdx.x / q_tiles;
+    const int h = bh % (int)p.H, b = bh / (int)p.H;
+    const int q0 = qt * FM;
+    int nblk = (int)((p.Skv + FN - 1) / FN);
+    if (p.causal) {
+        const int lim = (q0 + FM - 1) / FN + 1;  // last block that any row of this tile can see
+        if (lim < nblk) nblk = lim;
+    }
+
+    if (threadIdx.x == 0) {
+        ptx::mbar_init(q_full, 1);
+        for (int s = 0; s < 2; ++s) {
+            ptx::mbar_init(&k_full[s], 1);
+            ptx::mbar_init(&k_empty[s], 1);
+            ptx::mbar_init(&v_full[s], 1);
+            ptx::mbar_init(&v_empty[s], 1);
+            ptx::mbar_init(&s_full[s], 1);
+            ptx::mbar_init(&s_empty[s], 128);
+        }
+        ptx::mbar_init(p_full, 128);
+        ptx::mbar_init(pv_full, 1);
+        ptx::mbar_init(drain_bar, 1);
+        *abort_flag = 0;
+        ptx::fence_mbar_init();
+        ptx::fence_proxy_async();
+    }
+    if (warp == 1) ptx::tmem_alloc(tmem_slot, Cfg::TMEM_COLS);
+    ptx::tc_fence_before();
+    __syncthreads();
+    ptx::tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+    constexpr int fmt = std::is_same<T, __nv_bfloat16>::value ? 1 : 0;
+
+    if (warp == 0) {
+        // ------------------------------ TMA producer ------------------------------
+        if (ptx::elect_one()) {
+            ptx::prefetch_tensormap(&tmq);
+            ptx::prefetch_tensormap(&tmk);
+            ptx::prefetch_tensormap(&tmv);
+            ptx::mbar_arrive_expect_tx(q_full, Cfg::Q_BYTES);
+#pragma unroll
+            for (int db = 0; db < Cfg::DB; ++db) ptx::tma_load_4d(q_s + db * (FM * 128), &tmq, q_full, db * 64, q0, h, b);
+            bool ok = true;
+            int issued = 0;
+            for (int j = 0; j < nblk && ok; ++j) {
+                const int s = j & 1;
+                const uint32_t ph = (uint32_t)(j >> 1) & 1u;
+                if (!ptx::mbar_wait_bounded(&k_empty[s], ph ^ 1u, abort_flag)) { ok = false; break; }
+                ptx::mbar_arrive_expect_tx(&k_full[s], Cfg::KV_BYTES);
+#pragma unroll
+                for (int db = 0; db < Cfg::DB; ++db)
+                    ptx::tma_load_4d(k_s + s * Cfg::KV_BYTES + db * (FN * 128), &tmk, &k_full[s], db * 64, j * FN, h, b);
+                if (!ptx::mbar_wait_bounded(&v_empty[s], ph ^ 1u, abort_flag)) { ok = false; issued = j * 2 + 1; break; }
+                ptx::mbar_arrive_expect_tx(&v_full[s], Cfg::KV_BYTES);
+#pragma unroll
+                for (int db = 0; db < Cfg::DB; ++db)
+                    ptx::tma_load_4d(v_s + s * Cfg::KV_BYTES + db * (FN * 128), &tmv, &v_full[s], db * 64, j * FN, h, b);
+                issued = j * 2 + 2;
+            }
+            if (!ok) {
+                // Unwinding: wait (bounded) for this thread's own copies before shared memory is given up.
+                atomicOr(&g_sdpa_status[0], 16u);
+                const uint64_t t0 = ptx::globaltimer_ns();
+                auto drain = [&](uint64_t* bar, uint32_t parity) {
+                    while (!ptx::mbar_try_wait(bar, parity)) {
+                        if (ptx::globaltimer_ns() - t0 > ptx::kWaitLimitNs) break;
+                    }
+                };
+                drain(q_full, 0);
+                for (int n = (issued > 4 ? issued - 4 : 0); n < issued; ++n) {
+                    const int j = n >> 1;
+                    drain((n & 1) ? &v_full[j & 1] : &k_full[j & 1], (uint32_t)(j >> 1) & 1u);
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------ MMA issuer --------------------------------
+        if (ptx::elect_one()) {
+            constexpr uint32_t idesc_s = ptx::make_idesc_f16(fmt, FM, FN, 0);
+            constexpr uint32_t idesc_o = ptx::make_idesc_f16(fmt, FM, D, 1);
+            const uint32_t q_addr = ptx::smem_u32(q_s), p_addr = ptx::smem_u32(p_s);
+            bool ok = true;
+            auto issue_qk = [&](int j) -> bool {
+                const int s = j & 1;
+                const uint32_t ph = (uint32_t)(j >> 1) & 1u;
+                if (!ptx::mbar_wait_bounded(&k_full[s], ph, abort_flag)) return false;
+                if (!ptx::mbar_wait_bounded(&s_empty[s], ph ^ 1u, abort_flag)) return false;
+                ptx::tc_fence_after();
+                const uint32_t k_addr = ptx::smem_u32(k_s + s * Cfg::KV_BYTES);
+#pragma unroll
+                for (int kk = 0; kk < D / 16; ++kk) {
+                    const uint32_t q_off = (uint32_t)((kk >> 2) * (FM * 128) + (kk & 3) * 32);
+                    const uint32_t k_off = (uint32_t)((kk >> 2) * (FN * 128) + (kk & 3) * 32);
+                    ptx::mma_f16_ss(tmem_base + (uint32_t)(s * FN), ptx::make_kmajor_sw128_desc(q_addr + q_off),
+                                    ptx::make_kmajor_sw128_desc(k_addr + k_off), idesc_s, kk != 0 ? 1u : 0u);
+                }
+                ptx::tc_commit(&k_empty[s]);
+                ptx::tc_commit(&s_full[s]);
+                return true;
+            };
+            if (!ptx::mbar_wait_bounded(q_full, 0, abort_flag)) ok = false;
+            if (ok && nblk > 0) ok = issue_qk(0);
+            for (int j = 0; j < nblk && ok; ++j) {
+                if (j + 1 < nblk) {
+                    if (!issue_qk(j + 1)) { ok = false; break; }
+                }
+                const int s = j & 1;
+                if (!ptx::mbar_wait_bounded(p_full, (uint32_t)j & 1u, abort_flag)) { ok = false; break; }
+                if (!ptx::mbar_wait_bounded(&v_full[s], (uint32_t)(j >> 1) & 1u, abort_flag)) { ok = false; break; }
+                ptx::tc_fence_after();
+                const uint32_t v_addr = ptx::smem_u32(v_s + s * Cfg::KV_BYTES);
+#pragma unroll
+                for (int kk = 0; kk < FN / 16; ++kk) {
+                    // O (+)= P V: the first block overwrites, later blocks accumulate in TMEM
+                    ptx::mma_f16_ss(tmem_base + Cfg::O_COL, ptx::make_kmajor_sw128_desc(p_addr + (uint32_t)(kk * 32)),
+                                    ptx::make_mnmajor_sw128_desc(v_addr + (uint32_t)(kk * 16 * 128), FN * 128), idesc_o,
+                                    (j | kk) != 0 ? 1u : 0u);
+                }
+                ptx::tc_commit(&v_empty[s]);
+                ptx::tc_commit(pv_full);
+            }
+            if (!ok) {
+                atomicOr(&g_sdpa_status[0], 32u);
+                ptx::tc_commit(drain_bar);
+                const uint64_t t0 = ptx::globaltimer_ns();
+                while (!ptx::mbar_try_wait(drain_bar, 0)) {
+                    if (ptx::globaltimer_ns() - t0 > ptx::kWaitLimitNs) break;
+                }
+            }
+        }
+    } else {
+        // ------------------------------ softmax / output rows ---------------------
+        // One query row per thread. The output accumulates in TMEM; it is rescaled only when some row
+        // of the warp sees its maximum grow by more than 2^kRescaleThreshold (the running maximum is
+        // allowed to lag, the final division by the row sum makes the result exact either way).
+        const int quad = warp & 3;
+        const int r_in_tile = quad * 32 + lane;
+        const int row = q0 + r_in_tile;
+        const uint32_t lane_field = (uint32_t)(quad * 32) << 16;
+        const float sl2 = p.scale * kLog2e;
+        const int skv = (int)p.Skv;
+        const T* mrow = nullptr;
+        if (p.mask != nullptr && row < p.Sq)
+            mrow = reinterpret_cast<const T*>(p.mask) + (int64_t)b * p.m_sb + (int64_t)h * p.m_sh + (int64_t)row * p.m_sq;
+        float m_run = -INFINITY, l_run = 0.f;
+        bool ok = true;
+
+        for (int j = 0; j < nblk; ++j) {
+            const int sb = j & 1;
+            // wait results are made warp-uniform: the TMEM accesses below are warp-collective
+            if (!__all_sync(0xffffffffu, ptx::mbar_wait_bounded(&s_full[sb], (uint32_t)(j >> 1) & 1u, abort_flag))) { ok = false; break; }
+            ptx::tc_fence_after();
+            const uint32_t s_taddr = tmem_base + lane_field + (uint32_t)(sb * FN);
+            const int col_base = j * FN;
+            uint32_t r0[32], r1[32];
+            ptx::tmem_ld_32x32(s_taddr, r0);
+            ptx::tmem_ld_32x32(s_taddr + 32u, r1);
+            ptx::tmem_ld_wait();
+            float sc[FN];  // scores in the log2 domain
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+                sc[i] = __uint_as_float(r0[i]) * sl2;
+                sc[32 + i] = __uint_as_float(r1[i]) * sl2;
+            }
+            // All of this warp's reads of the score buffer are done: the next Q K^T may overwrite it.
+            ptx::tc_fence_before();
+            ptx::mbar_arrive(&s_empty[sb]);
+            const bool masked_block = (p.mask != nullptr) || (col_base + FN > skv) || (p.causal && (col_base + FN - 1 > q0));
+            if (masked_block) {  // uniform over the CTA
+#pragma unroll
+                for (int i = 0; i < FN; ++i) {
+                    const int col = col_base + i;
+                    if (mrow != nullptr && col < skv) sc[i] += Cvt<T>::to_f(mrow[(int64_t)col * p.m_sk]) * kLog2e;
+                    if (col >= skv || (p.causal && col > row)) sc[i] = -INFINITY;
+                }
+            }
+            float mx = sc[0];
+#pragma unroll
+            for (int i = 1; i < FN; ++i) mx = fmaxf(mx, sc[i]);
+            const float m_new = fmaxf(m_run, mx);
+            const bool grow = m_new > m_run + kRescaleThreshold;  // also true for the first finite maximum
+            const bool warp_rescale = __any_sync(0xffffffffu, grow);
+            // P of the previous block has been consumed (and O is quiescent) once its P V has completed.
+            if (j > 0) {
+                if (!__all_sync(0xffffffffu, ptx::mbar_wait_bounded(pv_full, (uint32_t)(j - 1) & 1u, abort_flag))) { ok = false; break; }
+                ptx::tc_fence_after();
+            }
+            if (warp_rescale) {
+                const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
+                const float alpha = ptx::ex2_approx(m_run - m_use);  // 0 when there was no finite maximum yet
+                if (j > 0) {
+#pragma unroll
+                    for (int c = 0; c < D / 32; ++c) {
+                        uint32_t o[32];
+                        const uint32_t o_taddr = tmem_base + lane_field + Cfg::O_COL + (uint32_t)(c * 32);
+                        ptx::tmem_ld_32x32(o_taddr, o);
+                        ptx::tmem_ld_wait();
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+                        ptx::tmem_st_32x32(o_taddr, o);
+                    }
+                    ptx::tmem_st_wait();
+                }
+                l_run *= alpha;
+                m_run = m_new;
+            }
+            const float m_use = (m_run == -INFINITY) ? 0.f : m_run;
+            // probabilities -> shared memory (row r_in_tile of the swizzled K-major P tile)
+#pragma unroll
+            for (int t = 0; t < FN / 8; ++t) {
+                Vec16<T> pv;
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    const float pr = ptx::ex2_approx(sc[t * 8 + i] - m_use);
+                    l_run += pr;
+                    pv.v[i] = Cvt<T>::from_f(pr);
+                }
+                uint8_t* dst = p_s + r_in_tile * 128 + ((t ^ (r_in_tile & 7)) << 4);
+                *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<const uint4*>(&pv);
+            }
+            ptx::fence_proxy_async();  // P (generic-proxy stores) must be visible to the tensor core
+            ptx::tc_fence_before();
+            ptx::mbar_arrive(p_full);
+        }
+        if (ok && nblk > 0) {
+            if (!__all_sync(0xffffffffu, ptx::mbar_wait_bounded(pv_full, (uint32_t)(nblk - 1) & 1u, abort_flag))) ok = false;
+        }
+        if (ok) {
+            ptx::tc_fence_after();
+            const float inv_l = 1.0f / l_run;
+            T* orow = reinterpret_cast<T*>(p.out) + (int64_t)b * p.o_sb + (int64_t)h * p.o_sh + (int64_t)row * p.o_ss;
+#pragma unroll
+            for (int c = 0; c < D / 32; ++c) {
+                uint32_t o[32];
+                if (nblk > 0) {
+                    ptx::tmem_ld_32x32(tmem_base + lane_field + Cfg::O_COL + (uint32_t)(c * 32), o);
+                    ptx::tmem_ld_wait();
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) o[i] = 0u;
+                }
+                if (row < p.Sq) {
+#pragma unroll
+                    for (int t = 0; t < 4; ++t) {
+                        Vec16<T> ov;
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) ov.v[i] = Cvt<T>::from_f(__uint_as_float(o[t * 8 + i]) * inv_l);
+                        st16(orow + c * 32 + t * 8, ov);
+                    }
+                }
+            }
+        } else if (lane == 0) {
+            atomicOr(&g_sdpa_status[0], 64u);
+        }
+    }
+
+    ptx::tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        ptx::tc_fence_after();
+        ptx::tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
+    }
+}
+
+template <typename T, int D>
+int launch_flash_tc(const SdpaParams& p, cudaStream_t st) {
+    using Cfg = FlashCfg<D>;
+    constexpr bool is_bf16 = std::is_same<T, __nv_bfloat16>::value;
+    CUtensorMap tq, tk, tv;
+    if (!make_tmap_bhsd_16bit(&tq, p.q, p.B, p.H, p.Sq, D, p.q_sb, p.q_sh, p.q_ss, FM, is_bf16) ||
+        !make_tmap_bhsd_16bit(&tk, p.k, p.B, p.H, p.Skv, D, p.k_sb, p.k_sh, p.k_ss, FN, is_bf16) ||
+        !make_tmap_bhsd_16bit(&tv, p.v, p.B, p.H, p.Skv, D, p.v_sb, p.v_sh, p.v_ss, FN, is_bf16))
+        return fail(XG_ERR_UNSUPPORTED, "xg_sdpa_fwd: tensor-map encoding failed (strides must be multiples of 8 elements)");
+    auto kern = flash_tc_kernel<T, D>;
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
+    if (e != cudaSuccess) {
+        cudaGetLastError();
+        return fail(XG_ERR_LAUNCH, "xg_sdpa_fwd: cannot reserve shared memory: %s", cudaGetErrorString(e));
+    }
+    const int64_t grid = p.B * p.H * ((p.Sq + FM - 1) / FM);
+    if (grid > 0x7fffffffLL) return fail(XG_ERR_TOO_LARGE, "xg_sdpa_fwd: too many tiles");
+    kern<<<(unsigned)grid, kFlashThreads, Cfg::SMEM_BYTES, st>>>(tq, tk, tv, p);
+    return check_launch("xg_sdpa_fwd");
+}
+
+// ---------------------------------------------------------------------------------------
+// SIMT kernel: one warp per query row, true fp32 arithmetic, any dtype / strides, D <= 256.
+// Lane t scores key j0 + t; the output row is spread over the lanes (element d = lane + 32 u).
+// ---------------------------------------------------------------------------------------
+constexpr int kSimtWarps = 4;
+constexpr int kSimtMaxD = 256;
+
+template <typename T>
+__global__ void __launch_bounds__(kSimtWarps * 32) sdpa_simt_kernel(const SdpaParams p) {
+    __shared__ float qs[kSimtWarps][kSimtMaxD];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int64_t gr = (int64_t)blockIdx.x * kSimtWarps + warp;  // global query row over (b, h, i)
+    if (gr >= p.B * p.H * p.Sq) return;
+    const int64_t i = gr % p.Sq;
+    const int64_t bh = gr / p.Sq;
+    const int64_t h = bh % p.H, b = bh / p.H;
+    const int D = (int)p.D;
+    const T* qrow = reinterpret_cast<const T*>(p.q) + b * p.q_sb + h * p.q_sh + i * p.q_ss;
+    const T* kbase = reinterpret_cast<const T*>(p.k) + b * p.k_sb + h * p.k_sh;
+    const T* vbase = reinterpret_cast<const T*>(p.v) + b * p.v_sb + h * p.v_sh;
+    const T* mrow = p.mask ? reinterpret_cast<const T*>(p.mask) + b * p.m_sb + h * p.m_sh + i * p.m_sq : nullptr;
+    for (int d = lane; d < D; d += 32) qs[warp][d] = Cvt<T>::to_f(qrow[d]);
+    __syncwarp();
+    float o[kSimtMaxD / 32];
+#pragma unroll
+    for (int u = 0; u < kSimtMaxD / 32; ++u) o[u] = 0.f;
+    float m_run = -INFINITY, l_run = 0.f;
+    int64_t kv_end = p.Skv;
+    if (p.causal && i + 1 < kv_end) kv_end = i + 1;
+    for (int64_t j0 = 0; j0 < kv_end; j0 += 32) {
+        const int64_t j = j0 + lane;
+        float s = -INFINITY;
+        if (j < kv_end) {
+            const T* kr = kbase + j * p.k_ss;
+            float acc = 0.f;
+            for (int d = 0; d < D; ++d) acc = fmaf(qs[warp][d], Cvt<T>::to_f(kr[d]), acc);
+            s = acc * p.scale;
+            if (mrow) s += Cvt<T>::to_f(mrow[j * p.m_sk]);
+        }
+        const float m_new = fmaxf(m_run, warp_max(s));
+        const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
+        const float alpha = expf(m_run - m_use);
+        const float pj = expf(s - m_use);
+        l_run = l_run * alpha + warp_sum(pj);
+#pragma unroll
+        for (int u = 0; u < kSimtMaxD / 32; ++u) o[u] *= alpha;
+        const int cnt = (int)((kv_end - j0) < 32 ? (kv_end - j0) : 32);
+        for (int t = 0; t < cnt; ++t) {
+            const float pt = __shfl_sync(0xffffffffu, pj, t);
+            const T* vr = vbase + (j0 + t) * p.v_ss;
+#pragma unroll
+            for (int u = 0; u < kSimtMaxD / 32; ++u) {
+                const int d = lane + 32 * u;
+                if (d < D) o[u] = fmaf(pt, Cvt<T>::to_f(vr[d]), o[u]);
+            }
+        }
+        m_run = m_new;
+    }
+    const float inv_l = 1.0f / l_run;
+    T* orow = reinterpret_cast<T*>(p.out) + b * p.o_sb + h * p.o_sh + i * p.o_ss;
+#pragma unroll
+    for (int u = 0; u < kSimtMaxD / 32; ++u) {
+        const int d = lane + 32 * u;
+        if (d < D) orow[d] = Cvt<T>::from_f(o[u] * inv_l);
+    }
+}
+
+template <typename T>
+int launch_simt(const SdpaParams& p, cudaStream_t st) {
+    const int64_t rows = p.B * p.H * p.Sq;
+    const int64_t grid = (rows + kSimtWarps - 1) / kSimtWarps;
+    if (grid > 0x7fffffffLL) return fail(XG_ERR_TOO_LARGE, "xg_sdpa_fwd: too many rows");
+    sdpa_simt_kernel<T><<<(unsigned)grid, kSimtWarps * 32, 0, st>>>(p);
+    return check_launch("xg_sdpa_fwd");
+}
+
+}  // namespace
+}  // namespace xg
+
+namespace xg {
+int read_sdpa_status(unsigned int* host_out, int reset) {
+    unsigned int v[4] = {0, 0, 0, 0};
+    if (cudaMemcpyFromSymbol(v, g_sdpa_status, sizeof(v)) != cudaSuccess) {
+        cudaGetLastError();
+        return fail(XG_ERR_DEVICE, "xg_tc_status: cannot read device status");
+    }
+    *host_out = v[0];
+    if (reset && v[0] != 0) {
+        unsigned int z[4] = {0, 0, 0, 0};
+        cudaMemcpyToSymbol(g_sdpa_status, z, sizeof(z));
+    }
+    return XG_OK;
+}
+}  // namespace xg
 
 extern "C" int xg_sdpa_fwd(const void* q, const void* k, const void* v, const void* mask, void* out, int64_t B, int64_t H,
                            int64_t Sq, int64_t Skv, int64_t D, const int64_t* q_strides3, const int64_t* k_strides3,
                            const int64_t* v_strides3, const int64_t* o_strides3, const int64_t* mask_strides4, float scale,
                            int causal, int dtype, void* stream) {
-    return xg::fail(XG_ERR_UNSUPPORTED, "xg_sdpa_fwd: not built yet");
+    using namespace xg;
+    if (!q || !k || !v || !out || !q_strides3 || !k_strides3 || !v_strides3 || !o_strides3)
+        return fail(XG_ERR_INVALID_ARG, "xg_sdpa_fwd: null pointer");
+    if (mask && !mask_strides4) return fail(XG_ERR_INVALID_ARG, "xg_sdpa_fwd: mask given without strides");
+    if (B < 0 || H < 0 || Sq < 0 || Skv < 0 || D <= 0) return fail(XG_ERR_INVALID_ARG, "xg_sdpa_fwd: bad extents");
+    if (dtype_size(dtype) == 0) return fail(XG_ERR_INVALID_ARG, "xg_sdpa_fwd: bad dtype %d", dtype);
+    if (D > kSimtMaxD) return fail(XG_ERR_UNSUPPORTED, "xg_sdpa_fwd: head_dim %lld > %d", (long long)D, kSimtMaxD);
+    if (B * H * Sq == 0) return XG_OK;
+    SdpaParams p;
+    p.q = q; p.k = k; p.v = v; p.mask = mask; p.out = out;
+    p.B = B; p.H = H; p.Sq = Sq; p.Skv = Skv; p.D = D;
+    p.q_sb = q_strides3[0]; p.q_sh = q_strides3[1]; p.q_ss = q_strides3[2];
+    p.k_sb = k_strides3[0]; p.k_sh = k_strides3[1]; p.k_ss = k_strides3[2];
+    p.v_sb = v_strides3[0]; p.v_sh = v_strides3[1]; p.v_ss = v_strides3[2];
+    p.o_sb = o_strides3[0]; p.o_sh = o_strides3[1]; p.o_ss = o_strides3[2];
+    p.m_sb = mask ? mask_strides4[0] : 0; p.m_sh = mask ? mask_strides4[1] : 0;
+    p.m_sq = mask ? mask_strides4[2] : 0; p.m_sk = mask ? mask_strides4[3] : 0;
+    p.scale = scale;
+    p.causal = causal ? 1 : 0;
+    cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+
+    auto tma_ok = [&](const void* ptr, int64_t sb, int64_t sh, int64_t ss, int64_t S) {
+        auto okst = [&](int64_t s, int64_t extent) { return extent == 1 || (s > 0 && s % 8 == 0); };
+        return aligned16(ptr) && okst(ss, S) && okst(sh, H) && okst(sb, B);
+    };
+    const bool tc = (dtype != XG_F32) && (D == 64 || D == 128) && Skv > 0 && tma_ok(q, p.q_sb, p.q_sh, p.q_ss, Sq) &&
+                    tma_ok(k, p.k_sb, p.k_sh, p.k_ss, Skv) && tma_ok(v, p.v_sb, p.v_sh, p.v_ss, Skv) && aligned16(out) &&
+                    p.o_ss % 8 == 0 && p.o_sh % 8 == 0 && p.o_sb % 8 == 0 && Sq < 0x7fffff00LL && Skv < 0x7fffff00LL;
+    if (tc) {
+        if (dtype == XG_BF16) return D == 128 ? launch_flash_tc<__nv_bfloat16, 128>(p, st) : launch_flash_tc<__nv_bfloat16, 64>(p, st);
+        return D == 128 ? launch_flash_tc<__half, 128>(p, st) : launch_flash_tc<__half, 64>(p, st);
+    }
+    switch (dtype) {
+        case XG_F32: return launch_simt<float>(p, st);
+        case XG_BF16: return launch_simt<__nv_bfloat16>(p, st);
+        default: return launch_simt<__half>(p, st);
+    }
 }

@@ -20,6 +20,47 @@ from . import lib as _lib
 
 NS = "xg_sm100"
 
+# Launch accounting for the benchmark: every C-ABI call that enqueues a kernel bumps the counter;
+# when GEMM_EVENTS is a list, dense launches are bracketed by CUDA events on the launching stream
+# and (start, end, flops) is appended.
+_LAUNCHES = 0
+GEMM_EVENTS = None
+
+
+def reset_counters() -> None:
+    global _LAUNCHES
+    _LAUNCHES = 0
+
+
+def launch_count() -> int:
+    return _LAUNCHES
+
+
+def _bump(n: int = 1) -> None:
+    global _LAUNCHES
+    _LAUNCHES += n
+
+
+class _GemmTimer:
+    def __init__(self, ref: torch.Tensor, flops: int):
+        self.on = GEMM_EVENTS is not None
+        if self.on:
+            self.flops = flops
+            self.stream = torch.cuda.current_stream(ref.device)
+            self.e0 = torch.cuda.Event(enable_timing=True)
+            self.e1 = torch.cuda.Event(enable_timing=True)
+
+    def __enter__(self):
+        if self.on:
+            self.e0.record(self.stream)
+        return self
+
+    def __exit__(self, *exc):
+        if self.on:
+            self.e1.record(self.stream)
+            GEMM_EVENTS.append((self.e0, self.e1, self.flops))
+        return False
+
 _DTYPE_CODE = {torch.float32: _lib.XG_F32, torch.bfloat16: _lib.XG_BF16, torch.float16: _lib.XG_F16}
 
 
@@ -80,10 +121,12 @@ def _norm_call(kind: str, x, residual, weight, bias, eps: float, want_sum: bool)
         rc = L.xg_rmsnorm(_ptr(x2), _ptr(r2), _ptr(w), _ptr(y), _ptr(s), rows, hidden, _row_stride(x2),
                           _row_stride(r2) if r2 is not None else 0, float(eps), code, wcode, _stream(x))
         _lib.check(rc, "xg_rmsnorm")
+        _bump()
     else:
         rc = L.xg_layernorm(_ptr(x2), _ptr(r2), _ptr(w), _ptr(b), _ptr(y), _ptr(s), rows, hidden, _row_stride(x2),
                             _row_stride(r2) if r2 is not None else 0, float(eps), code, wcode, _stream(x))
         _lib.check(rc, "xg_layernorm")
+        _bump()
     y = y.view(x.shape)
     if want_sum:
         return y, s.view(x.shape)
@@ -171,6 +214,7 @@ def rope(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> torch.Tensor:
     rc = _lib.load().xg_rope(_ptr(x), _ptr(cos2), _ptr(sin2), _ptr(y), B, H, S, D, x.stride(0), x.stride(1), x.stride(2),
                              _code(x.dtype), _stream(x))
     _lib.check(rc, "xg_rope")
+    _bump()
     return y
 
 
@@ -189,6 +233,7 @@ def swiglu(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
     rc = _lib.load().xg_swiglu(_ptr(g2), _ptr(u2), _ptr(out), rows, cols, _row_stride(g2), _row_stride(u2), cols,
                                _code(gate.dtype), _stream(gate))
     _lib.check(rc, "xg_swiglu")
+    _bump()
     return out.view(gate.shape)
 
 
@@ -223,10 +268,12 @@ def dense(x: torch.Tensor, weight: torch.Tensor, weight_trans: bool, bias: Optio
         residual = _mat(residual.to(x.dtype))
         ldr = _row_stride(residual)
     out = torch.empty((M, N), dtype=x.dtype, device=x.device)
-    rc = _lib.load().xg_gemm_bias_act(_ptr(x), _ptr(weight), _ptr(bias), _ptr(residual), _ptr(out), M, N, K, _row_stride(x),
-                                      _row_stride(weight), N, ldr, 1 if weight_trans else 0, _lib.ACT_CODES[act],
-                                      _code(x.dtype), _stream(x))
+    with _GemmTimer(x, 2 * M * N * K):
+        rc = _lib.load().xg_gemm_bias_act(_ptr(x), _ptr(weight), _ptr(bias), _ptr(residual), _ptr(out), M, N, K,
+                                          _row_stride(x), _row_stride(weight), N, ldr, 1 if weight_trans else 0,
+                                          _lib.ACT_CODES[act], _code(x.dtype), _stream(x))
     _lib.check(rc, "xg_gemm_bias_act")
+    _bump()
     return out
 
 
@@ -257,6 +304,7 @@ def batch_dense(x: torch.Tensor, weight: torch.Tensor, weight_trans: bool, bias:
                                        weight.shape[2], N, N, M * K, weight.shape[1] * weight.shape[2], sbias, sr, M * N,
                                        1 if weight_trans else 0, _lib.ACT_CODES[act], _code(x.dtype), _stream(x))
     _lib.check(rc, "xg_bgemm_bias_act")
+    _bump()
     return out
 
 
@@ -276,9 +324,11 @@ def dense_swiglu(x: torch.Tensor, w_gate: torch.Tensor, w_up: torch.Tensor) -> t
     M, K = x.shape
     N = w_gate.shape[0]
     out = torch.empty((M, N), dtype=x.dtype, device=x.device)
-    rc = _lib.load().xg_gemm_swiglu(_ptr(x), _ptr(w_gate), _ptr(w_up), _ptr(out), M, N, K, _row_stride(x),
-                                    _row_stride(w_gate), N, _code(x.dtype), _stream(x))
+    with _GemmTimer(x, 4 * M * N * K):
+        rc = _lib.load().xg_gemm_swiglu(_ptr(x), _ptr(w_gate), _ptr(w_up), _ptr(out), M, N, K, _row_stride(x),
+                                        _row_stride(w_gate), N, _code(x.dtype), _stream(x))
     _lib.check(rc, "xg_gemm_swiglu")
+    _bump()
     return out
 
 
@@ -316,6 +366,7 @@ def sdpa(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, attn_mask: Optional[
                                  _lib.i64_array(v.stride()[:3]), _lib.i64_array(out.stride()[:3]), mstr, float(scale),
                                  1 if is_causal else 0, _code(q.dtype), _stream(q))
     _lib.check(rc, "xg_sdpa_fwd")
+    _bump()
     return out
 
 
@@ -333,6 +384,7 @@ def _seg_copy(srcs: Sequence[int], dsts: Sequence[int], src_ld: Sequence[int], d
     rc = _lib.load().xg_seg_copy(_lib.ptr_array(srcs), _lib.ptr_array(dsts), _lib.i64_array(src_ld), _lib.i64_array(dst_ld),
                                  _lib.i64_array(lens), n, rows, _ptr(mask), 1 if zero_when else 0, _stream(ref))
     _lib.check(rc, "xg_seg_copy")
+    _bump()
 
 
 def _norm_slices(width: int, starts: Sequence[int], ends: Sequence[int]):
@@ -497,6 +549,7 @@ def gather_stack(tables: List[torch.Tensor], idx: torch.Tensor, row_mask: Option
                                     F, _ptr(idx), idx.stride(0), idx.stride(1), _ptr(_mask_bytes(row_mask, rows)),
                                     1 if zero_when else 0, _ptr(out), rows, D, F * D, out.element_size(), _stream(idx))
     _lib.check(rc, "xg_gather_rows")
+    _bump()
     # keep the contiguous copies alive until the launch is enqueued (stream-ordered frees make this safe)
     del tabs
     return out
