@@ -1,0 +1,111 @@
+"""Small stand-alone cases of each kernel, for profiling and quick timing.
+
+    python -m xpu_graph_b200.kernel_cases <case> [--iters N]
+
+Each case holds well under a few GB on the device and launches the named kernel ``iters`` times
+(default 3) after one warm-up, then prints the mean device time measured with CUDA events. Sizes are
+larger than L2 so that DRAM counters mean something.
+"""
+from __future__ import annotations
+
+import argparse
+import sys
+
+import torch
+
+
+def _time(fn, iters):
+    fn()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(iters):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / iters
+
+
+def main(argv=None):
+    from . import lib, ops  # noqa: F401
+
+    X = torch.ops.xg_sm100
+    ap = argparse.ArgumentParser()
+    ap.add_argument("case", choices=["gemm", "gemm_swiglu", "gemm_small_m", "add_rms_norm", "layer_norm", "sdpa", "rope", "swiglu",
+                                     "gather", "slice_cat", "gemm_f32"])
+    ap.add_argument("--iters", type=int, default=3)
+    args = ap.parse_args(argv)
+    dev = torch.device("cuda")
+    bf = torch.bfloat16
+    g = torch.Generator(device=dev).manual_seed(0)
+
+    def rn(*shape, dtype=bf, std=1.0):
+        return (torch.randn(*shape, generator=g, device=dev) * std).to(dtype)
+
+    if args.case == "gemm":
+        M, K, N = 8192, 4096, 11008
+        a, w, b = rn(M, K), rn(N, K, std=0.02), rn(N, std=0.02)
+        ms = _time(lambda: X.dense(a, w, True, b, None, "gelu"), args.iters)
+        print(f"gemm {M}x{K}x{N} gelu: {ms:.4f} ms, {2 * M * N * K / ms / 1e9:.1f} TFLOP/s")
+    elif args.case == "gemm_small_m":
+        M, K, N = 256, 4096, 11008
+        a, w, b = rn(M, K), rn(N, K, std=0.02), rn(N, std=0.02)
+        ms = _time(lambda: X.dense(a, w, True, b, None, "silu"), args.iters)
+        print(f"gemm {M}x{K}x{N} silu: {ms:.4f} ms, {2 * M * N * K / ms / 1e9:.1f} TFLOP/s")
+    elif args.case == "gemm_swiglu":
+        M, K, N = 8192, 4096, 11008
+        a, wg, wu = rn(M, K), rn(N, K, std=0.02), rn(N, K, std=0.02)
+        ms = _time(lambda: X.dense_swiglu(a, wg, wu), args.iters)
+        print(f"gemm_swiglu {M}x{K}x{N}: {ms:.4f} ms, {4 * M * N * K / ms / 1e9:.1f} TFLOP/s")
+    elif args.case == "gemm_f32":
+        M, K, N = 16384, 1728, 1024
+        a, w, b = rn(M, K, dtype=torch.float32), rn(N, K, dtype=torch.float32, std=0.02), rn(N, dtype=torch.float32, std=0.02)
+        ms = _time(lambda: X.dense(a, w, True, b, None, "relu"), args.iters)
+        print(f"gemm_f32 {M}x{K}x{N} relu: {ms:.4f} ms, {2 * M * N * K / ms / 1e9:.1f} TFLOP/s")
+    elif args.case == "add_rms_norm":
+        rows, hidden = 32768, 8192
+        x, r, w = rn(rows, hidden), rn(rows, hidden), rn(hidden)
+        ms = _time(lambda: X.add_rms_norm(x, r, w, 1e-6), args.iters)
+        print(f"add_rms_norm (2 outputs) {rows}x{hidden}: {ms:.4f} ms, {8 * rows * hidden / ms / 1e6:.0f} GB/s")
+    elif args.case == "layer_norm":
+        rows, hidden = 32768, 4096
+        x, r, w, b = rn(rows, hidden), rn(rows, hidden), rn(hidden), rn(hidden)
+        ms = _time(lambda: X.add_layer_norm_y(x, r, w, b, 1e-5), args.iters)
+        print(f"add_layer_norm (1 output) {rows}x{hidden}: {ms:.4f} ms, {6 * rows * hidden / ms / 1e6:.0f} GB/s")
+    elif args.case == "sdpa":
+        B, H, S, D = 4, 32, 2048, 128
+        q, k, v = rn(B, H, S, D), rn(B, H, S, D), rn(B, H, S, D)
+        ms = _time(lambda: X.sdpa(q, k, v, None, D ** -0.5, True), args.iters)
+        print(f"sdpa causal {B}x{H}x{S}x{D}: {ms:.4f} ms, {2 * B * H * S * S * D / ms / 1e9:.1f} TFLOP/s")
+    elif args.case == "rope":
+        B, H, S, D = 8, 32, 2048, 128
+        x, cos, sin = rn(B, H, S, D), rn(S, D), rn(S, D)
+        ms = _time(lambda: X.rope(x, cos, sin), args.iters)
+        print(f"rope {B}x{H}x{S}x{D}: {ms:.4f} ms, {4 * x.numel() / ms / 1e6:.0f} GB/s")
+    elif args.case == "swiglu":
+        rows, cols = 16384, 11008
+        a, b = rn(rows, cols), rn(rows, cols)
+        ms = _time(lambda: X.swiglu(a, b), args.iters)
+        print(f"swiglu {rows}x{cols}: {ms:.4f} ms, {6 * rows * cols / ms / 1e6:.0f} GB/s")
+    elif args.case == "gather":
+        rows, F, D, T = 65536, 26, 64, 100000
+        tables = [rn(T, D, dtype=torch.float32, std=0.01) for _ in range(F)]
+        idx = torch.randint(0, T, (rows, F), generator=g, device=dev)
+        mask = torch.rand(rows, 1, generator=g, device=dev) < 0.3
+        ms = _time(lambda: X.gather_stack(tables, idx, mask, True), args.iters)
+        print(f"gather_stack {rows}x{F}x{D}: {ms:.4f} ms, {(2 * rows * F * D * 4 + rows * F * 8) / ms / 1e6:.0f} GB/s")
+    elif args.case == "slice_cat":
+        rows, width = 65536, 4310
+        src = rn(rows, width, dtype=torch.float32)
+        starts = [64 * i for i in range(50)]
+        ends = [s + 64 for s in starts]
+        ms = _time(lambda: X.slice_cat(src, starts, ends, None, False), args.iters)
+        print(f"slice_cat {rows}x{width} -> 50x64: {ms:.4f} ms, {2 * rows * 50 * 64 * 4 / ms / 1e6:.0f} GB/s")
+    if lib.tc_status() != 0:
+        print("WARNING: tensor-core status word is non-zero", file=sys.stderr)
+        return 1
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())
