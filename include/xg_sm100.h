@@ -91,13 +91,14 @@ int xg_layernorm(const void* x, const void* residual, const void* weight, const 
 
 /*
  * Rotate-half rotary embedding: y = x*cos + cat(-x[..., D/2:], x[..., :D/2])*sin.
- * x: [B, H, S, D] addressed by element strides (D contiguous); cos/sin: [S, D] contiguous, same
- * dtype as x; y: [B, H, S, D] contiguous. The reference has no RoPE op; this replaces the
- * 2x slice + neg + cat + 2x mul + add chain that the graph carries (semantics of the aten ops).
+ * x, y: [B, H, S, D], each addressed by element strides (D contiguous), so a [B, S, H, D] buffer
+ * viewed as [B, H, S, D] is read and written in place of a transpose copy; cos/sin: [S, D]
+ * contiguous, same dtype as x. The reference has no RoPE op; this replaces the 2x slice + neg + cat +
+ * 2x mul + add chain that the graph carries (semantics of the aten ops).
  */
 int xg_rope(const void* x, const void* cos, const void* sin, void* y, int64_t B, int64_t H, int64_t S,
-            int64_t D, int64_t x_stride_b, int64_t x_stride_h, int64_t x_stride_s, int dtype,
-            void* stream);
+            int64_t D, int64_t x_stride_b, int64_t x_stride_h, int64_t x_stride_s, int64_t y_stride_b,
+            int64_t y_stride_h, int64_t y_stride_s, int dtype, void* stream);
 
 /*
  * SwiGLU: out = silu(gate) * up, row-major [rows, cols] with separate row strides (a packed

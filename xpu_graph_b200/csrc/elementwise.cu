@@ -15,40 +15,42 @@ struct RopeParams {
     const void* sin;
     void* y;
     int64_t B, H, S, D;
-    int64_t sb, sh, ss;
+    int64_t sb, sh, ss;     // x strides (elements)
+    int64_t yb, yh, ys;     // y strides (elements)
 };
 
+// grid.x covers (s, half-vector) of one (b, h) plane with 32-bit index math; grid.y strides over planes.
 template <typename T>
 __global__ void __launch_bounds__(256) rope_vec_kernel(const RopeParams p) {
     constexpr int EPV = Vec16<T>::N;
     const int hv_per_row = (int)(p.D / 2 / EPV);
-    const int64_t total = p.B * p.H * p.S * hv_per_row;
-    const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-    if (idx >= total) return;
-    const int hv = (int)(idx % hv_per_row);
-    const int64_t row = idx / hv_per_row;  // (b, h, s) flattened
-    const int64_t s = row % p.S;
-    const int64_t bh = row / p.S;
-    const int64_t h = bh % p.H;
-    const int64_t b = bh / p.H;
+    const uint32_t per_plane = (uint32_t)p.S * (uint32_t)hv_per_row;
+    const uint32_t idx = blockIdx.x * 256u + threadIdx.x;
+    if (idx >= per_plane) return;
+    const uint32_t s = idx / (uint32_t)hv_per_row;
+    const uint32_t hv = idx - s * (uint32_t)hv_per_row;
     const int64_t half = p.D / 2;
-    const T* xr = reinterpret_cast<const T*>(p.x) + b * p.sb + h * p.sh + s * p.ss;
-    const T* cr = reinterpret_cast<const T*>(p.cos) + s * p.D;
-    const T* sr = reinterpret_cast<const T*>(p.sin) + s * p.D;
-    T* yr = reinterpret_cast<T*>(p.y) + row * p.D;
     const int64_t j = (int64_t)hv * EPV;
-    const Vec16<T> x1 = ld16_stream(xr + j), x2 = ld16_stream(xr + j + half);
+    const T* cr = reinterpret_cast<const T*>(p.cos) + (int64_t)s * p.D;
+    const T* sr = reinterpret_cast<const T*>(p.sin) + (int64_t)s * p.D;
     const Vec16<T> c1 = ld16(cr + j), c2 = ld16(cr + j + half);
     const Vec16<T> s1 = ld16(sr + j), s2 = ld16(sr + j + half);
-    Vec16<T> o1, o2;
+    const int64_t planes = p.B * p.H;
+    for (int64_t bh = blockIdx.y; bh < planes; bh += gridDim.y) {
+        const int64_t b = bh / p.H, h = bh - b * p.H;
+        const T* xr = reinterpret_cast<const T*>(p.x) + b * p.sb + h * p.sh + (int64_t)s * p.ss;
+        T* yr = reinterpret_cast<T*>(p.y) + b * p.yb + h * p.yh + (int64_t)s * p.ys;
+        const Vec16<T> x1 = ld16_stream(xr + j), x2 = ld16_stream(xr + j + half);
+        Vec16<T> o1, o2;
 #pragma unroll
-    for (int i = 0; i < EPV; ++i) {
-        const float a = Cvt<T>::to_f(x1.v[i]), bb = Cvt<T>::to_f(x2.v[i]);
-        o1.v[i] = Cvt<T>::from_f(a * Cvt<T>::to_f(c1.v[i]) - bb * Cvt<T>::to_f(s1.v[i]));
-        o2.v[i] = Cvt<T>::from_f(bb * Cvt<T>::to_f(c2.v[i]) + a * Cvt<T>::to_f(s2.v[i]));
+        for (int i = 0; i < EPV; ++i) {
+            const float a = Cvt<T>::to_f(x1.v[i]), bb = Cvt<T>::to_f(x2.v[i]);
+            o1.v[i] = Cvt<T>::from_f(a * Cvt<T>::to_f(c1.v[i]) - bb * Cvt<T>::to_f(s1.v[i]));
+            o2.v[i] = Cvt<T>::from_f(bb * Cvt<T>::to_f(c2.v[i]) + a * Cvt<T>::to_f(s2.v[i]));
+        }
+        st16(yr + j, o1);
+        st16(yr + j + half, o2);
     }
-    st16(yr + j, o1);
-    st16(yr + j + half, o2);
 }
 
 template <typename T>
@@ -66,7 +68,7 @@ __global__ void __launch_bounds__(256) rope_scalar_kernel(const RopeParams p) {
     const T* xr = reinterpret_cast<const T*>(p.x) + b * p.sb + h * p.sh + s * p.ss;
     const T* cr = reinterpret_cast<const T*>(p.cos) + s * p.D;
     const T* sr = reinterpret_cast<const T*>(p.sin) + s * p.D;
-    T* yr = reinterpret_cast<T*>(p.y) + row * p.D;
+    T* yr = reinterpret_cast<T*>(p.y) + b * p.yb + h * p.yh + s * p.ys;
     const float a = Cvt<T>::to_f(xr[j]), bb = Cvt<T>::to_f(xr[j + half]);
     yr[j] = Cvt<T>::from_f(a * Cvt<T>::to_f(cr[j]) - bb * Cvt<T>::to_f(sr[j]));
     yr[j + half] = Cvt<T>::from_f(bb * Cvt<T>::to_f(cr[j + half]) + a * Cvt<T>::to_f(sr[j + half]));
@@ -77,12 +79,26 @@ int launch_rope(const RopeParams& p, cudaStream_t st) {
     constexpr int EPV = Vec16<T>::N;
     const int64_t half = p.D / 2;
     const bool vec_ok = (half % EPV == 0) && aligned16(p.x) && aligned16(p.cos) && aligned16(p.sin) && aligned16(p.y) &&
-                        p.sb % EPV == 0 && p.sh % EPV == 0 && p.ss % EPV == 0;
-    const int64_t total = p.B * p.H * p.S * (vec_ok ? half / EPV : half);
-    const int64_t grid = (total + 255) / 256;
-    if (grid > 0x7fffffffLL) return fail(XG_ERR_TOO_LARGE, "xg_rope: tensor too large");
-    if (vec_ok) rope_vec_kernel<T><<<(unsigned)grid, 256, 0, st>>>(p);
-    else rope_scalar_kernel<T><<<(unsigned)grid, 256, 0, st>>>(p);
+                        p.sb % EPV == 0 && p.sh % EPV == 0 && p.ss % EPV == 0 && p.yb % EPV == 0 && p.yh % EPV == 0 &&
+                        p.ys % EPV == 0 && p.S * (half / EPV) < 0x7fffffffLL;
+    if (vec_ok) {
+        const int64_t per_plane = p.S * (half / EPV);
+        const int64_t gx = (per_plane + 255) / 256;
+        const int64_t planes = p.B * p.H;
+        // enough CTAs to fill the GPU several times over, the rest of the planes are looped over
+        int64_t gy = planes;
+        const int64_t want = 32LL * num_sms();
+        if (gx * gy > want) gy = (want + gx - 1) / gx;
+        if (gy < 1) gy = 1;
+        if (gy > 65535) gy = 65535;
+        if (gy > planes) gy = planes;
+        rope_vec_kernel<T><<<dim3((unsigned)gx, (unsigned)gy), 256, 0, st>>>(p);
+    } else {
+        const int64_t total = p.B * p.H * p.S * half;
+        const int64_t grid = (total + 255) / 256;
+        if (grid > 0x7fffffffLL) return fail(XG_ERR_TOO_LARGE, "xg_rope: tensor too large");
+        rope_scalar_kernel<T><<<(unsigned)grid, 256, 0, st>>>(p);
+    }
     return check_launch("xg_rope");
 }
 
@@ -96,8 +112,13 @@ struct SwigluParams {
     int64_t rows, cols, ldg, ldu, ldo;
 };
 
-// expf (not __expf): the fp32 path must stay within 1e-5 relative of aten's silu.
-__device__ __forceinline__ float silu_f(float g) { return g / (1.0f + expf(-g)); }
+// fp32 tensors use expf and a true division (the fp32 path must stay within 1e-5 relative of aten's
+// silu); 16-bit tensors use the fast intrinsics, whose error is far below half a bf16/f16 ulp.
+template <typename T>
+__device__ __forceinline__ float silu_f(float g) {
+    if (sizeof(T) == 4) return g / (1.0f + expf(-g));
+    return __fdividef(g, 1.0f + __expf(-g));
+}
 
 template <typename T, int UNROLL>
 __global__ void __launch_bounds__(256) swiglu_vec_kernel(const SwigluParams p) {
@@ -125,7 +146,7 @@ __global__ void __launch_bounds__(256) swiglu_vec_kernel(const SwigluParams p) {
             Vec16<T> o;
 #pragma unroll
             for (int i = 0; i < EPV; ++i)
-                o.v[i] = Cvt<T>::from_f(silu_f(Cvt<T>::to_f(g[k].v[i])) * Cvt<T>::to_f(u[k].v[i]));
+                o.v[i] = Cvt<T>::from_f(silu_f<T>(Cvt<T>::to_f(g[k].v[i])) * Cvt<T>::to_f(u[k].v[i]));
             st16(reinterpret_cast<T*>(p.out) + off_o[k], o);
         }
     }
@@ -139,7 +160,7 @@ __global__ void __launch_bounds__(256) swiglu_scalar_kernel(const SwigluParams p
     const int64_t r = idx / p.cols, c = idx - r * p.cols;
     const float g = Cvt<T>::to_f(reinterpret_cast<const T*>(p.gate)[r * p.ldg + c]);
     const float u = Cvt<T>::to_f(reinterpret_cast<const T*>(p.up)[r * p.ldu + c]);
-    reinterpret_cast<T*>(p.out)[r * p.ldo + c] = Cvt<T>::from_f(silu_f(g) * u);
+    reinterpret_cast<T*>(p.out)[r * p.ldo + c] = Cvt<T>::from_f(silu_f<T>(g) * u);
 }
 
 template <typename T>
@@ -165,13 +186,14 @@ int launch_swiglu(const SwigluParams& p, cudaStream_t st) {
 }  // namespace xg
 
 extern "C" int xg_rope(const void* x, const void* cos, const void* sin, void* y, int64_t B, int64_t H, int64_t S,
-                       int64_t D, int64_t x_stride_b, int64_t x_stride_h, int64_t x_stride_s, int dtype, void* stream) {
+                       int64_t D, int64_t x_stride_b, int64_t x_stride_h, int64_t x_stride_s, int64_t y_stride_b,
+                       int64_t y_stride_h, int64_t y_stride_s, int dtype, void* stream) {
     using namespace xg;
     if (!x || !cos || !sin || !y) return fail(XG_ERR_INVALID_ARG, "xg_rope: null pointer");
     if (B < 0 || H < 0 || S < 0 || D <= 0 || (D & 1)) return fail(XG_ERR_INVALID_ARG, "xg_rope: bad extents (D must be even)");
     if (dtype_size(dtype) == 0) return fail(XG_ERR_INVALID_ARG, "xg_rope: bad dtype %d", dtype);
     if (B * H * S == 0) return XG_OK;
-    RopeParams p{x, cos, sin, y, B, H, S, D, x_stride_b, x_stride_h, x_stride_s};
+    RopeParams p{x, cos, sin, y, B, H, S, D, x_stride_b, x_stride_h, x_stride_s, y_stride_b, y_stride_h, y_stride_s};
     cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
     switch (dtype) {
         case XG_F32: return launch_rope<float>(p, st);

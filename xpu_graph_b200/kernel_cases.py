@@ -63,7 +63,7 @@ def main(argv=None):
         ms = _time(lambda: X.dense(a, w, True, b, None, "relu"), args.iters)
         print(f"gemm_f32 {M}x{K}x{N} relu: {ms:.4f} ms, {2 * M * N * K / ms / 1e9:.1f} TFLOP/s")
     elif args.case == "add_rms_norm":
-        rows, hidden = 32768, 8192
+        rows, hidden = 16384, 8192
         x, r, w = rn(rows, hidden), rn(rows, hidden), rn(hidden)
         ms = _time(lambda: X.add_rms_norm(x, r, w, 1e-6), args.iters)
         print(f"add_rms_norm (2 outputs) {rows}x{hidden}: {ms:.4f} ms, {8 * rows * hidden / ms / 1e6:.0f} GB/s")

@@ -38,7 +38,7 @@ SIGNATURES = {
     "xg_layernorm": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64,
                              c_int64, c_float, c_int, c_int, c_void_p]),
     "xg_rope": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64, c_int64, c_int64,
-                        c_int64, c_int, c_void_p]),
+                        c_int64, c_int64, c_int64, c_int64, c_int, c_void_p]),
     "xg_swiglu": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64, c_int64, c_int, c_void_p]),
     "xg_gemm_bias_act": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64,
                                  c_int64, c_int64, c_int64, c_int, c_int, c_int, c_void_p]),

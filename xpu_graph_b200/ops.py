@@ -93,6 +93,16 @@ def _row_stride(x2: torch.Tensor) -> int:
     return x2.stride(0) if x2.shape[0] > 1 else max(x2.stride(0), x2.shape[1])
 
 
+def _empty_like_layout(x: torch.Tensor) -> torch.Tensor:
+    """[B, H, S, D] output that keeps x's memory layout when x is a [B, S, H, D] buffer viewed with
+    dims 1 and 2 swapped (so that the transpose + reshape after attention stays a view); contiguous
+    otherwise."""
+    B, H, S, D = x.shape
+    if x.stride(3) == 1 and x.stride(1) == D and x.stride(2) == H * D and x.stride(0) == S * H * D and H > 1 and S > 1:
+        return torch.empty((B, S, H, D), dtype=x.dtype, device=x.device).transpose(1, 2)
+    return torch.empty((B, H, S, D), dtype=x.dtype, device=x.device)
+
+
 def _coef(w: torch.Tensor, dtype: torch.dtype) -> torch.Tensor:
     """Affine coefficients are passed as fp32 or as the activation dtype."""
     if w.dtype not in (torch.float32, dtype):
@@ -210,9 +220,9 @@ def rope(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> torch.Tensor:
         x = x.contiguous()
     cos2 = cos.reshape(S, D).to(x.dtype).contiguous()
     sin2 = sin.reshape(S, D).to(x.dtype).contiguous()
-    y = torch.empty((B, H, S, D), dtype=x.dtype, device=x.device)
+    y = _empty_like_layout(x)
     rc = _lib.load().xg_rope(_ptr(x), _ptr(cos2), _ptr(sin2), _ptr(y), B, H, S, D, x.stride(0), x.stride(1), x.stride(2),
-                             _code(x.dtype), _stream(x))
+                             y.stride(0), y.stride(1), y.stride(2), _code(x.dtype), _stream(x))
     _lib.check(rc, "xg_rope")
     _bump()
     return y
@@ -220,7 +230,7 @@ def rope(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> torch.Tensor:
 
 @rope.register_fake
 def _(x, cos, sin):
-    return torch.empty(x.shape, dtype=x.dtype, device=x.device)
+    return _empty_like_layout(x)
 
 
 @torch.library.custom_op(f"{NS}::swiglu", mutates_args=(), device_types="cuda")
@@ -360,7 +370,7 @@ def sdpa(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, attn_mask: Optional[
         m = m.expand(B, H, Sq, Skv)
         attn_mask = m
         mstr = _lib.i64_array(m.stride())
-    out = torch.empty((B, H, Sq, D), dtype=q.dtype, device=q.device)
+    out = _empty_like_layout(q)
     rc = _lib.load().xg_sdpa_fwd(_ptr(q), _ptr(k), _ptr(v), _ptr(attn_mask), _ptr(out), B, H, Sq, Skv, D,
                                  _lib.i64_array(q.stride()[:3]), _lib.i64_array(k.stride()[:3]),
                                  _lib.i64_array(v.stride()[:3]), _lib.i64_array(out.stride()[:3]), mstr, float(scale),
@@ -372,7 +382,7 @@ def sdpa(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, attn_mask: Optional[
 
 @sdpa.register_fake
 def _(q, k, v, attn_mask, scale, is_causal):
-    return torch.empty(q.shape, dtype=q.dtype, device=q.device)
+    return _empty_like_layout(q if q.stride(3) == 1 else q.contiguous())
 
 
 # --------------------------------------------------------------------------------------------

@@ -1,0 +1,558 @@
+"""Target patterns of ``cuda_sm100``: FX rewrites that xpu_graph's own patterns do not perform.
+
+xpu_graph's structure patterns (CustomRMSNorm, CustomLayerNorm, CustomDenseLayer, FusedSlice, ...)
+already route to this target's modules through ``get_structure_replacements``. The classes below
+cover the graph forms that reach the target un-matched on current PyTorch (SURVEY of the graphs:
+``aten.native_layer_norm`` from ``nn.LayerNorm``, pre-fused ``_scaled_dot_product_*`` ops, the
+rotate-half RoPE chain, ``mul(silu(mm), mm)``, residual adds next to a dense layer or a norm, and
+embedding + where + stack). Each is a ``Pattern`` subclass (passes/patterns/pattern.py:26-49) so it is
+run, linted, recompiled and logged ("Pattern.<Class> changed graph") by the pass manager like any
+built-in pattern; each rewrites aten nodes into ``call_module`` nodes only, so no pattern can match
+its own output and the fix-point loop (passes/pass_manager.py:62-82) terminates.
+"""
+from __future__ import annotations
+
+import operator
+from typing import Optional
+
+import torch
+from torch import fx
+from xpu_graph.config import OptLevel
+from xpu_graph.passes.patterns.pattern import Pattern, PatternGroup
+
+from .. import modules as M
+
+aten = torch.ops.aten
+INT64_MAX = 9223372036854775807
+DENSE_NAME = "custom_dense_layer_replacement"  # sub-module name used by structure/custom_denselayer.py:82
+
+
+# ---- helpers ---------------------------------------------------------------------------------
+def _val(node):
+    return node.meta.get("val") if isinstance(node, fx.Node) else None
+
+
+def _is(node, *targets) -> bool:
+    return isinstance(node, fx.Node) and node.op == "call_function" and node.target in targets
+
+
+def _tensor_ok(v, dims: Optional[int] = None) -> bool:
+    if not isinstance(v, torch.Tensor):
+        return False
+    if v.dtype not in M._SUPPORTED or v.device.type not in M.ALLOWED_DEVICE_TYPES:
+        return False
+    return dims is None or v.dim() == dims
+
+
+def _static(shape) -> bool:
+    return all(isinstance(s, int) for s in shape)
+
+
+def _only_user(node: fx.Node, user: fx.Node) -> bool:
+    return len(node.users) == 1 and next(iter(node.users)) is user
+
+
+def _module_call(gm: fx.GraphModule, node, cls) -> bool:
+    if not (isinstance(node, fx.Node) and node.op == "call_module"):
+        return False
+    try:
+        return isinstance(gm.get_submodule(node.target), cls)
+    except AttributeError:
+        return False
+
+
+def _ensure(gm: fx.GraphModule, name: str, factory) -> str:
+    if not hasattr(gm, name):
+        gm.add_submodule(name, factory())
+    return name
+
+
+def _fill_meta(gm: fx.GraphModule, node: fx.Node) -> None:
+    """Give a freshly inserted node its fake value right away (the pass runs under the compiler's fake
+    mode), so that later patterns of the same sweep can inspect it; on any problem the value is left
+    for the next FakeTensorProp (passes/fake_tensor_prop.py:39-69)."""
+    try:
+        args = fx.map_arg(node.args, lambda n: n.meta["val"])
+        if node.op == "call_module":
+            node.meta["val"] = gm.get_submodule(node.target)(*args)
+        elif node.op == "call_function":
+            node.meta["val"] = node.target(*args, **node.kwargs)
+    except Exception:
+        node.meta.pop("val", None)
+
+
+# ---- LayerNorm as lowered from nn.LayerNorm ---------------------------------------------------------
+class FusedNativeLayerNorm(Pattern):
+    """aten.native_layer_norm(x, [H], w, b, eps)[0] -> LayerNormModule. The reference's FusedLayerNorm
+    (common/fuse_layernorm.py:153-212) only matches the decomposed mean/var chain."""
+
+    _opt_level = OptLevel.level2
+
+    def process(self, gm: fx.GraphModule) -> bool:
+        changed = False
+        for node in list(gm.graph.nodes):
+            if not _is(node, aten.native_layer_norm.default) or len(node.args) != 5:
+                continue
+            x, shape, w, b, eps = node.args
+            xv = _val(x)
+            if w is None or b is None or not _tensor_ok(xv) or xv.dim() < 1 or list(shape) != [xv.shape[-1]]:
+                continue
+            users = list(node.users)
+            if not all(_is(u, operator.getitem) for u in users):
+                continue
+            if any(u.args[1] != 0 and len(u.users) > 0 for u in users):
+                continue  # mean / rstd are consumed: leave it alone
+            _ensure(gm, "xg_layer_norm", M.LayerNormModule)
+            with gm.graph.inserting_before(node):
+                new = gm.graph.call_module("xg_layer_norm", (x, w, b, eps))
+            _fill_meta(gm, new)
+            for u in users:
+                if u.args[1] == 0:
+                    u.replace_all_uses_with(new)
+                gm.graph.erase_node(u)
+            gm.graph.erase_node(node)
+            changed = True
+        return changed
+
+
+# ---- scaled dot product attention ----------------------------------------------------------------------
+def _sdpa_targets():
+    names = ["scaled_dot_product_attention", "_scaled_dot_product_flash_attention_for_cpu",
+             "_scaled_dot_product_flash_attention", "_scaled_dot_product_efficient_attention",
+             "_scaled_dot_product_cudnn_attention"]
+    out = {}
+    for n in names:
+        pkt = getattr(aten, n, None)
+        if pkt is not None and hasattr(pkt, "default"):
+            out[pkt.default] = (n == "scaled_dot_product_attention")
+    return out
+
+
+class FusedSdpa(Pattern):
+    """aten.scaled_dot_product_attention (as emitted by common/fuse_scaled_dot_product_attention.py:230-234)
+    and the pre-fused _scaled_dot_product_* forms that F.scaled_dot_product_attention lowers to
+    -> SDPAModule. Dropout, GQA and consumed log-sum-exp outputs are left untouched."""
+
+    _opt_level = OptLevel.level2
+
+    def process(self, gm: fx.GraphModule) -> bool:
+        from torch.fx.operator_schemas import normalize_function
+
+        targets = _sdpa_targets()
+        changed = False
+        for node in list(gm.graph.nodes):
+            if not (isinstance(node, fx.Node) and node.op == "call_function" and node.target in targets):
+                continue
+            single_output = targets[node.target]
+            try:
+                norm = normalize_function(node.target, node.args, node.kwargs, normalize_to_only_use_kwargs=True)
+            except Exception:
+                norm = None
+            if norm is None:
+                continue
+            kw = norm.kwargs
+            q, k, v = kw.get("query"), kw.get("key"), kw.get("value")
+            mask = kw.get("attn_mask", kw.get("attn_bias"))
+            scale = kw.get("scale")
+            if kw.get("dropout_p", 0.0) != 0.0 or kw.get("enable_gqa", False) or isinstance(scale, fx.Node):
+                continue
+            causal = bool(kw.get("is_causal", False))
+            qv, kv, vv = _val(q), _val(k), _val(v)
+            if not (_tensor_ok(qv, 4) and _tensor_ok(kv, 4) and _tensor_ok(vv, 4)):
+                continue
+            if not (qv.dtype == kv.dtype == vv.dtype) or qv.shape[1] != kv.shape[1] or qv.shape[-1] > 256:
+                continue
+            if qv.shape[-1] != vv.shape[-1] or (mask is not None and causal):
+                continue
+            if single_output:
+                outs = [node]
+            else:
+                users = list(node.users)
+                if not all(_is(u, operator.getitem) for u in users):
+                    continue
+                if any(u.args[1] != 0 and len(u.users) > 0 for u in users):
+                    continue
+                outs = [u for u in users if u.args[1] == 0]
+            _ensure(gm, "xg_sdpa", M.SDPAModule)
+            with gm.graph.inserting_before(node):
+                new = gm.graph.call_module("xg_sdpa", (q, k, v, mask, scale, causal))
+            _fill_meta(gm, new)
+            for o in outs:
+                o.replace_all_uses_with(new)
+            if not single_output:
+                for u in list(node.users):
+                    gm.graph.erase_node(u)
+            gm.graph.erase_node(node)
+            changed = True
+        return changed
+
+
+# ---- rotate-half RoPE --------------------------------------------------------------------------------------
+class FusedRoPE(Pattern):
+    """x*cos + cat(-x[..., D/2:], x[..., :D/2])*sin on a 4-D x -> RopeModule (one pass instead of seven)."""
+
+    _opt_level = OptLevel.level2
+
+    @staticmethod
+    def _match_rotate_half(cat: fx.Node):
+        if not _is(cat, aten.cat.default):
+            return None
+        parts = cat.args[0]
+        dim = cat.args[1] if len(cat.args) > 1 else 0
+        if len(parts) != 2 or not _is(parts[0], aten.neg.default):
+            return None
+        hi, lo = parts[0].args[0], parts[1]
+        if not (_is(hi, aten.slice.Tensor) and _is(lo, aten.slice.Tensor)) or hi.args[0] is not lo.args[0]:
+            return None
+        x = hi.args[0]
+        xv = _val(x)
+        if not _tensor_ok(xv, 4) or not _static(xv.shape):
+            return None
+        D = xv.shape[-1]
+        if D % 2 or dim not in (-1, 3):
+            return None
+
+        def sl(n):
+            a = list(n.args) + [None] * (5 - len(n.args))
+            d = a[1] if a[1] is not None else 0
+            start = a[2] if a[2] is not None else 0
+            end = a[3] if a[3] is not None else INT64_MAX
+            step = a[4] if a[4] is not None else 1
+            return d, start, min(end, D) if isinstance(end, int) else end, step
+
+        if sl(hi) != (dim if dim == 3 else -1, D // 2, D, 1) and sl(hi) != (3, D // 2, D, 1) and sl(hi) != (-1, D // 2, D, 1):
+            return None
+        if sl(lo)[1:] != (0, D // 2, 1) or sl(lo)[0] not in (-1, 3):
+            return None
+        if not (_only_user(hi, parts[0]) and _only_user(parts[0], cat) and _only_user(lo, cat)):
+            return None
+        return x
+
+    def process(self, gm: fx.GraphModule) -> bool:
+        changed = False
+        for node in list(gm.graph.nodes):
+            if not _is(node, aten.add.Tensor) or node.kwargs:
+                continue
+            m1, m2 = node.args
+            if not (_is(m1, aten.mul.Tensor) and _is(m2, aten.mul.Tensor)):
+                continue
+            found = None
+            for ma, mb in ((m1, m2), (m2, m1)):
+                for cat, sin in ((mb.args[0], mb.args[1]), (mb.args[1], mb.args[0])):
+                    x = self._match_rotate_half(cat) if isinstance(cat, fx.Node) else None
+                    if x is None:
+                        continue
+                    for xa, cos in ((ma.args[0], ma.args[1]), (ma.args[1], ma.args[0])):
+                        if xa is x and isinstance(cos, fx.Node) and isinstance(sin, fx.Node):
+                            found = (x, cos, sin, ma, mb, cat)
+                if found:
+                    break
+            if not found:
+                continue
+            x, cos, sin, ma, mb, cat = found
+            xv, cv, sv = _val(x), _val(cos), _val(sin)
+            S, D = xv.shape[2], xv.shape[3]
+            if not (isinstance(cv, torch.Tensor) and isinstance(sv, torch.Tensor)):
+                continue
+            if cv.numel() != S * D or sv.numel() != S * D or tuple(cv.shape[-2:]) != (S, D) or tuple(sv.shape[-2:]) != (S, D):
+                continue
+            if not (_only_user(ma, node) and _only_user(mb, node) and _only_user(cat, mb)):
+                continue
+            _ensure(gm, "xg_rope", M.RopeModule)
+            with gm.graph.inserting_before(node):
+                new = gm.graph.call_module("xg_rope", (x, cos, sin))
+            _fill_meta(gm, new)
+            node.replace_all_uses_with(new)
+            # erase the dead chain, consumers first
+            neg = cat.args[0][0]
+            hi, lo = neg.args[0], cat.args[0][1]
+            for dead in (node, ma, mb, cat, neg, hi, lo):
+                if len(dead.users) == 0:
+                    gm.graph.erase_node(dead)
+            changed = True
+        return changed
+
+
+# ---- SwiGLU ------------------------------------------------------------------------------------------------
+class FusedSwiGLU(Pattern):
+    """mul(silu(x @ Wg^T), x @ Wu^T) -> one dual GEMM with the SwiGLU epilogue (DenseSwiGLUModule);
+    mul(silu(g), u) otherwise -> SwiGLUModule (the NPU target fuses the packed form,
+    targets/npu/fuse_silu_mul.py:21-69)."""
+
+    _opt_level = OptLevel.level2
+    _pattern_group = PatternGroup.GROUP1
+
+    def process(self, gm: fx.GraphModule) -> bool:
+        changed = False
+        for node in list(gm.graph.nodes):
+            if not _is(node, aten.mul.Tensor) or len(node.args) != 2:
+                continue
+            a, b = node.args
+            if not (isinstance(a, fx.Node) and isinstance(b, fx.Node)):
+                continue
+            done = False
+            for g, u in ((a, b), (b, a)):
+                if (_module_call(gm, g, M.DenseLayerModule) and _module_call(gm, u, M.DenseLayerModule)
+                        and g.target == DENSE_NAME and u.target == DENSE_NAME):
+                    gx, gw, gt, gb, gact = g.args
+                    ux, uw, ut, ub, uact = u.args
+                    wv, uv, xv = _val(gw), _val(uw), _val(gx)
+                    if (gact == "silu" and uact == "none" and gx is ux and gt and ut and gb is None and ub is None
+                            and _only_user(g, node) and _only_user(u, node) and _tensor_ok(xv, 2)
+                            and xv.dtype in (torch.bfloat16, torch.float16) and isinstance(wv, torch.Tensor)
+                            and isinstance(uv, torch.Tensor) and wv.shape == uv.shape and xv.shape[1] % 8 == 0):
+                        _ensure(gm, "xg_dense_swiglu", M.DenseSwiGLUModule)
+                        with gm.graph.inserting_before(node):
+                            new = gm.graph.call_module("xg_dense_swiglu", (gx, gw, uw))
+                        _fill_meta(gm, new)
+                        node.replace_all_uses_with(new)
+                        for dead in (node, g, u):
+                            gm.graph.erase_node(dead)
+                        changed = done = True
+                        break
+                if _is(g, aten.silu.default) and _only_user(g, node):
+                    gv, uv = _val(g.args[0]), _val(u)
+                    if _tensor_ok(gv) and _tensor_ok(uv) and gv.shape == uv.shape and gv.dtype == uv.dtype and gv.dim() >= 1:
+                        _ensure(gm, "xg_swiglu", M.SwiGLUModule)
+                        with gm.graph.inserting_before(node):
+                            new = gm.graph.call_module("xg_swiglu", (g.args[0], u))
+                        _fill_meta(gm, new)
+                        node.replace_all_uses_with(new)
+                        gm.graph.erase_node(node)
+                        gm.graph.erase_node(g)
+                        changed = done = True
+                        break
+            if done:
+                continue
+        return changed
+
+
+# ---- residual add folded into the dense layer's epilogue ----------------------------------------------------
+class FusedDenseResidual(Pattern):
+    """add(dense(x, W, bias), r) (optionally through a reshape of the dense output) -> the dense layer
+    with r as its full [M, N] addend; the MLU dense module takes the same addend as a 2-D bias
+    (dense_layer_modules.py:43-56)."""
+
+    _opt_level = OptLevel.level2
+    _pattern_group = PatternGroup.GROUP1
+
+    def process(self, gm: fx.GraphModule) -> bool:
+        changed = False
+        for node in list(gm.graph.nodes):
+            if not _is(node, aten.add.Tensor) or node.kwargs or len(node.args) != 2:
+                continue
+            for d_side, other in ((node.args[0], node.args[1]), (node.args[1], node.args[0])):
+                if not (isinstance(d_side, fx.Node) and isinstance(other, fx.Node)):
+                    continue
+                dense, via = d_side, None
+                if _is(d_side, aten.reshape.default, aten.view.default, aten._unsafe_view.default) and _only_user(d_side, node):
+                    dense, via = d_side.args[0], d_side
+                if not (_module_call(gm, dense, M.DenseLayerModule) and dense.target == DENSE_NAME):
+                    continue
+                if not _only_user(dense, via if via is not None else node):
+                    continue
+                x, w, wt, bias, act = dense.args
+                dv, ov, av, bv = _val(dense), _val(other), _val(node), _val(bias)
+                if act != "none" or not (_tensor_ok(dv, 2) and _tensor_ok(ov) and isinstance(av, torch.Tensor)):
+                    continue
+                Mr, N = dv.shape
+                if not _static(dv.shape) or not _static(ov.shape) or ov.dtype != dv.dtype or ov.dim() < 1:
+                    continue
+                if ov.numel() != Mr * N or ov.shape[-1] != N or av.numel() != Mr * N:
+                    continue
+                if bias is not None and not (isinstance(bv, torch.Tensor) and bv.numel() == N and bv.dim() <= 2):
+                    continue
+                _ensure(gm, "xg_dense_residual", M.DenseResidualModule)
+                with gm.graph.inserting_before(node):
+                    r2 = other if ov.dim() == 2 else gm.graph.call_function(aten.reshape.default, (other, [Mr, N]))
+                    if r2 is not other:
+                        _fill_meta(gm, r2)
+                    new = gm.graph.call_module("xg_dense_residual", (x, w, wt, bias, r2, "none"))
+                    _fill_meta(gm, new)
+                    out = new if list(av.shape) == [Mr, N] else gm.graph.call_function(aten.reshape.default, (new, list(av.shape)))
+                    if out is not new:
+                        _fill_meta(gm, out)
+                node.replace_all_uses_with(out)
+                gm.graph.erase_node(node)
+                if via is not None:
+                    gm.graph.erase_node(via)
+                gm.graph.erase_node(dense)
+                changed = True
+                break
+        return changed
+
+
+# ---- residual add folded into the norm ---------------------------------------------------------------------
+class FusedAddNorm(Pattern):
+    """norm(a + b) -> one kernel that also returns the sum when it has other users
+    (store_output_before_norm, targets/mlu/fuse_add_norm.py:118-121, 150-180; NPU form
+    targets/npu/fuse_add_rmsnorm.py:28-115)."""
+
+    _opt_level = OptLevel.level2
+    _pattern_group = PatternGroup.GROUP2
+
+    def process(self, gm: fx.GraphModule) -> bool:
+        changed = False
+        for node in list(gm.graph.nodes):
+            is_rms = _module_call(gm, node, M.RMSNormModule)
+            is_ln = _module_call(gm, node, M.LayerNormModule)
+            if not (is_rms or is_ln):
+                continue
+            add = node.args[0]
+            if not _is(add, aten.add.Tensor) or add.kwargs or len(add.args) != 2:
+                continue
+            a, b = add.args
+            av, bv, sv = _val(a), _val(b), _val(add)
+            if not (_tensor_ok(av) and _tensor_ok(bv) and isinstance(sv, torch.Tensor)):
+                continue
+            if av.shape != bv.shape or av.dtype != bv.dtype or av.dtype != sv.dtype:
+                continue
+            store = len(add.users) > 1
+            if is_rms:
+                name = _ensure(gm, "xg_add_rms_norm" if store else "xg_add_rms_norm_y", lambda: M.AddRMSNormModule(store))
+                args = (a, b) + tuple(node.args[1:])
+            else:
+                name = _ensure(gm, "xg_add_layer_norm" if store else "xg_add_layer_norm_y", lambda: M.AddLayerNormModule(store))
+                args = (a, b) + tuple(node.args[1:])
+            with gm.graph.inserting_before(node):
+                new = gm.graph.call_module(name, args)
+                _fill_meta(gm, new)
+                if store:
+                    y = gm.graph.call_function(operator.getitem, (new, 0))
+                    s = gm.graph.call_function(operator.getitem, (new, 1))
+                    _fill_meta(gm, y)
+                    _fill_meta(gm, s)
+                else:
+                    y, s = new, None
+            node.replace_all_uses_with(y)
+            gm.graph.erase_node(node)
+            if store:
+                add.replace_all_uses_with(s, delete_user_cb=lambda u: u is not new)
+            if len(add.users) == 0:
+                gm.graph.erase_node(add)
+            changed = True
+        return changed
+
+
+# ---- embedding lookups + where + stack -------------------------------------------------------------------------
+class FusedEmbeddingStack(Pattern):
+    """stack([embedding(T_f, idx[:, f]) ...]) with the optional where(mask, 0, .) that the common
+    CombinePointwiseSink pass (common/combine_pointwise_sink.py:21-95) hoists above the un-bind/re-stack
+    -> GatherStackModule. The reference leaves the F lookups un-fused; its nearest relative is
+    torch_mlu.emb_concat (targets/mlu/structure_replacements/__init__.py:136)."""
+
+    _opt_level = OptLevel.level1
+
+    @staticmethod
+    def _match_lookups(stack0: fx.Node):
+        if not _is(stack0, aten.stack.default):
+            return None
+        embs = stack0.args[0]
+        dim = stack0.args[1] if len(stack0.args) > 1 else 0
+        if dim != 0 or len(embs) < 2:
+            return None
+        tables, idx = [], None
+        for f, e in enumerate(embs):
+            if not _is(e, aten.embedding.default) or len(e.args) != 2 or e.kwargs or not _only_user(e, stack0):
+                return None
+            t, sel = e.args
+            if not _is(sel, aten.select.int) or sel.args[1] != 1 or sel.args[2] != f:
+                return None
+            if idx is None:
+                idx = sel.args[0]
+            if sel.args[0] is not idx:
+                return None
+            tables.append(t)
+        iv = _val(idx)
+        tv = [_val(t) for t in tables]
+        if not isinstance(iv, torch.Tensor) or iv.dim() != 2 or iv.dtype != torch.int64 or iv.shape[1] != len(embs):
+            return None
+        if not all(_tensor_ok(t, 2) and t.shape[1] == tv[0].shape[1] and t.dtype == tv[0].dtype for t in tv):
+            return None
+        return tables, idx
+
+    @staticmethod
+    def _is_zero_const(gm: fx.GraphModule, n) -> bool:
+        if isinstance(n, (int, float)):
+            return n == 0
+        if isinstance(n, fx.Node) and n.op == "get_attr":
+            t = gm
+            try:
+                for part in n.target.split("."):
+                    t = getattr(t, part)
+            except AttributeError:
+                return False
+            return isinstance(t, torch.Tensor) and not bool(t.ne(0).any())
+        if _is(n, aten.zeros_like.default, aten.zeros.default):
+            return True
+        if _is(n, aten.full.default, aten.full_like.default):
+            return n.args[1] == 0
+        return False
+
+    def process(self, gm: fx.GraphModule) -> bool:
+        changed = False
+        for stack0 in list(gm.graph.nodes):
+            m = self._match_lookups(stack0)
+            if m is None:
+                continue
+            tables, idx = m
+            F = len(tables)
+            mask, top = None, stack0
+            if len(stack0.users) == 1:
+                w = next(iter(stack0.users))
+                if _is(w, aten.where.self) and w.args[2] is stack0 and self._is_zero_const(gm, w.args[1]):
+                    mv, iv = _val(w.args[0]), _val(idx)
+                    if isinstance(mv, torch.Tensor) and mv.dtype == torch.bool and tuple(mv.shape) == (iv.shape[0], 1):
+                        mask, top = w.args[0], w
+            # consumer A: unbind -> getitem(i) -> stack(dim=1) in order  => [B, F, D]
+            target, layout = None, None
+            if len(top.users) == 1:
+                ub = next(iter(top.users))
+                if _is(ub, aten.unbind.int) and (len(ub.args) == 1 or ub.args[1] == 0):
+                    gets = list(ub.users)
+                    if len(gets) == F and all(_is(g, operator.getitem) for g in gets):
+                        finals = {next(iter(g.users)) for g in gets if len(g.users) == 1}
+                        if len(finals) == 1 and all(len(g.users) == 1 for g in gets):
+                            fin = next(iter(finals))
+                            if _is(fin, aten.stack.default) and len(fin.args) > 1 and fin.args[1] == 1:
+                                order = [g.args[1] for g in fin.args[0] if _is(g, operator.getitem) and g.args[0] is ub]
+                                if order == list(range(F)):
+                                    target, layout = fin, "bfd"
+            if target is None:
+                # consumer B: the [F, B, D] stack (or masked stack) is used directly
+                target, layout = top, "fbd"
+            tv = _val(tables[0])
+            D = tv.shape[1]
+            _ensure(gm, "xg_gather_stack", M.GatherStackModule)
+            with gm.graph.inserting_before(target):
+                new = gm.graph.call_module("xg_gather_stack", (list(tables), idx, mask, True))
+                _fill_meta(gm, new)
+                B = _val(idx).shape[0]
+                out = gm.graph.call_function(aten.reshape.default, (new, [B, F, D]))
+                _fill_meta(gm, out)
+                if layout == "fbd":
+                    out = gm.graph.call_function(aten.transpose.int, (out, 0, 1))
+                    _fill_meta(gm, out)
+            target.replace_all_uses_with(out)
+            # sweep the dead chain from the consumer side
+            dead = [target]
+            while dead:
+                n = dead.pop()
+                if len(n.users) == 0 and n.op in ("call_function", "call_module"):
+                    ins = [a for a in n.all_input_nodes]
+                    gm.graph.erase_node(n)
+                    dead.extend(i for i in ins if len(i.users) == 0 and i.op == "call_function")
+            changed = True
+        return changed
+
+
+ALL_PATTERNS = [FusedNativeLayerNorm, FusedSdpa, FusedRoPE, FusedEmbeddingStack, FusedSwiGLU, FusedDenseResidual, FusedAddNorm]
+
+
+def get_all_patterns(config) -> dict:
+    """Target patterns keyed by group, filtered by the config (template: targets/mlu/__init__.py:8-29)."""
+    groups = {PatternGroup.GROUP0: [], PatternGroup.GROUP1: [], PatternGroup.GROUP2: []}
+    for cls in ALL_PATTERNS:
+        if cls.filter(config):
+            groups[cls._pattern_group].append(cls())
+    return groups
