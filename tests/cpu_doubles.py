@@ -1,0 +1,82 @@
+"""CPU stand-ins for the xg_sm100 ops — test doubles, registered only by the host-side test suite.
+
+They let FX graphs rewritten by the cuda_sm100 patterns run on CPU tensors so that the rewrites can be
+checked where there is no GPU. They call the oracle; the product package never imports this file.
+"""
+import torch
+
+from oracle import ref_ops
+
+_DONE = False
+
+
+def register():
+    global _DONE
+    if _DONE:
+        return
+    from xpu_graph_b200 import modules, ops
+
+    modules.ALLOWED_DEVICE_TYPES.add("cpu")
+
+    def k(op):
+        return op.register_kernel("cpu")
+
+    k(ops.rms_norm)(lambda x, weight, eps: ref_ops.rms_norm(x, weight, eps))
+    k(ops.layer_norm)(lambda x, weight, bias, eps: ref_ops.layer_norm(x, weight, bias, eps))
+    k(ops.add_rms_norm)(lambda x, residual, weight, eps: list(ref_ops.add_rms_norm(x, residual, weight, eps)))
+    k(ops.add_rms_norm_y)(lambda x, residual, weight, eps: ref_ops.add_rms_norm(x, residual, weight, eps)[0])
+    k(ops.add_layer_norm)(lambda x, residual, weight, bias, eps: list(ref_ops.add_layer_norm(x, residual, weight, bias, eps)))
+    k(ops.add_layer_norm_y)(lambda x, residual, weight, bias, eps: ref_ops.add_layer_norm(x, residual, weight, bias, eps)[0])
+    k(ops.rope)(lambda x, cos, sin: ref_ops.rope(x, cos.reshape(x.shape[2], x.shape[3]), sin.reshape(x.shape[2], x.shape[3])).contiguous())
+    k(ops.swiglu)(lambda gate, up: ref_ops.swiglu(gate, up))
+
+    def dense(x, weight, weight_trans, bias, residual, act):
+        y = x @ (weight.t() if weight_trans else weight)
+        if bias is not None:
+            y = y + bias
+        if residual is not None:
+            y = y + residual
+        return ref_ops._ACTS[act](y)
+
+    k(ops.dense)(dense)
+    k(ops.batch_dense)(lambda x, weight, weight_trans, bias, residual, act: ref_ops.batch_dense(
+        x, weight, weight_trans, bias if residual is None else residual, act))
+    k(ops.dense_swiglu)(lambda x, w_gate, w_up: ref_ops.dense_swiglu(x, w_gate, w_up))
+    k(ops.sdpa)(lambda q, k_, v, attn_mask, scale, is_causal: ref_ops.sdpa(q, k_, v, attn_mask, scale, is_causal).contiguous())
+
+    def slice_cat(src, starts, ends, row_mask, zero_when):
+        out = ref_ops.slice_cat(src, list(zip(starts, ends)))
+        if row_mask is not None:
+            out = out.clone()
+            out[(row_mask.reshape(-1) != 0) == zero_when] = 0
+        return out
+
+    k(ops.slice_cat)(slice_cat)
+    k(ops.multi_slice)(lambda src, starts, slice_len: ref_ops.multi_slice(src, starts, slice_len))
+
+    def slice_cat_multi(src, starts, ends, counts):
+        pairs, groups, pos = list(zip(starts, ends)), [], 0
+        for c in counts:
+            groups.append(pairs[pos:pos + c])
+            pos += c
+        return ref_ops.slice_cat_multi(src, groups)
+
+    k(ops.slice_cat_multi)(slice_cat_multi)
+
+    def cat_lastdim(xs, row_mask, zero_when):
+        out = torch.cat(xs, dim=-1)
+        if row_mask is not None:
+            out = out.clone()
+            out.view(-1, out.shape[-1])[(row_mask.reshape(-1) != 0) == zero_when] = 0
+        return out
+
+    k(ops.cat_lastdim)(cat_lastdim)
+
+    def gather_stack(tables, idx, row_mask, zero_when):
+        m = None
+        if row_mask is not None:
+            m = (row_mask.reshape(-1) != 0) == zero_when
+        return ref_ops.gather_stack(tables, idx, m)
+
+    k(ops.gather_stack)(gather_stack)
+    _DONE = True

@@ -1,0 +1,174 @@
+"""Generates tests/golden/golden_v1.pt by running the xpu_graph reference itself.
+
+Run where the xpu_graph source is importable (set XPU_GRAPH_SRC or keep it beside the repository):
+
+    python tests/golden/gen_golden.py
+
+What is recorded (inputs and outputs, all seeded, all small):
+  * the reference's own DefaultRMSNorm / DefaultLayerNorm modules
+    (passes/patterns/utils/default_replacements.py:19-36) on bf16 and fp32 rows;
+  * the reference's pass pipeline (target none, OptLevel.level2) compiling and running
+      - residual add + RMSNorm / LayerNorm graphs,
+      - Linear (+bias) + activation graphs (the dense-layer pattern's input),
+      - the decomposed bmm-softmax-bmm attention graph that FusedSDPA rewrites
+        (common/fuse_scaled_dot_product_attention.py:120-242), with and without an additive mask,
+      - slice + cat graphs incl. the INT64_MAX / negative-end cases of tests/mlu/test_fuse_slice_cat.py:293-323,
+      - multi-slice + stack, embedding + where + stack, RoPE and SwiGLU chains,
+      - the three benchmark graphs at reduced size (encoder block, Llama-style layer, recsys graph).
+The torch-version shims of xpu_graph_b200/target/compat.py are the only thing between this script and
+the unmodified reference.
+"""
+import os
+import sys
+
+import torch
+import torch.nn.functional as F
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+ROOT = os.path.dirname(os.path.dirname(HERE))
+sys.path.insert(0, ROOT)
+
+from xpu_graph_b200.target.compat import import_xpu_graph  # noqa: E402
+
+import_xpu_graph()
+from torch._dynamo.backends.common import aot_autograd  # noqa: E402
+from xpu_graph import OptLevel, Target, XpuGraph, XpuGraphConfig  # noqa: E402
+from xpu_graph.fx_utils import FxStage  # noqa: E402
+from xpu_graph.passes.patterns.utils.default_replacements import DefaultLayerNorm, DefaultRMSNorm  # noqa: E402
+
+from xpu_graph_b200.workloads import make_encoder, make_llama_layer, make_recsys, rotate_half  # noqa: E402
+
+MAX_INT64 = 9223372036854775807
+
+
+def ref_backend():
+    cfg = XpuGraphConfig(is_training=False, target=Target.none, opt_level=OptLevel.level2, enable_cache=False)
+    return aot_autograd(fw_compiler=XpuGraph(cfg)._get_compiler(FxStage.inference), keep_inference_input_mutations=True)
+
+
+def run_ref(fn, *inputs):
+    torch._dynamo.reset()
+    with torch.no_grad():
+        out = torch.compile(fn, backend=ref_backend(), dynamic=False)(*inputs)
+    return out
+
+
+def main():
+    G = {}
+    g = torch.Generator().manual_seed(1234)
+
+    def rn(*shape, dtype=torch.float32, std=1.0):
+        return (torch.randn(*shape, generator=g) * std).to(dtype)
+
+    # ---- the reference's own default norm modules -------------------------------------------------
+    for dt, tag in ((torch.bfloat16, "bf16"), (torch.float32, "f32")):
+        x, w, b = rn(6, 96, dtype=dt), (1 + 0.1 * rn(96)).to(dt), (0.1 * rn(96)).to(dt)
+        with torch.no_grad():
+            G[f"default_rms_{tag}"] = dict(x=x, w=w, eps=1e-6, y=DefaultRMSNorm()(x, w, 1e-6))
+            G[f"default_ln_{tag}"] = dict(x=x, w=w, b=b, eps=1e-5, y=DefaultLayerNorm()(x, w, b, 1e-5))
+
+    # ---- add + norm through the pipeline -----------------------------------------------------------
+    def add_rms(x, r, w):
+        s = x + r
+        sf = s.float()
+        y = (sf * torch.rsqrt(sf.pow(2).mean(-1, keepdim=True) + 1e-6) * w.float()).to(x.dtype)
+        return y, s
+
+    def add_ln(x, r, w, b):
+        s = x + r
+        return F.layer_norm(s.float(), s.shape[-1:], w.float(), b.float(), 1e-5).to(x.dtype), s
+
+    for dt, tag in ((torch.bfloat16, "bf16"), (torch.float32, "f32")):
+        x, r = rn(5, 128, dtype=dt), rn(5, 128, dtype=dt)
+        w, b = (1 + 0.1 * rn(128)).to(dt), (0.1 * rn(128)).to(dt)
+        y, s = run_ref(add_rms, x, r, w)
+        G[f"add_rms_{tag}"] = dict(x=x, r=r, w=w, eps=1e-6, y=y, s=s)
+        y, s = run_ref(add_ln, x, r, w, b)
+        G[f"add_ln_{tag}"] = dict(x=x, r=r, w=w, b=b, eps=1e-5, y=y, s=s)
+
+    # ---- dense layers --------------------------------------------------------------------------------
+    for act in ("none", "gelu", "relu", "silu", "sigmoid"):
+        fn = {"none": lambda t: t, "gelu": F.gelu, "relu": F.relu, "silu": F.silu, "sigmoid": torch.sigmoid}[act]
+        x, w, b = rn(24, 40), rn(56, 40, std=0.1), rn(56, std=0.1)
+        G[f"dense_{act}_f32"] = dict(x=x, w=w, b=b, act=act, y=run_ref(lambda x, w, b: fn(F.linear(x, w, b)), x, w, b))
+    x, w = rn(24, 40, dtype=torch.bfloat16), rn(56, 40, dtype=torch.bfloat16, std=0.1)
+    G["dense_nobias_bf16"] = dict(x=x, w=w, b=None, act="gelu", y=run_ref(lambda x, w: F.gelu(F.linear(x, w)), x, w))
+    x, w, r = rn(24, 40), rn(40, 56, std=0.1), rn(24, 56)
+    G["dense_kn_residual_f32"] = dict(x=x, w=w, r=r, y=run_ref(lambda x, w, r: torch.addmm(r, x, w), x, w, r))
+
+    # ---- attention: the decomposed form FusedSDPA matches -----------------------------------------------
+    def attn(q, k, v):
+        s = torch.bmm(q, k.transpose(1, 2)) * 0.125
+        return torch.bmm(torch.softmax(s, dim=-1), v)
+
+    def attn_mask(q, k, v, m):
+        s = torch.bmm(q, k.transpose(1, 2)) * 0.125 + m
+        return torch.bmm(torch.softmax(s, dim=-1), v)
+
+    q, k, v = rn(6, 38, 64), rn(6, 38, 64), rn(6, 38, 64)
+    G["sdpa_f32"] = dict(q=q, k=k, v=v, scale=0.125, y=run_ref(attn, q, k, v))
+    m = rn(6, 38, 38)
+    G["sdpa_mask_f32"] = dict(q=q, k=k, v=v, m=m, scale=0.125, y=run_ref(attn_mask, q, k, v, m))
+    qb, kb, vb = (t.to(torch.bfloat16) for t in (q, k, v))
+    G["sdpa_bf16"] = dict(q=qb, k=kb, v=vb, scale=0.125, y=run_ref(attn, qb, kb, vb))
+    q4, k4, v4 = rn(2, 3, 40, 32, dtype=torch.bfloat16), rn(2, 3, 40, 32, dtype=torch.bfloat16), rn(2, 3, 40, 32, dtype=torch.bfloat16)
+    G["sdpa_causal_bf16"] = dict(q=q4, k=k4, v=v4, y=run_ref(lambda q, k, v: F.scaled_dot_product_attention(q, k, v, is_causal=True), q4, k4, v4))
+
+    # ---- copy fusions ------------------------------------------------------------------------------------
+    src = rn(9, 120)
+    cases = {
+        "even": [(0, 32), (64, 96), (32, 64)],
+        "ragged": [(3, 10), (100, 119), (50, 51)],
+        "int64max": [(8, MAX_INT64), (0, 8)],
+        "negative_end": [(0, -100), (10, -3)],
+    }
+    for name, sl in cases.items():
+        fn = lambda s, sl=sl: torch.cat([s[:, a:b] for a, b in sl], dim=-1) + 0  # noqa: E731
+        G[f"slice_cat_{name}"] = dict(src=src, slices=sl, y=run_ref(fn, src))
+    srcb = src.to(torch.bfloat16)
+    G["slice_cat_bf16"] = dict(src=srcb, slices=cases["even"], y=run_ref(lambda s: torch.cat([s[:, a:b] for a, b in cases["even"]], dim=-1) + 0, srcb))
+    starts = [0, 40, 16, 100]
+    G["multi_slice"] = dict(src=src, starts=starts, length=12, y=run_ref(lambda s: torch.stack([s[:, a:a + 12] for a in starts], 0) + 0, src))
+    mask = torch.rand(9, 1, generator=g) < 0.4
+    G["masked_slice_cat"] = dict(src=src, mask=mask, slices=cases["even"],
+                                 y=run_ref(lambda s, m: torch.cat([torch.where(m, torch.zeros_like(s[:, a:b]), s[:, a:b]) for a, b in cases["even"]], -1), src, mask))
+    tables = [rn(20, 8, std=0.01) for _ in range(3)]
+    idx = torch.randint(0, 20, (9, 3), generator=g)
+
+    def emb(t0, t1, t2, idx, m):
+        es = [F.embedding(idx[:, f], t) for f, t in enumerate((t0, t1, t2))]
+        return torch.stack([torch.where(m, torch.zeros_like(e), e) for e in es], dim=1).reshape(idx.shape[0], -1)
+
+    G["gather_stack"] = dict(tables=tables, idx=idx, mask=mask, y=run_ref(emb, *tables, idx, mask))
+
+    # ---- RoPE and SwiGLU ---------------------------------------------------------------------------------------
+    for dt, tag in ((torch.bfloat16, "bf16"), (torch.float32, "f32")):
+        x, c, s = rn(2, 3, 10, 16, dtype=dt), rn(10, 16, dtype=dt), rn(10, 16, dtype=dt)
+        G[f"rope_{tag}"] = dict(x=x, cos=c, sin=s, y=run_ref(lambda x, c, s: x * c + rotate_half(x) * s, x, c, s))
+        a, b = rn(7, 48, dtype=dt), rn(7, 48, dtype=dt)
+        G[f"swiglu_{tag}"] = dict(gate=a, up=b, y=run_ref(lambda a, b: F.silu(a) * b, a, b))
+
+    # ---- the benchmark graphs at reduced size -----------------------------------------------------------------------
+    m, x = make_encoder(seed=0, batch=2, seq=16, hidden=64, heads=4, ffn=128)
+    G["encoder_small"] = dict(args=dict(seed=0, batch=2, seq=16, hidden=64, heads=4, ffn=128), y=run_ref(m, x))
+    m, inp = make_llama_layer(seed=3, batch=2, seq=24, hidden=128, heads=2, ffn=192)
+    G["llama_small"] = dict(args=dict(seed=3, batch=2, seq=24, hidden=128, heads=2, ffn=192), y=run_ref(m, *inp))
+    m, inp = make_recsys(seed=4, batch=32, table_rows=50)
+    G["recsys_small"] = dict(args=dict(seed=4, batch=32, table_rows=50), y=run_ref(m, *inp))
+
+    def compact(o):  # detach views from their (possibly larger) storages
+        if isinstance(o, torch.Tensor):
+            return o.detach().clone().contiguous()
+        if isinstance(o, dict):
+            return {k: compact(v) for k, v in o.items()}
+        if isinstance(o, (list, tuple)):
+            return type(o)(compact(v) for v in o)
+        return o
+
+    out = os.path.join(HERE, "golden_v1.pt")
+    torch.save(compact(G), out)
+    print(f"wrote {out}: {len(G)} cases, {os.path.getsize(out) / 1024:.0f} KiB")
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,81 @@
+"""Host-side checks of the C ABI: the library loads, exports every symbol the header declares, and
+rejects bad arguments with an error code before anything touches a GPU."""
+import ctypes
+import os
+import re
+
+import pytest
+
+from xpu_graph_b200 import lib
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+HEADER = os.path.join(ROOT, "include", "xg_sm100.h")
+
+
+def _declared_functions():
+    src = open(HEADER).read()
+    src = re.sub(r"/\*.*?\*/", "", src, flags=re.S)
+    return sorted(set(re.findall(r"\b(xg_[a-z0-9_]+)\s*\(", src)))
+
+
+def test_library_exports_every_declared_symbol():
+    names = _declared_functions()
+    assert len(names) >= 14
+    L = lib.load()
+    for n in names:
+        assert hasattr(L, n), f"{n} declared in include/xg_sm100.h but not exported"
+    assert set(names) == set(lib.SIGNATURES), "ctypes signature table and header disagree"
+    assert L.xg_version() >= 1000
+
+
+def test_missing_library_fails_loudly(tmp_path):
+    with pytest.raises(lib.XgLibraryError):
+        lib.load(str(tmp_path / "libxg_sm100.so"))
+    bogus = tmp_path / "bogus.so"
+    bogus.write_bytes(b"not an ELF file")
+    with pytest.raises(lib.XgLibraryError):
+        lib.load(str(bogus))
+
+
+def test_argument_validation_without_gpu():
+    L = lib.load()
+    # null pointers
+    assert L.xg_rmsnorm(None, None, None, None, None, 4, 8, 8, 0, 1e-6, lib.XG_BF16, lib.XG_BF16, None) == -1
+    assert "null" in lib.last_error()
+    buf = ctypes.create_string_buffer(4096)
+    p = ctypes.cast(buf, ctypes.c_void_p)
+    # bad extents / dtypes / strides
+    assert L.xg_rmsnorm(p, None, p, p, None, -1, 8, 8, 0, 1e-6, lib.XG_BF16, lib.XG_BF16, None) == -1
+    assert L.xg_rmsnorm(p, None, p, p, None, 4, 8, 4, 0, 1e-6, lib.XG_BF16, lib.XG_BF16, None) == -1
+    assert L.xg_rmsnorm(p, None, p, p, None, 4, 8, 8, 0, 1e-6, 7, 7, None) == -1
+    assert L.xg_rmsnorm(p, None, p, p, p, 4, 8, 8, 0, 1e-6, lib.XG_BF16, lib.XG_BF16, None) == -1  # sum_out without residual
+    assert L.xg_layernorm(p, None, p, None, p, None, 4, 8, 8, 0, 1e-5, lib.XG_F32, lib.XG_F32, None) == -1  # bias required
+    assert L.xg_rope(p, p, p, p, 1, 1, 4, 7, 28, 28, 7, 28, 28, 7, lib.XG_F32, None) == -1  # odd head dim
+    assert L.xg_swiglu(p, p, p, 4, 8, 4, 8, 8, lib.XG_F32, None) == -1
+    assert L.xg_gemm_bias_act(p, p, None, None, p, 4, 4, 0, 4, 4, 4, 0, 1, 0, lib.XG_F32, None) == -1  # K == 0
+    assert L.xg_gemm_bias_act(p, p, None, None, p, 4, 4, 8, 4, 8, 4, 0, 1, 0, lib.XG_F32, None) == -1  # lda < K
+    assert L.xg_gemm_bias_act(p, p, None, None, p, 4, 4, 8, 8, 8, 4, 0, 1, 9, lib.XG_F32, None) == -1  # bad act
+    assert L.xg_gemm_bias_act(p, p, None, None, p, 8, 8, 8, 8, 8, 8, 0, 0, 0, lib.XG_BF16, None) == -2  # [K,N] bf16: no kernel
+    assert "trans_b" in lib.last_error()
+    assert L.xg_gemm_swiglu(p, p, p, p, 8, 8, 8, 8, 8, 8, lib.XG_F32, None) == -2
+    assert L.xg_sdpa_fwd(None, None, None, None, None, 1, 1, 1, 1, 8, None, None, None, None, None, 1.0, 0, lib.XG_BF16, None) == -1
+    assert L.xg_gather_rows(None, None, 2, None, 2, 1, None, 1, None, 4, 8, 16, 4, None) == -1
+    assert L.xg_gather_rows(None, None, 2, None, 2, 1, None, 1, None, 4, 8, 16, 3, None) == -1  # elem_size
+    assert L.xg_seg_copy(None, None, None, None, None, 3, 4, None, 1, None) == -1
+    assert L.xg_tc_status(None, 0) == -1
+    # empty problems succeed without a launch
+    assert L.xg_seg_copy(None, None, None, None, None, 0, 4, None, 1, None) == 0
+    assert L.xg_swiglu(p, p, p, 0, 8, 8, 8, 8, lib.XG_F32, None) == 0
+    assert L.xg_rmsnorm(p, None, p, p, None, 0, 8, 8, 0, 1e-6, lib.XG_BF16, lib.XG_BF16, None) == 0
+
+
+def test_ops_have_no_cpu_kernel():
+    """The target has no CPU fallback: calling an op on CPU tensors raises instead of computing."""
+    import torch
+
+    from xpu_graph_b200 import ops  # noqa: F401
+
+    if "cpu" in getattr(__import__("xpu_graph_b200.modules", fromlist=["x"]), "ALLOWED_DEVICE_TYPES"):
+        pytest.skip("CPU test doubles already registered in this process")
+    with pytest.raises((NotImplementedError, RuntimeError)):
+        torch.ops.xg_sm100.rms_norm(torch.zeros(2, 8), torch.ones(8), 1e-6)

@@ -1,0 +1,261 @@
+"""The cuda_sm100 target inside the xpu_graph pass pipeline (host side, CPU graphs).
+
+Style follows the reference's pattern tests (e.g. tests/common/test_fuse_layernorm.py:58-134,
+tests/mlu/test_custom_denselayer.py:109-179): compile a small eager function through
+``torch.compile(backend=XpuGraph-based)``, compare with eager, and assert on the
+"Pattern.<Class> changed graph" log lines. The fused ops run on CPU through test doubles
+(tests/cpu_doubles.py), so this checks the graph rewrites, not the kernels.
+
+Skipped when the xpu_graph package is not importable.
+"""
+import logging
+
+import pytest
+import torch
+import torch.nn.functional as F
+
+from xpu_graph_b200.target.compat import reference_available
+
+pytestmark = pytest.mark.skipif(not reference_available(), reason="xpu_graph reference package not importable")
+
+MAX_INT64 = 9223372036854775807
+
+
+@pytest.fixture(autouse=True)
+def _reset_dynamo():
+    torch._dynamo.reset()
+    yield
+    torch._dynamo.reset()
+
+
+@pytest.fixture(scope="module")
+def tgt():
+    from tests import cpu_doubles
+
+    cpu_doubles.register()
+    from xpu_graph_b200 import target
+
+    target.install()
+    return target
+
+
+def _compile(tgt, fn, *inputs, **cfg):
+    cap = {}
+    be = tgt.backend(tgt.make_config(debug=True, **cfg), capture=cap)
+    with torch.no_grad():
+        want = fn(*inputs)
+        got = torch.compile(fn, backend=be, dynamic=False)(*inputs)
+    mods = [n.target for n in cap["gm"].graph.nodes if n.op == "call_module"]
+    atens = [str(n.target) for n in cap["gm"].graph.nodes if n.op == "call_function"]
+    return want, got, mods, atens
+
+
+@pytest.fixture()
+def xlog(caplog):
+    lg = logging.getLogger("xpu_graph")
+    old = lg.propagate
+    lg.propagate = True
+    caplog.set_level(logging.DEBUG, logger="xpu_graph")
+    yield caplog
+    lg.propagate = old
+
+
+def _same(a, b, tol=1e-5):
+    assert a.shape == b.shape and a.dtype == b.dtype
+    scale = max(b.float().abs().max().item(), 1e-6)
+    assert (a.float() - b.float()).abs().max().item() <= tol * scale
+
+
+def test_target_is_installed(tgt):
+    from xpu_graph.config import Target
+    from xpu_graph.passes.patterns.targets import get_all_patterns, get_structure_replacements
+
+    assert Target.cuda_sm100.value == "cuda_sm100" and Target("cuda_sm100") is Target.cuda_sm100
+    cfg = tgt.make_config()
+    reps = get_structure_replacements(cfg)
+    for name in ("CustomRMSNorm", "CustomLayerNorm", "CustomDenseLayer", "CustomBatchDenseLayer", "FusedSlice",
+                 "FusedCatSlice", "FusedSliceStackSum", "FusedMultipleSliceCat"):
+        assert name in reps and "target_mod" in reps[name]
+    pats = get_all_patterns(cfg)
+    names = {type(p).__name__ for group in pats.values() for p in group}
+    assert {"FusedNativeLayerNorm", "FusedSdpa", "FusedRoPE", "FusedSwiGLU", "FusedDenseResidual", "FusedAddNorm",
+            "FusedEmbeddingStack", "FusedCatLastDim"} <= names
+    # skip_patterns is honoured through Pattern.filter
+    pats = get_all_patterns(tgt.make_config(skip_patterns=["FusedRoPE"]))
+    assert "FusedRoPE" not in {type(p).__name__ for group in pats.values() for p in group}
+
+
+def test_llama_layer_graph(tgt, xlog):
+    from xpu_graph_b200.workloads import make_llama_layer
+
+    m, inp = make_llama_layer(seed=3, batch=2, seq=32, hidden=256, heads=2, ffn=384)
+    want, got, mods, atens = _compile(tgt, m, *inp)
+    _same(got, want, 1e-2)
+    assert mods == ["custom_rms_norm", "custom_dense_layer_replacement", "custom_dense_layer_replacement",
+                    "custom_dense_layer_replacement", "xg_rope", "xg_rope", "xg_sdpa", "xg_dense_residual",
+                    "custom_rms_norm", "xg_dense_swiglu", "xg_dense_residual"]
+    assert all(("reshape" in a or "transpose" in a) for a in atens), atens  # only views are left
+    for cls in ("CustomRMSNorm", "CustomDenseLayer", "FusedRoPE", "FusedSdpa", "FusedSwiGLU", "FusedDenseResidual"):
+        assert f"Pattern.{cls} changed graph" in xlog.text
+
+
+def test_encoder_block_graph(tgt, xlog):
+    from xpu_graph_b200.workloads import make_encoder
+
+    m, x = make_encoder(seed=0, batch=2, seq=16, hidden=64, heads=4, ffn=128)
+    want, got, mods, atens = _compile(tgt, m, x)
+    _same(got, want)
+    assert mods == ["xg_layer_norm", "custom_dense_layer_replacement", "xg_sdpa", "xg_dense_residual", "xg_layer_norm",
+                    "custom_dense_layer_replacement", "xg_dense_residual"]
+    for cls in ("FusedNativeLayerNorm", "CustomDenseLayer", "FusedSdpa", "FusedDenseResidual"):
+        assert f"Pattern.{cls} changed graph" in xlog.text
+
+
+def test_recsys_graph(tgt, xlog):
+    from xpu_graph_b200.workloads import make_recsys
+
+    m, inp = make_recsys(seed=4, batch=32, table_rows=50)
+    want, got, mods, atens = _compile(tgt, m, *inp)
+    _same(got, want)
+    assert mods == ["xg_gather_stack", "fuse_slice_cat", "xg_cat_lastdim", "custom_dense_layer_replacement",
+                    "custom_dense_layer_replacement", "custom_dense_layer_replacement"]
+    assert not any("embedding" in a or "where" in a or "slice" in a for a in atens)
+    for cls in ("FusedEmbeddingStack", "FusedCatSlice", "FusedCatLastDim", "CustomDenseLayer"):
+        assert f"Pattern.{cls} changed graph" in xlog.text
+
+
+@pytest.mark.parametrize("reuse_sum", [False, True])
+@pytest.mark.parametrize("kind", ["rms", "ln"])
+def test_add_norm(tgt, xlog, kind, reuse_sum):
+    g = torch.Generator().manual_seed(0)
+    x, r = torch.randn(6, 64, generator=g), torch.randn(6, 64, generator=g)
+    w, b = torch.randn(64, generator=g), torch.randn(64, generator=g)
+
+    def fn(x, r, w, b):
+        s = x + r
+        if kind == "rms":
+            y = s * torch.rsqrt(s.pow(2).mean(-1, keepdim=True) + 1e-6) * w
+        else:
+            y = F.layer_norm(s, s.shape[-1:], w, b, 1e-5)
+        return (y, s * 2.0) if reuse_sum else y
+
+    want, got, mods, atens = _compile(tgt, fn, x, r, w, b)
+    if reuse_sum:
+        _same(got[0], want[0])
+        _same(got[1], want[1])
+    else:
+        _same(got, want)
+    expect = {("rms", False): "xg_add_rms_norm_y", ("rms", True): "xg_add_rms_norm", ("ln", False): "xg_add_layer_norm_y",
+              ("ln", True): "xg_add_layer_norm"}[(kind, reuse_sum)]
+    assert mods == [expect], mods
+    assert "Pattern.FusedAddNorm changed graph" in xlog.text
+    assert not any("add.Tensor" in a for a in atens)
+
+
+@pytest.mark.parametrize("act", ["none", "gelu", "relu", "silu"])
+@pytest.mark.parametrize("bias", [False, True])
+def test_dense_layer(tgt, xlog, act, bias):
+    g = torch.Generator().manual_seed(1)
+    x, w, b = torch.randn(10, 24, generator=g), torch.randn(40, 24, generator=g), torch.randn(40, generator=g)
+    f = {"none": lambda t: t, "gelu": F.gelu, "relu": F.relu, "silu": F.silu}[act]
+    fn = (lambda x, w, b: f(F.linear(x, w, b))) if bias else (lambda x, w, b: f(F.linear(x, w)))
+    want, got, mods, atens = _compile(tgt, fn, x, w, b)
+    _same(got, want)
+    assert mods == ["custom_dense_layer_replacement"]
+    assert "Pattern.CustomDenseLayer changed graph" in xlog.text
+
+
+def test_bf16_dense_needs_linear_layout(tgt):
+    """bf16 x @ W with W given as [K, N] has no tensor-core kernel: the constraint function refuses the
+    fusion and the matmul stays an aten op (decided at compile time, nothing falls back at run time)."""
+    g = torch.Generator().manual_seed(2)
+    x = torch.randn(8, 16, generator=g).to(torch.bfloat16)
+    w = torch.randn(16, 24, generator=g).to(torch.bfloat16)
+    want, got, mods, atens = _compile(tgt, lambda x, w: F.relu(x @ w), x, w)
+    assert mods == []
+    assert any("mm" in a for a in atens)
+
+
+def test_decomposed_attention_goes_through_fused_sdpa(tgt, xlog):
+    g = torch.Generator().manual_seed(3)
+    q, k, v = (torch.randn(4, 20, 32, generator=g) for _ in range(3))
+
+    def fn(q, k, v):
+        s = torch.bmm(q, k.transpose(1, 2)) * 0.25
+        return torch.bmm(torch.softmax(s, dim=-1), v)
+
+    want, got, mods, atens = _compile(tgt, fn, q, k, v)
+    _same(got, want)
+    assert "xg_sdpa" in mods
+    assert "Pattern.FusedSDPA changed graph" in xlog.text and "Pattern.FusedSdpa changed graph" in xlog.text
+
+
+def test_slice_fusions_use_target_modules(tgt, xlog):
+    g = torch.Generator().manual_seed(4)
+    src = torch.randn(12, 200, generator=g)
+
+    def cat_fn(s):
+        return torch.cat([s[:, 0:32], s[:, 64:96], s[:, 100:MAX_INT64], s[:, 10:-150]], dim=-1) * 2.0
+
+    want, got, mods, atens = _compile(tgt, cat_fn, src)
+    assert torch.equal(got, want)
+    assert mods == ["fuse_slice_cat"]
+    assert "Pattern.FusedCatSlice changed graph" in xlog.text
+
+    def slice_fn(s):
+        a, b, c, d = s[:, 0:16], s[:, 40:56], s[:, 100:116], s[:, 7:23]
+        return a * 1.0 + b * 2.0 + c * 3.0 + d * 4.0
+
+    torch._dynamo.reset()
+    want, got, mods, atens = _compile(tgt, slice_fn, src)
+    _same(got, want)
+    assert any(m.startswith("fused_triton_slice") for m in mods)
+    assert "Pattern.FusedSlice changed graph" in xlog.text
+
+
+def test_rope_and_swiglu_standalone(tgt, xlog):
+    from xpu_graph_b200.workloads import rotate_half
+
+    g = torch.Generator().manual_seed(5)
+    x, c, s = torch.randn(2, 3, 10, 16, generator=g), torch.randn(10, 16, generator=g), torch.randn(10, 16, generator=g)
+    want, got, mods, atens = _compile(tgt, lambda x, c, s: x * c + rotate_half(x) * s, x, c, s)
+    _same(got, want)
+    assert mods == ["xg_rope"] and not any("cat" in a or "neg" in a for a in atens)
+    torch._dynamo.reset()
+    a, b = torch.randn(7, 48, generator=g), torch.randn(7, 48, generator=g)
+    want, got, mods, atens = _compile(tgt, lambda a, b: F.silu(a) * b, a, b)
+    _same(got, want)
+    assert mods == ["xg_swiglu"]
+
+
+def test_replacement_modules_are_picklable(tgt):
+    """The compile cache pickles graphs with their sub-modules (cache.py:113-179)."""
+    import pickle
+
+    from xpu_graph_b200 import modules as M
+
+    for mod in (M.RMSNormModule(), M.LayerNormModule(), M.DenseLayerModule(False), M.FuseSliceModule([0, 4, 8]),
+                M.FuseSliceCatSameInputModule(), M.FuseSliceCatSameInputModule_v2([[(0, 2)], [(2, 4), (6, 8)]]),
+                M.AddRMSNormModule(True), M.SDPAModule(), M.GatherStackModule()):
+        clone = pickle.loads(pickle.dumps(mod))
+        assert type(clone) is type(mod)
+
+
+def test_module_signatures_match_reference_call_sites(tgt):
+    """forward() parameter counts equal what the reference's structure patterns pass."""
+    import inspect
+
+    from xpu_graph_b200 import modules as M
+
+    def nparams(cls):
+        return len(inspect.signature(cls.forward).parameters) - 1
+
+    assert nparams(M.RMSNormModule) == 3       # (inputs, weight, eps)      custom_rmsnorm.py:28
+    assert nparams(M.LayerNormModule) == 4     # (inputs, weight, bias, eps) custom_layernorm.py:28
+    assert nparams(M.DenseLayerModule) == 5    # custom_denselayer.py:87-88
+    assert nparams(M.BatchDenseLayerModule) == 5
+    assert nparams(M.FuseSliceModule) == 2     # (src, slice_len)           fuse_slice.py:104-106
+    assert nparams(M.FuseSliceCatSameInputModule) == 2
+    assert nparams(M.FuseSliceCatSameInputModule_v2) == 2
+    assert len(inspect.signature(M.DenseLayerModule.__init__).parameters) == 2   # M(fast_act)
+    assert len(inspect.signature(M.FuseSliceModule.__init__).parameters) == 2    # M(start_indices)

@@ -19,6 +19,10 @@ from . import ops  # noqa: F401  (registers torch.ops.xg_sm100.*)
 _X = torch.ops.xg_sm100
 
 _SUPPORTED = (torch.float32, torch.bfloat16, torch.float16)
+# Device types on which the fusions are applied. The kernels exist for CUDA only; the host-side test
+# suite adds "cpu" together with CPU stand-ins for the ops so that the graph rewrites can be exercised
+# without a GPU.
+ALLOWED_DEVICE_TYPES = {"cuda"}
 
 
 # ---- normalisation -------------------------------------------------------------------------
@@ -102,7 +106,7 @@ def can_fuse_custom_denselayer(inputs, weight, weight_trans, bias, act_str):
         return False
     if bias is not None and bias.dtype != inputs.dtype:
         return False
-    if not inputs.is_cuda:
+    if inputs.device.type not in ALLOWED_DEVICE_TYPES:
         return False
     if inputs.dtype != torch.float32:
         # tensor-core kernel: weights in Linear layout [N, K], K a multiple of 8 (16-byte rows for TMA)
@@ -132,13 +136,23 @@ class BatchDenseLayerModule(torch.nn.Module):
 def can_fuse_custom_batch_denselayer(inputs, weight, weight_trans, bias, act_str):
     if act_str not in ["gelu", "silu", "none"]:
         return False
-    if inputs.dim() != 3 or weight.dim() != 3 or not inputs.is_cuda:
+    if inputs.dim() != 3 or weight.dim() != 3 or inputs.device.type not in ALLOWED_DEVICE_TYPES:
         return False
     if inputs.dtype not in _SUPPORTED or weight.dtype != inputs.dtype:
         return False
     if inputs.dtype != torch.float32 and (not weight_trans or inputs.shape[2] % 8 != 0):
         return False
     return True
+
+
+class DenseResidualModule(torch.nn.Module):
+    """Dense layer with both a per-column bias and a full [M, N] addend (a residual) in one epilogue:
+    act(inputs @ W + bias + residual)."""
+
+    def forward(self, inputs, weight, weight_trans, bias, residual, act):
+        if bias is not None and bias.dim() != 1:
+            bias = bias.reshape(-1)
+        return _X.dense(inputs, weight, bool(weight_trans), bias, residual, act)
 
 
 class DenseSwiGLUModule(torch.nn.Module):

@@ -2,8 +2,8 @@
 
 xpu_graph's structure patterns (CustomRMSNorm, CustomLayerNorm, CustomDenseLayer, FusedSlice, ...)
 already route to this target's modules through ``get_structure_replacements``. The classes below
-cover the graph forms that reach the target un-matched on current PyTorch (SURVEY of the graphs:
-``aten.native_layer_norm`` from ``nn.LayerNorm``, pre-fused ``_scaled_dot_product_*`` ops, the
+cover the graph forms that reach the target un-matched on current PyTorch releases
+(``aten.native_layer_norm`` from ``nn.LayerNorm``, pre-fused ``_scaled_dot_product_*`` ops, the
 rotate-half RoPE chain, ``mul(silu(mm), mm)``, residual adds next to a dense layer or a norm, and
 embedding + where + stack). Each is a ``Pattern`` subclass (passes/patterns/pattern.py:26-49) so it is
 run, linted, recompiled and logged ("Pattern.<Class> changed graph") by the pass manager like any
@@ -25,6 +25,7 @@ from .. import modules as M
 aten = torch.ops.aten
 INT64_MAX = 9223372036854775807
 DENSE_NAME = "custom_dense_layer_replacement"  # sub-module name used by structure/custom_denselayer.py:82
+_RESHAPES = (aten.reshape.default, aten.view.default, aten._unsafe_view.default)
 
 
 # ---- helpers ---------------------------------------------------------------------------------
@@ -291,35 +292,46 @@ class FusedSwiGLU(Pattern):
             if not (isinstance(a, fx.Node) and isinstance(b, fx.Node)):
                 continue
             done = False
-            for g, u in ((a, b), (b, a)):
+            for g0, u0 in ((a, b), (b, a)):
+                # the two dense outputs may each sit behind an identical reshape ([M, N] -> [B, S, N])
+                g, u, via_g, via_u = g0, u0, None, None
+                if (_is(g0, *_RESHAPES) and _is(u0, *_RESHAPES) and list(g0.args[1]) == list(u0.args[1])
+                        and _only_user(g0, node) and _only_user(u0, node)):
+                    g, u, via_g, via_u = g0.args[0], u0.args[0], g0, u0
                 if (_module_call(gm, g, M.DenseLayerModule) and _module_call(gm, u, M.DenseLayerModule)
                         and g.target == DENSE_NAME and u.target == DENSE_NAME):
                     gx, gw, gt, gb, gact = g.args
                     ux, uw, ut, ub, uact = u.args
                     wv, uv, xv = _val(gw), _val(uw), _val(gx)
                     if (gact == "silu" and uact == "none" and gx is ux and gt and ut and gb is None and ub is None
-                            and _only_user(g, node) and _only_user(u, node) and _tensor_ok(xv, 2)
+                            and _only_user(g, via_g if via_g is not None else node)
+                            and _only_user(u, via_u if via_u is not None else node) and _tensor_ok(xv, 2)
                             and xv.dtype in (torch.bfloat16, torch.float16) and isinstance(wv, torch.Tensor)
                             and isinstance(uv, torch.Tensor) and wv.shape == uv.shape and xv.shape[1] % 8 == 0):
                         _ensure(gm, "xg_dense_swiglu", M.DenseSwiGLUModule)
                         with gm.graph.inserting_before(node):
                             new = gm.graph.call_module("xg_dense_swiglu", (gx, gw, uw))
-                        _fill_meta(gm, new)
-                        node.replace_all_uses_with(new)
-                        for dead in (node, g, u):
-                            gm.graph.erase_node(dead)
+                            _fill_meta(gm, new)
+                            out = new
+                            if via_g is not None:
+                                out = gm.graph.call_function(aten.reshape.default, (new, list(via_g.args[1])))
+                                _fill_meta(gm, out)
+                        node.replace_all_uses_with(out)
+                        for dead in (node, via_g, via_u, g, u):
+                            if dead is not None:
+                                gm.graph.erase_node(dead)
                         changed = done = True
                         break
-                if _is(g, aten.silu.default) and _only_user(g, node):
-                    gv, uv = _val(g.args[0]), _val(u)
+                if _is(g0, aten.silu.default) and _only_user(g0, node):
+                    gv, uv = _val(g0.args[0]), _val(u0)
                     if _tensor_ok(gv) and _tensor_ok(uv) and gv.shape == uv.shape and gv.dtype == uv.dtype and gv.dim() >= 1:
                         _ensure(gm, "xg_swiglu", M.SwiGLUModule)
                         with gm.graph.inserting_before(node):
-                            new = gm.graph.call_module("xg_swiglu", (g.args[0], u))
+                            new = gm.graph.call_module("xg_swiglu", (g0.args[0], u0))
                         _fill_meta(gm, new)
                         node.replace_all_uses_with(new)
                         gm.graph.erase_node(node)
-                        gm.graph.erase_node(g)
+                        gm.graph.erase_node(g0)
                         changed = done = True
                         break
             if done:
@@ -345,7 +357,7 @@ class FusedDenseResidual(Pattern):
                 if not (isinstance(d_side, fx.Node) and isinstance(other, fx.Node)):
                     continue
                 dense, via = d_side, None
-                if _is(d_side, aten.reshape.default, aten.view.default, aten._unsafe_view.default) and _only_user(d_side, node):
+                if _is(d_side, *_RESHAPES) and _only_user(d_side, node):
                     dense, via = d_side.args[0], d_side
                 if not (_module_call(gm, dense, M.DenseLayerModule) and dense.target == DENSE_NAME):
                     continue
@@ -546,7 +558,45 @@ class FusedEmbeddingStack(Pattern):
         return changed
 
 
-ALL_PATTERNS = [FusedNativeLayerNorm, FusedSdpa, FusedRoPE, FusedEmbeddingStack, FusedSwiGLU, FusedDenseResidual, FusedAddNorm]
+# ---- cat along the last dim -------------------------------------------------------------------------------------
+class FusedCatLastDim(Pattern):
+    """aten.cat of >= 2 tensors along the last dim -> one segmented copy (CatLastDimModule). Runs after
+    the slice fusions (structure/fuse_slice_cat.py:52-95 re-emits a cat of the fused slices and the
+    remaining inputs), so what is left is a plain concatenation."""
+
+    _opt_level = OptLevel.level1
+    _pattern_group = PatternGroup.GROUP2
+
+    def process(self, gm: fx.GraphModule) -> bool:
+        changed = False
+        for node in list(gm.graph.nodes):
+            if not _is(node, aten.cat.default):
+                continue
+            parts = node.args[0]
+            dim = node.args[1] if len(node.args) > 1 else 0
+            vals = [_val(p) for p in parts]
+            if len(parts) < 2 or not all(isinstance(v, torch.Tensor) for v in vals):
+                continue
+            nd = vals[0].dim()
+            if nd < 2 or dim not in (-1, nd - 1):
+                continue
+            if any(_is(p, aten.slice.Tensor) for p in parts):
+                continue  # leave slices to the slice-cat fusion
+            if not all(v.dim() == nd and v.dtype == vals[0].dtype and v.shape[:-1] == vals[0].shape[:-1]
+                       and v.device.type in M.ALLOWED_DEVICE_TYPES and _static(v.shape) for v in vals):
+                continue
+            _ensure(gm, "xg_cat_lastdim", M.CatLastDimModule)
+            with gm.graph.inserting_before(node):
+                new = gm.graph.call_module("xg_cat_lastdim", (list(parts),))
+            _fill_meta(gm, new)
+            node.replace_all_uses_with(new)
+            gm.graph.erase_node(node)
+            changed = True
+        return changed
+
+
+ALL_PATTERNS = [FusedNativeLayerNorm, FusedSdpa, FusedRoPE, FusedEmbeddingStack, FusedSwiGLU, FusedDenseResidual,
+                FusedAddNorm, FusedCatLastDim]
 
 
 def get_all_patterns(config) -> dict:
