@@ -50,3 +50,43 @@ def test_recsys_graph(cuda_device):
         want = model(dense, idx, mask)
     got = FusedRecsysGraph(model.to(cuda_device))(dense.to(cuda_device), idx.to(cuda_device), mask.to(cuda_device))
     assert_parity(got, want, "recsys graph fp32")
+
+
+def test_cuda_graph_replay_encoder(cuda_device):
+    """Capture the fused encoder block once, replay it on new inputs (the reference's GraphRunner contract)."""
+    from xpu_graph_b200.fused_graphs import FusedEncoderBlock
+    from xpu_graph_b200.graph_runner import CUDAGraphRunner
+    from xpu_graph_b200.workloads import make_encoder
+
+    model, x = make_encoder(seed=0)
+    fused = FusedEncoderBlock(model.to(cuda_device))
+    runner = CUDAGraphRunner(fused)
+    xd = x.to(cuda_device)
+    runner.capture(xd, clone_args=True)
+    g = torch.Generator().manual_seed(99)
+    for _ in range(2):
+        x2 = torch.randn(x.shape, generator=g)
+        with torch.no_grad():
+            want = model.cpu()(x2)
+        model.to(cuda_device)
+        got = runner(x2.to(cuda_device)).clone()
+        assert_parity(got, want, "graph replay")
+
+
+def test_cuda_graph_replay_llama_small(cuda_device):
+    from xpu_graph_b200 import lib
+    from xpu_graph_b200.fused_graphs import FusedLlamaDecoderLayer
+    from xpu_graph_b200.graph_runner import CUDAGraphRunner
+    from xpu_graph_b200.workloads import make_llama_layer
+
+    model, (x, cos, sin) = make_llama_layer(seed=3, batch=1, seq=256, hidden=512, heads=4, ffn=1376)
+    with torch.no_grad():
+        want = model(x, cos, sin)
+    fused = FusedLlamaDecoderLayer(model.to(cuda_device))
+    runner = CUDAGraphRunner(fused)
+    args = (x.to(cuda_device), cos.to(cuda_device), sin.to(cuda_device))
+    runner.capture(*args, clone_args=True)
+    got = runner(*args).clone()
+    torch.cuda.synchronize()
+    assert lib.tc_status() == 0
+    assert_parity(got, want, "llama graph replay")
