@@ -55,8 +55,8 @@ def test_argument_validation_without_gpu():
     assert L.xg_gemm_bias_act(p, p, None, None, p, 4, 4, 0, 4, 4, 4, 0, 1, 0, lib.XG_F32, None) == -1  # K == 0
     assert L.xg_gemm_bias_act(p, p, None, None, p, 4, 4, 8, 4, 8, 4, 0, 1, 0, lib.XG_F32, None) == -1  # lda < K
     assert L.xg_gemm_bias_act(p, p, None, None, p, 4, 4, 8, 8, 8, 4, 0, 1, 9, lib.XG_F32, None) == -1  # bad act
-    assert L.xg_gemm_bias_act(p, p, None, None, p, 8, 8, 8, 8, 8, 8, 0, 0, 0, lib.XG_BF16, None) == -2  # [K,N] bf16: no kernel
-    assert "trans_b" in lib.last_error()
+    assert L.xg_gemm_bias_act(p, p, None, None, p, 8, 8, 8, 12, 8, 8, 0, 1, 0, lib.XG_BF16, None) == -2  # lda not 16-byte rows
+    assert "16-byte" in lib.last_error()
     assert L.xg_gemm_swiglu(p, p, p, p, 8, 8, 8, 8, 8, 8, lib.XG_F32, None) == -2
     assert L.xg_sdpa_fwd(None, None, None, None, None, 1, 1, 1, 1, 8, None, None, None, None, None, 1.0, 0, lib.XG_BF16, None) == -1
     assert L.xg_gather_rows(None, None, 2, None, 2, 1, None, 1, None, 4, 8, 16, 4, None) == -1

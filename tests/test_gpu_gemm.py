@@ -56,6 +56,20 @@ def test_dense_bias_forms(cuda_device, bias_form):
     assert_parity(got, ref_ops.dense(x, w, True, bias, "gelu"), f"dense bias {bias_form}")
 
 
+@pytest.mark.parametrize("act", ["none", "gelu"])
+@pytest.mark.parametrize("M,K,N", [(128, 64, 256), (300, 512, 1000), (130, 72, 264), (64, 4096, 128)])
+def test_dense_bf16_kn_weights(cuda_device, M, K, N, act):
+    """Weights given as [K, N] (x @ W without a transpose): consumed MN-major by the tensor cores."""
+    from xpu_graph_b200 import lib
+    from xpu_graph_b200.modules import DenseLayerModule
+
+    x, w, b = _mk(M, K, N, torch.bfloat16, 27, weight_trans=False)
+    got = DenseLayerModule(False)(x.to(cuda_device), w.to(cuda_device), False, b.to(cuda_device), act)
+    torch.cuda.synchronize()
+    assert lib.tc_status() == 0
+    assert_parity(got, ref_ops.dense(x, w, False, b, act), f"dense bf16 [K,N] {M}x{K}x{N} {act}")
+
+
 def test_dense_fp16(cuda_device):
     from xpu_graph_b200.modules import DenseLayerModule
 

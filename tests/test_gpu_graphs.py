@@ -59,6 +59,7 @@ def test_cuda_graph_replay_encoder(cuda_device):
     from xpu_graph_b200.workloads import make_encoder
 
     model, x = make_encoder(seed=0)
+    cpu_model, _ = make_encoder(seed=0)  # same seed: an identical copy that stays on the CPU
     fused = FusedEncoderBlock(model.to(cuda_device))
     runner = CUDAGraphRunner(fused)
     xd = x.to(cuda_device)
@@ -67,8 +68,7 @@ def test_cuda_graph_replay_encoder(cuda_device):
     for _ in range(2):
         x2 = torch.randn(x.shape, generator=g)
         with torch.no_grad():
-            want = model.cpu()(x2)
-        model.to(cuda_device)
+            want = cpu_model(x2)
         got = runner(x2.to(cuda_device)).clone()
         assert_parity(got, want, "graph replay")
 

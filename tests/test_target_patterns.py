@@ -165,15 +165,20 @@ def test_dense_layer(tgt, xlog, act, bias):
     assert "Pattern.CustomDenseLayer changed graph" in xlog.text
 
 
-def test_bf16_dense_needs_linear_layout(tgt):
-    """bf16 x @ W with W given as [K, N] has no tensor-core kernel: the constraint function refuses the
-    fusion and the matmul stays an aten op (decided at compile time, nothing falls back at run time)."""
+def test_bf16_dense_needs_tma_aligned_rows(tgt):
+    """bf16 x @ W with rows that are not multiples of 16 bytes has no tensor-core kernel: the constraint
+    function refuses the fusion and the matmul stays an aten op (decided at compile time, nothing falls
+    back at run time). Aligned [K, N] weights are fused."""
     g = torch.Generator().manual_seed(2)
     x = torch.randn(8, 16, generator=g).to(torch.bfloat16)
-    w = torch.randn(16, 24, generator=g).to(torch.bfloat16)
+    w = torch.randn(16, 20, generator=g).to(torch.bfloat16)
     want, got, mods, atens = _compile(tgt, lambda x, w: F.relu(x @ w), x, w)
     assert mods == []
     assert any("mm" in a for a in atens)
+    torch._dynamo.reset()
+    w = torch.randn(16, 24, generator=g).to(torch.bfloat16)
+    want, got, mods, atens = _compile(tgt, lambda x, w: F.relu(x @ w), x, w)
+    assert mods == ["custom_dense_layer_replacement"]
 
 
 def test_decomposed_attention_goes_through_fused_sdpa(tgt, xlog):

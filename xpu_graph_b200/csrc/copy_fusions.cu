@@ -14,6 +14,7 @@ constexpr int kMaxSegs = 64;     // segments per launch (kernel parameter space)
 constexpr int kLutMax = 8192;    // output units per row per launch (32 KiB of shared memory)
 constexpr int kCopyThreads = 256;
 constexpr int kCopyUnroll = 4;
+constexpr int kGatherRows = 8;    // rows per CTA in the gather kernel
 
 struct SegDesc {
     const char* src;
@@ -57,6 +58,32 @@ __global__ void __launch_bounds__(kCopyThreads) seg_copy_kernel(const __grid_con
     const int64_t left = p.rows - r0;
     const int nrows = (int)(left < p.rows_per_cta ? left : p.rows_per_cta);
     const int W = p.width;
+    if (W >= 128) {
+        // wide rows: walk the columns with stride 256 and take the same column of up to 4 rows at once
+        // (no index division; 4 loads in flight per thread)
+        for (int rb = 0; rb < nrows; rb += kCopyUnroll) {
+            for (int c = threadIdx.x; c < W; c += kCopyThreads) {
+                const uint32_t e = lut[c];
+                const SegDesc& sd = segs[e >> 24];
+                const int64_t j = (int64_t)(e & 0xffffffu) * sizeof(U);
+                U v[kCopyUnroll];
+#pragma unroll
+                for (int k = 0; k < kCopyUnroll; ++k) {
+                    if (rb + k < nrows) {
+                        const int64_t row = r0 + rb + k;
+                        bool zero = false;
+                        if (p.mask != nullptr) zero = ((p.mask[row] != 0) == (p.zero_when != 0));
+                        v[k] = zero ? zero_unit<U>() : *reinterpret_cast<const U*>(sd.src + row * sd.src_ld + j);
+                    }
+                }
+#pragma unroll
+                for (int k = 0; k < kCopyUnroll; ++k) {
+                    if (rb + k < nrows) *reinterpret_cast<U*>(sd.dst + (r0 + rb + k) * sd.dst_ld + j) = v[k];
+                }
+            }
+        }
+        return;
+    }
     const int total = nrows * W;  // host keeps rows_per_cta * width below 2^31
     for (int i0 = threadIdx.x; i0 < total; i0 += kCopyThreads * kCopyUnroll) {
         U v[kCopyUnroll];
@@ -137,39 +164,42 @@ __global__ void __launch_bounds__(kCopyThreads) gather_rows_kernel(const __grid_
         trows[k] = p.table_rows[k];
     }
     __syncthreads();
+    // One CTA owns kGatherRows consecutive rows; a thread walks the (field, unit) columns of a row with stride 256
+    // and takes the same column of 4 rows at once: 4 index loads, then 4 table loads in flight, 32-bit index math.
     const int upr = p.units_per_row;
-    const int64_t per_row = (int64_t)p.F * upr;
-    const int64_t total = p.rows * per_row;
-    const int64_t base = ((int64_t)blockIdx.x * kCopyUnroll) * kCopyThreads + threadIdx.x;
-    U v[kCopyUnroll];
-    U* d[kCopyUnroll];
+    const int per_row = p.F * upr;
+    const int64_t r0 = (int64_t)blockIdx.x * kGatherRows;
+    for (int rb = 0; rb < kGatherRows; rb += kCopyUnroll) {
+        for (int c = threadIdx.x; c < per_row; c += kCopyThreads) {
+            const int f = c / upr;
+            const int u = c - f * upr;
+            int64_t ix[kCopyUnroll];
 #pragma unroll
-    for (int k = 0; k < kCopyUnroll; ++k) {
-        const int64_t i = base + (int64_t)k * kCopyThreads;
-        if (i < total) {
-            const int64_t r = i / per_row;
-            const int rem = (int)(i - r * per_row);
-            const int f = rem / upr;
-            const int u = rem - f * upr;
-            const int64_t ix = p.idx[r * p.idx_rs + (int64_t)(p.f0 + f) * p.idx_cs];
-            bool zero = (ix < 0) || (ix >= trows[f]);
-            if (p.mask != nullptr) zero = zero || ((p.mask[r] != 0) == (p.zero_when != 0));
-            d[k] = reinterpret_cast<U*>(p.out + r * p.out_ld_bytes + (int64_t)(p.f0 + f) * p.row_bytes) + u;
-            v[k] = zero ? zero_unit<U>() : reinterpret_cast<const U*>(tab[f] + ix * p.row_bytes)[u];
+            for (int k = 0; k < kCopyUnroll; ++k) {
+                const int64_t r = r0 + rb + k;
+                ix[k] = (r < p.rows) ? p.idx[r * p.idx_rs + (int64_t)(p.f0 + f) * p.idx_cs] : -1;
+            }
+            U v[kCopyUnroll];
+#pragma unroll
+            for (int k = 0; k < kCopyUnroll; ++k) {
+                const int64_t r = r0 + rb + k;
+                bool zero = (ix[k] < 0) || (ix[k] >= trows[f]);
+                if (r < p.rows && p.mask != nullptr) zero = zero || ((p.mask[r] != 0) == (p.zero_when != 0));
+                v[k] = zero ? zero_unit<U>() : reinterpret_cast<const U*>(tab[f] + ix[k] * p.row_bytes)[u];
+            }
+#pragma unroll
+            for (int k = 0; k < kCopyUnroll; ++k) {
+                const int64_t r = r0 + rb + k;
+                if (r < p.rows)
+                    reinterpret_cast<U*>(p.out + r * p.out_ld_bytes + (int64_t)(p.f0 + f) * p.row_bytes)[u] = v[k];
+            }
         }
-    }
-#pragma unroll
-    for (int k = 0; k < kCopyUnroll; ++k) {
-        const int64_t i = base + (int64_t)k * kCopyThreads;
-        if (i < total) *d[k] = v[k];
     }
 }
 
 template <typename U>
 int launch_gather(const GatherParams& p, cudaStream_t st) {
-    const int64_t total = p.rows * p.F * p.units_per_row;
-    const int64_t per_cta = (int64_t)kCopyThreads * kCopyUnroll;
-    const int64_t grid = (total + per_cta - 1) / per_cta;
+    const int64_t grid = (p.rows + kGatherRows - 1) / kGatherRows;
     if (grid > 0x7fffffffLL) return fail(XG_ERR_TOO_LARGE, "xg_gather_rows: too many tiles");
     gather_rows_kernel<U><<<(unsigned)grid, kCopyThreads, 0, st>>>(p);
     return check_launch("xg_gather_rows");
@@ -277,6 +307,7 @@ extern "C" int xg_gather_rows(const void* const* tables, const int64_t* table_ro
             p.table_rows[k] = table_rows[f0 + k];
         }
         p.units_per_row = (int32_t)(row_bytes / unit);
+        if ((int64_t)p.F * p.units_per_row > 0x3fffffffLL) return fail(XG_ERR_TOO_LARGE, "xg_gather_rows: F * D too large");
         p.zero_when = mask_zero_when;
         p.rows = rows;
         p.row_bytes = row_bytes;

@@ -120,34 +120,36 @@ __device__ __forceinline__ float silu_f(float g) {
     return __fdividef(g, 1.0f + __expf(-g));
 }
 
-template <typename T, int UNROLL>
+// One CTA owns ROWS consecutive rows; a thread walks the row's 16-byte vectors with stride 256 and handles the
+// same column of all ROWS rows at once (2*ROWS loads in flight, no index division anywhere).
+template <typename T, int ROWS>
 __global__ void __launch_bounds__(256) swiglu_vec_kernel(const SwigluParams p) {
     constexpr int EPV = Vec16<T>::N;
-    const int64_t vec_per_row = p.cols / EPV;
-    const int64_t total = p.rows * vec_per_row;
-    const int64_t base = ((int64_t)blockIdx.x * UNROLL) * blockDim.x + threadIdx.x;
-    Vec16<T> g[UNROLL], u[UNROLL];
-    int64_t off_o[UNROLL];
+    const int vec_per_row = (int)(p.cols / EPV);
+    const int64_t r0 = (int64_t)blockIdx.x * ROWS;
+    const T* gp = reinterpret_cast<const T*>(p.gate);
+    const T* up = reinterpret_cast<const T*>(p.up);
+    T* op = reinterpret_cast<T*>(p.out);
+    for (int c = threadIdx.x; c < vec_per_row; c += 256) {
+        Vec16<T> g[ROWS], u[ROWS];
 #pragma unroll
-    for (int k = 0; k < UNROLL; ++k) {
-        const int64_t idx = base + (int64_t)k * blockDim.x;
-        if (idx < total) {
-            const int64_t r = idx / vec_per_row;
-            const int64_t c = (idx - r * vec_per_row) * EPV;
-            g[k] = ld16_stream(reinterpret_cast<const T*>(p.gate) + r * p.ldg + c);
-            u[k] = ld16_stream(reinterpret_cast<const T*>(p.up) + r * p.ldu + c);
-            off_o[k] = r * p.ldo + c;
+        for (int k = 0; k < ROWS; ++k) {
+            const int64_t r = r0 + k;
+            if (r < p.rows) {
+                g[k] = ld16_stream(gp + r * p.ldg + (int64_t)c * EPV);
+                u[k] = ld16_stream(up + r * p.ldu + (int64_t)c * EPV);
+            }
         }
-    }
 #pragma unroll
-    for (int k = 0; k < UNROLL; ++k) {
-        const int64_t idx = base + (int64_t)k * blockDim.x;
-        if (idx < total) {
-            Vec16<T> o;
+        for (int k = 0; k < ROWS; ++k) {
+            const int64_t r = r0 + k;
+            if (r < p.rows) {
+                Vec16<T> o;
 #pragma unroll
-            for (int i = 0; i < EPV; ++i)
-                o.v[i] = Cvt<T>::from_f(silu_f<T>(Cvt<T>::to_f(g[k].v[i])) * Cvt<T>::to_f(u[k].v[i]));
-            st16(reinterpret_cast<T*>(p.out) + off_o[k], o);
+                for (int i = 0; i < EPV; ++i)
+                    o.v[i] = Cvt<T>::from_f(silu_f<T>(Cvt<T>::to_f(g[k].v[i])) * Cvt<T>::to_f(u[k].v[i]));
+                st16(op + r * p.ldo + (int64_t)c * EPV, o);
+            }
         }
     }
 }
@@ -169,9 +171,8 @@ int launch_swiglu(const SwigluParams& p, cudaStream_t st) {
     constexpr int UNROLL = 4;
     const bool vec_ok = p.cols % EPV == 0 && p.ldg % EPV == 0 && p.ldu % EPV == 0 && p.ldo % EPV == 0 &&
                         aligned16(p.gate) && aligned16(p.up) && aligned16(p.out);
-    if (vec_ok) {
-        const int64_t total = p.rows * (p.cols / EPV);
-        const int64_t grid = (total + 256 * UNROLL - 1) / (256 * UNROLL);
+    if (vec_ok && p.cols / EPV < 0x7fffffffLL) {
+        const int64_t grid = (p.rows + UNROLL - 1) / UNROLL;
         if (grid > 0x7fffffffLL) return fail(XG_ERR_TOO_LARGE, "xg_swiglu: tensor too large");
         swiglu_vec_kernel<T, UNROLL><<<(unsigned)grid, 256, 0, st>>>(p);
     } else {

@@ -4,7 +4,8 @@
 
 namespace xg {
 int gemm_tc_entry(const void* A, const void* B, const void* bias, const void* residual, void* out, int64_t M, int64_t N,
-                  int64_t K, int64_t lda, int64_t ldb, int64_t ldc, int64_t ldr, int act, int dtype, cudaStream_t st);
+                  int64_t K, int64_t lda, int64_t ldb, int64_t ldc, int64_t ldr, int trans_b, int act, int dtype,
+                  cudaStream_t st);
 int gemm_f32_entry(const void* A, const void* B, const void* bias, const void* residual, void* out, int64_t M, int64_t N,
                    int64_t K, int64_t lda, int64_t ldb, int64_t ldc, int64_t ldr, int trans_b, int act, cudaStream_t st);
 int gemm_swiglu_entry(const void* A, const void* Wg, const void* Wu, void* out, int64_t M, int64_t N, int64_t K,
@@ -34,9 +35,7 @@ extern "C" int xg_gemm_bias_act(const void* A, const void* B, const void* bias, 
     if (rc != XG_OK) return rc;
     cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
     if (dtype == XG_F32) return gemm_f32_entry(A, B, bias, residual, out, M, N, K, lda, ldb, ldc, ldr, trans_b, act, st);
-    if (!trans_b)
-        return fail(XG_ERR_UNSUPPORTED, "xg_gemm_bias_act: 16-bit weights must be [N, K] (trans_b = 1); [K, N] has no kernel");
-    return gemm_tc_entry(A, B, bias, residual, out, M, N, K, lda, ldb, ldc, ldr, act, dtype, st);
+    return gemm_tc_entry(A, B, bias, residual, out, M, N, K, lda, ldb, ldc, ldr, trans_b, act, dtype, st);
 }
 
 extern "C" int xg_bgemm_bias_act(const void* A, const void* B, const void* bias, const void* residual, void* out,

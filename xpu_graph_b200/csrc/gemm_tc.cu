@@ -121,7 +121,9 @@ __device__ __forceinline__ void tile_coords(int t, int num_m, int num_n, int& mb
 
 // SWIGLU: the W tile is [gate rows ; up rows] (BN/2 each, two TMA loads), so accumulator columns
 // [0, BN/2) hold A @ Wg^T and [BN/2, BN) hold A @ Wu^T; the epilogue writes silu(gate) * up, BN/2 wide.
-template <typename T, int BN, bool SWIGLU>
+// B_MN: W is given as [K, N] row-major (N contiguous): its tiles are loaded as BN/64 boxes of [64 k x 64 n] and
+// consumed MN-major (the layout TMA leaves: rows = k, 128-byte rows of n), so no transpose is ever materialised.
+template <typename T, int BN, bool SWIGLU, bool B_MN>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                const __grid_constant__ CUtensorMap tmap_b2, const GemmParams p) {
@@ -190,6 +192,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                         ptx::tma_load_2d(smem_b + stage * Cfg::B_BYTES, &tmap_b, &full_bar[stage], kb * BK, nb * OUT_BN);
                         ptx::tma_load_2d(smem_b + stage * Cfg::B_BYTES + Cfg::B_BYTES / 2, &tmap_b2, &full_bar[stage],
                                          kb * BK, nb * OUT_BN);
+                    } else if (B_MN) {
+#pragma unroll
+                        for (int j = 0; j < BN / 64; ++j)
+                            ptx::tma_load_2d(smem_b + stage * Cfg::B_BYTES + j * (BK * 128), &tmap_b, &full_bar[stage],
+                                             nb * BN + j * 64, kb * BK);
                     } else {
                         ptx::tma_load_2d(smem_b + stage * Cfg::B_BYTES, &tmap_b, &full_bar[stage], kb * BK, nb * BN);
                     }
@@ -214,7 +221,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     } else if (warp == 1) {
         // ------------------------------ MMA issuer --------------------------------
         if (ptx::elect_one()) {
-            constexpr uint32_t idesc = ptx::make_idesc_f16(sizeof(T) == 2 && std::is_same<T, __nv_bfloat16>::value ? 1 : 0, BM, BN);
+            constexpr uint32_t idesc = ptx::make_idesc_f16(std::is_same<T, __nv_bfloat16>::value ? 1 : 0, BM, BN, B_MN ? 1 : 0);
             int stage = 0;
             uint32_t phase = 0;
             int acc = 0;
@@ -230,11 +237,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                     const uint32_t a_addr = ptx::smem_u32(smem_a + stage * Cfg::A_BYTES);
                     const uint32_t b_addr = ptx::smem_u32(smem_b + stage * Cfg::B_BYTES);
                     const uint64_t da = ptx::make_kmajor_sw128_desc(a_addr);
-                    const uint64_t db = ptx::make_kmajor_sw128_desc(b_addr);
+                    const uint64_t db = B_MN ? ptx::make_mnmajor_sw128_desc(b_addr, BK * 128) : ptx::make_kmajor_sw128_desc(b_addr);
 #pragma unroll
                     for (int k = 0; k < BK / UMMA_K; ++k) {
-                        // +32 bytes per 16-element K step, in the descriptor's 16-byte address units
-                        ptx::mma_f16_ss(tmem_d, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc, (kb | k) != 0 ? 1u : 0u);
+                        // K-major: +32 bytes per 16-element K step; MN-major: +16 rows of 128 bytes
+                        // (both in the descriptor's 16-byte address units)
+                        const uint64_t db_k = db + (uint64_t)(B_MN ? k * 128 : k * 2);
+                        ptx::mma_f16_ss(tmem_d, da + (uint64_t)(k * 2), db_k, idesc, (kb | k) != 0 ? 1u : 0u);
                     }
                     ptx::tc_commit(&empty_bar[stage]);  // stage reusable once these MMAs have read it
                     if (++stage == STAGES) { stage = 0; phase ^= 1u; }
@@ -351,11 +360,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     }
 }
 
-template <typename T, int BN, bool SWIGLU>
+template <typename T, int BN, bool SWIGLU, bool B_MN>
 int launch_gemm_tc(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tb2, const GemmParams& p,
                    cudaStream_t st) {
     using Cfg = GemmCfg<BN>;
-    auto kern = gemm_tc_kernel<T, BN, SWIGLU>;
+    auto kern = gemm_tc_kernel<T, BN, SWIGLU, B_MN>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
     if (e != cudaSuccess) {
         cudaGetLastError();
@@ -370,7 +379,7 @@ int launch_gemm_tc(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorM
 
 template <typename T>
 int gemm_tc_dispatch(const void* A, const void* B, const void* bias, const void* residual, void* out, int64_t M,
-                     int64_t N, int64_t K, int64_t lda, int64_t ldb, int64_t ldc, int64_t ldr, int act,
+                     int64_t N, int64_t K, int64_t lda, int64_t ldb, int64_t ldc, int64_t ldr, int trans_b, int act,
                      cudaStream_t st) {
     constexpr bool is_bf16 = std::is_same<T, __nv_bfloat16>::value;
     // Tile width: the widest tile that still gives every SM work.
@@ -381,8 +390,9 @@ int gemm_tc_dispatch(const void* A, const void* B, const void* bias, const void*
     if (bn == 128 && mblk * ((N + 127) / 128) < sms) bn = 64;
 
     CUtensorMap ta, tb;
-    if (!make_tmap_2d_16bit(&ta, A, (uint64_t)M, (uint64_t)K, (uint64_t)lda, BM, BK, is_bf16) ||
-        !make_tmap_2d_16bit(&tb, B, (uint64_t)N, (uint64_t)K, (uint64_t)ldb, (uint32_t)bn, BK, is_bf16))
+    const bool b_ok = trans_b ? make_tmap_2d_16bit(&tb, B, (uint64_t)N, (uint64_t)K, (uint64_t)ldb, (uint32_t)bn, BK, is_bf16)
+                              : make_tmap_2d_16bit(&tb, B, (uint64_t)K, (uint64_t)N, (uint64_t)ldb, BK, 64, is_bf16);
+    if (!make_tmap_2d_16bit(&ta, A, (uint64_t)M, (uint64_t)K, (uint64_t)lda, BM, BK, is_bf16) || !b_ok)
         return fail(XG_ERR_UNSUPPORTED, "xg_gemm_bias_act: tensor-map encoding failed (M=%lld N=%lld K=%lld lda=%lld ldb=%lld)",
                     (long long)M, (long long)N, (long long)K, (long long)lda, (long long)ldb);
     GemmParams p;
@@ -396,10 +406,17 @@ int gemm_tc_dispatch(const void* A, const void* B, const void* bias, const void*
     p.num_m_blocks = (int)mblk;
     p.num_n_blocks = (int)((N + bn - 1) / bn);
     p.num_k_blocks = (int)((K + BK - 1) / BK);
+    if (!trans_b) {
+        switch (bn) {
+            case 256: return launch_gemm_tc<T, 256, false, true>(ta, tb, tb, p, st);
+            case 128: return launch_gemm_tc<T, 128, false, true>(ta, tb, tb, p, st);
+            default: return launch_gemm_tc<T, 64, false, true>(ta, tb, tb, p, st);
+        }
+    }
     switch (bn) {
-        case 256: return launch_gemm_tc<T, 256, false>(ta, tb, tb, p, st);
-        case 128: return launch_gemm_tc<T, 128, false>(ta, tb, tb, p, st);
-        default: return launch_gemm_tc<T, 64, false>(ta, tb, tb, p, st);
+        case 256: return launch_gemm_tc<T, 256, false, false>(ta, tb, tb, p, st);
+        case 128: return launch_gemm_tc<T, 128, false, false>(ta, tb, tb, p, st);
+        default: return launch_gemm_tc<T, 64, false, false>(ta, tb, tb, p, st);
     }
 }
 
@@ -423,22 +440,23 @@ int gemm_swiglu_dispatch(const void* A, const void* Wg, const void* Wu, void* ou
     p.num_m_blocks = (int)((M + BM - 1) / BM);
     p.num_n_blocks = (int)((N + 127) / 128);
     p.num_k_blocks = (int)((K + BK - 1) / BK);
-    return launch_gemm_tc<T, 256, true>(ta, tg, tu, p, st);
+    return launch_gemm_tc<T, 256, true, false>(ta, tg, tu, p, st);
 }
 
 }  // namespace
 
-// Entry used by xg_gemm_bias_act for 16-bit dtypes with W given as [N, K] (trans_b = 1).
+// Entry used by xg_gemm_bias_act for 16-bit dtypes; W is [N, K] (trans_b = 1) or [K, N] (trans_b = 0).
 int gemm_tc_entry(const void* A, const void* B, const void* bias, const void* residual, void* out, int64_t M, int64_t N,
-                  int64_t K, int64_t lda, int64_t ldb, int64_t ldc, int64_t ldr, int act, int dtype, cudaStream_t st) {
+                  int64_t K, int64_t lda, int64_t ldb, int64_t ldc, int64_t ldr, int trans_b, int act, int dtype,
+                  cudaStream_t st) {
     if (!aligned16(A) || !aligned16(B) || lda % 8 != 0 || ldb % 8 != 0)
         return fail(XG_ERR_UNSUPPORTED, "xg_gemm_bias_act: A/W must be 16-byte aligned with row strides multiple of 8 elements");
     if (M * N == 0) return XG_OK;
     if (M > (int64_t)BM * 0x7fffff || N > (int64_t)64 * 0x7fffff || K > 0x7fffffff)
         return fail(XG_ERR_TOO_LARGE, "xg_gemm_bias_act: extent too large");
     if (dtype == XG_BF16)
-        return gemm_tc_dispatch<__nv_bfloat16>(A, B, bias, residual, out, M, N, K, lda, ldb, ldc, ldr, act, st);
-    return gemm_tc_dispatch<__half>(A, B, bias, residual, out, M, N, K, lda, ldb, ldc, ldr, act, st);
+        return gemm_tc_dispatch<__nv_bfloat16>(A, B, bias, residual, out, M, N, K, lda, ldb, ldc, ldr, trans_b, act, st);
+    return gemm_tc_dispatch<__half>(A, B, bias, residual, out, M, N, K, lda, ldb, ldc, ldr, trans_b, act, st);
 }
 
 int gemm_swiglu_entry(const void* A, const void* Wg, const void* Wu, void* out, int64_t M, int64_t N, int64_t K,

@@ -270,9 +270,14 @@ flash_tc_kernel(const __grid_constant__ CUtensorMap tmq, const __grid_constant__
                     if (col >= skv || (p.causal && col > row)) sc[i] = -INFINITY;
                 }
             }
-            float mx = sc[0];
+            // 8 independent chains instead of one 64-deep dependency chain
+            float mxp[8];
 #pragma unroll
-            for (int i = 1; i < FN; ++i) mx = fmaxf(mx, sc[i]);
+            for (int i = 0; i < 8; ++i) mxp[i] = sc[i];
+#pragma unroll
+            for (int i = 8; i < FN; ++i) mxp[i & 7] = fmaxf(mxp[i & 7], sc[i]);
+            const float mx = fmaxf(fmaxf(fmaxf(mxp[0], mxp[1]), fmaxf(mxp[2], mxp[3])),
+                                   fmaxf(fmaxf(mxp[4], mxp[5]), fmaxf(mxp[6], mxp[7])));
             const float m_new = fmaxf(m_run, mx);
             const bool grow = m_new > m_run + kRescaleThreshold;  // also true for the first finite maximum
             const bool warp_rescale = __any_sync(0xffffffffu, grow);
@@ -302,18 +307,20 @@ flash_tc_kernel(const __grid_constant__ CUtensorMap tmq, const __grid_constant__
             }
             const float m_use = (m_run == -INFINITY) ? 0.f : m_run;
             // probabilities -> shared memory (row r_in_tile of the swizzled K-major P tile)
+            float lp[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};  // independent partial row sums
 #pragma unroll
             for (int t = 0; t < FN / 8; ++t) {
                 Vec16<T> pv;
 #pragma unroll
                 for (int i = 0; i < 8; ++i) {
                     const float pr = ptx::ex2_approx(sc[t * 8 + i] - m_use);
-                    l_run += pr;
+                    lp[i] += pr;
                     pv.v[i] = Cvt<T>::from_f(pr);
                 }
                 uint8_t* dst = p_s + r_in_tile * 128 + ((t ^ (r_in_tile & 7)) << 4);
                 *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<const uint4*>(&pv);
             }
+            l_run += ((lp[0] + lp[1]) + (lp[2] + lp[3])) + ((lp[4] + lp[5]) + (lp[6] + lp[7]));
             ptx::fence_proxy_async();  // P (generic-proxy stores) must be visible to the tensor core
             ptx::tc_fence_before();
             ptx::mbar_arrive(p_full);

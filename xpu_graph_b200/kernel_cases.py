@@ -26,15 +26,87 @@ def _time(fn, iters):
     return e0.elapsed_time(e1) / iters
 
 
+def _time_graphed(fn, reps=10, iters=5):
+    """Device time per call with the host out of the picture: `reps` calls are captured in one CUDA graph."""
+    fn()
+    torch.cuda.synchronize()
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        fn()
+    torch.cuda.current_stream().wait_stream(side)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph, stream=side):
+        for _ in range(reps):
+            fn()
+    graph.replay()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(iters):
+        graph.replay()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / (iters * reps)
+
+
+def sweep():
+    """Stand-alone sweeps of the norm and dense-layer kernels (the shapes of benchmark configs 2 and 3),
+    printed as markdown tables with the achieved fraction of the measured peaks."""
+    import json
+    import os
+
+    from . import workloads as W
+
+    X = torch.ops.xg_sm100
+    dev = torch.device("cuda")
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    peaks = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
+    pk = os.path.join(root, "MEASURED_PEAKS.json")
+    if os.path.exists(pk):
+        peaks = json.load(open(pk))
+    print(f"peaks: HBM {peaks['hbm_gbs']:.0f} GB/s, bf16 {peaks['bf16_tflops']:.0f} TFLOP/s (burst)\n")
+    print("| rows | hidden | pattern | us | GB/s | of measured HBM |")
+    print("|---:|---:|---|---:|---:|---:|")
+    for hidden in W.NORM_SWEEP_HIDDEN:
+        for rows in W.NORM_SWEEP_ROWS:
+            x, r, gamma, beta = W.make_norm_inputs(rows, hidden, device=dev)
+            cases = [
+                ("add+RMSNorm (1 out)", lambda: X.add_rms_norm_y(x, r, gamma, 1e-6), 6),
+                ("add+RMSNorm (2 out)", lambda: X.add_rms_norm(x, r, gamma, 1e-6), 8),
+                ("add+LayerNorm (1 out)", lambda: X.add_layer_norm_y(x, r, gamma, beta, 1e-5), 6),
+                ("add+LayerNorm (2 out)", lambda: X.add_layer_norm(x, r, gamma, beta, 1e-5), 8),
+            ]
+            for name, fn, bpe in cases:
+                ms = _time_graphed(fn)
+                gbs = bpe * rows * hidden / ms / 1e6
+                print(f"| {rows} | {hidden} | {name} | {ms * 1e3:.1f} | {gbs:.0f} | {gbs / peaks['hbm_gbs']:.2f} |")
+            del x, r
+    print()
+    print("| M | K | N | epilogue | us | TFLOP/s | of measured bf16 | GB/s (A+W+out) |")
+    print("|---:|---:|---:|---|---:|---:|---:|---:|")
+    for (M, K, N) in W.GEMM_SWEEP:
+        a, w, b = W.make_gemm_inputs(M, K, N, device=dev)
+        for act in ("gelu", "silu"):
+            ms = _time_graphed(lambda: X.dense(a, w, True, b, None, act), reps=5)
+            tf = 2 * M * N * K / ms / 1e9
+            gbs = 2 * (M * K + N * K + M * N) / ms / 1e6
+            print(f"| {M} | {K} | {N} | bias+{act} | {ms * 1e3:.1f} | {tf:.0f} | {tf / peaks['bf16_tflops']:.2f} | {gbs:.0f} |")
+        del a, w
+    return 0
+
+
 def main(argv=None):
     from . import lib, ops  # noqa: F401
 
     X = torch.ops.xg_sm100
     ap = argparse.ArgumentParser()
-    ap.add_argument("case", choices=["gemm", "gemm_swiglu", "gemm_small_m", "add_rms_norm", "layer_norm", "sdpa", "rope", "swiglu",
+    ap.add_argument("case", choices=["sweep", "gemm", "gemm_swiglu", "gemm_small_m", "add_rms_norm", "layer_norm", "sdpa", "rope", "swiglu",
                                      "gather", "slice_cat", "gemm_f32"])
     ap.add_argument("--iters", type=int, default=3)
     args = ap.parse_args(argv)
+    if args.case == "sweep":
+        return sweep()
     dev = torch.device("cuda")
     bf = torch.bfloat16
     g = torch.Generator(device=dev).manual_seed(0)

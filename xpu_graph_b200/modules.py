@@ -109,10 +109,11 @@ def can_fuse_custom_denselayer(inputs, weight, weight_trans, bias, act_str):
     if inputs.device.type not in ALLOWED_DEVICE_TYPES:
         return False
     if inputs.dtype != torch.float32:
-        # tensor-core kernel: weights in Linear layout [N, K], K a multiple of 8 (16-byte rows for TMA)
-        if not weight_trans:
-            return False
+        # tensor-core kernel: every TMA-read row must be a multiple of 16 bytes: K for the activations and
+        # [N, K] weights, N for weights given as [K, N]
         if inputs.shape[1] % 8 != 0:
+            return False
+        if not weight_trans and weight.shape[1] % 8 != 0:
             return False
     return True
 
@@ -140,7 +141,7 @@ def can_fuse_custom_batch_denselayer(inputs, weight, weight_trans, bias, act_str
         return False
     if inputs.dtype not in _SUPPORTED or weight.dtype != inputs.dtype:
         return False
-    if inputs.dtype != torch.float32 and (not weight_trans or inputs.shape[2] % 8 != 0):
+    if inputs.dtype != torch.float32 and (inputs.shape[2] % 8 != 0 or (not weight_trans and weight.shape[2] % 8 != 0)):
         return False
     return True
 
