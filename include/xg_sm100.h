@@ -124,6 +124,21 @@ int xg_gemm_bias_act(const void* A, const void* B, const void* bias, const void*
                      int64_t ldr, int trans_b, int act, int dtype, void* stream);
 
 /*
+ * Same as xg_gemm_bias_act with caller-provided scratch memory. For small M (few output tiles) the
+ * 16-bit kernel splits K over several CTAs per tile: each writes its fp32 partial sums to `workspace`
+ * ([splits][M][N] floats) and a second pass reduces them in a fixed order (deterministic) and applies
+ * bias / residual / activation. xg_gemm_workspace_bytes returns the size this shape would like (0 when
+ * splitting does not pay); a smaller or null workspace only lowers the split factor. The workspace
+ * must be 16-byte aligned device memory; its contents before and after the call are unspecified.
+ * Reference counterpart: the same torch_mlu_ops.matmul call site as xg_gemm_bias_act.
+ */
+int xg_gemm_bias_act_ws(const void* A, const void* B, const void* bias, const void* residual, void* out,
+                        int64_t M, int64_t N, int64_t K, int64_t lda, int64_t ldb, int64_t ldc,
+                        int64_t ldr, int trans_b, int act, int dtype, void* workspace,
+                        int64_t workspace_bytes, void* stream);
+int64_t xg_gemm_workspace_bytes(int64_t M, int64_t N, int64_t K, int dtype);
+
+/*
  * Batched form: out[b] = act( A[b] @ W[b] + bias[b] + residual[b] ), batch strides in elements
  * (0 broadcasts). Replaces: dense_layer_modules.py:71-120 (BatchDenseLayerModule) as called by
  * passes/patterns/structure/custom_denselayer.py:111-117.
@@ -190,6 +205,17 @@ int xg_gather_rows(const void* const* tables, const int64_t* table_rows, int64_t
                    int64_t idx_row_stride, int64_t idx_col_stride, const uint8_t* row_mask,
                    int mask_zero_when, void* out, int64_t rows, int64_t D, int64_t out_ld,
                    int elem_size, void* stream);
+
+/*
+ * Batched sum over one dim of n contiguous 3-D tensors in one launch: outputs[k] = sum(inputs[k], dim),
+ * shapes3 = HOST array [n][3] of (s0, s1, s2); dim 0 -> [s1, s2], dim 1 -> [s0, s2], dim 2 -> [s0, s1]
+ * (contiguous, same dtype, fp32 accumulation). inputs/outputs: HOST arrays of device pointers.
+ * Replaces: targets/mlu/triton_kernel/fused_sum_3d.py:131-205 (fused_sum_3d_input) as called by
+ * targets/mlu/structure_replacements/__init__.py:147-165 (ComboSumModule) for
+ * passes/patterns/structure/fuse_combosum.py:82-98 (ComboSum3dInp).
+ */
+int xg_sum3d(const void* const* inputs, void* const* outputs, const int64_t* shapes3, int64_t n, int dim,
+             int dtype, void* stream);
 
 #ifdef __cplusplus
 }

@@ -200,3 +200,11 @@ def gather_stack(tables, idx, mask=None):
         out = out.copy()
         out[_np(mask).reshape(-1).astype(bool), :] = 0
     return _like(out, tables[0])
+
+
+def combo_sum(inputs, dim):
+    """targets/mlu/structure_replacements/__init__.py:147-165 (ComboSumModule): sum(x, dim[0]) for each
+    3-D tensor of the list, i.e. the aten.sum.dim_IntList nodes that ComboSum3dInp batches
+    (passes/patterns/structure/fuse_combosum.py:82-98)."""
+    d = dim[0] if isinstance(dim, (list, tuple)) else dim
+    return [x.sum(dim=d) for x in inputs]

@@ -79,4 +79,5 @@ def register():
         return ref_ops.gather_stack(tables, idx, m)
 
     k(ops.gather_stack)(gather_stack)
+    k(ops.sum3d)(lambda inputs, dim: ref_ops.combo_sum(inputs, dim))
     _DONE = True

@@ -120,3 +120,20 @@ def test_gather_strided_index(cuda_device):
     idx_t = torch.randint(0, 50, (4, 300), generator=g, dtype=torch.int64)
     got = GatherStackModule()([t.to(cuda_device) for t in tables], idx_t.to(cuda_device).t())
     assert_bit_exact(got, ref_ops.gather_stack(tables, idx_t.t().contiguous(), None), "gather strided idx")
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("dim", [0, 1, 2])
+def test_combo_sum(cuda_device, dim, dtype):
+    """Batched sum over one dim of several 3-D tensors (ComboSum3dInp), ragged shapes incl. an empty one."""
+    from tests.helpers import assert_parity
+    from xpu_graph_b200.modules import ComboSumModule
+
+    g = torch.Generator().manual_seed(16)
+    shapes = [(300, 26, 64), (7, 3, 5), (129, 64, 8), (1, 1, 1), (50, 33, 100), (0, 4, 4)]
+    xs = [torch.randn(*s, generator=g).to(dtype) for s in shapes]
+    got = ComboSumModule()([x.to(cuda_device) for x in xs], [dim])
+    want = ref_ops.combo_sum([x.float() for x in xs], [dim])
+    assert len(got) == len(want)
+    for a, e in zip(got, want):
+        assert_parity(a, e.to(dtype), f"combo_sum dim {dim}")

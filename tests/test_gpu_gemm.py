@@ -70,6 +70,32 @@ def test_dense_bf16_kn_weights(cuda_device, M, K, N, act):
     assert_parity(got, ref_ops.dense(x, w, False, b, act), f"dense bf16 [K,N] {M}x{K}x{N} {act}")
 
 
+@pytest.mark.parametrize("M,K,N,act,with_res", [(256, 4096, 4096, "gelu", False), (256, 4096, 11008, "silu", False),
+                                                (130, 1024, 1000, "none", True), (100, 2048, 1002, "relu", True),
+                                                (512, 1024, 512, "gelu", True), (1, 4096, 4096, "none", False)])
+def test_dense_split_k(cuda_device, M, K, N, act, with_res):
+    """Small-M shapes: the kernel splits K across CTAs and reduces fp32 partial sums from scratch memory
+    (allocated by the op). Checked against the oracle and for run-to-run bit equality."""
+    from xpu_graph_b200 import lib
+    from xpu_graph_b200.modules import DenseResidualModule
+
+    assert lib.load().xg_gemm_workspace_bytes(M, N, K, lib.XG_BF16) > 0, "shape expected to use split-K"
+    x, w, b = _mk(M, K, N, torch.bfloat16, 28)
+    g = torch.Generator().manual_seed(29)
+    r = torch.randn(M, N, generator=g).to(torch.bfloat16) if with_res else None
+    args = (x.to(cuda_device), w.to(cuda_device), True, b.to(cuda_device), r.to(cuda_device) if with_res else None, act)
+    got = DenseResidualModule()(*args)
+    again = DenseResidualModule()(*args)
+    torch.cuda.synchronize()
+    assert lib.tc_status() == 0
+    want = ref_ops.dense(x, w, True, b, "none")
+    if with_res:
+        want = want + r
+    want = ref_ops._ACTS[act](want)
+    assert_parity(got, want, f"split-K dense {M}x{K}x{N}")
+    assert torch.equal(got, again), "split-K reduction must be deterministic"
+
+
 def test_dense_fp16(cuda_device):
     from xpu_graph_b200.modules import DenseLayerModule
 

@@ -264,3 +264,23 @@ def test_module_signatures_match_reference_call_sites(tgt):
     assert nparams(M.FuseSliceCatSameInputModule_v2) == 2
     assert len(inspect.signature(M.DenseLayerModule.__init__).parameters) == 2   # M(fast_act)
     assert len(inspect.signature(M.FuseSliceModule.__init__).parameters) == 2    # M(start_indices)
+
+
+def test_combo_sum_after_multi_slice_cat(tgt, xlog):
+    """Two slice+cat groups of one source (merged by FusedMultipleSliceCat) reshaped to 3-D and summed:
+    ComboSum3dInp batches the sums into the target's ComboSumModule."""
+    g = torch.Generator().manual_seed(6)
+    src = torch.randn(12, 200, generator=g)
+
+    def fn(s):
+        a = torch.cat([s[:, 0:16], s[:, 32:48]], dim=-1).view(12, 2, 16).sum(dim=1)
+        b = torch.cat([s[:, 64:80], s[:, 100:116], s[:, 120:136]], dim=-1).view(12, 3, 16).sum(dim=1)
+        return a * 2.0, b * 3.0
+
+    want, got, mods, atens = _compile(tgt, fn, src)
+    _same(got[0], want[0])
+    _same(got[1], want[1])
+    assert "Pattern.FusedMultipleSliceCat changed graph" in xlog.text
+    assert any(m.startswith("fuse_slice_cat_v2") for m in mods)
+    assert "Pattern.ComboSum3dInp changed graph" in xlog.text
+    assert "combo_sum" in mods and not any("sum" in a for a in atens)

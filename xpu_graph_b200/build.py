@@ -26,6 +26,7 @@ SOURCES = [
     "gemm_tc.cu",
     "gemm_f32.cu",
     "sdpa.cu",
+    "sum3d.cu",
 ]
 
 NVCC_FLAGS = [

@@ -5,9 +5,8 @@
 namespace xg {
 int gemm_tc_entry(const void* A, const void* B, const void* bias, const void* residual, void* out, int64_t M, int64_t N,
                   int64_t K, int64_t lda, int64_t ldb, int64_t ldc, int64_t ldr, int trans_b, int act, int dtype,
-                  cudaStream_t st);
-int gemm_f32_entry(const void* A, const void* B, const void* bias, const void* residual, void* out, int64_t M, int64_t N,
-                   int64_t K, int64_t lda, int64_t ldb, int64_t ldc, int64_t ldr, int trans_b, int act, cudaStream_t st);
+                  void* workspace, int64_t ws_bytes, cudaStream_t st, bool force_split = false);
+int64_t gemm_workspace_bytes(int64_t M, int64_t N, int64_t K);
 int gemm_swiglu_entry(const void* A, const void* Wg, const void* Wu, void* out, int64_t M, int64_t N, int64_t K,
                       int64_t lda, int64_t ldw, int64_t ldc, int dtype, cudaStream_t st);
 int read_tc_status(unsigned int* host_out, int reset);
@@ -27,15 +26,30 @@ int validate_gemm(const char* name, const void* A, const void* B, const void* re
 }  // namespace
 }  // namespace xg
 
-extern "C" int xg_gemm_bias_act(const void* A, const void* B, const void* bias, const void* residual, void* out,
-                                int64_t M, int64_t N, int64_t K, int64_t lda, int64_t ldb, int64_t ldc, int64_t ldr,
-                                int trans_b, int act, int dtype, void* stream) {
+extern "C" int xg_gemm_bias_act_ws(const void* A, const void* B, const void* bias, const void* residual, void* out,
+                                   int64_t M, int64_t N, int64_t K, int64_t lda, int64_t ldb, int64_t ldc, int64_t ldr,
+                                   int trans_b, int act, int dtype, void* workspace, int64_t workspace_bytes,
+                                   void* stream) {
     using namespace xg;
     int rc = validate_gemm("xg_gemm_bias_act", A, B, residual, out, M, N, K, lda, ldb, ldc, ldr, trans_b, act, dtype);
     if (rc != XG_OK) return rc;
+    if (workspace_bytes < 0) return fail(XG_ERR_INVALID_ARG, "xg_gemm_bias_act_ws: negative workspace size");
     cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
     if (dtype == XG_F32) return gemm_f32_entry(A, B, bias, residual, out, M, N, K, lda, ldb, ldc, ldr, trans_b, act, st);
-    return gemm_tc_entry(A, B, bias, residual, out, M, N, K, lda, ldb, ldc, ldr, trans_b, act, dtype, st);
+    return gemm_tc_entry(A, B, bias, residual, out, M, N, K, lda, ldb, ldc, ldr, trans_b, act, dtype, workspace,
+                         workspace_bytes, st);
+}
+
+extern "C" int xg_gemm_bias_act(const void* A, const void* B, const void* bias, const void* residual, void* out,
+                                int64_t M, int64_t N, int64_t K, int64_t lda, int64_t ldb, int64_t ldc, int64_t ldr,
+                                int trans_b, int act, int dtype, void* stream) {
+    return xg_gemm_bias_act_ws(A, B, bias, residual, out, M, N, K, lda, ldb, ldc, ldr, trans_b, act, dtype, nullptr, 0,
+                               stream);
+}
+
+extern "C" int64_t xg_gemm_workspace_bytes(int64_t M, int64_t N, int64_t K, int dtype) {
+    if (M <= 0 || N <= 0 || K <= 0 || (dtype != XG_BF16 && dtype != XG_F16)) return 0;
+    return xg::gemm_workspace_bytes(M, N, K);
 }
 
 extern "C" int xg_bgemm_bias_act(const void* A, const void* B, const void* bias, const void* residual, void* out,

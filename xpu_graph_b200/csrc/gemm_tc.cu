@@ -21,6 +21,15 @@
 
 namespace xg {
 
+int gemm_tc_entry(const void* A, const void* B, const void* bias, const void* residual, void* out, int64_t M, int64_t N,
+                  int64_t K, int64_t lda, int64_t ldb, int64_t ldc, int64_t ldr, int trans_b, int act, int dtype,
+                  void* workspace, int64_t ws_bytes, cudaStream_t st, bool force_split = false);
+
+struct GemmPlan {
+    int bn;      // tile width: 64, 128 or 256
+    int splits;  // split-K factor (1 = none)
+};
+
 // ---- tensor-map helpers (host) ----------------------------------------------------------------
 PFN_encodeTiled get_encode_tiled() {
     static PFN_encodeTiled fn = nullptr;
@@ -87,7 +96,16 @@ struct GemmParams {
     int vec_ok;       // out (and residual) rows are 16-byte addressable
     int bias_vec_ok;  // bias pointer 16-byte aligned
     int num_m_blocks, num_n_blocks, num_k_blocks;
+    int splits;      // > 1: split-K, every (tile, split) unit writes raw fp32 accumulators to `partial`
+    float* partial;  // [splits][M][N] fp32 workspace (split-K only)
 };
+
+// k-block range of split s of `splits` over nkb blocks (balanced, every split non-empty when splits <= nkb)
+__device__ __forceinline__ void split_range(int s, int splits, int nkb, int& kb0, int& kb1) {
+    const int base = nkb / splits, rem = nkb % splits;
+    kb0 = s * base + (s < rem ? s : rem);
+    kb1 = kb0 + base + (s < rem ? 1 : 0);
+}
 
 template <int BN>
 struct GemmCfg {
@@ -167,7 +185,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     ptx::tc_fence_after();
     const uint32_t tmem_base = *tmem_base_slot;
 
-    const int num_tiles = p.num_m_blocks * p.num_n_blocks;
+    const int num_tiles = p.num_m_blocks * p.num_n_blocks * p.splits;  // work units: (tile, split)
     const int nkb = p.num_k_blocks;
 
     if (warp == 0) {
@@ -182,9 +200,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             uint32_t armed_phase = 0;           // parity of that load's phase, one bit per stage
             bool ok = true;
             for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
-                int mb, nb;
-                tile_coords(t, p.num_m_blocks, p.num_n_blocks, mb, nb);
-                for (int kb = 0; kb < nkb; ++kb) {
+                int mb, nb, kb0, kb1;
+                tile_coords(t / p.splits, p.num_m_blocks, p.num_n_blocks, mb, nb);
+                split_range(t % p.splits, p.splits, nkb, kb0, kb1);
+                for (int kb = kb0; kb < kb1; ++kb) {
                     if (!ptx::mbar_wait_bounded(&empty_bar[stage], phase ^ 1u, abort_flag)) { ok = false; break; }
                     ptx::mbar_arrive_expect_tx(&full_bar[stage], Cfg::STAGE_BYTES);
                     ptx::tma_load_2d(smem_a + stage * Cfg::A_BYTES, &tmap_a, &full_bar[stage], kb * BK, mb * BM);
@@ -231,7 +250,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                 if (!ptx::mbar_wait_bounded(&tmem_empty[acc], acc_phase ^ 1u, abort_flag)) { ok = false; break; }
                 ptx::tc_fence_after();
                 const uint32_t tmem_d = tmem_base + (uint32_t)(acc * BN);
-                for (int kb = 0; kb < nkb; ++kb) {
+                int kb0, kb1;
+                split_range(t % p.splits, p.splits, nkb, kb0, kb1);
+                for (int kb = kb0; kb < kb1; ++kb) {
                     if (!ptx::mbar_wait_bounded(&full_bar[stage], phase, abort_flag)) { ok = false; break; }
                     ptx::tc_fence_after();
                     const uint32_t a_addr = ptx::smem_u32(smem_a + stage * Cfg::A_BYTES);
@@ -243,7 +264,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                         // K-major: +32 bytes per 16-element K step; MN-major: +16 rows of 128 bytes
                         // (both in the descriptor's 16-byte address units)
                         const uint64_t db_k = db + (uint64_t)(B_MN ? k * 128 : k * 2);
-                        ptx::mma_f16_ss(tmem_d, da + (uint64_t)(k * 2), db_k, idesc, (kb | k) != 0 ? 1u : 0u);
+                        ptx::mma_f16_ss(tmem_d, da + (uint64_t)(k * 2), db_k, idesc, ((kb - kb0) | k) != 0 ? 1u : 0u);
                     }
                     ptx::tc_commit(&empty_bar[stage]);  // stage reusable once these MMAs have read it
                     if (++stage == STAGES) { stage = 0; phase ^= 1u; }
@@ -273,7 +294,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         const T* resid = reinterpret_cast<const T*>(p.residual);
         for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
             int mb, nb;
-            tile_coords(t, p.num_m_blocks, p.num_n_blocks, mb, nb);
+            tile_coords(t / p.splits, p.num_m_blocks, p.num_n_blocks, mb, nb);
             // warp-uniform result: the TMEM loads below are warp-collective
             if (!__all_sync(0xffffffffu, ptx::mbar_wait_bounded(&tmem_full[acc], acc_phase, abort_flag))) { ok = false; break; }
             ptx::tc_fence_after();
@@ -297,6 +318,22 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                     for (int i = 0; i < 32; ++i) v[i] = (v[i] / (1.0f + __expf(-v[i]))) * __uint_as_float(r[i]);
                 }
                 const bool full = (col0 + 32 <= p.N);
+                if (p.splits > 1) {
+                    // split-K: raw fp32 partial sums; bias / residual / activation happen in the reduce kernel
+                    if (row_ok) {
+                        float* prow = p.partial + ((int64_t)(t % p.splits) * p.M + row) * p.N + col0;
+                        if (full && (p.N & 3) == 0) {
+#pragma unroll
+                            for (int i = 0; i < 32; i += 4)
+                                *reinterpret_cast<float4*>(prow + i) = make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
+                        } else {
+#pragma unroll
+                            for (int i = 0; i < 32; ++i)
+                                if (col0 + i < p.N) prow[i] = v[i];
+                        }
+                    }
+                    continue;
+                }
                 if (bias != nullptr) {
                     if (full && p.bias_vec_ok) {
 #pragma unroll
@@ -360,6 +397,38 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     }
 }
 
+// Second pass of split-K: out = act(sum_s partial[s] + bias + residual), 4 columns per thread.
+template <typename T>
+__global__ void __launch_bounds__(256) splitk_reduce_kernel(const GemmParams p) {
+    const int64_t n4 = (p.N + 3) / 4;
+    const int64_t total = p.M * n4;
+    const int64_t idx = (int64_t)blockIdx.x * 256 + threadIdx.x;
+    if (idx >= total) return;
+    const int64_t row = idx / n4;
+    const int64_t col0 = (idx - row * n4) * 4;
+    const int ncol = (int)((p.N - col0) < 4 ? (p.N - col0) : 4);
+    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+    const bool vec = (ncol == 4) && ((p.N & 3) == 0);
+    for (int s = 0; s < p.splits; ++s) {  // fixed order: deterministic
+        const float* src = p.partial + ((int64_t)s * p.M + row) * p.N + col0;
+        if (vec) {
+            const float4 f = *reinterpret_cast<const float4*>(src);
+            acc[0] += f.x; acc[1] += f.y; acc[2] += f.z; acc[3] += f.w;
+        } else {
+            for (int i = 0; i < ncol; ++i) acc[i] += src[i];
+        }
+    }
+    const T* bias = reinterpret_cast<const T*>(p.bias);
+    const T* resid = reinterpret_cast<const T*>(p.residual);
+    T* out = reinterpret_cast<T*>(p.out);
+    for (int i = 0; i < ncol; ++i) {
+        float v = acc[i];
+        if (bias) v += Cvt<T>::to_f(bias[col0 + i]);
+        if (resid) v += Cvt<T>::to_f(resid[row * p.ldr + col0 + i]);
+        out[row * p.ldc + col0 + i] = Cvt<T>::from_f(apply_act(v, p.act));
+    }
+}
+
 template <typename T, int BN, bool SWIGLU, bool B_MN>
 int launch_gemm_tc(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tb2, const GemmParams& p,
                    cudaStream_t st) {
@@ -371,23 +440,71 @@ int launch_gemm_tc(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorM
         return fail(XG_ERR_LAUNCH, "xg_gemm_bias_act: cannot reserve %d bytes of shared memory: %s", Cfg::SMEM_BYTES,
                     cudaGetErrorString(e));
     }
-    const int tiles = p.num_m_blocks * p.num_n_blocks;
+    const int tiles = p.num_m_blocks * p.num_n_blocks * p.splits;
     const int grid = tiles < num_sms() ? tiles : num_sms();
     kern<<<grid, kGemmThreads, Cfg::SMEM_BYTES, st>>>(ta, tb, tb2, p);
-    return check_launch("xg_gemm_bias_act");
+    int rc = check_launch("xg_gemm_bias_act");
+    if (rc != XG_OK || p.splits <= 1) return rc;
+    const int64_t total = p.M * ((p.N + 3) / 4);
+    splitk_reduce_kernel<T><<<(unsigned)((total + 255) / 256), 256, 0, st>>>(p);
+    return check_launch("xg_gemm_bias_act (split-K reduce)");
 }
+
+}  // namespace
+
+// Tile width and split-K factor for an [M, N, K] problem given `ws_bytes` of fp32 scratch (0 = none).
+// Without scratch: the widest tile that still gives every SM work. With scratch and a small M (the
+// weight-streaming regime, where a CTA's traffic is dominated by re-reading A once per n-tile): keep the
+// widest tile and split K so that (tiles x splits) fills the SMs in whole waves.
+GemmPlan plan_gemm(int64_t M, int64_t N, int64_t K, int64_t ws_bytes, int sms) {
+    GemmPlan pl;
+    const int64_t mblk = (M + BM - 1) / BM;
+    pl.bn = 256;
+    if (mblk * ((N + 255) / 256) < sms) pl.bn = 128;
+    if (pl.bn == 128 && mblk * ((N + 127) / 128) < sms) pl.bn = 64;
+    pl.splits = 1;
+    const int64_t nkb = (K + BK - 1) / BK;
+    if (ws_bytes <= 0 || M > 512 || nkb < 8) return pl;
+    // Small M is the weight-streaming regime: what a CTA costs is the bytes it pulls through its SM
+    // ((128 + bn) rows of 128 bytes per k-block), so compare plans by bytes per SM, reduce pass included.
+    const int64_t tiles256 = mblk * ((N + 255) / 256);
+    const int64_t tiles_bn = mblk * ((N + pl.bn - 1) / pl.bn);
+    const double base_cost = (double)((tiles_bn + sms - 1) / sms) * (BM + pl.bn) * 128.0 * (double)nkb;
+    double best = base_cost * 0.85;  // split only for a clear win
+    for (int s = 2; s <= 16 && s * 4 <= nkb; ++s) {
+        if ((int64_t)s * M * N * 4 > ws_bytes) break;
+        const double waves = (double)((tiles256 * s + sms - 1) / sms);
+        const double gemm_bytes = waves * (BM + 256) * 128.0 * ((double)nkb / s);
+        const double reduce_bytes = (double)(s + 1) * (double)M * (double)N * 4.0 / sms;
+        if (gemm_bytes + reduce_bytes < best) {
+            best = gemm_bytes + reduce_bytes;
+            pl.bn = 256;
+            pl.splits = s;
+        }
+    }
+    return pl;
+}
+
+int64_t gemm_workspace_bytes(int64_t M, int64_t N, int64_t K) {
+    const GemmPlan pl = plan_gemm(M, N, K, (int64_t)1 << 40, num_sms());
+    return pl.splits > 1 ? (int64_t)pl.splits * M * N * 4 : 0;
+}
+
+namespace {
 
 template <typename T>
 int gemm_tc_dispatch(const void* A, const void* B, const void* bias, const void* residual, void* out, int64_t M,
                      int64_t N, int64_t K, int64_t lda, int64_t ldb, int64_t ldc, int64_t ldr, int trans_b, int act,
-                     cudaStream_t st) {
+                     void* workspace, int64_t ws_bytes, bool force_split, cudaStream_t st) {
     constexpr bool is_bf16 = std::is_same<T, __nv_bfloat16>::value;
-    // Tile width: the widest tile that still gives every SM work.
     const int64_t mblk = (M + BM - 1) / BM;
-    const int sms = num_sms();
-    int bn = 256;
-    if (mblk * ((N + 255) / 256) < sms) bn = 128;
-    if (bn == 128 && mblk * ((N + 127) / 128) < sms) bn = 64;
+    if (workspace == nullptr || (reinterpret_cast<uintptr_t>(workspace) & 15u) != 0) ws_bytes = 0;
+    GemmPlan pl = plan_gemm(M, N, K, ws_bytes, num_sms());
+    if (force_split && pl.splits == 1 && ws_bytes >= 2 * M * N * 4 && (K + BK - 1) / BK >= 2) {
+        pl.bn = 256;  // the caller asked for the split path: the smallest split that the scratch holds
+        pl.splits = 2;
+    }
+    const int bn = pl.bn;
 
     CUtensorMap ta, tb;
     const bool b_ok = trans_b ? make_tmap_2d_16bit(&tb, B, (uint64_t)N, (uint64_t)K, (uint64_t)ldb, (uint32_t)bn, BK, is_bf16)
@@ -406,6 +523,8 @@ int gemm_tc_dispatch(const void* A, const void* B, const void* bias, const void*
     p.num_m_blocks = (int)mblk;
     p.num_n_blocks = (int)((N + bn - 1) / bn);
     p.num_k_blocks = (int)((K + BK - 1) / BK);
+    p.splits = pl.splits;
+    p.partial = pl.splits > 1 ? reinterpret_cast<float*>(workspace) : nullptr;
     if (!trans_b) {
         switch (bn) {
             case 256: return launch_gemm_tc<T, 256, false, true>(ta, tb, tb, p, st);
@@ -440,6 +559,8 @@ int gemm_swiglu_dispatch(const void* A, const void* Wg, const void* Wu, void* ou
     p.num_m_blocks = (int)((M + BM - 1) / BM);
     p.num_n_blocks = (int)((N + 127) / 128);
     p.num_k_blocks = (int)((K + BK - 1) / BK);
+    p.splits = 1;
+    p.partial = nullptr;
     return launch_gemm_tc<T, 256, true, false>(ta, tg, tu, p, st);
 }
 
@@ -448,15 +569,15 @@ int gemm_swiglu_dispatch(const void* A, const void* Wg, const void* Wu, void* ou
 // Entry used by xg_gemm_bias_act for 16-bit dtypes; W is [N, K] (trans_b = 1) or [K, N] (trans_b = 0).
 int gemm_tc_entry(const void* A, const void* B, const void* bias, const void* residual, void* out, int64_t M, int64_t N,
                   int64_t K, int64_t lda, int64_t ldb, int64_t ldc, int64_t ldr, int trans_b, int act, int dtype,
-                  cudaStream_t st) {
+                  void* workspace, int64_t ws_bytes, cudaStream_t st, bool force_split) {
     if (!aligned16(A) || !aligned16(B) || lda % 8 != 0 || ldb % 8 != 0)
         return fail(XG_ERR_UNSUPPORTED, "xg_gemm_bias_act: A/W must be 16-byte aligned with row strides multiple of 8 elements");
     if (M * N == 0) return XG_OK;
     if (M > (int64_t)BM * 0x7fffff || N > (int64_t)64 * 0x7fffff || K > 0x7fffffff)
         return fail(XG_ERR_TOO_LARGE, "xg_gemm_bias_act: extent too large");
     if (dtype == XG_BF16)
-        return gemm_tc_dispatch<__nv_bfloat16>(A, B, bias, residual, out, M, N, K, lda, ldb, ldc, ldr, trans_b, act, st);
-    return gemm_tc_dispatch<__half>(A, B, bias, residual, out, M, N, K, lda, ldb, ldc, ldr, trans_b, act, st);
+        return gemm_tc_dispatch<__nv_bfloat16>(A, B, bias, residual, out, M, N, K, lda, ldb, ldc, ldr, trans_b, act, workspace, ws_bytes, force_split, st);
+    return gemm_tc_dispatch<__half>(A, B, bias, residual, out, M, N, K, lda, ldb, ldc, ldr, trans_b, act, workspace, ws_bytes, force_split, st);
 }
 
 int gemm_swiglu_entry(const void* A, const void* Wg, const void* Wu, void* out, int64_t M, int64_t N, int64_t K,

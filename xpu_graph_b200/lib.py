@@ -42,6 +42,9 @@ SIGNATURES = {
     "xg_swiglu": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64, c_int64, c_int, c_void_p]),
     "xg_gemm_bias_act": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64,
                                  c_int64, c_int64, c_int64, c_int, c_int, c_int, c_void_p]),
+    "xg_gemm_bias_act_ws": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64,
+                                    c_int64, c_int64, c_int64, c_int, c_int, c_int, c_void_p, c_int64, c_void_p]),
+    "xg_gemm_workspace_bytes": (c_int64, [c_int64, c_int64, c_int64, c_int]),
     "xg_bgemm_bias_act": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64,
                                   c_int64, c_int64, c_int64, c_int64, c_int64, c_int64, c_int64, c_int64, c_int64,
                                   c_int, c_int, c_int, c_void_p]),
@@ -50,6 +53,7 @@ SIGNATURES = {
     "xg_sdpa_fwd": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64,
                             c_int64, _I64P, _I64P, _I64P, _I64P, _I64P, c_float, c_int, c_int, c_void_p]),
     "xg_seg_copy": (c_int, [_VPP, _VPP, _I64P, _I64P, _I64P, c_int64, c_int64, c_void_p, c_int, c_void_p]),
+    "xg_sum3d": (c_int, [_VPP, _VPP, _I64P, c_int64, c_int, c_int, c_void_p]),
     "xg_gather_rows": (c_int, [_VPP, _I64P, c_int64, c_void_p, c_int64, c_int64, c_void_p, c_int, c_void_p, c_int64,
                                c_int64, c_int64, c_int, c_void_p]),
 }

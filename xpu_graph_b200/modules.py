@@ -250,6 +250,18 @@ class GatherStackModule(torch.nn.Module):
         return _X.gather_stack(list(tables), idx, row_mask, bool(zero_when))
 
 
+class ComboSumModule(torch.nn.Module):
+    """ComboSum3dInp target (structure/fuse_combosum.py:82-98): forward(input_list, dim) -> list of
+    sum(x, dim[0]); one launch for the whole list (the MLU module splits by size,
+    targets/mlu/structure_replacements/__init__.py:147-165)."""
+
+    def forward(self, input_list, dim):
+        d = dim[0] if isinstance(dim, (list, tuple)) else dim
+        if d < 0:
+            d += 3
+        return _X.sum3d(list(input_list), int(d))
+
+
 def get_structure_replacements(config=None) -> dict:
     """Structure-pattern name -> module (or (module, constraint_fn)), the dict that
     passes/patterns/targets/__init__.py:13-27 normalises."""
@@ -260,6 +272,7 @@ def get_structure_replacements(config=None) -> dict:
         "FusedCatSlice": FuseSliceCatSameInputModule,
         "FusedSliceStackSum": FuseSliceCatSameInputModule,
         "FusedMultipleSliceCat": FuseSliceCatSameInputModule_v2,
+        "ComboSum3dInp": ComboSumModule,
         "CustomDenseLayer": (DenseLayerModule, can_fuse_custom_denselayer),
         "CustomBatchDenseLayer": (BatchDenseLayerModule, can_fuse_custom_batch_denselayer),
     }

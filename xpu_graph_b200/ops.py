@@ -278,12 +278,18 @@ def dense(x: torch.Tensor, weight: torch.Tensor, weight_trans: bool, bias: Optio
         residual = _mat(residual.to(x.dtype))
         ldr = _row_stride(residual)
     out = torch.empty((M, N), dtype=x.dtype, device=x.device)
+    L = _lib.load()
+    ws, ws_bytes = None, 0
+    if x.dtype != torch.float32 and M <= 512:
+        ws_bytes = int(L.xg_gemm_workspace_bytes(M, N, K, _code(x.dtype)))
+        if ws_bytes > 0:  # split-K scratch for weight-streaming shapes (small M)
+            ws = torch.empty(ws_bytes, dtype=torch.uint8, device=x.device)
     with _GemmTimer(x, 2 * M * N * K):
-        rc = _lib.load().xg_gemm_bias_act(_ptr(x), _ptr(weight), _ptr(bias), _ptr(residual), _ptr(out), M, N, K,
-                                          _row_stride(x), _row_stride(weight), N, ldr, 1 if weight_trans else 0,
-                                          _lib.ACT_CODES[act], _code(x.dtype), _stream(x))
+        rc = L.xg_gemm_bias_act_ws(_ptr(x), _ptr(weight), _ptr(bias), _ptr(residual), _ptr(out), M, N, K,
+                                   _row_stride(x), _row_stride(weight), N, ldr, 1 if weight_trans else 0,
+                                   _lib.ACT_CODES[act], _code(x.dtype), _ptr(ws), ws_bytes, _stream(x))
     _lib.check(rc, "xg_gemm_bias_act")
-    _bump()
+    _bump(2 if ws is not None else 1)
     return out
 
 
@@ -568,3 +574,36 @@ def gather_stack(tables: List[torch.Tensor], idx: torch.Tensor, row_mask: Option
 @gather_stack.register_fake
 def _(tables, idx, row_mask, zero_when):
     return torch.empty((idx.shape[0], len(tables) * tables[0].shape[1]), dtype=tables[0].dtype, device=idx.device)
+
+
+@torch.library.custom_op(f"{NS}::sum3d", mutates_args=(), device_types="cuda")
+def sum3d(inputs: List[torch.Tensor], dim: int) -> List[torch.Tensor]:
+    """[sum(x, dim) for x in inputs] for 3-D tensors, one launch for the whole list."""
+    xs, outs, shapes = [], [], []
+    for x in inputs:
+        if x.dim() != 3:
+            raise ValueError("xg_sm100::sum3d expects 3-D tensors")
+        if x.dtype != inputs[0].dtype:
+            raise ValueError("xg_sm100::sum3d: inputs must share a dtype")
+        x = x.contiguous()
+        xs.append(x)
+        s0, s1, s2 = x.shape
+        shapes += [s0, s1, s2]
+        oshape = (s1, s2) if dim == 0 else ((s0, s2) if dim == 1 else (s0, s1))
+        outs.append(torch.empty(oshape, dtype=x.dtype, device=x.device))
+    if xs:
+        rc = _lib.load().xg_sum3d(_lib.ptr_array([x.data_ptr() for x in xs]), _lib.ptr_array([o.data_ptr() for o in outs]),
+                                  _lib.i64_array(shapes), len(xs), int(dim), _code(xs[0].dtype), _stream(xs[0]))
+        _lib.check(rc, "xg_sum3d")
+        _bump()
+    return outs
+
+
+@sum3d.register_fake
+def _(inputs, dim):
+    outs = []
+    for x in inputs:
+        s0, s1, s2 = x.shape
+        oshape = (s1, s2) if dim == 0 else ((s0, s2) if dim == 1 else (s0, s1))
+        outs.append(torch.empty(oshape, dtype=x.dtype, device=x.device))
+    return outs
