@@ -70,9 +70,9 @@ def test_dense_bf16_kn_weights(cuda_device, M, K, N, act):
     assert_parity(got, ref_ops.dense(x, w, False, b, act), f"dense bf16 [K,N] {M}x{K}x{N} {act}")
 
 
-@pytest.mark.parametrize("M,K,N,act,with_res", [(256, 4096, 4096, "gelu", False), (256, 4096, 11008, "silu", False),
-                                                (130, 1024, 1000, "none", True), (100, 2048, 1002, "relu", True),
-                                                (512, 1024, 512, "gelu", True), (1, 4096, 4096, "none", False)])
+@pytest.mark.parametrize("M,K,N,act,with_res", [(64, 4096, 4096, "gelu", False), (32, 4096, 11008, "silu", False),
+                                                (128, 4096, 1000, "none", True), (100, 2048, 1002, "relu", True),
+                                                (16, 1024, 512, "gelu", True), (1, 4096, 4096, "none", False)])
 def test_dense_split_k(cuda_device, M, K, N, act, with_res):
     """Small-M shapes: the kernel splits K across CTAs and reduces fp32 partial sums from scratch memory
     (allocated by the op). Checked against the oracle and for run-to-run bit equality."""

@@ -7,6 +7,8 @@ int gemm_tc_entry(const void* A, const void* B, const void* bias, const void* re
                   int64_t K, int64_t lda, int64_t ldb, int64_t ldc, int64_t ldr, int trans_b, int act, int dtype,
                   void* workspace, int64_t ws_bytes, cudaStream_t st, bool force_split = false);
 int64_t gemm_workspace_bytes(int64_t M, int64_t N, int64_t K);
+int gemm_f32_entry(const void* A, const void* B, const void* bias, const void* residual, void* out, int64_t M, int64_t N,
+                   int64_t K, int64_t lda, int64_t ldb, int64_t ldc, int64_t ldr, int trans_b, int act, cudaStream_t st);
 int gemm_swiglu_entry(const void* A, const void* Wg, const void* Wu, void* out, int64_t M, int64_t N, int64_t K,
                       int64_t lda, int64_t ldw, int64_t ldc, int dtype, cudaStream_t st);
 int read_tc_status(unsigned int* host_out, int reset);

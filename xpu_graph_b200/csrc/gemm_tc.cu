@@ -464,20 +464,29 @@ GemmPlan plan_gemm(int64_t M, int64_t N, int64_t K, int64_t ws_bytes, int sms) {
     if (pl.bn == 128 && mblk * ((N + 127) / 128) < sms) pl.bn = 64;
     pl.splits = 1;
     const int64_t nkb = (K + BK - 1) / BK;
-    if (ws_bytes <= 0 || M > 512 || nkb < 8) return pl;
-    // Small M is the weight-streaming regime: what a CTA costs is the bytes it pulls through its SM
-    // ((128 + bn) rows of 128 bytes per k-block), so compare plans by bytes per SM, reduce pass included.
+    if (ws_bytes <= 0 || M > 128 || nkb < 8) return pl;  // measured: at M = 256 a split loses (see below)
+    // Small M is the weight-streaming regime. Two limits, both expressed in bytes one SM handles:
+    //   pull : what a CTA drags through its SM, (128 + bn) rows of 128 bytes per k-block, times the waves;
+    //   hbm  : the problem's DRAM traffic (weights + activations + the fp32 partial sums written and read
+    //          back by a split) divided over the SMs at the measured ratio of HBM to per-SM L2 bandwidth (~45x).
+    // A split also pays a second launch. Measured on B200: at M = 256 the partial sums cost more than the
+    // split saves (16 us unsplit vs 21 us 4-way at N = K = 4096), so only smaller M ends up split.
     const int64_t tiles256 = mblk * ((N + 255) / 256);
     const int64_t tiles_bn = mblk * ((N + pl.bn - 1) / pl.bn);
-    const double base_cost = (double)((tiles_bn + sms - 1) / sms) * (BM + pl.bn) * 128.0 * (double)nkb;
-    double best = base_cost * 0.85;  // split only for a clear win
+    const double io_bytes = 2.0 * ((double)N * K + (double)M * K + (double)M * N);
+    const double ratio = 45.0, launch_cost = 0.4e6;
+    auto cost_of = [&](double pull, double partial_bytes, bool split) {
+        const double hbm = (io_bytes + partial_bytes) / ratio;
+        return (pull > hbm ? pull : hbm) + (split ? launch_cost : 0.0);
+    };
+    double best = cost_of((double)((tiles_bn + sms - 1) / sms) * (BM + pl.bn) * 128.0 * (double)nkb, 0.0, false) * 0.9;
     for (int s = 2; s <= 16 && s * 4 <= nkb; ++s) {
         if ((int64_t)s * M * N * 4 > ws_bytes) break;
         const double waves = (double)((tiles256 * s + sms - 1) / sms);
-        const double gemm_bytes = waves * (BM + 256) * 128.0 * ((double)nkb / s);
-        const double reduce_bytes = (double)(s + 1) * (double)M * (double)N * 4.0 / sms;
-        if (gemm_bytes + reduce_bytes < best) {
-            best = gemm_bytes + reduce_bytes;
+        const double pull = waves * (BM + 256) * 128.0 * ((double)nkb / s);
+        const double c = cost_of(pull, 2.0 * s * (double)M * N * 4.0, true);
+        if (c < best) {
+            best = c;
             pl.bn = 256;
             pl.splits = s;
         }

@@ -101,7 +101,7 @@ def main(argv=None):
 
     X = torch.ops.xg_sm100
     ap = argparse.ArgumentParser()
-    ap.add_argument("case", choices=["sweep", "gemm", "gemm_swiglu", "gemm_small_m", "add_rms_norm", "layer_norm", "sdpa", "rope", "swiglu",
+    ap.add_argument("case", choices=["sweep", "gemm_splitk", "gemm", "gemm_swiglu", "gemm_small_m", "add_rms_norm", "layer_norm", "sdpa", "rope", "swiglu",
                                      "gather", "slice_cat", "gemm_f32"])
     ap.add_argument("--iters", type=int, default=3)
     args = ap.parse_args(argv)
@@ -124,6 +124,27 @@ def main(argv=None):
         a, w, b = rn(M, K), rn(N, K, std=0.02), rn(N, std=0.02)
         ms = _time(lambda: X.dense(a, w, True, b, None, "silu"), args.iters)
         print(f"gemm {M}x{K}x{N} silu: {ms:.4f} ms, {2 * M * N * K / ms / 1e9:.1f} TFLOP/s")
+    elif args.case == "gemm_splitk":
+        # small-M dense layers: split-K with scratch (what the op does) against the same kernel without scratch
+        import ctypes
+
+        L = lib.load()
+        K, N = 4096, 11008
+        w, b = rn(N, K, std=0.02), rn(N, std=0.02)
+        for M in (16, 64, 128, 256):
+            a = rn(M, K)
+            out = torch.empty(M, N, device=dev, dtype=bf)
+            st = torch.cuda.current_stream().cuda_stream
+
+            def plain():
+                L.xg_gemm_bias_act(a.data_ptr(), w.data_ptr(), b.data_ptr(), None, out.data_ptr(), M, N, K, K, K, N, 0, 1, 1, 1,
+                                   torch.cuda.current_stream().cuda_stream)
+
+            ms0 = _time_graphed(plain)
+            ms1 = _time_graphed(lambda: X.dense(a, w, True, b, None, "gelu"))
+            ws = L.xg_gemm_workspace_bytes(M, N, K, 1)
+            print(f"M={M}: no scratch {ms0 * 1e3:.1f} us, op (scratch {ws / 1e6:.1f} MB) {ms1 * 1e3:.1f} us, "
+                  f"weights at {2 * N * K / min(ms0, ms1) / 1e6:.0f} GB/s")
     elif args.case == "gemm_swiglu":
         M, K, N = 8192, 4096, 11008
         a, wg, wu = rn(M, K), rn(N, K, std=0.02), rn(N, K, std=0.02)

@@ -280,7 +280,7 @@ def dense(x: torch.Tensor, weight: torch.Tensor, weight_trans: bool, bias: Optio
     out = torch.empty((M, N), dtype=x.dtype, device=x.device)
     L = _lib.load()
     ws, ws_bytes = None, 0
-    if x.dtype != torch.float32 and M <= 512:
+    if x.dtype != torch.float32 and M <= 128:
         ws_bytes = int(L.xg_gemm_workspace_bytes(M, N, K, _code(x.dtype)))
         if ws_bytes > 0:  # split-K scratch for weight-streaming shapes (small M)
             ws = torch.empty(ws_bytes, dtype=torch.uint8, device=x.device)
