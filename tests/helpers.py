@@ -15,7 +15,10 @@ def error_stats(actual: torch.Tensor, expected: torch.Tensor):
     return max_abs, mean_rel
 
 
-def assert_parity(actual: torch.Tensor, expected: torch.Tensor, what: str = ""):
+def assert_parity(actual: torch.Tensor, expected: torch.Tensor, what: str = "", magnitude: torch.Tensor = None):
+    """`magnitude`: optional tensor of operand magnitudes for sums that can cancel (a residual add): the
+    relative tolerance then applies to max(|expected|, |magnitude|), because eager rounds the addends to the
+    tensor dtype before adding and that rounding error does not shrink with the sum."""
     assert actual.shape == expected.shape, f"{what}: shape {tuple(actual.shape)} vs {tuple(expected.shape)}"
     assert actual.dtype == expected.dtype, f"{what}: dtype {actual.dtype} vs {expected.dtype}"
     a, e = actual.detach().float().cpu(), expected.detach().float().cpu()
@@ -25,7 +28,8 @@ def assert_parity(actual: torch.Tensor, expected: torch.Tensor, what: str = ""):
         rtol, atol = F32_RTOL, F32_RTOL * max(scale, 1e-30)
     else:
         rtol, atol = BF16_RTOL, BF16_ATOL
-    bad = (a - e).abs() > (atol + rtol * e.abs())
+    ref_mag = e.abs() if magnitude is None else torch.maximum(e.abs(), magnitude.detach().float().cpu().abs())
+    bad = (a - e).abs() > (atol + rtol * ref_mag)
     if bad.any():
         max_abs, mean_rel = error_stats(actual, expected)
         idx = bad.nonzero()[0].tolist()
