@@ -139,6 +139,30 @@ int xg_gemm_bias_act_ws(const void* A, const void* B, const void* bias, const vo
 int64_t xg_gemm_workspace_bytes(int64_t M, int64_t N, int64_t K, int dtype);
 
 /*
+ * Split-K dense layer for hosts that cannot allocate device memory. Some embedders of this library own
+ * no allocator they may call at this point: a plugin running inside another framework's stream-ordered
+ * memory pool, a runtime whose memory budget was fixed at start-up, or a real-time serving loop in which a
+ * cudaMalloc (an implicit device synchronisation) is not acceptable. For them the fp32 partial sums go to a
+ * 32 MiB array that is part of the library image (xg_gemm_static_scratch_bytes() returns the size; every GPU
+ * that loads the library holds it until the process exits) instead of a caller workspace. Inputs and outputs
+ * are still the caller's. Same arithmetic as xg_gemm_bias_act_ws with a 2-way or wider split.
+ *   - 16-bit dtypes only; XG_ERR_TOO_LARGE when 2*M*N*4 bytes exceed the array (M*N > 4 Mi elements),
+ *     XG_ERR_UNSUPPORTED when K fits a single 64-wide k-block.
+ *   - The first call on each device resolves the array's device address (cudaGetSymbolAddress, a short
+ *     host-side set-up step); make that first call before starting any stream capture.
+ *   - No cudaMalloc / cudaFree / allocating library call is made, on the first call or later.
+ *   - All calls share the one array and it keeps whatever the previous call left there; every partial
+ *     sum that is read has been written earlier in the same call, so nothing needs clearing. Two calls
+ *     whose kernels overlap on the GPU (different streams, or several host threads) race on the array:
+ *     serialise them.
+ * This entry point has no counterpart in the reference.
+ */
+int xg_gemm_bias_act_static(const void* A, const void* B, const void* bias, const void* residual, void* out,
+                            int64_t M, int64_t N, int64_t K, int64_t lda, int64_t ldb, int64_t ldc,
+                            int64_t ldr, int trans_b, int act, int dtype, void* stream);
+int64_t xg_gemm_static_scratch_bytes(void);
+
+/*
  * Batched form: out[b] = act( A[b] @ W[b] + bias[b] + residual[b] ), batch strides in elements
  * (0 broadcasts). Replaces: dense_layer_modules.py:71-120 (BatchDenseLayerModule) as called by
  * passes/patterns/structure/custom_denselayer.py:111-117.

@@ -7,6 +7,10 @@ int gemm_tc_entry(const void* A, const void* B, const void* bias, const void* re
                   int64_t K, int64_t lda, int64_t ldb, int64_t ldc, int64_t ldr, int trans_b, int act, int dtype,
                   void* workspace, int64_t ws_bytes, cudaStream_t st, bool force_split = false);
 int64_t gemm_workspace_bytes(int64_t M, int64_t N, int64_t K);
+int gemm_tc_static_entry(const void* A, const void* B, const void* bias, const void* residual, void* out, int64_t M,
+                         int64_t N, int64_t K, int64_t lda, int64_t ldb, int64_t ldc, int64_t ldr, int trans_b, int act,
+                         int dtype, cudaStream_t st);
+int64_t static_scratch_capacity();
 int gemm_f32_entry(const void* A, const void* B, const void* bias, const void* residual, void* out, int64_t M, int64_t N,
                    int64_t K, int64_t lda, int64_t ldb, int64_t ldc, int64_t ldr, int trans_b, int act, cudaStream_t st);
 int gemm_swiglu_entry(const void* A, const void* Wg, const void* Wu, void* out, int64_t M, int64_t N, int64_t K,
@@ -48,6 +52,20 @@ extern "C" int xg_gemm_bias_act(const void* A, const void* B, const void* bias, 
     return xg_gemm_bias_act_ws(A, B, bias, residual, out, M, N, K, lda, ldb, ldc, ldr, trans_b, act, dtype, nullptr, 0,
                                stream);
 }
+
+extern "C" int xg_gemm_bias_act_static(const void* A, const void* B, const void* bias, const void* residual, void* out,
+                                       int64_t M, int64_t N, int64_t K, int64_t lda, int64_t ldb, int64_t ldc,
+                                       int64_t ldr, int trans_b, int act, int dtype, void* stream) {
+    using namespace xg;
+    int rc = validate_gemm("xg_gemm_bias_act_static", A, B, residual, out, M, N, K, lda, ldb, ldc, ldr, trans_b, act, dtype);
+    if (rc != XG_OK) return rc;
+    if (dtype != XG_BF16 && dtype != XG_F16)
+        return fail(XG_ERR_UNSUPPORTED, "xg_gemm_bias_act_static: 16-bit dtypes only (the fp32 kernel uses no scratch)");
+    return gemm_tc_static_entry(A, B, bias, residual, out, M, N, K, lda, ldb, ldc, ldr, trans_b, act, dtype,
+                                reinterpret_cast<cudaStream_t>(stream));
+}
+
+extern "C" int64_t xg_gemm_static_scratch_bytes(void) { return xg::static_scratch_capacity(); }
 
 extern "C" int64_t xg_gemm_workspace_bytes(int64_t M, int64_t N, int64_t K, int dtype) {
     if (M <= 0 || N <= 0 || K <= 0 || (dtype != XG_BF16 && dtype != XG_F16)) return 0;

@@ -589,6 +589,57 @@ int gemm_tc_entry(const void* A, const void* B, const void* bias, const void* re
     return gemm_tc_dispatch<__half>(A, B, bias, residual, out, M, N, K, lda, ldb, ldc, ldr, trans_b, act, workspace, ws_bytes, force_split, st);
 }
 
+// ---- split-K on a fixed, library-owned scratch array (nothing is allocated by anyone) ------------------
+constexpr int64_t kStaticScratchBytes = 32ll << 20;  // 32 MiB, held by every GPU that loads the library
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+
+int64_t static_scratch_capacity() { return kStaticScratchBytes; }
+
+// Device address of the scratch array on the current device. In host code the array's name is only a
+// handle for the runtime, not a pointer a kernel could use, so the address is resolved with
+// cudaGetSymbolAddress - once per device, with that device current - and cached.
+static int static_scratch_address(void** out) {
+    constexpr int kMaxDevices = 64;
+    static std::mutex mu;
+    static void* cached[kMaxDevices] = {nullptr};
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) {
+        cudaGetLastError();
+        return fail(XG_ERR_DEVICE, "xg_gemm_bias_act_static: no usable current device");
+    }
+    std::lock_guard<std::mutex> lock(mu);
+    if (cached[dev] == nullptr) {
+        void* ptr = nullptr;
+        cudaError_t e = cudaGetSymbolAddress(&ptr, g_static_scratch);
+        if (e != cudaSuccess || ptr == nullptr) {
+            cudaGetLastError();
+            return fail(XG_ERR_DEVICE, "xg_gemm_bias_act_static: cudaGetSymbolAddress failed: %s", cudaGetErrorString(e));
+        }
+        cached[dev] = ptr;
+    }
+    *out = cached[dev];
+    return XG_OK;
+}
+
+int gemm_tc_static_entry(const void* A, const void* B, const void* bias, const void* residual, void* out, int64_t M,
+                         int64_t N, int64_t K, int64_t lda, int64_t ldb, int64_t ldc, int64_t ldr, int trans_b, int act,
+                         int dtype, cudaStream_t st) {
+    if (M * N == 0) return XG_OK;
+    const int64_t need = 2 * M * N * 4;  // two fp32 partial-sum planes is the least a split needs
+    if (need > kStaticScratchBytes)
+        return fail(XG_ERR_TOO_LARGE,
+                    "xg_gemm_bias_act_static: M*N = %lld needs %lld bytes of scratch for a 2-way split, the built-in array "
+                    "holds %lld; use xg_gemm_bias_act_ws with your own workspace",
+                    (long long)(M * N), (long long)need, (long long)kStaticScratchBytes);
+    if ((K + BK - 1) / BK < 2)
+        return fail(XG_ERR_UNSUPPORTED, "xg_gemm_bias_act_static: K = %lld is a single k-block, nothing to split", (long long)K);
+    void* scratch = nullptr;
+    int rc = static_scratch_address(&scratch);
+    if (rc != XG_OK) return rc;
+    return gemm_tc_entry(A, B, bias, residual, out, M, N, K, lda, ldb, ldc, ldr, trans_b, act, dtype, scratch,
+                         kStaticScratchBytes, st, /*force_split=*/true);
+}
+
 int gemm_swiglu_entry(const void* A, const void* Wg, const void* Wu, void* out, int64_t M, int64_t N, int64_t K,
                       int64_t lda, int64_t ldw, int64_t ldc, int dtype, cudaStream_t st) {
     if (!aligned16(A) || !aligned16(Wg) || !aligned16(Wu) || lda % 8 != 0 || ldw % 8 != 0)

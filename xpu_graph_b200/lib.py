@@ -45,6 +45,9 @@ SIGNATURES = {
     "xg_gemm_bias_act_ws": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64,
                                     c_int64, c_int64, c_int64, c_int, c_int, c_int, c_void_p, c_int64, c_void_p]),
     "xg_gemm_workspace_bytes": (c_int64, [c_int64, c_int64, c_int64, c_int]),
+    "xg_gemm_bias_act_static": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64,
+                                        c_int64, c_int64, c_int64, c_int, c_int, c_int, c_void_p]),
+    "xg_gemm_static_scratch_bytes": (c_int64, []),
     "xg_bgemm_bias_act": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64,
                                   c_int64, c_int64, c_int64, c_int64, c_int64, c_int64, c_int64, c_int64, c_int64,
                                   c_int, c_int, c_int, c_void_p]),
