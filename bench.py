@@ -119,6 +119,16 @@ def _cpu_layer_and_inputs(seq: int):
     return make_llama_layer(seed=3, batch=1, seq=seq, hidden=HIDDEN, heads=HEADS, ffn=FFN, dtype=torch.bfloat16)
 
 
+def _use_all_host_threads() -> int:
+    """torch.distributed.run exports OMP_NUM_THREADS=1; the CPU arms are meant to use every core this process may run on."""
+    try:
+        n = len(os.sched_getaffinity(0))
+    except AttributeError:
+        n = os.cpu_count() or 1
+    torch.set_num_threads(max(n, 1))
+    return torch.get_num_threads()
+
+
 def _time_cpu(layer, inputs, steps: int, warmup: int) -> float:
     with torch.no_grad():
         for _ in range(warmup):
@@ -143,6 +153,7 @@ def run_reference(args) -> dict:
     from oracle import ref_ops  # noqa: F401  (the oracle package is the reference path's restatement)
 
     steps, warmup = args.steps, max(args.warmup, 1)
+    _use_all_host_threads()
     seq = _pick_cpu_seq(150.0, steps + warmup)
     layer, inp = _cpu_layer_and_inputs(seq)
     sec = _time_cpu(layer, inp, steps, warmup)
@@ -247,7 +258,7 @@ def run_ours(args) -> dict | None:
         with open(tpath) as f:
             traffic = json.load(f).get("dram_bytes_per_launch_mean")
     roofline = {"bound": "tensor", "achieved": achieved, "peak": peaks["tflops"], "unit": "TFLOP/s",
-                "frac": achieved / peaks["tflops"], "traffic": traffic, "kernel": "gemm_tc_kernel",
+                "frac": achieved / peaks["tflops"], "traffic": traffic, "kernel": "gemm_tc_pair_kernel (tcgen05 cta_group::2 dense layers)",
                 "launches_timed": len(gemm_events), "peak_source": peaks["source"],
                 "gemm_share_of_step": gemm_ms / ms_total if ms_total > 0 else None}
 
@@ -280,6 +291,7 @@ def run_ours(args) -> dict | None:
     # ---- CPU baseline (rank 0, N = 1 only): the oracle's eager layer on a bounded sample --------
     cpu_baseline = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        _use_all_host_threads()
         seq = _pick_cpu_seq(25.0, 2)
         cl, ci = _cpu_layer_and_inputs(seq)
         sec = _time_cpu(cl, ci, 1, 1)

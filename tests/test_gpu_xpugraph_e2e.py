@@ -1,0 +1,113 @@
+"""The real thing on the GPU: eager models compiled by torch.compile through the xpu_graph pass pipeline with
+the cuda_sm100 target, executed on sm_100a kernels, compared with the eager (pattern-disabled) models on CPU.
+
+Needs the xpu_graph package importable on the GPU box (an offline install under baseline/_ref, or XPU_GRAPH_SRC);
+skipped otherwise. The graph rewrites themselves are covered without a GPU in tests/test_target_patterns.py.
+"""
+import logging
+import time
+
+import pytest
+import torch
+
+from tests.helpers import assert_parity
+from xpu_graph_b200.target.compat import reference_available
+
+pytestmark = [pytest.mark.gpu, pytest.mark.skipif(not reference_available(), reason="xpu_graph package not importable")]
+
+
+@pytest.fixture(autouse=True)
+def _reset_dynamo():
+    torch._dynamo.reset()
+    yield
+    torch._dynamo.reset()
+
+
+def _compile_run(model, inputs, **cfg):
+    from xpu_graph_b200 import target
+
+    cap = {}
+    be = target.backend(target.make_config(**cfg), capture=cap)
+    compiled = torch.compile(model, backend=be, dynamic=False)
+    with torch.no_grad():
+        out = compiled(*inputs)
+    torch.cuda.synchronize()
+    gm = cap["gm"]
+    graph = getattr(gm, "gm", gm).graph if not hasattr(gm, "graph") else gm.graph
+    mods = [n.target for n in graph.nodes if n.op == "call_module"]
+    atens = [str(n.target) for n in graph.nodes if n.op == "call_function"]
+    return compiled, out, mods, atens
+
+
+def test_llama_layer_compiled_on_gpu(cuda_device):
+    from xpu_graph_b200 import lib
+    from xpu_graph_b200.workloads import make_llama_layer
+
+    model, (x, cos, sin) = make_llama_layer(seed=3, batch=2, seq=320, hidden=512, heads=4, ffn=1376)
+    with torch.no_grad():
+        want = model(x, cos, sin)
+    model = model.to(cuda_device)
+    inputs = (x.to(cuda_device), cos.to(cuda_device), sin.to(cuda_device))
+    compiled, got, mods, atens = _compile_run(model, inputs)
+    assert lib.tc_status() == 0
+    assert_parity(got, want, "compiled llama layer")
+    assert mods == ["custom_rms_norm", "custom_dense_layer_replacement", "custom_dense_layer_replacement",
+                    "custom_dense_layer_replacement", "xg_rope", "xg_rope", "xg_sdpa", "xg_dense_residual",
+                    "custom_rms_norm", "xg_dense_swiglu", "xg_dense_residual"], mods
+    assert all(("reshape" in a or "transpose" in a or "view" in a) for a in atens), atens
+
+
+def test_encoder_block_compiled_on_gpu(cuda_device):
+    from xpu_graph_b200.workloads import make_encoder
+
+    model, x = make_encoder(seed=0)
+    with torch.no_grad():
+        want = model(x)
+    compiled, got, mods, atens = _compile_run(model.to(cuda_device), (x.to(cuda_device),))
+    assert_parity(got, want, "compiled encoder block")
+    assert mods.count("xg_layer_norm") == 2 and "xg_sdpa" in mods and mods.count("xg_dense_residual") == 2, mods
+
+
+def test_recsys_graph_compiled_on_gpu(cuda_device):
+    from xpu_graph_b200.workloads import make_recsys
+
+    model, (dense, idx, mask) = make_recsys(seed=4, batch=2048, table_rows=5000)
+    with torch.no_grad():
+        want = model(dense, idx, mask)
+    compiled, got, mods, atens = _compile_run(model.to(cuda_device), (dense.to(cuda_device), idx.to(cuda_device), mask.to(cuda_device)))
+    assert_parity(got, want, "compiled recsys graph")
+    assert mods == ["xg_gather_stack", "fuse_slice_cat", "xg_cat_lastdim", "custom_dense_layer_replacement",
+                    "custom_dense_layer_replacement", "custom_dense_layer_replacement"], mods
+
+
+def test_device_graph_vendor_compiler(cuda_device):
+    """vendor_compiler_config={"compiler": "device_graph"}: the rewritten encoder graph is captured into one CUDA
+    graph and replayed; results stay equal to eager on new inputs and replay is faster than launch by launch."""
+    from xpu_graph_b200.workloads import make_encoder
+
+    model, x = make_encoder(seed=0)
+    cpu_model, _ = make_encoder(seed=0)
+    model = model.to(cuda_device)
+    compiled, got, mods, atens = _compile_run(model, (x.to(cuda_device),), vendor_compiler_config={"compiler": "device_graph"})
+    with torch.no_grad():
+        assert_parity(got, cpu_model(x), "device_graph first call")
+        g = torch.Generator().manual_seed(123)
+        for _ in range(2):
+            x2 = torch.randn(x.shape, generator=g)
+            assert_parity(compiled(x2.to(cuda_device)), cpu_model(x2), "device_graph replay")
+        plain, *_ = _compile_run(model, (x.to(cuda_device),))
+        xd = x.to(cuda_device)
+
+        def clock(fn):
+            for _ in range(5):
+                fn(xd)
+            torch.cuda.synchronize()
+            t0 = time.perf_counter()
+            for _ in range(50):
+                fn(xd)
+            torch.cuda.synchronize()
+            return (time.perf_counter() - t0) / 50
+
+        t_graph, t_plain = clock(compiled), clock(plain)
+    print(f"encoder block: captured {t_graph * 1e6:.0f} us, launch-by-launch {t_plain * 1e6:.0f} us per call")
+    assert t_graph < t_plain

@@ -7,6 +7,7 @@ is not modified): it adds ``Target.cuda_sm100`` next to ``mlu`` / ``none`` / ``n
 
     xpu_graph.passes.patterns.targets.cuda_sm100                         -> get_all_patterns(config)
     xpu_graph.passes.patterns.targets.cuda_sm100.structure_replacements  -> get_structure_replacements(config)
+    xpu_graph.backends.cuda_sm100                                        -> cuda_sm100_compile (CUDA-graph capture)
 
 ``backend(config)`` returns the callable to pass to ``torch.compile(..., backend=...)``; it enters
 xpu_graph through its own aot_autograd branch (compiler.py:143-153), which is the path that works on
@@ -60,6 +61,16 @@ def install():
         sys.modules[name] = tmod
         sys.modules[f"{name}.structure_replacements"] = smod
         setattr(sys.modules[pkg], TARGET_NAME, tmod)
+    bname = f"xpu_graph.backends.{TARGET_NAME}"
+    if bname not in sys.modules:  # vendor-compiler hook looked up by backends/__init__.py:19-25
+        import xpu_graph.backends as _backends
+
+        from . import device_graph as _dg
+
+        bmod = types.ModuleType(bname)
+        setattr(bmod, f"{TARGET_NAME}_compile", _dg.cuda_sm100_compile)
+        sys.modules[bname] = bmod
+        setattr(_backends, TARGET_NAME, bmod)
     return member
 
 
