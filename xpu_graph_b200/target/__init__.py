@@ -84,17 +84,18 @@ def make_config(**overrides):
     return XpuGraphConfig(**kwargs)
 
 
-def backend(config=None, capture=None):
+def backend(config=None, capture=None, cache=None):
     """``torch.compile`` backend: XpuGraph's inference compiler behind aot_autograd.
 
-    ``capture``: optional dict; the optimised GraphModule is stored under ``capture['gm']``."""
+    ``capture``: optional dict; the optimised GraphModule is stored under ``capture['gm']``.
+    ``cache``: optional XpuGraphCache (e.g. ``XpuGraphLocalCache(path)``) used when ``config.enable_cache``."""
     install()
     from torch._dynamo.backends.common import aot_autograd
     from xpu_graph import XpuGraph
     from xpu_graph.fx_utils import FxStage
 
     cfg = config if config is not None else make_config()
-    inner = XpuGraph(cfg)._get_compiler(FxStage.inference)
+    inner = XpuGraph(cfg, cache)._get_compiler(FxStage.inference)
 
     def fw_compiler(gm, example_inputs):
         out = inner(gm, example_inputs)
