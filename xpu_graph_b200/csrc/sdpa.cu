@@ -56,10 +56,42 @@ struct FlashCfg {
     static constexpr int P_BYTES = FM * FN * 2;
     // Two CTAs share an SM (tiles 112 KiB at D = 128), so there is no alignment slack: the kernel checks
     // that the dynamic shared-memory window starts on a 1024-byte boundary and reports if it does not.
-    static constexpr int SMEM_BYTES = Q_BYTES + 4 * KV_BYTES + P_BYTES + 256;
+    static constexpr int SMEM_BYTES = Q_BYTES + 4 * KV_BYTES + P_BYTES + 256;  // tiles + barriers
     static constexpr int TMEM_COLS = 256;             // S0 [0,64) S1 [64,128) O [128, 128+D)
     static constexpr uint32_t O_COL = 128;
 };
+
+// Work list of the persistent CTAs: tile L -> (batch*head, query tile). Consecutive L stay inside one
+// (batch, head), so the CTAs running at the same time share that head's K/V through L2. Within a head the
+// causal order alternates heavy and light query tiles (last, first, last-1, second, ...): any two neighbours
+// add up to the same number of key blocks, so a CTA that takes every gridDim.x-th tile gets an even share
+// (the host makes gridDim.x even).
+struct FlashTile {
+    int b, h, q0, nblk;
+};
+__device__ __forceinline__ FlashTile flash_tile(const SdpaParams& p, int L, int q_tiles) {
+    const int bh = L / q_tiles, k = L - bh * q_tiles;
+    const int qt = p.causal ? ((k & 1) ? (k >> 1) : (q_tiles - 1 - (k >> 1))) : k;
+    FlashTile t;
+    t.h = bh % (int)p.H;
+    t.b = bh / (int)p.H;
+    t.q0 = qt * FM;
+    t.nblk = (int)((p.Skv + FN - 1) / FN);
+    if (p.causal) {
+        const int lim = (t.q0 + FM - 1) / FN + 1;  // last block that any row of this tile can see
+        if (lim < t.nblk) t.nblk = lim;
+    }
+    return t;
+}
+
+// i-th tile of this CTA: CTAs take neighbouring tiles in pairs (2c, 2c+1), then (2(c+G), 2(c+G)+1), ...
+// Returns -1 when the CTA is done, -2 for the missing second half of a trailing odd pair.
+__device__ __forceinline__ int flash_tile_index(int i, int num_tiles) {
+    const int first = 2 * ((int)blockIdx.x + (i >> 1) * (int)gridDim.x);
+    if (first >= num_tiles) return -1;
+    const int L = first + (i & 1);
+    return L < num_tiles ? L : -2;
+}
 
 template <typename T, int D>
 __global__ void __launch_bounds__(kFlashThreads, 2)
@@ -72,9 +104,9 @@ flash_tc_kernel(const __grid_constant__ CUtensorMap tmq, const __grid_constant__
     uint8_t* v_s = k_s + 2 * Cfg::KV_BYTES;       // [2][KV_BYTES]
     uint8_t* p_s = v_s + 2 * Cfg::KV_BYTES;
     uint64_t* bars = reinterpret_cast<uint64_t*>(p_s + Cfg::P_BYTES);
-    uint64_t* q_full = bars;          // 1
-    uint64_t* k_full = bars + 1;      // 2
-    uint64_t* k_empty = bars + 3;     // 2
+    uint64_t* q_full = bars;          // 1   one phase per tile
+    uint64_t* k_full = bars + 1;      // 2   the block barriers below run on per-role block counters that
+    uint64_t* k_empty = bars + 3;     // 2   keep counting across the tiles of this CTA
     uint64_t* v_full = bars + 5;      // 2
     uint64_t* v_empty = bars + 7;     // 2
     uint64_t* s_full = bars + 9;      // 2
@@ -82,7 +114,8 @@ flash_tc_kernel(const __grid_constant__ CUtensorMap tmq, const __grid_constant__
     uint64_t* p_full = bars + 13;     // 1
     uint64_t* pv_full = bars + 14;    // 1
     uint64_t* drain_bar = bars + 15;  // 1
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 16);
+    uint64_t* q_empty = bars + 16;    // 1   all Q K^T of a tile have read Q
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 17);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     if ((ptx::smem_u32(smem) & 1023u) != 0) {  // uniform over the CTA: the swizzled tiles need this alignment
@@ -92,19 +125,11 @@ flash_tc_kernel(const __grid_constant__ CUtensorMap tmq, const __grid_constant__
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int q_tiles = (int)((p.Sq + FM - 1) / FM);
-    // Heavy (late) causal tiles first: the longest CTAs start earliest.
-    const int qt = p.causal ? (q_tiles - 1 - (int)(blockIdx.x % q_tiles)) : (int)(blockIdx.x % q_tiles);
-    const int bh = blockIdx.x / q_tiles;
-    const int h = bh % (int)p.H, b = bh / (int)p.H;
-    const int q0 = qt * FM;
-    int nblk = (int)((p.Skv + FN - 1) / FN);
-    if (p.causal) {
-        const int lim = (q0 + FM - 1) / FN + 1;  // last block that any row of this tile can see
-        if (lim < nblk) nblk = lim;
-    }
+    const int num_tiles = q_tiles * (int)(p.B * p.H);
 
     if (threadIdx.x == 0) {
         ptx::mbar_init(q_full, 1);
+        ptx::mbar_init(q_empty, 1);
         for (int s = 0; s < 2; ++s) {
             ptx::mbar_init(&k_full[s], 1);
             ptx::mbar_init(&k_empty[s], 1);
@@ -133,39 +158,40 @@ flash_tc_kernel(const __grid_constant__ CUtensorMap tmq, const __grid_constant__
             ptx::prefetch_tensormap(&tmq);
             ptx::prefetch_tensormap(&tmk);
             ptx::prefetch_tensormap(&tmv);
-            ptx::mbar_arrive_expect_tx(q_full, Cfg::Q_BYTES);
-#pragma unroll
-            for (int db = 0; db < Cfg::DB; ++db) ptx::tma_load_4d(q_s + db * (FM * 128), &tmq, q_full, db * 64, q0, h, b);
             bool ok = true;
-            int issued = 0;
-            for (int j = 0; j < nblk && ok; ++j) {
-                const int s = j & 1;
-                const uint32_t ph = (uint32_t)(j >> 1) & 1u;
-                if (!ptx::mbar_wait_bounded(&k_empty[s], ph ^ 1u, abort_flag)) { ok = false; break; }
-                ptx::mbar_arrive_expect_tx(&k_full[s], Cfg::KV_BYTES);
+            uint32_t n = 0;      // key blocks loaded so far (all tiles)
+            uint32_t tile_n = 0; // tiles started so far
+            for (int i = 0; ok; ++i) {
+                const int L = flash_tile_index(i, num_tiles);
+                if (L == -1) break;
+                if (L == -2) continue;
+                const FlashTile t = flash_tile(p, L, q_tiles);
+                const uint32_t tile_par = tile_n++ & 1u;
+                // Q may be overwritten once every Q K^T of the previous tile has completed
+                if (!ptx::mbar_wait_bounded(q_empty, tile_par ^ 1u, abort_flag)) { ok = false; break; }
+                ptx::mbar_arrive_expect_tx(q_full, Cfg::Q_BYTES);
 #pragma unroll
-                for (int db = 0; db < Cfg::DB; ++db)
-                    ptx::tma_load_4d(k_s + s * Cfg::KV_BYTES + db * (FN * 128), &tmk, &k_full[s], db * 64, j * FN, h, b);
-                if (!ptx::mbar_wait_bounded(&v_empty[s], ph ^ 1u, abort_flag)) { ok = false; issued = j * 2 + 1; break; }
-                ptx::mbar_arrive_expect_tx(&v_full[s], Cfg::KV_BYTES);
+                for (int db = 0; db < Cfg::DB; ++db) ptx::tma_load_4d(q_s + db * (FM * 128), &tmq, q_full, db * 64, t.q0, t.h, t.b);
+                for (int j = 0; j < t.nblk; ++j, ++n) {
+                    const int s = (int)(n & 1u);
+                    const uint32_t ph = (n >> 1) & 1u;
+                    if (!ptx::mbar_wait_bounded(&k_empty[s], ph ^ 1u, abort_flag)) { ok = false; break; }
+                    ptx::mbar_arrive_expect_tx(&k_full[s], Cfg::KV_BYTES);
 #pragma unroll
-                for (int db = 0; db < Cfg::DB; ++db)
-                    ptx::tma_load_4d(v_s + s * Cfg::KV_BYTES + db * (FN * 128), &tmv, &v_full[s], db * 64, j * FN, h, b);
-                issued = j * 2 + 2;
+                    for (int db = 0; db < Cfg::DB; ++db)
+                        ptx::tma_load_4d(k_s + s * Cfg::KV_BYTES + db * (FN * 128), &tmk, &k_full[s], db * 64, j * FN, t.h, t.b);
+                    if (!ptx::mbar_wait_bounded(&v_empty[s], ph ^ 1u, abort_flag)) { ok = false; break; }
+                    ptx::mbar_arrive_expect_tx(&v_full[s], Cfg::KV_BYTES);
+#pragma unroll
+                    for (int db = 0; db < Cfg::DB; ++db)
+                        ptx::tma_load_4d(v_s + s * Cfg::KV_BYTES + db * (FN * 128), &tmv, &v_full[s], db * 64, j * FN, t.h, t.b);
+                }
             }
             if (!ok) {
-                // Unwinding: wait (bounded) for this thread's own copies before shared memory is given up.
+                // Unwinding: give this thread's own copies a bounded time to land before shared memory is given up.
                 atomicOr(&g_sdpa_status[0], 16u);
                 const uint64_t t0 = ptx::globaltimer_ns();
-                auto drain = [&](uint64_t* bar, uint32_t parity) {
-                    while (!ptx::mbar_try_wait(bar, parity)) {
-                        if (ptx::globaltimer_ns() - t0 > ptx::kWaitLimitNs) break;
-                    }
-                };
-                drain(q_full, 0);
-                for (int n = (issued > 4 ? issued - 4 : 0); n < issued; ++n) {
-                    const int j = n >> 1;
-                    drain((n & 1) ? &v_full[j & 1] : &k_full[j & 1], (uint32_t)(j >> 1) & 1u);
+                while (ptx::globaltimer_ns() - t0 < 20000ull) {
                 }
             }
         }
@@ -176,9 +202,12 @@ flash_tc_kernel(const __grid_constant__ CUtensorMap tmq, const __grid_constant__
             constexpr uint32_t idesc_o = ptx::make_idesc_f16(fmt, FM, D, 1);
             const uint32_t q_addr = ptx::smem_u32(q_s), p_addr = ptx::smem_u32(p_s);
             bool ok = true;
-            auto issue_qk = [&](int j) -> bool {
-                const int s = j & 1;
-                const uint32_t ph = (uint32_t)(j >> 1) & 1u;
+            uint32_t nq = 0;  // Q K^T blocks issued so far (all tiles)
+            uint32_t np = 0;  // P V blocks issued so far
+            uint32_t tile_n = 0;
+            auto issue_qk = [&]() -> bool {
+                const int s = (int)(nq & 1u);
+                const uint32_t ph = (nq >> 1) & 1u;
                 if (!ptx::mbar_wait_bounded(&k_full[s], ph, abort_flag)) return false;
                 if (!ptx::mbar_wait_bounded(&s_empty[s], ph ^ 1u, abort_flag)) return false;
                 ptx::tc_fence_after();
@@ -192,28 +221,38 @@ flash_tc_kernel(const __grid_constant__ CUtensorMap tmq, const __grid_constant__
                 }
                 ptx::tc_commit(&k_empty[s]);
                 ptx::tc_commit(&s_full[s]);
+                ++nq;
                 return true;
             };
-            if (!ptx::mbar_wait_bounded(q_full, 0, abort_flag)) ok = false;
-            if (ok && nblk > 0) ok = issue_qk(0);
-            for (int j = 0; j < nblk && ok; ++j) {
-                if (j + 1 < nblk) {
-                    if (!issue_qk(j + 1)) { ok = false; break; }
-                }
-                const int s = j & 1;
-                if (!ptx::mbar_wait_bounded(p_full, (uint32_t)j & 1u, abort_flag)) { ok = false; break; }
-                if (!ptx::mbar_wait_bounded(&v_full[s], (uint32_t)(j >> 1) & 1u, abort_flag)) { ok = false; break; }
-                ptx::tc_fence_after();
-                const uint32_t v_addr = ptx::smem_u32(v_s + s * Cfg::KV_BYTES);
+            for (int i = 0; ok; ++i) {
+                const int L = flash_tile_index(i, num_tiles);
+                if (L == -1) break;
+                if (L == -2) continue;
+                const FlashTile t = flash_tile(p, L, q_tiles);
+                if (!ptx::mbar_wait_bounded(q_full, tile_n++ & 1u, abort_flag)) { ok = false; break; }
+                if (t.nblk > 0) ok = issue_qk();
+                if (ok && t.nblk == 1) ptx::tc_commit(q_empty);
+                for (int j = 0; j < t.nblk && ok; ++j, ++np) {
+                    if (j + 1 < t.nblk) {
+                        if (!issue_qk()) { ok = false; break; }
+                        if (j + 2 == t.nblk) ptx::tc_commit(q_empty);  // that was the tile's last Q K^T
+                    }
+                    const int s = (int)(np & 1u);
+                    if (!ptx::mbar_wait_bounded(p_full, np & 1u, abort_flag)) { ok = false; break; }
+                    if (!ptx::mbar_wait_bounded(&v_full[s], (np >> 1) & 1u, abort_flag)) { ok = false; break; }
+                    ptx::tc_fence_after();
+                    const uint32_t v_addr = ptx::smem_u32(v_s + s * Cfg::KV_BYTES);
 #pragma unroll
-                for (int kk = 0; kk < FN / 16; ++kk) {
-                    // O (+)= P V: the first block overwrites, later blocks accumulate in TMEM
-                    ptx::mma_f16_ss(tmem_base + Cfg::O_COL, ptx::make_kmajor_sw128_desc(p_addr + (uint32_t)(kk * 32)),
-                                    ptx::make_mnmajor_sw128_desc(v_addr + (uint32_t)(kk * 16 * 128), FN * 128), idesc_o,
-                                    (j | kk) != 0 ? 1u : 0u);
+                    for (int kk = 0; kk < FN / 16; ++kk) {
+                        // O (+)= P V: the tile's first block overwrites, later blocks accumulate in TMEM
+                        ptx::mma_f16_ss(tmem_base + Cfg::O_COL, ptx::make_kmajor_sw128_desc(p_addr + (uint32_t)(kk * 32)),
+                                        ptx::make_mnmajor_sw128_desc(v_addr + (uint32_t)(kk * 16 * 128), FN * 128), idesc_o,
+                                        (j | kk) != 0 ? 1u : 0u);
+                    }
+                    ptx::tc_commit(&v_empty[s]);
+                    ptx::tc_commit(pv_full);
                 }
-                ptx::tc_commit(&v_empty[s]);
-                ptx::tc_commit(pv_full);
+                if (ok && t.nblk == 0) ptx::tc_commit(q_empty);
             }
             if (!ok) {
                 atomicOr(&g_sdpa_status[0], 32u);
@@ -231,107 +270,115 @@ flash_tc_kernel(const __grid_constant__ CUtensorMap tmq, const __grid_constant__
         // allowed to lag, the final division by the row sum makes the result exact either way).
         const int quad = warp & 3;
         const int r_in_tile = quad * 32 + lane;
-        const int row = q0 + r_in_tile;
         const uint32_t lane_field = (uint32_t)(quad * 32) << 16;
         const float sl2 = p.scale * kLog2e;
         const int skv = (int)p.Skv;
-        const T* mrow = nullptr;
-        if (p.mask != nullptr && row < p.Sq)
-            mrow = reinterpret_cast<const T*>(p.mask) + (int64_t)b * p.m_sb + (int64_t)h * p.m_sh + (int64_t)row * p.m_sq;
-        float m_run = -INFINITY, l_run = 0.f;
         bool ok = true;
+        uint32_t n = 0;  // key blocks processed so far (all tiles)
 
-        for (int j = 0; j < nblk; ++j) {
-            const int sb = j & 1;
-            // wait results are made warp-uniform: the TMEM accesses below are warp-collective
-            if (!__all_sync(0xffffffffu, ptx::mbar_wait_bounded(&s_full[sb], (uint32_t)(j >> 1) & 1u, abort_flag))) { ok = false; break; }
-            ptx::tc_fence_after();
-            const uint32_t s_taddr = tmem_base + lane_field + (uint32_t)(sb * FN);
-            const int col_base = j * FN;
-            uint32_t r0[32], r1[32];
-            ptx::tmem_ld_32x32(s_taddr, r0);
-            ptx::tmem_ld_32x32(s_taddr + 32u, r1);
-            ptx::tmem_ld_wait();
-            float sc[FN];  // scores in the log2 domain
-#pragma unroll
-            for (int i = 0; i < 32; ++i) {
-                sc[i] = __uint_as_float(r0[i]) * sl2;
-                sc[32 + i] = __uint_as_float(r1[i]) * sl2;
-            }
-            // All of this warp's reads of the score buffer are done: the next Q K^T may overwrite it.
-            ptx::tc_fence_before();
-            ptx::mbar_arrive(&s_empty[sb]);
-            const bool masked_block = (p.mask != nullptr) || (col_base + FN > skv) || (p.causal && (col_base + FN - 1 > q0));
-            if (masked_block) {  // uniform over the CTA
-#pragma unroll
-                for (int i = 0; i < FN; ++i) {
-                    const int col = col_base + i;
-                    if (mrow != nullptr && col < skv) sc[i] += Cvt<T>::to_f(mrow[(int64_t)col * p.m_sk]) * kLog2e;
-                    if (col >= skv || (p.causal && col > row)) sc[i] = -INFINITY;
-                }
-            }
-            // 8 independent chains instead of one 64-deep dependency chain
-            float mxp[8];
-#pragma unroll
-            for (int i = 0; i < 8; ++i) mxp[i] = sc[i];
-#pragma unroll
-            for (int i = 8; i < FN; ++i) mxp[i & 7] = fmaxf(mxp[i & 7], sc[i]);
-            const float mx = fmaxf(fmaxf(fmaxf(mxp[0], mxp[1]), fmaxf(mxp[2], mxp[3])),
-                                   fmaxf(fmaxf(mxp[4], mxp[5]), fmaxf(mxp[6], mxp[7])));
-            const float m_new = fmaxf(m_run, mx);
-            const bool grow = m_new > m_run + kRescaleThreshold;  // also true for the first finite maximum
-            const bool warp_rescale = __any_sync(0xffffffffu, grow);
-            // P of the previous block has been consumed (and O is quiescent) once its P V has completed.
-            if (j > 0) {
-                if (!__all_sync(0xffffffffu, ptx::mbar_wait_bounded(pv_full, (uint32_t)(j - 1) & 1u, abort_flag))) { ok = false; break; }
+        for (int i = 0; ok; ++i) {
+            const int L = flash_tile_index(i, num_tiles);
+            if (L == -1) break;
+            if (L == -2) continue;
+            const FlashTile t = flash_tile(p, L, q_tiles);
+            const int q0 = t.q0, nblk = t.nblk;
+            const int row = q0 + r_in_tile;
+            const T* mrow = nullptr;
+            if (p.mask != nullptr && row < p.Sq)
+                mrow = reinterpret_cast<const T*>(p.mask) + (int64_t)t.b * p.m_sb + (int64_t)t.h * p.m_sh + (int64_t)row * p.m_sq;
+            float m_run = -INFINITY, l_run = 0.f;
+
+            for (int j = 0; j < nblk; ++j, ++n) {
+                const int sb = (int)(n & 1u);
+                // wait results are made warp-uniform: the TMEM accesses below are warp-collective
+                if (!__all_sync(0xffffffffu, ptx::mbar_wait_bounded(&s_full[sb], (n >> 1) & 1u, abort_flag))) { ok = false; break; }
                 ptx::tc_fence_after();
-            }
-            if (warp_rescale) {
-                const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
-                const float alpha = ptx::ex2_approx(m_run - m_use);  // 0 when there was no finite maximum yet
-                if (j > 0) {
+                const uint32_t s_taddr = tmem_base + lane_field + (uint32_t)(sb * FN);
+                const int col_base = j * FN;
+                uint32_t r0[32], r1[32];
+                ptx::tmem_ld_32x32(s_taddr, r0);
+                ptx::tmem_ld_32x32(s_taddr + 32u, r1);
+                ptx::tmem_ld_wait();
+                float sc[FN];  // scores in the log2 domain
 #pragma unroll
-                    for (int c = 0; c < D / 32; ++c) {
-                        uint32_t o[32];
-                        const uint32_t o_taddr = tmem_base + lane_field + Cfg::O_COL + (uint32_t)(c * 32);
-                        ptx::tmem_ld_32x32(o_taddr, o);
-                        ptx::tmem_ld_wait();
+                for (int i = 0; i < 32; ++i) {
+                    sc[i] = __uint_as_float(r0[i]) * sl2;
+                    sc[32 + i] = __uint_as_float(r1[i]) * sl2;
+                }
+                // All of this warp's reads of the score buffer are done: the next Q K^T may overwrite it.
+                ptx::tc_fence_before();
+                ptx::mbar_arrive(&s_empty[sb]);
+                const bool masked_block = (p.mask != nullptr) || (col_base + FN > skv) || (p.causal && (col_base + FN - 1 > q0));
+                if (masked_block) {  // uniform over the CTA
 #pragma unroll
-                        for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
-                        ptx::tmem_st_32x32(o_taddr, o);
+                    for (int i = 0; i < FN; ++i) {
+                        const int col = col_base + i;
+                        if (mrow != nullptr && col < skv) sc[i] += Cvt<T>::to_f(mrow[(int64_t)col * p.m_sk]) * kLog2e;
+                        if (col >= skv || (p.causal && col > row)) sc[i] = -INFINITY;
                     }
-                    ptx::tmem_st_wait();
                 }
-                l_run *= alpha;
-                m_run = m_new;
-            }
-            const float m_use = (m_run == -INFINITY) ? 0.f : m_run;
-            // probabilities -> shared memory (row r_in_tile of the swizzled K-major P tile)
-            float lp[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};  // independent partial row sums
+                // 8 independent chains instead of one 64-deep dependency chain
+                float mxp[8];
 #pragma unroll
-            for (int t = 0; t < FN / 8; ++t) {
-                Vec16<T> pv;
+                for (int i = 0; i < 8; ++i) mxp[i] = sc[i];
 #pragma unroll
-                for (int i = 0; i < 8; ++i) {
-                    const float pr = ptx::ex2_approx(sc[t * 8 + i] - m_use);
-                    lp[i] += pr;
-                    pv.v[i] = Cvt<T>::from_f(pr);
+                for (int i = 8; i < FN; ++i) mxp[i & 7] = fmaxf(mxp[i & 7], sc[i]);
+                const float mx = fmaxf(fmaxf(fmaxf(mxp[0], mxp[1]), fmaxf(mxp[2], mxp[3])),
+                                       fmaxf(fmaxf(mxp[4], mxp[5]), fmaxf(mxp[6], mxp[7])));
+                const float m_new = fmaxf(m_run, mx);
+                const bool grow = m_new > m_run + kRescaleThreshold;  // also true for the first finite maximum
+                const bool warp_rescale = __any_sync(0xffffffffu, grow);
+                // P of the previous block has been consumed (and O is quiescent) once its P V has completed.
+                if (j > 0) {
+                    if (!__all_sync(0xffffffffu, ptx::mbar_wait_bounded(pv_full, (n - 1) & 1u, abort_flag))) { ok = false; break; }
+                    ptx::tc_fence_after();
                 }
-                uint8_t* dst = p_s + r_in_tile * 128 + ((t ^ (r_in_tile & 7)) << 4);
-                *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<const uint4*>(&pv);
+                if (warp_rescale) {
+                    const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
+                    const float alpha = ptx::ex2_approx(m_run - m_use);  // 0 when there was no finite maximum yet
+                    if (j > 0) {
+#pragma unroll
+                        for (int c = 0; c < D / 32; ++c) {
+                            uint32_t o[32];
+                            const uint32_t o_taddr = tmem_base + lane_field + Cfg::O_COL + (uint32_t)(c * 32);
+                            ptx::tmem_ld_32x32(o_taddr, o);
+                            ptx::tmem_ld_wait();
+#pragma unroll
+                            for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+                            ptx::tmem_st_32x32(o_taddr, o);
+                        }
+                        ptx::tmem_st_wait();
+                    }
+                    l_run *= alpha;
+                    m_run = m_new;
+                }
+                const float m_use = (m_run == -INFINITY) ? 0.f : m_run;
+                // probabilities -> shared memory (row r_in_tile of the swizzled K-major P tile)
+                float lp[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};  // independent partial row sums
+#pragma unroll
+                for (int t8 = 0; t8 < FN / 8; ++t8) {
+                    Vec16<T> pv;
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+                        const float pr = ptx::ex2_approx(sc[t8 * 8 + i] - m_use);
+                        lp[i] += pr;
+                        pv.v[i] = Cvt<T>::from_f(pr);
+                    }
+                    uint8_t* dst = p_s + r_in_tile * 128 + ((t8 ^ (r_in_tile & 7)) << 4);
+                    *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<const uint4*>(&pv);
+                }
+                l_run += ((lp[0] + lp[1]) + (lp[2] + lp[3])) + ((lp[4] + lp[5]) + (lp[6] + lp[7]));
+                ptx::fence_proxy_async();  // P (generic-proxy stores) must be visible to the tensor core
+                ptx::tc_fence_before();
+                ptx::mbar_arrive(p_full);
             }
-            l_run += ((lp[0] + lp[1]) + (lp[2] + lp[3])) + ((lp[4] + lp[5]) + (lp[6] + lp[7]));
-            ptx::fence_proxy_async();  // P (generic-proxy stores) must be visible to the tensor core
-            ptx::tc_fence_before();
-            ptx::mbar_arrive(p_full);
-        }
-        if (ok && nblk > 0) {
-            if (!__all_sync(0xffffffffu, ptx::mbar_wait_bounded(pv_full, (uint32_t)(nblk - 1) & 1u, abort_flag))) ok = false;
-        }
-        if (ok) {
+            if (!ok) break;
+            if (nblk > 0) {
+                if (!__all_sync(0xffffffffu, ptx::mbar_wait_bounded(pv_full, (n - 1) & 1u, abort_flag))) { ok = false; break; }
+            }
             ptx::tc_fence_after();
             const float inv_l = 1.0f / l_run;
-            T* orow = reinterpret_cast<T*>(p.out) + (int64_t)b * p.o_sb + (int64_t)h * p.o_sh + (int64_t)row * p.o_ss;
+            T* orow = reinterpret_cast<T*>(p.out) + (int64_t)t.b * p.o_sb + (int64_t)t.h * p.o_sh + (int64_t)row * p.o_ss;
 #pragma unroll
             for (int c = 0; c < D / 32; ++c) {
                 uint32_t o[32];
@@ -344,17 +391,19 @@ flash_tc_kernel(const __grid_constant__ CUtensorMap tmq, const __grid_constant__
                 }
                 if (row < p.Sq) {
 #pragma unroll
-                    for (int t = 0; t < 4; ++t) {
+                    for (int t4 = 0; t4 < 4; ++t4) {
                         Vec16<T> ov;
 #pragma unroll
-                        for (int i = 0; i < 8; ++i) ov.v[i] = Cvt<T>::from_f(__uint_as_float(o[t * 8 + i]) * inv_l);
-                        st16(orow + c * 32 + t * 8, ov);
+                        for (int i = 0; i < 8; ++i) ov.v[i] = Cvt<T>::from_f(__uint_as_float(o[t4 * 8 + i]) * inv_l);
+                        st16(orow + c * 32 + t4 * 8, ov);
                     }
                 }
             }
-        } else if (lane == 0) {
-            atomicOr(&g_sdpa_status[0], 64u);
+            // this thread's reads of O are complete before it can arrive on p_full for the next tile's first
+            // block, and the next tile's first P V (which overwrites O) waits for that arrival
+            ptx::tc_fence_before();
         }
+        if (!ok && lane == 0) atomicOr(&g_sdpa_status[0], 64u);
     }
 
     ptx::tc_fence_before();
@@ -380,9 +429,12 @@ int launch_flash_tc(const SdpaParams& p, cudaStream_t st) {
         cudaGetLastError();
         return fail(XG_ERR_LAUNCH, "xg_sdpa_fwd: cannot reserve shared memory: %s", cudaGetErrorString(e));
     }
-    const int64_t grid = p.B * p.H * ((p.Sq + FM - 1) / FM);
-    if (grid > 0x7fffffffLL) return fail(XG_ERR_TOO_LARGE, "xg_sdpa_fwd: too many tiles");
-    kern<<<(unsigned)grid, kFlashThreads, Cfg::SMEM_BYTES, st>>>(tq, tk, tv, p);
+    const int64_t tiles = p.B * p.H * ((p.Sq + FM - 1) / FM);
+    if (tiles > 0x7fffffffLL) return fail(XG_ERR_TOO_LARGE, "xg_sdpa_fwd: too many tiles");
+    const int64_t resident = 2LL * num_sms();  // persistent CTAs, two per SM
+    const int64_t pairs = (tiles + 1) / 2;      // a CTA takes tiles in neighbouring (heavy, light) pairs
+    const unsigned grid = (unsigned)(pairs < resident ? pairs : resident);
+    kern<<<grid, kFlashThreads, Cfg::SMEM_BYTES, st>>>(tq, tk, tv, p);
     return check_launch("xg_sdpa_fwd");
 }
 
