@@ -180,6 +180,16 @@ int xg_bgemm_bias_act(const void* A, const void* B, const void* bias, const void
 int xg_gemm_swiglu(const void* A, const void* Wg, const void* Wu, void* out, int64_t M, int64_t N,
                    int64_t K, int64_t lda, int64_t ldw, int64_t ldc, int dtype, void* stream);
 
+/*
+ * Projection with the rotary embedding in the epilogue: out[r, :] = rope(round(A[r, :] @ W^T)) per head, where row
+ * r is token (r / S, r % S), heads are consecutive blocks of D output columns, and cos/sin are [S, D] tables of
+ * the output dtype (rotate-half form, as xg_rope). W: [N, K] Linear layout, N % D == 0, D in {64, 128}. The
+ * projection result is rounded to the tensor dtype before the rotation, as the un-fused graph does.
+ * Replaces: the dense layer (structure/custom_denselayer.py:80-88) followed by the RoPE chain of xg_rope.
+ */
+int xg_gemm_rope(const void* A, const void* W, const void* cos, const void* sin, void* out, int64_t M, int64_t N,
+                 int64_t K, int64_t lda, int64_t ldw, int64_t ldc, int64_t S, int64_t D, int dtype, void* stream);
+
 /* ---- attention ------------------------------------------------------------------------- */
 
 /*

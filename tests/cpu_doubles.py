@@ -41,6 +41,14 @@ def register():
     k(ops.dense)(dense)
     k(ops.batch_dense)(lambda x, weight, weight_trans, bias, residual, act: ref_ops.batch_dense(
         x, weight, weight_trans, bias if residual is None else residual, act))
+    def dense_rope(x, weight, cos, sin, seq_len, head_dim):
+        y = x @ weight.t()
+        M, N = y.shape
+        y4 = y.view(M // seq_len, seq_len, N // head_dim, head_dim).transpose(1, 2)
+        r = ref_ops.rope(y4, cos.reshape(seq_len, head_dim), sin.reshape(seq_len, head_dim))
+        return r.transpose(1, 2).reshape(M, N).contiguous()
+
+    k(ops.dense_rope)(dense_rope)
     k(ops.dense_swiglu)(lambda x, w_gate, w_up: ref_ops.dense_swiglu(x, w_gate, w_up))
     k(ops.sdpa)(lambda q, k_, v, attn_mask, scale, is_causal: ref_ops.sdpa(q, k_, v, attn_mask, scale, is_causal).contiguous())
 

@@ -133,6 +133,31 @@ def test_dense_swiglu(cuda_device):
     assert_parity(got, ref_ops.dense_swiglu(x, wg, wu), "dense_swiglu")
 
 
+@pytest.mark.parametrize("B,S,H,D,K", [(2, 64, 2, 128, 256), (1, 200, 3, 64, 128), (2, 320, 4, 128, 512), (3, 33, 1, 64, 64)])
+def test_dense_rope(cuda_device, B, S, H, D, K):
+    """Projection with the rotary embedding in the epilogue == dense layer followed by the RoPE kernel (bit for
+    bit: both round the projection to bf16 and rotate in fp32), and within tolerance of the eager chain."""
+    from xpu_graph_b200 import lib
+    from xpu_graph_b200.modules import DenseLayerModule, DenseRopeModule, RopeModule
+
+    g = torch.Generator().manual_seed(41)
+    x = torch.randn(B * S, K, generator=g).to(torch.bfloat16)
+    w = (0.05 * torch.randn(H * D, K, generator=g)).to(torch.bfloat16)
+    inv = 1.0 / (10000.0 ** (torch.arange(0, D, 2).float() / D))
+    ang = torch.outer(torch.arange(S).float(), inv)
+    emb = torch.cat((ang, ang), dim=-1)
+    cos, sin = emb.cos().to(torch.bfloat16), emb.sin().to(torch.bfloat16)
+    xd, wd, cd, sd = (t.to(cuda_device) for t in (x, w, cos, sin))
+    got = DenseRopeModule()(xd, wd, cd, sd, B, S, H, D)
+    two_step = RopeModule()(DenseLayerModule(False)(xd, wd, True, None, "none").view(B, S, H, D).transpose(1, 2), cd, sd)
+    torch.cuda.synchronize()
+    assert lib.tc_status() == 0
+    assert got.shape == (B, H, S, D)
+    assert torch.equal(got, two_step), "fused epilogue must equal dense + rope kernels bit for bit"
+    want = ref_ops.rope(ref_ops.dense(x, w, True, None, "none").view(B, S, H, D).transpose(1, 2), cos, sin)
+    assert_parity(got, want, f"dense_rope {B}x{S}x{H}x{D}")
+
+
 def test_batch_dense(cuda_device):
     from xpu_graph_b200.modules import BatchDenseLayerModule
 

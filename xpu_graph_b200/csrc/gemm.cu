@@ -3,9 +3,11 @@
 #include "common.cuh"
 
 namespace xg {
+struct GemmExtras;
 int gemm_tc_entry(const void* A, const void* B, const void* bias, const void* residual, void* out, int64_t M, int64_t N,
                   int64_t K, int64_t lda, int64_t ldb, int64_t ldc, int64_t ldr, int trans_b, int act, int dtype,
-                  void* workspace, int64_t ws_bytes, cudaStream_t st, bool force_split = false);
+                  void* workspace, int64_t ws_bytes, cudaStream_t st, bool force_split = false,
+                  const GemmExtras* extras = nullptr);
 int64_t gemm_workspace_bytes(int64_t M, int64_t N, int64_t K);
 int gemm_tc_static_entry(const void* A, const void* B, const void* bias, const void* residual, void* out, int64_t M,
                          int64_t N, int64_t K, int64_t lda, int64_t ldb, int64_t ldc, int64_t ldr, int trans_b, int act,
@@ -15,6 +17,8 @@ int gemm_f32_entry(const void* A, const void* B, const void* bias, const void* r
                    int64_t K, int64_t lda, int64_t ldb, int64_t ldc, int64_t ldr, int trans_b, int act, cudaStream_t st);
 int gemm_swiglu_entry(const void* A, const void* Wg, const void* Wu, void* out, int64_t M, int64_t N, int64_t K,
                       int64_t lda, int64_t ldw, int64_t ldc, int dtype, cudaStream_t st);
+int gemm_rope_entry(const void* A, const void* W, const void* cos, const void* sin, void* out, int64_t M, int64_t N, int64_t K,
+                    int64_t lda, int64_t ldw, int64_t ldc, int64_t S, int64_t D, int dtype, cudaStream_t st);
 int read_tc_status(unsigned int* host_out, int reset);
 int read_sdpa_status(unsigned int* host_out, int reset);
 
@@ -100,6 +104,16 @@ extern "C" int xg_gemm_swiglu(const void* A, const void* Wg, const void* Wu, voi
     if (dtype != XG_BF16 && dtype != XG_F16) return fail(XG_ERR_UNSUPPORTED, "xg_gemm_swiglu: 16-bit dtypes only");
     if (lda < K || ldw < K || ldc < N) return fail(XG_ERR_INVALID_ARG, "xg_gemm_swiglu: leading dimension too small");
     return gemm_swiglu_entry(A, Wg, Wu, out, M, N, K, lda, ldw, ldc, dtype, reinterpret_cast<cudaStream_t>(stream));
+}
+
+extern "C" int xg_gemm_rope(const void* A, const void* W, const void* cos, const void* sin, void* out, int64_t M, int64_t N,
+                            int64_t K, int64_t lda, int64_t ldw, int64_t ldc, int64_t S, int64_t D, int dtype, void* stream) {
+    using namespace xg;
+    if (!A || !W || !cos || !sin || !out) return fail(XG_ERR_INVALID_ARG, "xg_gemm_rope: null pointer");
+    if (M < 0 || N < 0 || K <= 0) return fail(XG_ERR_INVALID_ARG, "xg_gemm_rope: bad extents");
+    if (dtype != XG_BF16 && dtype != XG_F16) return fail(XG_ERR_UNSUPPORTED, "xg_gemm_rope: 16-bit dtypes only");
+    if (lda < K || ldw < K || ldc < N) return fail(XG_ERR_INVALID_ARG, "xg_gemm_rope: leading dimension too small");
+    return gemm_rope_entry(A, W, cos, sin, out, M, N, K, lda, ldw, ldc, S, D, dtype, reinterpret_cast<cudaStream_t>(stream));
 }
 
 extern "C" int xg_tc_status(unsigned int* status, int reset) {

@@ -22,9 +22,19 @@
 
 namespace xg {
 
+// Optional rotary-embedding epilogue: out[row, h*D + j] gets the rotate-half RoPE of the accumulator row at
+// position (row % S), with cos/sin tables [S, D] of the output dtype.
+struct GemmExtras {
+    const void* rope_cos = nullptr;
+    const void* rope_sin = nullptr;
+    int64_t rope_S = 0;
+    int rope_D = 0;
+};
+
 int gemm_tc_entry(const void* A, const void* B, const void* bias, const void* residual, void* out, int64_t M, int64_t N,
                   int64_t K, int64_t lda, int64_t ldb, int64_t ldc, int64_t ldr, int trans_b, int act, int dtype,
-                  void* workspace, int64_t ws_bytes, cudaStream_t st, bool force_split = false);
+                  void* workspace, int64_t ws_bytes, cudaStream_t st, bool force_split = false,
+                  const GemmExtras* extras = nullptr);
 
 struct GemmPlan {
     int bn;      // tile width: 64, 128 or 256
@@ -97,6 +107,10 @@ struct GemmParams {
     int vec_ok;       // out (and residual) rows are 16-byte addressable
     int bias_vec_ok;  // bias pointer 16-byte aligned
     int num_m_blocks, num_n_blocks, num_k_blocks;
+    const void* rope_cos;  // non-null: rotary-embedding epilogue (see GemmExtras)
+    const void* rope_sin;
+    int64_t rope_S;
+    int rope_D;
     int splits;      // > 1: split-K, every (tile, split) unit writes raw fp32 accumulators to `partial`
     float* partial;  // [splits][M][N] fp32 workspace (split-K only)
 };
@@ -148,6 +162,50 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams& p, uint32_t tmem
     T* out = reinterpret_cast<T*>(p.out);
     const T* bias = reinterpret_cast<const T*>(p.bias);
     const T* resid = reinterpret_cast<const T*>(p.residual);
+    if (!SWIGLU && p.rope_cos != nullptr) {
+        // Rotary epilogue: the two halves of a head (columns j and j + D/2) meet in one thread, which owns the whole
+        // row of the tile: read the two 32-column chunks that are D/2 apart, rotate, store both. The host guarantees
+        // N % D == 0, D in {64, 128}, 16-byte addressable rows and tables.
+        const int D = p.rope_D, half_chunks = D / 64;  // chunks of 32 per half head: 1 (D = 64) or 2 (D = 128)
+        const int64_t pos = row_ok ? row % p.rope_S : 0;
+        const T* cosr = reinterpret_cast<const T*>(p.rope_cos) + pos * D;
+        const T* sinr = reinterpret_cast<const T*>(p.rope_sin) + pos * D;
+#pragma unroll 1
+        for (int c = 0; c < OUT_BN / 32; ++c) {
+            const int in_head = c % (2 * half_chunks);
+            if (in_head >= half_chunks) continue;  // second half: handled with its partner below
+            const int64_t col0 = (int64_t)nb * OUT_BN + c * 32;
+            if (col0 >= p.N) break;
+            const int c2 = c + half_chunks;
+            uint32_t r1[32], r2[32];
+            const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(acc * BN);
+            ptx::tmem_ld_32x32(taddr + (uint32_t)(c * 32), r1);
+            ptx::tmem_ld_32x32(taddr + (uint32_t)(c2 * 32), r2);
+            ptx::tmem_ld_wait();
+            if (row_ok) {
+                const int j0 = (c % (2 * half_chunks)) * 32;  // column inside the head of the first half
+                T* o1 = out + row * p.ldc + col0;
+                T* o2 = o1 + D / 2;
+#pragma unroll
+                for (int i = 0; i < 32; i += 8) {
+                    const Vec16<T> c1 = ld16(cosr + j0 + i), s1 = ld16(sinr + j0 + i);
+                    const Vec16<T> cc2 = ld16(cosr + j0 + D / 2 + i), s2 = ld16(sinr + j0 + D / 2 + i);
+                    Vec16<T> y1, y2;
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        // the projection result is rounded to the tensor dtype first, as the un-fused graph does
+                        const float a = Cvt<T>::to_f(Cvt<T>::from_f(__uint_as_float(r1[i + j])));
+                        const float b = Cvt<T>::to_f(Cvt<T>::from_f(__uint_as_float(r2[i + j])));
+                        y1.v[j] = Cvt<T>::from_f(a * Cvt<T>::to_f(c1.v[j]) - b * Cvt<T>::to_f(s1.v[j]));
+                        y2.v[j] = Cvt<T>::from_f(b * Cvt<T>::to_f(cc2.v[j]) + a * Cvt<T>::to_f(s2.v[j]));
+                    }
+                    st16(o1 + i, y1);
+                    st16(o2 + i, y2);
+                }
+            }
+        }
+        return;
+    }
 #pragma unroll 1
     for (int c = 0; c < OUT_BN / 32; ++c) {
         const int64_t col0 = (int64_t)nb * OUT_BN + c * 32;
@@ -737,8 +795,9 @@ namespace {
 template <typename T>
 int gemm_tc_dispatch(const void* A, const void* B, const void* bias, const void* residual, void* out, int64_t M,
                      int64_t N, int64_t K, int64_t lda, int64_t ldb, int64_t ldc, int64_t ldr, int trans_b, int act,
-                     void* workspace, int64_t ws_bytes, bool force_split, cudaStream_t st) {
+                     void* workspace, int64_t ws_bytes, bool force_split, const GemmExtras* ex, cudaStream_t st) {
     constexpr bool is_bf16 = std::is_same<T, __nv_bfloat16>::value;
+    if (ex && ex->rope_cos) ws_bytes = 0;  // the rotary epilogue lives in the GEMM kernel: no split-K
     const int64_t mblk = (M + BM - 1) / BM;
     if (workspace == nullptr || (reinterpret_cast<uintptr_t>(workspace) & 15u) != 0) ws_bytes = 0;
     GemmPlan pl = plan_gemm(M, N, K, ws_bytes, num_sms());
@@ -746,6 +805,7 @@ int gemm_tc_dispatch(const void* A, const void* B, const void* bias, const void*
         pl.bn = 256;  // the caller asked for the split path: the smallest split that the scratch holds
         pl.splits = 2;
     }
+    if (ex && ex->rope_cos && pl.bn < 128) pl.bn = 128;  // a head (<= 128 columns) must not straddle two tiles
     const int bn = pl.bn;
 
     CUtensorMap ta, tb;
@@ -760,6 +820,10 @@ int gemm_tc_dispatch(const void* A, const void* B, const void* bias, const void*
     p.residual = residual;
     p.M = M; p.N = N; p.K = K; p.ldc = ldc; p.ldr = ldr;
     p.act = act;
+    p.rope_cos = ex ? ex->rope_cos : nullptr;
+    p.rope_sin = ex ? ex->rope_sin : nullptr;
+    p.rope_S = ex ? ex->rope_S : 0;
+    p.rope_D = ex ? ex->rope_D : 0;
     p.vec_ok = (ldc % 8 == 0) && aligned16(out) && (!residual || (ldr % 8 == 0 && aligned16(residual)));
     p.bias_vec_ok = bias ? aligned16(bias) : 0;
     if (trans_b && pl.splits == 1 && use_cta_pairs(M, N, 256)) {
@@ -808,6 +872,10 @@ int gemm_swiglu_dispatch(const void* A, const void* Wg, const void* Wu, void* ou
     p.residual = nullptr;
     p.M = M; p.N = N; p.K = K; p.ldc = ldc; p.ldr = 0;
     p.act = XG_ACT_NONE;
+    p.rope_cos = nullptr;
+    p.rope_sin = nullptr;
+    p.rope_S = 0;
+    p.rope_D = 0;
     p.vec_ok = (ldc % 8 == 0) && aligned16(out);
     p.bias_vec_ok = 0;
     p.num_n_blocks = (int)((N + 127) / 128);
@@ -827,15 +895,15 @@ int gemm_swiglu_dispatch(const void* A, const void* Wg, const void* Wu, void* ou
 // Entry used by xg_gemm_bias_act for 16-bit dtypes; W is [N, K] (trans_b = 1) or [K, N] (trans_b = 0).
 int gemm_tc_entry(const void* A, const void* B, const void* bias, const void* residual, void* out, int64_t M, int64_t N,
                   int64_t K, int64_t lda, int64_t ldb, int64_t ldc, int64_t ldr, int trans_b, int act, int dtype,
-                  void* workspace, int64_t ws_bytes, cudaStream_t st, bool force_split) {
+                  void* workspace, int64_t ws_bytes, cudaStream_t st, bool force_split, const GemmExtras* extras) {
     if (!aligned16(A) || !aligned16(B) || lda % 8 != 0 || ldb % 8 != 0)
         return fail(XG_ERR_UNSUPPORTED, "xg_gemm_bias_act: A/W must be 16-byte aligned with row strides multiple of 8 elements");
     if (M * N == 0) return XG_OK;
     if (M > (int64_t)BM * 0x7fffff || N > (int64_t)64 * 0x7fffff || K > 0x7fffffff)
         return fail(XG_ERR_TOO_LARGE, "xg_gemm_bias_act: extent too large");
     if (dtype == XG_BF16)
-        return gemm_tc_dispatch<__nv_bfloat16>(A, B, bias, residual, out, M, N, K, lda, ldb, ldc, ldr, trans_b, act, workspace, ws_bytes, force_split, st);
-    return gemm_tc_dispatch<__half>(A, B, bias, residual, out, M, N, K, lda, ldb, ldc, ldr, trans_b, act, workspace, ws_bytes, force_split, st);
+        return gemm_tc_dispatch<__nv_bfloat16>(A, B, bias, residual, out, M, N, K, lda, ldb, ldc, ldr, trans_b, act, workspace, ws_bytes, force_split, extras, st);
+    return gemm_tc_dispatch<__half>(A, B, bias, residual, out, M, N, K, lda, ldb, ldc, ldr, trans_b, act, workspace, ws_bytes, force_split, extras, st);
 }
 
 // ---- split-K on a fixed, library-owned scratch array (nothing is allocated by anyone) ------------------
@@ -887,6 +955,20 @@ int gemm_tc_static_entry(const void* A, const void* B, const void* bias, const v
     if (rc != XG_OK) return rc;
     return gemm_tc_entry(A, B, bias, residual, out, M, N, K, lda, ldb, ldc, ldr, trans_b, act, dtype, scratch,
                          kStaticScratchBytes, st, /*force_split=*/true);
+}
+
+int gemm_rope_entry(const void* A, const void* W, const void* cos, const void* sin, void* out, int64_t M, int64_t N, int64_t K,
+                    int64_t lda, int64_t ldw, int64_t ldc, int64_t S, int64_t D, int dtype, cudaStream_t st) {
+    if (D != 64 && D != 128) return fail(XG_ERR_UNSUPPORTED, "xg_gemm_rope: head_dim must be 64 or 128");
+    if (N % D != 0 || S <= 0) return fail(XG_ERR_INVALID_ARG, "xg_gemm_rope: N must be a multiple of head_dim and S positive");
+    if (!aligned16(cos) || !aligned16(sin) || !aligned16(out) || ldc % 8 != 0)
+        return fail(XG_ERR_UNSUPPORTED, "xg_gemm_rope: tables and output rows must be 16-byte addressable");
+    GemmExtras ex;
+    ex.rope_cos = cos;
+    ex.rope_sin = sin;
+    ex.rope_S = S;
+    ex.rope_D = (int)D;
+    return gemm_tc_entry(A, W, nullptr, nullptr, out, M, N, K, lda, ldw, ldc, 0, 1, XG_ACT_NONE, dtype, nullptr, 0, st, false, &ex);
 }
 
 int gemm_swiglu_entry(const void* A, const void* Wg, const void* Wu, void* out, int64_t M, int64_t N, int64_t K,

@@ -17,13 +17,15 @@ from .workloads import EncoderBlock, LlamaDecoderLayer, RecsysGraph
 
 
 class FusedLlamaDecoderLayer(nn.Module):
-    """RMSNorm | 3x dense | 2x RoPE | flash SDPA | dense(+residual) | add-free RMSNorm | dual-GEMM SwiGLU |
-    dense(+residual). The two residual adds ride in the GEMM epilogues (the [M, N] addend form of the
-    dense layer), so the block is 10 kernels."""
+    """RMSNorm | 2x dense with the RoPE epilogue (q, k) | dense (v) | flash SDPA | dense(+residual) | RMSNorm |
+    dual-GEMM SwiGLU | dense(+residual). The two residual adds ride in the GEMM epilogues (the [M, N] addend
+    form of the dense layer) and RoPE in the q/k projections' epilogues, so the block is 9 kernels."""
 
-    def __init__(self, layer: LlamaDecoderLayer, fuse_swiglu_gemm: bool = True):
+    def __init__(self, layer: LlamaDecoderLayer, fuse_swiglu_gemm: bool = True, fuse_rope_gemm: bool = True):
         super().__init__()
         self.layer = layer
+        self.fuse_rope_gemm = fuse_rope_gemm and layer.head_dim in (64, 128)
+        self.dense_rope = M.DenseRopeModule()
         self.heads, self.head_dim = layer.heads, layer.head_dim
         self.eps1, self.eps2 = layer.input_norm.eps, layer.post_norm.eps
         self.fuse_swiglu_gemm = fuse_swiglu_gemm
@@ -40,11 +42,15 @@ class FusedLlamaDecoderLayer(nn.Module):
         B, S, Hd = x.shape
         x2 = x.reshape(B * S, Hd)
         h = self.norm(x2, L.input_norm.weight, self.eps1)
-        q = self.dense(h, L.q_proj.weight, True, None, "none").view(B, S, self.heads, self.head_dim).transpose(1, 2)
-        k = self.dense(h, L.k_proj.weight, True, None, "none").view(B, S, self.heads, self.head_dim).transpose(1, 2)
+        if self.fuse_rope_gemm:
+            q = self.dense_rope(h, L.q_proj.weight, cos, sin, B, S, self.heads, self.head_dim)
+            k = self.dense_rope(h, L.k_proj.weight, cos, sin, B, S, self.heads, self.head_dim)
+        else:
+            q = self.dense(h, L.q_proj.weight, True, None, "none").view(B, S, self.heads, self.head_dim).transpose(1, 2)
+            k = self.dense(h, L.k_proj.weight, True, None, "none").view(B, S, self.heads, self.head_dim).transpose(1, 2)
+            q = self.rope(q, cos, sin)
+            k = self.rope(k, cos, sin)
         v = self.dense(h, L.v_proj.weight, True, None, "none").view(B, S, self.heads, self.head_dim).transpose(1, 2)
-        q = self.rope(q, cos, sin)
-        k = self.rope(k, cos, sin)
         a = self.sdpa(q, k, v, None, None, True)  # [B, H, S, D]
         a2 = a.transpose(1, 2).reshape(B * S, Hd)
         x2 = self.dense(a2, L.o_proj.weight, True, x2, "none")  # residual as the full [M, N] addend

@@ -53,6 +53,8 @@ SIGNATURES = {
                                   c_int, c_int, c_int, c_void_p]),
     "xg_gemm_swiglu": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64, c_int64,
                                c_int64, c_int, c_void_p]),
+    "xg_gemm_rope": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64, c_int64,
+                             c_int64, c_int64, c_int64, c_int, c_void_p]),
     "xg_sdpa_fwd": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64,
                             c_int64, _I64P, _I64P, _I64P, _I64P, _I64P, c_float, c_int, c_int, c_void_p]),
     "xg_seg_copy": (c_int, [_VPP, _VPP, _I64P, _I64P, _I64P, c_int64, c_int64, c_void_p, c_int, c_void_p]),

@@ -163,6 +163,16 @@ class DenseSwiGLUModule(torch.nn.Module):
         return _X.dense_swiglu(inputs, w_gate, w_up)
 
 
+class DenseRopeModule(torch.nn.Module):
+    """q/k projection with the rotary embedding applied in the GEMM epilogue:
+    forward(inputs [B*S, K], weight [H*D, K], cos, sin, B, S, H, D) -> [B, H, S, D] (a view of the [B, S, H*D]
+    result, i.e. exactly what reshape + transpose + RopeModule returned)."""
+
+    def forward(self, inputs, weight, cos, sin, B, S, H, D):
+        y = _X.dense_rope(inputs, weight, cos, sin, int(S), int(D))
+        return y.view(B, S, H, D).transpose(1, 2)
+
+
 class SwiGLUModule(torch.nn.Module):
     """silu(gate) * up (targets/npu/fuse_silu_mul.py:21-69 applies the same fusion to a packed tensor)."""
 

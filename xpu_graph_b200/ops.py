@@ -353,6 +353,31 @@ def _(x, w_gate, w_up):
     return torch.empty((x.shape[0], w_gate.shape[0]), dtype=x.dtype, device=x.device)
 
 
+@torch.library.custom_op(f"{NS}::dense_rope", mutates_args=(), device_types="cuda")
+def dense_rope(x: torch.Tensor, weight: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, seq_len: int,
+               head_dim: int) -> torch.Tensor:
+    """rope(x @ weight^T) with the rotation in the GEMM epilogue. x: [B*S, K] (row r is token r % seq_len of its
+    sequence), weight: [H*D, K]; cos/sin broadcastable from [S, D]. Returns [B*S, H*D]."""
+    x = _mat(x)
+    weight = _mat(weight)
+    M, K = x.shape
+    N = weight.shape[0]
+    cos2 = cos.reshape(seq_len, head_dim).to(x.dtype).contiguous()
+    sin2 = sin.reshape(seq_len, head_dim).to(x.dtype).contiguous()
+    out = torch.empty((M, N), dtype=x.dtype, device=x.device)
+    with _GemmTimer(x, 2 * M * N * K):
+        rc = _lib.load().xg_gemm_rope(_ptr(x), _ptr(weight), _ptr(cos2), _ptr(sin2), _ptr(out), M, N, K, _row_stride(x),
+                                      _row_stride(weight), N, seq_len, head_dim, _code(x.dtype), _stream(x))
+    _lib.check(rc, "xg_gemm_rope")
+    _bump()
+    return out
+
+
+@dense_rope.register_fake
+def _(x, weight, cos, sin, seq_len, head_dim):
+    return torch.empty((x.shape[0], weight.shape[0]), dtype=x.dtype, device=x.device)
+
+
 # --------------------------------------------------------------------------------------------
 # attention
 # --------------------------------------------------------------------------------------------

@@ -558,6 +558,48 @@ class FusedEmbeddingStack(Pattern):
         return changed
 
 
+# ---- RoPE folded into the projection's epilogue ------------------------------------------------------------------
+class FusedDenseRope(Pattern):
+    """rope(transpose(reshape(dense(x, W), [B, S, H, D]), 1, 2)) -> DenseRopeModule: the rotation runs in the GEMM
+    epilogue, which saves one full read and write of q / k. Runs after FusedRoPE and CustomDenseLayer."""
+
+    _opt_level = OptLevel.level2
+    _pattern_group = PatternGroup.GROUP2
+
+    def process(self, gm: fx.GraphModule) -> bool:
+        changed = False
+        for node in list(gm.graph.nodes):
+            if not _module_call(gm, node, M.RopeModule):
+                continue
+            tr, cos, sin = node.args
+            if not (_is(tr, aten.transpose.int) and set(tr.args[1:3]) == {1, 2} and _only_user(tr, node)):
+                continue
+            rs = tr.args[0]
+            if not (_is(rs, *_RESHAPES) and _only_user(rs, tr)):
+                continue
+            dense = rs.args[0]
+            if not (_module_call(gm, dense, M.DenseLayerModule) and dense.target == DENSE_NAME and _only_user(dense, rs)):
+                continue
+            x, w, wt, bias, act = dense.args
+            xv, rv = _val(x), _val(rs)
+            if not (wt and bias is None and act == "none" and _tensor_ok(xv, 2) and isinstance(rv, torch.Tensor)):
+                continue
+            if xv.dtype not in (torch.bfloat16, torch.float16) or rv.dim() != 4 or not _static(rv.shape):
+                continue
+            B, S, H, D = rv.shape
+            if D not in (64, 128) or xv.shape[0] != B * S or xv.shape[1] % 8 != 0:
+                continue
+            _ensure(gm, "xg_dense_rope", M.DenseRopeModule)
+            with gm.graph.inserting_before(node):
+                new = gm.graph.call_module("xg_dense_rope", (x, w, cos, sin, B, S, H, D))
+            _fill_meta(gm, new)
+            node.replace_all_uses_with(new)
+            for dead in (node, tr, rs, dense):
+                gm.graph.erase_node(dead)
+            changed = True
+        return changed
+
+
 # ---- cat along the last dim -------------------------------------------------------------------------------------
 class FusedCatLastDim(Pattern):
     """aten.cat of >= 2 tensors along the last dim -> one segmented copy (CatLastDimModule). Runs after
@@ -596,7 +638,7 @@ class FusedCatLastDim(Pattern):
 
 
 ALL_PATTERNS = [FusedNativeLayerNorm, FusedSdpa, FusedRoPE, FusedEmbeddingStack, FusedSwiGLU, FusedDenseResidual,
-                FusedAddNorm, FusedCatLastDim]
+                FusedAddNorm, FusedCatLastDim, FusedDenseRope]
 
 
 def get_all_patterns(config) -> dict:
