@@ -3,11 +3,11 @@
 // 16-bit inputs with head_dim 64 or 128 run on the tensor cores (flash_tc_kernel):
 //   one CTA per (batch, head, 128-query tile); warp 0 streams K/V tiles with TMA (2-stage ring),
 //   warp 1's elected thread issues tcgen05.mma for S = Q K^T (into one of two TMEM buffers, so the
-//   next block's scores are computed while the current block is in softmax) and for P V (P staged in
-//   shared memory as bf16/f16 in the 128-byte-swizzled K-major layout, V consumed MN-major exactly as
-//   TMA leaves it); warps 2..5 own one query row per thread: they read the row's scores from TMEM,
-//   keep the running max / sum, write P, and accumulate the output row in registers
-//   (O = (O + PV_prev) * alpha), so no shuffles and no TMEM read-modify-write are needed.
+//   next block's scores are computed while the current block is in softmax) and for P V (P read from
+//   TMEM, V consumed MN-major exactly as TMA leaves it); warps 2..5 own one query row per thread: they
+//   read the row's scores from TMEM, keep the running max / sum and write the probabilities back as
+//   packed 16-bit pairs over the first half of the same score buffer, so a block's softmax never waits
+//   for the previous block's P V. O accumulates in TMEM and is rescaled lazily.
 //   Causal tiles beyond the diagonal are skipped.
 // Everything else (fp32, other head dims) runs a warp-per-query SIMT kernel in true fp32.
 #include "common.cuh"
@@ -53,11 +53,11 @@ struct FlashCfg {
     static constexpr int DB = D / 64;                 // 64-wide head-dim blocks
     static constexpr int Q_BYTES = FM * D * 2;
     static constexpr int KV_BYTES = FN * D * 2;       // one K or V tile
-    static constexpr int P_BYTES = FM * FN * 2;
-    // Two CTAs share an SM (tiles 112 KiB at D = 128), so there is no alignment slack: the kernel checks
-    // that the dynamic shared-memory window starts on a 1024-byte boundary and reports if it does not.
-    static constexpr int SMEM_BYTES = Q_BYTES + 4 * KV_BYTES + P_BYTES + 256;  // tiles + barriers
-    static constexpr int TMEM_COLS = 256;             // S0 [0,64) S1 [64,128) O [128, 128+D)
+    // Two CTAs share an SM, and the window carries no alignment slack: the kernel checks that the
+    // dynamic shared-memory window starts on a 1024-byte boundary and reports if it does not.
+    static constexpr int SMEM_BYTES = Q_BYTES + 4 * KV_BYTES + 256;  // tiles + barriers
+    // S0 [0,64) S1 [64,128) O [128, 128+D); P of block n overlays columns [0,32) of score buffer n & 1
+    static constexpr int TMEM_COLS = 256;
     static constexpr uint32_t O_COL = 128;
 };
 
@@ -102,16 +102,15 @@ flash_tc_kernel(const __grid_constant__ CUtensorMap tmq, const __grid_constant__
     uint8_t* q_s = smem;
     uint8_t* k_s = q_s + Cfg::Q_BYTES;            // [2][KV_BYTES]
     uint8_t* v_s = k_s + 2 * Cfg::KV_BYTES;       // [2][KV_BYTES]
-    uint8_t* p_s = v_s + 2 * Cfg::KV_BYTES;
-    uint64_t* bars = reinterpret_cast<uint64_t*>(p_s + Cfg::P_BYTES);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(v_s + 2 * Cfg::KV_BYTES);
     uint64_t* q_full = bars;          // 1   one phase per tile
     uint64_t* k_full = bars + 1;      // 2   the block barriers below run on per-role block counters that
     uint64_t* k_empty = bars + 3;     // 2   keep counting across the tiles of this CTA
     uint64_t* v_full = bars + 5;      // 2
     uint64_t* v_empty = bars + 7;     // 2
     uint64_t* s_full = bars + 9;      // 2
-    uint64_t* s_empty = bars + 11;    // 2
-    uint64_t* p_full = bars + 13;     // 1
+    uint64_t* o_full = bars + 11;     // 1   one phase per tile: the tile's last P V has completed
+    uint64_t* p_full = bars + 12;     // 2   a softmax warp may run one block ahead of the slowest one
     uint64_t* pv_full = bars + 14;    // 1
     uint64_t* drain_bar = bars + 15;  // 1
     uint64_t* q_empty = bars + 16;    // 1   all Q K^T of a tile have read Q
@@ -136,10 +135,11 @@ flash_tc_kernel(const __grid_constant__ CUtensorMap tmq, const __grid_constant__
             ptx::mbar_init(&v_full[s], 1);
             ptx::mbar_init(&v_empty[s], 1);
             ptx::mbar_init(&s_full[s], 1);
-            ptx::mbar_init(&s_empty[s], 128);
         }
-        ptx::mbar_init(p_full, 128);
+        ptx::mbar_init(&p_full[0], 128);
+        ptx::mbar_init(&p_full[1], 128);
         ptx::mbar_init(pv_full, 1);
+        ptx::mbar_init(o_full, 1);
         ptx::mbar_init(drain_bar, 1);
         *abort_flag = 0;
         ptx::fence_mbar_init();
@@ -200,16 +200,18 @@ flash_tc_kernel(const __grid_constant__ CUtensorMap tmq, const __grid_constant__
         if (ptx::elect_one()) {
             constexpr uint32_t idesc_s = ptx::make_idesc_f16(fmt, FM, FN, 0);
             constexpr uint32_t idesc_o = ptx::make_idesc_f16(fmt, FM, D, 1);
-            const uint32_t q_addr = ptx::smem_u32(q_s), p_addr = ptx::smem_u32(p_s);
+            const uint32_t q_addr = ptx::smem_u32(q_s);
             bool ok = true;
             uint32_t nq = 0;  // Q K^T blocks issued so far (all tiles)
             uint32_t np = 0;  // P V blocks issued so far
             uint32_t tile_n = 0;
+            // Score buffer nq & 1 is free without a barrier of its own: this thread has already waited for
+            // p_full of block nq - 2 (the softmax warps had read S and written P by then) and issued that
+            // block's P V before this point, and the tensor core runs this thread's MMAs in issue order.
             auto issue_qk = [&]() -> bool {
                 const int s = (int)(nq & 1u);
                 const uint32_t ph = (nq >> 1) & 1u;
                 if (!ptx::mbar_wait_bounded(&k_full[s], ph, abort_flag)) return false;
-                if (!ptx::mbar_wait_bounded(&s_empty[s], ph ^ 1u, abort_flag)) return false;
                 ptx::tc_fence_after();
                 const uint32_t k_addr = ptx::smem_u32(k_s + s * Cfg::KV_BYTES);
 #pragma unroll
@@ -238,19 +240,21 @@ flash_tc_kernel(const __grid_constant__ CUtensorMap tmq, const __grid_constant__
                         if (j + 2 == t.nblk) ptx::tc_commit(q_empty);  // that was the tile's last Q K^T
                     }
                     const int s = (int)(np & 1u);
-                    if (!ptx::mbar_wait_bounded(p_full, np & 1u, abort_flag)) { ok = false; break; }
+                    if (!ptx::mbar_wait_bounded(&p_full[s], (np >> 1) & 1u, abort_flag)) { ok = false; break; }
                     if (!ptx::mbar_wait_bounded(&v_full[s], (np >> 1) & 1u, abort_flag)) { ok = false; break; }
                     ptx::tc_fence_after();
                     const uint32_t v_addr = ptx::smem_u32(v_s + s * Cfg::KV_BYTES);
 #pragma unroll
                     for (int kk = 0; kk < FN / 16; ++kk) {
                         // O (+)= P V: the tile's first block overwrites, later blocks accumulate in TMEM
-                        ptx::mma_f16_ss(tmem_base + Cfg::O_COL, ptx::make_kmajor_sw128_desc(p_addr + (uint32_t)(kk * 32)),
+                        // P: 16 keys = 8 TMEM columns of packed pairs per step, in score buffer np & 1
+                        ptx::mma_f16_ts(tmem_base + Cfg::O_COL, tmem_base + (uint32_t)(s * FN + kk * 8),
                                         ptx::make_mnmajor_sw128_desc(v_addr + (uint32_t)(kk * 16 * 128), FN * 128), idesc_o,
                                         (j | kk) != 0 ? 1u : 0u);
                     }
                     ptx::tc_commit(&v_empty[s]);
                     ptx::tc_commit(pv_full);
+                    if (j + 1 == t.nblk) ptx::tc_commit(o_full);
                 }
                 if (ok && t.nblk == 0) ptx::tc_commit(q_empty);
             }
@@ -274,7 +278,8 @@ flash_tc_kernel(const __grid_constant__ CUtensorMap tmq, const __grid_constant__
         const float sl2 = p.scale * kLog2e;
         const int skv = (int)p.Skv;
         bool ok = true;
-        uint32_t n = 0;  // key blocks processed so far (all tiles)
+        uint32_t n = 0;       // key blocks processed so far (all tiles)
+        uint32_t tile_n = 0;  // tiles finished so far
 
         for (int i = 0; ok; ++i) {
             const int L = flash_tile_index(i, num_tiles);
@@ -286,7 +291,7 @@ flash_tc_kernel(const __grid_constant__ CUtensorMap tmq, const __grid_constant__
             const T* mrow = nullptr;
             if (p.mask != nullptr && row < p.Sq)
                 mrow = reinterpret_cast<const T*>(p.mask) + (int64_t)t.b * p.m_sb + (int64_t)t.h * p.m_sh + (int64_t)row * p.m_sq;
-            float m_run = -INFINITY, l_run = 0.f;
+            float m_run = -INFINITY, l_run = 0.f;  // running maximum (log2 domain, scaled) and row sum
 
             for (int j = 0; j < nblk; ++j, ++n) {
                 const int sb = (int)(n & 1u);
@@ -295,48 +300,54 @@ flash_tc_kernel(const __grid_constant__ CUtensorMap tmq, const __grid_constant__
                 ptx::tc_fence_after();
                 const uint32_t s_taddr = tmem_base + lane_field + (uint32_t)(sb * FN);
                 const int col_base = j * FN;
-                uint32_t r0[32], r1[32];
-                ptx::tmem_ld_32x32(s_taddr, r0);
-                ptx::tmem_ld_32x32(s_taddr + 32u, r1);
-                ptx::tmem_ld_wait();
-                float sc[FN];  // scores in the log2 domain
+                float sc[FN];  // raw scores; exp2(sc * mul - m) is the probability
+                {
+                    uint32_t r0[32], r1[32];
+                    ptx::tmem_ld_32x32(s_taddr, r0);
+                    ptx::tmem_ld_32x32(s_taddr + 32u, r1);
+                    ptx::tmem_ld_wait();
 #pragma unroll
-                for (int i = 0; i < 32; ++i) {
-                    sc[i] = __uint_as_float(r0[i]) * sl2;
-                    sc[32 + i] = __uint_as_float(r1[i]) * sl2;
+                    for (int i = 0; i < 32; ++i) {
+                        sc[i] = __uint_as_float(r0[i]);
+                        sc[32 + i] = __uint_as_float(r1[i]);
+                    }
                 }
-                // All of this warp's reads of the score buffer are done: the next Q K^T may overwrite it.
-                ptx::tc_fence_before();
-                ptx::mbar_arrive(&s_empty[sb]);
+                float mul = sl2;
                 const bool masked_block = (p.mask != nullptr) || (col_base + FN > skv) || (p.causal && (col_base + FN - 1 > q0));
-                if (masked_block) {  // uniform over the CTA
+                if (masked_block || !(sl2 > 0.f)) {  // uniform over the CTA; scores go to the log2 domain here
 #pragma unroll
                     for (int i = 0; i < FN; ++i) {
                         const int col = col_base + i;
+                        sc[i] *= sl2;
                         if (mrow != nullptr && col < skv) sc[i] += Cvt<T>::to_f(mrow[(int64_t)col * p.m_sk]) * kLog2e;
                         if (col >= skv || (p.causal && col > row)) sc[i] = -INFINITY;
                     }
+                    mul = 1.f;
                 }
-                // 8 independent chains instead of one 64-deep dependency chain
+                // 8 independent chains of 3-input maxima instead of one 64-deep dependency chain
                 float mxp[8];
 #pragma unroll
-                for (int i = 0; i < 8; ++i) mxp[i] = sc[i];
+                for (int i = 0; i < 8; ++i) mxp[i] = ptx::fmax3(sc[i], sc[8 + i], sc[16 + i]);
 #pragma unroll
-                for (int i = 8; i < FN; ++i) mxp[i & 7] = fmaxf(mxp[i & 7], sc[i]);
-                const float mx = fmaxf(fmaxf(fmaxf(mxp[0], mxp[1]), fmaxf(mxp[2], mxp[3])),
-                                       fmaxf(fmaxf(mxp[4], mxp[5]), fmaxf(mxp[6], mxp[7])));
+                for (int i = 24; i < FN; i += 16)
+#pragma unroll
+                    for (int c = 0; c < 8; ++c) mxp[c] = ptx::fmax3(mxp[c], sc[i + c], sc[i + 8 + c]);
+                // (i = 24: 24..39, i = 40: 40..55) leaves 56..63
+#pragma unroll
+                for (int c = 0; c < 8; ++c) mxp[c] = fmaxf(mxp[c], sc[56 + c]);
+                const float mx = ptx::fmax3(ptx::fmax3(mxp[0], mxp[1], mxp[2]), ptx::fmax3(mxp[3], mxp[4], mxp[5]),
+                                            fmaxf(mxp[6], mxp[7])) * mul;
                 const float m_new = fmaxf(m_run, mx);
                 const bool grow = m_new > m_run + kRescaleThreshold;  // also true for the first finite maximum
                 const bool warp_rescale = __any_sync(0xffffffffu, grow);
-                // P of the previous block has been consumed (and O is quiescent) once its P V has completed.
-                if (j > 0) {
-                    if (!__all_sync(0xffffffffu, ptx::mbar_wait_bounded(pv_full, (n - 1) & 1u, abort_flag))) { ok = false; break; }
-                    ptx::tc_fence_after();
-                }
                 if (warp_rescale) {
-                    const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
-                    const float alpha = ptx::ex2_approx(m_run - m_use);  // 0 when there was no finite maximum yet
+                    const float m_to = (m_new == -INFINITY) ? 0.f : m_new;
+                    const float alpha = ptx::ex2_approx(m_run - m_to);  // 0 when there was no finite maximum yet
                     if (j > 0) {
+                        // O must be quiescent: P V of the previous block has completed. s_full of this block
+                        // already implies the P V two blocks back, so the barrier is at most one phase behind.
+                        if (!__all_sync(0xffffffffu, ptx::mbar_wait_bounded(pv_full, (n - 1) & 1u, abort_flag))) { ok = false; break; }
+                        ptx::tc_fence_after();
 #pragma unroll
                         for (int c = 0; c < D / 32; ++c) {
                             uint32_t o[32];
@@ -347,34 +358,31 @@ flash_tc_kernel(const __grid_constant__ CUtensorMap tmq, const __grid_constant__
                             for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
                             ptx::tmem_st_32x32(o_taddr, o);
                         }
-                        ptx::tmem_st_wait();
                     }
                     l_run *= alpha;
                     m_run = m_new;
                 }
-                const float m_use = (m_run == -INFINITY) ? 0.f : m_run;
-                // probabilities -> shared memory (row r_in_tile of the swizzled K-major P tile)
+                const float neg_m = (m_run == -INFINITY) ? 0.f : -m_run;
+                // probabilities -> packed 16-bit pairs over columns [0, 32) of this block's score buffer
+                uint32_t pk[32];
                 float lp[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};  // independent partial row sums
 #pragma unroll
-                for (int t8 = 0; t8 < FN / 8; ++t8) {
-                    Vec16<T> pv;
-#pragma unroll
-                    for (int i = 0; i < 8; ++i) {
-                        const float pr = ptx::ex2_approx(sc[t8 * 8 + i] - m_use);
-                        lp[i] += pr;
-                        pv.v[i] = Cvt<T>::from_f(pr);
-                    }
-                    uint8_t* dst = p_s + r_in_tile * 128 + ((t8 ^ (r_in_tile & 7)) << 4);
-                    *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<const uint4*>(&pv);
+                for (int i = 0; i < FN; i += 2) {
+                    const float p0 = ptx::ex2_approx(fmaf(sc[i], mul, neg_m));
+                    const float p1 = ptx::ex2_approx(fmaf(sc[i + 1], mul, neg_m));
+                    lp[(i >> 1) & 7] += p0 + p1;
+                    pk[i >> 1] = ptx::pack2<T>(p0, p1);
                 }
                 l_run += ((lp[0] + lp[1]) + (lp[2] + lp[3])) + ((lp[4] + lp[5]) + (lp[6] + lp[7]));
-                ptx::fence_proxy_async();  // P (generic-proxy stores) must be visible to the tensor core
+                ptx::tmem_st_32x32(s_taddr, pk);
+                ptx::tmem_st_wait();  // P (and a rescaled O) are in TMEM before the P V is released
                 ptx::tc_fence_before();
-                ptx::mbar_arrive(p_full);
+                ptx::mbar_arrive(&p_full[sb]);
             }
             if (!ok) break;
             if (nblk > 0) {
-                if (!__all_sync(0xffffffffu, ptx::mbar_wait_bounded(pv_full, (n - 1) & 1u, abort_flag))) { ok = false; break; }
+                if (!__all_sync(0xffffffffu, ptx::mbar_wait_bounded(o_full, tile_n & 1u, abort_flag))) { ok = false; break; }
+                ++tile_n;
             }
             ptx::tc_fence_after();
             const float inv_l = 1.0f / l_run;
