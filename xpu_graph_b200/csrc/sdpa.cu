@@ -13,7 +13,6 @@
 #include "common.cuh"
 #include "sm100_ptx.cuh"
 
-#include <cstdlib>
 #include <type_traits>
 
 namespace xg {
@@ -94,7 +93,7 @@ __device__ __forceinline__ int flash_tile_index(int i, int num_tiles) {
     return L < num_tiles ? L : -2;
 }
 
-template <typename T, int D, int kPolyEvery>
+template <typename T, int D>
 __global__ void __launch_bounds__(kFlashThreads, 2)
 flash_tc_kernel(const __grid_constant__ CUtensorMap tmq, const __grid_constant__ CUtensorMap tmk,
                 const __grid_constant__ CUtensorMap tmv, const SdpaParams p) {
@@ -364,9 +363,7 @@ flash_tc_kernel(const __grid_constant__ CUtensorMap tmq, const __grid_constant__
                     m_run = m_new;
                 }
                 const float neg_m = (m_run == -INFINITY) ? 0.f : -m_run;
-                // probabilities -> packed 16-bit pairs over columns [0, 32) of this block's score buffer.
-                // One pair in kPolyEvery takes its exponentials on the FMA pipe (the special-function unit
-                // is as loaded as the tensor core at this tile shape).
+                // probabilities -> packed 16-bit pairs over columns [0, 32) of this block's score buffer
                 uint32_t pk[32];
                 float lp[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};  // independent partial row sums (4 pairs)
 #pragma unroll
@@ -374,12 +371,8 @@ flash_tc_kernel(const __grid_constant__ CUtensorMap tmq, const __grid_constant__
                     float x0, x1, p0, p1;
                     ptx::fma2(x0, x1, sc[i], sc[i + 1], mul, mul, neg_m, neg_m);
                     const int pair = i >> 1;
-                    if (kPolyEvery > 0 && (pair % (kPolyEvery > 0 ? kPolyEvery : 1)) == (kPolyEvery - 1)) {
-                        ptx::ex2_poly2(p0, p1, x0, x1);
-                    } else {
-                        p0 = ptx::ex2_approx(x0);
-                        p1 = ptx::ex2_approx(x1);
-                    }
+                    p0 = ptx::ex2_approx(x0);
+                    p1 = ptx::ex2_approx(x1);
                     ptx::add2(lp[2 * (pair & 3)], lp[2 * (pair & 3) + 1], lp[2 * (pair & 3)], lp[2 * (pair & 3) + 1], p0, p1);
                     pk[pair] = ptx::pack2<T>(p0, p1);
                 }
@@ -432,8 +425,8 @@ flash_tc_kernel(const __grid_constant__ CUtensorMap tmq, const __grid_constant__
     }
 }
 
-template <typename T, int D, int POLY>
-int launch_flash_tc_v(const SdpaParams& p, cudaStream_t st) {
+template <typename T, int D>
+int launch_flash_tc(const SdpaParams& p, cudaStream_t st) {
     using Cfg = FlashCfg<D>;
     constexpr bool is_bf16 = std::is_same<T, __nv_bfloat16>::value;
     CUtensorMap tq, tk, tv;
@@ -441,7 +434,7 @@ int launch_flash_tc_v(const SdpaParams& p, cudaStream_t st) {
         !make_tmap_bhsd_16bit(&tk, p.k, p.B, p.H, p.Skv, D, p.k_sb, p.k_sh, p.k_ss, FN, is_bf16) ||
         !make_tmap_bhsd_16bit(&tv, p.v, p.B, p.H, p.Skv, D, p.v_sb, p.v_sh, p.v_ss, FN, is_bf16))
         return fail(XG_ERR_UNSUPPORTED, "xg_sdpa_fwd: tensor-map encoding failed (strides must be multiples of 8 elements)");
-    auto kern = flash_tc_kernel<T, D, POLY>;
+    auto kern = flash_tc_kernel<T, D>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
     if (e != cudaSuccess) {
         cudaGetLastError();
@@ -454,21 +447,6 @@ int launch_flash_tc_v(const SdpaParams& p, cudaStream_t st) {
     const unsigned grid = (unsigned)(pairs < resident ? pairs : resident);
     kern<<<grid, kFlashThreads, Cfg::SMEM_BYTES, st>>>(tq, tk, tv, p);
     return check_launch("xg_sdpa_fwd");
-}
-
-template <typename T, int D>
-int launch_flash_tc(const SdpaParams& p, cudaStream_t st) {
-    static const int poly = [] {
-        const char* e = getenv("XG_SDPA_POLY");
-        return e ? atoi(e) : 0;
-    }();
-    switch (poly) {
-        case 0: return launch_flash_tc_v<T, D, 0>(p, st);
-        case 2: return launch_flash_tc_v<T, D, 2>(p, st);
-        case 3: return launch_flash_tc_v<T, D, 3>(p, st);
-        case 4: return launch_flash_tc_v<T, D, 4>(p, st);
-        default: return launch_flash_tc_v<T, D, 0>(p, st);
-    }
 }
 
 // ---------------------------------------------------------------------------------------

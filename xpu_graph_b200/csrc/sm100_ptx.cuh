@@ -59,21 +59,6 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
     return ok != 0;
 }
 
-// Same, letting the hardware park the thread for up to `hint_ns` while the phase is incomplete.
-__device__ __forceinline__ bool mbar_try_wait_hint(uint64_t* bar, uint32_t parity, uint32_t hint_ns) {
-    uint32_t ok;
-    asm volatile(
-        "{\n\t"
-        ".reg .pred P;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 P, [%1], %2, %3;\n\t"
-        "selp.u32 %0, 1, 0, P;\n\t"
-        "}\n"
-        : "=r"(ok)
-        : "r"(smem_u32(bar)), "r"(parity), "r"(hint_ns)
-        : "memory");
-    return ok != 0;
-}
-
 // Wait for the phase with the given parity to complete, for at most `limit_ns`. `abort_flag`
 // (shared memory) is polled so that one role's time-out releases the others quickly.
 constexpr uint64_t kWaitLimitNs = 2000000000ull;  // 2 s
@@ -227,35 +212,6 @@ __device__ __forceinline__ void add2(float& d0, float& d1, float a0, float a1, f
         "}\n"
         : "=f"(d0), "=f"(d1)
         : "f"(a0), "f"(a1), "f"(b0), "f"(b1));
-}
-// Same sum rounded towards minus infinity (used to take floor() with the 1.5 * 2^23 trick).
-__device__ __forceinline__ void add2_rm(float& d0, float& d1, float a0, float a1, float b0, float b1) {
-    asm("{\n\t"
-        ".reg .b64 ra, rb, rd;\n\t"
-        "mov.b64 ra, {%2, %3};\n\t"
-        "mov.b64 rb, {%4, %5};\n\t"
-        "add.rm.f32x2 rd, ra, rb;\n\t"
-        "mov.b64 {%0, %1}, rd;\n\t"
-        "}\n"
-        : "=f"(d0), "=f"(d1)
-        : "f"(a0), "f"(a1), "f"(b0), "f"(b1));
-}
-// 2^x for a pair, on the FMA and integer pipes instead of the special-function unit: x = floor(x) + f,
-// 2^f from a cubic fitted on [0, 1) (relative error below 8e-5, well under the 16-bit rounding of the
-// result's consumers), the integer part added into the exponent field. Arguments below -126 give 2^-126.
-__device__ __forceinline__ void ex2_poly2(float& y0, float& y1, float x0, float x1) {
-    constexpr float kMagic = 12582912.f;  // 1.5 * 2^23: one ulp is 1, so a round-down add takes the floor
-    x0 = fmaxf(x0, -126.f);
-    x1 = fmaxf(x1, -126.f);
-    float r0, r1, i0, i1, f0, f1, p0, p1;
-    add2_rm(r0, r1, x0, x1, kMagic, kMagic);
-    add2(i0, i1, r0, r1, -kMagic, -kMagic);
-    add2(f0, f1, x0, x1, -i0, -i1);
-    fma2(p0, p1, f0, f1, 0.07802402973175049f, 0.07802402973175049f, 0.22606706619262695f, 0.22606706619262695f);
-    fma2(p0, p1, p0, p1, f0, f1, 0.6958339810371399f, 0.6958339810371399f);
-    fma2(p0, p1, p0, p1, f0, f1, 0.9999251365661621f, 0.9999251365661621f);
-    y0 = __int_as_float(__float_as_int(p0) + (__float_as_int(r0) << 23));
-    y1 = __int_as_float(__float_as_int(p1) + (__float_as_int(r1) << 23));
 }
 // max of three (one instruction on sm_100)
 __device__ __forceinline__ float fmax3(float a, float b, float c) {
