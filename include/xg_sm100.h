@@ -251,6 +251,21 @@ int xg_gather_rows(const void* const* tables, const int64_t* table_rows, int64_t
 int xg_sum3d(const void* const* inputs, void* const* outputs, const int64_t* shapes3, int64_t n, int dim,
              int dtype, void* stream);
 
+/*
+ * Row reductions written side by side: out[b, k*C + c] = sum over r in [r0_k, r1_k) of
+ * a_k[b, r, c] * (b_ptrs ? b_k[b, r, c] : 1) for k = 0..n-1. a_k / b_k are contiguous [*, R_k, C] tensors addressed
+ * as base + b * batch_stride + r * C + c (a batch stride of 0 broadcasts one slab over the batch); row_ranges2 =
+ * HOST array [n][2] of (r0, r1); a_ptrs / b_ptrs / strides: HOST arrays. out: [B, out_ld] with out_ld >= n*C.
+ * fp32 accumulation. When all segments read one tensor from the same first row every input row is read once.
+ * Replaces: targets/mlu/triton_kernel/fused_slice_sum_cat.py (fuse_slice_sum_cat) as called by
+ * targets/mlu/fuse_sum_cat.py:76-115 (SliceSumCatOperation, pattern FusedCatSum :242-252), and
+ * targets/mlu/triton_kernel/fused_mul_sum_cat.py (fused_mul_sum_cat_2inp) as called by
+ * targets/mlu/fuse_mul_sum_cat.py:16-50 (FusedMulSumCatReplacement, pattern FusedMulSumCat :97-123).
+ */
+int xg_rowsum_cat(const void* const* a_ptrs, const void* const* b_ptrs, const int64_t* a_batch_strides,
+                  const int64_t* b_batch_strides, const int64_t* row_ranges2, int64_t n, int64_t B, int64_t C,
+                  void* out, int64_t out_ld, int dtype, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -208,3 +208,20 @@ def combo_sum(inputs, dim):
     (passes/patterns/structure/fuse_combosum.py:82-98)."""
     d = dim[0] if isinstance(dim, (list, tuple)) else dim
     return [x.sum(dim=d) for x in inputs]
+
+
+def slice_sum_cat(src, slices):
+    """cat([src[:, s:e, :].sum(1)], -1): the eager graph that targets/mlu/fuse_sum_cat.py:120-252 rewrites (and the
+    fallback branch of SliceSumCatOperation.forward, :104-111)."""
+    return torch.cat([src[:, s:e, :].sum(dim=1) for s, e in slices], dim=-1)
+
+
+def sum_cat(inputs):
+    """cat([x.sum(1)], -1) over different tensors (targets/mlu/fuse_sum_cat.py:20-43)."""
+    return torch.cat([x.sum(dim=1) for x in inputs], dim=-1)
+
+
+def mul_sum_cat(mul_list):
+    """cat([(a_i * b_i).sum(1)], -1) with mul_list = [a_0, b_0, a_1, b_1, ...], batch broadcast allowed
+    (targets/mlu/fuse_mul_sum_cat.py:16-50)."""
+    return torch.cat([(mul_list[i] * mul_list[i + 1]).sum(dim=1) for i in range(0, len(mul_list), 2)], dim=-1)

@@ -88,4 +88,14 @@ def register():
 
     k(ops.gather_stack)(gather_stack)
     k(ops.sum3d)(lambda inputs, dim: ref_ops.combo_sum(inputs, dim))
+    k(ops.slice_sum_cat)(lambda src, starts, ends: ref_ops.slice_sum_cat(src, list(zip(starts, ends))))
+    k(ops.sum_cat)(lambda inputs: ref_ops.sum_cat(inputs))
+
+    def mul_sum_cat(lhs, rhs):
+        ml = []
+        for a, b in zip(lhs, rhs):
+            ml += [a, b]
+        return ref_ops.mul_sum_cat(ml)
+
+    k(ops.mul_sum_cat)(mul_sum_cat)
     _DONE = True

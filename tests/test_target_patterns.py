@@ -287,6 +287,32 @@ def test_combo_sum_after_multi_slice_cat(tgt, xlog):
     assert "combo_sum" in mods and not any("sum" in a for a in atens)
 
 
+def test_sum_cat_fusions(tgt, xlog):
+    """slice -> sum -> cat, mul -> sum -> cat and sum -> cat along the last dim become one module call each
+    (graph forms of targets/mlu/fuse_sum_cat.py and fuse_mul_sum_cat.py; the reference's tests
+    tests/mlu/test_fuse_sum_cat.py / test_mul_sum_cat.py compare compiled vs eager the same way)."""
+    g = torch.Generator().manual_seed(8)
+    x = torch.randn(6, 40, 16, generator=g)
+    a = [torch.randn(6, 5, 8, generator=g) for _ in range(3)]
+    b = [torch.randn(1 if i == 1 else 6, 5, 8, generator=g) for i in range(3)]
+    y = [torch.randn(6, r, 8, generator=g) for r in (3, 7, 4)]
+
+    def fn(x, a0, a1, a2, b0, b1, b2, y0, y1, y2):
+        s = torch.cat([x[:, 0:10, :].sum(dim=1), x[:, 0:25, :].sum(dim=1), x[:, 0:4, :].sum(dim=1), x[:, 8:40, :].sum(dim=1)], dim=-1)
+        m = torch.cat([(a0 * b0).sum(dim=1), (a1 * b1).sum(dim=1), (a2 * b2).sum(dim=1)], dim=-1)
+        c = torch.cat([y0.sum(dim=1), y1.sum(dim=1), y2.sum(dim=1)], dim=-1)
+        return s * 2.0, m + 1.0, c - 1.0
+
+    want, got, mods, atens = _compile(tgt, fn, x, *a, *b, *y)
+    for w, o in zip(want, got):
+        _same(o, w, 1e-5)
+    assert "Pattern.FusedSliceSumCat changed graph" in xlog.text
+    assert "Pattern.FusedMulSumCat changed graph" in xlog.text
+    assert "Pattern.FusedSumCat changed graph" in xlog.text
+    assert any(m.startswith("xg_slice_sum_cat") for m in mods) and "xg_mul_sum_cat" in mods and "xg_sum_cat" in mods
+    assert not any("sum" in t or "cat" in t or "slice" in t for t in atens)
+
+
 def test_compile_cache_round_trip(tgt, xlog, tmp_path):
     """The compile cache (cache.py:113-179, 270-326) pickles the rewritten graph with the target's sub-modules and
     custom-op nodes; a second compilation of the same graph loads the artifact instead of re-running the passes

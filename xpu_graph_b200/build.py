@@ -27,6 +27,7 @@ SOURCES = [
     "gemm_f32.cu",
     "sdpa.cu",
     "sum3d.cu",
+    "rowsum_cat.cu",
 ]
 
 NVCC_FLAGS = [

@@ -102,7 +102,7 @@ def main(argv=None):
     X = torch.ops.xg_sm100
     ap = argparse.ArgumentParser()
     ap.add_argument("case", choices=["sweep", "gemm_splitk", "gemm", "gemm_swiglu", "gemm_small_m", "add_rms_norm", "layer_norm", "sdpa", "rope", "swiglu",
-                                     "gather", "slice_cat", "gemm_f32"])
+                                     "gather", "slice_cat", "gemm_f32", "slice_sum_cat", "mul_sum_cat"])
     ap.add_argument("--iters", type=int, default=3)
     args = ap.parse_args(argv)
     if args.case == "sweep":
@@ -187,6 +187,18 @@ def main(argv=None):
         mask = torch.rand(rows, 1, generator=g, device=dev) < 0.3
         ms = _time(lambda: X.gather_stack(tables, idx, mask, True), args.iters)
         print(f"gather_stack {rows}x{F}x{D}: {ms:.4f} ms, {(2 * rows * F * D * 4 + rows * F * 8) / ms / 1e6:.0f} GB/s")
+    elif args.case == "slice_sum_cat":
+        B, R, C = 65536, 50, 64
+        x = rn(B, R, C, dtype=torch.float32)
+        starts, ends = [0, 0, 0, 0], [10, 25, 50, 4]
+        ms = _time(lambda: X.slice_sum_cat(x, starts, ends), args.iters)
+        print(f"slice_sum_cat {B}x{R}x{C} fp32, 4 prefix ranges: {ms:.4f} ms, {(B * R * C + B * 4 * C) * 4 / ms / 1e6:.0f} GB/s")
+    elif args.case == "mul_sum_cat":
+        B, R, C, n = 65536, 10, 64, 4
+        lhs = [rn(B, R, C, dtype=torch.float32) for _ in range(n)]
+        rhs = [rn(B, R, C, dtype=torch.float32) for _ in range(n)]
+        ms = _time(lambda: X.mul_sum_cat(lhs, rhs), args.iters)
+        print(f"mul_sum_cat {n} x {B}x{R}x{C} fp32: {ms:.4f} ms, {(2 * n * B * R * C + B * n * C) * 4 / ms / 1e6:.0f} GB/s")
     elif args.case == "slice_cat":
         rows, width = 65536, 4310
         src = rn(rows, width, dtype=torch.float32)

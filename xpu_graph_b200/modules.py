@@ -272,6 +272,35 @@ class ComboSumModule(torch.nn.Module):
         return _X.sum3d(list(input_list), int(d))
 
 
+class SliceSumCatModule(torch.nn.Module):
+    """slice(dim 1) -> sum(dim 1) -> cat(dim -1) of one [B, R, C] tensor in one pass: M(slice_param)(input) with
+    slice_param = [(start, end), ...], the interface of targets/mlu/fuse_sum_cat.py:76-115 (SliceSumCatOperation)."""
+
+    def __init__(self, slice_param):
+        super().__init__()
+        self.starts = [int(s) for s, _ in slice_param]
+        self.ends = [int(e) for _, e in slice_param]
+
+    def forward(self, input):
+        return _X.slice_sum_cat(input, self.starts, self.ends)
+
+
+class SumCatModule(torch.nn.Module):
+    """sum(dim 1) -> cat(dim -1) of several [B, R_k, C] tensors (targets/mlu/fuse_sum_cat.py:20-43,
+    ConcatenateSumOperation2): forward(inputs)."""
+
+    def forward(self, inputs):
+        return _X.sum_cat(list(inputs))
+
+
+class MulSumCatModule(torch.nn.Module):
+    """cat([sum(a_i * b_i, dim 1)], dim -1): forward(mul_list) with mul_list = [a_0, b_0, a_1, b_1, ...], the interface
+    of targets/mlu/fuse_mul_sum_cat.py:16-50 (FusedMulSumCatReplacement); operands may broadcast over the batch."""
+
+    def forward(self, mul_list):
+        return _X.mul_sum_cat(list(mul_list[0::2]), list(mul_list[1::2]))
+
+
 def get_structure_replacements(config=None) -> dict:
     """Structure-pattern name -> module (or (module, constraint_fn)), the dict that
     passes/patterns/targets/__init__.py:13-27 normalises."""

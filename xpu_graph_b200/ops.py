@@ -632,3 +632,83 @@ def _(inputs, dim):
         oshape = (s1, s2) if dim == 0 else ((s0, s2) if dim == 1 else (s0, s1))
         outs.append(torch.empty(oshape, dtype=x.dtype, device=x.device))
     return outs
+
+
+# ---- row sums written side by side -----------------------------------------------------------------
+def _rowsum_cat_impl(a_list, b_list, ranges, batch):
+    a0 = a_list[0]
+    C = a0.shape[-1]
+    n = len(a_list)
+    xs, ys, a_bs, b_bs = [], [], [], []
+    for k in range(n):
+        a = a_list[k].contiguous()
+        if a.dim() != 3 or a.shape[-1] != C or a.dtype != a0.dtype or a.shape[0] not in (1, batch):
+            raise ValueError("xg_sm100::rowsum_cat: operands must be [batch or 1, rows, C] tensors of one dtype")
+        xs.append(a)
+        a_bs.append(0 if a.shape[0] == 1 and batch != 1 else a.shape[1] * C)
+        if b_list is not None:
+            b = b_list[k].contiguous()
+            if b.dim() != 3 or b.shape[1:] != a.shape[1:] or b.dtype != a0.dtype or b.shape[0] not in (1, batch):
+                raise ValueError("xg_sm100::rowsum_cat: second operands must match the first in rows, C and dtype")
+            ys.append(b)
+            b_bs.append(0 if b.shape[0] == 1 and batch != 1 else b.shape[1] * C)
+        r0, r1 = ranges[2 * k], ranges[2 * k + 1]
+        if not (0 <= r0 <= r1 <= a.shape[1]):
+            raise ValueError("xg_sm100::rowsum_cat: row range outside the operand")
+    out = torch.empty((batch, n * C), dtype=a0.dtype, device=a0.device)
+    rc = _lib.load().xg_rowsum_cat(
+        _lib.ptr_array([x.data_ptr() for x in xs]), _lib.ptr_array([y.data_ptr() for y in ys]) if b_list is not None else None,
+        _lib.i64_array(a_bs), _lib.i64_array(b_bs) if b_list is not None else None, _lib.i64_array(list(ranges)), n,
+        batch, C, out.data_ptr(), n * C, _code(a0.dtype), _stream(a0))
+    _lib.check(rc, "xg_rowsum_cat")
+    _bump()
+    return out
+
+
+@torch.library.custom_op(f"{NS}::slice_sum_cat", mutates_args=(), device_types="cuda")
+def slice_sum_cat(src: torch.Tensor, starts: List[int], ends: List[int]) -> torch.Tensor:
+    """cat([src[:, s:e, :].sum(1) for s, e in zip(starts, ends)], -1) for a [B, R, C] tensor."""
+    if src.dim() != 3:
+        raise ValueError("xg_sm100::slice_sum_cat expects a 3-D tensor")
+    R = src.shape[1]
+    ranges = []
+    for s0, e0 in zip(starts, ends):  # aten.slice clamping
+        s1 = min(max(s0 + R if s0 < 0 else s0, 0), R)
+        e1 = min(max(e0 + R if e0 < 0 else e0, 0), R)
+        ranges += [s1, max(e1, s1)]
+    return _rowsum_cat_impl([src] * len(starts), None, ranges, src.shape[0])
+
+
+@slice_sum_cat.register_fake
+def _(src, starts, ends):
+    return torch.empty((src.shape[0], len(starts) * src.shape[2]), dtype=src.dtype, device=src.device)
+
+
+@torch.library.custom_op(f"{NS}::sum_cat", mutates_args=(), device_types="cuda")
+def sum_cat(inputs: List[torch.Tensor]) -> torch.Tensor:
+    """cat([x.sum(1) for x in inputs], -1) for [B, R_k, C] tensors."""
+    ranges = []
+    for x in inputs:
+        ranges += [0, x.shape[1]]
+    return _rowsum_cat_impl(list(inputs), None, ranges, inputs[0].shape[0])
+
+
+@sum_cat.register_fake
+def _(inputs):
+    return torch.empty((inputs[0].shape[0], len(inputs) * inputs[0].shape[2]), dtype=inputs[0].dtype, device=inputs[0].device)
+
+
+@torch.library.custom_op(f"{NS}::mul_sum_cat", mutates_args=(), device_types="cuda")
+def mul_sum_cat(lhs: List[torch.Tensor], rhs: List[torch.Tensor]) -> torch.Tensor:
+    """cat([(a * b).sum(1) for a, b in zip(lhs, rhs)], -1) for [B or 1, R, C] tensors (batch broadcast)."""
+    batch = max(max(a.shape[0], b.shape[0]) for a, b in zip(lhs, rhs))
+    ranges = []
+    for a in lhs:
+        ranges += [0, a.shape[1]]
+    return _rowsum_cat_impl(list(lhs), list(rhs), ranges, batch)
+
+
+@mul_sum_cat.register_fake
+def _(lhs, rhs):
+    batch = max(max(a.shape[0], b.shape[0]) for a, b in zip(lhs, rhs))
+    return torch.empty((batch, len(lhs) * lhs[0].shape[2]), dtype=lhs[0].dtype, device=lhs[0].device)

@@ -68,6 +68,14 @@ def _ensure(gm: fx.GraphModule, name: str, factory) -> str:
     return name
 
 
+def _unique(gm: fx.GraphModule, stem: str) -> str:
+    """A sub-module name not yet used by `gm` (for modules that carry per-site parameters)."""
+    i = 0
+    while hasattr(gm, f"{stem}_{i}"):
+        i += 1
+    return f"{stem}_{i}"
+
+
 def _fill_meta(gm: fx.GraphModule, node: fx.Node) -> None:
     """Give a freshly inserted node its fake value right away (the pass runs under the compiler's fake
     mode), so that later patterns of the same sweep can inspect it; on any problem the value is left
@@ -637,7 +645,194 @@ class FusedCatLastDim(Pattern):
         return changed
 
 
-ALL_PATTERNS = [FusedNativeLayerNorm, FusedSdpa, FusedRoPE, FusedEmbeddingStack, FusedSwiGLU, FusedDenseResidual,
+# ---- row sums written side by side ------------------------------------------------------------------------------
+def _sum_dim1(node) -> bool:
+    """aten.sum.dim_IntList(x, [1]) of a 3-D tensor without keepdim."""
+    if not _is(node, aten.sum.dim_IntList) or len(node.args) < 2 or len(node.args) > 2 or node.kwargs:
+        return False
+    v = _val(node.args[0])
+    return list(node.args[1]) == [1] and _tensor_ok(v, 3) and _static(v.shape)
+
+
+def _replace_run(gm: fx.GraphModule, cat: fx.Node, lo: int, hi: int, new: fx.Node) -> None:
+    """Inputs lo..hi (inclusive) of the last-dim cat are replaced by `new`; a cat of one input disappears."""
+    parts = list(cat.args[0])
+    rest = parts[:lo] + [new] + parts[hi + 1:]
+    if len(rest) == 1:
+        cat.replace_all_uses_with(new)
+    else:
+        with gm.graph.inserting_before(cat):
+            new_cat = gm.graph.call_function(aten.cat.default, (rest, -1))
+        _fill_meta(gm, new_cat)
+        cat.replace_all_uses_with(new_cat)
+    gm.graph.erase_node(cat)
+    for old in parts[lo:hi + 1]:
+        chain = [old]
+        while chain:
+            n = chain.pop()
+            if isinstance(n, fx.Node) and len(n.users) == 0 and n.op == "call_function":
+                chain.extend(a for a in n.args if isinstance(a, fx.Node))
+                gm.graph.erase_node(n)
+
+
+def _last_dim_cat(node):
+    if not _is(node, aten.cat.default):
+        return None
+    parts = node.args[0]
+    dim = node.args[1] if len(node.args) > 1 else 0
+    vals = [_val(q) for q in parts]
+    if len(parts) < 2 or not all(isinstance(v, torch.Tensor) and v.dim() == 2 for v in vals) or dim not in (-1, 1):
+        return None
+    return list(parts)
+
+
+class FusedSliceSumCat(Pattern):
+    """cat([x[:, s_k:e_k, :].sum(1) ...], -1) over one 3-D tensor -> SliceSumCatModule: every row of x is read once
+    (the graph form of targets/mlu/fuse_sum_cat.py:120-252; any start row, two or more slices)."""
+
+    _opt_level = OptLevel.level2
+    _pattern_group = PatternGroup.GROUP0
+
+    def process(self, gm: fx.GraphModule) -> bool:
+        changed = False
+        for cat in list(gm.graph.nodes):
+            parts = _last_dim_cat(cat)
+            if parts is None:
+                continue
+
+            def src_of(q):
+                if not (_sum_dim1(q) and _only_user(q, cat)):
+                    return None
+                sl = q.args[0]
+                if not (_is(sl, aten.slice.Tensor) and _only_user(sl, q) and len(sl.args) >= 4 and sl.args[1] == 1):
+                    return None
+                if len(sl.args) > 4 and sl.args[4] != 1:
+                    return None
+                if not (isinstance(sl.args[2], int) and isinstance(sl.args[3], int)):
+                    return None
+                v = _val(sl.args[0])
+                return sl.args[0] if _tensor_ok(v, 3) and _static(v.shape) else None
+
+            i = 0
+            while i < len(parts):
+                src = src_of(parts[i])
+                j = i
+                while src is not None and j + 1 < len(parts) and src_of(parts[j + 1]) is src:
+                    j += 1
+                if src is None or j == i:
+                    i += 1
+                    continue
+                params = [(q.args[0].args[2], q.args[0].args[3]) for q in parts[i:j + 1]]
+                name = _unique(gm, "xg_slice_sum_cat")
+                gm.add_submodule(name, M.SliceSumCatModule(params))
+                with gm.graph.inserting_before(cat):
+                    new = gm.graph.call_module(name, (src,))
+                _fill_meta(gm, new)
+                _replace_run(gm, cat, i, j, new)
+                changed = True
+                break  # the cat node is gone; later runs are found on the next sweep
+        return changed
+
+
+class FusedSumCat(Pattern):
+    """cat([x_k.sum(1) ...], -1) over different [B, R_k, C] tensors -> SumCatModule (the graph form served by
+    ConcatenateSumOperation2, targets/mlu/fuse_sum_cat.py:20-43)."""
+
+    _opt_level = OptLevel.level2
+    _pattern_group = PatternGroup.GROUP0
+
+    def process(self, gm: fx.GraphModule) -> bool:
+        changed = False
+        for cat in list(gm.graph.nodes):
+            parts = _last_dim_cat(cat)
+            if parts is None:
+                continue
+
+            def ok(q, ref):
+                if not (_sum_dim1(q) and _only_user(q, cat)) or _is(q.args[0], aten.slice.Tensor, aten.mul.Tensor):
+                    return False
+                v = _val(q.args[0])
+                return ref is None or (v.shape[0] == ref.shape[0] and v.shape[2] == ref.shape[2] and v.dtype == ref.dtype)
+
+            i = 0
+            while i < len(parts):
+                if not ok(parts[i], None):
+                    i += 1
+                    continue
+                ref = _val(parts[i].args[0])
+                j = i
+                while j + 1 < len(parts) and ok(parts[j + 1], ref):
+                    j += 1
+                if j == i:
+                    i += 1
+                    continue
+                _ensure(gm, "xg_sum_cat", M.SumCatModule)
+                with gm.graph.inserting_before(cat):
+                    new = gm.graph.call_module("xg_sum_cat", ([q.args[0] for q in parts[i:j + 1]],))
+                _fill_meta(gm, new)
+                _replace_run(gm, cat, i, j, new)
+                changed = True
+                break
+        return changed
+
+
+class FusedMulSumCat(Pattern):
+    """cat([(a_k * b_k).sum(1) ...], -1) -> MulSumCatModule (the graph form of targets/mlu/fuse_mul_sum_cat.py:53-123);
+    a_k / b_k are [B or 1, R, C] tensors of one shape apart from the batch."""
+
+    _opt_level = OptLevel.level2
+    _pattern_group = PatternGroup.GROUP0
+
+    def process(self, gm: fx.GraphModule) -> bool:
+        changed = False
+        for cat in list(gm.graph.nodes):
+            parts = _last_dim_cat(cat)
+            if parts is None:
+                continue
+
+            def ok(q, ref):
+                if not (_is(q, aten.sum.dim_IntList) and len(q.args) == 2 and list(q.args[1]) == [1] and _only_user(q, cat)):
+                    return False
+                mul = q.args[0]
+                if not (_is(mul, aten.mul.Tensor) and _only_user(mul, q)):
+                    return False
+                va, vb = _val(mul.args[0]), _val(mul.args[1])
+                if not (_tensor_ok(va, 3) and _tensor_ok(vb, 3) and _static(va.shape) and _static(vb.shape)):
+                    return False
+                if va.shape[1:] != vb.shape[1:] or va.dtype != vb.dtype:
+                    return False
+                batch = max(va.shape[0], vb.shape[0])
+                if va.shape[0] not in (1, batch) or vb.shape[0] not in (1, batch):
+                    return False
+                return ref is None or (batch == ref[0] and va.shape[2] == ref[1] and va.dtype == ref[2])
+
+            i = 0
+            while i < len(parts):
+                if not ok(parts[i], None):
+                    i += 1
+                    continue
+                va, vb = (_val(a) for a in parts[i].args[0].args[:2])
+                ref = (max(va.shape[0], vb.shape[0]), va.shape[2], va.dtype)
+                j = i
+                while j + 1 < len(parts) and ok(parts[j + 1], ref):
+                    j += 1
+                if j == i:
+                    i += 1
+                    continue
+                mul_list = []
+                for q in parts[i:j + 1]:
+                    mul_list += [q.args[0].args[0], q.args[0].args[1]]
+                _ensure(gm, "xg_mul_sum_cat", M.MulSumCatModule)
+                with gm.graph.inserting_before(cat):
+                    new = gm.graph.call_module("xg_mul_sum_cat", (mul_list,))
+                _fill_meta(gm, new)
+                _replace_run(gm, cat, i, j, new)
+                changed = True
+                break
+        return changed
+
+
+ALL_PATTERNS = [FusedSliceSumCat, FusedMulSumCat, FusedSumCat, FusedNativeLayerNorm, FusedSdpa, FusedRoPE, FusedEmbeddingStack, FusedSwiGLU, FusedDenseResidual,
                 FusedAddNorm, FusedCatLastDim, FusedDenseRope]
 
 
