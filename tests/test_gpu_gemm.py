@@ -118,6 +118,61 @@ def test_dense_fp32(cuda_device, M, K, N, act, weight_trans):
     assert_parity(got, want, f"dense fp32 {M}x{K}x{N} {act}")
 
 
+@pytest.mark.parametrize("weight_trans", [True, False])
+@pytest.mark.parametrize("M,K,N,act,with_res", [(2048, 512, 1024, "relu", False), (1100, 1000, 520, "gelu", True),
+                                                (4096, 1728, 1024, "none", False), (300, 4100, 450, "sigmoid", True)])
+def test_dense_fp32_on_tensor_cores(cuda_device, M, K, N, act, with_res, weight_trans):
+    """fp32 dense layers of at least 2^30 FLOPs run from three bf16 planes per operand on the tensor cores: the result
+    must stay within the fp32 tolerance of fp64 math (ragged M / N / K, both weight layouts, bias + residual + act)."""
+    from xpu_graph_b200 import lib, ops
+
+    assert ops._f32_on_tensor_cores(M, N, K)
+    x, w, b = _mk(M, K, N, torch.float32, 26, weight_trans)
+    r = torch.randn(M, N, generator=torch.Generator().manual_seed(27)) if with_res else None
+    launches = ops.launch_count()
+    got = torch.ops.xg_sm100.dense(x.to(cuda_device), w.to(cuda_device), weight_trans, b.to(cuda_device),
+                                   r.to(cuda_device) if with_res else None, act)
+    torch.cuda.synchronize()
+    assert ops.launch_count() - launches >= 3  # operand split(s), the tensor-core GEMM, the fp32 epilogue
+    assert lib.tc_status() == 0
+    y = x.double() @ (w.double().t() if weight_trans else w.double()) + b.double()
+    if with_res:
+        y = y + r.double()
+    want = ref_ops._ACTS[act](y).float()
+    assert_parity(got, want, f"dense fp32 (bf16 planes) {M}x{K}x{N} {act}")
+
+
+def test_split_bf16x3_planes_add_up(cuda_device):
+    """x0 + x1 + x2 reproduces x to 2^-24 relative; padding columns are zero; the transposed form agrees."""
+    from xpu_graph_b200 import lib
+
+    L = lib.load()
+    g = torch.Generator().manual_seed(28)
+    x = (torch.randn(37, 100, generator=g) * torch.logspace(-20, 20, 100)).to(cuda_device)
+    Kp = int(L.xg_gemm_f32x3_padded_k(100))
+    assert Kp == 128
+    out = torch.full((37, 3 * Kp), 7.0, dtype=torch.bfloat16, device=cuda_device)
+    assert L.xg_split_bf16x3(x.data_ptr(), 37, 100, 100, 0, out.data_ptr(), None) == 0
+    planes = out.view(37, 3, Kp).float()
+    assert torch.all(planes[:, :, 100:] == 0)
+    back = planes[:, 0, :100].double() + planes[:, 1, :100].double() + planes[:, 2, :100].double()
+    assert ((back - x.double()).abs() <= x.double().abs() * 2.0 ** -24).all()
+    xt = x.t().contiguous()  # [K, rows]
+    out_t = torch.empty_like(out)
+    assert L.xg_split_bf16x3(xt.data_ptr(), 37, 100, 37, 1, out_t.data_ptr(), None) == 0
+    assert torch.equal(out_t, out)
+
+
+def test_dense_fp32_weight_planes_follow_the_weight(cuda_device):
+    """The bf16 planes of a weight are kept between calls; an in-place update of the weight must not reuse them."""
+    x, w, b = _mk(2048, 512, 1024, torch.float32, 29)
+    x, w = x.to(cuda_device), w.to(cuda_device)
+    y1 = torch.ops.xg_sm100.dense(x, w, True, None, None, "none")
+    w.mul_(2.0)
+    y2 = torch.ops.xg_sm100.dense(x, w, True, None, None, "none")
+    assert_parity(y2, (y1 * 2.0), "dense fp32 after an in-place weight update")
+
+
 def test_dense_swiglu(cuda_device):
     from xpu_graph_b200 import lib
     from xpu_graph_b200.modules import DenseSwiGLUModule

@@ -25,6 +25,7 @@ SOURCES = [
     "gemm.cu",
     "gemm_tc.cu",
     "gemm_f32.cu",
+    "split_bf16x3.cu",
     "sdpa.cu",
     "sum3d.cu",
     "rowsum_cat.cu",

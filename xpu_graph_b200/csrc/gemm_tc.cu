@@ -112,8 +112,24 @@ struct GemmParams {
     int64_t rope_S;
     int rope_D;
     int splits;      // > 1: split-K, every (tile, split) unit writes raw fp32 accumulators to `partial`
-    float* partial;  // [splits][M][N] fp32 workspace (split-K only)
+    float* partial;  // [splits][M][N] fp32 workspace (split-K, or the raw fp32 result)
+    // Operands made of K-segments laid side by side (the three bf16 planes of an fp32 matrix): the k-blocks run over
+    // `seg_blocks`-long segment PAIRS, pair i reading segment (seg_a >> 4i) & 15 of A against (seg_b >> 4i) & 15 of W.
+    int seg_blocks = 0;
+    uint32_t seg_a = 0, seg_b = 0;
+    int raw_f32 = 0;  // 1: write the fp32 accumulators to `partial` as they are (splits == 1)
 };
+
+// Element offsets along K of k-block kb in the A and the W tensor map.
+__device__ __forceinline__ void kblock_coords(const GemmParams& p, int kb, int& ka, int& kw) {
+    if (p.seg_blocks == 0) {
+        ka = kw = kb * BK;
+        return;
+    }
+    const int pair = kb / p.seg_blocks, kk = kb - pair * p.seg_blocks;
+    ka = ((int)((p.seg_a >> (4 * pair)) & 15u) * p.seg_blocks + kk) * BK;
+    kw = ((int)((p.seg_b >> (4 * pair)) & 15u) * p.seg_blocks + kk) * BK;
+}
 
 // k-block range of split s of `splits` over nkb blocks (balanced, every split non-empty when splits <= nkb)
 __device__ __forceinline__ void split_range(int s, int splits, int nkb, int& kb0, int& kb1) {
@@ -224,8 +240,8 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams& p, uint32_t tmem
             for (int i = 0; i < 32; ++i) v[i] = __fdividef(v[i], 1.0f + __expf(-v[i])) * __uint_as_float(r[i]);
         }
         const bool full = (col0 + 32 <= p.N);
-        if (p.splits > 1) {
-            // split-K: raw fp32 partial sums; bias / residual / activation happen in the reduce kernel
+        if (p.splits > 1 || p.raw_f32) {
+            // split-K (or an fp32 result): raw fp32 partial sums; bias / residual / activation happen in the reduce kernel
             if (row_ok) {
                 float* prow = p.partial + ((int64_t)split * p.M + row) * p.N + col0;
                 if (full && (p.N & 3) == 0) {
@@ -356,7 +372,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                 for (int kb = kb0; kb < kb1; ++kb) {
                     if (!ptx::mbar_wait_bounded(&empty_bar[stage], phase ^ 1u, abort_flag)) { ok = false; break; }
                     ptx::mbar_arrive_expect_tx(&full_bar[stage], Cfg::STAGE_BYTES);
-                    ptx::tma_load_2d(smem_a + stage * Cfg::A_BYTES, &tmap_a, &full_bar[stage], kb * BK, mb * BM);
+                    int ka, kw;
+                    kblock_coords(p, kb, ka, kw);
+                    ptx::tma_load_2d(smem_a + stage * Cfg::A_BYTES, &tmap_a, &full_bar[stage], ka, mb * BM);
                     if (SWIGLU) {
                         ptx::tma_load_2d(smem_b + stage * Cfg::B_BYTES, &tmap_b, &full_bar[stage], kb * BK, nb * OUT_BN);
                         ptx::tma_load_2d(smem_b + stage * Cfg::B_BYTES + Cfg::B_BYTES / 2, &tmap_b2, &full_bar[stage],
@@ -367,7 +385,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                             ptx::tma_load_2d(smem_b + stage * Cfg::B_BYTES + j * (BK * 128), &tmap_b, &full_bar[stage],
                                              nb * BN + j * 64, kb * BK);
                     } else {
-                        ptx::tma_load_2d(smem_b + stage * Cfg::B_BYTES, &tmap_b, &full_bar[stage], kb * BK, nb * BN);
+                        ptx::tma_load_2d(smem_b + stage * Cfg::B_BYTES, &tmap_b, &full_bar[stage], kw, nb * BN);
                     }
                     armed |= 1u << stage;
                     armed_phase = (armed_phase & ~(1u << stage)) | (phase << stage);
@@ -552,12 +570,14 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                     if (!ptx::mbar_wait_bounded(&empty_bar[stage], phase ^ 1u, abort_flag)) { ok = false; break; }
                     if (rank == 0) ptx::mbar_arrive_expect_tx(&full_bar[stage], 2 * PAIR_STAGE_BYTES);
                     const uint32_t full_leader = ptx::map_to_cta(ptx::smem_u32(&full_bar[stage]), 0);
-                    ptx::tma_load_2d_pair(smem_a + stage * A_BYTES, &tmap_a, full_leader, kb * BK, mb * 256 + (int)rank * BM);
+                    int ka, kw;
+                    kblock_coords(p, kb, ka, kw);
+                    ptx::tma_load_2d_pair(smem_a + stage * A_BYTES, &tmap_a, full_leader, ka, mb * 256 + (int)rank * BM);
                     if (SWIGLU)  // leader: gate rows, partner: up rows of the same 128 output columns
-                        ptx::tma_load_2d_pair(smem_b + stage * B_BYTES, rank == 0 ? &tmap_b : &tmap_b2, full_leader, kb * BK,
+                        ptx::tma_load_2d_pair(smem_b + stage * B_BYTES, rank == 0 ? &tmap_b : &tmap_b2, full_leader, kw,
                                               nb * OUT_BN);
                     else
-                        ptx::tma_load_2d_pair(smem_b + stage * B_BYTES, &tmap_b, full_leader, kb * BK,
+                        ptx::tma_load_2d_pair(smem_b + stage * B_BYTES, &tmap_b, full_leader, kw,
                                               nb * BN + (int)rank * (BN / 2));
                     ++issued;
                     if (++stage == STAGES) { stage = 0; phase ^= 1u; }
@@ -904,6 +924,68 @@ int gemm_tc_entry(const void* A, const void* B, const void* bias, const void* re
     if (dtype == XG_BF16)
         return gemm_tc_dispatch<__nv_bfloat16>(A, B, bias, residual, out, M, N, K, lda, ldb, ldc, ldr, trans_b, act, workspace, ws_bytes, force_split, extras, st);
     return gemm_tc_dispatch<__half>(A, B, bias, residual, out, M, N, K, lda, ldb, ldc, ldr, trans_b, act, workspace, ws_bytes, force_split, extras, st);
+}
+
+// ---- fp32 problems on the bf16 tensor cores ------------------------------------------------------------
+// A3 [M, 3*Kp] and W3 [N, 3*Kp] hold the three bf16 planes of the fp32 operands (split_bf16x3.cu). The product is
+// the sum of the six plane pairs whose weight is at least 2^-16, smallest first, accumulated in fp32 in TMEM by the
+// ordinary bf16 kernels running over 6*Kp/64 k-blocks: about 2^-23 relative error per product, at one sixth of the
+// bf16 rate. The fp32 accumulators go to `raw` ([M, N] contiguous: `out` itself when it is, else caller scratch);
+// bias, residual, activation and a strided output are applied by one more pass.
+int gemm_f32x3_entry(const void* A3, const void* W3, const void* bias, const void* residual, void* out, int64_t M,
+                     int64_t N, int64_t Kp, int64_t ldc, int64_t ldr, int act, void* raw, cudaStream_t st) {
+    if (M * N == 0) return XG_OK;
+    if (Kp <= 0 || Kp % BK != 0) return fail(XG_ERR_INVALID_ARG, "xg_gemm_f32x3: the padded K must be a positive multiple of %d", BK);
+    if (!aligned16(A3) || !aligned16(W3) || !aligned16(raw))
+        return fail(XG_ERR_UNSUPPORTED, "xg_gemm_f32x3: operands and the result buffer must be 16-byte aligned");
+    if (M > (int64_t)BM * 0x7fffff || N > (int64_t)64 * 0x7fffff || 6 * Kp > 0x7fffffff)
+        return fail(XG_ERR_TOO_LARGE, "xg_gemm_f32x3: extent too large");
+    GemmParams p;
+    p.out = out;
+    p.bias = bias;
+    p.residual = residual;
+    p.M = M; p.N = N; p.K = 3 * Kp; p.ldc = ldc; p.ldr = ldr;
+    p.act = act;
+    p.rope_cos = nullptr;
+    p.rope_sin = nullptr;
+    p.rope_S = 0;
+    p.rope_D = 0;
+    p.vec_ok = 0;
+    p.bias_vec_ok = 0;
+    p.splits = 1;
+    p.partial = reinterpret_cast<float*>(raw);
+    p.raw_f32 = 1;
+    p.seg_blocks = (int)(Kp / BK);
+    p.seg_a = 0x010120u;  // pairs (A plane, W plane): (0,2) (2,0) (1,1) (0,1) (1,0) (0,0)
+    p.seg_b = 0x001102u;
+    p.num_k_blocks = 6 * p.seg_blocks;
+    CUtensorMap ta, tb;
+    int rc;
+    if (!make_tmap_2d_16bit(&ta, A3, (uint64_t)M, (uint64_t)(3 * Kp), (uint64_t)(3 * Kp), BM, BK, true))
+        return fail(XG_ERR_UNSUPPORTED, "xg_gemm_f32x3: tensor-map encoding failed");
+    if (use_cta_pairs(M, N, 256)) {
+        if (!make_tmap_2d_16bit(&tb, W3, (uint64_t)N, (uint64_t)(3 * Kp), (uint64_t)(3 * Kp), 128, BK, true))
+            return fail(XG_ERR_UNSUPPORTED, "xg_gemm_f32x3: tensor-map encoding failed");
+        p.num_m_blocks = (int)((M + 255) / 256);
+        p.num_n_blocks = (int)((N + 255) / 256);
+        rc = launch_gemm_pair<__nv_bfloat16, false>(ta, tb, tb, p, st);
+    } else {
+        const GemmPlan pl = plan_gemm(M, N, 6 * Kp, 0, num_sms());
+        if (!make_tmap_2d_16bit(&tb, W3, (uint64_t)N, (uint64_t)(3 * Kp), (uint64_t)(3 * Kp), (uint32_t)pl.bn, BK, true))
+            return fail(XG_ERR_UNSUPPORTED, "xg_gemm_f32x3: tensor-map encoding failed");
+        p.num_m_blocks = (int)((M + BM - 1) / BM);
+        p.num_n_blocks = (int)((N + pl.bn - 1) / pl.bn);
+        switch (pl.bn) {
+            case 256: rc = launch_gemm_tc<__nv_bfloat16, 256, false, false>(ta, tb, tb, p, st); break;
+            case 128: rc = launch_gemm_tc<__nv_bfloat16, 128, false, false>(ta, tb, tb, p, st); break;
+            default: rc = launch_gemm_tc<__nv_bfloat16, 64, false, false>(ta, tb, tb, p, st); break;
+        }
+    }
+    if (rc != XG_OK) return rc;
+    if (raw == out && ldc == N && !bias && !residual && act == XG_ACT_NONE) return XG_OK;  // the result is in place
+    const int64_t total = M * ((N + 3) / 4);
+    splitk_reduce_kernel<float><<<(unsigned)((total + 255) / 256), 256, 0, st>>>(p);
+    return check_launch("xg_gemm_f32x3 (epilogue)");
 }
 
 // ---- split-K on a fixed, library-owned scratch array (nothing is allocated by anyone) ------------------

@@ -12,6 +12,7 @@ Registration pattern follows passes/patterns/targets/mlu/triton_kernel/fused_sli
 from __future__ import annotations
 
 import ctypes
+import os
 from typing import List, Optional, Sequence
 
 import torch
@@ -259,6 +260,52 @@ def _mat(t: torch.Tensor) -> torch.Tensor:
     return t if t.stride(-1) == 1 else t.contiguous()
 
 
+# fp32 dense layers above this many FLOPs run on the bf16 tensor cores from three bf16 planes per operand
+# (fp32-grade results at several times the FMA rate); smaller ones stay on the FMA kernel, whose launch is cheaper.
+F32_TENSOR_MIN_FLOPS = 1 << 30
+F32_TENSOR_MAX_K = 8192  # measured error vs fp64 grows from 2e-6 (K = 1728) to 6e-6 (K = 4096) of the output scale
+
+
+def _f32_on_tensor_cores(M: int, N: int, K: int) -> bool:
+    if os.environ.get("XG_F32_TENSOR", "1") == "0":
+        return False
+    return 2 * M * N * K >= F32_TENSOR_MIN_FLOPS and K <= F32_TENSOR_MAX_K
+
+
+def _weight_planes(L, weight: torch.Tensor, weight_trans: bool, N: int, K: int) -> torch.Tensor:
+    """The three bf16 planes of an fp32 weight, [N, 3*Kp]. They ride on the weight tensor object itself and are
+    rebuilt when its version counter, layout or orientation changes, so a dense layer's weight is split once in
+    inference and the planes go away with the tensor; a fresh view of a weight is simply split again."""
+    tag = (weight._version, weight.data_ptr(), tuple(weight.shape), tuple(weight.stride()), bool(weight_trans))
+    kept = getattr(weight, "_xg_bf16_planes", None)
+    if kept is not None and kept[0] == tag:
+        return kept[1]
+    Kp = int(L.xg_gemm_f32x3_padded_k(K))
+    w3 = torch.empty((N, 3 * Kp), dtype=torch.bfloat16, device=weight.device)
+    rc = L.xg_split_bf16x3(_ptr(weight), N, K, _row_stride(weight), 0 if weight_trans else 1, _ptr(w3), _stream(weight))
+    _lib.check(rc, "xg_split_bf16x3")
+    _bump()
+    try:
+        weight._xg_bf16_planes = (tag, w3)
+    except (AttributeError, RuntimeError):  # a tensor type without instance attributes: no reuse
+        pass
+    return w3
+
+
+def _dense_f32x3(L, x, weight, weight_trans, bias, residual, ldr, act, out, M, N, K):
+    Kp = int(L.xg_gemm_f32x3_padded_k(K))
+    w3 = _weight_planes(L, weight, weight_trans, N, K)
+    a3 = torch.empty((M, 3 * Kp), dtype=torch.bfloat16, device=x.device)
+    rc = L.xg_split_bf16x3(_ptr(x), M, K, _row_stride(x), 0, _ptr(a3), _stream(x))
+    _lib.check(rc, "xg_split_bf16x3")
+    with _GemmTimer(x, 2 * M * N * K):
+        rc = L.xg_gemm_f32x3(_ptr(a3), _ptr(w3), _ptr(bias), _ptr(residual), _ptr(out), M, N, K, N, ldr,
+                             _lib.ACT_CODES[act], None, 0, _stream(x))
+    _lib.check(rc, "xg_gemm_f32x3")
+    _bump(3 if (bias is not None or residual is not None or act != "none") else 2)
+    return out
+
+
 @torch.library.custom_op(f"{NS}::dense", mutates_args=(), device_types="cuda")
 def dense(x: torch.Tensor, weight: torch.Tensor, weight_trans: bool, bias: Optional[torch.Tensor],
           residual: Optional[torch.Tensor], act: str) -> torch.Tensor:
@@ -279,6 +326,8 @@ def dense(x: torch.Tensor, weight: torch.Tensor, weight_trans: bool, bias: Optio
         ldr = _row_stride(residual)
     out = torch.empty((M, N), dtype=x.dtype, device=x.device)
     L = _lib.load()
+    if x.dtype == torch.float32 and _f32_on_tensor_cores(M, N, K):
+        return _dense_f32x3(L, x, weight, weight_trans, bias, residual, ldr, act, out, M, N, K)
     ws, ws_bytes = None, 0
     if x.dtype != torch.float32 and M <= 128:
         ws_bytes = int(L.xg_gemm_workspace_bytes(M, N, K, _code(x.dtype)))
