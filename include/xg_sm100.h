@@ -167,18 +167,18 @@ int64_t xg_gemm_static_scratch_bytes(void);
  * (x = x0 + x1 + x2, 3 x 8 significand bits) laid side by side per row: xg_split_bf16x3 writes
  * out3[r][s * Kp + k], Kp = xg_gemm_f32x3_padded_k(K) (K rounded up to 64, zero-filled), from x [rows, K]
  * (transpose = 0, row stride ld) or from x [K, rows] (transpose = 1). xg_gemm_f32x3 then computes
- * out = act(A @ W^T + bias + residual) in fp32 from A3 [M, 3*Kp] and W3 [N, 3*Kp] (the six plane products of
- * weight >= 2^-16, fp32 accumulation): results agree with an fp32 FMA GEMM to about 1e-6 relative. bias [N],
- * residual [M, ldr] and out [M, ldc] are fp32. `workspace` (M*N*4 bytes) is needed only when out is strided
- * (ldc != N) or not 16-byte aligned. A weight's planes can be kept across calls.
- * Same reference interface as xg_gemm_bias_act (dense_layer_modules.py:9-57) for fp32 tensors; the reference
- * leaves fp32 matmuls to the vendor BLAS.
+ * act(A @ W^T + bias + residual) in fp32 from A3 [M, 3*Kp] and W3 [N, 3*Kp] (the six plane products of
+ * weight >= 2^-16, fp32 accumulation): results agree with an fp32 FMA GEMM to about 1e-6 relative. bias [N] and
+ * residual [M, ldr] are fp32. out_planes = 0: out is fp32 [M, ldc]. out_planes = 1: out receives the result already
+ * cut into planes, [M, 3 * xg_gemm_f32x3_padded_k(N)] bf16 with the padding columns zero, i.e. the A3 of a following
+ * layer (no residual in this form). A weight's planes can be kept across calls.
+ * Same reference interface as xg_gemm_bias_act (dense_layer_modules.py:9-57) for fp32 tensors; chaining layers
+ * through plane outputs stands where the reference fuses serial matmuls (targets/mlu/fuse_densetower.py:272-316).
  */
 int64_t xg_gemm_f32x3_padded_k(int64_t K);
 int xg_split_bf16x3(const void* x, int64_t rows, int64_t K, int64_t ld, int transpose, void* out3, void* stream);
 int xg_gemm_f32x3(const void* A3, const void* W3, const void* bias, const void* residual, void* out, int64_t M,
-                  int64_t N, int64_t K, int64_t ldc, int64_t ldr, int act, void* workspace, int64_t workspace_bytes,
-                  void* stream);
+                  int64_t N, int64_t K, int64_t ldc, int64_t ldr, int act, int out_planes, void* stream);
 
 /*
  * Batched form: out[b] = act( A[b] @ W[b] + bias[b] + residual[b] ), batch strides in elements

@@ -98,4 +98,12 @@ def register():
         return ref_ops.mul_sum_cat(ml)
 
     k(ops.mul_sum_cat)(mul_sum_cat)
+
+    def dense_tower(x, weights, weight_trans, biases, act_names):
+        y = x
+        for w, t, b, a in zip(weights, weight_trans, biases, act_names.split(",")):
+            y = dense(y, w, t, b, None, a)
+        return y
+
+    k(ops.dense_tower)(dense_tower)
     _DONE = True

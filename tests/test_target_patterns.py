@@ -287,6 +287,24 @@ def test_combo_sum_after_multi_slice_cat(tgt, xlog):
     assert "combo_sum" in mods and not any("sum" in a for a in atens)
 
 
+def test_dense_tower(tgt, xlog):
+    """Three chained fp32 Linear+ReLU layers, each large enough for the tensor-core path, collapse into one
+    DenseTowerModule call; a small chain is left as separate dense layers."""
+    torch.manual_seed(9)
+    big = torch.nn.Sequential(torch.nn.Linear(512, 512), torch.nn.ReLU(), torch.nn.Linear(512, 512), torch.nn.ReLU(),
+                              torch.nn.Linear(512, 256)).eval()
+    x = torch.randn(4096, 512)
+    want, got, mods, atens = _compile(tgt, big, x)
+    _same(got, want, 1e-4)
+    assert "Pattern.FusedDenseTower changed graph" in xlog.text
+    assert "xg_dense_tower" in mods and "custom_dense_layer_replacement" not in mods
+
+    small = torch.nn.Sequential(torch.nn.Linear(64, 64), torch.nn.ReLU(), torch.nn.Linear(64, 32)).eval()
+    want, got, mods, atens = _compile(tgt, small, torch.randn(128, 64))
+    _same(got, want, 1e-4)
+    assert "xg_dense_tower" not in mods
+
+
 def test_sum_cat_fusions(tgt, xlog):
     """slice -> sum -> cat, mul -> sum -> cat and sum -> cat along the last dim become one module call each
     (graph forms of targets/mlu/fuse_sum_cat.py and fuse_mul_sum_cat.py; the reference's tests

@@ -20,7 +20,7 @@ int gemm_swiglu_entry(const void* A, const void* Wg, const void* Wu, void* out, 
 int gemm_rope_entry(const void* A, const void* W, const void* cos, const void* sin, void* out, int64_t M, int64_t N, int64_t K,
                     int64_t lda, int64_t ldw, int64_t ldc, int64_t S, int64_t D, int dtype, cudaStream_t st);
 int gemm_f32x3_entry(const void* A3, const void* W3, const void* bias, const void* residual, void* out, int64_t M,
-                     int64_t N, int64_t Kp, int64_t ldc, int64_t ldr, int act, void* raw, cudaStream_t st);
+                     int64_t N, int64_t Kp, int64_t ldc, int64_t ldr, int act, int out_planes, cudaStream_t st);
 int read_tc_status(unsigned int* host_out, int reset);
 int read_sdpa_status(unsigned int* host_out, int reset);
 
@@ -119,21 +119,13 @@ extern "C" int xg_gemm_rope(const void* A, const void* W, const void* cos, const
 }
 
 extern "C" int xg_gemm_f32x3(const void* A3, const void* W3, const void* bias, const void* residual, void* out, int64_t M,
-                             int64_t N, int64_t K, int64_t ldc, int64_t ldr, int act, void* workspace,
-                             int64_t workspace_bytes, void* stream) {
+                             int64_t N, int64_t K, int64_t ldc, int64_t ldr, int act, int out_planes, void* stream) {
     using namespace xg;
     if (!A3 || !W3 || !out) return fail(XG_ERR_INVALID_ARG, "xg_gemm_f32x3: null A3/W3/out");
     if (M < 0 || N < 0 || K <= 0) return fail(XG_ERR_INVALID_ARG, "xg_gemm_f32x3: bad extents");
     if (act < XG_ACT_NONE || act > XG_ACT_SIGMOID) return fail(XG_ERR_INVALID_ARG, "xg_gemm_f32x3: bad activation %d", act);
-    if (ldc < N || (residual && ldr < N)) return fail(XG_ERR_INVALID_ARG, "xg_gemm_f32x3: leading dimension too small");
-    void* raw = out;
-    if (ldc != N || !aligned16(out)) {  // the accumulators need a dense, aligned [M, N] fp32 buffer
-        if (!workspace || workspace_bytes < M * N * 4)
-            return fail(XG_ERR_INVALID_ARG, "xg_gemm_f32x3: a strided or unaligned output needs %lld bytes of workspace",
-                        (long long)(M * N * 4));
-        raw = workspace;
-    }
-    return gemm_f32x3_entry(A3, W3, bias, residual, out, M, N, xg_gemm_f32x3_padded_k(K), ldc, ldr, act, raw,
+    if (!out_planes && (ldc < N || (residual && ldr < N))) return fail(XG_ERR_INVALID_ARG, "xg_gemm_f32x3: leading dimension too small");
+    return gemm_f32x3_entry(A3, W3, bias, residual, out, M, N, xg_gemm_f32x3_padded_k(K), ldc, ldr, act, out_planes ? 1 : 0,
                             reinterpret_cast<cudaStream_t>(stream));
 }
 

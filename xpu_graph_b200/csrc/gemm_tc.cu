@@ -112,12 +112,15 @@ struct GemmParams {
     int64_t rope_S;
     int rope_D;
     int splits;      // > 1: split-K, every (tile, split) unit writes raw fp32 accumulators to `partial`
-    float* partial;  // [splits][M][N] fp32 workspace (split-K, or the raw fp32 result)
+    float* partial;  // [splits][M][N] fp32 workspace (split-K only)
     // Operands made of K-segments laid side by side (the three bf16 planes of an fp32 matrix): the k-blocks run over
     // `seg_blocks`-long segment PAIRS, pair i reading segment (seg_a >> 4i) & 15 of A against (seg_b >> 4i) & 15 of W.
     int seg_blocks = 0;
     uint32_t seg_a = 0, seg_b = 0;
-    int raw_f32 = 0;  // 1: write the fp32 accumulators to `partial` as they are (splits == 1)
+    // fp32 problems (operands given as bf16 planes): 1 = out, bias and residual are fp32; 2 = out is the next layer's
+    // operand, three bf16 planes per row ([M, 3 * out_kp], columns N..out_kp-1 zero), bias fp32, no residual.
+    int f32_mode = 0;
+    int64_t out_kp = 0;
 };
 
 // Element offsets along K of k-block kb in the A and the W tensor map.
@@ -225,7 +228,7 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams& p, uint32_t tmem
 #pragma unroll 1
     for (int c = 0; c < OUT_BN / 32; ++c) {
         const int64_t col0 = (int64_t)nb * OUT_BN + c * 32;
-        if (col0 >= p.N) break;  // warp-uniform
+        if (col0 >= (p.f32_mode == 2 ? p.out_kp : p.N)) break;  // warp-uniform
         uint32_t r[32];
         const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(acc * BN + c * 32);
         ptx::tmem_ld_32x32(taddr, r);
@@ -240,8 +243,58 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams& p, uint32_t tmem
             for (int i = 0; i < 32; ++i) v[i] = __fdividef(v[i], 1.0f + __expf(-v[i])) * __uint_as_float(r[i]);
         }
         const bool full = (col0 + 32 <= p.N);
-        if (p.splits > 1 || p.raw_f32) {
-            // split-K (or an fp32 result): raw fp32 partial sums; bias / residual / activation happen in the reduce kernel
+        if (p.f32_mode != 0) {
+            const float* biasf = reinterpret_cast<const float*>(p.bias);
+            if (biasf != nullptr) {
+#pragma unroll
+                for (int i = 0; i < 32; ++i)
+                    if (col0 + i < p.N) v[i] += biasf[col0 + i];
+            }
+            if (!row_ok) continue;
+            if (p.f32_mode == 1) {
+                const float* rr = p.residual ? reinterpret_cast<const float*>(p.residual) + row * p.ldr + col0 : nullptr;
+                float* orow = reinterpret_cast<float*>(p.out) + row * p.ldc + col0;
+                if (full && p.vec_ok) {
+#pragma unroll
+                    for (int i = 0; i < 32; i += 4) {
+                        float4 o = make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
+                        if (rr != nullptr) {
+                            const float4 r4 = *reinterpret_cast<const float4*>(rr + i);
+                            o.x += r4.x; o.y += r4.y; o.z += r4.z; o.w += r4.w;
+                        }
+                        o.x = apply_act(o.x, p.act); o.y = apply_act(o.y, p.act);
+                        o.z = apply_act(o.z, p.act); o.w = apply_act(o.w, p.act);
+                        *reinterpret_cast<float4*>(orow + i) = o;
+                    }
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 32; ++i)
+                        if (col0 + i < p.N) orow[i] = apply_act(v[i] + (rr != nullptr ? rr[i] : 0.f), p.act);
+                }
+            } else {
+                // next layer's operand: x = x0 + x1 + x2 in bf16, plane s at columns [s * out_kp, s * out_kp + out_kp)
+                __nv_bfloat16* o3 = reinterpret_cast<__nv_bfloat16*>(p.out) + row * (3 * p.out_kp) + col0;
+#pragma unroll
+                for (int i = 0; i < 32; i += 8) {
+                    if (col0 + i >= p.out_kp) break;
+                    Vec16<__nv_bfloat16> q0, q1, q2;
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        const float x = (col0 + i + j < p.N) ? apply_act(v[i + j], p.act) : 0.f;
+                        q0.v[j] = __float2bfloat16_rn(x);
+                        const float r1 = x - __bfloat162float(q0.v[j]);
+                        q1.v[j] = __float2bfloat16_rn(r1);
+                        q2.v[j] = __float2bfloat16_rn(r1 - __bfloat162float(q1.v[j]));
+                    }
+                    st16(o3 + i, q0);
+                    st16(o3 + p.out_kp + i, q1);
+                    st16(o3 + 2 * p.out_kp + i, q2);
+                }
+            }
+            continue;
+        }
+        if (p.splits > 1) {
+            // split-K: raw fp32 partial sums; bias / residual / activation happen in the reduce kernel
             if (row_ok) {
                 float* prow = p.partial + ((int64_t)split * p.M + row) * p.N + col0;
                 if (full && (p.N & 3) == 0) {
@@ -930,14 +983,15 @@ int gemm_tc_entry(const void* A, const void* B, const void* bias, const void* re
 // A3 [M, 3*Kp] and W3 [N, 3*Kp] hold the three bf16 planes of the fp32 operands (split_bf16x3.cu). The product is
 // the sum of the six plane pairs whose weight is at least 2^-16, smallest first, accumulated in fp32 in TMEM by the
 // ordinary bf16 kernels running over 6*Kp/64 k-blocks: about 2^-23 relative error per product, at one sixth of the
-// bf16 rate. The fp32 accumulators go to `raw` ([M, N] contiguous: `out` itself when it is, else caller scratch);
-// bias, residual, activation and a strided output are applied by one more pass.
+// bf16 rate. The epilogue adds the fp32 bias / residual, applies the activation and stores fp32 - or, for a layer
+// that feeds another one, stores the result directly as that layer's three bf16 planes.
 int gemm_f32x3_entry(const void* A3, const void* W3, const void* bias, const void* residual, void* out, int64_t M,
-                     int64_t N, int64_t Kp, int64_t ldc, int64_t ldr, int act, void* raw, cudaStream_t st) {
+                     int64_t N, int64_t Kp, int64_t ldc, int64_t ldr, int act, int out_planes, cudaStream_t st) {
     if (M * N == 0) return XG_OK;
     if (Kp <= 0 || Kp % BK != 0) return fail(XG_ERR_INVALID_ARG, "xg_gemm_f32x3: the padded K must be a positive multiple of %d", BK);
-    if (!aligned16(A3) || !aligned16(W3) || !aligned16(raw))
-        return fail(XG_ERR_UNSUPPORTED, "xg_gemm_f32x3: operands and the result buffer must be 16-byte aligned");
+    if (!aligned16(A3) || !aligned16(W3)) return fail(XG_ERR_UNSUPPORTED, "xg_gemm_f32x3: operands must be 16-byte aligned");
+    if (out_planes && (!aligned16(out) || residual))
+        return fail(XG_ERR_UNSUPPORTED, "xg_gemm_f32x3: the plane output must be 16-byte aligned and takes no residual");
     if (M > (int64_t)BM * 0x7fffff || N > (int64_t)64 * 0x7fffff || 6 * Kp > 0x7fffffff)
         return fail(XG_ERR_TOO_LARGE, "xg_gemm_f32x3: extent too large");
     GemmParams p;
@@ -950,17 +1004,18 @@ int gemm_f32x3_entry(const void* A3, const void* W3, const void* bias, const voi
     p.rope_sin = nullptr;
     p.rope_S = 0;
     p.rope_D = 0;
-    p.vec_ok = 0;
+    // fp32 rows in 16-byte steps (four floats)
+    p.vec_ok = (ldc % 4 == 0) && aligned16(out) && (!residual || (ldr % 4 == 0 && aligned16(residual)));
     p.bias_vec_ok = 0;
     p.splits = 1;
-    p.partial = reinterpret_cast<float*>(raw);
-    p.raw_f32 = 1;
+    p.partial = nullptr;
+    p.f32_mode = out_planes ? 2 : 1;
+    p.out_kp = out_planes ? (N + BK - 1) / BK * BK : 0;
     p.seg_blocks = (int)(Kp / BK);
     p.seg_a = 0x010120u;  // pairs (A plane, W plane): (0,2) (2,0) (1,1) (0,1) (1,0) (0,0)
     p.seg_b = 0x001102u;
     p.num_k_blocks = 6 * p.seg_blocks;
     CUtensorMap ta, tb;
-    int rc;
     if (!make_tmap_2d_16bit(&ta, A3, (uint64_t)M, (uint64_t)(3 * Kp), (uint64_t)(3 * Kp), BM, BK, true))
         return fail(XG_ERR_UNSUPPORTED, "xg_gemm_f32x3: tensor-map encoding failed");
     if (use_cta_pairs(M, N, 256)) {
@@ -968,24 +1023,18 @@ int gemm_f32x3_entry(const void* A3, const void* W3, const void* bias, const voi
             return fail(XG_ERR_UNSUPPORTED, "xg_gemm_f32x3: tensor-map encoding failed");
         p.num_m_blocks = (int)((M + 255) / 256);
         p.num_n_blocks = (int)((N + 255) / 256);
-        rc = launch_gemm_pair<__nv_bfloat16, false>(ta, tb, tb, p, st);
-    } else {
-        const GemmPlan pl = plan_gemm(M, N, 6 * Kp, 0, num_sms());
-        if (!make_tmap_2d_16bit(&tb, W3, (uint64_t)N, (uint64_t)(3 * Kp), (uint64_t)(3 * Kp), (uint32_t)pl.bn, BK, true))
-            return fail(XG_ERR_UNSUPPORTED, "xg_gemm_f32x3: tensor-map encoding failed");
-        p.num_m_blocks = (int)((M + BM - 1) / BM);
-        p.num_n_blocks = (int)((N + pl.bn - 1) / pl.bn);
-        switch (pl.bn) {
-            case 256: rc = launch_gemm_tc<__nv_bfloat16, 256, false, false>(ta, tb, tb, p, st); break;
-            case 128: rc = launch_gemm_tc<__nv_bfloat16, 128, false, false>(ta, tb, tb, p, st); break;
-            default: rc = launch_gemm_tc<__nv_bfloat16, 64, false, false>(ta, tb, tb, p, st); break;
-        }
+        return launch_gemm_pair<__nv_bfloat16, false>(ta, tb, tb, p, st);
     }
-    if (rc != XG_OK) return rc;
-    if (raw == out && ldc == N && !bias && !residual && act == XG_ACT_NONE) return XG_OK;  // the result is in place
-    const int64_t total = M * ((N + 3) / 4);
-    splitk_reduce_kernel<float><<<(unsigned)((total + 255) / 256), 256, 0, st>>>(p);
-    return check_launch("xg_gemm_f32x3 (epilogue)");
+    const GemmPlan pl = plan_gemm(M, N, 6 * Kp, 0, num_sms());
+    if (!make_tmap_2d_16bit(&tb, W3, (uint64_t)N, (uint64_t)(3 * Kp), (uint64_t)(3 * Kp), (uint32_t)pl.bn, BK, true))
+        return fail(XG_ERR_UNSUPPORTED, "xg_gemm_f32x3: tensor-map encoding failed");
+    p.num_m_blocks = (int)((M + BM - 1) / BM);
+    p.num_n_blocks = (int)((N + pl.bn - 1) / pl.bn);
+    switch (pl.bn) {
+        case 256: return launch_gemm_tc<__nv_bfloat16, 256, false, false>(ta, tb, tb, p, st);
+        case 128: return launch_gemm_tc<__nv_bfloat16, 128, false, false>(ta, tb, tb, p, st);
+        default: return launch_gemm_tc<__nv_bfloat16, 64, false, false>(ta, tb, tb, p, st);
+    }
 }
 
 // ---- split-K on a fixed, library-owned scratch array (nothing is allocated by anyone) ------------------

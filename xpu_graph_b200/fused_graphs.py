@@ -13,6 +13,7 @@ import torch
 import torch.nn as nn
 
 from . import modules as M
+from . import ops
 from .workloads import EncoderBlock, LlamaDecoderLayer, RecsysGraph
 
 
@@ -96,7 +97,8 @@ class FusedEncoderBlock(nn.Module):
 
 class FusedRecsysGraph(nn.Module):
     """slice+cat of the dense features (one copy kernel) | 26 embedding lookups + where + stack (one
-    gather kernel) | cat | 3x dense+bias+ReLU."""
+    gather kernel) | cat | 3x dense+bias+ReLU (one dense-tower call when the layers are large enough for the fp32
+    tensor-core path)."""
 
     def __init__(self, graph: RecsysGraph):
         super().__init__()
@@ -107,6 +109,7 @@ class FusedRecsysGraph(nn.Module):
         self.gather = M.GatherStackModule()
         self.cat = M.CatLastDimModule()
         self.dense = M.DenseLayerModule(False)
+        self.tower = M.DenseTowerModule()
 
     @torch.no_grad()
     def forward(self, dense, idx, mask):
@@ -114,6 +117,10 @@ class FusedRecsysGraph(nn.Module):
         d = self.slice_cat(dense, self.slices)
         s = self.gather(list(G.tables), idx, mask, True)
         h = self.cat([d, s])
+        dims = [h.shape[1]] + [layer.weight.shape[0] for layer in G.layers]
+        if h.dtype == torch.float32 and ops.dense_tower_eligible(h.shape[0], dims):
+            return self.tower(h, [layer.weight for layer in G.layers], [True] * len(G.layers),
+                              [layer.bias for layer in G.layers], ["relu"] * len(G.layers))
         for layer in G.layers:
             h = self.dense(h, layer.weight, True, layer.bias, "relu")
         return h

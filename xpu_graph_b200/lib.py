@@ -61,7 +61,7 @@ SIGNATURES = {
     "xg_gemm_f32x3_padded_k": (c_int64, [c_int64]),
     "xg_split_bf16x3": (c_int, [c_void_p, c_int64, c_int64, c_int64, c_int, c_void_p, c_void_p]),
     "xg_gemm_f32x3": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64, c_int64,
-                              c_int, c_void_p, c_int64, c_void_p]),
+                              c_int, c_int, c_void_p]),
     "xg_sum3d": (c_int, [_VPP, _VPP, _I64P, c_int64, c_int, c_int, c_void_p]),
     "xg_rowsum_cat": (c_int, [_VPP, _VPP, _I64P, _I64P, _I64P, c_int64, c_int64, c_int64, c_void_p, c_int64, c_int, c_void_p]),
     "xg_gather_rows": (c_int, [_VPP, _I64P, c_int64, c_void_p, c_int64, c_int64, c_void_p, c_int, c_void_p, c_int64,

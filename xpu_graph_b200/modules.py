@@ -272,6 +272,16 @@ class ComboSumModule(torch.nn.Module):
         return _X.sum3d(list(input_list), int(d))
 
 
+class DenseTowerModule(torch.nn.Module):
+    """A chain of fp32 dense layers in one call: forward(x, weights, weight_trans, biases, acts) with one entry per
+    layer. Stands where the reference fuses serial matmuls into one kernel (targets/mlu/fuse_densetower.py:272-316,
+    triton_kernel/fused_serial_mm_2dot.py / _3dot.py): here the layers stay separate tensor-core GEMMs and the
+    activations travel between them as bf16 planes."""
+
+    def forward(self, x, weights, weight_trans, biases, acts):
+        return _X.dense_tower(x, list(weights), [bool(t) for t in weight_trans], list(biases), ",".join(str(a) for a in acts))
+
+
 class SliceSumCatModule(torch.nn.Module):
     """slice(dim 1) -> sum(dim 1) -> cat(dim -1) of one [B, R, C] tensor in one pass: M(slice_param)(input) with
     slice_param = [(start, end), ...], the interface of targets/mlu/fuse_sum_cat.py:76-115 (SliceSumCatOperation)."""

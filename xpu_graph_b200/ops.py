@@ -300,10 +300,67 @@ def _dense_f32x3(L, x, weight, weight_trans, bias, residual, ldr, act, out, M, N
     _lib.check(rc, "xg_split_bf16x3")
     with _GemmTimer(x, 2 * M * N * K):
         rc = L.xg_gemm_f32x3(_ptr(a3), _ptr(w3), _ptr(bias), _ptr(residual), _ptr(out), M, N, K, N, ldr,
-                             _lib.ACT_CODES[act], None, 0, _stream(x))
+                             _lib.ACT_CODES[act], 0, _stream(x))
     _lib.check(rc, "xg_gemm_f32x3")
-    _bump(3 if (bias is not None or residual is not None or act != "none") else 2)
+    _bump(2)
     return out
+
+
+def dense_tower_eligible(M: int, dims: Sequence[int]) -> bool:
+    """Every layer of an fp32 tower [K0 -> K1 -> ... -> Kn] over M rows qualifies for the tensor-core path."""
+    return all(_f32_on_tensor_cores(M, dims[i + 1], dims[i]) for i in range(len(dims) - 1))
+
+
+@torch.library.custom_op(f"{NS}::dense_tower", mutates_args=(), device_types="cuda")
+def dense_tower(x: torch.Tensor, weights: List[torch.Tensor], weight_trans: List[bool], biases: List[Optional[torch.Tensor]],
+                act_names: str) -> torch.Tensor:
+    """A chain of fp32 dense layers y_i = act_i(y_{i-1} @ W_i + b_i); act_names = "relu,relu,none" (one per layer).
+    On the tensor-core path every inner layer's epilogue writes its result straight as the next layer's three bf16
+    planes, so no fp32 activation is stored or re-read between layers; the last layer stores fp32."""
+    acts = act_names.split(",")
+    if not (len(acts) == len(weights) == len(weight_trans) == len(biases)):
+        raise ValueError("xg_sm100::dense_tower: one weight, orientation, bias and activation per layer")
+    if x.dim() != 2 or x.dtype != torch.float32:
+        raise ValueError("xg_sm100::dense_tower expects a 2-D fp32 input")
+    n = len(weights)
+    M = x.shape[0]
+    dims = [x.shape[1]] + [(w.shape[0] if t else w.shape[1]) for w, t in zip(weights, weight_trans)]
+    if not dense_tower_eligible(M, dims):
+        y = x
+        for i in range(n):
+            y = dense(y, weights[i], weight_trans[i], biases[i], None, acts[i])
+        return y
+    L = _lib.load()
+    x = _mat(x)
+    a3 = torch.empty((M, 3 * int(L.xg_gemm_f32x3_padded_k(dims[0]))), dtype=torch.bfloat16, device=x.device)
+    rc = L.xg_split_bf16x3(_ptr(x), M, dims[0], _row_stride(x), 0, _ptr(a3), _stream(x))
+    _lib.check(rc, "xg_split_bf16x3")
+    _bump()
+    for i in range(n):
+        K, N = dims[i], dims[i + 1]
+        w = _mat(weights[i])
+        if (w.shape[1] if weight_trans[i] else w.shape[0]) != K:
+            raise ValueError("xg_sm100::dense_tower: inner dimensions differ")
+        w3 = _weight_planes(L, w, weight_trans[i], N, K)
+        b = biases[i].to(torch.float32).contiguous() if biases[i] is not None else None
+        last = i == n - 1
+        if last:
+            out = torch.empty((M, N), dtype=torch.float32, device=x.device)
+        else:
+            out = torch.empty((M, 3 * int(L.xg_gemm_f32x3_padded_k(N))), dtype=torch.bfloat16, device=x.device)
+        with _GemmTimer(x, 2 * M * N * K):
+            rc = L.xg_gemm_f32x3(_ptr(a3), _ptr(w3), _ptr(b), None, _ptr(out), M, N, K, N, 0, _lib.ACT_CODES[acts[i]],
+                                 0 if last else 1, _stream(x))
+        _lib.check(rc, "xg_gemm_f32x3")
+        _bump()
+        a3 = out
+    return a3
+
+
+@dense_tower.register_fake
+def _(x, weights, weight_trans, biases, act_names):
+    N = weights[-1].shape[0] if weight_trans[-1] else weights[-1].shape[1]
+    return torch.empty((x.shape[0], N), dtype=x.dtype, device=x.device)
 
 
 @torch.library.custom_op(f"{NS}::dense", mutates_args=(), device_types="cuda")

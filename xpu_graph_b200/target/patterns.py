@@ -832,7 +832,52 @@ class FusedMulSumCat(Pattern):
         return changed
 
 
-ALL_PATTERNS = [FusedSliceSumCat, FusedMulSumCat, FusedSumCat, FusedNativeLayerNorm, FusedSdpa, FusedRoPE, FusedEmbeddingStack, FusedSwiGLU, FusedDenseResidual,
+# ---- chains of fp32 dense layers ---------------------------------------------------------------------------------
+class FusedDenseTower(Pattern):
+    """dense(dense(dense(x))) in fp32, each inner result used only by the next layer -> DenseTowerModule, when every
+    layer is large enough for the tensor-core path (ops.dense_tower_eligible). The graph form of
+    targets/mlu/fuse_densetower.py:272-316 (FusedDenseTower2 / 3), for any depth >= 2."""
+
+    _opt_level = OptLevel.level2
+    _pattern_group = PatternGroup.GROUP2
+
+    def process(self, gm: fx.GraphModule) -> bool:
+        from .. import ops as _ops
+
+        def is_dense(n):
+            if not (_module_call(gm, n, M.DenseLayerModule) and n.target == DENSE_NAME and len(n.args) == 5):
+                return False
+            v, xv, bv = _val(n), _val(n.args[0]), _val(n.args[3])
+            if not (_tensor_ok(v, 2) and _tensor_ok(xv, 2) and v.dtype == torch.float32 and _static(v.shape) and _static(xv.shape)):
+                return False
+            return n.args[3] is None or (isinstance(bv, torch.Tensor) and bv.dim() == 1 and bv.numel() == v.shape[1])
+
+        changed = False
+        for tail in reversed(list(gm.graph.nodes)):
+            if not is_dense(tail) or any(is_dense(u) and u.args[0] is tail and _only_user(tail, u) for u in tail.users):
+                continue  # not a dense layer, or not the last one of its chain
+            chain = [tail]
+            while is_dense(chain[0].args[0]) and _only_user(chain[0].args[0], chain[0]):
+                chain.insert(0, chain[0].args[0])
+            if len(chain) < 2:
+                continue
+            x = chain[0].args[0]
+            dims = [_val(x).shape[1]] + [_val(n).shape[1] for n in chain]
+            if not _ops.dense_tower_eligible(_val(x).shape[0], dims):
+                continue
+            _ensure(gm, "xg_dense_tower", M.DenseTowerModule)
+            with gm.graph.inserting_before(tail):
+                new = gm.graph.call_module("xg_dense_tower", (x, [n.args[1] for n in chain], [n.args[2] for n in chain],
+                                                              [n.args[3] for n in chain], [n.args[4] for n in chain]))
+            _fill_meta(gm, new)
+            tail.replace_all_uses_with(new)
+            for n in reversed(chain):
+                gm.graph.erase_node(n)
+            changed = True
+        return changed
+
+
+ALL_PATTERNS = [FusedDenseTower, FusedSliceSumCat, FusedMulSumCat, FusedSumCat, FusedNativeLayerNorm, FusedSdpa, FusedRoPE, FusedEmbeddingStack, FusedSwiGLU, FusedDenseResidual,
                 FusedAddNorm, FusedCatLastDim, FusedDenseRope]
 
 
