@@ -238,16 +238,35 @@ def test_dense_rope(cuda_device, B, S, H, D, K):
     assert_parity(got, want, f"dense_rope {B}x{S}x{H}x{D}")
 
 
-def test_batch_dense(cuda_device):
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16, torch.float32])
+@pytest.mark.parametrize("b,M,K,N,weight_trans,act,with_bias", [
+    (3, 130, 64, 72, True, "gelu", True),      # ragged rows and columns
+    (16, 256, 512, 384, True, "relu", True),   # many entries, one launch
+    (5, 100, 200, 136, False, "none", True),   # weights given as [b, K, N]
+    (2, 64, 4096, 128, True, "silu", False),   # deep K
+    (1, 77, 64, 64, True, "none", True),       # a batch of one takes the 2-D path
+])
+def test_batch_dense(cuda_device, b, M, K, N, weight_trans, act, with_bias, dtype):
+    from xpu_graph_b200 import lib, ops
     from xpu_graph_b200.modules import BatchDenseLayerModule
 
     g = torch.Generator().manual_seed(26)
-    b, M, K, N = 3, 130, 64, 72
-    x = torch.randn(b, M, K, generator=g).to(torch.bfloat16)
-    w = (0.05 * torch.randn(b, N, K, generator=g)).to(torch.bfloat16)
-    bias = (0.05 * torch.randn(b, 1, N, generator=g)).to(torch.bfloat16)
-    got = BatchDenseLayerModule()(x.to(cuda_device), w.to(cuda_device), True, bias.to(cuda_device), "gelu")
-    assert_parity(got, ref_ops.batch_dense(x, w, True, bias, "gelu"), "batch_dense")
+    x = torch.randn(b, M, K, generator=g).to(dtype)
+    w = (0.05 * torch.randn(b, N, K, generator=g)).to(dtype)
+    if not weight_trans:
+        w = w.transpose(1, 2).contiguous()
+    bias = (0.05 * torch.randn(b, 1, N, generator=g)).to(dtype) if with_bias else None
+    launches = ops.launch_count()
+    got = BatchDenseLayerModule()(x.to(cuda_device), w.to(cuda_device), weight_trans,
+                                  bias.to(cuda_device) if with_bias else None, act)
+    torch.cuda.synchronize()
+    assert ops.launch_count() - launches == 1
+    assert lib.tc_status() == 0
+    if dtype == torch.float32:
+        want = ref_ops.batch_dense(x.double(), w.double(), weight_trans, bias.double() if with_bias else None, act).float()
+    else:
+        want = ref_ops.batch_dense(x, w, weight_trans, bias, act)
+    assert_parity(got, want, f"batch_dense {b}x{M}x{K}x{N} {dtype}")
 
 
 def test_config3_cell(cuda_device):

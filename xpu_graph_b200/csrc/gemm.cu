@@ -21,6 +21,11 @@ int gemm_rope_entry(const void* A, const void* W, const void* cos, const void* s
                     int64_t lda, int64_t ldw, int64_t ldc, int64_t S, int64_t D, int dtype, cudaStream_t st);
 int gemm_f32x3_entry(const void* A3, const void* W3, const void* bias, const void* residual, void* out, int64_t M,
                      int64_t N, int64_t Kp, int64_t ldc, int64_t ldr, int act, int out_planes, cudaStream_t st);
+bool bgemm_single_launch_ok(const void* A, const void* B, int64_t batch, int64_t M, int64_t N, int64_t K, int64_t lda,
+                            int64_t ldb, int64_t sa, int64_t sb, int dtype);
+int bgemm_tc_entry(const void* A, const void* B, const void* bias, const void* residual, void* out, int64_t batch, int64_t M,
+                   int64_t N, int64_t K, int64_t lda, int64_t ldb, int64_t ldc, int64_t ldr, int64_t sa, int64_t sb,
+                   int64_t sbias, int64_t sr, int64_t sc, int trans_b, int act, int dtype, cudaStream_t st);
 int read_tc_status(unsigned int* host_out, int reset);
 int read_sdpa_status(unsigned int* host_out, int reset);
 
@@ -86,6 +91,13 @@ extern "C" int xg_bgemm_bias_act(const void* A, const void* B, const void* bias,
     if (batch < 0) return fail(XG_ERR_INVALID_ARG, "xg_bgemm_bias_act: negative batch");
     const int es = dtype_size(dtype);
     if (es == 0) return fail(XG_ERR_INVALID_ARG, "xg_bgemm_bias_act: bad dtype %d", dtype);
+    if (batch == 0 || M * N == 0) return XG_OK;
+    if (bgemm_single_launch_ok(A, B, batch, M, N, K, lda, ldb, stride_a, stride_b, dtype)) {
+        int rc = validate_gemm("xg_bgemm_bias_act", A, B, residual, out, M, N, K, lda, ldb, ldc, ldr, trans_b, act, dtype);
+        if (rc != XG_OK) return rc;
+        return bgemm_tc_entry(A, B, bias, residual, out, batch, M, N, K, lda, ldb, ldc, ldr, stride_a, stride_b, stride_bias,
+                              stride_r, stride_c, trans_b, act, dtype, reinterpret_cast<cudaStream_t>(stream));
+    }
     for (int64_t b = 0; b < batch; ++b) {
         const char* Ab = reinterpret_cast<const char*>(A) + b * stride_a * es;
         const char* Bb = reinterpret_cast<const char*>(B) + b * stride_b * es;

@@ -71,6 +71,21 @@ bool make_tmap_2d_16bit(CUtensorMap* out, const void* base, uint64_t rows, uint6
     return r == CUDA_SUCCESS;
 }
 
+// [batch][rows][cols] with row stride ld and batch stride bs (elements): dims (cols, rows, batch), box (box_cols, box_rows, 1).
+bool make_tmap_3d_16bit(CUtensorMap* out, const void* base, uint64_t batch, uint64_t rows, uint64_t cols, uint64_t ld,
+                        uint64_t bs, uint32_t box_rows, uint32_t box_cols, bool is_bf16) {
+    PFN_encodeTiled enc = get_encode_tiled();
+    if (!enc) return false;
+    cuuint64_t dims[3] = {cols, rows, batch};
+    cuuint64_t strides[2] = {ld * 2, bs * 2};
+    cuuint32_t box[3] = {box_cols, box_rows, 1};
+    cuuint32_t estr[3] = {1, 1, 1};
+    CUresult r = enc(out, is_bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3,
+                     const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                     CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS;
+}
+
 bool make_tmap_bhsd_16bit(CUtensorMap* out, const void* base, uint64_t B, uint64_t H, uint64_t S, uint64_t D,
                           uint64_t stride_b, uint64_t stride_h, uint64_t stride_s, uint32_t box_rows, bool is_bf16) {
     PFN_encodeTiled enc = get_encode_tiled();
@@ -121,6 +136,10 @@ struct GemmParams {
     // operand, three bf16 planes per row ([M, 3 * out_kp], columns N..out_kp-1 zero), bias fp32, no residual.
     int f32_mode = 0;
     int64_t out_kp = 0;
+    // Batched problems (single-CTA kernel): the tensor maps carry the batch as a third dimension, a work unit is
+    // (batch entry, tile), and out / bias / residual advance by these many elements per entry.
+    int batch = 1;
+    int64_t bs_out = 0, bs_bias = 0, bs_res = 0;
 };
 
 // Element offsets along K of k-block kb in the A and the W tensor map.
@@ -176,11 +195,11 @@ __device__ __forceinline__ void tile_coords(int t, int num_m, int num_n, int& mb
 // Warp-collective (tcgen05.ld): all 32 lanes call it, rows past M only skip the stores.
 template <typename T, int BN, bool SWIGLU>
 __device__ __forceinline__ void epilogue_tile(const GemmParams& p, uint32_t tmem_base, int acc, int quad, int64_t row,
-                                              bool row_ok, int nb, int split) {
+                                              bool row_ok, int nb, int split, int entry = 0) {
     constexpr int OUT_BN = SWIGLU ? BN / 2 : BN;
-    T* out = reinterpret_cast<T*>(p.out);
-    const T* bias = reinterpret_cast<const T*>(p.bias);
-    const T* resid = reinterpret_cast<const T*>(p.residual);
+    T* out = reinterpret_cast<T*>(p.out) + entry * p.bs_out;
+    const T* bias = p.bias ? reinterpret_cast<const T*>(p.bias) + entry * p.bs_bias : nullptr;
+    const T* resid = p.residual ? reinterpret_cast<const T*>(p.residual) + entry * p.bs_res : nullptr;
     if (!SWIGLU && p.rope_cos != nullptr) {
         // Rotary epilogue: the two halves of a head (columns j and j + D/2) meet in one thread, which owns the whole
         // row of the tile: read the two 32-column chunks that are D/2 apart, rotate, store both. The host guarantees
@@ -404,7 +423,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     ptx::tc_fence_after();
     const uint32_t tmem_base = *tmem_base_slot;
 
-    const int num_tiles = p.num_m_blocks * p.num_n_blocks * p.splits;  // work units: (tile, split)
+    const int tiles_per_entry = p.num_m_blocks * p.num_n_blocks;
+    const int num_tiles = tiles_per_entry * p.splits * p.batch;  // work units: (batch entry, tile, split); batch > 1 has no splits
     const int nkb = p.num_k_blocks;
 
     if (warp == 0) {
@@ -420,13 +440,29 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             bool ok = true;
             for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
                 int mb, nb, kb0, kb1;
-                tile_coords(t / p.splits, p.num_m_blocks, p.num_n_blocks, mb, nb);
+                const int unit = t / p.splits, entry = unit / tiles_per_entry;
+                tile_coords(unit - entry * tiles_per_entry, p.num_m_blocks, p.num_n_blocks, mb, nb);
                 split_range(t % p.splits, p.splits, nkb, kb0, kb1);
                 for (int kb = kb0; kb < kb1; ++kb) {
                     if (!ptx::mbar_wait_bounded(&empty_bar[stage], phase ^ 1u, abort_flag)) { ok = false; break; }
                     ptx::mbar_arrive_expect_tx(&full_bar[stage], Cfg::STAGE_BYTES);
                     int ka, kw;
                     kblock_coords(p, kb, ka, kw);
+                    if (p.batch > 1) {  // 3-D maps (k, row, entry); plain and [K, N] weights only
+                        ptx::tma_load_3d(smem_a + stage * Cfg::A_BYTES, &tmap_a, &full_bar[stage], ka, mb * BM, entry);
+                        if (B_MN) {
+#pragma unroll
+                            for (int j = 0; j < BN / 64; ++j)
+                                ptx::tma_load_3d(smem_b + stage * Cfg::B_BYTES + j * (BK * 128), &tmap_b, &full_bar[stage],
+                                                 nb * BN + j * 64, kb * BK, entry);
+                        } else {
+                            ptx::tma_load_3d(smem_b + stage * Cfg::B_BYTES, &tmap_b, &full_bar[stage], kw, nb * BN, entry);
+                        }
+                        armed |= 1u << stage;
+                        armed_phase = (armed_phase & ~(1u << stage)) | (phase << stage);
+                        if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+                        continue;
+                    }
                     ptx::tma_load_2d(smem_a + stage * Cfg::A_BYTES, &tmap_a, &full_bar[stage], ka, mb * BM);
                     if (SWIGLU) {
                         ptx::tma_load_2d(smem_b + stage * Cfg::B_BYTES, &tmap_b, &full_bar[stage], kb * BK, nb * OUT_BN);
@@ -515,13 +551,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         const T* resid = reinterpret_cast<const T*>(p.residual);
         for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
             int mb, nb;
-            tile_coords(t / p.splits, p.num_m_blocks, p.num_n_blocks, mb, nb);
+            const int unit = t / p.splits, entry = unit / tiles_per_entry;
+            tile_coords(unit - entry * tiles_per_entry, p.num_m_blocks, p.num_n_blocks, mb, nb);
             // warp-uniform result: the TMEM loads below are warp-collective
             if (!__all_sync(0xffffffffu, ptx::mbar_wait_bounded(&tmem_full[acc], acc_phase, abort_flag))) { ok = false; break; }
             ptx::tc_fence_after();
             const int64_t row = (int64_t)mb * BM + quad * 32 + lane;
             const bool row_ok = row < p.M;
-            epilogue_tile<T, BN, SWIGLU>(p, tmem_base, acc, quad, row, row_ok, nb, t % p.splits);
+            epilogue_tile<T, BN, SWIGLU>(p, tmem_base, acc, quad, row, row_ok, nb, t % p.splits, entry);
             // All of this warp's TMEM reads are complete (wait::ld above): return the buffer.
             ptx::tc_fence_before();
             __syncwarp();
@@ -793,8 +830,8 @@ int launch_gemm_tc(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorM
         return fail(XG_ERR_LAUNCH, "xg_gemm_bias_act: cannot reserve %d bytes of shared memory: %s", Cfg::SMEM_BYTES,
                     cudaGetErrorString(e));
     }
-    const int tiles = p.num_m_blocks * p.num_n_blocks * p.splits;
-    const int grid = tiles < num_sms() ? tiles : num_sms();
+    const int64_t tiles = (int64_t)p.num_m_blocks * p.num_n_blocks * p.splits * p.batch;
+    const int grid = (int)(tiles < num_sms() ? tiles : num_sms());
     kern<<<grid, kGemmThreads, Cfg::SMEM_BYTES, st>>>(ta, tb, tb2, p);
     int rc = check_launch("xg_gemm_bias_act");
     if (rc != XG_OK || p.splits <= 1) return rc;
@@ -977,6 +1014,79 @@ int gemm_tc_entry(const void* A, const void* B, const void* bias, const void* re
     if (dtype == XG_BF16)
         return gemm_tc_dispatch<__nv_bfloat16>(A, B, bias, residual, out, M, N, K, lda, ldb, ldc, ldr, trans_b, act, workspace, ws_bytes, force_split, extras, st);
     return gemm_tc_dispatch<__half>(A, B, bias, residual, out, M, N, K, lda, ldb, ldc, ldr, trans_b, act, workspace, ws_bytes, force_split, extras, st);
+}
+
+// ---- batched dense layers in one launch -----------------------------------------------------------------
+// out[e] = act(A[e] @ W[e] + bias[e] + residual[e]) for e < batch, all entries of one shape: the persistent
+// single-CTA kernel walks (entry, tile) units, its tensor maps carrying the batch as a third dimension.
+// Returns XG_ERR_UNSUPPORTED (without a message for the caller to act on) when the strides do not fit a tensor map.
+template <typename T>
+static int bgemm_tc_dispatch(const void* A, const void* B, const void* bias, const void* residual, void* out, int64_t batch,
+                             int64_t M, int64_t N, int64_t K, int64_t lda, int64_t ldb, int64_t ldc, int64_t ldr,
+                             int64_t sa, int64_t sb, int64_t sbias, int64_t sr, int64_t sc, int trans_b, int act,
+                             cudaStream_t st) {
+    constexpr bool is_bf16 = std::is_same<T, __nv_bfloat16>::value;
+    const int64_t mblk = (M + BM - 1) / BM;
+    int bn = 256;
+    if (batch * mblk * ((N + 255) / 256) < num_sms()) bn = 128;
+    if (bn == 128 && batch * mblk * ((N + 127) / 128) < num_sms()) bn = 64;
+    CUtensorMap ta, tb;
+    const bool b_ok = trans_b ? make_tmap_3d_16bit(&tb, B, (uint64_t)batch, (uint64_t)N, (uint64_t)K, (uint64_t)ldb, (uint64_t)sb, (uint32_t)bn, BK, is_bf16)
+                              : make_tmap_3d_16bit(&tb, B, (uint64_t)batch, (uint64_t)K, (uint64_t)N, (uint64_t)ldb, (uint64_t)sb, BK, 64, is_bf16);
+    if (!b_ok || !make_tmap_3d_16bit(&ta, A, (uint64_t)batch, (uint64_t)M, (uint64_t)K, (uint64_t)lda, (uint64_t)sa, BM, BK, is_bf16))
+        return fail(XG_ERR_UNSUPPORTED, "xg_bgemm_bias_act: tensor-map encoding failed");
+    GemmParams p;
+    p.out = out;
+    p.bias = bias;
+    p.residual = residual;
+    p.M = M; p.N = N; p.K = K; p.ldc = ldc; p.ldr = ldr;
+    p.act = act;
+    p.rope_cos = nullptr;
+    p.rope_sin = nullptr;
+    p.rope_S = 0;
+    p.rope_D = 0;
+    p.vec_ok = (ldc % 8 == 0) && (sc % 8 == 0) && aligned16(out) && (!residual || (ldr % 8 == 0 && sr % 8 == 0 && aligned16(residual)));
+    p.bias_vec_ok = bias ? (aligned16(bias) && sbias % 8 == 0) : 0;
+    p.num_m_blocks = (int)mblk;
+    p.num_n_blocks = (int)((N + bn - 1) / bn);
+    p.num_k_blocks = (int)((K + BK - 1) / BK);
+    p.splits = 1;
+    p.partial = nullptr;
+    p.batch = (int)batch;
+    p.bs_out = sc;
+    p.bs_bias = sbias;
+    p.bs_res = sr;
+    if (!trans_b) {
+        switch (bn) {
+            case 256: return launch_gemm_tc<T, 256, false, true>(ta, tb, tb, p, st);
+            case 128: return launch_gemm_tc<T, 128, false, true>(ta, tb, tb, p, st);
+            default: return launch_gemm_tc<T, 64, false, true>(ta, tb, tb, p, st);
+        }
+    }
+    switch (bn) {
+        case 256: return launch_gemm_tc<T, 256, false, false>(ta, tb, tb, p, st);
+        case 128: return launch_gemm_tc<T, 128, false, false>(ta, tb, tb, p, st);
+        default: return launch_gemm_tc<T, 64, false, false>(ta, tb, tb, p, st);
+    }
+}
+
+// True when the batched problem can run as one launch (16-bit dtype, TMA-addressable operands, more than one entry).
+bool bgemm_single_launch_ok(const void* A, const void* B, int64_t batch, int64_t M, int64_t N, int64_t K, int64_t lda,
+                            int64_t ldb, int64_t sa, int64_t sb, int dtype) {
+    if (dtype != XG_BF16 && dtype != XG_F16) return false;
+    if (batch < 2 || batch > 65535 || M <= 0 || N <= 0 || K <= 0) return false;
+    if (!aligned16(A) || !aligned16(B) || lda % 8 != 0 || ldb % 8 != 0) return false;
+    if (sa <= 0 || sb <= 0 || sa % 8 != 0 || sb % 8 != 0) return false;  // a broadcast operand (stride 0) takes the per-entry path
+    const int64_t units = batch * ((M + BM - 1) / BM) * ((N + 63) / 64);
+    return units < 0x7fffffffLL && M <= (int64_t)BM * 0x7fffff && N <= (int64_t)64 * 0x7fffff && K <= 0x7fffffff;
+}
+
+int bgemm_tc_entry(const void* A, const void* B, const void* bias, const void* residual, void* out, int64_t batch, int64_t M,
+                   int64_t N, int64_t K, int64_t lda, int64_t ldb, int64_t ldc, int64_t ldr, int64_t sa, int64_t sb,
+                   int64_t sbias, int64_t sr, int64_t sc, int trans_b, int act, int dtype, cudaStream_t st) {
+    if (dtype == XG_BF16)
+        return bgemm_tc_dispatch<__nv_bfloat16>(A, B, bias, residual, out, batch, M, N, K, lda, ldb, ldc, ldr, sa, sb, sbias, sr, sc, trans_b, act, st);
+    return bgemm_tc_dispatch<__half>(A, B, bias, residual, out, batch, M, N, K, lda, ldb, ldc, ldr, sa, sb, sbias, sr, sc, trans_b, act, st);
 }
 
 // ---- fp32 problems on the bf16 tensor cores ------------------------------------------------------------

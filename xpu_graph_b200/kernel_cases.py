@@ -102,7 +102,7 @@ def main(argv=None):
     X = torch.ops.xg_sm100
     ap = argparse.ArgumentParser()
     ap.add_argument("case", choices=["sweep", "gemm_splitk", "gemm", "gemm_swiglu", "gemm_small_m", "add_rms_norm", "layer_norm", "sdpa", "rope", "swiglu",
-                                     "gather", "slice_cat", "gemm_f32", "slice_sum_cat", "mul_sum_cat"])
+                                     "gather", "slice_cat", "gemm_f32", "slice_sum_cat", "mul_sum_cat", "batch_dense"])
     ap.add_argument("--iters", type=int, default=3)
     args = ap.parse_args(argv)
     if args.case == "sweep":
@@ -187,6 +187,13 @@ def main(argv=None):
         mask = torch.rand(rows, 1, generator=g, device=dev) < 0.3
         ms = _time(lambda: X.gather_stack(tables, idx, mask, True), args.iters)
         print(f"gather_stack {rows}x{F}x{D}: {ms:.4f} ms, {(2 * rows * F * D * 4 + rows * F * 8) / ms / 1e6:.0f} GB/s")
+    elif args.case == "batch_dense":
+        b, M, K, N = 64, 256, 512, 512
+        x, w = rn(b, M, K), rn(b, N, K, std=0.02)
+        bias = rn(b, 1, N, std=0.02)
+        ms = _time(lambda: X.batch_dense(x, w, True, bias, None, "relu"), args.iters)
+        ms2 = _time(lambda: torch.relu(torch.baddbmm(bias, x, w.transpose(1, 2))), args.iters)
+        print(f"batch_dense {b} x {M}x{K}x{N} bf16: {ms:.4f} ms, {2 * b * M * N * K / ms / 1e9:.1f} TFLOP/s (torch baddbmm+relu {ms2:.4f} ms)")
     elif args.case == "slice_sum_cat":
         B, R, C = 65536, 50, 64
         x = rn(B, R, C, dtype=torch.float32)
