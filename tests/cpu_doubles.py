@@ -106,4 +106,9 @@ def register():
         return y
 
     k(ops.dense_tower)(dense_tower)
+
+    def combo_dense(inputs, weights, weight_trans, biases, act):
+        return torch.stack([dense(x, w, weight_trans, b, None, act) for x, w, b in zip(inputs, weights, biases)])
+
+    k(ops.combo_dense)(combo_dense)
     _DONE = True

@@ -269,6 +269,27 @@ def test_batch_dense(cuda_device, b, M, K, N, weight_trans, act, with_bias, dtyp
     assert_parity(got, want, f"batch_dense {b}x{M}x{K}x{N} {dtype}")
 
 
+def test_combo_dense(cuda_device):
+    """Six same-shape dense layers in one batched launch: separate tensors are stacked, slabs of one buffer are
+    used in place; both agree with the per-layer oracle."""
+    from xpu_graph_b200 import ops
+    from xpu_graph_b200.modules import ComboDenseModule
+
+    g = torch.Generator().manual_seed(33)
+    T, M, K, N = 6, 96, 128, 200
+    xs = [torch.randn(M, K, generator=g).to(torch.bfloat16) for _ in range(T)]
+    ws = [(0.05 * torch.randn(N, K, generator=g)).to(torch.bfloat16) for _ in range(T)]
+    bs = [(0.05 * torch.randn(N, generator=g)).to(torch.bfloat16) for _ in range(T)]
+    want = torch.stack([ref_ops.dense(x, w, True, b, "relu") for x, w, b in zip(xs, ws, bs)])
+    got = ComboDenseModule()([x.to(cuda_device) for x in xs], [w.to(cuda_device) for w in ws], [b.to(cuda_device) for b in bs], "relu", True)
+    assert_parity(got, want, "combo_dense (stacked operands)")
+    xcat = torch.stack(xs).to(cuda_device)
+    wcat = torch.stack(ws).to(cuda_device)
+    assert ops._stack_or_view(list(xcat.unbind(0))).data_ptr() == xcat.data_ptr()  # no copy for slabs of one buffer
+    got2 = ComboDenseModule()(list(xcat.unbind(0)), list(wcat.unbind(0)), [b.to(cuda_device) for b in bs], "relu", True)
+    assert_parity(got2, want, "combo_dense (operands in place)")
+
+
 def test_config3_cell(cuda_device):
     """One full-size cell of the matmul sweep (M=4096, K=4096, N=11008, GELU): sampled rows against the
     oracle plus linearity in the bias (out(b) - out(0) == b before the activation)."""

@@ -305,6 +305,30 @@ def test_dense_tower(tgt, xlog):
     assert "xg_dense_tower" not in mods
 
 
+def test_combo_dense(tgt, xlog):
+    """Five parallel bf16 Linear+ReLU layers of one shape over different inputs -> one ComboDenseModule call;
+    three of them are too few (the reference's width of 4) and stay separate."""
+    torch.manual_seed(10)
+
+    class Towers(torch.nn.Module):
+        def __init__(self, n):
+            super().__init__()
+            self.layers = torch.nn.ModuleList(torch.nn.Linear(64, 48) for _ in range(n))
+
+        def forward(self, *xs):
+            return tuple(torch.relu(layer(x)) for layer, x in zip(self.layers, xs))
+
+    for n, fused in ((5, True), (3, False)):
+        m = Towers(n).to(torch.bfloat16).eval()
+        xs = [torch.randn(32, 64).to(torch.bfloat16) for _ in range(n)]
+        want, got, mods, atens = _compile(tgt, m, *xs)
+        for w, o in zip(want, got):
+            _same(o, w, 2e-2)
+        assert ("xg_combo_dense" in mods) == fused
+        if fused:
+            assert "Pattern.FusedComboDense changed graph" in xlog.text and "custom_dense_layer_replacement" not in mods
+
+
 def test_sum_cat_fusions(tgt, xlog):
     """slice -> sum -> cat, mul -> sum -> cat and sum -> cat along the last dim become one module call each
     (graph forms of targets/mlu/fuse_sum_cat.py and fuse_mul_sum_cat.py; the reference's tests

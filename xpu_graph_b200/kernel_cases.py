@@ -96,17 +96,48 @@ def sweep():
     return 0
 
 
+def graphs(iters: int) -> int:
+    """The two fp32 configurations that are not the benchmark line: the small encoder block (config 1, batch 2 x seq 128,
+    launch-bound: also timed as one replayed CUDA graph) and the recsys graph (config 5, batch 16384), each as the fused op
+    sequence of this target and as the same model in eager CUDA PyTorch (TF32 off)."""
+    from .fused_graphs import FusedEncoderBlock, FusedRecsysGraph
+    from .graph_runner import CUDAGraphRunner
+    from .workloads import make_encoder, make_recsys
+
+    dev = torch.device("cuda")
+    torch.backends.cuda.matmul.allow_tf32 = False
+    for name, make, fused_cls in (("encoder block (config 1)", make_encoder, FusedEncoderBlock), ("recsys graph (config 5)", make_recsys, FusedRecsysGraph)):
+        model, inputs = make()
+        model = model.to(dev).eval()
+        inputs = [t.to(dev) for t in (inputs if isinstance(inputs, (list, tuple)) else [inputs])]
+        fused = fused_cls(model)
+        with torch.no_grad():
+            want, got = model(*inputs), fused(*inputs)
+            err = (got - want).abs().max().item() / max(want.abs().max().item(), 1e-30)
+            ms_eager = _time(lambda: model(*inputs), iters)
+            ms_fused = _time(lambda: fused(*inputs), iters)
+            runner = CUDAGraphRunner(fused)
+            runner.capture(*inputs)
+            ms_graph = _time(lambda: runner(*inputs), iters)
+        n = inputs[0].shape[0]
+        print(f"{name}: batch {n}: fused {ms_fused:.4f} ms ({n / ms_fused * 1e3:.0f} samples/s), as one CUDA graph {ms_graph:.4f} ms "
+              f"({n / ms_graph * 1e3:.0f} samples/s), eager CUDA {ms_eager:.4f} ms; max |diff| / scale vs eager {err:.1e}")
+    return 0
+
+
 def main(argv=None):
     from . import lib, ops  # noqa: F401
 
     X = torch.ops.xg_sm100
     ap = argparse.ArgumentParser()
     ap.add_argument("case", choices=["sweep", "gemm_splitk", "gemm", "gemm_swiglu", "gemm_small_m", "add_rms_norm", "layer_norm", "sdpa", "rope", "swiglu",
-                                     "gather", "slice_cat", "gemm_f32", "slice_sum_cat", "mul_sum_cat", "batch_dense"])
+                                     "gather", "slice_cat", "gemm_f32", "slice_sum_cat", "mul_sum_cat", "batch_dense", "graphs"])
     ap.add_argument("--iters", type=int, default=3)
     args = ap.parse_args(argv)
     if args.case == "sweep":
         return sweep()
+    if args.case == "graphs":
+        return graphs(args.iters)
     dev = torch.device("cuda")
     bf = torch.bfloat16
     g = torch.Generator(device=dev).manual_seed(0)

@@ -272,6 +272,15 @@ class ComboSumModule(torch.nn.Module):
         return _X.sum3d(list(input_list), int(d))
 
 
+class ComboDenseModule(torch.nn.Module):
+    """Many same-shape dense layers in one batched launch: forward(input_list, weight_list, bias_list, act,
+    weight_trans) -> stacked [T, M, N] (callers unbind it). The place of FusedCombineBmm,
+    targets/mlu/combo_matmul.py:22-113 (stacked bmm / grouped GEMM)."""
+
+    def forward(self, input_list, weight_list, bias_list, act, weight_trans):
+        return _X.combo_dense(list(input_list), list(weight_list), bool(weight_trans), list(bias_list), str(act))
+
+
 class DenseTowerModule(torch.nn.Module):
     """A chain of fp32 dense layers in one call: forward(x, weights, weight_trans, biases, acts) with one entry per
     layer. Stands where the reference fuses serial matmuls into one kernel (targets/mlu/fuse_densetower.py:272-316,

@@ -262,7 +262,7 @@ def _mat(t: torch.Tensor) -> torch.Tensor:
 
 # fp32 dense layers above this many FLOPs run on the bf16 tensor cores from three bf16 planes per operand
 # (fp32-grade results at several times the FMA rate); smaller ones stay on the FMA kernel, whose launch is cheaper.
-F32_TENSOR_MIN_FLOPS = 1 << 30
+F32_TENSOR_MIN_FLOPS = int(os.environ.get("XG_F32_TENSOR_MIN_FLOPS", str(1 << 30)))
 F32_TENSOR_MAX_K = 8192  # measured error vs fp64 grows from 2e-6 (K = 1728) to 6e-6 (K = 4096) of the output scale
 
 
@@ -434,6 +434,42 @@ def batch_dense(x: torch.Tensor, weight: torch.Tensor, weight_trans: bool, bias:
 def _(x, weight, weight_trans, bias, residual, act):
     N = weight.shape[1] if weight_trans else weight.shape[2]
     return torch.empty((x.shape[0], x.shape[1], N), dtype=x.dtype, device=x.device)
+
+
+@torch.library.custom_op(f"{NS}::combo_dense", mutates_args=(), device_types="cuda")
+def combo_dense(inputs: List[torch.Tensor], weights: List[torch.Tensor], weight_trans: bool,
+                biases: List[Optional[torch.Tensor]], act: str) -> torch.Tensor:
+    """T same-shape dense layers act(x_t @ W_t + b_t) as one batched launch; returns the stacked [T, M, N] result.
+    Operands that are not already consecutive slabs of one buffer are stacked first."""
+    T = len(inputs)
+    if T == 0 or len(weights) != T or len(biases) != T:
+        raise ValueError("xg_sm100::combo_dense: one input, weight and bias entry per layer")
+    x = _stack_or_view(inputs)
+    w = _stack_or_view(weights)
+    has_bias = biases[0] is not None
+    if any((b is not None) != has_bias for b in biases):
+        raise ValueError("xg_sm100::combo_dense: either every layer has a bias or none")
+    b = torch.stack([bi.reshape(1, -1) for bi in biases]) if has_bias else None  # [T, 1, N]
+    return batch_dense(x, w, weight_trans, b, None, act)
+
+
+def _stack_or_view(ts: Sequence[torch.Tensor]) -> torch.Tensor:
+    """[T, ...] tensor of the list's members: a view when they are equally spaced contiguous slabs of one storage
+    (the outputs of an unbind / split), else a stacked copy."""
+    t0 = ts[0]
+    if len(ts) > 1 and all(t.is_contiguous() and t.shape == t0.shape and t.dtype == t0.dtype for t in ts):
+        step = ts[1].data_ptr() - t0.data_ptr()
+        same_store = all(t.untyped_storage().data_ptr() == t0.untyped_storage().data_ptr() for t in ts)
+        if same_store and step == t0.numel() * t0.element_size() and all(
+                ts[i].data_ptr() - t0.data_ptr() == i * step for i in range(len(ts))):
+            return t0.as_strided((len(ts),) + tuple(t0.shape), (t0.numel(),) + tuple(t0.stride()), t0.storage_offset())
+    return torch.stack(list(ts))
+
+
+@combo_dense.register_fake
+def _(inputs, weights, weight_trans, biases, act):
+    N = weights[0].shape[0] if weight_trans else weights[0].shape[1]
+    return torch.empty((len(inputs), inputs[0].shape[0], N), dtype=inputs[0].dtype, device=inputs[0].device)
 
 
 @torch.library.custom_op(f"{NS}::dense_swiglu", mutates_args=(), device_types="cuda")

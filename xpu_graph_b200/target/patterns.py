@@ -832,6 +832,63 @@ class FusedMulSumCat(Pattern):
         return changed
 
 
+# ---- many same-shape dense layers -------------------------------------------------------------------------------------
+COMBO_MIN_WIDTH = 4  # the reference's default width (utils/combo_utils.py:40-41)
+
+
+class FusedComboDense(Pattern):
+    """>= 4 independent dense layers of one shape, dtype, orientation and activation -> one ComboDenseModule call
+    (a batched launch) + unbind. The graph form of targets/mlu/combo_matmul.py:116-232, restricted to groups whose
+    operands are all defined before the group's first member, so that the combined node can take that member's
+    place without reordering the graph."""
+
+    _opt_level = OptLevel.level2
+    _pattern_group = PatternGroup.GROUP2
+
+    def process(self, gm: fx.GraphModule) -> bool:
+        order = {n: i for i, n in enumerate(gm.graph.nodes)}
+        groups = {}
+        for n in gm.graph.nodes:
+            if not (_module_call(gm, n, M.DenseLayerModule) and n.target == DENSE_NAME and len(n.args) == 5):
+                continue
+            x, w, wt, bias, act = n.args
+            xv, wv, bv, v = _val(x), _val(w), _val(bias), _val(n)
+            if not (_tensor_ok(xv, 2) and _tensor_ok(wv, 2) and _tensor_ok(v, 2) and _static(xv.shape) and _static(wv.shape)):
+                continue
+            if xv.dtype not in (torch.bfloat16, torch.float16) or wv.dtype != xv.dtype:
+                continue  # the batched launch is a 16-bit tensor-core path
+            if xv.shape[1] % 8 != 0 or wv.shape[1] % 8 != 0:
+                continue  # rows must be addressable by a tensor map
+            if bias is not None and not (isinstance(bv, torch.Tensor) and bv.numel() == v.shape[1] and bv.dim() <= 2 and bv.dtype == xv.dtype):
+                continue
+            key = (tuple(xv.shape), tuple(wv.shape), bool(wt), bias is not None, act, xv.dtype)
+            groups.setdefault(key, []).append(n)
+        changed = False
+        for key, nodes in groups.items():
+            if len(nodes) < COMBO_MIN_WIDTH:
+                continue
+            first = order[nodes[0]]
+            # every operand of every member precedes the first member: the members are then mutually independent too
+            members = [n for n in nodes if all(not isinstance(a, fx.Node) or order[a] < first for a in n.args)]
+            if len(members) < COMBO_MIN_WIDTH:
+                continue
+            _ensure(gm, "xg_combo_dense", M.ComboDenseModule)
+            with gm.graph.inserting_before(nodes[0]):
+                new = gm.graph.call_module("xg_combo_dense", ([n.args[0] for n in members], [n.args[1] for n in members],
+                                                              [n.args[3] for n in members], key[4], key[2]))
+                _fill_meta(gm, new)
+                parts = gm.graph.call_function(aten.unbind.int, (new,))
+                _fill_meta(gm, parts)
+                for i, n in enumerate(members):
+                    item = gm.graph.call_function(operator.getitem, (parts, i))
+                    _fill_meta(gm, item)
+                    n.replace_all_uses_with(item)
+            for n in members:
+                gm.graph.erase_node(n)
+            changed = True
+        return changed
+
+
 # ---- chains of fp32 dense layers ---------------------------------------------------------------------------------
 class FusedDenseTower(Pattern):
     """dense(dense(dense(x))) in fp32, each inner result used only by the next layer -> DenseTowerModule, when every
@@ -877,7 +934,7 @@ class FusedDenseTower(Pattern):
         return changed
 
 
-ALL_PATTERNS = [FusedDenseTower, FusedSliceSumCat, FusedMulSumCat, FusedSumCat, FusedNativeLayerNorm, FusedSdpa, FusedRoPE, FusedEmbeddingStack, FusedSwiGLU, FusedDenseResidual,
+ALL_PATTERNS = [FusedDenseTower, FusedComboDense, FusedSliceSumCat, FusedMulSumCat, FusedSumCat, FusedNativeLayerNorm, FusedSdpa, FusedRoPE, FusedEmbeddingStack, FusedSwiGLU, FusedDenseResidual,
                 FusedAddNorm, FusedCatLastDim, FusedDenseRope]
 
 
