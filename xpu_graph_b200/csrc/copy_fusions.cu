@@ -59,16 +59,17 @@ __global__ void __launch_bounds__(kCopyThreads) seg_copy_kernel(const __grid_con
     const int nrows = (int)(left < p.rows_per_cta ? left : p.rows_per_cta);
     const int W = p.width;
     if (W >= 128) {
-        // wide rows: walk the columns with stride 256 and take the same column of up to 4 rows at once
-        // (no index division; 4 loads in flight per thread)
-        for (int rb = 0; rb < nrows; rb += kCopyUnroll) {
+        // wide rows: walk the columns with stride 256 and take the same column of several rows at once
+        // (no index division; 64 bytes of loads in flight per thread: 4 rows of 16-byte units, 8 of narrower ones)
+        constexpr int kRowsAtOnce = sizeof(U) >= 16 ? kCopyUnroll : 2 * kCopyUnroll;
+        for (int rb = 0; rb < nrows; rb += kRowsAtOnce) {
             for (int c = threadIdx.x; c < W; c += kCopyThreads) {
                 const uint32_t e = lut[c];
                 const SegDesc& sd = segs[e >> 24];
                 const int64_t j = (int64_t)(e & 0xffffffu) * sizeof(U);
-                U v[kCopyUnroll];
+                U v[kRowsAtOnce];
 #pragma unroll
-                for (int k = 0; k < kCopyUnroll; ++k) {
+                for (int k = 0; k < kRowsAtOnce; ++k) {
                     if (rb + k < nrows) {
                         const int64_t row = r0 + rb + k;
                         bool zero = false;
@@ -77,7 +78,7 @@ __global__ void __launch_bounds__(kCopyThreads) seg_copy_kernel(const __grid_con
                     }
                 }
 #pragma unroll
-                for (int k = 0; k < kCopyUnroll; ++k) {
+                for (int k = 0; k < kRowsAtOnce; ++k) {
                     if (rb + k < nrows) *reinterpret_cast<U*>(sd.dst + (r0 + rb + k) * sd.dst_ld + j) = v[k];
                 }
             }
@@ -238,7 +239,8 @@ extern "C" int xg_seg_copy(const void* const* src_ptrs, void* const* dst_ptrs, c
         if (p.nseg == 0) return XG_OK;
         // ~8192 units per CTA, but at least ~4 CTAs per SM when the row count allows it.
         int64_t rpc = kLutMax / p.width;
-        if (rpc < 4) rpc = 4;  // amortise the look-up table build for wide rows
+        const int64_t min_rows = unit >= 16 ? kCopyUnroll : 2 * kCopyUnroll;  // the rows a thread takes at once
+        if (rpc < min_rows) rpc = min_rows;  // also amortises the look-up table build for wide rows
         const int64_t want_ctas = 4LL * num_sms();
         const int64_t cap = (rows + want_ctas - 1) / want_ctas;
         if (rpc > cap) rpc = cap;

@@ -113,11 +113,15 @@ struct SwigluParams {
 };
 
 // fp32 tensors use expf and a true division (the fp32 path must stay within 1e-5 relative of aten's
-// silu); 16-bit tensors use the fast intrinsics, whose error is far below half a bf16/f16 ulp.
+// silu); 16-bit tensors use silu(g) = h + h * tanh(h), h = g / 2, with the hardware tanh: one special-function
+// operation per element instead of two, error about 2^-11 of the result (below a bf16 ulp, about one f16 ulp).
 template <typename T>
 __device__ __forceinline__ float silu_f(float g) {
     if (sizeof(T) == 4) return g / (1.0f + expf(-g));
-    return __fdividef(g, 1.0f + __expf(-g));
+    const float h = 0.5f * g;
+    float t;
+    asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(h));
+    return fmaf(h, t, h);
 }
 
 // One CTA owns ROWS consecutive rows; a thread walks the row's 16-byte vectors with stride 256 and handles the
