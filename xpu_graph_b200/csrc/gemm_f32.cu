@@ -131,6 +131,103 @@ __global__ void __launch_bounds__(256) gemm_f32_kernel(const GemmF32Params p) {
     }
 }
 
+// Small problems (fewer 64 x 64 tiles than SMs) are latency-bound in the kernel above: every 16-wide k-tile costs a
+// round trip to L2. This variant gives each CTA a small output tile and the whole K-panel of both operands, 256 k at
+// a time, fetched with one burst of 16-byte asynchronous copies, so a k-chunk costs one round trip; the inner
+// product reads both panels as float4 along k (A rows are shared by the 16 threads of a row group, the B rows of the
+// 8 threads of a wavefront fall into distinct bank groups with the 260-float row pitch). W must be [N, K].
+// 128 threads as 8 (m) x 16 (n); thread (ty, tx) owns a TM x TN micro-tile; BM = 8 TM, BN = 16 TN.
+constexpr int kPanelK = 256;
+constexpr int kPanelPitch = kPanelK + 4;  // floats; rows stay 16-byte aligned
+
+__device__ __forceinline__ void cp_async16(void* smem_dst, const void* gsrc, bool valid) {
+    const uint32_t d = (uint32_t)__cvta_generic_to_shared(smem_dst);
+    const int bytes = valid ? 16 : 0;  // 0 source bytes: the 16 destination bytes are zero-filled
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 16, %2;" ::"r"(d), "l"(gsrc), "r"(bytes) : "memory");
+}
+
+template <int TM, int TN>
+__global__ void __launch_bounds__(128) gemm_f32_panel_kernel(const GemmF32Params p) {
+    constexpr int BM = 8 * TM, BN = 16 * TN;
+    extern __shared__ __align__(16) float panel[];
+    float* As = panel;                      // [BM][kPanelPitch]
+    float* Bs = panel + BM * kPanelPitch;   // [BN][kPanelPitch]
+    const int tid = threadIdx.x;
+    const int tx = tid & 15, ty = tid >> 4;
+    const int64_t m0 = (int64_t)blockIdx.y * BM, n0 = (int64_t)blockIdx.x * BN;
+    float acc[TM][TN];
+#pragma unroll
+    for (int i = 0; i < TM; ++i)
+#pragma unroll
+        for (int j = 0; j < TN; ++j) acc[i][j] = 0.f;
+
+    for (int64_t k0 = 0; k0 < p.K; k0 += kPanelK) {
+        const int kc = (int)((p.K - k0) < kPanelK ? (p.K - k0) : kPanelK);  // multiple of 4 (host-checked)
+        const int vec_per_row = kc / 4;
+        if (k0 > 0) __syncthreads();  // the previous chunk has been consumed
+        for (int idx = tid; idx < BM * vec_per_row; idx += 128) {
+            const int r = idx / vec_per_row, v = idx - r * vec_per_row;
+            const int64_t gm = m0 + r;
+            cp_async16(As + r * kPanelPitch + 4 * v, p.A + (gm < p.M ? gm : 0) * p.lda + k0 + 4 * v, gm < p.M);
+        }
+        for (int idx = tid; idx < BN * vec_per_row; idx += 128) {
+            const int r = idx / vec_per_row, v = idx - r * vec_per_row;
+            const int64_t gn = n0 + r;
+            cp_async16(Bs + r * kPanelPitch + 4 * v, p.B + (gn < p.N ? gn : 0) * p.ldb + k0 + 4 * v, gn < p.N);
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+        asm volatile("cp.async.wait_group 0;" ::: "memory");
+        __syncthreads();
+        for (int k = 0; k < kc; k += 4) {
+            float4 a[TM], b[TN];
+#pragma unroll
+            for (int i = 0; i < TM; ++i) a[i] = *reinterpret_cast<const float4*>(As + (ty * TM + i) * kPanelPitch + k);
+#pragma unroll
+            for (int j = 0; j < TN; ++j) b[j] = *reinterpret_cast<const float4*>(Bs + (tx * TN + j) * kPanelPitch + k);
+#pragma unroll
+            for (int i = 0; i < TM; ++i)
+#pragma unroll
+                for (int j = 0; j < TN; ++j) {
+                    float c = acc[i][j];
+                    c = fmaf(a[i].x, b[j].x, c);
+                    c = fmaf(a[i].y, b[j].y, c);
+                    c = fmaf(a[i].z, b[j].z, c);
+                    c = fmaf(a[i].w, b[j].w, c);
+                    acc[i][j] = c;
+                }
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < TM; ++i) {
+        const int64_t gm = m0 + ty * TM + i;
+        if (gm >= p.M) continue;
+#pragma unroll
+        for (int j = 0; j < TN; ++j) {
+            const int64_t gn = n0 + tx * TN + j;
+            if (gn >= p.N) continue;
+            float v = acc[i][j];
+            if (p.bias) v += p.bias[gn];
+            if (p.residual) v += p.residual[gm * p.ldr + gn];
+            p.out[gm * p.ldc + gn] = act_f32(v, p.act);
+        }
+    }
+}
+
+template <int TM, int TN>
+int launch_panel(const GemmF32Params& p, cudaStream_t st) {
+    constexpr int BM = 8 * TM, BN = 16 * TN;
+    constexpr int smem = (BM + BN) * kPanelPitch * (int)sizeof(float);
+    auto kern = gemm_f32_panel_kernel<TM, TN>;
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) {
+        cudaGetLastError();
+        return fail(XG_ERR_LAUNCH, "xg_gemm_bias_act(f32): cannot reserve %d bytes of shared memory: %s", smem, cudaGetErrorString(e));
+    }
+    dim3 grid((unsigned)((p.N + BN - 1) / BN), (unsigned)((p.M + BM - 1) / BM));
+    kern<<<grid, 128, smem, st>>>(p);
+    return check_launch("xg_gemm_bias_act(f32)");
+}
+
 }  // namespace
 
 int gemm_f32_entry(const void* A, const void* B, const void* bias, const void* residual, void* out, int64_t M, int64_t N,
@@ -139,6 +236,14 @@ int gemm_f32_entry(const void* A, const void* B, const void* bias, const void* r
     GemmF32Params p{reinterpret_cast<const float*>(A), reinterpret_cast<const float*>(B), reinterpret_cast<const float*>(bias),
                     reinterpret_cast<const float*>(residual), reinterpret_cast<float*>(out), M, N, K, lda, ldb, ldc, ldr,
                     trans_b, act};
+    const int64_t tiles64 = ((M + 63) / 64) * ((N + 63) / 64);
+    const bool panel_ok = trans_b && K % 4 == 0 && lda % 4 == 0 && ldb % 4 == 0 && aligned16(A) && aligned16(B) &&
+                          (M + 15) / 16 <= 65535;
+    if (panel_ok && tiles64 < num_sms()) {  // latency-bound sizes: small tiles, whole K-panels per round trip
+        const int64_t tiles_32x64 = ((M + 31) / 32) * ((N + 63) / 64);
+        if (tiles_32x64 * 3 >= 2LL * num_sms()) return launch_panel<4, 4>(p, st);
+        return launch_panel<2, 2>(p, st);
+    }
     const int64_t big_tiles = ((M + 127) / 128) * ((N + 127) / 128);
     if (big_tiles >= 2LL * num_sms()) {
         dim3 grid((unsigned)((N + 127) / 128), (unsigned)((M + 127) / 128));
