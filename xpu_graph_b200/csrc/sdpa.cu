@@ -451,14 +451,14 @@ int launch_flash_tc(const SdpaParams& p, cudaStream_t st) {
 
 // ---------------------------------------------------------------------------------------
 // SIMT kernel: one warp per query row, true fp32 arithmetic, any dtype / strides, D <= 256.
-// Lane t scores key j0 + t; the output row is spread over the lanes (element d = lane + 32 u).
+// Key rows and value rows are read with coalesced loads (lane l holds elements l + 32 u of the head dim); lane t keeps
+// the score of key j0 + t; the output row is spread over the lanes the same way.
 // ---------------------------------------------------------------------------------------
 constexpr int kSimtWarps = 4;
 constexpr int kSimtMaxD = 256;
 
 template <typename T>
 __global__ void __launch_bounds__(kSimtWarps * 32) sdpa_simt_kernel(const SdpaParams p) {
-    __shared__ float qs[kSimtWarps][kSimtMaxD];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int64_t gr = (int64_t)blockIdx.x * kSimtWarps + warp;  // global query row over (b, h, i)
     if (gr >= p.B * p.H * p.Sq) return;
@@ -470,8 +470,10 @@ __global__ void __launch_bounds__(kSimtWarps * 32) sdpa_simt_kernel(const SdpaPa
     const T* kbase = reinterpret_cast<const T*>(p.k) + b * p.k_sb + h * p.k_sh;
     const T* vbase = reinterpret_cast<const T*>(p.v) + b * p.v_sb + h * p.v_sh;
     const T* mrow = p.mask ? reinterpret_cast<const T*>(p.mask) + b * p.m_sb + h * p.m_sh + i * p.m_sq : nullptr;
-    for (int d = lane; d < D; d += 32) qs[warp][d] = Cvt<T>::to_f(qrow[d]);
-    __syncwarp();
+    const int nu = (D + 31) / 32;  // head-dim elements (and output columns) per lane
+    float qreg[kSimtMaxD / 32];
+#pragma unroll
+    for (int u = 0; u < kSimtMaxD / 32; ++u) qreg[u] = (lane + 32 * u < D) ? Cvt<T>::to_f(qrow[lane + 32 * u]) : 0.f;
     float o[kSimtMaxD / 32];
 #pragma unroll
     for (int u = 0; u < kSimtMaxD / 32; ++u) o[u] = 0.f;
@@ -480,13 +482,39 @@ __global__ void __launch_bounds__(kSimtWarps * 32) sdpa_simt_kernel(const SdpaPa
     if (p.causal && i + 1 < kv_end) kv_end = i + 1;
     for (int64_t j0 = 0; j0 < kv_end; j0 += 32) {
         const int64_t j = j0 + lane;
+        const int cnt = (int)((kv_end - j0) < 32 ? (kv_end - j0) : 32);
+        // Scores of keys j0 .. j0+cnt-1. All lanes work on one key at a time, each on its slice of the head dim
+        // (coalesced 128-byte loads of the key row, then a warp reduction); four keys are in flight so that the
+        // loads and the shuffle chains overlap. Lane t keeps the score of key j0 + t. (A lane walking its own key
+        // row would touch 32 different lines per load and saturate the L1 instead.)
         float s = -INFINITY;
+        for (int t0 = 0; t0 < cnt; t0 += 4) {
+            float part[4] = {0.f, 0.f, 0.f, 0.f};
+            for (int u = 0; u < nu; ++u) {
+                const int d = lane + 32 * u;
+                float qv = 0.f;
+#pragma unroll
+                for (int uu = 0; uu < kSimtMaxD / 32; ++uu)
+                    if (uu == u) qv = qreg[uu];
+                float kv[4];
+#pragma unroll
+                for (int e = 0; e < 4; ++e)
+                    kv[e] = (t0 + e < cnt && d < D) ? Cvt<T>::to_f(kbase[(j0 + t0 + e) * p.k_ss + d]) : 0.f;
+#pragma unroll
+                for (int e = 0; e < 4; ++e) part[e] = fmaf(qv, kv[e], part[e]);
+            }
+#pragma unroll
+            for (int o2 = 16; o2 > 0; o2 >>= 1)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) part[e] += __shfl_xor_sync(0xffffffffu, part[e], o2);
+#pragma unroll
+            for (int e = 0; e < 4; ++e)
+                if (lane == t0 + e) s = part[e] * p.scale;
+        }
         if (j < kv_end) {
-            const T* kr = kbase + j * p.k_ss;
-            float acc = 0.f;
-            for (int d = 0; d < D; ++d) acc = fmaf(qs[warp][d], Cvt<T>::to_f(kr[d]), acc);
-            s = acc * p.scale;
             if (mrow) s += Cvt<T>::to_f(mrow[j * p.m_sk]);
+        } else {
+            s = -INFINITY;
         }
         const float m_new = fmaxf(m_run, warp_max(s));
         const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
@@ -495,14 +523,20 @@ __global__ void __launch_bounds__(kSimtWarps * 32) sdpa_simt_kernel(const SdpaPa
         l_run = l_run * alpha + warp_sum(pj);
 #pragma unroll
         for (int u = 0; u < kSimtMaxD / 32; ++u) o[u] *= alpha;
-        const int cnt = (int)((kv_end - j0) < 32 ? (kv_end - j0) : 32);
-        for (int t = 0; t < cnt; ++t) {
-            const float pt = __shfl_sync(0xffffffffu, pj, t);
-            const T* vr = vbase + (j0 + t) * p.v_ss;
-#pragma unroll
-            for (int u = 0; u < kSimtMaxD / 32; ++u) {
+        for (int t0 = 0; t0 < cnt; t0 += 8) {  // eight value rows in flight at a time
+            for (int u = 0; u < nu; ++u) {
                 const int d = lane + 32 * u;
-                if (d < D) o[u] = fmaf(pt, Cvt<T>::to_f(vr[d]), o[u]);
+                float vv[8];
+#pragma unroll
+                for (int e = 0; e < 8; ++e)
+                    vv[e] = (t0 + e < cnt && d < D) ? Cvt<T>::to_f(vbase[(j0 + t0 + e) * p.v_ss + d]) : 0.f;
+                float a = 0.f;
+#pragma unroll
+                for (int e = 0; e < 8; ++e) a = fmaf(__shfl_sync(0xffffffffu, pj, t0 + e), vv[e], a);
+                // o[u] with a runtime u would leave the registers: select the slot with a compile-time loop
+#pragma unroll
+                for (int uu = 0; uu < kSimtMaxD / 32; ++uu)
+                    if (uu == u) o[uu] += a;
             }
         }
         m_run = m_new;
