@@ -79,3 +79,24 @@ def test_ops_have_no_cpu_kernel():
         pytest.skip("CPU test doubles already registered in this process")
     with pytest.raises((NotImplementedError, RuntimeError)):
         torch.ops.xg_sm100.rms_norm(torch.zeros(2, 8), torch.ones(8), 1e-6)
+
+
+def test_stack_or_view_reuses_slabs_of_one_buffer():
+    """Operands of a combo dense call that are consecutive slabs of one buffer are used in place; anything else is
+    stacked (host logic only, no GPU needed)."""
+    import torch
+
+    from xpu_graph_b200 import ops
+
+    base = torch.arange(4 * 6 * 8, dtype=torch.float32).reshape(4, 6, 8)
+    v = ops._stack_or_view(list(base.unbind(0)))
+    assert v.data_ptr() == base.data_ptr() and torch.equal(v, base)
+    mid = ops._stack_or_view(list(base[1:3].unbind(0)))
+    assert mid.data_ptr() == base[1].data_ptr() and torch.equal(mid, base[1:3])
+    separate = [base[i].clone() for i in range(4)]
+    w = ops._stack_or_view(separate)
+    assert w.data_ptr() not in {t.data_ptr() for t in separate} and torch.equal(w, base)
+    shuffled = [base[2], base[0], base[1]]
+    assert torch.equal(ops._stack_or_view(shuffled), torch.stack(shuffled))
+    strided = [base[:, i, :] for i in range(3)]  # not contiguous slabs
+    assert torch.equal(ops._stack_or_view(strided), torch.stack(strided))
