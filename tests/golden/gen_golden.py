@@ -15,6 +15,9 @@ What is recorded (inputs and outputs, all seeded, all small):
       - slice + cat graphs incl. the INT64_MAX / negative-end cases of tests/mlu/test_fuse_slice_cat.py:293-323,
       - multi-slice + stack, embedding + where + stack, RoPE and SwiGLU chains,
       - the three benchmark graphs at reduced size (encoder block, Llama-style layer, recsys graph).
+`python tests/golden/gen_golden.py v2` writes tests/golden/golden_v2.pt the same way: slice -> sum -> cat,
+mul -> sum -> cat and sum -> cat graphs (targets/mlu/fuse_sum_cat.py, fuse_mul_sum_cat.py), a chain of three dense
+layers, four parallel dense layers of one shape, and a bmm + bias + GELU graph.
 The torch-version shims of xpu_graph_b200/target/compat.py are the only thing between this script and
 the unmodified reference.
 """
@@ -170,5 +173,65 @@ def main():
     print(f"wrote {out}: {len(G)} cases, {os.path.getsize(out) / 1024:.0f} KiB")
 
 
+def main_v2():
+    """Second fixture file: the row-sum fusions, chained / parallel / batched dense layers (added after golden_v1.pt;
+    a separate file and generator so that the first one is never rewritten)."""
+    G = {}
+    g = torch.Generator().manual_seed(4321)
+
+    def rn(*shape, dtype=torch.float32, std=1.0):
+        return (torch.randn(*shape, generator=g) * std).to(dtype)
+
+    for dt, tag in ((torch.float32, "f32"), (torch.bfloat16, "bf16")):
+        x = rn(6, 40, 16, dtype=dt)
+        for name, sl in (("prefix", [(0, 10), (0, 25), (0, 40), (0, 4)]), ("general", [(3, 10), (0, 25), (12, 40)])):
+            G[f"slice_sum_cat_{name}_{tag}"] = dict(x=x, slices=sl, y=run_ref(
+                lambda t, sl=sl: torch.cat([t[:, a:b, :].sum(dim=1) for a, b in sl], dim=-1) + 0, x))
+        a = [rn(6, 5, 8, dtype=dt) for _ in range(3)]
+        b = [rn(1 if i == 1 else 6, 5, 8, dtype=dt) for i in range(3)]
+        G[f"mul_sum_cat_{tag}"] = dict(a=a, b=b, y=run_ref(
+            lambda a0, a1, a2, b0, b1, b2: torch.cat([(a0 * b0).sum(dim=1), (a1 * b1).sum(dim=1), (a2 * b2).sum(dim=1)], dim=-1) + 0, *a, *b))
+        ys = [rn(6, r, 8, dtype=dt) for r in (3, 7, 4)]
+        G[f"sum_cat_{tag}"] = dict(xs=ys, y=run_ref(lambda y0, y1, y2: torch.cat([y0.sum(dim=1), y1.sum(dim=1), y2.sum(dim=1)], dim=-1) + 0, *ys))
+
+    # chained dense layers (the dense tower) and parallel same-shape ones (the combo dense layer), fp32 / bf16
+    x = rn(12, 24)
+    ws = [rn(32, 24, std=0.2), rn(16, 32, std=0.2), rn(8, 16, std=0.2)]
+    bs = [rn(32, std=0.1), rn(16, std=0.1), rn(8, std=0.1)]
+
+    def tower(x, w0, w1, w2, b0, b1, b2):
+        h = torch.relu(F.linear(x, w0, b0))
+        h = torch.relu(F.linear(h, w1, b1))
+        return F.linear(h, w2, b2)
+
+    G["dense_tower_f32"] = dict(x=x, ws=ws, bs=bs, acts=["relu", "relu", "none"], y=run_ref(tower, x, *ws, *bs))
+    xs = [rn(10, 16, dtype=torch.bfloat16) for _ in range(4)]
+    wc = [rn(24, 16, dtype=torch.bfloat16, std=0.2) for _ in range(4)]
+    bc = [rn(24, dtype=torch.bfloat16, std=0.1) for _ in range(4)]
+
+    def combo(*t):
+        return tuple(torch.relu(F.linear(t[i], t[4 + i], t[8 + i])) for i in range(4))
+
+    G["combo_dense_bf16"] = dict(xs=xs, ws=wc, bs=bc, act="relu", y=list(run_ref(combo, *xs, *wc, *bc)))
+    xb, wb, bb = rn(3, 10, 16), rn(3, 16, 12, std=0.2), rn(3, 1, 12, std=0.1)
+    G["batch_dense_f32"] = dict(x=xb, w=wb, b=bb, act="gelu", y=run_ref(lambda x, w, b: F.gelu(torch.bmm(x, w) + b), xb, wb, bb))
+
+    def compact(o):
+        if isinstance(o, torch.Tensor):
+            return o.detach().clone().contiguous()
+        if isinstance(o, dict):
+            return {k: compact(v) for k, v in o.items()}
+        if isinstance(o, (list, tuple)):
+            return type(o)(compact(v) for v in o)
+        return o
+
+    out = os.path.join(HERE, "golden_v2.pt")
+    torch.save(compact(G), out)
+    print(f"wrote {out}: {len(G)} cases, {os.path.getsize(out) / 1024:.0f} KiB")
+
+
 if __name__ == "__main__":
-    main()
+    if len(sys.argv) > 1 and sys.argv[1] == "v2":
+        main_v2()
+    else:
+        main()

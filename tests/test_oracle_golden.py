@@ -114,3 +114,39 @@ def test_benchmark_graphs_small(G):
     m, inp = make_recsys(**c["args"])
     with torch.no_grad():
         _close(m(*inp), c["y"], "recsys")
+
+
+# ---- second fixture file: row-sum fusions, chained / parallel / batched dense layers ------------------------------
+GOLDEN2 = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "golden_v2.pt")
+
+
+@pytest.fixture(scope="module")
+def G2():
+    return torch.load(GOLDEN2)
+
+
+@pytest.mark.parametrize("tag", ["f32", "bf16"])
+def test_row_sum_fusions(G2, tag):
+    for name in ("prefix", "general"):
+        c = G2[f"slice_sum_cat_{name}_{tag}"]
+        assert_bit_exact(ref_ops.slice_sum_cat(c["x"], c["slices"]), c["y"], f"slice_sum_cat {name}")
+    c = G2[f"mul_sum_cat_{tag}"]
+    ml = []
+    for a, b in zip(c["a"], c["b"]):
+        ml += [a, b]
+    assert_bit_exact(ref_ops.mul_sum_cat(ml), c["y"], "mul_sum_cat")
+    c = G2[f"sum_cat_{tag}"]
+    assert_bit_exact(ref_ops.sum_cat(c["xs"]), c["y"], "sum_cat")
+
+
+def test_dense_chains(G2):
+    c = G2["dense_tower_f32"]
+    y = c["x"]
+    for w, b, a in zip(c["ws"], c["bs"], c["acts"]):
+        y = ref_ops.dense(y, w, True, b, a)
+    _close(y, c["y"], "dense tower")
+    c = G2["combo_dense_bf16"]
+    for x, w, b, want in zip(c["xs"], c["ws"], c["bs"], c["y"]):
+        _close(ref_ops.dense(x, w, True, b, c["act"]), want, "combo dense member")
+    c = G2["batch_dense_f32"]
+    _close(ref_ops.batch_dense(c["x"], c["w"], False, c["b"], c["act"]), c["y"], "batch dense")
