@@ -93,3 +93,27 @@ def test_rowsum_cat_rejects_bad_arguments(cuda_device):
     assert L.xg_rowsum_cat(a, a, bs, None, lib.i64_array([0, 4]), 1, 2, 8, out.data_ptr(), 8, 0, None) == -1      # strides missing
     assert L.xg_rowsum_cat(a, None, bs, None, lib.i64_array([0, 4]), 1, 2, 8, out.data_ptr(), 8, 9, None) == -1   # dtype
     assert b"xg_rowsum_cat" in ctypes.c_char_p(L.xg_last_error()).value
+
+
+@pytest.mark.parametrize("tag", ["f32", "bf16"])
+def test_against_reference_fixtures(cuda_device, tag):
+    """The same graphs as recorded from the reference's own pipeline (tests/golden/golden_v2.pt)."""
+    import os
+
+    from xpu_graph_b200.modules import MulSumCatModule, SliceSumCatModule, SumCatModule
+
+    G = torch.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "golden_v2.pt"))
+    for name in ("prefix", "general"):
+        c = G[f"slice_sum_cat_{name}_{tag}"]
+        got = SliceSumCatModule(c["slices"])(c["x"].to(cuda_device))
+        mag = ref_ops.slice_sum_cat(c["x"].float().abs(), c["slices"]) * (1e-2 if tag == "bf16" else 1e-3)
+        assert_parity(got, c["y"], f"fixture slice_sum_cat {name} {tag}", magnitude=mag)
+    c = G[f"mul_sum_cat_{tag}"]
+    ml = []
+    for a, b in zip(c["a"], c["b"]):
+        ml += [a.to(cuda_device), b.to(cuda_device)]
+    mag = ref_ops.mul_sum_cat([t.float().abs().cpu() for t in ml]) * (1e-2 if tag == "bf16" else 1e-3)
+    assert_parity(MulSumCatModule()(ml), c["y"], f"fixture mul_sum_cat {tag}", magnitude=mag)
+    c = G[f"sum_cat_{tag}"]
+    mag = ref_ops.sum_cat([t.float().abs() for t in c["xs"]]) * (1e-2 if tag == "bf16" else 1e-3)
+    assert_parity(SumCatModule()([t.to(cuda_device) for t in c["xs"]]), c["y"], f"fixture sum_cat {tag}", magnitude=mag)

@@ -113,6 +113,19 @@ constexpr int UMMA_K = 16;
 constexpr int kGemmThreads = 192;
 constexpr int GROUP_M = 16;
 
+// Scalar kernel parameters. The struct is kept at 128 bytes: next to three tensor maps the parameter block is then
+// exactly 512 bytes. (Measured: 16 bytes more cost the CTA-pair kernel 5 % of its throughput and 30 % with a residual
+// epilogue - the same source with a padded struct reproduces it - so the fields of the mutually exclusive variants
+// share storage.)
+enum GemmMode : int {
+    kModePlain = 0,      // 16-bit output; split-K when splits > 1 (split.partial)
+    kModeRope = 1,       // rotary-embedding epilogue (rope.*)
+    kModeF32 = 2,        // fp32 problem from bf16 planes: out, bias and residual are fp32 (f32.*)
+    kModeF32Planes = 3,  // same, out is the next layer's operand: three bf16 planes per row ([M, 3 * out_kp], columns
+                         // N..out_kp-1 zero), bias fp32, no residual
+    kModeBatch = 4,      // batched (single-CTA kernel): 3-D tensor maps, work units (entry, tile) (batch.*)
+};
+
 struct GemmParams {
     void* out;
     const void* bias;
@@ -122,35 +135,50 @@ struct GemmParams {
     int vec_ok;       // out (and residual) rows are 16-byte addressable
     int bias_vec_ok;  // bias pointer 16-byte aligned
     int num_m_blocks, num_n_blocks, num_k_blocks;
-    const void* rope_cos;  // non-null: rotary-embedding epilogue (see GemmExtras)
-    const void* rope_sin;
-    int64_t rope_S;
-    int rope_D;
-    int splits;      // > 1: split-K, every (tile, split) unit writes raw fp32 accumulators to `partial`
-    float* partial;  // [splits][M][N] fp32 workspace (split-K only)
-    // Operands made of K-segments laid side by side (the three bf16 planes of an fp32 matrix): the k-blocks run over
-    // `seg_blocks`-long segment PAIRS, pair i reading segment (seg_a >> 4i) & 15 of A against (seg_b >> 4i) & 15 of W.
-    int seg_blocks = 0;
-    uint32_t seg_a = 0, seg_b = 0;
-    // fp32 problems (operands given as bf16 planes): 1 = out, bias and residual are fp32; 2 = out is the next layer's
-    // operand, three bf16 planes per row ([M, 3 * out_kp], columns N..out_kp-1 zero), bias fp32, no residual.
-    int f32_mode = 0;
-    int64_t out_kp = 0;
-    // Batched problems (single-CTA kernel): the tensor maps carry the batch as a third dimension, a work unit is
-    // (batch entry, tile), and out / bias / residual advance by these many elements per entry.
-    int batch = 1;
-    int64_t bs_out = 0, bs_bias = 0, bs_res = 0;
+    int splits;  // > 1: split-K, every (tile, split) unit writes raw fp32 accumulators to split.partial
+    int mode;    // GemmMode
+    union {
+        struct {
+            float* partial;  // [splits][M][N] fp32 workspace
+        } split;
+        struct {
+            const void* cos;
+            const void* sin;
+            int64_t S;
+            int D;
+        } rope;
+        struct {
+            // Operands made of K-segments laid side by side (the three bf16 planes of an fp32 matrix): the k-blocks run
+            // over `seg_blocks`-long segment PAIRS, pair i reading segment (seg_a >> 4i) & 15 of A against
+            // (seg_b >> 4i) & 15 of W.
+            int seg_blocks;
+            uint32_t seg_a, seg_b;
+            int pad_;
+            int64_t out_kp;
+        } f32;
+        struct {
+            int64_t bs_out, bs_bias, bs_res;  // elements per entry
+            int count;
+        } batch;
+    };
 };
+static_assert(sizeof(GemmParams) == 128, "GemmParams must stay at 128 bytes (512-byte kernel parameter block)");
+
+__host__ __device__ __forceinline__ int f32_mode_of(const GemmParams& p) {
+    return p.mode == kModeF32 ? 1 : (p.mode == kModeF32Planes ? 2 : 0);
+}
+__host__ __device__ __forceinline__ int batch_of(const GemmParams& p) { return p.mode == kModeBatch ? p.batch.count : 1; }
 
 // Element offsets along K of k-block kb in the A and the W tensor map.
 __device__ __forceinline__ void kblock_coords(const GemmParams& p, int kb, int& ka, int& kw) {
-    if (p.seg_blocks == 0) {
+    if (f32_mode_of(p) == 0) {
         ka = kw = kb * BK;
         return;
     }
-    const int pair = kb / p.seg_blocks, kk = kb - pair * p.seg_blocks;
-    ka = ((int)((p.seg_a >> (4 * pair)) & 15u) * p.seg_blocks + kk) * BK;
-    kw = ((int)((p.seg_b >> (4 * pair)) & 15u) * p.seg_blocks + kk) * BK;
+    const int sb = p.f32.seg_blocks;
+    const int pair = kb / sb, kk = kb - pair * sb;
+    ka = ((int)((p.f32.seg_a >> (4 * pair)) & 15u) * sb + kk) * BK;
+    kw = ((int)((p.f32.seg_b >> (4 * pair)) & 15u) * sb + kk) * BK;
 }
 
 // k-block range of split s of `splits` over nkb blocks (balanced, every split non-empty when splits <= nkb)
@@ -197,17 +225,23 @@ template <typename T, int BN, bool SWIGLU>
 __device__ __forceinline__ void epilogue_tile(const GemmParams& p, uint32_t tmem_base, int acc, int quad, int64_t row,
                                               bool row_ok, int nb, int split, int entry = 0) {
     constexpr int OUT_BN = SWIGLU ? BN / 2 : BN;
-    T* out = reinterpret_cast<T*>(p.out) + entry * p.bs_out;
-    const T* bias = p.bias ? reinterpret_cast<const T*>(p.bias) + entry * p.bs_bias : nullptr;
-    const T* resid = p.residual ? reinterpret_cast<const T*>(p.residual) + entry * p.bs_res : nullptr;
-    if (!SWIGLU && p.rope_cos != nullptr) {
+    T* out = reinterpret_cast<T*>(p.out);
+    const T* bias = reinterpret_cast<const T*>(p.bias);
+    const T* resid = reinterpret_cast<const T*>(p.residual);
+    if (p.mode == kModeBatch) {
+        out += entry * p.batch.bs_out;
+        if (bias) bias += entry * p.batch.bs_bias;
+        if (resid) resid += entry * p.batch.bs_res;
+    }
+    const int f32_mode = f32_mode_of(p);
+    if (!SWIGLU && p.mode == kModeRope) {
         // Rotary epilogue: the two halves of a head (columns j and j + D/2) meet in one thread, which owns the whole
         // row of the tile: read the two 32-column chunks that are D/2 apart, rotate, store both. The host guarantees
         // N % D == 0, D in {64, 128}, 16-byte addressable rows and tables.
-        const int D = p.rope_D, half_chunks = D / 64;  // chunks of 32 per half head: 1 (D = 64) or 2 (D = 128)
-        const int64_t pos = row_ok ? row % p.rope_S : 0;
-        const T* cosr = reinterpret_cast<const T*>(p.rope_cos) + pos * D;
-        const T* sinr = reinterpret_cast<const T*>(p.rope_sin) + pos * D;
+        const int D = p.rope.D, half_chunks = D / 64;  // chunks of 32 per half head: 1 (D = 64) or 2 (D = 128)
+        const int64_t pos = row_ok ? row % p.rope.S : 0;
+        const T* cosr = reinterpret_cast<const T*>(p.rope.cos) + pos * D;
+        const T* sinr = reinterpret_cast<const T*>(p.rope.sin) + pos * D;
 #pragma unroll 1
         for (int c = 0; c < OUT_BN / 32; ++c) {
             const int in_head = c % (2 * half_chunks);
@@ -247,7 +281,7 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams& p, uint32_t tmem
 #pragma unroll 1
     for (int c = 0; c < OUT_BN / 32; ++c) {
         const int64_t col0 = (int64_t)nb * OUT_BN + c * 32;
-        if (col0 >= (p.f32_mode == 2 ? p.out_kp : p.N)) break;  // warp-uniform
+        if (col0 >= (f32_mode == 2 ? p.f32.out_kp : p.N)) break;  // warp-uniform
         uint32_t r[32];
         const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(acc * BN + c * 32);
         ptx::tmem_ld_32x32(taddr, r);
@@ -262,7 +296,7 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams& p, uint32_t tmem
             for (int i = 0; i < 32; ++i) v[i] = __fdividef(v[i], 1.0f + __expf(-v[i])) * __uint_as_float(r[i]);
         }
         const bool full = (col0 + 32 <= p.N);
-        if (p.f32_mode != 0) {
+        if (f32_mode != 0) {
             const float* biasf = reinterpret_cast<const float*>(p.bias);
             if (biasf != nullptr) {
 #pragma unroll
@@ -270,7 +304,7 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams& p, uint32_t tmem
                     if (col0 + i < p.N) v[i] += biasf[col0 + i];
             }
             if (!row_ok) continue;
-            if (p.f32_mode == 1) {
+            if (f32_mode == 1) {
                 const float* rr = p.residual ? reinterpret_cast<const float*>(p.residual) + row * p.ldr + col0 : nullptr;
                 float* orow = reinterpret_cast<float*>(p.out) + row * p.ldc + col0;
                 if (full && p.vec_ok) {
@@ -292,10 +326,10 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams& p, uint32_t tmem
                 }
             } else {
                 // next layer's operand: x = x0 + x1 + x2 in bf16, plane s at columns [s * out_kp, s * out_kp + out_kp)
-                __nv_bfloat16* o3 = reinterpret_cast<__nv_bfloat16*>(p.out) + row * (3 * p.out_kp) + col0;
+                __nv_bfloat16* o3 = reinterpret_cast<__nv_bfloat16*>(p.out) + row * (3 * p.f32.out_kp) + col0;
 #pragma unroll
                 for (int i = 0; i < 32; i += 8) {
-                    if (col0 + i >= p.out_kp) break;
+                    if (col0 + i >= p.f32.out_kp) break;
                     Vec16<__nv_bfloat16> q0, q1, q2;
 #pragma unroll
                     for (int j = 0; j < 8; ++j) {
@@ -306,8 +340,8 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams& p, uint32_t tmem
                         q2.v[j] = __float2bfloat16_rn(r1 - __bfloat162float(q1.v[j]));
                     }
                     st16(o3 + i, q0);
-                    st16(o3 + p.out_kp + i, q1);
-                    st16(o3 + 2 * p.out_kp + i, q2);
+                    st16(o3 + p.f32.out_kp + i, q1);
+                    st16(o3 + 2 * p.f32.out_kp + i, q2);
                 }
             }
             continue;
@@ -315,7 +349,7 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams& p, uint32_t tmem
         if (p.splits > 1) {
             // split-K: raw fp32 partial sums; bias / residual / activation happen in the reduce kernel
             if (row_ok) {
-                float* prow = p.partial + ((int64_t)split * p.M + row) * p.N + col0;
+                float* prow = p.split.partial + ((int64_t)split * p.M + row) * p.N + col0;
                 if (full && (p.N & 3) == 0) {
 #pragma unroll
                     for (int i = 0; i < 32; i += 4)
@@ -424,7 +458,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     const uint32_t tmem_base = *tmem_base_slot;
 
     const int tiles_per_entry = p.num_m_blocks * p.num_n_blocks;
-    const int num_tiles = tiles_per_entry * p.splits * p.batch;  // work units: (batch entry, tile, split); batch > 1 has no splits
+    const int num_tiles = tiles_per_entry * p.splits * batch_of(p);  // work units: (batch entry, tile, split); batch > 1 has no splits
     const int nkb = p.num_k_blocks;
 
     if (warp == 0) {
@@ -448,7 +482,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                     ptx::mbar_arrive_expect_tx(&full_bar[stage], Cfg::STAGE_BYTES);
                     int ka, kw;
                     kblock_coords(p, kb, ka, kw);
-                    if (p.batch > 1) {  // 3-D maps (k, row, entry); plain and [K, N] weights only
+                    if (p.mode == kModeBatch) {  // 3-D maps (k, row, entry); plain and [K, N] weights only
                         ptx::tma_load_3d(smem_a + stage * Cfg::A_BYTES, &tmap_a, &full_bar[stage], ka, mb * BM, entry);
                         if (B_MN) {
 #pragma unroll
@@ -800,7 +834,7 @@ __global__ void __launch_bounds__(256) splitk_reduce_kernel(const GemmParams p) 
     float acc[4] = {0.f, 0.f, 0.f, 0.f};
     const bool vec = (ncol == 4) && ((p.N & 3) == 0);
     for (int s = 0; s < p.splits; ++s) {  // fixed order: deterministic
-        const float* src = p.partial + ((int64_t)s * p.M + row) * p.N + col0;
+        const float* src = p.split.partial + ((int64_t)s * p.M + row) * p.N + col0;
         if (vec) {
             const float4 f = *reinterpret_cast<const float4*>(src);
             acc[0] += f.x; acc[1] += f.y; acc[2] += f.z; acc[3] += f.w;
@@ -830,7 +864,7 @@ int launch_gemm_tc(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorM
         return fail(XG_ERR_LAUNCH, "xg_gemm_bias_act: cannot reserve %d bytes of shared memory: %s", Cfg::SMEM_BYTES,
                     cudaGetErrorString(e));
     }
-    const int64_t tiles = (int64_t)p.num_m_blocks * p.num_n_blocks * p.splits * p.batch;
+    const int64_t tiles = (int64_t)p.num_m_blocks * p.num_n_blocks * p.splits * batch_of(p);
     const int grid = (int)(tiles < num_sms() ? tiles : num_sms());
     kern<<<grid, kGemmThreads, Cfg::SMEM_BYTES, st>>>(ta, tb, tb2, p);
     int rc = check_launch("xg_gemm_bias_act");
@@ -930,10 +964,15 @@ int gemm_tc_dispatch(const void* A, const void* B, const void* bias, const void*
     p.residual = residual;
     p.M = M; p.N = N; p.K = K; p.ldc = ldc; p.ldr = ldr;
     p.act = act;
-    p.rope_cos = ex ? ex->rope_cos : nullptr;
-    p.rope_sin = ex ? ex->rope_sin : nullptr;
-    p.rope_S = ex ? ex->rope_S : 0;
-    p.rope_D = ex ? ex->rope_D : 0;
+    p.mode = kModePlain;
+    p.split.partial = nullptr;
+    if (ex && ex->rope_cos) {
+        p.mode = kModeRope;
+        p.rope.cos = ex->rope_cos;
+        p.rope.sin = ex->rope_sin;
+        p.rope.S = ex->rope_S;
+        p.rope.D = ex->rope_D;
+    }
     p.vec_ok = (ldc % 8 == 0) && aligned16(out) && (!residual || (ldr % 8 == 0 && aligned16(residual)));
     p.bias_vec_ok = bias ? aligned16(bias) : 0;
     if (trans_b && pl.splits == 1 && use_cta_pairs(M, N, 256)) {
@@ -945,14 +984,13 @@ int gemm_tc_dispatch(const void* A, const void* B, const void* bias, const void*
         p.num_n_blocks = (int)((N + 255) / 256);
         p.num_k_blocks = (int)((K + BK - 1) / BK);
         p.splits = 1;
-        p.partial = nullptr;
         return launch_gemm_pair<T, false>(ta, tbp, tbp, p, st);
     }
     p.num_m_blocks = (int)mblk;
     p.num_n_blocks = (int)((N + bn - 1) / bn);
     p.num_k_blocks = (int)((K + BK - 1) / BK);
     p.splits = pl.splits;
-    p.partial = pl.splits > 1 ? reinterpret_cast<float*>(workspace) : nullptr;
+    if (pl.splits > 1) p.split.partial = reinterpret_cast<float*>(workspace);  // (never together with the rotary epilogue)
     if (!trans_b) {
         switch (bn) {
             case 256: return launch_gemm_tc<T, 256, false, true>(ta, tb, tb, p, st);
@@ -982,16 +1020,13 @@ int gemm_swiglu_dispatch(const void* A, const void* Wg, const void* Wu, void* ou
     p.residual = nullptr;
     p.M = M; p.N = N; p.K = K; p.ldc = ldc; p.ldr = 0;
     p.act = XG_ACT_NONE;
-    p.rope_cos = nullptr;
-    p.rope_sin = nullptr;
-    p.rope_S = 0;
-    p.rope_D = 0;
+    p.mode = kModePlain;
     p.vec_ok = (ldc % 8 == 0) && aligned16(out);
     p.bias_vec_ok = 0;
     p.num_n_blocks = (int)((N + 127) / 128);
     p.num_k_blocks = (int)((K + BK - 1) / BK);
     p.splits = 1;
-    p.partial = nullptr;
+    p.split.partial = nullptr;
     if (use_cta_pairs(M, N, 128)) {
         p.num_m_blocks = (int)((M + 255) / 256);
         return launch_gemm_pair<T, true>(ta, tg, tu, p, st);
@@ -1041,21 +1076,18 @@ static int bgemm_tc_dispatch(const void* A, const void* B, const void* bias, con
     p.residual = residual;
     p.M = M; p.N = N; p.K = K; p.ldc = ldc; p.ldr = ldr;
     p.act = act;
-    p.rope_cos = nullptr;
-    p.rope_sin = nullptr;
-    p.rope_S = 0;
-    p.rope_D = 0;
+    p.mode = kModePlain;
     p.vec_ok = (ldc % 8 == 0) && (sc % 8 == 0) && aligned16(out) && (!residual || (ldr % 8 == 0 && sr % 8 == 0 && aligned16(residual)));
     p.bias_vec_ok = bias ? (aligned16(bias) && sbias % 8 == 0) : 0;
     p.num_m_blocks = (int)mblk;
     p.num_n_blocks = (int)((N + bn - 1) / bn);
     p.num_k_blocks = (int)((K + BK - 1) / BK);
     p.splits = 1;
-    p.partial = nullptr;
-    p.batch = (int)batch;
-    p.bs_out = sc;
-    p.bs_bias = sbias;
-    p.bs_res = sr;
+    p.mode = kModeBatch;
+    p.batch.count = (int)batch;
+    p.batch.bs_out = sc;
+    p.batch.bs_bias = sbias;
+    p.batch.bs_res = sr;
     if (!trans_b) {
         switch (bn) {
             case 256: return launch_gemm_tc<T, 256, false, true>(ta, tb, tb, p, st);
@@ -1110,21 +1142,18 @@ int gemm_f32x3_entry(const void* A3, const void* W3, const void* bias, const voi
     p.residual = residual;
     p.M = M; p.N = N; p.K = 3 * Kp; p.ldc = ldc; p.ldr = ldr;
     p.act = act;
-    p.rope_cos = nullptr;
-    p.rope_sin = nullptr;
-    p.rope_S = 0;
-    p.rope_D = 0;
+    p.mode = kModePlain;
     // fp32 rows in 16-byte steps (four floats)
     p.vec_ok = (ldc % 4 == 0) && aligned16(out) && (!residual || (ldr % 4 == 0 && aligned16(residual)));
     p.bias_vec_ok = 0;
     p.splits = 1;
-    p.partial = nullptr;
-    p.f32_mode = out_planes ? 2 : 1;
-    p.out_kp = out_planes ? (N + BK - 1) / BK * BK : 0;
-    p.seg_blocks = (int)(Kp / BK);
-    p.seg_a = 0x010120u;  // pairs (A plane, W plane): (0,2) (2,0) (1,1) (0,1) (1,0) (0,0)
-    p.seg_b = 0x001102u;
-    p.num_k_blocks = 6 * p.seg_blocks;
+    p.mode = out_planes ? kModeF32Planes : kModeF32;
+    p.f32.out_kp = out_planes ? (N + BK - 1) / BK * BK : 0;
+    p.f32.seg_blocks = (int)(Kp / BK);
+    p.f32.seg_a = 0x010120u;  // pairs (A plane, W plane): (0,2) (2,0) (1,1) (0,1) (1,0) (0,0)
+    p.f32.seg_b = 0x001102u;
+    p.f32.pad_ = 0;
+    p.num_k_blocks = 6 * p.f32.seg_blocks;
     CUtensorMap ta, tb;
     if (!make_tmap_2d_16bit(&ta, A3, (uint64_t)M, (uint64_t)(3 * Kp), (uint64_t)(3 * Kp), BM, BK, true))
         return fail(XG_ERR_UNSUPPORTED, "xg_gemm_f32x3: tensor-map encoding failed");
