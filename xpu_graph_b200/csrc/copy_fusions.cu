@@ -237,13 +237,14 @@ extern "C" int xg_seg_copy(const void* const* src_ptrs, void* const* dst_ptrs, c
     p.zero_when = mask_zero_when;
     auto flush = [&]() -> int {
         if (p.nseg == 0) return XG_OK;
-        // ~8192 units per CTA, but at least ~4 CTAs per SM when the row count allows it.
-        int64_t rpc = kLutMax / p.width;
-        const int64_t min_rows = unit >= 16 ? kCopyUnroll : 2 * kCopyUnroll;  // the rows a thread takes at once
-        if (rpc < min_rows) rpc = min_rows;  // also amortises the look-up table build for wide rows
-        const int64_t want_ctas = 4LL * num_sms();
-        const int64_t cap = (rows + want_ctas - 1) / want_ctas;
-        if (rpc > cap) rpc = cap;
+        // Rows per CTA: every CTA first copies the segment list out of the (large) parameter block and builds the
+        // look-up table, so a CTA should take many rows - about 16 CTAs per SM over the whole launch - but never
+        // fewer than a thread takes at once.
+        const int64_t min_rows = unit >= 16 ? kCopyUnroll : 2 * kCopyUnroll;
+        const int64_t want_ctas = 16LL * num_sms();
+        int64_t rpc = (rows + want_ctas - 1) / want_ctas;
+        rpc = (rpc + min_rows - 1) / min_rows * min_rows;  // whole groups of the rows a thread takes at once
+        if (rpc * p.width > 0x3fffffffLL) rpc = 0x3fffffffLL / p.width;  // the narrow-row path indexes rows * width in 32 bits
         if (rpc < 1) rpc = 1;
         p.rows_per_cta = (int32_t)rpc;
         int rc = dispatch_seg_copy(unit, p, st);
