@@ -182,8 +182,11 @@ int xg_gemm_f32x3(const void* A3, const void* W3, const void* bias, const void* 
 
 /*
  * Batched form: out[b] = act( A[b] @ W[b] + bias[b] + residual[b] ), batch strides in elements
- * (0 broadcasts). Replaces: dense_layer_modules.py:71-120 (BatchDenseLayerModule) as called by
- * passes/patterns/structure/custom_denselayer.py:111-117.
+ * (0 broadcasts). 16-bit problems with positive, 16-byte aligned operand strides run as ONE launch over
+ * (entry, tile) work units; fp32 and broadcast operands run entry by entry.
+ * Replaces: dense_layer_modules.py:71-120 (BatchDenseLayerModule) as called by
+ * passes/patterns/structure/custom_denselayer.py:111-117; also the stacked-bmm form of
+ * targets/mlu/combo_matmul.py:53-87 (FusedCombineBmm.forward_bmm).
  */
 int xg_bgemm_bias_act(const void* A, const void* B, const void* bias, const void* residual, void* out,
                       int64_t batch, int64_t M, int64_t N, int64_t K, int64_t lda, int64_t ldb,
