@@ -318,6 +318,23 @@ def test_combo_dense(tgt, xlog):
         def forward(self, *xs):
             return tuple(torch.relu(layer(x)) for layer, x in zip(self.layers, xs))
 
+    class TwoLevels(torch.nn.Module):  # the second level's operands are the first level's results
+        def __init__(self):
+            super().__init__()
+            self.l1 = torch.nn.ModuleList(torch.nn.Linear(64, 64) for _ in range(4))
+            self.l2 = torch.nn.ModuleList(torch.nn.Linear(64, 48) for _ in range(4))
+
+        def forward(self, *xs):
+            hs = [torch.relu(layer(x)) for layer, x in zip(self.l1, xs)]
+            return tuple(layer(h) for layer, h in zip(self.l2, hs))
+
+    m = TwoLevels().to(torch.bfloat16).eval()
+    xs = [torch.randn(32, 64).to(torch.bfloat16) for _ in range(4)]
+    want, got, mods, atens = _compile(tgt, m, *xs)
+    for w, o in zip(want, got):
+        _same(o, w, 3e-2)
+    assert "xg_combo_dense" in mods and "custom_dense_layer_replacement" not in mods
+
     for n, fused in ((5, True), (3, False)):
         m = Towers(n).to(torch.bfloat16).eval()
         xs = [torch.randn(32, 64).to(torch.bfloat16) for _ in range(n)]

@@ -885,7 +885,7 @@ class FusedComboDense(Pattern):
                     n.replace_all_uses_with(item)
             for n in members:
                 gm.graph.erase_node(n)
-            changed = True
+            return True  # one group per sweep: the node order used above is stale now; the pass manager calls again
         return changed
 
 
@@ -911,6 +911,8 @@ class FusedDenseTower(Pattern):
 
         changed = False
         for tail in reversed(list(gm.graph.nodes)):
+            if getattr(tail, "_erased", False):
+                continue  # an inner layer of a chain that this sweep has already replaced
             if not is_dense(tail) or any(is_dense(u) and u.args[0] is tail and _only_user(tail, u) for u in tail.users):
                 continue  # not a dense layer, or not the last one of its chain
             chain = [tail]
