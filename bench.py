@@ -164,7 +164,7 @@ def run_reference(args) -> dict:
     return {
         "impl": "reference",
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": steps, "warmup": warmup,
-        "ms_per_step": sec * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "ms_per_step": sec * 1e3, "higher_is_better": True, "scaling": "strong" if strong else "weak", "vs_baseline": None,
         "dtype": "bf16", "data": "synthetic",
         "config": {"workload": WORKLOAD, "l2": "inputs_exceed_l2"},
         "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample},
@@ -196,10 +196,16 @@ def run_ours(args) -> dict | None:
     from xpu_graph_b200.workloads import make_llama_layer
 
     lib.load()
-    # Replica r owns samples [r*BATCH, (r+1)*BATCH) of the global batch: seeds differ per rank, weights do not.
-    lo, hi = shard_batch(world * BATCH, world, rank)
-    assert hi - lo == BATCH
-    layer, (x, cos, sin) = make_llama_layer(seed=3, batch=BATCH, seq=SEQ, hidden=HIDDEN, heads=HEADS, ffn=FFN,
+    # Weak scaling (default): every replica takes BATCH samples per step. --global-batch G: strong scaling, the G
+    # samples of a step are split evenly over the replicas.
+    strong = args.global_batch > 0
+    if strong and args.global_batch % world != 0:
+        raise SystemExit(f"--global-batch {args.global_batch} is not divisible by {world} GPUs")
+    per_gpu = args.global_batch // world if strong else BATCH
+    # Replica r owns samples [r*per_gpu, (r+1)*per_gpu) of the global batch: seeds differ per rank, weights do not.
+    lo, hi = shard_batch(world * per_gpu, world, rank)
+    assert hi - lo == per_gpu
+    layer, (x, cos, sin) = make_llama_layer(seed=3, batch=per_gpu, seq=SEQ, hidden=HIDDEN, heads=HEADS, ffn=FFN,
                                             dtype=torch.bfloat16, device="cpu")
     if rank > 0:
         g = torch.Generator().manual_seed(3 + 1000 * rank)
@@ -283,7 +289,7 @@ def run_ours(args) -> dict | None:
     launches = ops.launch_count()
     gemm_events, ops.GEMM_EVENTS = ops.GEMM_EVENTS, None
     ms_step = ms_total / steps
-    value = world * BATCH / (ms_step * 1e-3)
+    value = world * per_gpu / (ms_step * 1e-3)
 
     # dominant kernel: the tcgen05 GEMM; algorithmic FLOPs per launch / mean launch duration (CUDA events)
     gemm_ms = sum(a.elapsed_time(b) for a, b, _ in gemm_events)
@@ -326,7 +332,7 @@ def run_ours(args) -> dict | None:
     barrier()
     e2e_ms = max_over_ranks(e0.elapsed_time(e1)) / steps
     nbytes = x_host.numel() * x_host.element_size()
-    e2e = {"value": world * BATCH / (e2e_ms * 1e-3), "unit": UNIT, "h2d_bytes_per_step": nbytes, "d2h_bytes_per_step": nbytes,
+    e2e = {"value": world * per_gpu / (e2e_ms * 1e-3), "unit": UNIT, "h2d_bytes_per_step": nbytes, "d2h_bytes_per_step": nbytes,
            "ms_per_step": e2e_ms, "overlap": "3-stream pipeline: H2D(i+1) | compute(i) | D2H(i-1)"}
 
     status = lib.tc_status()
@@ -350,9 +356,9 @@ def run_ours(args) -> dict | None:
         return None
     return {
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": steps, "warmup": warmup,
-        "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong" if strong else "weak", "vs_baseline": None,
         "dtype": "bf16", "data": "synthetic",
-        "config": {"workload": WORKLOAD, "per_gpu_batch": BATCH, "global_batch": world * BATCH, "seq_len": SEQ,
+        "config": {"workload": WORKLOAD, "per_gpu_batch": per_gpu, "global_batch": world * per_gpu, "seq_len": SEQ,
                    "parallelism": f"replicas x{world} (no collectives)", "l2": "inputs_exceed_l2", "graph": via,
                    "tokens_per_s": value * SEQ},
         "clocks": sampler.summary(),
@@ -370,6 +376,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--global-batch", type=int, default=0,
+                    help="strong scaling: split this many samples per step over the GPUs (default: 8 samples per GPU, weak scaling)")
     ap.add_argument("--no-xpu-graph", action="store_true", help="time the assembled op sequence even if xpu_graph is importable")
     args = ap.parse_args()
     if args.impl == "reference":
