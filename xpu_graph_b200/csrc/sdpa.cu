@@ -478,6 +478,7 @@ int launch_flash_tc(const SdpaParams& p, cudaStream_t st) {
 // ---------------------------------------------------------------------------------------
 constexpr int kSimtWarps = 4;
 constexpr int kSimtMaxD = 256;
+constexpr int kSimtKeys = 16;  // key / value rows whose loads are in flight together (the loop is latency-bound)
 
 template <typename T>
 __global__ void __launch_bounds__(kSimtWarps * 32) sdpa_simt_kernel(const SdpaParams p) {
@@ -506,31 +507,33 @@ __global__ void __launch_bounds__(kSimtWarps * 32) sdpa_simt_kernel(const SdpaPa
         const int64_t j = j0 + lane;
         const int cnt = (int)((kv_end - j0) < 32 ? (kv_end - j0) : 32);
         // Scores of keys j0 .. j0+cnt-1. All lanes work on one key at a time, each on its slice of the head dim
-        // (coalesced 128-byte loads of the key row, then a warp reduction); four keys are in flight so that the
-        // loads and the shuffle chains overlap. Lane t keeps the score of key j0 + t. (A lane walking its own key
+        // (coalesced 128-byte loads of the key row, then a warp reduction); sixteen keys are in flight so that
+        // the loads and the shuffle chains overlap. Lane t keeps the score of key j0 + t. (A lane walking its own key
         // row would touch 32 different lines per load and saturate the L1 instead.)
         float s = -INFINITY;
-        for (int t0 = 0; t0 < cnt; t0 += 4) {
-            float part[4] = {0.f, 0.f, 0.f, 0.f};
+        for (int t0 = 0; t0 < cnt; t0 += kSimtKeys) {
+            float part[kSimtKeys];
+#pragma unroll
+            for (int e = 0; e < kSimtKeys; ++e) part[e] = 0.f;
             for (int u = 0; u < nu; ++u) {
                 const int d = lane + 32 * u;
                 float qv = 0.f;
 #pragma unroll
                 for (int uu = 0; uu < kSimtMaxD / 32; ++uu)
                     if (uu == u) qv = qreg[uu];
-                float kv[4];
+                float kv[kSimtKeys];  // all loads of the group are issued before the first use: one round trip per group
 #pragma unroll
-                for (int e = 0; e < 4; ++e)
+                for (int e = 0; e < kSimtKeys; ++e)
                     kv[e] = (t0 + e < cnt && d < D) ? Cvt<T>::to_f(kbase[(j0 + t0 + e) * p.k_ss + d]) : 0.f;
 #pragma unroll
-                for (int e = 0; e < 4; ++e) part[e] = fmaf(qv, kv[e], part[e]);
+                for (int e = 0; e < kSimtKeys; ++e) part[e] = fmaf(qv, kv[e], part[e]);
             }
 #pragma unroll
             for (int o2 = 16; o2 > 0; o2 >>= 1)
 #pragma unroll
-                for (int e = 0; e < 4; ++e) part[e] += __shfl_xor_sync(0xffffffffu, part[e], o2);
+                for (int e = 0; e < kSimtKeys; ++e) part[e] += __shfl_xor_sync(0xffffffffu, part[e], o2);
 #pragma unroll
-            for (int e = 0; e < 4; ++e)
+            for (int e = 0; e < kSimtKeys; ++e)
                 if (lane == t0 + e) s = part[e] * p.scale;
         }
         if (j < kv_end) {
@@ -545,20 +548,23 @@ __global__ void __launch_bounds__(kSimtWarps * 32) sdpa_simt_kernel(const SdpaPa
         l_run = l_run * alpha + warp_sum(pj);
 #pragma unroll
         for (int u = 0; u < kSimtMaxD / 32; ++u) o[u] *= alpha;
-        for (int t0 = 0; t0 < cnt; t0 += 8) {  // eight value rows in flight at a time
+        for (int t0 = 0; t0 < cnt; t0 += kSimtKeys) {  // a group of value rows in flight at a time
             for (int u = 0; u < nu; ++u) {
                 const int d = lane + 32 * u;
-                float vv[8];
+                float vv[kSimtKeys];
 #pragma unroll
-                for (int e = 0; e < 8; ++e)
+                for (int e = 0; e < kSimtKeys; ++e)
                     vv[e] = (t0 + e < cnt && d < D) ? Cvt<T>::to_f(vbase[(j0 + t0 + e) * p.v_ss + d]) : 0.f;
-                float a = 0.f;
+                float a0 = 0.f, a1 = 0.f;
 #pragma unroll
-                for (int e = 0; e < 8; ++e) a = fmaf(__shfl_sync(0xffffffffu, pj, t0 + e), vv[e], a);
+                for (int e = 0; e < kSimtKeys; e += 2) {
+                    a0 = fmaf(__shfl_sync(0xffffffffu, pj, t0 + e), vv[e], a0);
+                    a1 = fmaf(__shfl_sync(0xffffffffu, pj, t0 + e + 1), vv[e + 1], a1);
+                }
                 // o[u] with a runtime u would leave the registers: select the slot with a compile-time loop
 #pragma unroll
                 for (int uu = 0; uu < kSimtMaxD / 32; ++uu)
-                    if (uu == u) o[uu] += a;
+                    if (uu == u) o[uu] += a0 + a1;
             }
         }
         m_run = m_new;
