@@ -176,6 +176,12 @@ def run_reference(args) -> dict:
 # ------------------------------------------------------------------------------------------------
 # our arm
 # ------------------------------------------------------------------------------------------------
+def _pci_bus_id(dev) -> str:
+    """domain:bus:device.function of a CUDA device, as sysfs names it."""
+    pr = torch.cuda.get_device_properties(dev)
+    return f"{pr.pci_domain_id:04x}:{pr.pci_bus_id:02x}:{pr.pci_device_id:02x}.0"
+
+
 def run_ours(args) -> dict | None:
     import torch.distributed as dist
 
@@ -250,6 +256,13 @@ def run_ours(args) -> dict | None:
                     via += " [xpu_graph-compiled output differed from the assembled sequence: not used]"
         except Exception as e:  # keep the benchmark alive on any integration problem
             via += f" [xpu_graph path unavailable: {type(e).__name__}]"
+    # With several replicas on one host, each keeps its pinned buffers (first touch) and copy threads next to its own GPU.
+    if world > 1:
+        from xpu_graph_b200.replicas import bind_to_device_numa_node
+        try:
+            bind_to_device_numa_node(_pci_bus_id(dev))
+        except Exception:  # placement is an optimisation only
+            pass
     x_host = x.pin_memory()
     out_host = torch.empty_like(x_host).pin_memory()
     x_dev, cos, sin = x_host.to(dev), cos.to(dev), sin.to(dev)

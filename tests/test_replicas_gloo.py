@@ -70,3 +70,31 @@ def test_two_rank_gloo_replicas():
     assert slowest == pytest.approx(0.020)
     assert sums == [sum(range(0, 8)), sum(range(8, 16))]
     assert aggregate_throughput([per_rank] * world, [0.010, 0.020]) == pytest.approx(16 / 0.020)
+
+
+def test_numa_placement_reads_sysfs(tmp_path):
+    """bind_to_device_numa_node against a fake sysfs tree: the GPU's node and that node's CPU list decide the
+    affinity; unknown devices and node -1 change nothing."""
+    import os
+
+    from xpu_graph_b200 import replicas
+
+    dev = tmp_path / "bus/pci/devices/0000:1b:00.0"
+    dev.mkdir(parents=True)
+    (dev / "numa_node").write_text("1\n")
+    node = tmp_path / "devices/system/node/node1"
+    node.mkdir(parents=True)
+    have = sorted(os.sched_getaffinity(0))
+    (node / "cpulist").write_text(f"{have[0]}-{have[0]},4096-4100\n")
+    assert replicas.numa_cpus_of_pci_device("0000:1B:00.0", str(tmp_path)) == {have[0], 4096, 4097, 4098, 4099, 4100}
+    assert replicas.numa_cpus_of_pci_device("0000:99:00.0", str(tmp_path)) is None
+    before = replicas.bind_to_device_numa_node("1b:00.0", str(tmp_path))
+    try:
+        if len(have) > 1:
+            assert before == set(have) and os.sched_getaffinity(0) == {have[0]}
+        else:
+            assert before is None
+    finally:
+        os.sched_setaffinity(0, set(have))
+    (dev / "numa_node").write_text("-1\n")
+    assert replicas.bind_to_device_numa_node("0000:1b:00.0", str(tmp_path)) is None

@@ -5,7 +5,8 @@ contiguous slice of the global batch. These helpers are pure host logic (tested 
 """
 from __future__ import annotations
 
-from typing import List, Tuple
+import os
+from typing import List, Optional, Set, Tuple
 
 
 def shard_batch(global_batch: int, world_size: int, rank: int) -> Tuple[int, int]:
@@ -32,3 +33,52 @@ def aggregate_throughput(samples_per_rank: List[int], seconds_per_rank: List[flo
     if slowest <= 0:
         raise ValueError("non-positive time")
     return sum(samples_per_rank) / slowest
+
+
+# ---- host placement of a replica ---------------------------------------------------------------------------------
+def _parse_cpulist(text: str) -> Set[int]:
+    cpus: Set[int] = set()
+    for part in text.strip().split(","):
+        if not part:
+            continue
+        if "-" in part:
+            a, b = part.split("-")
+            cpus.update(range(int(a), int(b) + 1))
+        else:
+            cpus.add(int(part))
+    return cpus
+
+
+def numa_cpus_of_pci_device(pci_bus_id: str, sysfs: str = "/sys") -> Optional[Set[int]]:
+    """CPUs of the NUMA node that the PCI device (domain:bus:device.function) hangs off, or None when the
+    platform does not say (single node, virtualised, files missing)."""
+    bdf = pci_bus_id.lower()
+    if bdf.count(":") == 1:
+        bdf = "0000:" + bdf
+    try:
+        with open(os.path.join(sysfs, "bus/pci/devices", bdf, "numa_node")) as f:
+            node = int(f.read().strip())
+        if node < 0:
+            return None
+        with open(os.path.join(sysfs, "devices/system/node", f"node{node}", "cpulist")) as f:
+            return _parse_cpulist(f.read()) or None
+    except (OSError, ValueError):
+        return None
+
+
+def bind_to_device_numa_node(pci_bus_id: str, sysfs: str = "/sys") -> Optional[Set[int]]:
+    """Restrict this process to the CPUs next to its GPU, so that the pinned host buffers of the replica (first touch)
+    and its copy threads sit on the memory controller the GPU's PCIe root is attached to. With eight replicas on a
+    two-socket host this keeps half of the host <-> device traffic off the inter-socket link. Returns the previous
+    affinity (to restore it), or None when nothing was changed."""
+    if not hasattr(os, "sched_setaffinity"):
+        return None
+    want = numa_cpus_of_pci_device(pci_bus_id, sysfs)
+    if not want:
+        return None
+    before = set(os.sched_getaffinity(0))
+    allowed = want & before
+    if not allowed or allowed == before:
+        return None
+    os.sched_setaffinity(0, allowed)
+    return before
