@@ -63,6 +63,25 @@ def test_argument_validation_without_gpu():
     assert L.xg_gather_rows(None, None, 2, None, 2, 1, None, 1, None, 4, 8, 16, 3, None) == -1  # elem_size
     assert L.xg_seg_copy(None, None, None, None, None, 3, 4, None, 1, None) == -1
     assert L.xg_tc_status(None, 0) == -1
+    # the fp32-on-tensor-core entry points, the batched dense layer, the row-sum fusions
+    assert L.xg_gemm_f32x3_padded_k(1) == 64 and L.xg_gemm_f32x3_padded_k(64) == 64 and L.xg_gemm_f32x3_padded_k(65) == 128
+    assert L.xg_gemm_f32x3_padded_k(0) == 0
+    assert L.xg_split_bf16x3(None, 4, 8, 8, 0, p, None) == -1
+    assert L.xg_split_bf16x3(p, 4, 8, 4, 0, p, None) == -1  # ld < K
+    assert L.xg_split_bf16x3(p, -1, 8, 8, 0, p, None) == -1
+    assert L.xg_split_bf16x3(p, 0, 8, 8, 0, p, None) == 0
+    assert L.xg_gemm_f32x3(None, p, None, None, p, 4, 4, 8, 4, 0, 0, 0, None) == -1
+    assert L.xg_gemm_f32x3(p, p, None, None, p, 4, 4, 0, 4, 0, 0, 0, None) == -1  # K == 0
+    assert L.xg_gemm_f32x3(p, p, None, None, p, 4, 4, 8, 2, 0, 0, 0, None) == -1  # ldc < N
+    assert L.xg_gemm_f32x3(p, p, None, None, p, 4, 4, 8, 4, 0, 7, 0, None) == -1  # bad activation
+    assert L.xg_gemm_f32x3(p, p, None, p, p, 4, 4, 8, 4, 4, 0, 1, None) == -2     # plane output takes no residual
+    assert L.xg_bgemm_bias_act(p, p, None, None, p, -1, 4, 4, 8, 8, 8, 4, 0, 32, 32, 0, 0, 16, 1, 0, lib.XG_BF16, None) == -1
+    assert L.xg_bgemm_bias_act(p, p, None, None, p, 0, 4, 4, 8, 8, 8, 4, 0, 32, 32, 0, 0, 16, 1, 0, lib.XG_BF16, None) == 0
+    a1 = lib.ptr_array([p.value])
+    assert L.xg_rowsum_cat(a1, None, lib.i64_array([32]), None, lib.i64_array([0, 4]), 1, -2, 8, p, 8, lib.XG_F32, None) == -1
+    assert L.xg_rowsum_cat(a1, None, lib.i64_array([32]), None, lib.i64_array([0, 4]), 0, 2, 8, p, 8, lib.XG_F32, None) == 0
+    assert L.xg_sum3d(None, None, None, 2, 1, lib.XG_F32, None) == -1
+    assert L.xg_sum3d(None, None, None, 1, 5, lib.XG_F32, None) == -1  # dim
     # empty problems succeed without a launch
     assert L.xg_seg_copy(None, None, None, None, None, 0, 4, None, 1, None) == 0
     assert L.xg_swiglu(p, p, p, 0, 8, 8, 8, 8, lib.XG_F32, None) == 0
