@@ -52,6 +52,22 @@ def test_recsys_graph(cuda_device):
     assert_parity(got, want, "recsys graph fp32")
 
 
+def test_recsys_graph_full_size(cuda_device):
+    """Config 5 at its full size (batch 16384, 26 tables of 1e5 rows): here all three MLP layers are large enough for the
+    fp32 tensor-core path, so the graph ends in one dense-tower call; checked against the eager model on the CPU."""
+    from xpu_graph_b200 import ops
+    from xpu_graph_b200.fused_graphs import FusedRecsysGraph
+    from xpu_graph_b200.workloads import make_recsys
+
+    model, (dense, idx, mask) = make_recsys(seed=4)
+    assert dense.shape[0] == 16384
+    with torch.no_grad():
+        want = model(dense, idx, mask)
+    assert ops.dense_tower_eligible(16384, [64 + 26 * 64, 1024, 512, 256])
+    got = FusedRecsysGraph(model.to(cuda_device))(dense.to(cuda_device), idx.to(cuda_device), mask.to(cuda_device))
+    assert_parity(got, want, "recsys graph fp32, full size")
+
+
 def test_cuda_graph_replay_encoder(cuda_device):
     """Capture the fused encoder block once, replay it on new inputs (the reference's GraphRunner contract)."""
     from xpu_graph_b200.fused_graphs import FusedEncoderBlock

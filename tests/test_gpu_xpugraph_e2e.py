@@ -80,6 +80,18 @@ def test_recsys_graph_compiled_on_gpu(cuda_device):
                     "custom_dense_layer_replacement", "custom_dense_layer_replacement"], mods
 
 
+def test_recsys_graph_full_size_compiled_on_gpu(cuda_device):
+    """At the benchmark's batch of 16384 the three dense layers collapse into one dense-tower call."""
+    from xpu_graph_b200.workloads import make_recsys
+
+    model, (dense, idx, mask) = make_recsys(seed=4)
+    with torch.no_grad():
+        want = model(dense, idx, mask)
+    compiled, got, mods, atens = _compile_run(model.to(cuda_device), (dense.to(cuda_device), idx.to(cuda_device), mask.to(cuda_device)))
+    assert_parity(got, want, "compiled recsys graph, full size")
+    assert mods == ["xg_gather_stack", "fuse_slice_cat", "xg_cat_lastdim", "xg_dense_tower"], mods
+
+
 def test_device_graph_vendor_compiler(cuda_device):
     """vendor_compiler_config={"compiler": "device_graph"}: the rewritten encoder graph is captured into one CUDA
     graph and replayed; results stay equal to eager on new inputs and replay is faster than launch by launch."""
