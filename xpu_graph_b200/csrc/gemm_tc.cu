@@ -824,6 +824,9 @@ int launch_gemm_pair(const CUtensorMap& ta, const CUtensorMap& tb, const CUtenso
 // Second pass of split-K: out = act(sum_s partial[s] + bias + residual), 4 columns per thread.
 template <typename T>
 __global__ void __launch_bounds__(256) splitk_reduce_kernel(const GemmParams p) {
+    // Launched with programmatic stream serialisation: its CTAs may be placed while the GEMM is still draining; this
+    // returns once the GEMM grid has completed and its partial sums are visible.
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     const int64_t n4 = (p.N + 3) / 4;
     const int64_t total = p.M * n4;
     const int64_t idx = (int64_t)blockIdx.x * 256 + threadIdx.x;
@@ -870,8 +873,22 @@ int launch_gemm_tc(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorM
     int rc = check_launch("xg_gemm_bias_act");
     if (rc != XG_OK || p.splits <= 1) return rc;
     const int64_t total = p.M * ((p.N + 3) / 4);
-    splitk_reduce_kernel<T><<<(unsigned)((total + 255) / 256), 256, 0, st>>>(p);
-    return check_launch("xg_gemm_bias_act (split-K reduce)");
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)((total + 255) / 256));
+    cfg.blockDim = dim3(256);
+    cfg.dynamicSmemBytes = 0;
+    cfg.stream = st;
+    cudaLaunchAttribute attr;
+    attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr.val.programmaticStreamSerializationAllowed = 1;  // overlap this launch's latency with the GEMM's tail
+    cfg.attrs = &attr;
+    cfg.numAttrs = 1;
+    cudaError_t le = cudaLaunchKernelEx(&cfg, splitk_reduce_kernel<T>, p);
+    if (le != cudaSuccess) {
+        cudaGetLastError();
+        return fail(XG_ERR_LAUNCH, "xg_gemm_bias_act (split-K reduce): %s", cudaGetErrorString(le));
+    }
+    return XG_OK;
 }
 
 }  // namespace
