@@ -314,6 +314,25 @@ flash_tc_kernel(const __grid_constant__ CUtensorMap tmq, const __grid_constant__
                 ptx::tc_fence_after();
                 const uint32_t s_taddr = tmem_base + lane_field + (uint32_t)(sb * FN);
                 const int col_base = j * FN;
+                // A block needs the general masking code when it carries an additive mask, crosses the end of the
+                // keys or has a non-positive scale. A block that is only cut by the causal diagonal is classified per
+                // warp (a warp owns 32 consecutive query rows): all keys visible, some, or none.
+                const bool general_mask = (p.mask != nullptr) || (col_base + FN > skv) || !(sl2 > 0.f);
+                const int warp_row0 = q0 + quad * 32;
+                const bool diag_none = !general_mask && p.causal && (col_base > warp_row0 + 31);
+                const bool diag_some = !general_mask && p.causal && !diag_none && (col_base + FN - 1 > warp_row0);
+                if (diag_none) {
+                    // every key of the block lies beyond the diagonal for these rows: the probabilities are zero and
+                    // neither the running maximum nor the row sum moves
+                    uint32_t zero[32];
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) zero[i] = 0u;
+                    ptx::tmem_st_32x32(s_taddr, zero);
+                    ptx::tmem_st_wait();
+                    ptx::tc_fence_before();
+                    ptx::mbar_arrive(&p_full[sb]);
+                    continue;
+                }
                 float sc[FN];  // raw scores; exp2(sc * mul - m) is the probability
                 {
                     uint32_t r0[32], r1[32];
@@ -327,8 +346,13 @@ flash_tc_kernel(const __grid_constant__ CUtensorMap tmq, const __grid_constant__
                     }
                 }
                 float mul = sl2;
-                const bool masked_block = (p.mask != nullptr) || (col_base + FN > skv) || (p.causal && (col_base + FN - 1 > q0));
-                if (masked_block || !(sl2 > 0.f)) {  // uniform over the CTA; scores go to the log2 domain here
+                if (diag_some) {  // raw scores beyond the diagonal become -inf; the scale stays in the exponent's FMA
+                    const int last_visible = row - col_base;
+#pragma unroll
+                    for (int i = 0; i < FN; ++i)
+                        if (i > last_visible) sc[i] = -INFINITY;
+                }
+                if (general_mask) {  // uniform over the CTA; scores go to the log2 domain here
 #pragma unroll
                     for (int i = 0; i < FN; ++i) {
                         const int col = col_base + i;
