@@ -69,7 +69,9 @@ struct FlashCfg {
     static constexpr int KV_BYTES = FN * D * 2;       // one K or V tile
     // Two CTAs share an SM, and the window carries no alignment slack: the kernel checks that the
     // dynamic shared-memory window starts on a 1024-byte boundary and reports if it does not.
-    static constexpr int SMEM_BYTES = Q_BYTES + 4 * KV_BYTES + 256;  // tiles + barriers
+    static constexpr int O_STAGE_BYTES = 4 * 32 * 128;  // a 32-row, 64-column slab per softmax warp
+    static constexpr int SMEM_BYTES = Q_BYTES + 4 * KV_BYTES + O_STAGE_BYTES + 256;  // tiles + staging + barriers
+    static_assert(2 * (SMEM_BYTES + 1024) <= 233472, "two CTAs must fit in one SM's shared memory");
     // S0 [0,64) S1 [64,128) O [128, 128+D); P of block n overlays columns [0,32) of score buffer n & 1
     static constexpr int TMEM_COLS = 256;
     static constexpr uint32_t O_COL = 128;
@@ -83,12 +85,11 @@ struct FlashCfg {
 struct FlashTile {
     int b, h, q0, nblk;
 };
-__device__ __forceinline__ FlashTile flash_tile(const FlashParams& p, int L, int q_tiles) {
-    const int bh = L / q_tiles, k = L - bh * q_tiles;
+__device__ __forceinline__ FlashTile flash_tile(const FlashParams& p, int b, int h, int k, int q_tiles) {
     const int qt = p.causal ? ((k & 1) ? (k >> 1) : (q_tiles - 1 - (k >> 1))) : k;
     FlashTile t;
-    t.h = bh % (int)p.H;
-    t.b = bh / (int)p.H;
+    t.h = h;
+    t.b = b;
     t.q0 = qt * FM;
     t.nblk = (int)((p.Skv + FN - 1) / FN);
     if (p.causal) {
@@ -98,13 +99,59 @@ __device__ __forceinline__ FlashTile flash_tile(const FlashParams& p, int L, int
     return t;
 }
 
-// i-th tile of this CTA: CTAs take neighbouring tiles in pairs (2c, 2c+1), then (2(c+G), 2(c+G)+1), ...
-// Returns -1 when the CTA is done, -2 for the missing second half of a trailing odd pair.
-__device__ __forceinline__ int flash_tile_index(int i, int num_tiles) {
-    const int first = 2 * ((int)blockIdx.x + (i >> 1) * (int)gridDim.x);
-    if (first >= num_tiles) return -1;
-    const int L = first + (i & 1);
-    return L < num_tiles ? L : -2;
+// A CTA takes neighbouring tiles in pairs (2c, 2c+1), then (2(c+G), 2(c+G)+1), ... Every role walks that list with
+// a cursor that keeps (batch, head, position in the head) of the pair's first tile and adds the decoded stride, so
+// that the integer divisions happen once per kernel and not once per tile.
+struct FlashCursor {
+    int L;        // list index of the current pair's first tile
+    int b, h, k;  // its batch, head and position in the head's order
+};
+struct FlashStride {  // 2 * gridDim.x tiles, decoded the same way (kept in shared memory)
+    int db, dh, dk;
+};
+__device__ __forceinline__ void flash_carry(int& b, int& h, int& k, int q_tiles, int H) {
+    if (k >= q_tiles) { k -= q_tiles; ++h; }
+    if (h >= H) { h -= H; ++b; }
+}
+__device__ __forceinline__ FlashStride flash_stride(const FlashParams& p, int q_tiles) {
+    FlashStride s;
+    const int step = 2 * (int)gridDim.x;
+    const int bh = step / q_tiles;
+    s.dk = step - bh * q_tiles;
+    s.db = bh / p.H;
+    s.dh = bh - s.db * p.H;
+    return s;
+}
+__device__ __forceinline__ FlashCursor flash_cursor(const FlashParams& p, int q_tiles) {
+    FlashCursor c;
+    c.L = 2 * (int)blockIdx.x;
+    const int bh = c.L / q_tiles;
+    c.k = c.L - bh * q_tiles;
+    c.b = bh / p.H;
+    c.h = bh - c.b * p.H;
+    return c;
+}
+// i-th tile of this CTA (i = 0, 1, 2, ... in order). Returns 0 with the tile in t, -1 when the CTA is done, -2 for
+// the missing second half of a trailing odd pair.
+__device__ __forceinline__ int flash_next(FlashCursor& c, const volatile FlashStride* stride, int i, int num_tiles, int q_tiles,
+                                          const FlashParams& p, FlashTile& t) {
+    if ((i & 1) == 0) {
+        if (i > 0) {
+            c.L += 2 * (int)gridDim.x;
+            c.k += stride->dk;
+            c.h += stride->dh;
+            c.b += stride->db;
+            flash_carry(c.b, c.h, c.k, q_tiles, p.H);  // k < 2 q_tiles and h <= 2 H - 1 here: one carry each is enough
+        }
+        if (c.L >= num_tiles) return -1;
+        t = flash_tile(p, c.b, c.h, c.k, q_tiles);
+        return 0;
+    }
+    if (c.L + 1 >= num_tiles) return -2;
+    int b = c.b, h = c.h, k = c.k + 1;
+    flash_carry(b, h, k, q_tiles, p.H);
+    t = flash_tile(p, b, h, k, q_tiles);
+    return 0;
 }
 
 template <typename T, int D>
@@ -116,7 +163,8 @@ flash_tc_kernel(const __grid_constant__ CUtensorMap tmq, const __grid_constant__
     uint8_t* q_s = smem;
     uint8_t* k_s = q_s + Cfg::Q_BYTES;            // [2][KV_BYTES]
     uint8_t* v_s = k_s + 2 * Cfg::KV_BYTES;       // [2][KV_BYTES]
-    uint64_t* bars = reinterpret_cast<uint64_t*>(v_s + 2 * Cfg::KV_BYTES);
+    uint8_t* o_stage = v_s + 2 * Cfg::KV_BYTES;   // [4 warps][32 rows][128 bytes]: output rows on their way out
+    uint64_t* bars = reinterpret_cast<uint64_t*>(o_stage + Cfg::O_STAGE_BYTES);
     uint64_t* q_full = bars;          // 1   one phase per tile
     uint64_t* k_full = bars + 1;      // 2   the block barriers below run on per-role block counters that
     uint64_t* k_empty = bars + 3;     // 2   keep counting across the tiles of this CTA
@@ -130,6 +178,7 @@ flash_tc_kernel(const __grid_constant__ CUtensorMap tmq, const __grid_constant__
     uint64_t* q_empty = bars + 16;    // 1   all Q K^T of a tile have read Q
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 17);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+    volatile FlashStride* stride = reinterpret_cast<volatile FlashStride*>(tmem_slot + 2);
 
     if ((ptx::smem_u32(smem) & 1023u) != 0) {  // uniform over the CTA: the swizzled tiles need this alignment
         if (threadIdx.x == 0) atomicOr(&g_sdpa_status[0], 128u);
@@ -156,6 +205,12 @@ flash_tc_kernel(const __grid_constant__ CUtensorMap tmq, const __grid_constant__
         ptx::mbar_init(o_full, 1);
         ptx::mbar_init(drain_bar, 1);
         *abort_flag = 0;
+        {
+            const FlashStride st = flash_stride(p, q_tiles);
+            stride->db = st.db;
+            stride->dh = st.dh;
+            stride->dk = st.dk;
+        }
         ptx::fence_mbar_init();
         ptx::fence_proxy_async();
     }
@@ -175,11 +230,12 @@ flash_tc_kernel(const __grid_constant__ CUtensorMap tmq, const __grid_constant__
             bool ok = true;
             uint32_t n = 0;      // key blocks loaded so far (all tiles)
             uint32_t tile_n = 0; // tiles started so far
+            FlashCursor cur = flash_cursor(p, q_tiles);
             for (int i = 0; ok; ++i) {
-                const int L = flash_tile_index(i, num_tiles);
-                if (L == -1) break;
-                if (L == -2) continue;
-                const FlashTile t = flash_tile(p, L, q_tiles);
+                FlashTile t;
+                const int tile_state = flash_next(cur, stride, i, num_tiles, q_tiles, p, t);
+                if (tile_state == -1) break;
+                if (tile_state == -2) continue;
                 const uint32_t tile_par = tile_n++ & 1u;
                 // Q may be overwritten once every Q K^T of the previous tile has completed
                 if (!ptx::mbar_wait_bounded(q_empty, tile_par ^ 1u, abort_flag)) { ok = false; break; }
@@ -219,6 +275,7 @@ flash_tc_kernel(const __grid_constant__ CUtensorMap tmq, const __grid_constant__
             uint32_t nq = 0;  // Q K^T blocks issued so far (all tiles)
             uint32_t np = 0;  // P V blocks issued so far
             uint32_t tile_n = 0;
+            FlashCursor cur = flash_cursor(p, q_tiles);
             // Score buffer nq & 1 is free without a barrier of its own: this thread has already waited for
             // p_full of block nq - 2 (the softmax warps had read S and written P by then) and issued that
             // block's P V before this point, and the tensor core runs this thread's MMAs in issue order.
@@ -241,10 +298,10 @@ flash_tc_kernel(const __grid_constant__ CUtensorMap tmq, const __grid_constant__
                 return true;
             };
             for (int i = 0; ok; ++i) {
-                const int L = flash_tile_index(i, num_tiles);
-                if (L == -1) break;
-                if (L == -2) continue;
-                const FlashTile t = flash_tile(p, L, q_tiles);
+                FlashTile t;
+                const int tile_state = flash_next(cur, stride, i, num_tiles, q_tiles, p, t);
+                if (tile_state == -1) break;
+                if (tile_state == -2) continue;
                 if (!ptx::mbar_wait_bounded(q_full, tile_n++ & 1u, abort_flag)) { ok = false; break; }
                 if (t.nblk > 0) ok = issue_qk();
                 if (ok && t.nblk == 1) ptx::tc_commit(q_empty);
@@ -294,12 +351,13 @@ flash_tc_kernel(const __grid_constant__ CUtensorMap tmq, const __grid_constant__
         bool ok = true;
         uint32_t n = 0;       // key blocks processed so far (all tiles)
         uint32_t tile_n = 0;  // tiles finished so far
+        FlashCursor cur = flash_cursor(p, q_tiles);
 
         for (int i = 0; ok; ++i) {
-            const int L = flash_tile_index(i, num_tiles);
-            if (L == -1) break;
-            if (L == -2) continue;
-            const FlashTile t = flash_tile(p, L, q_tiles);
+            FlashTile t;
+            const int tile_state = flash_next(cur, stride, i, num_tiles, q_tiles, p, t);
+            if (tile_state == -1) break;
+            if (tile_state == -2) continue;
             const int q0 = t.q0, nblk = t.nblk;
             const int row = q0 + r_in_tile;
             const T* mrow = nullptr;
@@ -427,8 +485,14 @@ flash_tc_kernel(const __grid_constant__ CUtensorMap tmq, const __grid_constant__
             }
             ptx::tc_fence_after();
             const float inv_l = 1.0f / l_run;
-            T* orow = reinterpret_cast<T*>(p.out) + (int64_t)t.b * p.o_sb + (int64_t)t.h * p.o_sh + (int64_t)row * p.o_ss;
-#pragma unroll
+            // A thread holds one output row, so storing from registers would touch 32 different lines per
+            // instruction. The rows go through a 4 KiB slab of shared memory per warp instead (64 head-dim columns
+            // at a time, 16-byte pieces XOR-swizzled by row so that neither side has bank conflicts) and leave as
+            // full 128-byte row segments, four rows per store instruction.
+            T* obase = reinterpret_cast<T*>(p.out) + (int64_t)t.b * p.o_sb + (int64_t)t.h * p.o_sh;
+            const uint32_t slab = ptx::smem_u32(o_stage) + (uint32_t)(quad * 4096);
+            // (not unrolled: this code runs once per tile, and its instruction fetches are what it costs)
+#pragma unroll 1
             for (int c = 0; c < D / 32; ++c) {
                 uint32_t o[32];
                 if (nblk > 0) {
@@ -438,14 +502,29 @@ flash_tc_kernel(const __grid_constant__ CUtensorMap tmq, const __grid_constant__
 #pragma unroll
                     for (int i = 0; i < 32; ++i) o[i] = 0u;
                 }
-                if (row < p.Sq) {
 #pragma unroll
-                    for (int t4 = 0; t4 < 4; ++t4) {
-                        Vec16<T> ov;
+                for (int t4 = 0; t4 < 4; ++t4) {
+                    uint32_t w[4];  // eight outputs as packed 16-bit pairs
 #pragma unroll
-                        for (int i = 0; i < 8; ++i) ov.v[i] = Cvt<T>::from_f(__uint_as_float(o[t4 * 8 + i]) * inv_l);
-                        st16(orow + c * 32 + t4 * 8, ov);
+                    for (int i = 0; i < 4; ++i) {
+                        float x0, x1;
+                        ptx::fma2(x0, x1, __uint_as_float(o[t4 * 8 + 2 * i]), __uint_as_float(o[t4 * 8 + 2 * i + 1]), inv_l, inv_l, 0.f, 0.f);
+                        w[i] = ptx::pack2<T>(x0, x1);
                     }
+                    const int piece = (c & 1) * 4 + t4;  // 16-byte piece of this row's 128-byte segment
+                    ptx::st_shared_v4(slab + (uint32_t)(lane * 128 + ((piece ^ (lane & 7)) << 4)), make_uint4(w[0], w[1], w[2], w[3]));
+                }
+                if (c & 1) {
+                    __syncwarp();
+#pragma unroll
+                    for (int it = 0; it < 8; ++it) {
+                        const int r = it * 4 + (lane >> 3), piece = lane & 7;
+                        const uint4 val = ptx::ld_shared_v4(slab + (uint32_t)(r * 128 + ((piece ^ (r & 7)) << 4)));
+                        const int orow_i = q0 + quad * 32 + r;
+                        if (orow_i < p.Sq)
+                            *reinterpret_cast<uint4*>(obase + (int64_t)orow_i * p.o_ss + (c >> 1) * 64 + piece * 8) = val;
+                    }
+                    __syncwarp();
                 }
             }
             // this thread's reads of O are complete before it can arrive on p_full for the next tile's first
