@@ -158,6 +158,38 @@ __global__ void __launch_bounds__(256) swiglu_vec_kernel(const SwigluParams p) {
     }
 }
 
+// Contiguous tensors (every row stride equals cols) are one long run of 16-byte vectors: a CTA takes 256 * U
+// consecutive vectors and a thread U of them, 256 apart, so that a row length that is not a multiple of 256 vectors
+// leaves no idle lanes at the end of every row.
+template <typename T, int U>
+__global__ void __launch_bounds__(256) swiglu_flat_kernel(const SwigluParams p, int64_t total_vec) {
+    constexpr int EPV = Vec16<T>::N;
+    const T* gp = reinterpret_cast<const T*>(p.gate);
+    const T* up = reinterpret_cast<const T*>(p.up);
+    T* op = reinterpret_cast<T*>(p.out);
+    const int64_t v0 = (int64_t)blockIdx.x * (256 * U) + threadIdx.x;
+    Vec16<T> g[U], u[U];
+#pragma unroll
+    for (int k = 0; k < U; ++k) {
+        const int64_t v = v0 + k * 256;
+        if (v < total_vec) {
+            g[k] = ld16_stream(gp + v * EPV);
+            u[k] = ld16_stream(up + v * EPV);
+        }
+    }
+#pragma unroll
+    for (int k = 0; k < U; ++k) {
+        const int64_t v = v0 + k * 256;
+        if (v < total_vec) {
+            Vec16<T> o;
+#pragma unroll
+            for (int i = 0; i < EPV; ++i)
+                o.v[i] = Cvt<T>::from_f(silu_f<T>(Cvt<T>::to_f(g[k].v[i])) * Cvt<T>::to_f(u[k].v[i]));
+            st16(op + v * EPV, o);
+        }
+    }
+}
+
 template <typename T>
 __global__ void __launch_bounds__(256) swiglu_scalar_kernel(const SwigluParams p) {
     const int64_t total = p.rows * p.cols;
@@ -175,7 +207,13 @@ int launch_swiglu(const SwigluParams& p, cudaStream_t st) {
     constexpr int UNROLL = 4;
     const bool vec_ok = p.cols % EPV == 0 && p.ldg % EPV == 0 && p.ldu % EPV == 0 && p.ldo % EPV == 0 &&
                         aligned16(p.gate) && aligned16(p.up) && aligned16(p.out);
-    if (vec_ok && p.cols / EPV < 0x7fffffffLL) {
+    const bool flat = p.ldg == p.cols && p.ldu == p.cols && p.ldo == p.cols;
+    if (vec_ok && flat) {
+        const int64_t total_vec = p.rows * (p.cols / EPV);
+        const int64_t grid = (total_vec + 256 * UNROLL - 1) / (256 * UNROLL);
+        if (grid > 0x7fffffffLL) return fail(XG_ERR_TOO_LARGE, "xg_swiglu: tensor too large");
+        if (grid > 0) swiglu_flat_kernel<T, UNROLL><<<(unsigned)grid, 256, 0, st>>>(p, total_vec);
+    } else if (vec_ok && p.cols / EPV < 0x7fffffffLL) {
         const int64_t grid = (p.rows + UNROLL - 1) / UNROLL;
         if (grid > 0x7fffffffLL) return fail(XG_ERR_TOO_LARGE, "xg_swiglu: tensor too large");
         swiglu_vec_kernel<T, UNROLL><<<(unsigned)grid, 256, 0, st>>>(p);
