@@ -154,7 +154,10 @@ __device__ __forceinline__ int flash_next(FlashCursor& c, const volatile FlashSt
     return 0;
 }
 
-template <typename T, int D>
+// MASKED: the kernel carries the general masking code (additive mask, key count that is not a multiple of the block,
+// non-positive scale). The common case is compiled without it: the code of a tile boundary runs once per tile, its
+// instruction fetches miss the instruction caches, and a smaller kernel keeps more of it resident.
+template <typename T, int D, bool MASKED>
 __global__ void __launch_bounds__(kFlashThreads, 2)
 flash_tc_kernel(const __grid_constant__ CUtensorMap tmq, const __grid_constant__ CUtensorMap tmk,
                 const __grid_constant__ CUtensorMap tmv, const FlashParams p) {
@@ -361,7 +364,7 @@ flash_tc_kernel(const __grid_constant__ CUtensorMap tmq, const __grid_constant__
             const int q0 = t.q0, nblk = t.nblk;
             const int row = q0 + r_in_tile;
             const T* mrow = nullptr;
-            if (p.mask != nullptr && row < p.Sq)
+            if (MASKED && p.mask != nullptr && row < p.Sq)
                 mrow = reinterpret_cast<const T*>(p.mask) + (int64_t)t.b * p.m_sb + (int64_t)t.h * p.m_sh + (int64_t)row * p.m_sq;
             float m_run = -INFINITY, l_run = 0.f;  // running maximum (log2 domain, scaled) and row sum
 
@@ -375,7 +378,7 @@ flash_tc_kernel(const __grid_constant__ CUtensorMap tmq, const __grid_constant__
                 // A block needs the general masking code when it carries an additive mask, crosses the end of the
                 // keys or has a non-positive scale. A block that is only cut by the causal diagonal is classified per
                 // warp (a warp owns 32 consecutive query rows): all keys visible, some, or none.
-                const bool general_mask = (p.mask != nullptr) || (col_base + FN > skv) || !(sl2 > 0.f);
+                const bool general_mask = MASKED && ((p.mask != nullptr) || (col_base + FN > skv) || !(sl2 > 0.f));
                 const int warp_row0 = q0 + quad * 32;
                 const bool diag_none = !general_mask && p.causal && (col_base > warp_row0 + 31);
                 const bool diag_some = !general_mask && p.causal && !diag_none && (col_base + FN - 1 > warp_row0);
@@ -410,7 +413,7 @@ flash_tc_kernel(const __grid_constant__ CUtensorMap tmq, const __grid_constant__
                     for (int i = 0; i < FN; ++i)
                         if (i > last_visible) sc[i] = -INFINITY;
                 }
-                if (general_mask) {  // uniform over the CTA; scores go to the log2 domain here
+                if (MASKED && general_mask) {  // uniform over the CTA; scores go to the log2 domain here
 #pragma unroll
                     for (int i = 0; i < FN; ++i) {
                         const int col = col_base + i;
@@ -444,8 +447,8 @@ flash_tc_kernel(const __grid_constant__ CUtensorMap tmq, const __grid_constant__
                         // already implies the P V two blocks back, so the barrier is at most one phase behind.
                         if (!__all_sync(0xffffffffu, ptx::mbar_wait_bounded(pv_full, (n - 1) & 1u, abort_flag))) { ok = false; break; }
                         ptx::tc_fence_after();
-#pragma unroll
-                        for (int c = 0; c < D / 32; ++c) {
+#pragma unroll 1
+                        for (int c = 0; c < D / 32; ++c) {  // rare path: kept small
                             uint32_t o[32];
                             const uint32_t o_taddr = tmem_base + lane_field + Cfg::O_COL + (uint32_t)(c * 32);
                             ptx::tmem_ld_32x32(o_taddr, o);
@@ -559,7 +562,8 @@ int launch_flash_tc(const SdpaParams& p, cudaStream_t st) {
     fp.B = (int)p.B; fp.H = (int)p.H; fp.Sq = (int)p.Sq; fp.Skv = (int)p.Skv;  // the caller keeps these below 2^31
     fp.scale = p.scale;
     fp.causal = p.causal;
-    auto kern = flash_tc_kernel<T, D>;
+    const bool masked = p.mask != nullptr || p.Skv % FN != 0 || !(p.scale > 0.f);
+    auto kern = masked ? flash_tc_kernel<T, D, true> : flash_tc_kernel<T, D, false>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
     if (e != cudaSuccess) {
         cudaGetLastError();
