@@ -56,6 +56,34 @@ def test_flash_tc_mask_and_cross_lengths(cuda_device):
     assert_parity(got, ref_ops.sdpa(q, k, v, keep, None, False), "sdpa boolean mask")
 
 
+@pytest.mark.parametrize("Sq,Skv,D", [(384, 384, 128), (640, 1024, 128), (1152, 1152, 64), (130, 192, 128), (256, 64, 64),
+                                       (1024, 1000, 128), (200, 513, 64)])
+def test_flash_tc_causal_diagonal_paths(cuda_device, Sq, Skv, D):
+    """Causal attention over several query tiles and key counts: blocks cut by the diagonal are handled per warp (all,
+    some or no keys visible), key counts that are not a multiple of the key block take the kernel variant with the
+    general masking code, and every output row leaves through the staged epilogue. The mask is top-left aligned as in
+    aten (row i sees keys 0..i), also when the lengths differ."""
+    q, k, v = _qkv(2, 3, Sq, Skv, D, torch.bfloat16, 40 + Sq)
+    got = _run(cuda_device, q, k, v, None, None, True)
+    exact = ref_ops.sdpa_math(q, k, v, None, None, True)
+    max_abs, mean_rel = error_stats(got, exact)
+    assert max_abs < 2e-2, f"causal {Sq}x{Skv}x{D}: max abs error vs fp32 math {max_abs}"
+    assert torch.isfinite(got.float()).all()
+
+
+def test_flash_tc_strided_output_rows(cuda_device):
+    """The output written as [B, S, H, D] (row stride H*D): the staged epilogue addresses rows by the caller's strides."""
+    from xpu_graph_b200 import ops  # noqa: F401
+
+    B, H, S, D = 2, 4, 320, 128
+    q, k, v = _qkv(B, H, S, S, D, torch.bfloat16, 77)
+    qd, kd, vd = (t.to(cuda_device).transpose(1, 2).contiguous().transpose(1, 2) for t in (q, k, v))  # [B,H,S,D] views of [B,S,H,D]
+    got = torch.ops.xg_sm100.sdpa(qd, kd, vd, None, D ** -0.5, True)
+    exact = ref_ops.sdpa_math(q, k, v, None, None, True)
+    max_abs, _ = error_stats(got, exact)
+    assert max_abs < 2e-2, f"max abs error {max_abs}"
+
+
 def test_flash_tc_transposed_views(cuda_device):
     """q/k/v as they leave the projections: [B, S, H*D] viewed and transposed to [B, H, S, D]."""
     B, S, H, D = 2, 260, 4, 128
