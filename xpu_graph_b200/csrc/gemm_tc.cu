@@ -916,7 +916,11 @@ GemmPlan plan_gemm(int64_t M, int64_t N, int64_t K, int64_t ws_bytes, int sms) {
     if (pl.bn == 128 && mblk * ((N + 127) / 128) < sms) pl.bn = 64;
     pl.splits = 1;
     const int64_t nkb = (K + BK - 1) / BK;
-    if (ws_bytes <= 0 || M > 128 || nkb < 8) return pl;  // measured: at M = 256 a split loses (see below)
+    static const int64_t split_max_m = []() -> int64_t {
+        const char* e = getenv("XG_GEMM_SPLIT_MAX_M");  // largest M that may be split (experiments; default 128)
+        return e ? atoll(e) : 128;
+    }();
+    if (ws_bytes <= 0 || M > split_max_m || nkb < 8) return pl;  // measured: at M = 256 a split loses (see below)
     // Small M is the weight-streaming regime. Two limits, both expressed in bytes one SM handles:
     //   pull : what a CTA drags through its SM, (128 + bn) rows of 128 bytes per k-block, times the waves;
     //   hbm  : the problem's DRAM traffic (weights + activations + the fp32 partial sums written and read
