@@ -916,17 +916,14 @@ GemmPlan plan_gemm(int64_t M, int64_t N, int64_t K, int64_t ws_bytes, int sms) {
     if (pl.bn == 128 && mblk * ((N + 127) / 128) < sms) pl.bn = 64;
     pl.splits = 1;
     const int64_t nkb = (K + BK - 1) / BK;
-    static const int64_t split_max_m = []() -> int64_t {
-        const char* e = getenv("XG_GEMM_SPLIT_MAX_M");  // largest M that may be split (experiments; default 128)
-        return e ? atoll(e) : 128;
-    }();
-    if (ws_bytes <= 0 || M > split_max_m || nkb < 8) return pl;  // measured: at M = 256 a split loses (see below)
+    if (ws_bytes <= 0 || M > 128 || nkb < 8) return pl;  // measured: at M = 256 a split loses (see below)
     // Small M is the weight-streaming regime. Two limits, both expressed in bytes one SM handles:
     //   pull : what a CTA drags through its SM, (128 + bn) rows of 128 bytes per k-block, times the waves;
     //   hbm  : the problem's DRAM traffic (weights + activations + the fp32 partial sums written and read
     //          back by a split) divided over the SMs at the measured ratio of HBM to per-SM L2 bandwidth (~45x).
     // A split also pays a second launch. Measured on B200: at M = 256 the partial sums cost more than the
-    // split saves (16 us unsplit vs 21 us 4-way at N = K = 4096), so only smaller M ends up split.
+    // split saves (15.6 us unsplit vs 22.4 / 19.8 / 29.8 us for 2 / 4 / 8 splits at N = K = 4096, with the reduce pass
+    // launched programmatically), so only smaller M ends up split.
     const int64_t tiles256 = mblk * ((N + 255) / 256);
     const int64_t tiles_bn = mblk * ((N + pl.bn - 1) / pl.bn);
     const double io_bytes = 2.0 * ((double)N * K + (double)M * K + (double)M * N);
