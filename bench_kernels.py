@@ -1,6 +1,7 @@
-"""Small stand-alone cases of each kernel, for profiling and quick timing.
+#!/usr/bin/env python
+"""Small stand-alone cases of each kernel, for profiling and quick timing (the per-kernel companion of bench.py).
 
-    python -m xpu_graph_b200.kernel_cases <case> [--iters N]
+    python bench_kernels.py <case> [--iters N]
 
 Each case holds well under a few GB on the device and launches the named kernel ``iters`` times
 (default 3) after one warm-up, then prints the mean device time measured with CUDA events. Sizes are
@@ -9,9 +10,14 @@ larger than L2 so that DRAM counters mean something.
 from __future__ import annotations
 
 import argparse
+import os
 import sys
 
-import torch
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+import torch  # noqa: E402
 
 
 def _time(fn, iters):
@@ -56,11 +62,11 @@ def sweep():
     import json
     import os
 
-    from . import workloads as W
+    from xpu_graph_b200 import workloads as W
 
     X = torch.ops.xg_sm100
     dev = torch.device("cuda")
-    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    root = ROOT
     peaks = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
     pk = os.path.join(root, "MEASURED_PEAKS.json")
     if os.path.exists(pk):
@@ -100,9 +106,9 @@ def graphs(iters: int) -> int:
     """The two fp32 configurations that are not the benchmark line: the small encoder block (config 1, batch 2 x seq 128,
     launch-bound: also timed as one replayed CUDA graph) and the recsys graph (config 5, batch 16384), each as the fused op
     sequence of this target and as the same model in eager CUDA PyTorch (TF32 off)."""
-    from .fused_graphs import FusedEncoderBlock, FusedRecsysGraph
-    from .graph_runner import CUDAGraphRunner
-    from .workloads import make_encoder, make_recsys
+    from xpu_graph_b200.fused_graphs import FusedEncoderBlock, FusedRecsysGraph
+    from xpu_graph_b200.graph_runner import CUDAGraphRunner
+    from xpu_graph_b200.workloads import make_encoder, make_recsys
 
     dev = torch.device("cuda")
     torch.backends.cuda.matmul.allow_tf32 = False
@@ -126,12 +132,13 @@ def graphs(iters: int) -> int:
 
 
 def main(argv=None):
-    from . import lib, ops  # noqa: F401
+    from xpu_graph_b200 import lib, ops  # noqa: F401
 
     X = torch.ops.xg_sm100
     ap = argparse.ArgumentParser()
     ap.add_argument("case", choices=["sweep", "gemm_splitk", "gemm", "gemm_swiglu", "gemm_small_m", "add_rms_norm", "layer_norm", "sdpa", "rope", "swiglu",
-                                     "gather", "slice_cat", "gemm_f32", "slice_sum_cat", "mul_sum_cat", "batch_dense", "graphs"])
+                                     "gather", "slice_cat", "gemm_f32", "slice_sum_cat", "mul_sum_cat", "batch_dense", "graphs", "layer_gemms",
+                                     "gemm_m256", "gemm_m64", "gemm_small_sweep", "layer_norm_small", "sdpa_full", "sdpa_simt", "gemm_f32_small"])
     ap.add_argument("--iters", type=int, default=3)
     args = ap.parse_args(argv)
     if args.case == "sweep":
@@ -176,6 +183,69 @@ def main(argv=None):
             ws = L.xg_gemm_workspace_bytes(M, N, K, 1)
             print(f"M={M}: no scratch {ms0 * 1e3:.1f} us, op (scratch {ws / 1e6:.1f} MB) {ms1 * 1e3:.1f} us, "
                   f"weights at {2 * N * K / min(ms0, ms1) / 1e6:.0f} GB/s")
+    elif args.case == "layer_gemms":
+        # the six dense launches of one benchmark step (Llama-style layer, 8 x 2048 tokens, hidden 4096, FFN 11008)
+        T, Hd, F, S, D = 16384, 4096, 11008, 2048, 128
+        x, res = rn(T, Hd), rn(T, Hd)
+        wq, wv, wo = rn(Hd, Hd, std=0.02), rn(Hd, Hd, std=0.02), rn(Hd, Hd, std=0.02)
+        wg, wu, wd = rn(F, Hd, std=0.02), rn(F, Hd, std=0.02), rn(Hd, F, std=0.02)
+        cos, sin = rn(S, D), rn(S, D)
+        h = rn(T, F)
+        ops_ = [("q/k projection + RoPE (xg_gemm_rope)", 2 * T * Hd * Hd, lambda: X.dense_rope(x, wq, cos, sin, S, D)),
+                ("v projection (xg_gemm_bias_act)", 2 * T * Hd * Hd, lambda: X.dense(x, wv, True, None, None, "none")),
+                ("o projection + residual", 2 * T * Hd * Hd, lambda: X.dense(x, wo, True, None, res, "none")),
+                ("gate/up dual GEMM + SwiGLU (xg_gemm_swiglu)", 4 * T * F * Hd, lambda: X.dense_swiglu(x, wg, wu)),
+                ("down projection + residual", 2 * T * Hd * F, lambda: X.dense(h, wd, True, None, res, "none"))]
+        for name, flops, fn in ops_:
+            ms = _time(fn, args.iters)
+            print(f"{name}: {ms:.4f} ms, {flops / ms / 1e9:.1f} TFLOP/s")
+    elif args.case == "gemm_m256":
+        M, K, N = 256, 4096, 4096
+        a, w, b = rn(M, K), rn(N, K, std=0.02), rn(N, std=0.02)
+        ms = _time_graphed(lambda: X.dense(a, w, True, b, None, "gelu"))
+        print(f"gemm {M}x{K}x{N} gelu: {ms * 1e3:.1f} us, {2 * M * N * K / ms / 1e9:.1f} TFLOP/s, "
+              f"{2 * (M * K + N * K + M * N) / ms / 1e6:.0f} GB/s (A + W + out)")
+    elif args.case == "gemm_m64":
+        # split-K through scratch memory (the op allocates the fp32 partial sums) followed by the reduction pass
+        M, K, N = 64, 4096, 4096
+        a, w, b = rn(M, K), rn(N, K, std=0.02), rn(N, std=0.02)
+        ms = _time_graphed(lambda: X.dense(a, w, True, b, None, "gelu"))
+        print(f"gemm {M}x{K}x{N} gelu (split-K + reduce): {ms * 1e3:.1f} us, {2 * (M * K + N * K + M * N) / ms / 1e6:.0f} GB/s (A + W + out)")
+    elif args.case == "gemm_small_sweep":
+        # dense layers with few output tiles against torch's (cuBLAS) linear on the same inputs, device time per call
+        import torch.nn.functional as F_
+
+        for (M, K, N) in [(16, 4096, 4096), (64, 4096, 4096), (128, 4096, 4096), (256, 4096, 4096), (512, 4096, 4096),
+                          (1024, 4096, 4096), (16, 4096, 11008), (128, 4096, 11008), (256, 4096, 11008), (512, 4096, 11008)]:
+            a, w, b = rn(M, K), rn(N, K, std=0.02), rn(N, std=0.02)
+            ms = _time_graphed(lambda: X.dense(a, w, True, b, None, "none"))
+            ms2 = _time_graphed(lambda: F_.linear(a, w, b))
+            gbs = 2 * (M * K + N * K + M * N) / ms / 1e6
+            print(f"| {M} | {K} | {N} | {ms * 1e3:.1f} | {2 * M * N * K / ms / 1e9:.0f} | {gbs:.0f} | {ms2 * 1e3:.1f} |")
+    elif args.case == "layer_norm_small":
+        rows, hidden = 8192, 4096
+        x, r, w, b = rn(rows, hidden), rn(rows, hidden), rn(hidden), rn(hidden)
+        ms = _time_graphed(lambda: X.add_layer_norm_y(x, r, w, b, 1e-5))
+        print(f"add_layer_norm (1 output) {rows}x{hidden}: {ms * 1e3:.1f} us, {6 * rows * hidden / ms / 1e6:.0f} GB/s")
+    elif args.case == "sdpa_full":
+        B, H, S, D = 8, 32, 2048, 128
+        q, k, v = rn(B, H, S, D), rn(B, H, S, D), rn(B, H, S, D)
+        for causal in (True, False):
+            ms = _time_graphed(lambda: X.sdpa(q, k, v, None, D ** -0.5, causal), reps=5)
+            flops = 4 * B * H * S * S * D / (2 if causal else 1)
+            print(f"sdpa {'causal' if causal else 'full'} {B}x{H}x{S}x{D}: {ms:.4f} ms, {flops / ms / 1e9:.1f} TFLOP/s")
+    elif args.case == "sdpa_simt":
+        # the encoder block's attention (fp32, [1, 8, 128, 64] after the batch is folded into the heads)
+        B, H, S, D = 1, 8, 128, 64
+        q, k, v = (rn(B, H, S, D, dtype=torch.float32) for _ in range(3))
+        ms = _time_graphed(lambda: X.sdpa(q, k, v, None, 0.125, False))
+        print(f"sdpa fp32 {B}x{H}x{S}x{D}: {ms * 1e3:.1f} us, {4 * B * H * S * S * D / ms / 1e6:.1f} GFLOP/s")
+    elif args.case == "gemm_f32_small":
+        # the encoder block's dense layers (fp32 FMA kernel): 256 rows, K / N of the four layers
+        for (M, K, N) in [(256, 256, 768), (256, 256, 256), (256, 256, 1024), (256, 1024, 256)]:
+            a, w, b = rn(M, K, dtype=torch.float32), rn(N, K, dtype=torch.float32, std=0.02), rn(N, dtype=torch.float32, std=0.02)
+            ms = _time_graphed(lambda: X.dense(a, w, True, b, None, "gelu"))
+            print(f"gemm_f32 {M}x{K}x{N} gelu: {ms * 1e3:.1f} us, {2 * M * N * K / ms / 1e9:.2f} TFLOP/s")
     elif args.case == "gemm_swiglu":
         M, K, N = 8192, 4096, 11008
         a, wg, wu = rn(M, K), rn(N, K, std=0.02), rn(N, K, std=0.02)

@@ -139,6 +139,22 @@ int xg_gemm_bias_act_ws(const void* A, const void* B, const void* bias, const vo
 int64_t xg_gemm_workspace_bytes(int64_t M, int64_t N, int64_t K, int dtype);
 
 /*
+ * The same dense layer (16-bit dtypes, W given as [N,K]) on the thread-block-cluster kernel with the caller's
+ * choice of decomposition: every 256 x `tile_n` output tile is computed by a cluster of `splits` CTA pairs, each
+ * pair taking a share of K, and the partial tiles are added through distributed shared memory in split order
+ * (deterministic; no scratch memory, no second launch). splits in 1..4; tile_n a multiple of 32 in 64..256 with
+ * tile_n / 32 >= splits; K must span at least `splits` 64-wide blocks. xg_gemm_bias_act picks this kernel (and
+ * these two numbers) by itself for problems with few output tiles; xg_gemm_cluster_plan reports that choice
+ * (returns 1 and fills splits / tile_n, or 0 when it would run another kernel). For autotuners and tests.
+ * Reference counterpart: the same torch_mlu_ops.matmul call site as xg_gemm_bias_act
+ * (targets/mlu/structure_replacements/dense_layer_modules.py:9-57).
+ */
+int xg_gemm_bias_act_cluster(const void* A, const void* W, const void* bias, const void* residual, void* out,
+                             int64_t M, int64_t N, int64_t K, int64_t lda, int64_t ldw, int64_t ldc, int64_t ldr,
+                             int act, int dtype, int splits, int tile_n, void* stream);
+int xg_gemm_cluster_plan(int64_t M, int64_t N, int64_t K, int dtype, int* splits, int* tile_n);
+
+/*
  * Split-K dense layer for hosts that cannot allocate device memory. Some embedders of this library own
  * no allocator they may call at this point: a plugin running inside another framework's stream-ordered
  * memory pool, a runtime whose memory budget was fixed at start-up, or a real-time serving loop in which a

@@ -26,6 +26,13 @@ def assert_parity(actual: torch.Tensor, expected: torch.Tensor, what: str = "", 
     if expected.dtype == torch.float32:
         scale = e.abs().max().item() if e.numel() else 1.0
         rtol, atol = F32_RTOL, F32_RTOL * max(scale, 1e-30)
+        if e.numel():
+            # both readings of "rel 1e-5" are shown: the bound applied here (error against the tensor's largest
+            # magnitude) and the element-wise ratio, which is large wherever an element is close to zero
+            d = (a - e).abs()
+            print(f"{what}: fp32 max|diff|/max|ref| = {d.max().item() / max(scale, 1e-30):.3g}, "
+                  f"element-wise max rel = {(d / e.abs().clamp_min(1e-30)).max().item():.3g} "
+                  f"(median |ref| {e.abs().median().item():.3g})")
     else:
         rtol, atol = BF16_RTOL, BF16_ATOL
     ref_mag = e.abs() if magnitude is None else torch.maximum(e.abs(), magnitude.detach().float().cpu().abs())
@@ -47,3 +54,25 @@ def assert_bit_exact(actual: torch.Tensor, expected: torch.Tensor, what: str = "
         it = {2: torch.int16, 4: torch.int32, 8: torch.int64}[a.element_size()]
         a, e = a.view(it), e.view(it)
     assert torch.equal(a, e), f"{what}: results differ bitwise"
+
+
+class LaunchCounter:
+    """Counts the kernel-launching calls made into the C ABI while active (``with LaunchCounter() as c: ...; c.n``)."""
+
+    def __enter__(self):
+        from xpu_graph_b200 import lib
+
+        self.n = 0
+        self.names = []
+
+        def before(name, args):
+            if name not in lib.QUERY_ENTRY_POINTS:
+                self.n += 1
+                self.names.append(name)
+
+        self._cm = lib.call_hook(before=before)
+        self._cm.__enter__()
+        return self
+
+    def __exit__(self, *exc):
+        return self._cm.__exit__(*exc)

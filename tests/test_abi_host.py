@@ -5,6 +5,7 @@ import os
 import re
 
 import pytest
+import torch
 
 from xpu_graph_b200 import lib
 
@@ -119,3 +120,44 @@ def test_stack_or_view_reuses_slabs_of_one_buffer():
     assert torch.equal(ops._stack_or_view(shuffled), torch.stack(shuffled))
     strided = [base[:, i, :] for i in range(3)]  # not contiguous slabs
     assert torch.equal(ops._stack_or_view(strided), torch.stack(strided))
+
+
+def test_multi_slice_refuses_slices_outside_the_row():
+    """FusedSlice passes end - start of the raw aten.slice arguments as the slice length (structure/fuse_slice.py:28);
+    a slice that aten would have clamped must be refused on the host, not read past the row on the device."""
+    import pytest
+
+    from xpu_graph_b200 import ops
+
+    assert ops._checked_starts(64, [0, 60, -4], 4) == [0, 60, 60]
+    for starts, length in (([62], 4), ([-70], 4), ([0], 65), ([0], 9223372036854775807), ([0], -1)):
+        with pytest.raises(ValueError):
+            ops._checked_starts(64, starts, length)
+    # the fake implementation (shape propagation in the compiler) refuses the same slices
+    from torch._subclasses.fake_tensor import FakeTensorMode
+
+    with FakeTensorMode():
+        src = torch.empty(8, 64)
+        assert tuple(torch.ops.xg_sm100.multi_slice(src, [0, 8], 8).shape) == (2, 8, 8)
+        with pytest.raises(Exception):
+            torch.ops.xg_sm100.multi_slice(src, [60], 8)
+
+
+def test_weight_plane_cache_key_with_untracked_tensors():
+    """Tensors made under torch.inference_mode() have no version counter: their planes are not cached (the key is
+    None) instead of raising; ordinary tensors are keyed on version, address, layout and orientation."""
+    from xpu_graph_b200 import ops
+
+    with torch.inference_mode():
+        w_inf = torch.randn(4, 8)
+    assert ops._planes_tag(w_inf, True) is None
+    w = torch.randn(4, 8)
+    t0 = ops._planes_tag(w, True)
+    assert t0 is not None and t0 != ops._planes_tag(w, False)
+    w.add_(1.0)
+    assert ops._planes_tag(w, True) != t0  # an in-place update moves the version counter
+    w.data.mul_(2.0)  # through .data it does not: that is what invalidate_weight_planes is for
+    w._xg_bf16_planes = ("stale", None)
+    ops.invalidate_weight_planes(w)
+    assert not hasattr(w, "_xg_bf16_planes")
+    ops.invalidate_weight_planes(w)  # idempotent

@@ -8,7 +8,7 @@ import pytest
 import torch
 
 from oracle import ref_ops
-from tests.helpers import assert_parity, error_stats
+from tests.helpers import LaunchCounter, assert_parity, error_stats
 
 pytestmark = pytest.mark.gpu
 
@@ -97,6 +97,87 @@ def test_dense_split_k(cuda_device, M, K, N, act, with_res):
     assert torch.equal(got, again), "split-K reduction must be deterministic"
 
 
+def _cluster_dense(L, lib, x, w, b, r, act, out, splits, tile_n):
+    M, K = x.shape
+    N = w.shape[0]
+    return L.xg_gemm_bias_act_cluster(x.data_ptr(), w.data_ptr(), b.data_ptr() if b is not None else None,
+                                      r.data_ptr() if r is not None else None, out.data_ptr(), M, N, K, x.stride(0),
+                                      w.stride(0), out.stride(0), r.stride(0) if r is not None else 0, lib.ACT_CODES[act],
+                                      lib.XG_BF16 if x.dtype == torch.bfloat16 else lib.XG_F16, splits, tile_n,
+                                      torch.cuda.current_stream().cuda_stream)
+
+
+@pytest.mark.parametrize("splits,tile_n", [(1, 64), (1, 160), (1, 256), (2, 64), (2, 128), (2, 256), (3, 96), (3, 256),
+                                           (4, 128), (4, 256)])
+@pytest.mark.parametrize("M,K,N,act,with_res", [(256, 4096, 1024, "gelu", False), (300, 1032, 520, "none", True),
+                                                (77, 512, 1000, "silu", True), (512, 2048, 264, "relu", False)])
+def test_dense_cluster_kernel(cuda_device, splits, tile_n, M, K, N, act, with_res):
+    """The cluster kernel at every decomposition (k-splits 1..4 x tile widths incl. the uneven column shares of 3
+    pairs), tile-aligned and ragged M / N / K, with bias, residual and activation: against the oracle, and bit-equal
+    from run to run (the partial tiles are added in split order)."""
+    from xpu_graph_b200 import lib
+
+    L = lib.load()
+    x, w, b = _mk(M, K, N, torch.bfloat16, 41)
+    g = torch.Generator().manual_seed(42)
+    r = torch.randn(M, N, generator=g).to(torch.bfloat16) if with_res else None
+    xd, wd, bd = x.to(cuda_device), w.to(cuda_device), b.to(cuda_device)
+    rd = r.to(cuda_device) if with_res else None
+    outs = []
+    for _ in range(2):
+        out = torch.full((M, N), float("nan"), device=cuda_device, dtype=torch.bfloat16)
+        lib.check(_cluster_dense(L, lib, xd, wd, bd, rd, act, out, splits, tile_n), "xg_gemm_bias_act_cluster")
+        outs.append(out)
+    torch.cuda.synchronize()
+    assert lib.tc_status() == 0, "a bounded wait expired inside the cluster kernel"
+    want = ref_ops.dense(x, w, True, b, "none")
+    if with_res:
+        want = want + r
+    want = ref_ops._ACTS[act](want)
+    assert_parity(outs[0], want, f"cluster dense {M}x{K}x{N} splits={splits} tile_n={tile_n}", magnitude=r)
+    assert torch.equal(outs[0], outs[1]), "the exchange must add the partial tiles in a fixed order"
+
+
+def test_dense_cluster_kernel_matches_unsplit_bitwise_inputs(cuda_device):
+    """fp16 and an odd leading dimension of the output (scalar store path), plus the argument checks of the entry point."""
+    from xpu_graph_b200 import lib
+
+    L = lib.load()
+    M, K, N = 260, 768, 328
+    x, w, b = _mk(M, K, N, torch.float16, 43)
+    xd, wd, bd = x.to(cuda_device), w.to(cuda_device), b.to(cuda_device)
+    wide = torch.zeros(M, N + 3, device=cuda_device, dtype=torch.float16)
+    out = wide[:, :N]  # row stride N + 3: not 16-byte addressable
+    lib.check(_cluster_dense(L, lib, xd, wd, bd, None, "gelu", out, 3, 128), "xg_gemm_bias_act_cluster")
+    torch.cuda.synchronize()
+    assert lib.tc_status() == 0
+    assert_parity(out.contiguous(), ref_ops.dense(x, w, True, b, "gelu"), "cluster dense fp16, odd ldc")
+    assert float(wide[:, N:].abs().max()) == 0.0, "columns beyond N must stay untouched"
+    good = torch.empty(M, N, device=cuda_device, dtype=torch.float16)
+    assert _cluster_dense(L, lib, xd, wd, bd, None, "none", good, 5, 256) == -1      # splits out of range
+    assert _cluster_dense(L, lib, xd, wd, bd, None, "none", good, 3, 64) == -1       # fewer 32-column chunks than pairs
+    assert _cluster_dense(L, lib, xd, wd, bd, None, "none", good, 2, 100) == -1      # tile width not a multiple of 32
+    short = torch.zeros(M, 64, device=cuda_device, dtype=torch.float16)
+    assert L.xg_gemm_bias_act_cluster(short.data_ptr(), wd.data_ptr(), None, None, good.data_ptr(), M, N, 64, 64, K, N, 0, 0,
+                                      lib.XG_F16, 2, 128, torch.cuda.current_stream().cuda_stream) == -1  # one k-block, two pairs
+
+
+def test_dense_picks_the_cluster_kernel_for_few_tiles(cuda_device):
+    """The planner's choice for the weight-streaming cells of the matmul sweep, and that the op needs no scratch there."""
+    import ctypes
+
+    from xpu_graph_b200 import lib
+
+    L = lib.load()
+    s, t = ctypes.c_int(0), ctypes.c_int(0)
+    for (M, N, K) in ((256, 4096, 4096), (256, 11008, 4096), (512, 4096, 4096)):
+        assert L.xg_gemm_cluster_plan(M, N, K, lib.XG_BF16, ctypes.byref(s), ctypes.byref(t)) == 1, (M, N, K)
+        assert 1 <= s.value <= 4 and 64 <= t.value <= 256 and t.value % 32 == 0
+        assert L.xg_gemm_workspace_bytes(M, N, K, lib.XG_BF16) == 0
+    for (M, N, K) in ((16384, 4096, 4096), (64, 4096, 4096)):  # the persistent pair kernel / split-K through scratch
+        assert L.xg_gemm_cluster_plan(M, N, K, lib.XG_BF16, ctypes.byref(s), ctypes.byref(t)) == 0, (M, N, K)
+
+
 def test_dense_fp16(cuda_device):
     from xpu_graph_b200.modules import DenseLayerModule
 
@@ -129,11 +210,11 @@ def test_dense_fp32_on_tensor_cores(cuda_device, M, K, N, act, with_res, weight_
     assert ops._f32_on_tensor_cores(M, N, K)
     x, w, b = _mk(M, K, N, torch.float32, 26, weight_trans)
     r = torch.randn(M, N, generator=torch.Generator().manual_seed(27)) if with_res else None
-    launches = ops.launch_count()
-    got = torch.ops.xg_sm100.dense(x.to(cuda_device), w.to(cuda_device), weight_trans, b.to(cuda_device),
-                                   r.to(cuda_device) if with_res else None, act)
+    with LaunchCounter() as calls:
+        got = torch.ops.xg_sm100.dense(x.to(cuda_device), w.to(cuda_device), weight_trans, b.to(cuda_device),
+                                       r.to(cuda_device) if with_res else None, act)
     torch.cuda.synchronize()
-    assert ops.launch_count() - launches >= 2  # operand split(s) and the tensor-core GEMM
+    assert calls.n >= 2 and "xg_gemm_f32x3" in calls.names  # operand split(s) and the tensor-core GEMM
     assert lib.tc_status() == 0
     y = x.double() @ (w.double().t() if weight_trans else w.double()) + b.double()
     if with_res:
@@ -256,11 +337,11 @@ def test_batch_dense(cuda_device, b, M, K, N, weight_trans, act, with_bias, dtyp
     if not weight_trans:
         w = w.transpose(1, 2).contiguous()
     bias = (0.05 * torch.randn(b, 1, N, generator=g)).to(dtype) if with_bias else None
-    launches = ops.launch_count()
-    got = BatchDenseLayerModule()(x.to(cuda_device), w.to(cuda_device), weight_trans,
-                                  bias.to(cuda_device) if with_bias else None, act)
+    with LaunchCounter() as calls:
+        got = BatchDenseLayerModule()(x.to(cuda_device), w.to(cuda_device), weight_trans,
+                                      bias.to(cuda_device) if with_bias else None, act)
     torch.cuda.synchronize()
-    assert ops.launch_count() - launches == 1
+    assert calls.names == ["xg_bgemm_bias_act"]
     assert lib.tc_status() == 0
     if dtype == torch.float32:
         want = ref_ops.batch_dense(x.double(), w.double(), weight_trans, bias.double() if with_bias else None, act).float()
@@ -290,23 +371,33 @@ def test_combo_dense(cuda_device):
     assert_parity(got2, want, "combo_dense (operands in place)")
 
 
-def test_config3_cell(cuda_device):
-    """One full-size cell of the matmul sweep (M=4096, K=4096, N=11008, GELU): sampled rows against the
-    oracle plus linearity in the bias (out(b) - out(0) == b before the activation)."""
+@pytest.mark.parametrize("act", ["gelu", "silu"])
+@pytest.mark.parametrize("N", [4096, 11008])
+@pytest.mark.parametrize("M", [256, 4096, 16384])
+def test_config3_cell(cuda_device, M, N, act):
+    """Every full-size cell of the matmul sweep (M in {256, 4096, 16384} x K = 4096 x N in {4096, 11008}, GELU and
+    SiLU, seed 2): sampled rows against the oracle (first / last row, both sides of every kind of tile edge) plus
+    linearity in the bias (out(b) - out(0) == b before the activation). The M = 256 cells run the cluster kernel
+    that splits K, the others the CTA-pair kernel."""
     from xpu_graph_b200 import lib
     from xpu_graph_b200.modules import DenseLayerModule
 
-    M, K, N = 4096, 4096, 11008
+    K = 4096
     g = torch.Generator(device=cuda_device).manual_seed(2)
     x = torch.randn(M, K, generator=g, device=cuda_device, dtype=torch.bfloat16)
     w = (0.02 * torch.randn(N, K, generator=g, device=cuda_device)).to(torch.bfloat16)
     b = (0.02 * torch.randn(N, generator=g, device=cuda_device)).to(torch.bfloat16)
-    got = DenseLayerModule(False)(x, w, True, b, "gelu")
+    got = DenseLayerModule(False)(x, w, True, b, act)
     torch.cuda.synchronize()
     assert lib.tc_status() == 0
-    sel = torch.tensor([0, 127, 128, 2049, 4095], device=cuda_device)
-    want = ref_ops.dense(x[sel].cpu(), w.cpu(), True, b.cpu(), "gelu")
-    assert_parity(got[sel], want, "config-3 rows")
-    lin = DenseLayerModule(False)(x, w, True, None, "none")
-    lin_b = DenseLayerModule(False)(x, w, True, b, "none")
-    assert ((lin_b.float() - lin.float()) - b.float()).abs().max().item() < 0.05
+    rows = sorted({0, 1, 127, 128, 255, M // 2 + 1, M - 129, M - 1} & set(range(M)))
+    sel = torch.tensor(rows, device=cuda_device)
+    want = ref_ops.dense(x[sel].cpu(), w.cpu(), True, b.cpu(), act)
+    assert_parity(got[sel], want, f"config-3 cell {M}x{K}x{N} {act}")
+    exact = ref_ops.dense(x[sel].cpu().float(), w.cpu().float(), True, b.cpu().float(), act)
+    max_abs, mean_rel = error_stats(got[sel], exact)
+    print(f"config-3 cell {M}x{K}x{N} {act}: max_abs={max_abs:.3g} mean_rel={mean_rel:.3g} vs fp32 math")
+    if act == "gelu":
+        lin = DenseLayerModule(False)(x, w, True, None, "none")
+        lin_b = DenseLayerModule(False)(x, w, True, b, "none")
+        assert ((lin_b.float() - lin.float()) - b.float()).abs().max().item() < 0.05

@@ -109,3 +109,29 @@ def test_config2_full_size_properties(cuda_device):
     assert_bit_exact(s[sel], want_s, "full-size sum rows")
     rms = (y.float() / w.float()).pow(2).mean(dim=1).sqrt()
     assert (rms - 1.0).abs().max().item() < 2e-2
+
+
+@pytest.mark.parametrize("store_sum", [False, True])
+def test_config2_full_size_layer_norm(cuda_device, store_sum):
+    """Full-size LayerNorm + residual cell of the norm sweep (65536 x 8192 bf16, seed 1), with one output and with
+    the sum as second output: sampled rows against the oracle (the sum bit-exact) and, over the whole tensor, the
+    property that (y - beta) / gamma has zero mean and unit variance per row."""
+    from xpu_graph_b200.modules import AddLayerNormModule
+
+    rows, hidden = 65536, 8192
+    g = torch.Generator(device=cuda_device).manual_seed(1)
+    x = torch.randn(rows, hidden, generator=g, device=cuda_device, dtype=torch.bfloat16)
+    r = torch.randn(rows, hidden, generator=g, device=cuda_device, dtype=torch.bfloat16)
+    w = (1.0 + 0.1 * torch.randn(hidden, generator=g, device=cuda_device)).to(torch.bfloat16)
+    b = (0.1 * torch.randn(hidden, generator=g, device=cuda_device)).to(torch.bfloat16)
+    out = AddLayerNormModule(store_sum)(x, r, w, b, 1e-5)
+    y, s = (out[0], out[1]) if store_sum else (out, None)
+    sel = torch.tensor([0, 1, 4095, 32768, 65535], device=cuda_device)
+    want_y, want_s = ref_ops.add_layer_norm(x[sel].cpu(), r[sel].cpu(), w.cpu(), b.cpu(), 1e-5)
+    assert_parity(y[sel], want_y, "full-size LayerNorm rows")
+    if store_sum:
+        assert_bit_exact(s[sel], want_s, "full-size LayerNorm sum rows")
+    for lo in range(0, rows, 16384):  # in slabs: the fp32 copy of the whole tensor would be 2 GiB
+        z = (y[lo:lo + 16384].float() - b.float()) / w.float()
+        assert z.mean(dim=1).abs().max().item() < 2e-2
+        assert (z.var(dim=1, unbiased=False) - 1.0).abs().max().item() < 3e-2

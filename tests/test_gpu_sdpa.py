@@ -65,9 +65,9 @@ def test_flash_tc_causal_diagonal_paths(cuda_device, Sq, Skv, D):
     aten (row i sees keys 0..i), also when the lengths differ."""
     q, k, v = _qkv(2, 3, Sq, Skv, D, torch.bfloat16, 40 + Sq)
     got = _run(cuda_device, q, k, v, None, None, True)
-    exact = ref_ops.sdpa_math(q, k, v, None, None, True)
-    max_abs, mean_rel = error_stats(got, exact)
-    assert max_abs < 2e-2, f"causal {Sq}x{Skv}x{D}: max abs error vs fp32 math {max_abs}"
+    assert_parity(got, ref_ops.sdpa(q, k, v, None, None, True), f"causal sdpa {Sq}x{Skv}x{D}")
+    max_abs, mean_rel = error_stats(got, ref_ops.sdpa_math(q, k, v, None, None, True))
+    print(f"causal sdpa {Sq}x{Skv}x{D}: max_abs={max_abs:.3g} mean_rel={mean_rel:.3g} vs fp32 math")
     assert torch.isfinite(got.float()).all()
 
 
@@ -79,9 +79,9 @@ def test_flash_tc_strided_output_rows(cuda_device):
     q, k, v = _qkv(B, H, S, S, D, torch.bfloat16, 77)
     qd, kd, vd = (t.to(cuda_device).transpose(1, 2).contiguous().transpose(1, 2) for t in (q, k, v))  # [B,H,S,D] views of [B,S,H,D]
     got = torch.ops.xg_sm100.sdpa(qd, kd, vd, None, D ** -0.5, True)
-    exact = ref_ops.sdpa_math(q, k, v, None, None, True)
-    max_abs, _ = error_stats(got, exact)
-    assert max_abs < 2e-2, f"max abs error {max_abs}"
+    assert_parity(got, ref_ops.sdpa(q, k, v, None, None, True), "sdpa with [B, S, H, D] output rows")
+    max_abs, mean_rel = error_stats(got, ref_ops.sdpa_math(q, k, v, None, None, True))
+    print(f"sdpa strided output: max_abs={max_abs:.3g} mean_rel={mean_rel:.3g} vs fp32 math")
 
 
 def test_flash_tc_transposed_views(cuda_device):

@@ -57,6 +57,32 @@ def test_llama_layer_compiled_on_gpu(cuda_device):
     assert all(("reshape" in a or "transpose" in a or "view" in a) for a in atens), atens
 
 
+def test_llama_layer_benchmark_size_compiled_on_gpu(cuda_device):
+    """The graph whose throughput is the headline number: the hidden-4096 / FFN-11008 decoder layer (seed 3) on one
+    2048-token sequence, compiled by torch.compile through the xpu_graph pipeline with this target. The compiled graph
+    must be the nine-op sequence whose ops tests/test_gpu_graphs.py::test_llama_layer_benchmark_size checks one by one
+    at this size, its result must equal that sequence's bit for bit, and end to end it must be at least as close to
+    the layer in fp32 as the eager bf16 layer on CPU is (max-abs and mean-rel against the eager result are printed)."""
+    from tests.test_gpu_graphs import _end_to_end_gate
+    from xpu_graph_b200 import lib
+    from xpu_graph_b200.fused_graphs import FusedLlamaDecoderLayer
+    from xpu_graph_b200.workloads import make_llama_layer
+
+    model, (x, cos, sin) = make_llama_layer(seed=3, batch=1, seq=2048, hidden=4096, heads=32, ffn=11008)
+    with torch.no_grad():
+        want = model(x, cos, sin)
+        exact = model.float()(x.float(), cos.float(), sin.float())
+    model = model.to(torch.bfloat16).to(cuda_device)
+    inputs = (x.to(cuda_device), cos.to(cuda_device), sin.to(cuda_device))
+    compiled, got, mods, atens = _compile_run(model, inputs)
+    assert lib.tc_status() == 0
+    assert sorted(mods) == sorted(["custom_rms_norm", "xg_dense_rope", "xg_dense_rope", "custom_dense_layer_replacement",
+                                   "xg_sdpa", "xg_dense_residual", "custom_rms_norm", "xg_dense_swiglu",
+                                   "xg_dense_residual"]), mods
+    assert torch.equal(got, FusedLlamaDecoderLayer(model)(*inputs)), "compiled graph and assembled op sequence must agree bitwise"
+    _end_to_end_gate(got, want, exact, "compiled llama layer 1x2048x4096 bf16")
+
+
 def test_encoder_block_compiled_on_gpu(cuda_device):
     from xpu_graph_b200.workloads import make_encoder
 
@@ -93,14 +119,19 @@ def test_recsys_graph_full_size_compiled_on_gpu(cuda_device):
 
 
 def test_device_graph_vendor_compiler(cuda_device):
-    """vendor_compiler_config={"compiler": "device_graph"}: the rewritten encoder graph is captured into one CUDA
-    graph and replayed; results stay equal to eager on new inputs and replay is faster than launch by launch."""
+    """vendor_compiler_config={"compiler": "device_graph"}: the rewritten encoder graph goes through the reference's
+    device_graph_compiler (backends/device_graph.py:54-130) with this target's GraphRunner subclass, is captured into
+    one CUDA graph and replayed; results stay equal to eager on new inputs and replay is faster than launch by
+    launch (the protocol of the reference's tests/mlu/test_mlu_graph.py:31-117)."""
     from xpu_graph_b200.workloads import make_encoder
 
     model, x = make_encoder(seed=0)
     cpu_model, _ = make_encoder(seed=0)
     model = model.to(cuda_device)
     compiled, got, mods, atens = _compile_run(model, (x.to(cuda_device),), vendor_compiler_config={"compiler": "device_graph"})
+    # the reference's capability partitioner ran: what is left at the top level are its fused partitions, each a lazily
+    # captured GraphRunner[Target.cuda] (every node of this graph lives on the device, so there is exactly one)
+    assert mods == ["fused_0"], mods
     with torch.no_grad():
         assert_parity(got, cpu_model(x), "device_graph first call")
         g = torch.Generator().manual_seed(123)
@@ -123,3 +154,25 @@ def test_device_graph_vendor_compiler(cuda_device):
         t_graph, t_plain = clock(compiled), clock(plain)
     print(f"encoder block: captured {t_graph * 1e6:.0f} us, launch-by-launch {t_plain * 1e6:.0f} us per call")
     assert t_graph < t_plain
+
+
+def test_interceptor_on_gpu(cuda_device, caplog):
+    """enable_interceptor="rtol=...,atol=...": the reference's interceptor (interceptor.py:93-179) runs the Dynamo graph
+    (eager CUDA aten) beside the graph compiled for this target on every call; with the kernels in order it stays silent."""
+    from xpu_graph_b200.workloads import make_encoder, make_llama_layer
+
+    lg = logging.getLogger("xpu_graph")
+    old = lg.propagate
+    lg.propagate = True
+    caplog.set_level(logging.INFO, logger="xpu_graph")
+    try:
+        model, x = make_encoder(seed=0)
+        model = model.to(cuda_device)
+        compiled, got, mods, atens = _compile_run(model, (x.to(cuda_device),), enable_interceptor="rtol=1e-4,atol=1e-5")
+        layer, (lx, cos, sin) = make_llama_layer(seed=3, batch=1, seq=256, hidden=512, heads=4, ffn=1376)
+        layer = layer.to(cuda_device)
+        _compile_run(layer, (lx.to(cuda_device), cos.to(cuda_device), sin.to(cuda_device)), enable_interceptor="rtol=2e-2,atol=2e-2")
+    finally:
+        lg.propagate = old
+    assert caplog.text.count("Monitored inference") >= 2
+    assert "diverges" not in caplog.text, caplog.text[-2000:]

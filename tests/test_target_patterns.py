@@ -85,6 +85,26 @@ def test_target_is_installed(tgt):
     assert "FusedRoPE" not in {type(p).__name__ for group in pats.values() for p in group}
 
 
+def test_graph_runner_is_registered_for_the_target(tgt):
+    """GraphRunner[Target.cuda_sm100] (device_graph_runner.py:146-191 shows the NPU / MLU registrations) resolves to the
+    CUDA subclass, also under the device-type alias that backends/device_graph.py:72 looks it up by; the vendor
+    compiler hook is published where backends/__init__.py:19-25 imports it from."""
+    import importlib
+
+    from xpu_graph.config import Target
+    from xpu_graph.device_graph_runner import GraphRunner
+    from xpu_graph_b200.graph_runner import CUDAGraphRunner
+
+    assert GraphRunner[Target.cuda_sm100] is CUDAGraphRunner and GraphRunner[Target("cuda")] is CUDAGraphRunner
+    assert issubclass(CUDAGraphRunner, GraphRunner)
+    runner = CUDAGraphRunner(lambda x: x + 1)
+    assert runner.captured is False and type(runner.clone()) is CUDAGraphRunner
+    hook = importlib.import_module("xpu_graph.backends.cuda_sm100").cuda_sm100_compile
+    gm = torch.fx.symbolic_trace(torch.nn.Linear(4, 4))
+    assert hook(gm, [torch.empty(2, 4)], is_inference=True) is gm                           # no capture asked for
+    assert hook(gm, [torch.empty(2, 4)], is_inference=True, compiler="device_graph") is gm  # host tensors: nothing to capture
+
+
 def test_llama_layer_graph(tgt, xlog):
     from xpu_graph_b200.workloads import make_llama_layer
 
@@ -153,6 +173,74 @@ def test_add_norm(tgt, xlog, kind, reuse_sum):
     assert not any("add.Tensor" in a for a in atens)
 
 
+@pytest.mark.parametrize("kind", ["rms", "ln"])
+def test_add_norm_with_an_earlier_user_of_the_sum(tgt, xlog, kind):
+    """A consumer of the sum that sits before the norm in the graph must still find its operand defined: the fused
+    call (whose second output replaces the sum) then takes the add's place instead of the norm's."""
+    g = torch.Generator().manual_seed(0)
+    x, r = torch.randn(6, 64, generator=g), torch.randn(6, 64, generator=g)
+    w, b = torch.randn(64, generator=g), torch.randn(64, generator=g)
+
+    def fn(x, r, w, b):
+        s = x + r
+        early = s * 2.0  # defined before the norm chain
+        if kind == "rms":
+            y = s * torch.rsqrt(s.pow(2).mean(-1, keepdim=True) + 1e-6) * w
+        else:
+            y = F.layer_norm(s, s.shape[-1:], w, b, 1e-5)
+        return y, early
+
+    want, got, mods, atens = _compile(tgt, fn, x, r, w, b)
+    _same(got[0], want[0])
+    _same(got[1], want[1])
+    assert mods == ["xg_add_rms_norm" if kind == "rms" else "xg_add_layer_norm"], mods
+    assert not any("add.Tensor" in a for a in atens)
+
+
+def test_add_norm_keeps_the_add_when_the_fused_call_cannot_move():
+    """Hand-built graph: the sum has a user before the norm AND the norm's weight is defined after the add, so the
+    fused call can neither stay at the norm (its second output would be used before it exists) nor move to the add.
+    The pattern then fuses without the second output and leaves the add in place; the graph must lint."""
+    from torch import fx
+
+    from xpu_graph_b200 import modules as M
+    from xpu_graph_b200.target.patterns import FusedAddNorm
+
+    graph = fx.Graph()
+    a, b = graph.placeholder("a"), graph.placeholder("b")
+    add = graph.call_function(torch.ops.aten.add.Tensor, (a, b))
+    early = graph.call_function(torch.ops.aten.mul.Tensor, (add, 2.0))
+    w = graph.placeholder("w")  # placeholders normally lead the graph; any late-defined operand behaves like this one
+    norm = graph.call_module("custom_rms_norm", (add, w, 1e-6))
+    graph.output((norm, early))
+    root = torch.nn.Module()
+    root.add_module("custom_rms_norm", M.RMSNormModule())
+    gm = fx.GraphModule(root, graph)
+    t = torch.empty(4, 8)
+    for n, v in ((a, t), (b, t), (add, t), (early, t), (w, torch.empty(8)), (norm, t)):
+        n.meta["val"] = v
+    M.ALLOWED_DEVICE_TYPES.add("cpu")
+    assert FusedAddNorm().process(gm) is True
+    gm.graph.lint()
+    mods = [n.target for n in gm.graph.nodes if n.op == "call_module"]
+    assert mods == ["xg_add_rms_norm_y"]
+    assert any(n.op == "call_function" and n.target is torch.ops.aten.add.Tensor for n in gm.graph.nodes)
+
+
+def test_rope_with_tables_of_another_dtype_is_left_alone(tgt):
+    """bf16 x with fp32 cos / sin: eager promotes the result to fp32; the kernel would return bf16 and round the
+    tables, so the chain must stay as it is."""
+    from xpu_graph_b200.workloads import rotate_half
+
+    g = torch.Generator().manual_seed(5)
+    x = torch.randn(2, 3, 10, 16, generator=g).to(torch.bfloat16)
+    c, s = torch.randn(10, 16, generator=g), torch.randn(10, 16, generator=g)
+    want, got, mods, atens = _compile(tgt, lambda x, c, s: x * c + rotate_half(x) * s, x, c, s)
+    assert got.dtype == torch.float32 == want.dtype
+    _same(got, want)
+    assert "xg_rope" not in mods
+
+
 @pytest.mark.parametrize("act", ["none", "gelu", "relu", "silu"])
 @pytest.mark.parametrize("bias", [False, True])
 def test_dense_layer(tgt, xlog, act, bias):
@@ -194,6 +282,101 @@ def test_decomposed_attention_goes_through_fused_sdpa(tgt, xlog):
     _same(got, want)
     assert "xg_sdpa" in mods
     assert "Pattern.FusedSDPA changed graph" in xlog.text and "Pattern.FusedSdpa changed graph" in xlog.text
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("form", ["functional", "module", "residual"])
+def test_rms_norm_as_lowered_from_torch(tgt, xlog, dtype, form):
+    """F.rms_norm / nn.RMSNorm reach the compiler as a pow-mean-add.Scalar-rsqrt chain (with an fp32 detour for 16-bit
+    inputs), which the reference's FusedRMSNorm does not match (check_ops.py:88-89 wants add.Tensor): the target's own
+    matcher turns it into the fused norm, and a preceding residual add is folded in as for the hand-written form."""
+    g = torch.Generator().manual_seed(11)
+    x, r = torch.randn(6, 64, generator=g).to(dtype), torch.randn(6, 64, generator=g).to(dtype)
+    if form == "module":
+        m = torch.nn.RMSNorm(64, eps=1e-6).to(dtype)
+        with torch.no_grad():
+            m.weight.copy_(torch.randn(64, generator=g))
+        want, got, mods, atens = _compile(tgt, m, x)
+        expect = ["xg_rms_norm"]
+    else:
+        w = torch.randn(64, generator=g).to(dtype)
+        if form == "functional":
+            want, got, mods, atens = _compile(tgt, lambda x, w: F.rms_norm(x, (64,), w, 1e-6), x, w)
+            expect = ["xg_rms_norm"]
+        else:
+            want, got, mods, atens = _compile(tgt, lambda x, r, w: F.rms_norm(x + r, (64,), w, 1e-6), x, r, w)
+            expect = ["xg_add_rms_norm_y"]
+    _same(got, want, 1e-5 if dtype == torch.float32 else 1e-2)
+    assert mods == expect, mods
+    assert "Pattern.FusedRmsNormLowered changed graph" in xlog.text
+    assert not any("rsqrt" in a or "pow" in a or "mean" in a for a in atens), atens
+
+
+def test_attention_with_a_tensor_scale(tgt, xlog):
+    """A tensor-valued softmax scale: the reference's FusedSDPA wraps it (SDPAWrappedScale,
+    default_replacements.py:39-55) instead of emitting the aten call; the target folds the scale into q and runs the
+    fused attention with scale 1."""
+    g = torch.Generator().manual_seed(3)
+    q, k, v = (torch.randn(4, 20, 32, generator=g) for _ in range(3))
+    scale = torch.tensor(0.3)
+
+    def fn(q, k, v, scale):
+        s = torch.bmm(q, k.transpose(1, 2)) * scale
+        return torch.bmm(torch.softmax(s, dim=-1), v)
+
+    want, got, mods, atens = _compile(tgt, fn, q, k, v, scale)
+    _same(got, want)
+    assert mods == ["xg_sdpa"], mods
+    assert "Pattern.FusedSDPA changed graph" in xlog.text and "Pattern.FusedSdpaTensorScale changed graph" in xlog.text
+
+
+def test_single_row_gathers(tgt, xlog):
+    """table[idx] in its three graph forms (embedding, advanced indexing on dim 0, index_select) -> the gather kernel;
+    negative indices of the indexing forms count from the end as in eager."""
+    g = torch.Generator().manual_seed(6)
+    table = torch.randn(50, 16, generator=g)
+    idx = torch.randint(0, 50, (7, 3), generator=g)
+    neg = torch.tensor([0, -1, 49, -50, 3])
+
+    def fn(table, idx, neg):
+        return F.embedding(idx, table) * 2.0, table[neg] + 1.0, torch.index_select(table, 0, idx[:, 0]) - 1.0
+
+    want, got, mods, atens = _compile(tgt, fn, table, idx, neg)
+    for a, b in zip(got, want):
+        _same(a, b)
+    assert sorted(mods) == ["xg_row_gather", "xg_row_gather", "xg_row_gather_wrap"], mods
+    assert "Pattern.FusedRowGather changed graph" in xlog.text
+    assert not any("embedding" in a or "index" in a for a in atens), atens
+
+
+def test_gather_with_a_repeated_index_uses_expand(tgt, xlog):
+    """gather(x, 1, idx.unsqueeze(-1).repeat(1, 1, C)): the repeat becomes an expand
+    (targets/mlu/repeat_to_expand.py:25-56 does the same for the MLU target)."""
+    g = torch.Generator().manual_seed(7)
+    x = torch.randn(4, 9, 8, generator=g)
+    idx = torch.randint(0, 9, (4, 5), generator=g)
+    want, got, mods, atens = _compile(tgt, lambda x, idx: torch.gather(x, 1, idx.unsqueeze(-1).repeat(1, 1, 8)) * 1.0, x, idx)
+    assert torch.equal(got, want)
+    assert "Pattern.GatherIndexRepeatToExpand changed graph" in xlog.text
+    assert not any("repeat" in a for a in atens) and any("expand" in a for a in atens), atens
+
+
+def test_masked_slice_cat(tgt, xlog):
+    """cat of where(mask, 0, slice) over one source: the common passes merge the per-slice where nodes, FusedCatSlice
+    fuses the slices, and the target folds the remaining where into the copy (MaskedSliceCatModule)."""
+    g = torch.Generator().manual_seed(8)
+    src = torch.randn(12, 200, generator=g)
+    mask = torch.rand(12, 1, generator=g) < 0.4
+
+    def fn(src, mask):
+        parts = [src[:, 0:32], src[:, 64:96], src[:, 100:132], src[:, 10:42]]
+        zero = torch.zeros_like(parts[0])
+        return torch.cat([torch.where(mask, zero, p) for p in parts], dim=-1)
+
+    want, got, mods, atens = _compile(tgt, fn, src, mask)
+    assert torch.equal(got, want)
+    assert mods == ["xg_masked_slice_cat"], (mods, atens)
+    assert not any("where" in a or "slice" in a for a in atens), atens
 
 
 def test_slice_fusions_use_target_modules(tgt, xlog):
@@ -394,18 +577,29 @@ def test_compile_cache_round_trip(tgt, xlog, tmp_path):
         _same(outs[1], m(*inp), 1e-2)
 
 
-def test_interceptor_monitors_the_target(tgt):
-    """enable_interceptor runs the original graph beside the compiled one (interceptor.py:93-179); with the
-    target installed the comparison passes within its tolerance."""
-    from xpu_graph import XpuGraph
+def test_interceptor_monitors_the_target(tgt, xlog, monkeypatch):
+    """enable_interceptor runs the original graph beside the compiled one on every call (interceptor.py:93-179); through
+    the target's backend() the reference's interceptor monitors the fused graph: agreement stays silent, a wrong
+    kernel is reported and dumped."""
+    from xpu_graph_b200 import modules as M
     from xpu_graph_b200.workloads import make_encoder
 
+    if torch._utils._get_available_device_type() is None:
+        # the interceptor forks the RNG state of "the available device type" (interceptor.py:127); a host without any
+        # accelerator has none, which torch.random.fork_rng rejects: name the CUDA module (zero devices to fork here)
+        monkeypatch.setattr(torch._utils, "_get_available_device_type", lambda: "cuda")
     m, x = make_encoder(seed=0, batch=2, seq=16, hidden=64, heads=4, ffn=128)
     cfg = tgt.make_config(enable_interceptor="rtol=1e-3,atol=1e-4")
-    try:
-        be = XpuGraph(cfg)
-        with torch.no_grad():
-            got = torch.compile(m, backend=be, dynamic=False)(x)
-            _same(got, m(x), 1e-4)
-    except Exception as e:  # the reference's own front-end (dispatch_graph) does not run on every torch release
-        pytest.skip(f"reference front-end unavailable on this torch: {type(e).__name__}")
+    with torch.no_grad():
+        compiled = torch.compile(m, backend=tgt.backend(cfg), dynamic=False)
+        got = compiled(x)
+        _same(got, m(x), 1e-4)
+        assert "Monitored inference" in xlog.text and "diverges" not in xlog.text
+        # a broken replacement is caught: make the fused LayerNorm return something else for one call
+        keep = M.LayerNormModule.forward
+        try:
+            M.LayerNormModule.forward = lambda self, inputs, weights, bias, epsilon: keep(self, inputs, weights, bias, epsilon) + 1.0
+            compiled(x)
+        finally:
+            M.LayerNormModule.forward = keep
+    assert "The inference pass diverges" in xlog.text

@@ -37,7 +37,8 @@ def _dense_ws(L, lib, x, w, b, r, act, out, ws):
                                  torch.cuda.current_stream().cuda_stream)
 
 
-@pytest.mark.parametrize("M,K,N,act", [(256, 4096, 4096, "gelu"), (200, 1024, 1000, "none"), (4096, 256, 256, "silu")])
+@pytest.mark.parametrize("M,K,N,act", [(256, 4096, 4096, "gelu"), (200, 1024, 1000, "none"), (4096, 256, 256, "silu"),
+                                       (64, 8192, 4096, "gelu")])
 def test_static_scratch_matches_workspace_entry(cuda_device, M, K, N, act):
     from xpu_graph_b200 import lib
 
@@ -63,8 +64,14 @@ def test_static_scratch_matches_workspace_entry(cuda_device, M, K, N, act):
         torch.cuda.synchronize()
         outs.append(out)
     assert lib.tc_status() == 0
+    # the same arithmetic restated on the CPU: act(x @ w^T + b + r)
+    from oracle import ref_ops
+
+    pre = ref_ops.dense(x.cpu(), w.cpu(), True, b.cpu(), "none") + r.cpu()
+    oracle = ref_ops._ACTS[act](pre)
     for out in outs:
         assert_parity(out, want, f"static-scratch dense {M}x{K}x{N} {act}", magnitude=r)
+        assert_parity(out, oracle, f"static-scratch dense {M}x{K}x{N} {act} vs the CPU oracle", magnitude=r)
     assert torch.equal(outs[0], outs[1]), "the second call must not see the first call's leftovers"
     # nothing but the two output tensors was allocated while the entry point ran
     grown = torch.cuda.memory_allocated() - before

@@ -24,6 +24,7 @@ SOURCES = [
     "copy_fusions.cu",
     "gemm.cu",
     "gemm_tc.cu",
+    "gemm_tc_ksplit.cu",
     "gemm_f32.cu",
     "split_bf16x3.cu",
     "sdpa.cu",

@@ -26,8 +26,13 @@ bool bgemm_single_launch_ok(const void* A, const void* B, int64_t batch, int64_t
 int bgemm_tc_entry(const void* A, const void* B, const void* bias, const void* residual, void* out, int64_t batch, int64_t M,
                    int64_t N, int64_t K, int64_t lda, int64_t ldb, int64_t ldc, int64_t ldr, int64_t sa, int64_t sb,
                    int64_t sbias, int64_t sr, int64_t sc, int trans_b, int act, int dtype, cudaStream_t st);
+bool plan_ksplit(int64_t M, int64_t N, int64_t K, int dtype, int* S_out, int* tn_out);
+int gemm_tc_ksplit_entry(const void* A, const void* W, const void* bias, const void* residual, void* out, int64_t M,
+                         int64_t N, int64_t K, int64_t lda, int64_t ldw, int64_t ldc, int64_t ldr, int act, int dtype, int S,
+                         int tn, cudaStream_t st);
 int read_tc_status(unsigned int* host_out, int reset);
 int read_sdpa_status(unsigned int* host_out, int reset);
+int read_ksplit_status(unsigned int* host_out, int reset);
 
 namespace {
 int validate_gemm(const char* name, const void* A, const void* B, const void* residual, void* out, int64_t M, int64_t N,
@@ -74,6 +79,28 @@ extern "C" int xg_gemm_bias_act_static(const void* A, const void* B, const void*
         return fail(XG_ERR_UNSUPPORTED, "xg_gemm_bias_act_static: 16-bit dtypes only (the fp32 kernel uses no scratch)");
     return gemm_tc_static_entry(A, B, bias, residual, out, M, N, K, lda, ldb, ldc, ldr, trans_b, act, dtype,
                                 reinterpret_cast<cudaStream_t>(stream));
+}
+
+extern "C" int xg_gemm_bias_act_cluster(const void* A, const void* W, const void* bias, const void* residual, void* out,
+                                        int64_t M, int64_t N, int64_t K, int64_t lda, int64_t ldw, int64_t ldc, int64_t ldr,
+                                        int act, int dtype, int splits, int tile_n, void* stream) {
+    using namespace xg;
+    int rc = validate_gemm("xg_gemm_bias_act_cluster", A, W, residual, out, M, N, K, lda, ldw, ldc, ldr, 1, act, dtype);
+    if (rc != XG_OK) return rc;
+    if (dtype != XG_BF16 && dtype != XG_F16)
+        return fail(XG_ERR_UNSUPPORTED, "xg_gemm_bias_act_cluster: 16-bit dtypes only");
+    if ((reinterpret_cast<uintptr_t>(A) & 15u) || (reinterpret_cast<uintptr_t>(W) & 15u) || lda % 8 != 0 || ldw % 8 != 0)
+        return fail(XG_ERR_UNSUPPORTED, "xg_gemm_bias_act_cluster: A/W must be 16-byte aligned with row strides multiple of 8 elements");
+    if (M == 0 || N == 0) return XG_OK;
+    if (M > (int64_t)256 * 0x7fff || N > (int64_t)64 * 0x7fffff || K > 0x7fffffff)
+        return fail(XG_ERR_TOO_LARGE, "xg_gemm_bias_act_cluster: extent too large");
+    return gemm_tc_ksplit_entry(A, W, bias, residual, out, M, N, K, lda, ldw, ldc, ldr, act, dtype, splits, tile_n,
+                                reinterpret_cast<cudaStream_t>(stream));
+}
+
+extern "C" int xg_gemm_cluster_plan(int64_t M, int64_t N, int64_t K, int dtype, int* splits, int* tile_n) {
+    if (!splits || !tile_n || M <= 0 || N <= 0 || K <= 0 || (dtype != XG_BF16 && dtype != XG_F16)) return 0;
+    return xg::plan_ksplit(M, N, K, dtype, splits, tile_n) ? 1 : 0;
 }
 
 extern "C" int64_t xg_gemm_static_scratch_bytes(void) { return xg::static_scratch_capacity(); }
@@ -148,6 +175,9 @@ extern "C" int xg_tc_status(unsigned int* status, int reset) {
     if (rc != XG_OK) return rc;
     rc = xg::read_sdpa_status(&b, reset);
     if (rc != XG_OK) return rc;
-    *status = a | b;
+    unsigned int c = 0;
+    rc = xg::read_ksplit_status(&c, reset);
+    if (rc != XG_OK) return rc;
+    *status = a | b | (c << 8);
     return XG_OK;
 }

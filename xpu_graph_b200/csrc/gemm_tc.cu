@@ -36,6 +36,11 @@ int gemm_tc_entry(const void* A, const void* B, const void* bias, const void* re
                   void* workspace, int64_t ws_bytes, cudaStream_t st, bool force_split = false,
                   const GemmExtras* extras = nullptr);
 
+bool plan_ksplit(int64_t M, int64_t N, int64_t K, int dtype, int* S_out, int* tn_out);
+int gemm_tc_ksplit_entry(const void* A, const void* W, const void* bias, const void* residual, void* out, int64_t M,
+                         int64_t N, int64_t K, int64_t lda, int64_t ldw, int64_t ldc, int64_t ldr, int act, int dtype, int S,
+                         int tn, cudaStream_t st);
+
 struct GemmPlan {
     int bn;      // tile width: 64, 128 or 256
     int splits;  // split-K factor (1 = none)
@@ -948,6 +953,8 @@ GemmPlan plan_gemm(int64_t M, int64_t N, int64_t K, int64_t ws_bytes, int sms) {
 }
 
 int64_t gemm_workspace_bytes(int64_t M, int64_t N, int64_t K) {
+    int S = 0, tn = 0;
+    if (plan_ksplit(M, N, K, XG_BF16, &S, &tn)) return 0;  // the cluster kernel reduces through shared memory
     const GemmPlan pl = plan_gemm(M, N, K, (int64_t)1 << 40, num_sms());
     return pl.splits > 1 ? (int64_t)pl.splits * M * N * 4 : 0;
 }
@@ -1064,6 +1071,12 @@ int gemm_tc_entry(const void* A, const void* B, const void* bias, const void* re
     if (M * N == 0) return XG_OK;
     if (M > (int64_t)BM * 0x7fffff || N > (int64_t)64 * 0x7fffff || K > 0x7fffffff)
         return fail(XG_ERR_TOO_LARGE, "xg_gemm_bias_act: extent too large");
+    if (trans_b && !force_split && !(extras && extras->rope_cos)) {
+        // few output tiles: K split over the CTA pairs of a cluster, partial sums exchanged through shared memory
+        int S = 0, tn = 0;
+        if (plan_ksplit(M, N, K, dtype, &S, &tn))
+            return gemm_tc_ksplit_entry(A, B, bias, residual, out, M, N, K, lda, ldb, ldc, ldr, act, dtype, S, tn, st);
+    }
     if (dtype == XG_BF16)
         return gemm_tc_dispatch<__nv_bfloat16>(A, B, bias, residual, out, M, N, K, lda, ldb, ldc, ldr, trans_b, act, workspace, ws_bytes, force_split, extras, st);
     return gemm_tc_dispatch<__half>(A, B, bias, residual, out, M, N, K, lda, ldb, ldc, ldr, trans_b, act, workspace, ws_bytes, force_split, extras, st);
@@ -1229,7 +1242,12 @@ static int static_scratch_address(void** out) {
 int gemm_tc_static_entry(const void* A, const void* B, const void* bias, const void* residual, void* out, int64_t M,
                          int64_t N, int64_t K, int64_t lda, int64_t ldb, int64_t ldc, int64_t ldr, int trans_b, int act,
                          int dtype, cudaStream_t st) {
-    if (M * N == 0) return XG_OK;
+    if (M < 0 || N < 0 || K < 0) return fail(XG_ERR_INVALID_ARG, "xg_gemm_bias_act_static: negative extent");
+    if (M == 0 || N == 0) return XG_OK;
+    // the extents are bounded before any product of them is formed: M * N of huge extents could wrap
+    if (M > kStaticScratchBytes || N > kStaticScratchBytes)
+        return fail(XG_ERR_TOO_LARGE, "xg_gemm_bias_act_static: M = %lld, N = %lld is beyond the built-in scratch array; use "
+                    "xg_gemm_bias_act_ws with your own workspace", (long long)M, (long long)N);
     const int64_t need = 2 * M * N * 4;  // two fp32 partial-sum planes is the least a split needs
     if (need > kStaticScratchBytes)
         return fail(XG_ERR_TOO_LARGE,

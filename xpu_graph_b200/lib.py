@@ -6,6 +6,7 @@ op that needs it fails loudly.
 """
 from __future__ import annotations
 
+import contextlib
 import ctypes
 import os
 import threading
@@ -45,6 +46,9 @@ SIGNATURES = {
     "xg_gemm_bias_act_ws": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64,
                                     c_int64, c_int64, c_int64, c_int, c_int, c_int, c_void_p, c_int64, c_void_p]),
     "xg_gemm_workspace_bytes": (c_int64, [c_int64, c_int64, c_int64, c_int]),
+    "xg_gemm_bias_act_cluster": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64,
+                                         c_int64, c_int64, c_int64, c_int, c_int, c_int, c_int, c_void_p]),
+    "xg_gemm_cluster_plan": (c_int, [c_int64, c_int64, c_int64, c_int, POINTER(c_int), POINTER(c_int)]),
     "xg_gemm_bias_act_static": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64,
                                         c_int64, c_int64, c_int64, c_int, c_int, c_int, c_void_p]),
     "xg_gemm_static_scratch_bytes": (c_int64, []),
@@ -127,3 +131,36 @@ def tc_status(reset: bool = True) -> int:
     out = c_uint(0)
     check(load().xg_tc_status(ctypes.byref(out), 1 if reset else 0), "xg_tc_status")
     return int(out.value)
+
+
+# entry points that enqueue no kernel (queries and status reads)
+QUERY_ENTRY_POINTS = frozenset({"xg_version", "xg_device_arch_ok", "xg_last_error", "xg_tc_status", "xg_gemm_workspace_bytes",
+                                "xg_gemm_static_scratch_bytes", "xg_gemm_f32x3_padded_k", "xg_gemm_cluster_plan"})
+
+
+@contextlib.contextmanager
+def call_hook(before=None, after=None):
+    """While active, every call into the library made through ``load()`` is reported: ``before(name, args)`` just
+    before the C function runs and ``after(name, args, rc)`` just after it returned (both optional; ``args`` are the
+    marshalled arguments in the header's order). For observers that live outside the ops - launch counters, timers
+    that bracket a kernel with events on the launching stream, call logs. Not thread-safe; do not nest."""
+    lib = load()
+    saved = {}
+    for name in SIGNATURES:
+        fn = getattr(lib, name)
+        saved[name] = fn
+
+        def wrapped(*args, _fn=fn, _name=name):
+            if before is not None:
+                before(_name, args)
+            rc = _fn(*args)
+            if after is not None:
+                after(_name, args, rc)
+            return rc
+
+        setattr(lib, name, wrapped)
+    try:
+        yield lib
+    finally:
+        for name, fn in saved.items():
+            setattr(lib, name, fn)

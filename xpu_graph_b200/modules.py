@@ -260,6 +260,23 @@ class GatherStackModule(torch.nn.Module):
         return _X.gather_stack(list(tables), idx, row_mask, bool(zero_when))
 
 
+class RowGatherModule(torch.nn.Module):
+    """table[idx] for a 2-D table and an integer index tensor of any shape -> [*idx.shape, D] (the single-lookup forms
+    aten.embedding, aten.index.Tensor with one index on dim 0, aten.index_select on dim 0). ``wrap_negative``: indices
+    below zero count from the end, as aten.index does (aten.embedding does not allow them)."""
+
+    def __init__(self, wrap_negative: bool = False):
+        super().__init__()
+        self.wrap_negative = bool(wrap_negative)
+
+    def forward(self, table, idx):
+        shape = list(idx.shape)
+        flat = idx.reshape(-1, 1).to(torch.int64)
+        if self.wrap_negative:
+            flat = torch.where(flat < 0, flat + table.shape[0], flat)
+        return _X.gather_stack([table], flat, None, True).view(shape + [table.shape[1]])
+
+
 class ComboSumModule(torch.nn.Module):
     """ComboSum3dInp target (structure/fuse_combosum.py:82-98): forward(input_list, dim) -> list of
     sum(x, dim[0]); one launch for the whole list (the MLU module splits by size,

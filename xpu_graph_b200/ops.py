@@ -21,47 +21,6 @@ from . import lib as _lib
 
 NS = "xg_sm100"
 
-# Launch accounting for the benchmark: every C-ABI call that enqueues a kernel bumps the counter;
-# when GEMM_EVENTS is a list, dense launches are bracketed by CUDA events on the launching stream
-# and (start, end, flops) is appended.
-_LAUNCHES = 0
-GEMM_EVENTS = None
-
-
-def reset_counters() -> None:
-    global _LAUNCHES
-    _LAUNCHES = 0
-
-
-def launch_count() -> int:
-    return _LAUNCHES
-
-
-def _bump(n: int = 1) -> None:
-    global _LAUNCHES
-    _LAUNCHES += n
-
-
-class _GemmTimer:
-    def __init__(self, ref: torch.Tensor, flops: int):
-        self.on = GEMM_EVENTS is not None
-        if self.on:
-            self.flops = flops
-            self.stream = torch.cuda.current_stream(ref.device)
-            self.e0 = torch.cuda.Event(enable_timing=True)
-            self.e1 = torch.cuda.Event(enable_timing=True)
-
-    def __enter__(self):
-        if self.on:
-            self.e0.record(self.stream)
-        return self
-
-    def __exit__(self, *exc):
-        if self.on:
-            self.e1.record(self.stream)
-            GEMM_EVENTS.append((self.e0, self.e1, self.flops))
-        return False
-
 _DTYPE_CODE = {torch.float32: _lib.XG_F32, torch.bfloat16: _lib.XG_BF16, torch.float16: _lib.XG_F16}
 
 
@@ -132,12 +91,10 @@ def _norm_call(kind: str, x, residual, weight, bias, eps: float, want_sum: bool)
         rc = L.xg_rmsnorm(_ptr(x2), _ptr(r2), _ptr(w), _ptr(y), _ptr(s), rows, hidden, _row_stride(x2),
                           _row_stride(r2) if r2 is not None else 0, float(eps), code, wcode, _stream(x))
         _lib.check(rc, "xg_rmsnorm")
-        _bump()
     else:
         rc = L.xg_layernorm(_ptr(x2), _ptr(r2), _ptr(w), _ptr(b), _ptr(y), _ptr(s), rows, hidden, _row_stride(x2),
                             _row_stride(r2) if r2 is not None else 0, float(eps), code, wcode, _stream(x))
         _lib.check(rc, "xg_layernorm")
-        _bump()
     y = y.view(x.shape)
     if want_sum:
         return y, s.view(x.shape)
@@ -225,7 +182,6 @@ def rope(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> torch.Tensor:
     rc = _lib.load().xg_rope(_ptr(x), _ptr(cos2), _ptr(sin2), _ptr(y), B, H, S, D, x.stride(0), x.stride(1), x.stride(2),
                              y.stride(0), y.stride(1), y.stride(2), _code(x.dtype), _stream(x))
     _lib.check(rc, "xg_rope")
-    _bump()
     return y
 
 
@@ -244,7 +200,6 @@ def swiglu(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
     rc = _lib.load().xg_swiglu(_ptr(g2), _ptr(u2), _ptr(out), rows, cols, _row_stride(g2), _row_stride(u2), cols,
                                _code(gate.dtype), _stream(gate))
     _lib.check(rc, "xg_swiglu")
-    _bump()
     return out.view(gate.shape)
 
 
@@ -272,23 +227,44 @@ def _f32_on_tensor_cores(M: int, N: int, K: int) -> bool:
     return 2 * M * N * K >= F32_TENSOR_MIN_FLOPS and K <= F32_TENSOR_MAX_K
 
 
+def _planes_tag(weight: torch.Tensor, weight_trans: bool):
+    """Key under which a weight's bf16 planes are kept, or None when the tensor cannot be tracked: tensors made under
+    torch.inference_mode() have no version counter, so their planes are rebuilt on every call."""
+    try:
+        version = weight._version
+    except RuntimeError:
+        return None
+    return (version, weight.data_ptr(), tuple(weight.shape), tuple(weight.stride()), bool(weight_trans))
+
+
+def invalidate_weight_planes(weight: torch.Tensor) -> None:
+    """Drop the bf16 planes kept for an fp32 weight. Needed after the weight was rewritten through ``.data`` (or any
+    other route that does not bump its version counter): the planes are keyed on the counter and would go stale."""
+    try:
+        del weight._xg_bf16_planes
+    except AttributeError:
+        pass
+
+
 def _weight_planes(L, weight: torch.Tensor, weight_trans: bool, N: int, K: int) -> torch.Tensor:
     """The three bf16 planes of an fp32 weight, [N, 3*Kp]. They ride on the weight tensor object itself and are
     rebuilt when its version counter, layout or orientation changes, so a dense layer's weight is split once in
-    inference and the planes go away with the tensor; a fresh view of a weight is simply split again."""
-    tag = (weight._version, weight.data_ptr(), tuple(weight.shape), tuple(weight.stride()), bool(weight_trans))
-    kept = getattr(weight, "_xg_bf16_planes", None)
+    inference and the planes go away with the tensor; a fresh view of a weight is simply split again. In-place
+    updates through ``weight.data`` do not move the counter: call ``invalidate_weight_planes`` after those. A
+    captured CUDA graph replays with the planes that existed at capture."""
+    tag = _planes_tag(weight, weight_trans)
+    kept = getattr(weight, "_xg_bf16_planes", None) if tag is not None else None
     if kept is not None and kept[0] == tag:
         return kept[1]
     Kp = int(L.xg_gemm_f32x3_padded_k(K))
     w3 = torch.empty((N, 3 * Kp), dtype=torch.bfloat16, device=weight.device)
     rc = L.xg_split_bf16x3(_ptr(weight), N, K, _row_stride(weight), 0 if weight_trans else 1, _ptr(w3), _stream(weight))
     _lib.check(rc, "xg_split_bf16x3")
-    _bump()
-    try:
-        weight._xg_bf16_planes = (tag, w3)
-    except (AttributeError, RuntimeError):  # a tensor type without instance attributes: no reuse
-        pass
+    if tag is not None:
+        try:
+            weight._xg_bf16_planes = (tag, w3)
+        except (AttributeError, RuntimeError):  # a tensor type without instance attributes: no reuse
+            pass
     return w3
 
 
@@ -298,11 +274,9 @@ def _dense_f32x3(L, x, weight, weight_trans, bias, residual, ldr, act, out, M, N
     a3 = torch.empty((M, 3 * Kp), dtype=torch.bfloat16, device=x.device)
     rc = L.xg_split_bf16x3(_ptr(x), M, K, _row_stride(x), 0, _ptr(a3), _stream(x))
     _lib.check(rc, "xg_split_bf16x3")
-    with _GemmTimer(x, 2 * M * N * K):
-        rc = L.xg_gemm_f32x3(_ptr(a3), _ptr(w3), _ptr(bias), _ptr(residual), _ptr(out), M, N, K, N, ldr,
-                             _lib.ACT_CODES[act], 0, _stream(x))
+    rc = L.xg_gemm_f32x3(_ptr(a3), _ptr(w3), _ptr(bias), _ptr(residual), _ptr(out), M, N, K, N, ldr,
+                         _lib.ACT_CODES[act], 0, _stream(x))
     _lib.check(rc, "xg_gemm_f32x3")
-    _bump(2)
     return out
 
 
@@ -335,7 +309,6 @@ def dense_tower(x: torch.Tensor, weights: List[torch.Tensor], weight_trans: List
     a3 = torch.empty((M, 3 * int(L.xg_gemm_f32x3_padded_k(dims[0]))), dtype=torch.bfloat16, device=x.device)
     rc = L.xg_split_bf16x3(_ptr(x), M, dims[0], _row_stride(x), 0, _ptr(a3), _stream(x))
     _lib.check(rc, "xg_split_bf16x3")
-    _bump()
     for i in range(n):
         K, N = dims[i], dims[i + 1]
         w = _mat(weights[i])
@@ -348,11 +321,9 @@ def dense_tower(x: torch.Tensor, weights: List[torch.Tensor], weight_trans: List
             out = torch.empty((M, N), dtype=torch.float32, device=x.device)
         else:
             out = torch.empty((M, 3 * int(L.xg_gemm_f32x3_padded_k(N))), dtype=torch.bfloat16, device=x.device)
-        with _GemmTimer(x, 2 * M * N * K):
-            rc = L.xg_gemm_f32x3(_ptr(a3), _ptr(w3), _ptr(b), None, _ptr(out), M, N, K, N, 0, _lib.ACT_CODES[acts[i]],
-                                 0 if last else 1, _stream(x))
+        rc = L.xg_gemm_f32x3(_ptr(a3), _ptr(w3), _ptr(b), None, _ptr(out), M, N, K, N, 0, _lib.ACT_CODES[acts[i]],
+                             0 if last else 1, _stream(x))
         _lib.check(rc, "xg_gemm_f32x3")
-        _bump()
         a3 = out
     return a3
 
@@ -390,12 +361,10 @@ def dense(x: torch.Tensor, weight: torch.Tensor, weight_trans: bool, bias: Optio
         ws_bytes = int(L.xg_gemm_workspace_bytes(M, N, K, _code(x.dtype)))
         if ws_bytes > 0:  # split-K scratch for weight-streaming shapes (small M)
             ws = torch.empty(ws_bytes, dtype=torch.uint8, device=x.device)
-    with _GemmTimer(x, 2 * M * N * K):
-        rc = L.xg_gemm_bias_act_ws(_ptr(x), _ptr(weight), _ptr(bias), _ptr(residual), _ptr(out), M, N, K,
-                                   _row_stride(x), _row_stride(weight), N, ldr, 1 if weight_trans else 0,
-                                   _lib.ACT_CODES[act], _code(x.dtype), _ptr(ws), ws_bytes, _stream(x))
+    rc = L.xg_gemm_bias_act_ws(_ptr(x), _ptr(weight), _ptr(bias), _ptr(residual), _ptr(out), M, N, K,
+                               _row_stride(x), _row_stride(weight), N, ldr, 1 if weight_trans else 0,
+                               _lib.ACT_CODES[act], _code(x.dtype), _ptr(ws), ws_bytes, _stream(x))
     _lib.check(rc, "xg_gemm_bias_act")
-    _bump(2 if ws is not None else 1)
     return out
 
 
@@ -426,7 +395,6 @@ def batch_dense(x: torch.Tensor, weight: torch.Tensor, weight_trans: bool, bias:
                                        weight.shape[2], N, N, M * K, weight.shape[1] * weight.shape[2], sbias, sr, M * N,
                                        1 if weight_trans else 0, _lib.ACT_CODES[act], _code(x.dtype), _stream(x))
     _lib.check(rc, "xg_bgemm_bias_act")
-    _bump()
     return out
 
 
@@ -482,11 +450,9 @@ def dense_swiglu(x: torch.Tensor, w_gate: torch.Tensor, w_up: torch.Tensor) -> t
     M, K = x.shape
     N = w_gate.shape[0]
     out = torch.empty((M, N), dtype=x.dtype, device=x.device)
-    with _GemmTimer(x, 4 * M * N * K):
-        rc = _lib.load().xg_gemm_swiglu(_ptr(x), _ptr(w_gate), _ptr(w_up), _ptr(out), M, N, K, _row_stride(x),
-                                        _row_stride(w_gate), N, _code(x.dtype), _stream(x))
+    rc = _lib.load().xg_gemm_swiglu(_ptr(x), _ptr(w_gate), _ptr(w_up), _ptr(out), M, N, K, _row_stride(x),
+                                    _row_stride(w_gate), N, _code(x.dtype), _stream(x))
     _lib.check(rc, "xg_gemm_swiglu")
-    _bump()
     return out
 
 
@@ -507,11 +473,9 @@ def dense_rope(x: torch.Tensor, weight: torch.Tensor, cos: torch.Tensor, sin: to
     cos2 = cos.reshape(seq_len, head_dim).to(x.dtype).contiguous()
     sin2 = sin.reshape(seq_len, head_dim).to(x.dtype).contiguous()
     out = torch.empty((M, N), dtype=x.dtype, device=x.device)
-    with _GemmTimer(x, 2 * M * N * K):
-        rc = _lib.load().xg_gemm_rope(_ptr(x), _ptr(weight), _ptr(cos2), _ptr(sin2), _ptr(out), M, N, K, _row_stride(x),
-                                      _row_stride(weight), N, seq_len, head_dim, _code(x.dtype), _stream(x))
+    rc = _lib.load().xg_gemm_rope(_ptr(x), _ptr(weight), _ptr(cos2), _ptr(sin2), _ptr(out), M, N, K, _row_stride(x),
+                                  _row_stride(weight), N, seq_len, head_dim, _code(x.dtype), _stream(x))
     _lib.check(rc, "xg_gemm_rope")
-    _bump()
     return out
 
 
@@ -549,7 +513,6 @@ def sdpa(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, attn_mask: Optional[
                                  _lib.i64_array(v.stride()[:3]), _lib.i64_array(out.stride()[:3]), mstr, float(scale),
                                  1 if is_causal else 0, _code(q.dtype), _stream(q))
     _lib.check(rc, "xg_sdpa_fwd")
-    _bump()
     return out
 
 
@@ -567,7 +530,6 @@ def _seg_copy(srcs: Sequence[int], dsts: Sequence[int], src_ld: Sequence[int], d
     rc = _lib.load().xg_seg_copy(_lib.ptr_array(srcs), _lib.ptr_array(dsts), _lib.i64_array(src_ld), _lib.i64_array(dst_ld),
                                  _lib.i64_array(lens), n, rows, _ptr(mask), 1 if zero_when else 0, _stream(ref))
     _lib.check(rc, "xg_seg_copy")
-    _bump()
 
 
 def _norm_slices(width: int, starts: Sequence[int], ends: Sequence[int]):
@@ -622,16 +584,33 @@ def _(src, starts, ends, row_mask, zero_when):
     return torch.empty((src.shape[0], sum(e - s for s, e in segs)), dtype=src.dtype, device=src.device)
 
 
+def _checked_starts(width: int, starts: Sequence[int], slice_len: int) -> List[int]:
+    """Slice starts with negative values wrapped; every slice [s, s + slice_len) has to lie inside the row. The
+    reference derives slice_len as end - start of the raw aten.slice arguments (structure/fuse_slice.py:28), so a slice
+    that aten would have clamped (an end past the width, INT64_MAX) arrives here with a length the row does not
+    have: that is refused instead of read past the row."""
+    if slice_len < 0:
+        raise ValueError(f"xg_sm100::multi_slice: negative slice length {slice_len}")
+    out = []
+    for s in starts:
+        s = s + width if s < 0 else s
+        if s < 0 or s + slice_len > width:
+            raise ValueError(f"xg_sm100::multi_slice: slice [{s}, {s + slice_len}) is outside a row of {width} elements")
+        out.append(s)
+    return out
+
+
 @torch.library.custom_op(f"{NS}::multi_slice", mutates_args=(), device_types="cuda")
 def multi_slice(src: torch.Tensor, starts: List[int], slice_len: int) -> torch.Tensor:
     """stack([src[..., s:s+slice_len] for s in starts], 0) -> [num, *src.shape[:-1], slice_len]."""
     lead = list(src.shape[:-1])
+    starts = _checked_starts(src.shape[-1], starts, slice_len)
     s2 = _rows_view(src)
     rows, width = s2.shape
     num = len(starts)
     out = torch.empty((num, rows, slice_len), dtype=src.dtype, device=src.device)
     es = src.element_size()
-    srcs = [s2.data_ptr() + (s + width if s < 0 else s) * es for s in starts]
+    srcs = [s2.data_ptr() + s * es for s in starts]
     dsts = [out.data_ptr() + k * rows * slice_len * es for k in range(num)]
     _seg_copy(srcs, dsts, [_row_stride(s2) * es] * num, [slice_len * es] * num, [slice_len * es] * num, rows, None, False, src)
     return out.view([num] + lead + [slice_len])
@@ -639,6 +618,7 @@ def multi_slice(src: torch.Tensor, starts: List[int], slice_len: int) -> torch.T
 
 @multi_slice.register_fake
 def _(src, starts, slice_len):
+    _checked_starts(src.shape[-1], starts, slice_len)
     return torch.empty([len(starts)] + list(src.shape[:-1]) + [slice_len], dtype=src.dtype, device=src.device)
 
 
@@ -732,7 +712,6 @@ def gather_stack(tables: List[torch.Tensor], idx: torch.Tensor, row_mask: Option
                                     F, _ptr(idx), idx.stride(0), idx.stride(1), _ptr(_mask_bytes(row_mask, rows)),
                                     1 if zero_when else 0, _ptr(out), rows, D, F * D, out.element_size(), _stream(idx))
     _lib.check(rc, "xg_gather_rows")
-    _bump()
     # keep the contiguous copies alive until the launch is enqueued (stream-ordered frees make this safe)
     del tabs
     return out
@@ -762,7 +741,6 @@ def sum3d(inputs: List[torch.Tensor], dim: int) -> List[torch.Tensor]:
         rc = _lib.load().xg_sum3d(_lib.ptr_array([x.data_ptr() for x in xs]), _lib.ptr_array([o.data_ptr() for o in outs]),
                                   _lib.i64_array(shapes), len(xs), int(dim), _code(xs[0].dtype), _stream(xs[0]))
         _lib.check(rc, "xg_sum3d")
-        _bump()
     return outs
 
 
@@ -803,7 +781,6 @@ def _rowsum_cat_impl(a_list, b_list, ranges, batch):
         _lib.i64_array(a_bs), _lib.i64_array(b_bs) if b_list is not None else None, _lib.i64_array(list(ranges)), n,
         batch, C, out.data_ptr(), n * C, _code(a0.dtype), _stream(a0))
     _lib.check(rc, "xg_rowsum_cat")
-    _bump()
     return out
 
 

@@ -87,7 +87,8 @@ def make_config(**overrides):
 def backend(config=None, capture=None, cache=None):
     """``torch.compile`` backend: XpuGraph's inference compiler behind aot_autograd.
 
-    ``capture``: optional dict; the optimised GraphModule is stored under ``capture['gm']``.
+    ``config.enable_interceptor`` ("rtol=2e-2,atol=1e-2", the reference's syntax) wraps the compiled function in the
+    reference's interceptor. ``capture``: optional dict; the optimised GraphModule is stored under ``capture['gm']``.
     ``cache``: optional XpuGraphCache (e.g. ``XpuGraphLocalCache(path)``) used when ``config.enable_cache``."""
     install()
     from torch._dynamo.backends.common import aot_autograd
@@ -103,4 +104,20 @@ def backend(config=None, capture=None, cache=None):
             capture["gm"] = out
         return out
 
-    return aot_autograd(fw_compiler=fw_compiler, keep_inference_input_mutations=True)
+    aot = aot_autograd(fw_compiler=fw_compiler, keep_inference_input_mutations=True)
+    if getattr(cfg, "enable_interceptor", None) is None:
+        return aot
+
+    # enable_interceptor="rtol=...,atol=...": xpu_graph's own interceptor (interceptor.py:16-41, 93-179) runs the
+    # Dynamo graph beside the compiled function on every call and logs / dumps divergences; its front-end attaches it
+    # at compiler.py:214-225, this entry does the same around the aot_autograd result.
+    def monitored_backend(dynamo_gm, example_inputs):
+        import os
+
+        from xpu_graph.interceptor import intercept
+
+        compiled = aot(dynamo_gm, example_inputs)
+        return intercept(compiled, golden_fn=dynamo_gm, fw_metadata=None, is_training=False,
+                         mark=os.environ.get("RANK", "0"), config_str=cfg.enable_interceptor)
+
+    return monitored_backend

@@ -124,6 +124,112 @@ class FusedNativeLayerNorm(Pattern):
         return changed
 
 
+# ---- RMSNorm as lowered from F.rms_norm / nn.RMSNorm -----------------------------------------------------------
+class FusedRmsNormLowered(Pattern):
+    """The two forms that ``F.rms_norm`` / ``nn.RMSNorm`` reach the compiler in on current PyTorch releases, neither of
+    which the reference's FusedRMSNorm matches (its chain matcher asks for ``aten.add.Tensor``,
+    passes/patterns/utils/check_ops.py:88-89 through common/fuse_rmsnorm.py:29-114):
+
+      * the decomposition  [to fp32] -> pow 2 -> mean(last dim, keepdim) -> add.Scalar(eps) -> rsqrt -> mul -> mul(weight)
+        [-> back to the input dtype];
+      * ``aten._fused_rms_norm(x, [H], weight, eps)`` whose second output (the reciprocal rms) is unused.
+
+    Both become an RMSNormModule call, after which the residual-add fusion applies as for the hand-written form."""
+
+    _opt_level = OptLevel.level2
+
+    @staticmethod
+    def _fp32_view_of(node):
+        """(source, cast) when `node` is `_to_copy(source, dtype=float32)` of a 16-bit tensor, else (node, None)."""
+        if _is(node, aten._to_copy.default) and node.kwargs.get("dtype") == torch.float32:
+            src = node.args[0]
+            sv = _val(src)
+            if isinstance(sv, torch.Tensor) and sv.dtype in (torch.bfloat16, torch.float16):
+                return src, node
+        return node, None
+
+    def _match_chain(self, gm, out):
+        """out = mul(mul(X, rsqrt(add.Scalar(mean(pow(X, 2), [last], True), eps))), W)"""
+        if not _is(out, aten.mul.Tensor) or len(out.args) != 2:
+            return None
+        for inner, w in ((out.args[0], out.args[1]), (out.args[1], out.args[0])):
+            if not (_is(inner, aten.mul.Tensor) and isinstance(w, fx.Node) and _only_user(inner, out)):
+                continue
+            for X, rs in ((inner.args[0], inner.args[1]), (inner.args[1], inner.args[0])):
+                if not (isinstance(X, fx.Node) and _is(rs, aten.rsqrt.default) and _only_user(rs, inner)):
+                    continue
+                add = rs.args[0]
+                if not (_is(add, aten.add.Scalar, aten.add.Tensor) and _only_user(add, rs)):
+                    continue
+                mean, eps = add.args[0], add.args[1]
+                if not isinstance(eps, (int, float)) or not (_is(mean, aten.mean.dim) and _only_user(mean, add)):
+                    continue
+                pw = mean.args[0]
+                if not (_is(pw, aten.pow.Tensor_Scalar) and pw.args[1] == 2 and pw.args[0] is X and _only_user(pw, mean)):
+                    continue
+                xv = _val(X)
+                if not _tensor_ok(xv) or xv.dim() < 1:
+                    continue
+                dims = list(mean.args[1]) if isinstance(mean.args[1], (list, tuple)) else [mean.args[1]]
+                keep = mean.args[2] if len(mean.args) > 2 else False
+                if len(dims) != 1 or dims[0] not in (-1, xv.dim() - 1) or not keep:
+                    continue
+                wv = _val(w)
+                if not (isinstance(wv, torch.Tensor) and wv.dim() == 1 and wv.shape[0] == xv.shape[-1]):
+                    continue
+                return X, w, float(eps), [out, inner, rs, add, mean, pw]
+        return None
+
+    def process(self, gm: fx.GraphModule) -> bool:
+        changed = False
+        for node in list(gm.graph.nodes):
+            fused = getattr(aten, "_fused_rms_norm", None)
+            if fused is not None and _is(node, fused.default) and len(node.args) >= 4:
+                x, shape, w, eps = node.args[:4]
+                xv = _val(x)
+                users = list(node.users)
+                if (w is not None and eps is not None and _tensor_ok(xv) and list(shape) == [xv.shape[-1]]
+                        and all(_is(u, operator.getitem) for u in users)
+                        and not any(u.args[1] != 0 and len(u.users) > 0 for u in users)):
+                    _ensure(gm, "xg_rms_norm", M.RMSNormModule)
+                    with gm.graph.inserting_before(node):
+                        new = gm.graph.call_module("xg_rms_norm", (x, w, float(eps)))
+                    _fill_meta(gm, new)
+                    for u in users:
+                        if u.args[1] == 0:
+                            u.replace_all_uses_with(new)
+                        gm.graph.erase_node(u)
+                    gm.graph.erase_node(node)
+                    changed = True
+                continue
+            m = self._match_chain(gm, node)
+            if m is None:
+                continue
+            X, w, eps, chain = m
+            src, cast_in = self._fp32_view_of(X)
+            out = node
+            if cast_in is not None:
+                # 16-bit input computed in fp32: the chain's only consumer has to be the cast back to the input dtype
+                if len(node.users) != 1:
+                    continue
+                back = next(iter(node.users))
+                if not (_is(back, aten._to_copy.default) and back.kwargs.get("dtype") == _val(src).dtype):
+                    continue
+                out = back
+            elif _val(X).dtype != torch.float32:
+                continue  # a 16-bit chain without the fp32 detour rounds after every step: not what the kernel computes
+            _ensure(gm, "xg_rms_norm", M.RMSNormModule)
+            with gm.graph.inserting_before(out):
+                new = gm.graph.call_module("xg_rms_norm", (src, w, eps))
+            _fill_meta(gm, new)
+            out.replace_all_uses_with(new)
+            for dead in ([out] if out is not node else []) + chain + ([cast_in] if cast_in is not None else []):
+                if len(dead.users) == 0:
+                    gm.graph.erase_node(dead)
+            changed = True
+        return changed
+
+
 # ---- scaled dot product attention ----------------------------------------------------------------------
 def _sdpa_targets():
     names = ["scaled_dot_product_attention", "_scaled_dot_product_flash_attention_for_cpu",
@@ -196,6 +302,47 @@ class FusedSdpa(Pattern):
         return changed
 
 
+class FusedSdpaTensorScale(Pattern):
+    """The reference's FusedSDPA keeps a tensor-valued softmax scale out of the aten call: at OptLevel.level2 it emits
+    a ``SDPAWrappedScale`` module whose op reads the scalar on the host (default_replacements.py:39-55,
+    common/fuse_scaled_dot_product_attention.py:149-161, 222-229), at level3 it folds the scale into q (:151-156). Here
+    the wrapped call becomes  q * scale  (the level-3 form: no host read, so the graph stays capturable) followed by
+    the flash kernel with scale 1."""
+
+    _opt_level = OptLevel.level2
+
+    def process(self, gm: fx.GraphModule) -> bool:
+        changed = False
+        for node in list(gm.graph.nodes):
+            if node.op != "call_module" or len(node.args) != 5:
+                continue
+            try:
+                sub = gm.get_submodule(node.target)
+            except AttributeError:
+                continue
+            if type(sub).__name__ != "SDPAWrappedScale":
+                continue
+            q, k, v, mask, scale = node.args
+            qv, kv, vv, sv = _val(q), _val(k), _val(v), _val(scale)
+            if not (_tensor_ok(qv, 4) and _tensor_ok(kv, 4) and _tensor_ok(vv, 4) and isinstance(sv, torch.Tensor)):
+                continue
+            if not (qv.dtype == kv.dtype == vv.dtype) or qv.shape[1] != kv.shape[1] or qv.shape[-1] > 256 or sv.numel() != 1:
+                continue
+            _ensure(gm, "xg_sdpa", M.SDPAModule)
+            with gm.graph.inserting_before(node):
+                qs = gm.graph.call_function(aten.mul.Tensor, (q, scale))
+                _fill_meta(gm, qs)
+                if _val(qs) is not None and _val(qs).dtype != qv.dtype:  # an fp32 scale promotes the product
+                    qs = gm.graph.call_function(aten._to_copy.default, (qs,), {"dtype": qv.dtype})
+                    _fill_meta(gm, qs)
+                new = gm.graph.call_module("xg_sdpa", (qs, k, v, mask, 1.0, False))
+            _fill_meta(gm, new)
+            node.replace_all_uses_with(new)
+            gm.graph.erase_node(node)
+            changed = True
+        return changed
+
+
 # ---- rotate-half RoPE --------------------------------------------------------------------------------------
 class FusedRoPE(Pattern):
     """x*cos + cat(-x[..., D/2:], x[..., :D/2])*sin on a 4-D x -> RopeModule (one pass instead of seven)."""
@@ -262,6 +409,11 @@ class FusedRoPE(Pattern):
             xv, cv, sv = _val(x), _val(cos), _val(sin)
             S, D = xv.shape[2], xv.shape[3]
             if not (isinstance(cv, torch.Tensor) and isinstance(sv, torch.Tensor)):
+                continue
+            # tables of another dtype (fp32 tables next to a 16-bit x) promote the eager result: the kernel computes and
+            # returns x's dtype, so such a chain is left alone
+            nv = _val(node)
+            if not (cv.dtype == sv.dtype == xv.dtype and isinstance(nv, torch.Tensor) and nv.dtype == xv.dtype):
                 continue
             if cv.numel() != S * D or sv.numel() != S * D or tuple(cv.shape[-2:]) != (S, D) or tuple(sv.shape[-2:]) != (S, D):
                 continue
@@ -428,13 +580,24 @@ class FusedAddNorm(Pattern):
             if av.shape != bv.shape or av.dtype != bv.dtype or av.dtype != sv.dtype:
                 continue
             store = len(add.users) > 1
+            anchor = node
+            if store:
+                # The sum's other users read the fused call's second output, so the call has to be defined before the
+                # earliest of them. When one precedes the norm, the call takes the add's place if the norm's remaining
+                # operands (weight, bias) are already defined there; otherwise the add stays for its other users.
+                order = {n: i for i, n in enumerate(gm.graph.nodes)}
+                if any(order[u] < order[node] for u in add.users if u is not node):
+                    if all(order[x] < order[add] for x in node.args[1:] if isinstance(x, fx.Node)):
+                        anchor = add.next
+                    else:
+                        store = False
             if is_rms:
                 name = _ensure(gm, "xg_add_rms_norm" if store else "xg_add_rms_norm_y", lambda: M.AddRMSNormModule(store))
                 args = (a, b) + tuple(node.args[1:])
             else:
                 name = _ensure(gm, "xg_add_layer_norm" if store else "xg_add_layer_norm_y", lambda: M.AddLayerNormModule(store))
                 args = (a, b) + tuple(node.args[1:])
-            with gm.graph.inserting_before(node):
+            with gm.graph.inserting_before(anchor):
                 new = gm.graph.call_module(name, args)
                 _fill_meta(gm, new)
                 if store:
@@ -562,6 +725,173 @@ class FusedEmbeddingStack(Pattern):
                     ins = [a for a in n.all_input_nodes]
                     gm.graph.erase_node(n)
                     dead.extend(i for i in ins if len(i.users) == 0 and i.op == "call_function")
+            changed = True
+        return changed
+
+
+# ---- single row gathers -------------------------------------------------------------------------------------------
+class FusedRowGather(Pattern):
+    """table[idx] on dim 0 of a 2-D table in its three graph forms - ``aten.embedding(table, idx)``,
+    ``aten.index.Tensor(table, [idx])`` and ``aten.index_select(table, 0, idx)`` - -> RowGatherModule (one pass of the
+    gather kernel). Lookups that feed a stack are taken by FusedEmbeddingStack first (this pattern runs in a later
+    group)."""
+
+    _opt_level = OptLevel.level1
+    _pattern_group = PatternGroup.GROUP2
+
+    def process(self, gm: fx.GraphModule) -> bool:
+        changed = False
+        for node in list(gm.graph.nodes):
+            table = idx = None
+            wrap = False
+            if _is(node, aten.embedding.default) and len(node.args) == 2 and not node.kwargs:
+                table, idx = node.args
+            elif _is(node, aten.index.Tensor) and len(node.args) == 2 and len(node.args[1]) == 1 and node.args[1][0] is not None:
+                table, idx, wrap = node.args[0], node.args[1][0], True
+            elif _is(node, aten.index_select.default) and len(node.args) == 3 and node.args[1] == 0:
+                table, idx = node.args[0], node.args[2]  # like embedding, index_select takes no negative indices
+            if table is None:
+                continue
+            tv, iv = _val(table), _val(idx)
+            if not (_tensor_ok(tv, 2) and isinstance(iv, torch.Tensor) and iv.dtype in (torch.int64, torch.int32)):
+                continue
+            if not (_static(tv.shape) and _static(iv.shape)) or iv.dim() < 1 or iv.device.type not in M.ALLOWED_DEVICE_TYPES:
+                continue
+            name = _ensure(gm, "xg_row_gather_wrap" if wrap else "xg_row_gather", lambda: M.RowGatherModule(wrap))
+            with gm.graph.inserting_before(node):
+                new = gm.graph.call_module(name, (table, idx))
+            _fill_meta(gm, new)
+            node.replace_all_uses_with(new)
+            gm.graph.erase_node(node)
+            changed = True
+        return changed
+
+
+class GatherIndexRepeatToExpand(Pattern):
+    """gather(x, dim, repeat(idx, reps)) -> gather(x, dim, expand(idx, ...)): the repeated index tensor is never
+    materialised (the reference's FusedGatherToCopy, targets/mlu/repeat_to_expand.py:25-56)."""
+
+    _opt_level = OptLevel.level1
+
+    def process(self, gm: fx.GraphModule) -> bool:
+        changed = False
+        for node in list(gm.graph.nodes):
+            if not _is(node, aten.gather.default) or len(node.args) < 3:
+                continue
+            rep = node.args[2]
+            if not (_is(rep, aten.repeat.default) and _only_user(rep, node)):
+                continue
+            src, reps = rep.args[0], list(rep.args[1])
+            sv = _val(src)
+            if not isinstance(sv, torch.Tensor) or len(reps) != sv.dim() or not _static(sv.shape):
+                continue
+            # a dim may be repeated only where the source has extent 1: that is exactly what expand can express
+            if any(r != 1 and sv.shape[i] != 1 for i, r in enumerate(reps)):
+                continue
+            with gm.graph.inserting_before(rep):
+                new = gm.graph.call_function(aten.expand.default, (src, [-1 if r == 1 else r for r in reps]))
+            _fill_meta(gm, new)
+            rep.replace_all_uses_with(new)
+            gm.graph.erase_node(rep)
+            changed = True
+        return changed
+
+
+# ---- where(mask, 0, slice-cat) --------------------------------------------------------------------------------------
+class FusedMaskedSliceCat(Pattern):
+    """cat([where(mask[B, 1], 0, src[:, s_i:e_i]) ...], -1) -> MaskedSliceCatModule: the row mask is applied while the
+    slices are copied (the computation of the reference's slice-where-cat kernel,
+    targets/mlu/triton_kernel/fused_slice_where_cat.py:12-73; its matcher, targets/mlu/fuse_slice_where_cat.py:147-216,
+    is switched off upstream). By the time target patterns run, the common passes have merged the per-slice ``where``
+    nodes into one (common/combine_pointwise_sink.py:21-95) and the slice fusions have replaced the slices, so the
+    graph arrives as
+
+        where(mask, 0, fuse_slice_cat(src, slices))                                       or, for equal-length slices,
+        cat(unbind(where(mask, 0, transpose(reshape(fuse_slice_cat(src, slices), [B, n, L]), 0, 1))), -1)
+
+    and both forms are matched here."""
+
+    _opt_level = OptLevel.level1
+    _pattern_group = PatternGroup.GROUP2
+
+    @staticmethod
+    def _mask_ok(gm, where, rows, dtype):
+        if not _is(where, aten.where.self) or len(where.args) != 3:
+            return False
+        mv = _val(where.args[0])
+        if not (isinstance(mv, torch.Tensor) and mv.dtype == torch.bool and tuple(mv.shape) == (rows, 1)):
+            return False
+        wv = _val(where)
+        return FusedEmbeddingStack._is_zero_const(gm, where.args[1]) and isinstance(wv, torch.Tensor) and wv.dtype == dtype
+
+    def _stacked_form(self, gm, node):
+        """node = cat / CatLastDimModule over getitem(unbind(where(mask, 0, transpose(reshape(slice_cat))))) in order."""
+        if _is(node, aten.cat.default):
+            parts = node.args[0]
+            dim = node.args[1] if len(node.args) > 1 else 0
+            if dim not in (-1, 1):
+                return None
+        elif _module_call(gm, node, M.CatLastDimModule) and len(node.args) == 1:
+            parts = node.args[0]
+        else:
+            return None
+        if len(parts) < 2 or not all(_is(q, operator.getitem) and _only_user(q, node) for q in parts):
+            return None
+        ub = parts[0].args[0]
+        if not (_is(ub, aten.unbind.int) and (len(ub.args) == 1 or ub.args[1] == 0) and len(ub.users) == len(parts)):
+            return None
+        if [q.args[0] for q in parts] != [ub] * len(parts) or [q.args[1] for q in parts] != list(range(len(parts))):
+            return None
+        where = ub.args[0]
+        if not (isinstance(where, fx.Node) and _only_user(where, ub)):
+            return None
+        tr = where.args[2] if _is(where, aten.where.self) and len(where.args) == 3 else None
+        if not (_is(tr, aten.transpose.int) and sorted(tr.args[1:3]) == [0, 1] and _only_user(tr, where)):
+            return None
+        rs = tr.args[0]
+        if not (_is(rs, *_RESHAPES) and _only_user(rs, tr)):
+            return None
+        sc = rs.args[0]
+        if not (_module_call(gm, sc, M.FuseSliceCatSameInputModule) and len(sc.args) == 2):
+            return None
+        ov, rv = _val(sc), _val(rs)
+        if not (isinstance(ov, torch.Tensor) and ov.dim() == 2 and isinstance(rv, torch.Tensor) and rv.dim() == 3):
+            return None
+        if rv.shape[0] != ov.shape[0] or rv.shape[1] != len(parts) or not self._mask_ok(gm, where, ov.shape[0], ov.dtype):
+            return None
+        # the slice-cat result may also feed the `size` node that the reshape takes its batch extent from
+        others = [u for u in sc.users if u is not rs]
+        if any(not (u.op == "call_method" and u.target == "size" and _only_user(u, rs)) for u in others):
+            return None
+        return where.args[0], sc, [ub, where, tr, rs] + others
+
+    def process(self, gm: fx.GraphModule) -> bool:
+        changed = False
+        for node in list(gm.graph.nodes):
+            mask = sc = None
+            dead = []
+            if _is(node, aten.where.self) and len(node.args) == 3:
+                cand = node.args[2]
+                if (_module_call(gm, cand, M.FuseSliceCatSameInputModule) and _only_user(cand, node) and len(cand.args) == 2
+                        and isinstance(_val(cand), torch.Tensor) and _val(cand).dim() == 2
+                        and self._mask_ok(gm, node, _val(cand).shape[0], _val(cand).dtype)):
+                    mask, sc = node.args[0], cand
+            else:
+                m = self._stacked_form(gm, node)
+                if m is not None:
+                    mask, sc, dead = m
+                    dead = list(node.args[0]) + dead
+            if sc is None:
+                continue
+            _ensure(gm, "xg_masked_slice_cat", M.MaskedSliceCatModule)
+            with gm.graph.inserting_before(node):
+                new = gm.graph.call_module("xg_masked_slice_cat", (sc.args[0], mask, sc.args[1]))
+            _fill_meta(gm, new)
+            node.replace_all_uses_with(new)
+            gm.graph.erase_node(node)
+            for d in dead + [sc]:
+                if len(d.users) == 0:
+                    gm.graph.erase_node(d)
             changed = True
         return changed
 
@@ -936,8 +1266,10 @@ class FusedDenseTower(Pattern):
         return changed
 
 
-ALL_PATTERNS = [FusedDenseTower, FusedComboDense, FusedSliceSumCat, FusedMulSumCat, FusedSumCat, FusedNativeLayerNorm, FusedSdpa, FusedRoPE, FusedEmbeddingStack, FusedSwiGLU, FusedDenseResidual,
-                FusedAddNorm, FusedCatLastDim, FusedDenseRope]
+ALL_PATTERNS = [FusedDenseTower, FusedComboDense, FusedSliceSumCat, FusedMulSumCat, FusedSumCat, FusedNativeLayerNorm,
+                FusedRmsNormLowered, FusedSdpa, FusedSdpaTensorScale, FusedRoPE, FusedEmbeddingStack, FusedSwiGLU,
+                FusedDenseResidual, FusedAddNorm, FusedCatLastDim, FusedDenseRope, FusedRowGather, GatherIndexRepeatToExpand,
+                FusedMaskedSliceCat]
 
 
 def get_all_patterns(config) -> dict:

@@ -118,6 +118,31 @@ class LlamaDecoderLayer(nn.Module):
         return x + self.down_proj(F.silu(self.gate_proj(h)) * self.up_proj(h))
 
 
+def llama_layer_stages(layer: LlamaDecoderLayer, x, cos, sin) -> dict:
+    """The eager layer, stage by stage: every intermediate tensor that a fused op of the rewritten graph consumes or
+    produces (same arithmetic as LlamaDecoderLayer.forward, in the layer's dtype). Lets a test feed each fused op
+    with exactly the inputs its eager counterpart saw, so that the comparison sees the rounding of that op alone."""
+    B, S, Hd = x.shape
+    H, D = layer.heads, layer.head_dim
+    st = {}
+    with torch.no_grad():
+        st["h1"] = layer.input_norm(x)
+        for name, proj in (("q", layer.q_proj), ("k", layer.k_proj), ("v", layer.v_proj)):
+            st[name + "_proj"] = proj(st["h1"]).view(B, S, H, D).transpose(1, 2)
+        st["q"] = st["q_proj"] * cos + rotate_half(st["q_proj"]) * sin
+        st["k"] = st["k_proj"] * cos + rotate_half(st["k_proj"]) * sin
+        st["attn"] = F.scaled_dot_product_attention(st["q"], st["k"], st["v_proj"], is_causal=True)
+        st["attn_rows"] = st["attn"].transpose(1, 2).reshape(B, S, Hd)
+        st["o"] = layer.o_proj(st["attn_rows"])
+        st["x1"] = x + st["o"]
+        st["h2"] = layer.post_norm(st["x1"])
+        st["gate"], st["up"] = layer.gate_proj(st["h2"]), layer.up_proj(st["h2"])
+        st["ffn_h"] = F.silu(st["gate"]) * st["up"]
+        st["down"] = layer.down_proj(st["ffn_h"])
+        st["out"] = st["x1"] + st["down"]
+    return st
+
+
 def make_llama_layer(seed=3, batch=8, seq=2048, hidden=4096, heads=32, ffn=11008, dtype=torch.bfloat16, device="cpu"):
     """Random-init weights ~N(0, 0.02) (norm weights 1), input ~N(0, 1), RoPE theta 10000."""
     g = torch.Generator().manual_seed(seed)
