@@ -13,8 +13,6 @@
 #include "common.cuh"
 #include "sm100_ptx.cuh"
 
-#include <cstdlib>
-#include <cstring>
 #include <type_traits>
 
 namespace xg {
@@ -156,32 +154,10 @@ __device__ __forceinline__ int flash_next(FlashCursor& c, const volatile FlashSt
     return 0;
 }
 
-// exp2 of two arguments on the FMA pipe (Cody-Waite: round to the nearest integer n with the 1.5 * 2^23 trick, a cubic
-// for 2^f on f in [-0.5, 0.5] with 7.7e-5 relative error - far inside the 16-bit probabilities' 2^-9 - and n added into
-// the exponent field). Arguments are clamped at -120 so that the exponent arithmetic cannot wrap; the result for
-// anything below is 2^-120, which is zero for every purpose here. Used for a fixed share of a block's exponentials so
-// that the special-function unit (16 results per clock per SM) is not the only pipe they queue on.
-__device__ __forceinline__ void exp2_poly2(float& p0, float& p1, float x0, float x1) {
-    constexpr float kMagic = 12582912.f;  // 1.5 * 2^23
-    x0 = fmaxf(x0, -120.f);
-    x1 = fmaxf(x1, -120.f);
-    float t0, t1, u0, u1, f0, f1;
-    ptx::add2(t0, t1, x0, x1, kMagic, kMagic);
-    ptx::add2(u0, u1, t0, t1, -kMagic, -kMagic);
-    ptx::fma2(f0, f1, u0, u1, -1.f, -1.f, x0, x1);
-    float q0, q1;
-    ptx::fma2(q0, q1, f0, f1, 0.05508868f, 0.05508868f, 0.24260405f, 0.24260405f);
-    ptx::fma2(q0, q1, q0, q1, f0, f1, 0.69327623f, 0.69327623f);
-    ptx::fma2(q0, q1, q0, q1, f0, f1, 0.99992895f, 0.99992895f);
-    // the low mantissa bits of t hold n (plus a constant whose shifted image is zero): add n to the exponent
-    p0 = __int_as_float(__float_as_int(q0) + (__float_as_int(t0) << 23));
-    p1 = __int_as_float(__float_as_int(q1) + (__float_as_int(t1) << 23));
-}
-
 // MASKED: the kernel carries the general masking code (additive mask, key count that is not a multiple of the block,
 // non-positive scale). The common case is compiled without it: the code of a tile boundary runs once per tile, its
 // instruction fetches miss the instruction caches, and a smaller kernel keeps more of it resident.
-template <typename T, int D, bool MASKED, int POLY = 0, bool EPI_WIDE = false>
+template <typename T, int D, bool MASKED>
 __global__ void __launch_bounds__(kFlashThreads, 2)
 flash_tc_kernel(const __grid_constant__ CUtensorMap tmq, const __grid_constant__ CUtensorMap tmk,
                 const __grid_constant__ CUtensorMap tmv, const FlashParams p) {
@@ -494,12 +470,8 @@ flash_tc_kernel(const __grid_constant__ CUtensorMap tmq, const __grid_constant__
                     float x0, x1, p0, p1;
                     ptx::fma2(x0, x1, sc[i], sc[i + 1], mul, mul, neg_m, neg_m);
                     const int pair = i >> 1;
-                    if (POLY > 0 && (pair & 7) < POLY) {  // compile-time choice per pair: POLY of every 8 pairs
-                        exp2_poly2(p0, p1, x0, x1);
-                    } else {
-                        p0 = ptx::ex2_approx(x0);
-                        p1 = ptx::ex2_approx(x1);
-                    }
+                    p0 = ptx::ex2_approx(x0);
+                    p1 = ptx::ex2_approx(x1);
                     ptx::add2(lp[2 * (pair & 3)], lp[2 * (pair & 3) + 1], lp[2 * (pair & 3)], lp[2 * (pair & 3) + 1], p0, p1);
                     pk[pair] = ptx::pack2<T>(p0, p1);
                 }
@@ -522,47 +494,6 @@ flash_tc_kernel(const __grid_constant__ CUtensorMap tmq, const __grid_constant__
             // full 128-byte row segments, four rows per store instruction.
             T* obase = reinterpret_cast<T*>(p.out) + (int64_t)t.b * p.o_sb + (int64_t)t.h * p.o_sh;
             const uint32_t slab = ptx::smem_u32(o_stage) + (uint32_t)(quad * 4096);
-            if (EPI_WIDE) {
-                // the whole output row is fetched from TMEM with one wait, then packed and sent out 64 columns at a time
-                uint32_t oo[D / 32][32];
-#pragma unroll
-                for (int c = 0; c < D / 32; ++c) {
-                    if (nblk > 0) {
-                        ptx::tmem_ld_32x32(tmem_base + lane_field + Cfg::O_COL + (uint32_t)(c * 32), oo[c]);
-                    } else {
-#pragma unroll
-                        for (int i = 0; i < 32; ++i) oo[c][i] = 0u;
-                    }
-                }
-                if (nblk > 0) ptx::tmem_ld_wait();
-#pragma unroll
-                for (int c = 0; c < D / 32; ++c) {
-#pragma unroll
-                    for (int t4 = 0; t4 < 4; ++t4) {
-                        uint32_t w[4];
-#pragma unroll
-                        for (int i = 0; i < 4; ++i) {
-                            float x0, x1;
-                            ptx::fma2(x0, x1, __uint_as_float(oo[c][t4 * 8 + 2 * i]), __uint_as_float(oo[c][t4 * 8 + 2 * i + 1]), inv_l, inv_l, 0.f, 0.f);
-                            w[i] = ptx::pack2<T>(x0, x1);
-                        }
-                        const int piece = (c & 1) * 4 + t4;
-                        ptx::st_shared_v4(slab + (uint32_t)(lane * 128 + ((piece ^ (lane & 7)) << 4)), make_uint4(w[0], w[1], w[2], w[3]));
-                    }
-                    if (c & 1) {
-                        __syncwarp();
-#pragma unroll
-                        for (int it = 0; it < 8; ++it) {
-                            const int r = it * 4 + (lane >> 3), piece = lane & 7;
-                            const uint4 val = ptx::ld_shared_v4(slab + (uint32_t)(r * 128 + ((piece ^ (r & 7)) << 4)));
-                            const int orow_i = q0 + quad * 32 + r;
-                            if (orow_i < p.Sq)
-                                *reinterpret_cast<uint4*>(obase + (int64_t)orow_i * p.o_ss + (c >> 1) * 64 + piece * 8) = val;
-                        }
-                        __syncwarp();
-                    }
-                }
-            } else
             // (not unrolled: this code runs once per tile, and its instruction fetches are what it costs)
 #pragma unroll 1
             for (int c = 0; c < D / 32; ++c) {
@@ -633,19 +564,6 @@ int launch_flash_tc(const SdpaParams& p, cudaStream_t st) {
     fp.causal = p.causal;
     const bool masked = p.mask != nullptr || p.Skv % FN != 0 || !(p.scale > 0.f);
     auto kern = masked ? flash_tc_kernel<T, D, true> : flash_tc_kernel<T, D, false>;
-    if (!masked && D == 128 && is_bf16) {  // EXPERIMENT: variants by XG_FLASH_VARIANT="poly,epi"
-        static const int var = []() { const char* e = getenv("XG_FLASH_VARIANT"); return e ? atoi(e) * 2 + (strchr(e, ',') ? atoi(strchr(e, ',') + 1) : 0) : 0; }();
-        switch (var) {
-            case 1: kern = flash_tc_kernel<T, D, false, 0, true>; break;
-            case 2: kern = flash_tc_kernel<T, D, false, 1, false>; break;
-            case 3: kern = flash_tc_kernel<T, D, false, 1, true>; break;
-            case 4: kern = flash_tc_kernel<T, D, false, 2, false>; break;
-            case 5: kern = flash_tc_kernel<T, D, false, 2, true>; break;
-            case 6: kern = flash_tc_kernel<T, D, false, 3, false>; break;
-            case 7: kern = flash_tc_kernel<T, D, false, 3, true>; break;
-            default: break;
-        }
-    }
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
     if (e != cudaSuccess) {
         cudaGetLastError();
