@@ -211,6 +211,18 @@ int xg_bgemm_bias_act(const void* A, const void* B, const void* bias, const void
                       int dtype, void* stream);
 
 /*
+ * Grouped form: out[e] = act( A[e] @ W[e] + bias[e] ) for `count` problems of one shape [M, N, K] whose operands lie
+ * wherever the caller has them: A, W, bias (nullable table, nullable entries) and out are host arrays of `count` device
+ * pointers; one launch per 12 entries walks (entry, tile) work units with each entry's own tensor maps, so nothing
+ * is stacked or copied. 16-bit dtypes; every A[e] / W[e] 16-byte aligned, lda / ldw multiples of 8 elements.
+ * Replaces: the grouped-GEMM form of targets/mlu/combo_matmul.py:87-113 (FusedCombineBmm.forward_groupgemm ->
+ * torch.ops.torch_mlu.grouped_gemm), emitted by FusedCombineMatMul (:116-232).
+ */
+int xg_gemm_group_bias_act(const void* const* A, const void* const* W, const void* const* bias, void* const* out,
+                           int64_t count, int64_t M, int64_t N, int64_t K, int64_t lda, int64_t ldw, int64_t ldc,
+                           int trans_b, int act, int dtype, void* stream);
+
+/*
  * Dual GEMM with SwiGLU epilogue: out = silu(A @ Wg^T) * (A @ Wu^T); Wg, Wu: [N, K] (Linear layout).
  * Replaces the mul(silu(mm), mm) sub-graph; elementwise part as targets/npu/fuse_silu_mul.py:21-69.
  */

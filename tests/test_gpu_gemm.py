@@ -350,25 +350,47 @@ def test_batch_dense(cuda_device, b, M, K, N, weight_trans, act, with_bias, dtyp
     assert_parity(got, want, f"batch_dense {b}x{M}x{K}x{N} {dtype}")
 
 
-def test_combo_dense(cuda_device):
-    """Six same-shape dense layers in one batched launch: separate tensors are stacked, slabs of one buffer are
-    used in place; both agree with the per-layer oracle."""
-    from xpu_graph_b200 import ops
+@pytest.mark.parametrize("T,M,K,N,weight_trans,with_bias", [(6, 96, 128, 200, True, True), (14, 130, 264, 72, True, False),
+                                                            (5, 256, 512, 384, False, True), (4, 64, 64, 1000, True, True)])
+def test_combo_dense(cuda_device, T, M, K, N, weight_trans, with_bias):
+    """T same-shape dense layers on separate tensors in one grouped launch (a pointer per layer: nothing is stacked or
+    copied; 14 layers need two launches of at most 12 entries), both weight layouts, against the per-layer oracle."""
+    from xpu_graph_b200 import lib
     from xpu_graph_b200.modules import ComboDenseModule
 
     g = torch.Generator().manual_seed(33)
-    T, M, K, N = 6, 96, 128, 200
     xs = [torch.randn(M, K, generator=g).to(torch.bfloat16) for _ in range(T)]
     ws = [(0.05 * torch.randn(N, K, generator=g)).to(torch.bfloat16) for _ in range(T)]
-    bs = [(0.05 * torch.randn(N, generator=g)).to(torch.bfloat16) for _ in range(T)]
-    want = torch.stack([ref_ops.dense(x, w, True, b, "relu") for x, w, b in zip(xs, ws, bs)])
-    got = ComboDenseModule()([x.to(cuda_device) for x in xs], [w.to(cuda_device) for w in ws], [b.to(cuda_device) for b in bs], "relu", True)
-    assert_parity(got, want, "combo_dense (stacked operands)")
+    if not weight_trans:
+        ws = [w.t().contiguous() for w in ws]
+    bs = [(0.05 * torch.randn(N, generator=g)).to(torch.bfloat16) if with_bias else None for _ in range(T)]
+    want = torch.stack([ref_ops.dense(x, w, weight_trans, b, "relu") for x, w, b in zip(xs, ws, bs)])
+    with LaunchCounter() as calls:
+        got = ComboDenseModule()([x.to(cuda_device) for x in xs], [w.to(cuda_device) for w in ws],
+                                 [b.to(cuda_device) if b is not None else None for b in bs], "relu", weight_trans)
+    torch.cuda.synchronize()
+    assert calls.names == ["xg_gemm_group_bias_act"], calls.names  # no stacking copy, no per-layer calls
+    assert lib.tc_status() == 0
+    assert_parity(got, want, f"combo_dense grouped T={T} {M}x{K}x{N}")
+
+
+def test_combo_dense_fallback_to_the_batched_form(cuda_device):
+    """fp32 layers do not qualify for the grouped kernel: separate tensors are stacked, slabs of one buffer are used in
+    place, and the batched entry point runs them."""
+    from xpu_graph_b200 import ops
+    from xpu_graph_b200.modules import ComboDenseModule
+
+    g = torch.Generator().manual_seed(34)
+    T, M, K, N = 4, 40, 64, 48
+    xs = [torch.randn(M, K, generator=g) for _ in range(T)]
+    ws = [0.05 * torch.randn(N, K, generator=g) for _ in range(T)]
+    bs = [0.05 * torch.randn(N, generator=g) for _ in range(T)]
+    want = torch.stack([ref_ops.dense(x.double(), w.double(), True, b.double(), "relu").float() for x, w, b in zip(xs, ws, bs)])
     xcat = torch.stack(xs).to(cuda_device)
     wcat = torch.stack(ws).to(cuda_device)
     assert ops._stack_or_view(list(xcat.unbind(0))).data_ptr() == xcat.data_ptr()  # no copy for slabs of one buffer
-    got2 = ComboDenseModule()(list(xcat.unbind(0)), list(wcat.unbind(0)), [b.to(cuda_device) for b in bs], "relu", True)
-    assert_parity(got2, want, "combo_dense (operands in place)")
+    got = ComboDenseModule()(list(xcat.unbind(0)), list(wcat.unbind(0)), [b.to(cuda_device) for b in bs], "relu", True)
+    assert_parity(got, want, "combo_dense fp32 (batched form)")
 
 
 @pytest.mark.parametrize("act", ["gelu", "silu"])

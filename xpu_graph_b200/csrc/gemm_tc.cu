@@ -896,6 +896,248 @@ int launch_gemm_tc(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorM
     return XG_OK;
 }
 
+
+// ---------------------------------------------------------------------------------------------------------
+// Grouped dense layers: `count` problems of one shape whose operands live wherever the caller has them
+// (a pointer per entry, no stacked copy). The persistent single-CTA kernel above, with the entry's tensor maps and
+// pointers taken from a table in the kernel's parameter space instead of a third tensor-map coordinate.
+// ---------------------------------------------------------------------------------------------------------
+constexpr int kGroupMax = 12;  // entries per launch: 12 x (2 tensor maps + 2 pointers) = 3264 bytes of parameters
+struct GroupTable {
+    CUtensorMap a[kGroupMax];
+    CUtensorMap w[kGroupMax];
+    void* out[kGroupMax];
+    const void* bias[kGroupMax];
+};
+
+template <typename T, int BN, bool B_MN>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+gemm_tc_group_kernel(const __grid_constant__ GroupTable tab, const GemmParams p, const int count) {
+    using Cfg = GemmCfg<BN>;
+    constexpr int STAGES = Cfg::STAGES;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint8_t* smem_a = smem;
+    uint8_t* smem_b = smem + STAGES * Cfg::A_BYTES;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * Cfg::STAGE_BYTES);
+    uint64_t* full_bar = bars;
+    uint64_t* empty_bar = bars + STAGES;
+    uint64_t* tmem_full = bars + 2 * STAGES;
+    uint64_t* tmem_empty = bars + 2 * STAGES + 2;
+    uint64_t* drain_bar = bars + 2 * STAGES + 4;
+    uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 5);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_base_slot + 1);
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            ptx::mbar_init(&full_bar[s], 1);
+            ptx::mbar_init(&empty_bar[s], 1);
+        }
+        for (int a = 0; a < 2; ++a) {
+            ptx::mbar_init(&tmem_full[a], 1);
+            ptx::mbar_init(&tmem_empty[a], 4);
+        }
+        ptx::mbar_init(drain_bar, 1);
+        *abort_flag = 0;
+        ptx::fence_mbar_init();
+        ptx::fence_proxy_async();
+    }
+    if (warp == 1) ptx::tmem_alloc(tmem_base_slot, Cfg::TMEM_COLS);
+    ptx::tc_fence_before();
+    __syncthreads();
+    ptx::tc_fence_after();
+    const uint32_t tmem_base = *tmem_base_slot;
+
+    const int tiles_per_entry = p.num_m_blocks * p.num_n_blocks;
+    const int num_tiles = tiles_per_entry * count;  // work units: (entry, tile)
+    const int nkb = p.num_k_blocks;
+
+    if (warp == 0) {
+        if (ptx::elect_one()) {
+            int stage = 0;
+            uint32_t phase = 0, armed = 0, armed_phase = 0;
+            bool ok = true;
+            for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+                const int entry = t / tiles_per_entry;
+                int mb, nb;
+                tile_coords(t - entry * tiles_per_entry, p.num_m_blocks, p.num_n_blocks, mb, nb);
+                const CUtensorMap* ta = &tab.a[entry];
+                const CUtensorMap* tw = &tab.w[entry];
+                for (int kb = 0; kb < nkb; ++kb) {
+                    if (!ptx::mbar_wait_bounded(&empty_bar[stage], phase ^ 1u, abort_flag)) { ok = false; break; }
+                    ptx::mbar_arrive_expect_tx(&full_bar[stage], Cfg::STAGE_BYTES);
+                    ptx::tma_load_2d(smem_a + stage * Cfg::A_BYTES, ta, &full_bar[stage], kb * BK, mb * BM);
+                    if (B_MN) {
+#pragma unroll
+                        for (int j = 0; j < BN / 64; ++j)
+                            ptx::tma_load_2d(smem_b + stage * Cfg::B_BYTES + j * (BK * 128), tw, &full_bar[stage], nb * BN + j * 64, kb * BK);
+                    } else {
+                        ptx::tma_load_2d(smem_b + stage * Cfg::B_BYTES, tw, &full_bar[stage], kb * BK, nb * BN);
+                    }
+                    armed |= 1u << stage;
+                    armed_phase = (armed_phase & ~(1u << stage)) | (phase << stage);
+                    if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+                }
+            }
+            if (!ok) {
+                atomicOr(&g_tc_status[0], 1u);
+                for (int s = 0; s < STAGES; ++s) {
+                    if (armed & (1u << s)) {
+                        const uint64_t t0 = ptx::globaltimer_ns();
+                        while (!ptx::mbar_try_wait(&full_bar[s], (armed_phase >> s) & 1u)) {
+                            if (ptx::globaltimer_ns() - t0 > ptx::kWaitLimitNs) break;
+                        }
+                    }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (ptx::elect_one()) {
+            constexpr uint32_t idesc = ptx::make_idesc_f16(std::is_same<T, __nv_bfloat16>::value ? 1 : 0, BM, BN, B_MN ? 1 : 0);
+            int stage = 0, acc = 0;
+            uint32_t phase = 0, acc_phase = 0;
+            bool ok = true;
+            for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+                if (!ptx::mbar_wait_bounded(&tmem_empty[acc], acc_phase ^ 1u, abort_flag)) { ok = false; break; }
+                ptx::tc_fence_after();
+                const uint32_t tmem_d = tmem_base + (uint32_t)(acc * BN);
+                for (int kb = 0; kb < nkb; ++kb) {
+                    if (!ptx::mbar_wait_bounded(&full_bar[stage], phase, abort_flag)) { ok = false; break; }
+                    ptx::tc_fence_after();
+                    const uint32_t a_addr = ptx::smem_u32(smem_a + stage * Cfg::A_BYTES);
+                    const uint32_t b_addr = ptx::smem_u32(smem_b + stage * Cfg::B_BYTES);
+                    const uint64_t da = ptx::make_kmajor_sw128_desc(a_addr);
+                    const uint64_t db = B_MN ? ptx::make_mnmajor_sw128_desc(b_addr, BK * 128) : ptx::make_kmajor_sw128_desc(b_addr);
+#pragma unroll
+                    for (int k = 0; k < BK / UMMA_K; ++k)
+                        ptx::mma_f16_ss(tmem_d, da + (uint64_t)(k * 2), db + (uint64_t)(B_MN ? k * 128 : k * 2), idesc, (kb | k) != 0 ? 1u : 0u);
+                    ptx::tc_commit(&empty_bar[stage]);
+                    if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+                }
+                if (!ok) break;
+                ptx::tc_commit(&tmem_full[acc]);
+                if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
+            }
+            if (!ok) {
+                atomicOr(&g_tc_status[0], 2u);
+                ptx::tc_commit(drain_bar);
+                const uint64_t t0 = ptx::globaltimer_ns();
+                while (!ptx::mbar_try_wait(drain_bar, 0)) {
+                    if (ptx::globaltimer_ns() - t0 > ptx::kWaitLimitNs) break;
+                }
+            }
+        }
+    } else {
+        const int quad = warp & 3;
+        int acc = 0;
+        uint32_t acc_phase = 0;
+        bool ok = true;
+        for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+            const int entry = t / tiles_per_entry;
+            int mb, nb;
+            tile_coords(t - entry * tiles_per_entry, p.num_m_blocks, p.num_n_blocks, mb, nb);
+            if (!__all_sync(0xffffffffu, ptx::mbar_wait_bounded(&tmem_full[acc], acc_phase, abort_flag))) { ok = false; break; }
+            ptx::tc_fence_after();
+            GemmParams pe = p;  // this entry's pointers; everything else is shared by the group
+            pe.out = tab.out[entry];
+            pe.bias = tab.bias[entry];
+            const int64_t row = (int64_t)mb * BM + quad * 32 + lane;
+            epilogue_tile<T, BN, false>(pe, tmem_base, acc, quad, row, row < p.M, nb, 0, 0);
+            ptx::tc_fence_before();
+            __syncwarp();
+            if (lane == 0) ptx::mbar_arrive(&tmem_empty[acc]);
+            if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
+        }
+        if (!ok && lane == 0) atomicOr(&g_tc_status[0], 4u);
+    }
+    ptx::tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        ptx::tc_fence_after();
+        ptx::tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
+    }
+}
+
+template <typename T, int BN, bool B_MN>
+int launch_gemm_group(const GroupTable& tab, const GemmParams& p, int count, cudaStream_t st) {
+    using Cfg = GemmCfg<BN>;
+    auto kern = gemm_tc_group_kernel<T, BN, B_MN>;
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
+    if (e != cudaSuccess) {
+        cudaGetLastError();
+        return fail(XG_ERR_LAUNCH, "xg_gemm_group_bias_act: cannot reserve %d bytes of shared memory: %s", Cfg::SMEM_BYTES,
+                    cudaGetErrorString(e));
+    }
+    const int64_t tiles = (int64_t)p.num_m_blocks * p.num_n_blocks * count;
+    const int grid = (int)(tiles < num_sms() ? tiles : num_sms());
+    kern<<<grid, kGemmThreads, Cfg::SMEM_BYTES, st>>>(tab, p, count);
+    return check_launch("xg_gemm_group_bias_act");
+}
+
+template <typename T>
+int gemm_group_dispatch(const void* const* A, const void* const* W, const void* const* bias, void* const* out, int64_t count,
+                        int64_t M, int64_t N, int64_t K, int64_t lda, int64_t ldw, int64_t ldc, int trans_b, int act,
+                        cudaStream_t st) {
+    constexpr bool is_bf16 = std::is_same<T, __nv_bfloat16>::value;
+    const int64_t mblk = (M + BM - 1) / BM;
+    int bn = 256;
+    if (count * mblk * ((N + 255) / 256) < num_sms()) bn = 128;
+    if (bn == 128 && count * mblk * ((N + 127) / 128) < num_sms()) bn = 64;
+    GemmParams p;
+    p.out = nullptr;
+    p.bias = nullptr;
+    p.residual = nullptr;
+    p.M = M; p.N = N; p.K = K; p.ldc = ldc; p.ldr = 0;
+    p.act = act;
+    p.mode = kModePlain;
+    p.split.partial = nullptr;
+    p.num_m_blocks = (int)mblk;
+    p.num_n_blocks = (int)((N + bn - 1) / bn);
+    p.num_k_blocks = (int)((K + BK - 1) / BK);
+    p.splits = 1;
+    for (int64_t first = 0; first < count; first += kGroupMax) {
+        const int n = (int)((count - first) < kGroupMax ? (count - first) : kGroupMax);
+        GroupTable tab;
+        bool vec = (ldc % 8 == 0), bias_vec = true;
+        for (int e = 0; e < n; ++e) {
+            const void* a = A[first + e];
+            const void* w = W[first + e];
+            void* o = out[first + e];
+            if (!a || !w || !o) return fail(XG_ERR_INVALID_ARG, "xg_gemm_group_bias_act: null pointer in entry %lld", (long long)(first + e));
+            if (!aligned16(a) || !aligned16(w))
+                return fail(XG_ERR_UNSUPPORTED, "xg_gemm_group_bias_act: entry %lld: A/W must be 16-byte aligned", (long long)(first + e));
+            const bool w_ok = trans_b ? make_tmap_2d_16bit(&tab.w[e], w, (uint64_t)N, (uint64_t)K, (uint64_t)ldw, (uint32_t)bn, BK, is_bf16)
+                                      : make_tmap_2d_16bit(&tab.w[e], w, (uint64_t)K, (uint64_t)N, (uint64_t)ldw, BK, 64, is_bf16);
+            if (!w_ok || !make_tmap_2d_16bit(&tab.a[e], a, (uint64_t)M, (uint64_t)K, (uint64_t)lda, BM, BK, is_bf16))
+                return fail(XG_ERR_UNSUPPORTED, "xg_gemm_group_bias_act: tensor-map encoding failed for entry %lld", (long long)(first + e));
+            tab.out[e] = o;
+            tab.bias[e] = bias ? bias[first + e] : nullptr;
+            vec = vec && aligned16(o);
+            bias_vec = bias_vec && (!tab.bias[e] || aligned16(tab.bias[e]));
+        }
+        for (int e = n; e < kGroupMax; ++e) {  // unused slots: valid descriptors, never dereferenced
+            tab.a[e] = tab.a[0];
+            tab.w[e] = tab.w[0];
+            tab.out[e] = nullptr;
+            tab.bias[e] = nullptr;
+        }
+        p.vec_ok = vec ? 1 : 0;
+        p.bias_vec_ok = bias_vec ? 1 : 0;
+        int rc;
+        if (!trans_b) {
+            rc = bn == 256 ? launch_gemm_group<T, 256, true>(tab, p, n, st)
+                           : (bn == 128 ? launch_gemm_group<T, 128, true>(tab, p, n, st) : launch_gemm_group<T, 64, true>(tab, p, n, st));
+        } else {
+            rc = bn == 256 ? launch_gemm_group<T, 256, false>(tab, p, n, st)
+                           : (bn == 128 ? launch_gemm_group<T, 128, false>(tab, p, n, st) : launch_gemm_group<T, 64, false>(tab, p, n, st));
+        }
+        if (rc != XG_OK) return rc;
+    }
+    return XG_OK;
+}
+
 }  // namespace
 
 // CTA pairs pay off once there are enough 256-row tiles to keep every pair busy. XG_GEMM_PAIRS=0/1 overrides.
@@ -1150,6 +1392,20 @@ int bgemm_tc_entry(const void* A, const void* B, const void* bias, const void* r
     if (dtype == XG_BF16)
         return bgemm_tc_dispatch<__nv_bfloat16>(A, B, bias, residual, out, batch, M, N, K, lda, ldb, ldc, ldr, sa, sb, sbias, sr, sc, trans_b, act, st);
     return bgemm_tc_dispatch<__half>(A, B, bias, residual, out, batch, M, N, K, lda, ldb, ldc, ldr, sa, sb, sbias, sr, sc, trans_b, act, st);
+}
+
+// Grouped dense layers (one shape, a pointer per entry): see gemm_tc_group_kernel.
+int gemm_group_entry(const void* const* A, const void* const* W, const void* const* bias, void* const* out, int64_t count,
+                     int64_t M, int64_t N, int64_t K, int64_t lda, int64_t ldw, int64_t ldc, int trans_b, int act, int dtype,
+                     cudaStream_t st) {
+    if (lda % 8 != 0 || ldw % 8 != 0)
+        return fail(XG_ERR_UNSUPPORTED, "xg_gemm_group_bias_act: row strides must be multiples of 8 elements");
+    if (M > (int64_t)BM * 0x7fffff || N > (int64_t)64 * 0x7fffff || K > 0x7fffffff ||
+        count * ((M + BM - 1) / BM) * ((N + 63) / 64) > 0x7fffffffLL)
+        return fail(XG_ERR_TOO_LARGE, "xg_gemm_group_bias_act: extent too large");
+    if (dtype == XG_BF16)
+        return gemm_group_dispatch<__nv_bfloat16>(A, W, bias, out, count, M, N, K, lda, ldw, ldc, trans_b, act, st);
+    return gemm_group_dispatch<__half>(A, W, bias, out, count, M, N, K, lda, ldw, ldc, trans_b, act, st);
 }
 
 // ---- fp32 problems on the bf16 tensor cores ------------------------------------------------------------

@@ -55,6 +55,8 @@ SIGNATURES = {
     "xg_bgemm_bias_act": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64,
                                   c_int64, c_int64, c_int64, c_int64, c_int64, c_int64, c_int64, c_int64, c_int64,
                                   c_int, c_int, c_int, c_void_p]),
+    "xg_gemm_group_bias_act": (c_int, [_VPP, _VPP, _VPP, _VPP, c_int64, c_int64, c_int64, c_int64, c_int64, c_int64, c_int64,
+                                       c_int, c_int, c_int, c_void_p]),
     "xg_gemm_swiglu": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64, c_int64,
                                c_int64, c_int, c_void_p]),
     "xg_gemm_rope": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64, c_int64,

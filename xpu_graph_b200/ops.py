@@ -407,11 +407,15 @@ def _(x, weight, weight_trans, bias, residual, act):
 @torch.library.custom_op(f"{NS}::combo_dense", mutates_args=(), device_types="cuda")
 def combo_dense(inputs: List[torch.Tensor], weights: List[torch.Tensor], weight_trans: bool,
                 biases: List[Optional[torch.Tensor]], act: str) -> torch.Tensor:
-    """T same-shape dense layers act(x_t @ W_t + b_t) as one batched launch; returns the stacked [T, M, N] result.
-    Operands that are not already consecutive slabs of one buffer are stacked first."""
+    """T same-shape dense layers act(x_t @ W_t + b_t) in one launch; returns the stacked [T, M, N] result. 16-bit
+    operands are used in place through the grouped kernel (a pointer per layer, no stacking copy); anything else goes
+    through the batched form, for which operands that are not consecutive slabs of one buffer are stacked first."""
     T = len(inputs)
     if T == 0 or len(weights) != T or len(biases) != T:
         raise ValueError("xg_sm100::combo_dense: one input, weight and bias entry per layer")
+    grouped = _combo_dense_grouped(inputs, weights, weight_trans, biases, act)
+    if grouped is not None:
+        return grouped
     x = _stack_or_view(inputs)
     w = _stack_or_view(weights)
     has_bias = biases[0] is not None
@@ -419,6 +423,36 @@ def combo_dense(inputs: List[torch.Tensor], weights: List[torch.Tensor], weight_
         raise ValueError("xg_sm100::combo_dense: either every layer has a bias or none")
     b = torch.stack([bi.reshape(1, -1) for bi in biases]) if has_bias else None  # [T, 1, N]
     return batch_dense(x, w, weight_trans, b, None, act)
+
+
+def _combo_dense_grouped(inputs, weights, weight_trans: bool, biases, act: str) -> Optional[torch.Tensor]:
+    """The grouped launch: every layer's operands are used where they are (a pointer per entry), the results land side
+    by side in one [T, M, N] tensor. Returns None when the operands do not qualify (fp32, shapes that differ, rows a
+    tensor map cannot address), and the caller falls back to the stacked batched form."""
+    x0, w0 = inputs[0], weights[0]
+    if x0.dtype not in (torch.bfloat16, torch.float16) or x0.dim() != 2 or w0.dim() != 2:
+        return None
+    xs, ws = [_mat(t) for t in inputs], [_mat(t) for t in weights]
+    M, K = xs[0].shape
+    N = ws[0].shape[0] if weight_trans else ws[0].shape[1]
+    lda, ldw = _row_stride(xs[0]), _row_stride(ws[0])
+    for x, w in zip(xs, ws):
+        if (x.shape != xs[0].shape or w.shape != ws[0].shape or x.dtype != x0.dtype or w.dtype != x0.dtype
+                or _row_stride(x) != lda or _row_stride(w) != ldw or x.data_ptr() % 16 or w.data_ptr() % 16):
+            return None
+    if (ws[0].shape[1] if weight_trans else ws[0].shape[0]) != K or lda % 8 or ldw % 8:
+        return None
+    bs = [None if b is None else b.reshape(-1).to(x0.dtype).contiguous() for b in biases]
+    if any(b is not None and b.numel() != N for b in bs):
+        return None
+    out = torch.empty((len(xs), M, N), dtype=x0.dtype, device=x0.device)
+    step = M * N * out.element_size()
+    rc = _lib.load().xg_gemm_group_bias_act(
+        _lib.ptr_array([x.data_ptr() for x in xs]), _lib.ptr_array([w.data_ptr() for w in ws]),
+        _lib.ptr_array([0 if b is None else b.data_ptr() for b in bs]), _lib.ptr_array([out.data_ptr() + i * step for i in range(len(xs))]),
+        len(xs), M, N, K, lda, ldw, N, 1 if weight_trans else 0, _lib.ACT_CODES[act], _code(x0.dtype), _stream(x0))
+    _lib.check(rc, "xg_gemm_group_bias_act")
+    return out
 
 
 def _stack_or_view(ts: Sequence[torch.Tensor]) -> torch.Tensor:
