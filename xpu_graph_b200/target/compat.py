@@ -22,10 +22,8 @@ def _find_source() -> str | None:
         return env
     here = os.path.dirname(os.path.abspath(__file__))
     repo = os.path.dirname(os.path.dirname(here))
-    for cand in (os.path.join(repo, "baseline", "_ref"), os.path.join(os.path.dirname(repo), "reference", "src")):
-        if os.path.isdir(os.path.join(cand, "xpu_graph")):
-            return cand
-    return None
+    cand = os.path.join(repo, "baseline", "_ref")  # an offline install next to this package
+    return cand if os.path.isdir(os.path.join(cand, "xpu_graph")) else None
 
 
 def import_xpu_graph():
