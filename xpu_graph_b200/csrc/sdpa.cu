@@ -423,59 +423,77 @@ flash_tc_kernel(const __grid_constant__ CUtensorMap tmq, const __grid_constant__
                     }
                     mul = 1.f;
                 }
-                // 8 independent chains of 3-input maxima instead of one 64-deep dependency chain
-                float mxp[8];
+                // The first block of a tile needs its maximum before any probability can be formed. Later blocks form
+                // their probabilities against the running maximum at once, while the block's own maximum is reduced
+                // alongside (the two instruction streams are independent); only when some row's maximum grew beyond the
+                // threshold - rare after a tile's first blocks - is O rescaled and the block done again.
+                if (j == 0) {
+                    // 8 independent chains of 3-input maxima instead of one 64-deep dependency chain
+                    float mxp[8];
 #pragma unroll
-                for (int i = 0; i < 8; ++i) mxp[i] = ptx::fmax3(sc[i], sc[8 + i], sc[16 + i]);
+                    for (int i = 0; i < 8; ++i) mxp[i] = ptx::fmax3(sc[i], sc[8 + i], sc[16 + i]);
 #pragma unroll
-                for (int i = 24; i < FN; i += 16)
+                    for (int i = 24; i < FN; i += 16)
 #pragma unroll
-                    for (int c = 0; c < 8; ++c) mxp[c] = ptx::fmax3(mxp[c], sc[i + c], sc[i + 8 + c]);
-                // (i = 24: 24..39, i = 40: 40..55) leaves 56..63
+                        for (int c = 0; c < 8; ++c) mxp[c] = ptx::fmax3(mxp[c], sc[i + c], sc[i + 8 + c]);
+                    // (i = 24: 24..39, i = 40: 40..55) leaves 56..63
 #pragma unroll
-                for (int c = 0; c < 8; ++c) mxp[c] = fmaxf(mxp[c], sc[56 + c]);
-                const float mx = ptx::fmax3(ptx::fmax3(mxp[0], mxp[1], mxp[2]), ptx::fmax3(mxp[3], mxp[4], mxp[5]),
-                                            fmaxf(mxp[6], mxp[7])) * mul;
-                const float m_new = fmaxf(m_run, mx);
-                const bool grow = m_new > m_run + kRescaleThreshold;  // also true for the first finite maximum
-                const bool warp_rescale = __any_sync(0xffffffffu, grow);
-                if (warp_rescale) {
-                    const float m_to = (m_new == -INFINITY) ? 0.f : m_new;
-                    const float alpha = ptx::ex2_approx(m_run - m_to);  // 0 when there was no finite maximum yet
-                    if (j > 0) {
-                        // O must be quiescent: P V of the previous block has completed. s_full of this block
-                        // already implies the P V two blocks back, so the barrier is at most one phase behind.
-                        if (!__all_sync(0xffffffffu, ptx::mbar_wait_bounded(pv_full, (n - 1) & 1u, abort_flag))) { ok = false; break; }
-                        ptx::tc_fence_after();
-#pragma unroll 1
-                        for (int c = 0; c < D / 32; ++c) {  // rare path: kept small
-                            uint32_t o[32];
-                            const uint32_t o_taddr = tmem_base + lane_field + Cfg::O_COL + (uint32_t)(c * 32);
-                            ptx::tmem_ld_32x32(o_taddr, o);
-                            ptx::tmem_ld_wait();
-#pragma unroll
-                            for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
-                            ptx::tmem_st_32x32(o_taddr, o);
-                        }
-                    }
-                    l_run *= alpha;
-                    m_run = m_new;
+                    for (int c = 0; c < 8; ++c) mxp[c] = fmaxf(mxp[c], sc[56 + c]);
+                    m_run = ptx::fmax3(ptx::fmax3(mxp[0], mxp[1], mxp[2]), ptx::fmax3(mxp[3], mxp[4], mxp[5]),
+                                       fmaxf(mxp[6], mxp[7])) * mul;
                 }
-                const float neg_m = (m_run == -INFINITY) ? 0.f : -m_run;
                 // probabilities -> packed 16-bit pairs over columns [0, 32) of this block's score buffer
                 uint32_t pk[32];
-                float lp[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};  // independent partial row sums (4 pairs)
+#pragma unroll 1
+                for (int attempt = 0; attempt < 2; ++attempt) {
+                    const float neg_m = (m_run == -INFINITY) ? 0.f : -m_run;
+                    float lp[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};  // independent partial row sums (4 pairs)
+                    float mxp[8];
 #pragma unroll
-                for (int i = 0; i < FN; i += 2) {
-                    float x0, x1, p0, p1;
-                    ptx::fma2(x0, x1, sc[i], sc[i + 1], mul, mul, neg_m, neg_m);
-                    const int pair = i >> 1;
-                    p0 = ptx::ex2_approx(x0);
-                    p1 = ptx::ex2_approx(x1);
-                    ptx::add2(lp[2 * (pair & 3)], lp[2 * (pair & 3) + 1], lp[2 * (pair & 3)], lp[2 * (pair & 3) + 1], p0, p1);
-                    pk[pair] = ptx::pack2<T>(p0, p1);
+                    for (int i = 0; i < 8; ++i) mxp[i] = -INFINITY;
+#pragma unroll
+                    for (int i = 0; i < FN; i += 2) {
+                        float x0, x1, p0, p1;
+                        ptx::fma2(x0, x1, sc[i], sc[i + 1], mul, mul, neg_m, neg_m);
+                        const int pair = i >> 1;
+                        p0 = ptx::ex2_approx(x0);
+                        p1 = ptx::ex2_approx(x1);
+                        mxp[pair & 7] = ptx::fmax3(mxp[pair & 7], sc[i], sc[i + 1]);
+                        ptx::add2(lp[2 * (pair & 3)], lp[2 * (pair & 3) + 1], lp[2 * (pair & 3)], lp[2 * (pair & 3) + 1], p0, p1);
+                        pk[pair] = ptx::pack2<T>(p0, p1);
+                    }
+                    const float l_blk = ((lp[0] + lp[1]) + (lp[2] + lp[3])) + ((lp[4] + lp[5]) + (lp[6] + lp[7]));
+                    if (attempt == 0 && j > 0) {  // uniform over the CTA
+                        const float mx = ptx::fmax3(ptx::fmax3(mxp[0], mxp[1], mxp[2]), ptx::fmax3(mxp[3], mxp[4], mxp[5]),
+                                                    fmaxf(mxp[6], mxp[7])) * mul;
+                        const float m_new = fmaxf(m_run, mx);
+                        const bool grow = m_new > m_run + kRescaleThreshold;  // also true for the first finite maximum
+                        if (__any_sync(0xffffffffu, grow)) {
+                            const float m_to = (m_new == -INFINITY) ? 0.f : m_new;
+                            const float alpha = ptx::ex2_approx(m_run - m_to);  // 0 when there was no finite maximum yet
+                            // O must be quiescent: P V of the previous block has completed. s_full of this block
+                            // already implies the P V two blocks back, so the barrier is at most one phase behind.
+                            if (!__all_sync(0xffffffffu, ptx::mbar_wait_bounded(pv_full, (n - 1) & 1u, abort_flag))) { ok = false; break; }
+                            ptx::tc_fence_after();
+#pragma unroll 1
+                            for (int c = 0; c < D / 32; ++c) {  // rare path: kept small
+                                uint32_t o[32];
+                                const uint32_t o_taddr = tmem_base + lane_field + Cfg::O_COL + (uint32_t)(c * 32);
+                                ptx::tmem_ld_32x32(o_taddr, o);
+                                ptx::tmem_ld_wait();
+#pragma unroll
+                                for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+                                ptx::tmem_st_32x32(o_taddr, o);
+                            }
+                            l_run *= alpha;
+                            m_run = m_new;
+                            continue;  // once more, against the new maximum
+                        }
+                    }
+                    l_run += l_blk;
+                    break;
                 }
-                l_run += ((lp[0] + lp[1]) + (lp[2] + lp[3])) + ((lp[4] + lp[5]) + (lp[6] + lp[7]));
+                if (!ok) break;
                 ptx::tmem_st_32x32(s_taddr, pk);
                 ptx::tmem_st_wait();  // P (and a rescaled O) are in TMEM before the P V is released
                 ptx::tc_fence_before();
