@@ -44,6 +44,33 @@ def test_flash_tc(cuda_device, B, H, S, D, causal, dtype):
     assert max_abs < 2e-2, f"max abs error vs fp32 math {max_abs}"
 
 
+@pytest.mark.parametrize("causal", [False, True])
+@pytest.mark.parametrize("D", [64, 128])
+@pytest.mark.parametrize("shape", ["ramp", "jump", "masked_tail"])
+def test_flash_tc_growing_row_maximum(cuda_device, shape, D, causal):
+    """Scores whose row maximum grows by far more than the lazy-rescale threshold in later key blocks: the kernel
+    forms a block's probabilities against the running maximum first and must rescale O and redo the block."""
+    B, H, S = 1, 2, 640
+    q, k, v = _qkv(B, H, S, S, D, torch.bfloat16, 33)
+    q = (q.float().abs() + 0.5).to(torch.bfloat16)  # positive queries: a key's scale sets the sign and size of its scores
+    mask = None
+    if shape == "ramp":      # every 64-key block is about 25 (natural units, after scaling) above the previous one
+        gain = torch.linspace(0.0, 8.0, S).view(1, 1, S, 1)
+        k = (k.float().abs() * gain).to(torch.bfloat16)
+    elif shape == "jump":    # small scores, then one block far above everything before it
+        k = (k.float() * 0.05).to(torch.bfloat16)
+        k[:, :, 400:420] = (k[:, :, 400:420].float().abs() * 400.0 + 4.0).to(torch.bfloat16)
+    else:                    # the general-mask variant of the kernel: additive mask, large scores late
+        gain = torch.linspace(0.0, 6.0, S).view(1, 1, S, 1)
+        k = (k.float().abs() * gain).to(torch.bfloat16)
+        g = torch.Generator().manual_seed(34)
+        mask = (torch.randn(B, 1, S, S, generator=g) * 2.0).to(torch.bfloat16)
+    got = _run(cuda_device, q, k, v, mask, None, causal)
+    want = ref_ops.sdpa(q, k, v, mask, None, causal)
+    assert torch.isfinite(got.float()).all()
+    assert_parity(got, want, f"sdpa growing maximum ({shape}) D={D} causal={causal}")
+
+
 def test_flash_tc_mask_and_cross_lengths(cuda_device):
     q, k, v = _qkv(2, 2, 130, 200, 64, torch.bfloat16, 31)
     g = torch.Generator().manual_seed(32)
