@@ -176,3 +176,37 @@ def test_interceptor_on_gpu(cuda_device, caplog):
         lg.propagate = old
     assert caplog.text.count("Monitored inference") >= 2
     assert "diverges" not in caplog.text, caplog.text[-2000:]
+
+
+def test_reference_front_end_on_gpu(cuda_device):
+    """torch.compile(model, backend=XpuGraph(config)) - the reference's own entry point (compiler.py:196-237, graph
+    dispatch by fx_utils.dispatch_graph) - with this target: the same kernels run (same launch sequence as through
+    target.backend()) and the results are bit-equal."""
+    from tests.helpers import LaunchCounter
+    from xpu_graph_b200 import lib, target
+    from xpu_graph_b200.workloads import make_llama_layer, make_recsys
+
+    layer, (x, cos, sin) = make_llama_layer(seed=3, batch=2, seq=320, hidden=512, heads=4, ffn=1376)
+    layer = layer.to(cuda_device)
+    cases = [(layer, (x.to(cuda_device), cos.to(cuda_device), sin.to(cuda_device)))]
+    model, inputs = make_recsys(seed=5, batch=512)
+    cases.append((model.to(cuda_device), tuple(t.to(cuda_device) for t in inputs)))
+    for model, inputs in cases:
+        through_backend, want, _, _ = _compile_run(model, inputs)
+        with LaunchCounter() as ours:
+            with torch.no_grad():
+                through_backend(*inputs)
+        torch._dynamo.reset()
+        compiled = torch.compile(model, backend=target.reference_backend(), dynamic=False)
+        with torch.no_grad():
+            compiled(*inputs)  # compiles
+            with LaunchCounter() as theirs:
+                got = compiled(*inputs)
+        torch.cuda.synchronize()
+        assert lib.tc_status() == 0
+        outs_w = want if isinstance(want, (tuple, list)) else (want,)
+        outs_g = got if isinstance(got, (tuple, list)) else (got,)
+        for a, b in zip(outs_g, outs_w):
+            assert torch.equal(a, b)
+        assert theirs.names and theirs.names == ours.names, (theirs.names, ours.names)
+

@@ -603,3 +603,30 @@ def test_interceptor_monitors_the_target(tgt, xlog, monkeypatch):
         finally:
             M.LayerNormModule.forward = keep
     assert "The inference pass diverges" in xlog.text
+
+
+def test_reference_front_end_runs_the_target(tgt, xlog, monkeypatch):
+    """torch.compile(model, backend=XpuGraph(config)) - the reference's own entry (compiler.py:196-237): graph dispatch
+    through fx_utils.dispatch_graph (repaired for this PyTorch by target/compat.py), the pass manager with this target's
+    patterns, the runtime artifact, and the interceptor fed with the forward metadata."""
+    from xpu_graph import XpuGraph
+    from xpu_graph_b200.workloads import make_encoder
+
+    if torch._utils._get_available_device_type() is None:
+        monkeypatch.setattr(torch._utils, "_get_available_device_type", lambda: "cuda")
+    m, x = make_encoder(seed=0, batch=2, seq=16, hidden=64, heads=4, ffn=128)
+    be = tgt.reference_backend(tgt.make_config(debug=True))
+    assert isinstance(be, XpuGraph)
+    with torch.no_grad():
+        got = torch.compile(m, backend=be, dynamic=False)(x)
+        _same(got, m(x), 1e-4)
+    assert "decompose graph complete" in xlog.text            # compiler.py:187: the dispatch_graph branch ran
+    for name in ("FusedNativeLayerNorm", "FusedSdpa"):
+        assert name in xlog.text, f"{name} did not fire through the reference front-end"
+    torch._dynamo.reset()
+    cfg = tgt.make_config(enable_interceptor="rtol=1e-3,atol=1e-4")
+    with torch.no_grad():
+        got = torch.compile(m, backend=tgt.reference_backend(cfg), dynamic=False)(x)
+        _same(got, m(x), 1e-4)
+    assert "Monitored inference" in xlog.text and "diverges" not in xlog.text
+

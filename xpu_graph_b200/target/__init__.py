@@ -121,3 +121,16 @@ def backend(config=None, capture=None, cache=None):
                          mark=os.environ.get("RANK", "0"), config_str=cfg.enable_interceptor)
 
     return monitored_backend
+
+
+def reference_backend(config=None, cache=None):
+    """``torch.compile`` backend: the reference's own front-end, ``XpuGraph(config)`` (compiler.py:196-237), with this
+    target installed - graph dispatch through ``fx_utils.dispatch_graph``, its pass manager, its runtime artifact and, if
+    ``config.enable_interceptor`` is set, its interceptor with the forward metadata. On PyTorch releases newer than the
+    ones xpu_graph was written against this relies on the repair in ``target/compat.py``; ``backend()`` enters the same
+    inference compiler through ``aot_autograd`` instead and does not need it."""
+    install()
+    from xpu_graph import XpuGraph
+
+    return XpuGraph(config if config is not None else make_config(), cache)
+
