@@ -138,7 +138,8 @@ def main(argv=None):
     ap = argparse.ArgumentParser()
     ap.add_argument("case", choices=["sweep", "gemm_splitk", "gemm", "gemm_swiglu", "gemm_small_m", "add_rms_norm", "layer_norm", "sdpa", "rope", "swiglu",
                                      "gather", "slice_cat", "gemm_f32", "slice_sum_cat", "mul_sum_cat", "batch_dense", "graphs", "layer_gemms",
-                                     "gemm_m256", "gemm_m64", "gemm_small_sweep", "layer_norm_small", "sdpa_full", "sdpa_simt", "gemm_f32_small"])
+                                     "gemm_m256", "gemm_m64", "gemm_small_sweep", "layer_norm_small", "sdpa_full", "sdpa_simt", "gemm_f32_small",
+                                     "mlp2"])
     ap.add_argument("--iters", type=int, default=3)
     args = ap.parse_args(argv)
     if args.case == "sweep":
@@ -246,6 +247,21 @@ def main(argv=None):
             a, w, b = rn(M, K, dtype=torch.float32), rn(N, K, dtype=torch.float32, std=0.02), rn(N, dtype=torch.float32, std=0.02)
             ms = _time_graphed(lambda: X.dense(a, w, True, b, None, "gelu"))
             print(f"gemm_f32 {M}x{K}x{N} gelu: {ms * 1e3:.1f} us, {2 * M * N * K / ms / 1e9:.2f} TFLOP/s")
+    elif args.case == "mlp2":
+        # two narrow 16-bit dense layers as one kernel (hidden activation on chip) against the same two layers as two
+        # launches of this library and as eager torch (cuBLAS + elementwise kernels), device time per call
+        import torch.nn.functional as F_
+
+        print("| rows | K1 -> N1 -> N2 | one kernel (us) | two launches (us) | eager torch (us) | bytes saved (MB) |")
+        print("|---:|---|---:|---:|---:|---:|")
+        for (M, K1, N1, N2) in [(16384, 512, 256, 256), (65536, 256, 256, 128), (16384, 256, 128, 64), (4096, 1024, 256, 40),
+                                (300, 256, 128, 64)]:
+            x, w1, b1 = rn(M, K1), rn(N1, K1, std=K1 ** -0.5), rn(N1, std=0.1)
+            w2, b2 = rn(N2, N1, std=N1 ** -0.5), rn(N2, std=0.1)
+            ms = _time_graphed(lambda: X.mlp2(x, w1, b1, w2, b2, "relu", "none"))
+            ms2 = _time_graphed(lambda: X.dense(X.dense(x, w1, True, b1, None, "relu"), w2, True, b2, None, "none"))
+            ms3 = _time_graphed(lambda: F_.linear(torch.relu(F_.linear(x, w1, b1)), w2, b2))
+            print(f"| {M} | {K1} -> {N1} -> {N2} | {ms * 1e3:.1f} | {ms2 * 1e3:.1f} | {ms3 * 1e3:.1f} | {4 * M * N1 / 1e6:.1f} |")
     elif args.case == "gemm_swiglu":
         M, K, N = 8192, 4096, 11008
         a, wg, wu = rn(M, K), rn(N, K, std=0.02), rn(N, K, std=0.02)

@@ -52,7 +52,8 @@ const char* xg_last_error(void);
 /*
  * Status word of the tensor-core kernels on the current device: 0 = healthy; non-zero = a bounded
  * wait inside a kernel expired (bit 0 producer, bit 1 MMA issuer, bit 2 epilogue, bits 4-6 the same
- * roles of the attention kernel) and that launch's output is invalid. This is the one entry point
+ * roles of the attention kernel, bits 8-10 of the cluster dense kernel, bits 16-18 of the two-layer kernel) and that
+ * launch's output is invalid. This is the one entry point
  * that synchronises (it copies the word back); reset != 0 clears it. No reference counterpart.
  */
 int xg_tc_status(unsigned int* status, int reset);
@@ -209,6 +210,22 @@ int xg_bgemm_bias_act(const void* A, const void* B, const void* bias, const void
                       int64_t ldc, int64_t ldr, int64_t stride_a, int64_t stride_b,
                       int64_t stride_bias, int64_t stride_r, int64_t stride_c, int trans_b, int act,
                       int dtype, void* stream);
+
+/*
+ * Two chained dense layers in one kernel: out = act2( act1( x @ W1^T + b1 ) @ W2^T + b2 ), x [M, K1], W1 [N1, K1],
+ * W2 [N2, N1] (both weights as nn.Linear stores them), out [M, N2]; row strides in elements; biases nullable.
+ * The hidden activation [M, N1] stays on chip: it is rounded to the 16-bit dtype (as the unfused graph rounds it
+ * when it stores the tensor) and handed to the second product through shared memory. 16-bit dtypes only;
+ * xg_mlp2_supported says whether a shape fits (K1 % 8 == 0, 16 <= N1 <= 256 with N1 % 8 == 0, N2 <= 256); x, W1, W2
+ * 16-byte aligned with row strides that are multiples of 8 elements.
+ * Replaces: FusedDenseTower2Replacement.forward -> fuse_serial_mm_2dot (targets/mlu/fuse_densetower.py:17-49, matched
+ * by FusedDenseTower2 :272-316; kernel triton_kernel/fused_serial_mm_2dot.py:142), whose condition is likewise that
+ * both weights fit on chip (:66-77).
+ */
+int xg_mlp2_supported(int64_t M, int64_t K1, int64_t N1, int64_t N2, int dtype);
+int xg_mlp2_bias_act(const void* x, const void* w1, const void* b1, const void* w2, const void* b2, void* out, int64_t M,
+                     int64_t K1, int64_t N1, int64_t N2, int64_t lda, int64_t ldw1, int64_t ldw2, int64_t ldc, int act1,
+                     int act2, int dtype, void* stream);
 
 /*
  * Grouped form: out[e] = act( A[e] @ W[e] + bias[e] ) for `count` problems of one shape [M, N, K] whose operands lie

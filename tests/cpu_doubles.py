@@ -106,6 +106,7 @@ def register():
         return y
 
     k(ops.dense_tower)(dense_tower)
+    k(ops.mlp2)(lambda x, w1, b1, w2, b2, act1, act2: dense(dense(x, w1, True, b1, None, act1), w2, True, b2, None, act2))
 
     def combo_dense(inputs, weights, weight_trans, biases, act):
         return torch.stack([dense(x, w, weight_trans, b, None, act) for x, w, b in zip(inputs, weights, biases)])

@@ -223,6 +223,77 @@ def test_dense_fp32_on_tensor_cores(cuda_device, M, K, N, act, with_res, weight_
     assert_parity(got, want, f"dense fp32 (bf16 planes) {M}x{K}x{N} {act}")
 
 
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("M,K1,N1,N2,acts,with_bias", [
+    (300, 256, 128, 64, ("relu", "none"), (True, True)),
+    (1000, 520, 200, 100, ("gelu", "sigmoid"), (True, False)),   # ragged K1 (not a multiple of 64), N1, N2
+    (16384, 512, 256, 256, ("relu", "relu"), (True, True)),      # the widest layers the kernel takes; one block per SM and more
+    (128, 64, 16, 1, ("silu", "none"), (False, True)),
+    (4100, 1024, 256, 40, ("none", "gelu"), (False, False)),
+    (40000, 72, 96, 136, ("relu", "silu"), (True, True)),        # several blocks per CTA
+])
+def test_mlp2(cuda_device, M, K1, N1, N2, acts, with_bias, dtype):
+    """Two chained dense layers in one kernel (the hidden activation handed over through shared memory) vs the two
+    layers one after the other on CPU, the hidden tensor rounded to the 16-bit dtype in between as eager does."""
+    from xpu_graph_b200 import lib, ops  # noqa: F401  (ops registers torch.ops.xg_sm100.*)
+
+    g = torch.Generator().manual_seed(41)
+    x = torch.randn(M, K1, generator=g).to(dtype)
+    w1 = (torch.randn(N1, K1, generator=g) * K1 ** -0.5).to(dtype)
+    w2 = (torch.randn(N2, N1, generator=g) * N1 ** -0.5).to(dtype)
+    b1 = (0.1 * torch.randn(N1, generator=g)).to(dtype) if with_bias[0] else None
+    b2 = (0.1 * torch.randn(N2, generator=g)).to(dtype) if with_bias[1] else None
+    dev = lambda t: t.to(cuda_device) if t is not None else None
+    got = torch.ops.xg_sm100.mlp2(dev(x), dev(w1), dev(b1), dev(w2), dev(b2), acts[0], acts[1])
+    torch.cuda.synchronize()
+    assert lib.tc_status() == 0, "a bounded wait expired inside the two-layer kernel"
+    # (a) the kernel's own arithmetic: fp32 through the first layer and its activation, ONE rounding of the hidden
+    #     tensor to the 16-bit dtype, fp32 through the second layer
+    f = lambda t: t.float() if t is not None else None
+    h = ref_ops.dense(f(x), f(w1), True, f(b1), acts[0]).to(dtype)
+    once = ref_ops.dense(f(h), f(w2), True, f(b2), acts[1]).to(dtype)
+    assert_parity(got, once, f"mlp2 {M}x{K1}->{N1}->{N2} {acts} {dtype} (hidden rounded once)")
+    # (b) the eager chain, which rounds the hidden tensor after the linear and again after the activation: its hidden
+    #     elements can sit one rounding step (2^-8 relative for bf16, 2^-11 for f16) away from the kernel's, so the
+    #     outputs may differ by that step times the sum of |h w| over the hidden width
+    want = ref_ops.dense(ref_ops.dense(x, w1, True, b1, acts[0]), w2, True, b2, acts[1])
+    step = 2.0 ** -8 if dtype == torch.bfloat16 else 2.0 ** -11
+    from tests.helpers import BF16_RTOL
+    assert_parity(got, want, f"mlp2 {M}x{K1}->{N1}->{N2} {acts} {dtype} (eager chain)",
+                  magnitude=(h.float().abs() @ w2.float().abs().t()) * (step / BF16_RTOL))
+
+
+def test_mlp2_strided_input_and_limits(cuda_device):
+    """A row-strided x (a column slice of a wider tensor) is read in place; shapes outside the kernel's limits are
+    refused with XG_ERR_UNSUPPORTED, and the tower op then runs the layers one by one."""
+    from xpu_graph_b200 import lib, ops  # noqa: F401
+    from xpu_graph_b200.modules import DenseTowerModule
+
+    g = torch.Generator().manual_seed(42)
+    wide = torch.randn(700, 384, generator=g).to(torch.bfloat16)
+    x = wide[:, 64:320]
+    w1 = (torch.randn(64, 256, generator=g) / 16).to(torch.bfloat16)
+    w2 = (torch.randn(32, 64, generator=g) / 8).to(torch.bfloat16)
+    got = torch.ops.xg_sm100.mlp2(wide.to(cuda_device)[:, 64:320], w1.to(cuda_device), None, w2.to(cuda_device), None, "relu", "none")
+    assert_parity(got, ref_ops.dense(ref_ops.dense(x, w1, True, None, "relu"), w2, True, None, "none"), "mlp2 strided x")
+    L = lib.load()
+    assert L.xg_mlp2_supported(128, 64, 512, 64, lib.XG_BF16) == 0      # hidden layer too wide
+    assert L.xg_mlp2_supported(128, 64, 100, 64, lib.XG_BF16) == 0      # N1 not a multiple of 8
+    assert L.xg_mlp2_supported(128, 64, 128, 64, lib.XG_F32) == 0
+    assert L.xg_mlp2_supported(128, 64, 128, 64, lib.XG_F16) == 1
+    # a three-layer 16-bit tower: the first two layers as one launch, the third (too wide to pair) on its own
+    w3 = (torch.randn(512, 32, generator=g) / 6).to(torch.bfloat16)
+    from tests.helpers import LaunchCounter
+    with LaunchCounter() as c:
+        got = DenseTowerModule()(x.to(cuda_device), [w1.to(cuda_device), w2.to(cuda_device), w3.to(cuda_device)],
+                                 [True, True, True], [None, None, None], ["relu", "relu", "none"])
+    torch.cuda.synchronize()
+    assert lib.tc_status() == 0
+    assert len(c.names) == 2 and c.names[0] == "xg_mlp2_bias_act" and c.names[1].startswith("xg_gemm_bias_act"), c.names
+    want = ref_ops.dense(ref_ops.dense(ref_ops.dense(x, w1, True, None, "relu"), w2, True, None, "relu"), w3, True, None, "none")
+    assert_parity(got, want, "16-bit dense tower")
+
+
 def test_dense_tower_fp32(cuda_device):
     """Recsys MLP sizes (1728 -> 1024 -> 512 -> 256 over 16384 rows, ReLU between): the inner results travel as bf16
     planes; the result must stay within the fp32 tolerance of fp64 math. A ragged tower checks the zero padding."""

@@ -488,6 +488,28 @@ def test_dense_tower(tgt, xlog):
     assert "xg_dense_tower" not in mods
 
 
+def test_dense_tower_16bit_pairs(tgt, xlog):
+    """bf16 Linear+ReLU -> Linear whose widths fit the two-layer kernel (N <= 256) become one DenseTowerModule call (the
+    graph form of targets/mlu/fuse_densetower.py:272-316); a chain whose hidden layer is too wide stays as it is."""
+    torch.manual_seed(10)
+    narrow = torch.nn.Sequential(torch.nn.Linear(192, 256), torch.nn.ReLU(), torch.nn.Linear(256, 64)).eval().to(torch.bfloat16)
+    x = torch.randn(512, 192).to(torch.bfloat16)
+    want, got, mods, atens = _compile(tgt, narrow, x)
+    _same(got, want, 2e-2)
+    assert "Pattern.FusedDenseTower changed graph" in xlog.text
+    assert mods == ["xg_dense_tower"], mods
+
+    three = torch.nn.Sequential(torch.nn.Linear(64, 128), torch.nn.GELU(), torch.nn.Linear(128, 128), torch.nn.Sigmoid(),
+                                torch.nn.Linear(128, 24)).eval().to(torch.bfloat16)
+    want, got, mods, atens = _compile(tgt, three, torch.randn(300, 64).to(torch.bfloat16))
+    _same(got, want, 2e-2)
+    assert mods == ["xg_dense_tower"], mods
+
+    wide = torch.nn.Sequential(torch.nn.Linear(64, 512), torch.nn.ReLU(), torch.nn.Linear(512, 512)).eval().to(torch.bfloat16)
+    want, got, mods, atens = _compile(tgt, wide, torch.randn(256, 64).to(torch.bfloat16))
+    assert "xg_dense_tower" not in mods
+
+
 def test_combo_dense(tgt, xlog):
     """Five parallel bf16 Linear+ReLU layers of one shape over different inputs -> one ComboDenseModule call;
     three of them are too few (the reference's width of 4) and stay separate."""

@@ -36,6 +36,7 @@ int gemm_group_entry(const void* const* A, const void* const* W, const void* con
 int read_tc_status(unsigned int* host_out, int reset);
 int read_sdpa_status(unsigned int* host_out, int reset);
 int read_ksplit_status(unsigned int* host_out, int reset);
+int read_mlp_status(unsigned int* host_out, int reset);
 
 namespace {
 int validate_gemm(const char* name, const void* A, const void* B, const void* residual, void* out, int64_t M, int64_t N,
@@ -195,6 +196,9 @@ extern "C" int xg_tc_status(unsigned int* status, int reset) {
     unsigned int c = 0;
     rc = xg::read_ksplit_status(&c, reset);
     if (rc != XG_OK) return rc;
-    *status = a | b | (c << 8);
+    unsigned int d = 0;
+    rc = xg::read_mlp_status(&d, reset);
+    if (rc != XG_OK) return rc;
+    *status = a | b | (c << 8) | (d << 16);
     return XG_OK;
 }

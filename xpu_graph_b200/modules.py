@@ -299,10 +299,11 @@ class ComboDenseModule(torch.nn.Module):
 
 
 class DenseTowerModule(torch.nn.Module):
-    """A chain of fp32 dense layers in one call: forward(x, weights, weight_trans, biases, acts) with one entry per
-    layer. Stands where the reference fuses serial matmuls into one kernel (targets/mlu/fuse_densetower.py:272-316,
-    triton_kernel/fused_serial_mm_2dot.py / _3dot.py): here the layers stay separate tensor-core GEMMs and the
-    activations travel between them as bf16 planes."""
+    """A chain of dense layers in one call: forward(x, weights, weight_trans, biases, acts) with one entry per layer.
+    Stands where the reference fuses serial matmuls into one kernel (targets/mlu/fuse_densetower.py:272-316,
+    triton_kernel/fused_serial_mm_2dot.py / _3dot.py). 16-bit towers: neighbouring narrow layers (N <= 256) run as one
+    kernel per pair with the hidden activation kept on chip (xg_mlp2_bias_act). fp32 towers: the layers stay separate
+    tensor-core GEMMs and the activations travel between them as bf16 planes."""
 
     def forward(self, x, weights, weight_trans, biases, acts):
         return _X.dense_tower(x, list(weights), [bool(t) for t in weight_trans], list(biases), ",".join(str(a) for a in acts))

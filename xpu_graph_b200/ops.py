@@ -285,6 +285,47 @@ def dense_tower_eligible(M: int, dims: Sequence[int]) -> bool:
     return all(_f32_on_tensor_cores(M, dims[i + 1], dims[i]) for i in range(len(dims) - 1))
 
 
+def mlp2_eligible(M: int, K1: int, N1: int, N2: int, dtype: torch.dtype, trans1: bool = True, trans2: bool = True) -> bool:
+    """Two chained 16-bit dense layers [K1 -> N1 -> N2] fit the single-kernel form: weights as nn.Linear stores them
+    ([N, K]), 16 <= N1 <= 256 with N1 % 8 == 0, N2 <= 256, K1 % 8 == 0 (the limits of xg_mlp2_supported)."""
+    return (dtype in (torch.bfloat16, torch.float16) and bool(trans1) and bool(trans2) and M > 0 and K1 >= 8 and K1 % 8 == 0
+            and 16 <= N1 <= 256 and N1 % 8 == 0 and 1 <= N2 <= 256)
+
+
+@torch.library.custom_op(f"{NS}::mlp2", mutates_args=(), device_types="cuda")
+def mlp2(x: torch.Tensor, w1: torch.Tensor, b1: Optional[torch.Tensor], w2: torch.Tensor, b2: Optional[torch.Tensor],
+         act1: str, act2: str) -> torch.Tensor:
+    """act2(act1(x @ w1^T + b1) @ w2^T + b2) in one kernel; w1 [N1, K1], w2 [N2, N1]; the hidden activation stays on chip
+    (rounded to the tensors' 16-bit dtype between the layers, as the unfused graph does)."""
+    if x.dim() != 2 or w1.dim() != 2 or w2.dim() != 2:
+        raise ValueError("xg_sm100::mlp2 expects 2-D x, w1 and w2")
+    x, w1, w2 = _mat(x), _mat(w1), _mat(w2)
+    M, K1 = x.shape
+    N1, N2 = w1.shape[0], w2.shape[0]
+    if w1.shape[1] != K1 or w2.shape[1] != N1:
+        raise ValueError("xg_sm100::mlp2: inner dimensions differ")
+    if w1.dtype != x.dtype or w2.dtype != x.dtype:
+        raise ValueError("xg_sm100::mlp2: x, w1 and w2 must share a dtype")
+    b1 = b1.to(x.dtype).contiguous() if b1 is not None else None
+    b2 = b2.to(x.dtype).contiguous() if b2 is not None else None
+    if (b1 is not None and b1.numel() != N1) or (b2 is not None and b2.numel() != N2):
+        raise ValueError("xg_sm100::mlp2: a bias does not match its layer's width")
+    out = torch.empty((M, N2), dtype=x.dtype, device=x.device)
+    if M == 0:
+        return out
+    L = _lib.load()
+    rc = L.xg_mlp2_bias_act(_ptr(x), _ptr(w1), _ptr(b1), _ptr(w2), _ptr(b2), _ptr(out), M, K1, N1, N2, _row_stride(x),
+                            _row_stride(w1), _row_stride(w2), N2, _lib.ACT_CODES[act1], _lib.ACT_CODES[act2],
+                            _code(x.dtype), _stream(x))
+    _lib.check(rc, "xg_mlp2_bias_act")
+    return out
+
+
+@mlp2.register_fake
+def _(x, w1, b1, w2, b2, act1, act2):
+    return torch.empty((x.shape[0], w2.shape[0]), dtype=x.dtype, device=x.device)
+
+
 @torch.library.custom_op(f"{NS}::dense_tower", mutates_args=(), device_types="cuda")
 def dense_tower(x: torch.Tensor, weights: List[torch.Tensor], weight_trans: List[bool], biases: List[Optional[torch.Tensor]],
                 act_names: str) -> torch.Tensor:
@@ -294,11 +335,22 @@ def dense_tower(x: torch.Tensor, weights: List[torch.Tensor], weight_trans: List
     acts = act_names.split(",")
     if not (len(acts) == len(weights) == len(weight_trans) == len(biases)):
         raise ValueError("xg_sm100::dense_tower: one weight, orientation, bias and activation per layer")
-    if x.dim() != 2 or x.dtype != torch.float32:
-        raise ValueError("xg_sm100::dense_tower expects a 2-D fp32 input")
+    if x.dim() != 2 or x.dtype not in (torch.float32, torch.bfloat16, torch.float16):
+        raise ValueError("xg_sm100::dense_tower expects a 2-D floating-point input")
     n = len(weights)
     M = x.shape[0]
     dims = [x.shape[1]] + [(w.shape[0] if t else w.shape[1]) for w, t in zip(weights, weight_trans)]
+    if x.dtype != torch.float32:
+        # 16-bit towers: neighbouring layers that fit the two-layer kernel run as one launch each, the rest layer by layer
+        y, i = x, 0
+        while i < n:
+            if i + 1 < n and mlp2_eligible(M, dims[i], dims[i + 1], dims[i + 2], x.dtype, weight_trans[i], weight_trans[i + 1]):
+                y = mlp2(y, weights[i], biases[i], weights[i + 1], biases[i + 1], acts[i], acts[i + 1])
+                i += 2
+            else:
+                y = dense(y, weights[i], weight_trans[i], biases[i], None, acts[i])
+                i += 1
+        return y
     if not dense_tower_eligible(M, dims):
         y = x
         for i in range(n):

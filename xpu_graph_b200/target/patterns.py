@@ -1221,9 +1221,11 @@ class FusedComboDense(Pattern):
 
 # ---- chains of fp32 dense layers ---------------------------------------------------------------------------------
 class FusedDenseTower(Pattern):
-    """dense(dense(dense(x))) in fp32, each inner result used only by the next layer -> DenseTowerModule, when every
-    layer is large enough for the tensor-core path (ops.dense_tower_eligible). The graph form of
-    targets/mlu/fuse_densetower.py:272-316 (FusedDenseTower2 / 3), for any depth >= 2."""
+    """dense(dense(dense(x))), each inner result used only by the next layer -> DenseTowerModule. fp32 chains of any
+    depth >= 2 when every layer is large enough for the tensor-core path (ops.dense_tower_eligible); 16-bit chains when
+    at least one pair of neighbouring layers fits the two-layer kernel (ops.mlp2_eligible: narrow layers whose hidden
+    activation then never leaves the SM). The graph form of targets/mlu/fuse_densetower.py:272-316
+    (FusedDenseTower2 / 3)."""
 
     _opt_level = OptLevel.level2
     _pattern_group = PatternGroup.GROUP2
@@ -1231,28 +1233,52 @@ class FusedDenseTower(Pattern):
     def process(self, gm: fx.GraphModule) -> bool:
         from .. import ops as _ops
 
-        def is_dense(n):
+        def is_dense(n, dtype=None):
             if not (_module_call(gm, n, M.DenseLayerModule) and n.target == DENSE_NAME and len(n.args) == 5):
                 return False
             v, xv, bv = _val(n), _val(n.args[0]), _val(n.args[3])
-            if not (_tensor_ok(v, 2) and _tensor_ok(xv, 2) and v.dtype == torch.float32 and _static(v.shape) and _static(xv.shape)):
+            if not (_tensor_ok(v, 2) and _tensor_ok(xv, 2) and _static(v.shape) and _static(xv.shape)):
+                return False
+            if v.dtype not in (torch.float32, torch.bfloat16, torch.float16) or xv.dtype != v.dtype:
+                return False
+            if dtype is not None and v.dtype != dtype:
+                return False
+            if not isinstance(n.args[2], bool) or not isinstance(n.args[4], str):
                 return False
             return n.args[3] is None or (isinstance(bv, torch.Tensor) and bv.dim() == 1 and bv.numel() == v.shape[1])
+
+        def worth_it(x, chain):
+            rows = _val(x).shape[0]
+            dims = [_val(x).shape[1]] + [_val(n).shape[1] for n in chain]
+            dtype = _val(chain[0]).dtype
+            if dtype == torch.float32:
+                return _ops.dense_tower_eligible(rows, dims)
+            # four or more independent layers of one shape are FusedComboDense's (one grouped launch for all of them)
+            head = chain[0]
+            alike = [m for m in gm.graph.nodes
+                     if is_dense(m, dtype) and m.args[2] == head.args[2] and m.args[4] == head.args[4]
+                     and _val(m.args[1]).shape == _val(head.args[1]).shape and _val(m.args[0]).shape == _val(x).shape]
+            if len(alike) >= 4:
+                return False
+            return any(_ops.mlp2_eligible(rows, dims[i], dims[i + 1], dims[i + 2], dtype, chain[i].args[2], chain[i + 1].args[2])
+                       for i in range(len(chain) - 1))
 
         changed = False
         for tail in reversed(list(gm.graph.nodes)):
             if getattr(tail, "_erased", False):
                 continue  # an inner layer of a chain that this sweep has already replaced
-            if not is_dense(tail) or any(is_dense(u) and u.args[0] is tail and _only_user(tail, u) for u in tail.users):
-                continue  # not a dense layer, or not the last one of its chain
+            if not is_dense(tail):
+                continue
+            dtype = _val(tail).dtype
+            if any(is_dense(u, dtype) and u.args[0] is tail and _only_user(tail, u) for u in tail.users):
+                continue  # not the last layer of its chain
             chain = [tail]
-            while is_dense(chain[0].args[0]) and _only_user(chain[0].args[0], chain[0]):
+            while is_dense(chain[0].args[0], dtype) and _only_user(chain[0].args[0], chain[0]):
                 chain.insert(0, chain[0].args[0])
             if len(chain) < 2:
                 continue
             x = chain[0].args[0]
-            dims = [_val(x).shape[1]] + [_val(n).shape[1] for n in chain]
-            if not _ops.dense_tower_eligible(_val(x).shape[0], dims):
+            if not worth_it(x, chain):
                 continue
             _ensure(gm, "xg_dense_tower", M.DenseTowerModule)
             with gm.graph.inserting_before(tail):
