@@ -248,11 +248,11 @@ def main(argv=None):
             ms = _time_graphed(lambda: X.dense(a, w, True, b, None, "gelu"))
             print(f"gemm_f32 {M}x{K}x{N} gelu: {ms * 1e3:.1f} us, {2 * M * N * K / ms / 1e9:.2f} TFLOP/s")
     elif args.case == "mlp2":
-        # two narrow 16-bit dense layers as one kernel (hidden activation on chip) against the same two layers as two
-        # launches of this library and as eager torch (cuBLAS + elementwise kernels), device time per call
+        # two / three narrow 16-bit dense layers as one kernel (hidden activations on chip) against the same layers as one
+        # launch each of this library and as eager torch (cuBLAS + elementwise kernels), device time per call
         import torch.nn.functional as F_
 
-        print("| rows | K1 -> N1 -> N2 | one kernel (us) | two launches (us) | eager torch (us) | bytes saved (MB) |")
+        print("| rows | layer widths | one kernel (us) | one launch per layer (us) | eager torch (us) | hidden bytes kept on chip (MB) |")
         print("|---:|---|---:|---:|---:|---:|")
         for (M, K1, N1, N2) in [(16384, 512, 256, 256), (65536, 256, 256, 128), (16384, 256, 128, 64), (4096, 1024, 256, 40),
                                 (300, 256, 128, 64)]:
@@ -262,6 +262,15 @@ def main(argv=None):
             ms2 = _time_graphed(lambda: X.dense(X.dense(x, w1, True, b1, None, "relu"), w2, True, b2, None, "none"))
             ms3 = _time_graphed(lambda: F_.linear(torch.relu(F_.linear(x, w1, b1)), w2, b2))
             print(f"| {M} | {K1} -> {N1} -> {N2} | {ms * 1e3:.1f} | {ms2 * 1e3:.1f} | {ms3 * 1e3:.1f} | {4 * M * N1 / 1e6:.1f} |")
+        for (M, K1, N1, N2, N3) in [(16384, 512, 256, 256, 128), (65536, 256, 256, 128, 64), (16384, 256, 128, 64, 32)]:
+            x, w1, b1 = rn(M, K1), rn(N1, K1, std=K1 ** -0.5), rn(N1, std=0.1)
+            w2, b2 = rn(N2, N1, std=N1 ** -0.5), rn(N2, std=0.1)
+            w3, b3 = rn(N3, N2, std=N2 ** -0.5), rn(N3, std=0.1)
+            ms = _time_graphed(lambda: X.mlp3(x, w1, b1, w2, b2, w3, b3, "relu", "relu", "none"))
+            ms2 = _time_graphed(lambda: X.dense(X.dense(X.dense(x, w1, True, b1, None, "relu"), w2, True, b2, None, "relu"),
+                                                w3, True, b3, None, "none"))
+            ms3 = _time_graphed(lambda: F_.linear(torch.relu(F_.linear(torch.relu(F_.linear(x, w1, b1)), w2, b2)), w3, b3))
+            print(f"| {M} | {K1} -> {N1} -> {N2} -> {N3} | {ms * 1e3:.1f} | {ms2 * 1e3:.1f} | {ms3 * 1e3:.1f} | {4 * M * (N1 + N2) / 1e6:.1f} |")
     elif args.case == "gemm_swiglu":
         M, K, N = 8192, 4096, 11008
         a, wg, wu = rn(M, K), rn(N, K, std=0.02), rn(N, K, std=0.02)

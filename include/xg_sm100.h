@@ -52,7 +52,7 @@ const char* xg_last_error(void);
 /*
  * Status word of the tensor-core kernels on the current device: 0 = healthy; non-zero = a bounded
  * wait inside a kernel expired (bit 0 producer, bit 1 MMA issuer, bit 2 epilogue, bits 4-6 the same
- * roles of the attention kernel, bits 8-10 of the cluster dense kernel, bits 16-18 of the two-layer kernel) and that
+ * roles of the attention kernel, bits 8-10 of the cluster dense kernel, bits 16-18 of the chained-layer kernel) and that
  * launch's output is invalid. This is the one entry point
  * that synchronises (it copies the word back); reset != 0 clears it. No reference counterpart.
  */
@@ -212,20 +212,27 @@ int xg_bgemm_bias_act(const void* A, const void* B, const void* bias, const void
                       int dtype, void* stream);
 
 /*
- * Two chained dense layers in one kernel: out = act2( act1( x @ W1^T + b1 ) @ W2^T + b2 ), x [M, K1], W1 [N1, K1],
- * W2 [N2, N1] (both weights as nn.Linear stores them), out [M, N2]; row strides in elements; biases nullable.
- * The hidden activation [M, N1] stays on chip: it is rounded to the 16-bit dtype (as the unfused graph rounds it
- * when it stores the tensor) and handed to the second product through shared memory. 16-bit dtypes only;
- * xg_mlp2_supported says whether a shape fits (K1 % 8 == 0, 16 <= N1 <= 256 with N1 % 8 == 0, N2 <= 256); x, W1, W2
- * 16-byte aligned with row strides that are multiples of 8 elements.
- * Replaces: FusedDenseTower2Replacement.forward -> fuse_serial_mm_2dot (targets/mlu/fuse_densetower.py:17-49, matched
- * by FusedDenseTower2 :272-316; kernel triton_kernel/fused_serial_mm_2dot.py:142), whose condition is likewise that
- * both weights fit on chip (:66-77).
+ * Two or three chained dense layers in one kernel: out = act2( act1( x @ W1^T + b1 ) @ W2^T + b2 ) (and a third layer
+ * on top for xg_mlp3_bias_act), x [M, K1], W1 [N1, K1], W2 [N2, N1], W3 [N3, N2] (weights as nn.Linear stores them),
+ * out [M, N_last]; row strides in elements; biases nullable. The hidden activations stay on chip: each is rounded to
+ * the 16-bit dtype (as the unfused graph rounds it when it stores the tensor) and handed to the next product through
+ * shared memory. 16-bit dtypes only; xg_mlp2_supported / xg_mlp3_supported say whether a shape fits (K1 % 8 == 0, every
+ * width <= 256, hidden widths >= 16 and multiples of 8); x and the weights 16-byte aligned with row strides that are
+ * multiples of 8 elements.
+ * Replaces: FusedDenseTower2Replacement.forward -> fuse_serial_mm_2dot and FusedDenseTower3Replacement.forward ->
+ * fuse_serial_mm_3dot (targets/mlu/fuse_densetower.py:14-49, 80-131, matched by FusedDenseTower2 / 3 :272-316; kernels
+ * triton_kernel/fused_serial_mm_2dot.py:142, fused_serial_mm_3dot.py:271), whose condition is likewise that the weights
+ * fit on chip (:66-77).
  */
 int xg_mlp2_supported(int64_t M, int64_t K1, int64_t N1, int64_t N2, int dtype);
+int xg_mlp3_supported(int64_t M, int64_t K1, int64_t N1, int64_t N2, int64_t N3, int dtype);
 int xg_mlp2_bias_act(const void* x, const void* w1, const void* b1, const void* w2, const void* b2, void* out, int64_t M,
                      int64_t K1, int64_t N1, int64_t N2, int64_t lda, int64_t ldw1, int64_t ldw2, int64_t ldc, int act1,
                      int act2, int dtype, void* stream);
+int xg_mlp3_bias_act(const void* x, const void* w1, const void* b1, const void* w2, const void* b2, const void* w3,
+                     const void* b3, void* out, int64_t M, int64_t K1, int64_t N1, int64_t N2, int64_t N3, int64_t lda,
+                     int64_t ldw1, int64_t ldw2, int64_t ldw3, int64_t ldc, int act1, int act2, int act3, int dtype,
+                     void* stream);
 
 /*
  * Grouped form: out[e] = act( A[e] @ W[e] + bias[e] ) for `count` problems of one shape [M, N, K] whose operands lie

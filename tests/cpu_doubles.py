@@ -106,6 +106,8 @@ def register():
         return y
 
     k(ops.dense_tower)(dense_tower)
+    k(ops.mlp3)(lambda x, w1, b1, w2, b2, w3, b3, a1, a2, a3: dense(dense(dense(x, w1, True, b1, None, a1), w2, True, b2, None, a2),
+                                                                   w3, True, b3, None, a3))
     k(ops.mlp2)(lambda x, w1, b1, w2, b2, act1, act2: dense(dense(x, w1, True, b1, None, act1), w2, True, b2, None, act2))
 
     def combo_dense(inputs, weights, weight_trans, biases, act):

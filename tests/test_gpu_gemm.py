@@ -263,6 +263,33 @@ def test_mlp2(cuda_device, M, K1, N1, N2, acts, with_bias, dtype):
                   magnitude=(h.float().abs() @ w2.float().abs().t()) * (step / BF16_RTOL))
 
 
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("M,dims,acts", [
+    (5000, [256, 256, 128, 64], ("relu", "relu", "none")),
+    (700, [72, 200, 104, 30], ("gelu", "silu", "sigmoid")),       # ragged everywhere
+    (30000, [512, 256, 256, 256], ("relu", "relu", "relu")),      # widest; several blocks per CTA
+])
+def test_mlp3(cuda_device, M, dims, acts, dtype):
+    """Three chained dense layers in one kernel vs the kernel's own arithmetic on CPU (fp32 through each layer, one
+    rounding of each hidden tensor to the 16-bit dtype)."""
+    from xpu_graph_b200 import lib, ops  # noqa: F401
+
+    g = torch.Generator().manual_seed(43)
+    x = torch.randn(M, dims[0], generator=g).to(dtype)
+    ws = [(torch.randn(dims[i + 1], dims[i], generator=g) * dims[i] ** -0.5).to(dtype) for i in range(3)]
+    bs = [(0.1 * torch.randn(dims[i + 1], generator=g)).to(dtype) for i in range(3)]
+    bs[1] = None
+    dev = lambda t: t.to(cuda_device) if t is not None else None
+    got = torch.ops.xg_sm100.mlp3(dev(x), dev(ws[0]), dev(bs[0]), dev(ws[1]), dev(bs[1]), dev(ws[2]), dev(bs[2]), *acts)
+    torch.cuda.synchronize()
+    assert lib.tc_status() == 0, "a bounded wait expired inside the chained-layer kernel"
+    f = lambda t: t.float() if t is not None else None
+    y = x
+    for w, b, a in zip(ws, bs, acts):
+        y = ref_ops.dense(f(y), f(w), True, f(b), a).to(dtype)
+    assert_parity(got, y, f"mlp3 {M}x{dims} {acts} {dtype}")
+
+
 def test_mlp2_strided_input_and_limits(cuda_device):
     """A row-strided x (a column slice of a wider tensor) is read in place; shapes outside the kernel's limits are
     refused with XG_ERR_UNSUPPORTED, and the tower op then runs the layers one by one."""
@@ -292,6 +319,15 @@ def test_mlp2_strided_input_and_limits(cuda_device):
     assert len(c.names) == 2 and c.names[0] == "xg_mlp2_bias_act" and c.names[1].startswith("xg_gemm_bias_act"), c.names
     want = ref_ops.dense(ref_ops.dense(ref_ops.dense(x, w1, True, None, "relu"), w2, True, None, "relu"), w3, True, None, "none")
     assert_parity(got, want, "16-bit dense tower")
+    # all three layers narrow: one launch
+    w3n = (torch.randn(48, 32, generator=g) / 6).to(torch.bfloat16)
+    with LaunchCounter() as c:
+        got = DenseTowerModule()(x.to(cuda_device), [w1.to(cuda_device), w2.to(cuda_device), w3n.to(cuda_device)],
+                                 [True, True, True], [None, None, None], ["relu", "relu", "none"])
+    torch.cuda.synchronize()
+    assert lib.tc_status() == 0 and c.names == ["xg_mlp3_bias_act"], c.names
+    want = ref_ops.dense(ref_ops.dense(ref_ops.dense(x, w1, True, None, "relu"), w2, True, None, "relu"), w3n, True, None, "none")
+    assert_parity(got, want, "16-bit dense tower, three narrow layers")
 
 
 def test_dense_tower_fp32(cuda_device):

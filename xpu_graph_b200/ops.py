@@ -326,6 +326,44 @@ def _(x, w1, b1, w2, b2, act1, act2):
     return torch.empty((x.shape[0], w2.shape[0]), dtype=x.dtype, device=x.device)
 
 
+def mlp3_eligible(M: int, K1: int, N1: int, N2: int, N3: int, dtype: torch.dtype, trans=(True, True, True)) -> bool:
+    """Three chained 16-bit dense layers fit the single-kernel form (the limits of xg_mlp3_supported)."""
+    return (mlp2_eligible(M, K1, N1, N2, dtype, trans[0], trans[1]) and bool(trans[2]) and 16 <= N2 and N2 % 8 == 0
+            and 1 <= N3 <= 256)
+
+
+@torch.library.custom_op(f"{NS}::mlp3", mutates_args=(), device_types="cuda")
+def mlp3(x: torch.Tensor, w1: torch.Tensor, b1: Optional[torch.Tensor], w2: torch.Tensor, b2: Optional[torch.Tensor],
+         w3: torch.Tensor, b3: Optional[torch.Tensor], act1: str, act2: str, act3: str) -> torch.Tensor:
+    """Three chained dense layers in one kernel (see mlp2); w3 [N3, N2]."""
+    if x.dim() != 2 or w1.dim() != 2 or w2.dim() != 2 or w3.dim() != 2:
+        raise ValueError("xg_sm100::mlp3 expects 2-D x and weights")
+    x, w1, w2, w3 = _mat(x), _mat(w1), _mat(w2), _mat(w3)
+    M, K1 = x.shape
+    N1, N2, N3 = w1.shape[0], w2.shape[0], w3.shape[0]
+    if w1.shape[1] != K1 or w2.shape[1] != N1 or w3.shape[1] != N2:
+        raise ValueError("xg_sm100::mlp3: inner dimensions differ")
+    if not (w1.dtype == w2.dtype == w3.dtype == x.dtype):
+        raise ValueError("xg_sm100::mlp3: x and the weights must share a dtype")
+    bs = [b.to(x.dtype).contiguous() if b is not None else None for b in (b1, b2, b3)]
+    if any(b is not None and b.numel() != n for b, n in zip(bs, (N1, N2, N3))):
+        raise ValueError("xg_sm100::mlp3: a bias does not match its layer's width")
+    out = torch.empty((M, N3), dtype=x.dtype, device=x.device)
+    if M == 0:
+        return out
+    L = _lib.load()
+    rc = L.xg_mlp3_bias_act(_ptr(x), _ptr(w1), _ptr(bs[0]), _ptr(w2), _ptr(bs[1]), _ptr(w3), _ptr(bs[2]), _ptr(out), M, K1, N1,
+                            N2, N3, _row_stride(x), _row_stride(w1), _row_stride(w2), _row_stride(w3), N3, _lib.ACT_CODES[act1],
+                            _lib.ACT_CODES[act2], _lib.ACT_CODES[act3], _code(x.dtype), _stream(x))
+    _lib.check(rc, "xg_mlp3_bias_act")
+    return out
+
+
+@mlp3.register_fake
+def _(x, w1, b1, w2, b2, w3, b3, act1, act2, act3):
+    return torch.empty((x.shape[0], w3.shape[0]), dtype=x.dtype, device=x.device)
+
+
 @torch.library.custom_op(f"{NS}::dense_tower", mutates_args=(), device_types="cuda")
 def dense_tower(x: torch.Tensor, weights: List[torch.Tensor], weight_trans: List[bool], biases: List[Optional[torch.Tensor]],
                 act_names: str) -> torch.Tensor:
@@ -341,10 +379,15 @@ def dense_tower(x: torch.Tensor, weights: List[torch.Tensor], weight_trans: List
     M = x.shape[0]
     dims = [x.shape[1]] + [(w.shape[0] if t else w.shape[1]) for w, t in zip(weights, weight_trans)]
     if x.dtype != torch.float32:
-        # 16-bit towers: neighbouring layers that fit the two-layer kernel run as one launch each, the rest layer by layer
+        # 16-bit towers: runs of three or two neighbouring layers that fit the chained-layer kernel run as one launch
+        # each, the rest layer by layer
         y, i = x, 0
         while i < n:
-            if i + 1 < n and mlp2_eligible(M, dims[i], dims[i + 1], dims[i + 2], x.dtype, weight_trans[i], weight_trans[i + 1]):
+            if i + 2 < n and mlp3_eligible(M, dims[i], dims[i + 1], dims[i + 2], dims[i + 3], x.dtype, weight_trans[i:i + 3]):
+                y = mlp3(y, weights[i], biases[i], weights[i + 1], biases[i + 1], weights[i + 2], biases[i + 2],
+                         acts[i], acts[i + 1], acts[i + 2])
+                i += 3
+            elif i + 1 < n and mlp2_eligible(M, dims[i], dims[i + 1], dims[i + 2], x.dtype, weight_trans[i], weight_trans[i + 1]):
                 y = mlp2(y, weights[i], biases[i], weights[i + 1], biases[i + 1], acts[i], acts[i + 1])
                 i += 2
             else:
