@@ -15,6 +15,7 @@ What is recorded (inputs and outputs, all seeded, all small):
       - slice + cat graphs incl. the INT64_MAX / negative-end cases of tests/mlu/test_fuse_slice_cat.py:293-323,
       - multi-slice + stack, embedding + where + stack, RoPE and SwiGLU chains,
       - the three benchmark graphs at reduced size (encoder block, Llama-style layer, recsys graph).
+`python tests/golden/gen_golden.py v3` writes tests/golden/golden_v3.pt (16-bit towers of narrow dense layers);
 `python tests/golden/gen_golden.py v2` writes tests/golden/golden_v2.pt the same way: slice -> sum -> cat,
 mul -> sum -> cat and sum -> cat graphs (targets/mlu/fuse_sum_cat.py, fuse_mul_sum_cat.py), a chain of three dense
 layers, four parallel dense layers of one shape, and a bmm + bias + GELU graph.
@@ -230,8 +231,49 @@ def main_v2():
     print(f"wrote {out}: {len(G)} cases, {os.path.getsize(out) / 1024:.0f} KiB")
 
 
+def main_v3():
+    """Third fixture file: 16-bit towers of two and three narrow dense layers (the shapes the chained-layer kernel
+    takes), run through the reference pipeline like the others."""
+    G = {}
+    g = torch.Generator().manual_seed(8765)
+
+    def rn(*shape, dtype=torch.float32, std=1.0):
+        return (torch.randn(*shape, generator=g) * std).to(dtype)
+
+    for dt, tag in ((torch.bfloat16, "bf16"), (torch.float16, "f16")):
+        for name, M, dims, acts in (("two", 200, [72, 96, 40], ["relu", "none"]),
+                                    ("three", 150, [64, 128, 64, 24], ["gelu", "relu", "sigmoid"])):
+            x = rn(M, dims[0], dtype=dt)
+            ws = [rn(dims[i + 1], dims[i], dtype=dt, std=dims[i] ** -0.5) for i in range(len(dims) - 1)]
+            bs = [rn(dims[i + 1], dtype=dt, std=0.1) for i in range(len(dims) - 1)]
+            fns = {"relu": torch.relu, "gelu": F.gelu, "sigmoid": torch.sigmoid, "none": lambda t: t}
+
+            def tower(x, *wb, acts=acts, n=len(ws)):
+                h = x
+                for i in range(n):
+                    h = fns[acts[i]](F.linear(h, wb[i], wb[n + i]))
+                return h + 0
+
+            G[f"tower_{name}_{tag}"] = dict(x=x, ws=ws, bs=bs, acts=acts, y=run_ref(tower, x, *ws, *bs))
+
+    def compact(o):
+        if isinstance(o, torch.Tensor):
+            return o.detach().clone().contiguous()
+        if isinstance(o, dict):
+            return {k: compact(v) for k, v in o.items()}
+        if isinstance(o, (list, tuple)):
+            return type(o)(compact(v) for v in o)
+        return o
+
+    out = os.path.join(HERE, "golden_v3.pt")
+    torch.save(compact(G), out)
+    print(f"wrote {out}: {len(G)} cases, {os.path.getsize(out) / 1024:.0f} KiB")
+
+
 if __name__ == "__main__":
     if len(sys.argv) > 1 and sys.argv[1] == "v2":
         main_v2()
+    elif len(sys.argv) > 1 and sys.argv[1] == "v3":
+        main_v3()
     else:
         main()

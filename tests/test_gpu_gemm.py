@@ -290,6 +290,27 @@ def test_mlp3(cuda_device, M, dims, acts, dtype):
     assert_parity(got, y, f"mlp3 {M}x{dims} {acts} {dtype}")
 
 
+@pytest.mark.parametrize("tag", ["bf16", "f16"])
+@pytest.mark.parametrize("name", ["two", "three"])
+def test_mlp_against_reference_fixtures(cuda_device, name, tag):
+    """The chained-layer kernel (through DenseTowerModule, one launch) on the inputs of tests/golden/golden_v3.pt vs the
+    outputs the reference pipeline recorded for them."""
+    import os
+
+    from tests.helpers import LaunchCounter
+    from xpu_graph_b200 import lib
+    from xpu_graph_b200.modules import DenseTowerModule
+
+    c = torch.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "golden_v3.pt"))[f"tower_{name}_{tag}"]
+    dev = lambda t: t.to(cuda_device)
+    with LaunchCounter() as launches:
+        got = DenseTowerModule()(dev(c["x"]), [dev(w) for w in c["ws"]], [True] * len(c["ws"]), [dev(b) for b in c["bs"]], c["acts"])
+    torch.cuda.synchronize()
+    assert lib.tc_status() == 0
+    assert launches.names == ["xg_mlp2_bias_act" if name == "two" else "xg_mlp3_bias_act"], launches.names
+    assert_parity(got, c["y"], f"chained-layer kernel vs reference fixture ({name}, {tag})")
+
+
 def test_mlp2_strided_input_and_limits(cuda_device):
     """A row-strided x (a column slice of a wider tensor) is read in place; shapes outside the kernel's limits are
     refused with XG_ERR_UNSUPPORTED, and the tower op then runs the layers one by one."""

@@ -150,3 +150,19 @@ def test_dense_chains(G2):
         _close(ref_ops.dense(x, w, True, b, c["act"]), want, "combo dense member")
     c = G2["batch_dense_f32"]
     _close(ref_ops.batch_dense(c["x"], c["w"], False, c["b"], c["act"]), c["y"], "batch dense")
+
+
+GOLDEN3 = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "golden_v3.pt")
+
+
+@pytest.mark.parametrize("tag", ["bf16", "f16"])
+@pytest.mark.parametrize("name", ["two", "three"])
+def test_narrow_towers(name, tag):
+    """16-bit towers of two / three narrow dense layers as the reference pipeline computes them (golden_v3.pt): the
+    oracle's layer-by-layer chain reproduces them."""
+    c = torch.load(GOLDEN3)[f"tower_{name}_{tag}"]
+    y = c["x"]
+    for w, b, a in zip(c["ws"], c["bs"], c["acts"]):
+        y = ref_ops.dense(y, w, True, b, a)
+    _close(y, c["y"], f"tower {name} {tag}")
+
