@@ -36,7 +36,8 @@ constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
 constexpr int H_SLABS = MAX_N / BK;         // the hidden block as 64-column slabs of [128 rows x 128 bytes]
 constexpr int H_BYTES = H_SLABS * A_BYTES;  // 64 KiB
 constexpr int MLP_SMEM_BYTES = STAGES * STAGE_BYTES + H_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
-constexpr int EPI_WARPS = 8;                // two per TMEM lane quadrant: a single warp per scheduler is latency-bound
+constexpr int EPI_WARPS = 8;                // two per TMEM lane quadrant (a single warp per scheduler is latency-bound):
+                                            // warp part p of a quadrant takes the 32-column chunks q = p, p + 2, ...
 constexpr int MLP_THREADS = 64 + EPI_WARPS * 32;  // warp 0 TMA, warp 1 MMA, warps 2..9 epilogue
 constexpr int TMEM_COLS = 512;              // acc1 [0, 256), acc2 [256, 512)
 
@@ -104,9 +105,10 @@ mlp_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ C
     uint64_t* empty_bar = bars + STAGES;      // [STAGES]
     uint64_t* acc_full = bars + 2 * STAGES;   // [2] a product into this accumulator region has completed
     uint64_t* acc_empty = acc_full + 2;       // [2] the epilogue warps have read the region (one arrival per warp)
-    uint64_t* h_full = acc_full + 4;          // a hidden block is in shared memory (every epilogue thread arrives)
-    uint64_t* drain_bar = acc_full + 5;
-    uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(acc_full + 6);
+    uint64_t* h_full = acc_full + 4;          // [H_SLABS] a 64-column slab of a hidden block is in shared memory (every
+                                              // epilogue thread writes 32 columns of each slab and arrives once per slab)
+    uint64_t* drain_bar = h_full + H_SLABS;
+    uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(drain_bar + 1);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_base_slot + 1);
 
     const int warp = threadIdx.x >> 5;
@@ -121,7 +123,7 @@ mlp_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ C
             ptx::mbar_init(&acc_full[r], 1);
             ptx::mbar_init(&acc_empty[r], EPI_WARPS);
         }
-        ptx::mbar_init(h_full, EPI_WARPS * 32);
+        for (int c = 0; c < H_SLABS; ++c) ptx::mbar_init(&h_full[c], EPI_WARPS * 32);
         ptx::mbar_init(drain_bar, 1);
         *abort_flag = 0;
         ptx::fence_mbar_init();
@@ -184,7 +186,7 @@ mlp_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ C
             int stage = 0;
             uint32_t phase = 0;
             uint32_t uses0 = 0, uses1 = 0;  // products issued into each accumulator region so far
-            uint32_t hands = 0;         // hand-overs consumed so far
+            uint32_t hand_par = 0;      // bit c: parity of slab barrier c's next phase (hand-overs differ in their slab counts)
             bool ok = true;
             for (int mb = blockIdx.x; mb < p.num_m_blocks && ok; mb += gridDim.x) {
                 for (int l = 0; l < p.layers && ok; ++l) {
@@ -192,12 +194,14 @@ mlp_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ C
                     const uint32_t idesc = ptx::make_idesc_f16(fmt, BM, p.np[l], 0);
                     // the region's previous product has been read by the epilogue warps
                     if (!ptx::mbar_wait_bounded(&acc_empty[r], ((r ? uses1 : uses0) & 1u) ^ 1u, abort_flag)) { ok = false; break; }
-                    if (l > 0) {  // the previous layer's result is in shared memory
-                        if (!ptx::mbar_wait_bounded(h_full, hands & 1u, abort_flag)) { ok = false; break; }
-                        ++hands;
-                    }
                     ptx::tc_fence_after();
                     for (int kb = 0; kb < p.nk[l]; ++kb) {
+                        // slab kb of the previous layer's result is in shared memory (the slabs arrive in order, so the
+                        // product starts while the later ones are still being written)
+                        if (l > 0) {
+                            if (!ptx::mbar_wait_bounded(&h_full[kb], (hand_par >> kb) & 1u, abort_flag)) { ok = false; break; }
+                            hand_par ^= 1u << kb;
+                        }
                         if (!ptx::mbar_wait_bounded(&full_bar[stage], phase, abort_flag)) { ok = false; break; }
                         ptx::tc_fence_after();
                         const uint64_t da = ptx::make_kmajor_sw128_desc(l == 0 ? ptx::smem_u32(smem_a + stage * A_BYTES)
@@ -275,11 +279,11 @@ mlp_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ C
                             const int piece = (q & 1) * 4 + t4;  // 16-byte piece of this row's 128-byte segment
                             ptx::st_shared_v4(slab + (uint32_t)((piece ^ (r_in_blk & 7)) << 4), make_uint4(w[0], w[1], w[2], w[3]));
                         }
+                        // this thread's part of slab q / 2 must be visible to the tensor core's (async proxy) reads
+                        ptx::fence_proxy_async();
+                        ptx::mbar_arrive(&h_full[q >> 1]);
                     }
-                    // the writes above must be visible to the tensor core's (async proxy) reads of shared memory
-                    ptx::fence_proxy_async();
                     ptx::tc_fence_before();
-                    ptx::mbar_arrive(h_full);
                 } else {
                     // ---- output block: acc -> + bias, act -> out ----
                     const int64_t row = (int64_t)mb * BM + r_in_blk;
