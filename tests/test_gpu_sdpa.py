@@ -132,6 +132,32 @@ def test_simt_fp32_encoder_shape(cuda_device, causal):
     assert_parity(got, want, "sdpa fp32")
 
 
+@pytest.mark.parametrize("causal", [False, True])
+@pytest.mark.parametrize("B,H,Sq,Skv,D", [(2, 3, 77, 91, 64), (1, 2, 300, 300, 32), (1, 2, 130, 517, 128), (2, 2, 16, 1, 64),
+                                          (1, 1, 1, 260, 64)])
+def test_tiled_fp32(cuda_device, B, H, Sq, Skv, D, causal):
+    """fp32 attention without a mask at head dims 32 / 64 / 128 runs on the shared-memory tiled kernel: ragged row and
+    key counts, several key chunks, rows that see a single key."""
+    q, k, v = _qkv(B, H, Sq, Skv, D, torch.float32, 37)
+    got = _run(cuda_device, q, k, v, None, None, causal)
+    want = ref_ops.sdpa_math(q.double(), k.double(), v.double(), None, None, causal).float()
+    assert_parity(got, want, f"sdpa fp32 tiled {B}x{H}x{Sq}x{Skv}x{D} causal={causal}")
+
+
+def test_tiled_fp32_strided_views_and_mask_fallback(cuda_device):
+    """q / k / v as transposed views of [B, S, H, D] buffers go through the tiled kernel in place; with an additive mask
+    the same shape runs on the row-per-warp kernel. Both against fp64 math."""
+    B, H, S, D = 2, 4, 100, 64
+    g = torch.Generator().manual_seed(38)
+    qb, kb, vb = (torch.randn(B, S, H, D, generator=g) for _ in range(3))
+    q, k, v = qb.transpose(1, 2), kb.transpose(1, 2), vb.transpose(1, 2)
+    got = _run(cuda_device, q, k, v, None, None, True)
+    assert_parity(got, ref_ops.sdpa_math(q.double(), k.double(), v.double(), None, None, True).float(), "sdpa fp32 tiled, strided views")
+    mask = torch.randn(S, S, generator=g)
+    got = _run(cuda_device, q, k, v, mask, None, False)
+    assert_parity(got, ref_ops.sdpa_math(q.double(), k.double(), v.double(), mask.double(), None, False).float(), "sdpa fp32 with mask")
+
+
 def test_simt_other_head_dims(cuda_device):
     q, k, v = _qkv(2, 2, 77, 91, 96, torch.bfloat16, 35)
     g = torch.Generator().manual_seed(36)

@@ -9,7 +9,8 @@
 //   packed 16-bit pairs over the first half of the same score buffer, so a block's softmax never waits
 //   for the previous block's P V. O accumulates in TMEM and is rescaled lazily.
 //   Causal tiles beyond the diagonal are skipped.
-// Everything else (fp32, other head dims) runs a warp-per-query SIMT kernel in true fp32.
+// Everything else runs in true fp32 on SIMT kernels: a shared-memory tiled kernel (head dim 32 / 64 / 128, no additive
+// mask) and a warp-per-query kernel (masks, other head dims).
 #include "common.cuh"
 #include "sm100_ptx.cuh"
 
@@ -703,6 +704,173 @@ __global__ void __launch_bounds__(kSimtWarps * 32) sdpa_simt_kernel(const SdpaPa
     }
 }
 
+// ---------------------------------------------------------------------------------------
+// Tiled SIMT kernel: true fp32 arithmetic for head dims 32 / 64 / 128 without an additive mask (the encoder block's
+// attention). A CTA owns 16 query rows of one (batch, head): 4 warps x 4 rows. Keys and values pass through shared
+// memory in chunks of 128 (each element is read from global memory once per CTA, coalesced, instead of once per query
+// row): lane t holds the scores of keys t, t + 32, t + 64, t + 96 for the warp's four rows (64 FMAs per eight 16-byte
+// shared-memory loads), the probabilities go back through shared memory, and lane t accumulates output columns t,
+// t + 32, ... Online softmax across chunks; a warp reduction per row and chunk.
+// ---------------------------------------------------------------------------------------
+constexpr int kTileQ = 16;
+constexpr int kTileK = 128;
+constexpr int kTileThreads = 128;
+
+template <int D>
+struct TileCfg {
+    static constexpr int KS = D + 4;  // key row stride in floats: an odd multiple of 16 bytes, so that the 16-byte loads of
+                                      // eight lanes (eight different keys) fall into 32 different banks
+    static constexpr int SMEM_BYTES = (kTileK * KS + kTileK * D + kTileQ * D + kTileQ * kTileK) * 4;
+};
+
+template <typename T, int D>
+__global__ void __launch_bounds__(kTileThreads) sdpa_tile_kernel(const SdpaParams p) {
+    using Cfg = TileCfg<D>;
+    constexpr int KS = Cfg::KS;
+    constexpr int NU = D / 32;  // output columns per lane
+    extern __shared__ __align__(16) float tile_smem[];
+    float* Ks = tile_smem;             // [kTileK][KS]
+    float* Vs = Ks + kTileK * KS;      // [kTileK][D]
+    float* Qs = Vs + kTileK * D;       // [kTileQ][D], pre-multiplied by the scale
+    float* Ps = Qs + kTileQ * D;       // [kTileQ][kTileK]
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int64_t bh = blockIdx.y;
+    const int64_t h = bh % p.H, b = bh / p.H;
+    const int q0 = (int)blockIdx.x * kTileQ;
+    const int Sq = (int)p.Sq, Skv = (int)p.Skv;
+    const T* qbase = reinterpret_cast<const T*>(p.q) + b * p.q_sb + h * p.q_sh;
+    const T* kbase = reinterpret_cast<const T*>(p.k) + b * p.k_sb + h * p.k_sh;
+    const T* vbase = reinterpret_cast<const T*>(p.v) + b * p.v_sb + h * p.v_sh;
+
+    for (int idx = threadIdx.x; idx < kTileQ * D; idx += kTileThreads) {
+        const int r = idx / D, d = idx - r * D;
+        Qs[idx] = (q0 + r < Sq) ? Cvt<T>::to_f(qbase[(int64_t)(q0 + r) * p.q_ss + d]) * p.scale : 0.f;
+    }
+    int kv_end = Skv;  // keys any row of this CTA can see
+    if (p.causal && q0 + kTileQ < kv_end) kv_end = q0 + kTileQ;
+
+    const int row0 = q0 + warp * 4;
+    float o[4][NU];
+    float m_run[4], l_run[4];
+#pragma unroll
+    for (int r = 0; r < 4; ++r) {
+        m_run[r] = -INFINITY;
+        l_run[r] = 0.f;
+#pragma unroll
+        for (int u = 0; u < NU; ++u) o[r][u] = 0.f;
+    }
+    const float* qw = Qs + warp * 4 * D;
+    float* pw = Ps + warp * 4 * kTileK;
+
+    for (int k0 = 0; k0 < kv_end; k0 += kTileK) {
+        __syncthreads();  // the previous chunk has been consumed (first time: Qs is complete)
+        // this chunk's keys and values (zeros beyond the last visible key), coalesced along the head dim
+#pragma unroll 4
+        for (int idx = threadIdx.x; idx < kTileK * D; idx += kTileThreads) {
+            const int key = idx / D, d = idx - key * D;
+            const bool in = k0 + key < kv_end;
+            Ks[key * KS + d] = in ? Cvt<T>::to_f(kbase[(int64_t)(k0 + key) * p.k_ss + d]) : 0.f;
+            Vs[idx] = in ? Cvt<T>::to_f(vbase[(int64_t)(k0 + key) * p.v_ss + d]) : 0.f;
+        }
+        __syncthreads();
+        // scores of keys k0 + lane + 32 i for the warp's four rows
+        float sc[4][4];
+#pragma unroll
+        for (int r = 0; r < 4; ++r)
+#pragma unroll
+            for (int i = 0; i < 4; ++i) sc[r][i] = 0.f;
+#pragma unroll 4
+        for (int d = 0; d < D; d += 4) {
+            float4 qv[4];
+#pragma unroll
+            for (int r = 0; r < 4; ++r) qv[r] = *reinterpret_cast<const float4*>(qw + r * D + d);  // same address in every lane
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const float4 kv = *reinterpret_cast<const float4*>(Ks + (lane + 32 * i) * KS + d);
+#pragma unroll
+                for (int r = 0; r < 4; ++r)
+                    sc[r][i] = fmaf(qv[r].x, kv.x, fmaf(qv[r].y, kv.y, fmaf(qv[r].z, kv.z, fmaf(qv[r].w, kv.w, sc[r][i]))));
+            }
+        }
+        // online softmax per row; the probabilities go to shared memory for the second product
+#pragma unroll
+        for (int r = 0; r < 4; ++r) {
+            const int row = row0 + r;
+            float mx = -INFINITY;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const int key = k0 + lane + 32 * i;
+                if (key >= Skv || (p.causal && key > row)) sc[r][i] = -INFINITY;
+                mx = fmaxf(mx, sc[r][i]);
+            }
+            const float m_new = fmaxf(m_run[r], warp_max(mx));
+            const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
+            const float alpha = expf(m_run[r] - m_use);
+            float part = 0.f;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const float pj = expf(sc[r][i] - m_use);
+                part += pj;
+                pw[r * kTileK + lane + 32 * i] = pj;
+            }
+            l_run[r] = l_run[r] * alpha + warp_sum(part);
+            m_run[r] = m_new;
+#pragma unroll
+            for (int u = 0; u < NU; ++u) o[r][u] *= alpha;
+        }
+        __syncwarp();
+        // o += P V: four keys per step (the probabilities of a row as one 16-byte load, the same in every lane)
+        int cnt = kv_end - k0;
+        if (cnt > kTileK) cnt = kTileK;
+        for (int k = 0; k < cnt; k += 4) {
+            float4 pv[4];
+#pragma unroll
+            for (int r = 0; r < 4; ++r) pv[r] = *reinterpret_cast<const float4*>(pw + r * kTileK + k);
+#pragma unroll
+            for (int u = 0; u < NU; ++u) {
+                const float v0 = Vs[(k + 0) * D + lane + 32 * u], v1 = Vs[(k + 1) * D + lane + 32 * u];
+                const float v2 = Vs[(k + 2) * D + lane + 32 * u], v3 = Vs[(k + 3) * D + lane + 32 * u];
+#pragma unroll
+                for (int r = 0; r < 4; ++r)
+                    o[r][u] = fmaf(pv[r].x, v0, fmaf(pv[r].y, v1, fmaf(pv[r].z, v2, fmaf(pv[r].w, v3, o[r][u]))));
+            }
+        }
+    }
+    T* obase = reinterpret_cast<T*>(p.out) + b * p.o_sb + h * p.o_sh;
+#pragma unroll
+    for (int r = 0; r < 4; ++r) {
+        if (row0 + r >= Sq) continue;
+        const float inv_l = 1.0f / l_run[r];
+#pragma unroll
+        for (int u = 0; u < NU; ++u) obase[(int64_t)(row0 + r) * p.o_ss + lane + 32 * u] = Cvt<T>::from_f(o[r][u] * inv_l);
+    }
+}
+
+template <typename T, int D>
+int launch_tile(const SdpaParams& p, cudaStream_t st) {
+    using Cfg = TileCfg<D>;
+    auto kern = sdpa_tile_kernel<T, D>;
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
+    if (e != cudaSuccess) {
+        cudaGetLastError();
+        return fail(XG_ERR_LAUNCH, "xg_sdpa_fwd: cannot reserve shared memory: %s", cudaGetErrorString(e));
+    }
+    const int64_t qt = (p.Sq + kTileQ - 1) / kTileQ, bh = p.B * p.H;
+    if (qt > 0x7fffffffLL || bh > 65535) return -1;  // the caller falls back to the row-per-warp kernel
+    kern<<<dim3((unsigned)qt, (unsigned)bh), kTileThreads, Cfg::SMEM_BYTES, st>>>(p);
+    return check_launch("xg_sdpa_fwd");
+}
+
+template <typename T>
+int launch_tile_any(const SdpaParams& p, cudaStream_t st) {
+    switch ((int)p.D) {
+        case 32: return launch_tile<T, 32>(p, st);
+        case 64: return launch_tile<T, 64>(p, st);
+        case 128: return launch_tile<T, 128>(p, st);
+        default: return -1;
+    }
+}
+
 template <typename T>
 int launch_simt(const SdpaParams& p, cudaStream_t st) {
     const int64_t rows = p.B * p.H * p.Sq;
@@ -766,6 +934,15 @@ extern "C" int xg_sdpa_fwd(const void* q, const void* k, const void* v, const vo
     if (tc) {
         if (dtype == XG_BF16) return D == 128 ? launch_flash_tc<__nv_bfloat16, 128>(p, st) : launch_flash_tc<__nv_bfloat16, 64>(p, st);
         return D == 128 ? launch_flash_tc<__half, 128>(p, st) : launch_flash_tc<__half, 64>(p, st);
+    }
+    if (mask == nullptr && Sq < 0x7fffff00LL && Skv < 0x7fffff00LL) {  // -1: not a shape the tiled kernel takes
+        int rc = -1;
+        switch (dtype) {
+            case XG_F32: rc = launch_tile_any<float>(p, st); break;
+            case XG_BF16: rc = launch_tile_any<__nv_bfloat16>(p, st); break;
+            default: rc = launch_tile_any<__half>(p, st); break;
+        }
+        if (rc != -1) return rc;
     }
     switch (dtype) {
         case XG_F32: return launch_simt<float>(p, st);
