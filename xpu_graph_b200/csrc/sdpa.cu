@@ -746,6 +746,8 @@ __global__ void __launch_bounds__(kTileThreads) sdpa_tile_kernel(const SdpaParam
         const int r = idx / D, d = idx - r * D;
         Qs[idx] = (q0 + r < Sq) ? Cvt<T>::to_f(qbase[(int64_t)(q0 + r) * p.q_ss + d]) * p.scale : 0.f;
     }
+    const bool vec_ok = ((reinterpret_cast<uintptr_t>(kbase) | reinterpret_cast<uintptr_t>(vbase)) & 15u) == 0 &&
+                        p.k_ss % (16 / (int)sizeof(T)) == 0 && p.v_ss % (16 / (int)sizeof(T)) == 0;
     int kv_end = Skv;  // keys any row of this CTA can see
     if (p.causal && q0 + kTileQ < kv_end) kv_end = q0 + kTileQ;
 
@@ -764,13 +766,38 @@ __global__ void __launch_bounds__(kTileThreads) sdpa_tile_kernel(const SdpaParam
 
     for (int k0 = 0; k0 < kv_end; k0 += kTileK) {
         __syncthreads();  // the previous chunk has been consumed (first time: Qs is complete)
-        // this chunk's keys and values (zeros beyond the last visible key), coalesced along the head dim
+        // this chunk's keys and values (zeros beyond the last visible key), coalesced along the head dim; 16-byte loads
+        // where the rows allow them, many of them in flight per thread (the chunk is a single round trip to L2)
+        if (vec_ok) {
+            constexpr int EV = 16 / (int)sizeof(T);  // elements per 16-byte load
+            constexpr int VPR = D / EV;              // loads per row
+#pragma unroll 8
+            for (int idx = threadIdx.x; idx < kTileK * VPR; idx += kTileThreads) {
+                const int key = idx / VPR, d = (idx - key * VPR) * EV;
+                Vec16<T> kv, vv;
+                if (k0 + key < kv_end) {
+                    kv = ld16(kbase + (int64_t)(k0 + key) * p.k_ss + d);
+                    vv = ld16(vbase + (int64_t)(k0 + key) * p.v_ss + d);
+                } else {
+#pragma unroll
+                    for (int e = 0; e < EV; ++e) kv.v[e] = vv.v[e] = Cvt<T>::from_f(0.f);
+                }
+#pragma unroll
+                for (int e = 0; e < EV; e += 4) {
+                    *reinterpret_cast<float4*>(Ks + key * KS + d + e) = make_float4(Cvt<T>::to_f(kv.v[e]), Cvt<T>::to_f(kv.v[e + 1]),
+                                                                                    Cvt<T>::to_f(kv.v[e + 2]), Cvt<T>::to_f(kv.v[e + 3]));
+                    *reinterpret_cast<float4*>(Vs + key * D + d + e) = make_float4(Cvt<T>::to_f(vv.v[e]), Cvt<T>::to_f(vv.v[e + 1]),
+                                                                                   Cvt<T>::to_f(vv.v[e + 2]), Cvt<T>::to_f(vv.v[e + 3]));
+                }
+            }
+        } else {
 #pragma unroll 4
-        for (int idx = threadIdx.x; idx < kTileK * D; idx += kTileThreads) {
-            const int key = idx / D, d = idx - key * D;
-            const bool in = k0 + key < kv_end;
-            Ks[key * KS + d] = in ? Cvt<T>::to_f(kbase[(int64_t)(k0 + key) * p.k_ss + d]) : 0.f;
-            Vs[idx] = in ? Cvt<T>::to_f(vbase[(int64_t)(k0 + key) * p.v_ss + d]) : 0.f;
+            for (int idx = threadIdx.x; idx < kTileK * D; idx += kTileThreads) {
+                const int key = idx / D, d = idx - key * D;
+                const bool in = k0 + key < kv_end;
+                Ks[key * KS + d] = in ? Cvt<T>::to_f(kbase[(int64_t)(k0 + key) * p.k_ss + d]) : 0.f;
+                Vs[idx] = in ? Cvt<T>::to_f(vbase[(int64_t)(k0 + key) * p.v_ss + d]) : 0.f;
+            }
         }
         __syncthreads();
         // scores of keys k0 + lane + 32 i for the warp's four rows
