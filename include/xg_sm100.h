@@ -213,7 +213,9 @@ int xg_bgemm_bias_act(const void* A, const void* B, const void* bias, const void
 
 /*
  * Two or three chained dense layers in one kernel: out = act2( act1( x @ W1^T + b1 ) @ W2^T + b2 ) (and a third layer
- * on top for xg_mlp3_bias_act), x [M, K1], W1 [N1, K1], W2 [N2, N1], W3 [N3, N2] (weights as nn.Linear stores them),
+ * on top for xg_mlp3_bias_act), x [M, K1], W1 [N1, K1], W2 [N2, N1], W3 [N3, N2] as nn.Linear stores them, or - for
+ * every layer l whose bit (1 << l) is set in weights_kn - as [K, N] (the operand of torch.matmul(x, W), the form of the
+ * reference's own test, tests/mlu/test_fuse_densetower.py:18-35; such a weight's N must be a multiple of 8);
  * out [M, N_last]; row strides in elements; biases nullable. The hidden activations stay on chip: each is rounded to
  * the 16-bit dtype (as the unfused graph rounds it when it stores the tensor) and handed to the next product through
  * shared memory. 16-bit dtypes only; xg_mlp2_supported / xg_mlp3_supported say whether a shape fits (K1 % 8 == 0, every
@@ -228,11 +230,11 @@ int xg_mlp2_supported(int64_t M, int64_t K1, int64_t N1, int64_t N2, int dtype);
 int xg_mlp3_supported(int64_t M, int64_t K1, int64_t N1, int64_t N2, int64_t N3, int dtype);
 int xg_mlp2_bias_act(const void* x, const void* w1, const void* b1, const void* w2, const void* b2, void* out, int64_t M,
                      int64_t K1, int64_t N1, int64_t N2, int64_t lda, int64_t ldw1, int64_t ldw2, int64_t ldc, int act1,
-                     int act2, int dtype, void* stream);
+                     int act2, int weights_kn, int dtype, void* stream);
 int xg_mlp3_bias_act(const void* x, const void* w1, const void* b1, const void* w2, const void* b2, const void* w3,
                      const void* b3, void* out, int64_t M, int64_t K1, int64_t N1, int64_t N2, int64_t N3, int64_t lda,
-                     int64_t ldw1, int64_t ldw2, int64_t ldw3, int64_t ldc, int act1, int act2, int act3, int dtype,
-                     void* stream);
+                     int64_t ldw1, int64_t ldw2, int64_t ldw3, int64_t ldc, int act1, int act2, int act3, int weights_kn,
+                     int dtype, void* stream);
 
 /*
  * Grouped form: out[e] = act( A[e] @ W[e] + bias[e] ) for `count` problems of one shape [M, N, K] whose operands lie

@@ -106,9 +106,14 @@ def register():
         return y
 
     k(ops.dense_tower)(dense_tower)
-    k(ops.mlp3)(lambda x, w1, b1, w2, b2, w3, b3, a1, a2, a3: dense(dense(dense(x, w1, True, b1, None, a1), w2, True, b2, None, a2),
-                                                                   w3, True, b3, None, a3))
-    k(ops.mlp2)(lambda x, w1, b1, w2, b2, act1, act2: dense(dense(x, w1, True, b1, None, act1), w2, True, b2, None, act2))
+    def mlp_chain(x, ws, bs, acts, weights_kn):
+        y = x
+        for l, (w, b, a) in enumerate(zip(ws, bs, acts)):
+            y = dense(y, w, not ((weights_kn >> l) & 1), b, None, a)
+        return y
+
+    k(ops.mlp3)(lambda x, w1, b1, w2, b2, w3, b3, a1, a2, a3, weights_kn=0: mlp_chain(x, (w1, w2, w3), (b1, b2, b3), (a1, a2, a3), weights_kn))
+    k(ops.mlp2)(lambda x, w1, b1, w2, b2, a1, a2, weights_kn=0: mlp_chain(x, (w1, w2), (b1, b2), (a1, a2), weights_kn))
 
     def combo_dense(inputs, weights, weight_trans, biases, act):
         return torch.stack([dense(x, w, weight_trans, b, None, act) for x, w, b in zip(inputs, weights, biases)])

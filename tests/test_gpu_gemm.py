@@ -311,6 +311,34 @@ def test_mlp_against_reference_fixtures(cuda_device, name, tag):
     assert_parity(got, c["y"], f"chained-layer kernel vs reference fixture ({name}, {tag})")
 
 
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_mlp_kn_weights(cuda_device, dtype):
+    """Weights stored [K, N] (the operand of torch.matmul(x, W), the form of the reference's dense-tower test) are
+    consumed MN-major as TMA leaves them: all layers [K, N], and a mix of both layouts."""
+    from xpu_graph_b200 import lib, ops  # noqa: F401
+
+    g = torch.Generator().manual_seed(44)
+    M, dims = 1500, [200, 256, 104, 48]
+    x = torch.randn(M, dims[0], generator=g).to(dtype)
+    ws_nk = [(torch.randn(dims[i + 1], dims[i], generator=g) * dims[i] ** -0.5).to(dtype) for i in range(3)]
+    bs = [(0.1 * torch.randn(dims[i + 1], generator=g)).to(dtype) for i in range(3)]
+    acts = ("relu", "gelu", "none")
+    dev = lambda t: t.to(cuda_device)
+    f = lambda t: t.float()
+    y = x
+    for w, b, a in zip(ws_nk, bs, acts):
+        y = ref_ops.dense(f(y), f(w), True, f(b), a).to(dtype)
+    for mask in (0b111, 0b101, 0b010):
+        ws = [w.t().contiguous() if (mask >> l) & 1 else w for l, w in enumerate(ws_nk)]
+        got = torch.ops.xg_sm100.mlp3(dev(x), dev(ws[0]), dev(bs[0]), dev(ws[1]), dev(bs[1]), dev(ws[2]), dev(bs[2]), *acts, mask)
+        torch.cuda.synchronize()
+        assert lib.tc_status() == 0
+        assert_parity(got, y, f"mlp3 with weight layout mask {mask:03b} {dtype}")
+    y2 = ref_ops.dense(ref_ops.dense(f(x), f(ws_nk[0]), True, f(bs[0]), "silu").to(dtype).float(), f(ws_nk[1]), True, None, "none").to(dtype)
+    got = torch.ops.xg_sm100.mlp2(dev(x), dev(ws_nk[0].t().contiguous()), dev(bs[0]), dev(ws_nk[1].t().contiguous()), None, "silu", "none", 3)
+    assert_parity(got, y2, f"mlp2 with [K, N] weights {dtype}")
+
+
 def test_mlp2_strided_input_and_limits(cuda_device):
     """A row-strided x (a column slice of a wider tensor) is read in place; shapes outside the kernel's limits are
     refused with XG_ERR_UNSUPPORTED, and the tower op then runs the layers one by one."""

@@ -510,6 +510,30 @@ def test_dense_tower_16bit_pairs(tgt, xlog):
     assert "xg_dense_tower" not in mods
 
 
+def test_dense_tower_matmul_form(tgt, xlog):
+    """The graph of the reference's own dense-tower test (tests/mlu/test_fuse_densetower.py:18-35): fp16
+    matmul(x, W) + bias (+ relu) three times with weights stored [K, N]. With widths the chained-layer kernel can take
+    it becomes one DenseTowerModule call; with the reference's exact sizes (20 -> 32 -> 16 -> 1: a 40-byte row stride
+    and a one-column [K, N] weight, neither of which a TMA descriptor can address) the result still matches eager."""
+    import torch.nn.functional as F
+
+    def fn0(x, w1, w2, w3, b1, b2, b3):
+        out = F.relu(torch.matmul(x, w1) + b1)
+        out = F.relu(torch.matmul(out, w2) + b2)
+        return torch.matmul(out, w3) + b3
+
+    g = torch.Generator().manual_seed(11)
+    for sizes, fused in (((24, 32, 16, 8), True), ((20, 32, 16, 1), False)):
+        x = torch.randn(16, sizes[0], generator=g).to(torch.float16)
+        ws = [(torch.randn(sizes[i], sizes[i + 1], generator=g) * sizes[i] ** -0.5).to(torch.float16) for i in range(3)]
+        bs = [torch.randn(sizes[i + 1], generator=g).to(torch.float16) for i in range(3)]
+        want, got, mods, atens = _compile(tgt, fn0, x, *ws, *bs)
+        _same(got, want, 2e-2)
+        if fused:
+            assert mods == ["xg_dense_tower"], mods
+        torch._dynamo.reset()
+
+
 def test_combo_dense(tgt, xlog):
     """Five parallel bf16 Linear+ReLU layers of one shape over different inputs -> one ComboDenseModule call;
     three of them are too few (the reference's width of 4) and stay separate."""

@@ -53,7 +53,8 @@ struct MlpParams {
     int np[MAX_LAYERS];          // MMA N of each product: the width rounded up to 16
     int nk[MAX_LAYERS];          // 64-column k-blocks of each product (over K1 for layer 1, over N_{l-1} after)
     int act[MAX_LAYERS];
-    int bias_vec_ok[MAX_LAYERS];
+    int bias_vec_ok;             // bit l: bias l allows 16-byte loads
+    int w_kn;                    // bit l: weight l is stored [K, N] (consumed MN-major) instead of [N, K]
     int out_vec_ok;              // out and ldc allow 16-byte stores
 };
 static_assert(sizeof(MlpParams) <= 128, "the scalar parameters stay within 128 bytes beside the tensor maps");
@@ -149,7 +150,11 @@ mlp_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ C
             for (int mb = blockIdx.x; mb < p.num_m_blocks && ok; mb += gridDim.x) {
                 for (int l = 0; l < p.layers && ok; ++l) {
                     const CUtensorMap* tw = l == 0 ? &tmap_w1 : (l == 1 ? &tmap_w2 : &tmap_w3);
-                    const uint32_t w_bytes = (uint32_t)p.np[l] * BK * 2;
+                    // [N, K] weights: one box of np rows x 64 k-columns. [K, N] weights: boxes of 64 k-rows x 64 n-columns,
+                    // one per 64 output columns, which the MMA consumes MN-major exactly as TMA leaves them.
+                    const bool kn = (p.w_kn >> l) & 1;
+                    const int n_boxes = (p.np[l] + 63) / 64;
+                    const uint32_t w_bytes = kn ? (uint32_t)n_boxes * (BK * 128) : (uint32_t)p.np[l] * BK * 2;
                     for (int kb = 0; kb < p.nk[l]; ++kb) {
                         if (!ptx::mbar_wait_bounded(&empty_bar[stage], phase ^ 1u, abort_flag)) { ok = false; break; }
                         if (l == 0) {
@@ -158,7 +163,12 @@ mlp_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ C
                         } else {
                             ptx::mbar_arrive_expect_tx(&full_bar[stage], w_bytes);
                         }
-                        ptx::tma_load_2d(smem_b + stage * B_BYTES, tw, &full_bar[stage], kb * BK, 0);
+                        if (kn) {
+                            for (int jn = 0; jn < n_boxes; ++jn)
+                                ptx::tma_load_2d(smem_b + stage * B_BYTES + jn * (BK * 128), tw, &full_bar[stage], jn * 64, kb * BK);
+                        } else {
+                            ptx::tma_load_2d(smem_b + stage * B_BYTES, tw, &full_bar[stage], kb * BK, 0);
+                        }
                         armed |= 1u << stage;
                         armed_phase = (armed_phase & ~(1u << stage)) | (phase << stage);
                         if (++stage == STAGES) { stage = 0; phase ^= 1u; }
@@ -191,7 +201,8 @@ mlp_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ C
             for (int mb = blockIdx.x; mb < p.num_m_blocks && ok; mb += gridDim.x) {
                 for (int l = 0; l < p.layers && ok; ++l) {
                     const int r = l & 1;
-                    const uint32_t idesc = ptx::make_idesc_f16(fmt, BM, p.np[l], 0);
+                    const bool kn = (p.w_kn >> l) & 1;
+                    const uint32_t idesc = ptx::make_idesc_f16(fmt, BM, p.np[l], kn ? 1 : 0);
                     // the region's previous product has been read by the epilogue warps
                     if (!ptx::mbar_wait_bounded(&acc_empty[r], ((r ? uses1 : uses0) & 1u) ^ 1u, abort_flag)) { ok = false; break; }
                     ptx::tc_fence_after();
@@ -206,11 +217,13 @@ mlp_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ C
                         ptx::tc_fence_after();
                         const uint64_t da = ptx::make_kmajor_sw128_desc(l == 0 ? ptx::smem_u32(smem_a + stage * A_BYTES)
                                                                                 : h_addr + (uint32_t)(kb * A_BYTES));
-                        const uint64_t db = ptx::make_kmajor_sw128_desc(ptx::smem_u32(smem_b + stage * B_BYTES));
+                        const uint32_t b_addr = ptx::smem_u32(smem_b + stage * B_BYTES);
+                        const uint64_t db = kn ? ptx::make_mnmajor_sw128_desc(b_addr, BK * 128) : ptx::make_kmajor_sw128_desc(b_addr);
 #pragma unroll
-                        for (int k = 0; k < BK / 16; ++k)  // +32 bytes per 16-element K step, in the descriptor's 16-byte units
-                            ptx::mma_f16_ss(tmem_base + (uint32_t)(r * MAX_N), da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc,
-                                            (kb | k) != 0 ? 1u : 0u);
+                        for (int k = 0; k < BK / 16; ++k)  // per 16-element K step: K-major +32 bytes, MN-major +16 rows of 128
+                                                           // bytes (both in the descriptor's 16-byte units)
+                            ptx::mma_f16_ss(tmem_base + (uint32_t)(r * MAX_N), da + (uint64_t)(k * 2), db + (uint64_t)(kn ? k * 128 : k * 2),
+                                            idesc, (kb | k) != 0 ? 1u : 0u);
                         ptx::tc_commit(&empty_bar[stage]);
                         if (++stage == STAGES) { stage = 0; phase ^= 1u; }
                     }
@@ -260,7 +273,7 @@ mlp_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ C
                             ptx::tmem_ld_wait();
 #pragma unroll
                             for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(raw[i]);
-                            finish_chunk<T>(v, bias, p.bias_vec_ok[l] != 0, col0, p.N[l], p.act[l]);
+                            finish_chunk<T>(v, bias, ((p.bias_vec_ok >> l) & 1) != 0, col0, p.N[l], p.act[l]);
                             if (col0 + 32 > p.N[l]) {  // columns beyond the layer's width: zeros, whatever act(0) is
 #pragma unroll
                                 for (int i = 0; i < 32; ++i)
@@ -295,7 +308,7 @@ mlp_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ C
                         float v[32];
 #pragma unroll
                         for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(raw[i]);
-                        finish_chunk<T>(v, bias, p.bias_vec_ok[l] != 0, col0, p.N[l], p.act[l]);
+                        finish_chunk<T>(v, bias, ((p.bias_vec_ok >> l) & 1) != 0, col0, p.N[l], p.act[l]);
                         if (!row_ok) continue;
                         T* orow = out + row * p.ldc + col0;
                         if (col0 + 32 <= p.N[l] && p.out_vec_ok) {
@@ -333,7 +346,8 @@ mlp_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ C
 
 template <typename T>
 int launch_mlp(const char* who, const void* x, int layers, const void* const* w, const void* const* b, void* out, int64_t M,
-               int64_t K1, const int64_t* N, int64_t lda, const int64_t* ldw, int64_t ldc, const int* act, cudaStream_t st) {
+               int64_t K1, const int64_t* N, int64_t lda, const int64_t* ldw, int64_t ldc, const int* act, int weights_kn,
+               cudaStream_t st) {
     constexpr bool is_bf16 = std::is_same<T, __nv_bfloat16>::value;
     MlpParams p;
     p.out = out;
@@ -342,6 +356,8 @@ int launch_mlp(const char* who, const void* x, int layers, const void* const* w,
     p.layers = layers;
     p.num_m_blocks = (int)((M + BM - 1) / BM);
     p.out_vec_ok = (aligned16(out) && ldc % 8 == 0) ? 1 : 0;
+    p.bias_vec_ok = 0;
+    p.w_kn = 0;
     CUtensorMap tx, tw[MAX_LAYERS];
     bool maps_ok = make_tmap_2d_16bit(&tx, x, (uint64_t)M, (uint64_t)K1, (uint64_t)lda, BM, BK, is_bf16);
     for (int l = 0; l < MAX_LAYERS; ++l) {
@@ -352,8 +368,13 @@ int launch_mlp(const char* who, const void* x, int layers, const void* const* w,
         p.np[l] = (int)((N[s] + 15) / 16 * 16);
         p.nk[l] = (int)((k + BK - 1) / BK);
         p.act[l] = act[s];
-        p.bias_vec_ok[l] = (b[s] != nullptr && aligned16(b[s])) ? 1 : 0;
-        maps_ok = maps_ok && make_tmap_2d_16bit(&tw[l], w[s], (uint64_t)N[s], (uint64_t)k, (uint64_t)ldw[s], (uint32_t)p.np[l], BK, is_bf16);
+        if (b[s] != nullptr && aligned16(b[s])) p.bias_vec_ok |= 1 << l;
+        if ((weights_kn >> s) & 1) {
+            p.w_kn |= 1 << l;
+            maps_ok = maps_ok && make_tmap_2d_16bit(&tw[l], w[s], (uint64_t)k, (uint64_t)N[s], (uint64_t)ldw[s], BK, 64, is_bf16);
+        } else {
+            maps_ok = maps_ok && make_tmap_2d_16bit(&tw[l], w[s], (uint64_t)N[s], (uint64_t)k, (uint64_t)ldw[s], (uint32_t)p.np[l], BK, is_bf16);
+        }
     }
     if (!maps_ok) return fail(XG_ERR_UNSUPPORTED, "%s: tensor-map encoding failed", who);
     auto kern = mlp_kernel<T>;
@@ -378,8 +399,8 @@ bool mlp_supported(int64_t M, int64_t K1, int layers, const int64_t* N, int dtyp
 }
 
 int mlp_entry(const char* who, const void* x, int layers, const void* const* w, const void* const* b, void* out, int64_t M,
-              int64_t K1, const int64_t* N, int64_t lda, const int64_t* ldw, int64_t ldc, const int* act, int dtype,
-              void* stream) {
+              int64_t K1, const int64_t* N, int64_t lda, const int64_t* ldw, int64_t ldc, const int* act, int weights_kn,
+              int dtype, void* stream) {
     if (!x || !out) return fail(XG_ERR_INVALID_ARG, "%s: null pointer", who);
     if (M < 0 || K1 <= 0) return fail(XG_ERR_INVALID_ARG, "%s: bad extents", who);
     for (int l = 0; l < layers; ++l) {
@@ -395,14 +416,16 @@ int mlp_entry(const char* who, const void* x, int layers, const void* const* w, 
     if (lda < K1 || ldc < N[layers - 1]) return fail(XG_ERR_INVALID_ARG, "%s: a row stride is shorter than its row", who);
     if (!aligned16(x) || lda % 8 != 0)
         return fail(XG_ERR_UNSUPPORTED, "%s: x must be 16-byte aligned with a row stride that is a multiple of 8 elements", who);
+    if (weights_kn < 0 || weights_kn >= (1 << layers)) return fail(XG_ERR_INVALID_ARG, "%s: bad weight layout mask", who);
     for (int l = 0; l < layers; ++l) {
-        if (ldw[l] < (l == 0 ? K1 : N[l - 1])) return fail(XG_ERR_INVALID_ARG, "%s: a row stride is shorter than its row", who);
+        const bool kn = (weights_kn >> l) & 1;  // rows of a [K, N] weight are N long
+        if (ldw[l] < (kn ? N[l] : (l == 0 ? K1 : N[l - 1]))) return fail(XG_ERR_INVALID_ARG, "%s: a row stride is shorter than its row", who);
         if (!aligned16(w[l]) || ldw[l] % 8 != 0)
             return fail(XG_ERR_UNSUPPORTED, "%s: weights must be 16-byte aligned with row strides that are multiples of 8 elements", who);
     }
     cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
-    if (dtype == XG_BF16) return launch_mlp<__nv_bfloat16>(who, x, layers, w, b, out, M, K1, N, lda, ldw, ldc, act, st);
-    return launch_mlp<__half>(who, x, layers, w, b, out, M, K1, N, lda, ldw, ldc, act, st);
+    if (dtype == XG_BF16) return launch_mlp<__nv_bfloat16>(who, x, layers, w, b, out, M, K1, N, lda, ldw, ldc, act, weights_kn, st);
+    return launch_mlp<__half>(who, x, layers, w, b, out, M, K1, N, lda, ldw, ldc, act, weights_kn, st);
 }
 
 }  // namespace
@@ -435,21 +458,21 @@ extern "C" int xg_mlp3_supported(int64_t M, int64_t K1, int64_t N1, int64_t N2, 
 
 extern "C" int xg_mlp2_bias_act(const void* x, const void* w1, const void* b1, const void* w2, const void* b2, void* out,
                                 int64_t M, int64_t K1, int64_t N1, int64_t N2, int64_t lda, int64_t ldw1, int64_t ldw2,
-                                int64_t ldc, int act1, int act2, int dtype, void* stream) {
+                                int64_t ldc, int act1, int act2, int weights_kn, int dtype, void* stream) {
     const void* w[2] = {w1, w2};
     const void* b[2] = {b1, b2};
     const int64_t N[2] = {N1, N2}, ldw[2] = {ldw1, ldw2};
     const int act[2] = {act1, act2};
-    return xg::mlp_entry("xg_mlp2_bias_act", x, 2, w, b, out, M, K1, N, lda, ldw, ldc, act, dtype, stream);
+    return xg::mlp_entry("xg_mlp2_bias_act", x, 2, w, b, out, M, K1, N, lda, ldw, ldc, act, weights_kn, dtype, stream);
 }
 
 extern "C" int xg_mlp3_bias_act(const void* x, const void* w1, const void* b1, const void* w2, const void* b2, const void* w3,
                                 const void* b3, void* out, int64_t M, int64_t K1, int64_t N1, int64_t N2, int64_t N3,
                                 int64_t lda, int64_t ldw1, int64_t ldw2, int64_t ldw3, int64_t ldc, int act1, int act2,
-                                int act3, int dtype, void* stream) {
+                                int act3, int weights_kn, int dtype, void* stream) {
     const void* w[3] = {w1, w2, w3};
     const void* b[3] = {b1, b2, b3};
     const int64_t N[3] = {N1, N2, N3}, ldw[3] = {ldw1, ldw2, ldw3};
     const int act[3] = {act1, act2, act3};
-    return xg::mlp_entry("xg_mlp3_bias_act", x, 3, w, b, out, M, K1, N, lda, ldw, ldc, act, dtype, stream);
+    return xg::mlp_entry("xg_mlp3_bias_act", x, 3, w, b, out, M, K1, N, lda, ldw, ldc, act, weights_kn, dtype, stream);
 }

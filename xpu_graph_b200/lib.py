@@ -59,9 +59,9 @@ SIGNATURES = {
                                        c_int, c_int, c_int, c_void_p]),
     "xg_mlp2_supported": (c_int, [c_int64, c_int64, c_int64, c_int64, c_int]),
     "xg_mlp3_supported": (c_int, [c_int64, c_int64, c_int64, c_int64, c_int64, c_int]),
-    "xg_mlp3_bias_act": (c_int, [c_void_p] * 8 + [c_int64] * 10 + [c_int] * 4 + [c_void_p]),
+    "xg_mlp3_bias_act": (c_int, [c_void_p] * 8 + [c_int64] * 10 + [c_int] * 5 + [c_void_p]),
     "xg_mlp2_bias_act": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64,
-                                 c_int64, c_int64, c_int64, c_int64, c_int, c_int, c_int, c_void_p]),
+                                 c_int64, c_int64, c_int64, c_int64, c_int, c_int, c_int, c_int, c_void_p]),
     "xg_gemm_swiglu": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64, c_int64,
                                c_int64, c_int, c_void_p]),
     "xg_gemm_rope": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64, c_int64,

@@ -286,26 +286,39 @@ def dense_tower_eligible(M: int, dims: Sequence[int]) -> bool:
 
 
 def mlp2_eligible(M: int, K1: int, N1: int, N2: int, dtype: torch.dtype, trans1: bool = True, trans2: bool = True) -> bool:
-    """Two chained 16-bit dense layers [K1 -> N1 -> N2] fit the single-kernel form: weights as nn.Linear stores them
-    ([N, K]), 16 <= N1 <= 256 with N1 % 8 == 0, N2 <= 256, K1 % 8 == 0 (the limits of xg_mlp2_supported)."""
-    return (dtype in (torch.bfloat16, torch.float16) and bool(trans1) and bool(trans2) and M > 0 and K1 >= 8 and K1 % 8 == 0
-            and 16 <= N1 <= 256 and N1 % 8 == 0 and 1 <= N2 <= 256)
+    """Two chained 16-bit dense layers [K1 -> N1 -> N2] fit the single-kernel form: 16 <= N1 <= 256 with N1 % 8 == 0,
+    N2 <= 256, K1 % 8 == 0 (the limits of xg_mlp2_supported); a weight stored [K, N] (not transposed) needs N % 8 == 0."""
+    return (dtype in (torch.bfloat16, torch.float16) and M > 0 and K1 >= 8 and K1 % 8 == 0
+            and 16 <= N1 <= 256 and N1 % 8 == 0 and 1 <= N2 <= 256 and (bool(trans2) or N2 % 8 == 0))
+
+
+def _mlp_dims(x, ws, weights_kn, who):
+    """Layer widths of a chain; weight l is [N, K] unless bit l of weights_kn says [K, N]."""
+    k = x.shape[1]
+    dims = []
+    for l, w in enumerate(ws):
+        kn = (weights_kn >> l) & 1
+        wk, wn = (w.shape[0], w.shape[1]) if kn else (w.shape[1], w.shape[0])
+        if wk != k:
+            raise ValueError(f"xg_sm100::{who}: inner dimensions differ")
+        if w.dtype != x.dtype:
+            raise ValueError(f"xg_sm100::{who}: x and the weights must share a dtype")
+        dims.append(wn)
+        k = wn
+    return dims
 
 
 @torch.library.custom_op(f"{NS}::mlp2", mutates_args=(), device_types="cuda")
 def mlp2(x: torch.Tensor, w1: torch.Tensor, b1: Optional[torch.Tensor], w2: torch.Tensor, b2: Optional[torch.Tensor],
-         act1: str, act2: str) -> torch.Tensor:
-    """act2(act1(x @ w1^T + b1) @ w2^T + b2) in one kernel; w1 [N1, K1], w2 [N2, N1]; the hidden activation stays on chip
-    (rounded to the tensors' 16-bit dtype between the layers, as the unfused graph does)."""
+         act1: str, act2: str, weights_kn: int = 0) -> torch.Tensor:
+    """act2(act1(x @ W1 + b1) @ W2 + b2) in one kernel; weight l is given as [N, K] (nn.Linear's layout) or, if bit l of
+    weights_kn is set, as [K, N]; the hidden activation stays on chip (rounded to the tensors' 16-bit dtype between the
+    layers, as the unfused graph does)."""
     if x.dim() != 2 or w1.dim() != 2 or w2.dim() != 2:
         raise ValueError("xg_sm100::mlp2 expects 2-D x, w1 and w2")
     x, w1, w2 = _mat(x), _mat(w1), _mat(w2)
     M, K1 = x.shape
-    N1, N2 = w1.shape[0], w2.shape[0]
-    if w1.shape[1] != K1 or w2.shape[1] != N1:
-        raise ValueError("xg_sm100::mlp2: inner dimensions differ")
-    if w1.dtype != x.dtype or w2.dtype != x.dtype:
-        raise ValueError("xg_sm100::mlp2: x, w1 and w2 must share a dtype")
+    N1, N2 = _mlp_dims(x, (w1, w2), weights_kn, "mlp2")
     b1 = b1.to(x.dtype).contiguous() if b1 is not None else None
     b2 = b2.to(x.dtype).contiguous() if b2 is not None else None
     if (b1 is not None and b1.numel() != N1) or (b2 is not None and b2.numel() != N2):
@@ -315,36 +328,32 @@ def mlp2(x: torch.Tensor, w1: torch.Tensor, b1: Optional[torch.Tensor], w2: torc
         return out
     L = _lib.load()
     rc = L.xg_mlp2_bias_act(_ptr(x), _ptr(w1), _ptr(b1), _ptr(w2), _ptr(b2), _ptr(out), M, K1, N1, N2, _row_stride(x),
-                            _row_stride(w1), _row_stride(w2), N2, _lib.ACT_CODES[act1], _lib.ACT_CODES[act2],
+                            _row_stride(w1), _row_stride(w2), N2, _lib.ACT_CODES[act1], _lib.ACT_CODES[act2], weights_kn,
                             _code(x.dtype), _stream(x))
     _lib.check(rc, "xg_mlp2_bias_act")
     return out
 
 
 @mlp2.register_fake
-def _(x, w1, b1, w2, b2, act1, act2):
-    return torch.empty((x.shape[0], w2.shape[0]), dtype=x.dtype, device=x.device)
+def _(x, w1, b1, w2, b2, act1, act2, weights_kn=0):
+    return torch.empty((x.shape[0], w2.shape[1] if (weights_kn >> 1) & 1 else w2.shape[0]), dtype=x.dtype, device=x.device)
 
 
 def mlp3_eligible(M: int, K1: int, N1: int, N2: int, N3: int, dtype: torch.dtype, trans=(True, True, True)) -> bool:
     """Three chained 16-bit dense layers fit the single-kernel form (the limits of xg_mlp3_supported)."""
-    return (mlp2_eligible(M, K1, N1, N2, dtype, trans[0], trans[1]) and bool(trans[2]) and 16 <= N2 and N2 % 8 == 0
-            and 1 <= N3 <= 256)
+    return (mlp2_eligible(M, K1, N1, N2, dtype, trans[0], trans[1]) and 16 <= N2 and N2 % 8 == 0
+            and 1 <= N3 <= 256 and (bool(trans[2]) or N3 % 8 == 0))
 
 
 @torch.library.custom_op(f"{NS}::mlp3", mutates_args=(), device_types="cuda")
 def mlp3(x: torch.Tensor, w1: torch.Tensor, b1: Optional[torch.Tensor], w2: torch.Tensor, b2: Optional[torch.Tensor],
-         w3: torch.Tensor, b3: Optional[torch.Tensor], act1: str, act2: str, act3: str) -> torch.Tensor:
-    """Three chained dense layers in one kernel (see mlp2); w3 [N3, N2]."""
+         w3: torch.Tensor, b3: Optional[torch.Tensor], act1: str, act2: str, act3: str, weights_kn: int = 0) -> torch.Tensor:
+    """Three chained dense layers in one kernel (see mlp2)."""
     if x.dim() != 2 or w1.dim() != 2 or w2.dim() != 2 or w3.dim() != 2:
         raise ValueError("xg_sm100::mlp3 expects 2-D x and weights")
     x, w1, w2, w3 = _mat(x), _mat(w1), _mat(w2), _mat(w3)
     M, K1 = x.shape
-    N1, N2, N3 = w1.shape[0], w2.shape[0], w3.shape[0]
-    if w1.shape[1] != K1 or w2.shape[1] != N1 or w3.shape[1] != N2:
-        raise ValueError("xg_sm100::mlp3: inner dimensions differ")
-    if not (w1.dtype == w2.dtype == w3.dtype == x.dtype):
-        raise ValueError("xg_sm100::mlp3: x and the weights must share a dtype")
+    N1, N2, N3 = _mlp_dims(x, (w1, w2, w3), weights_kn, "mlp3")
     bs = [b.to(x.dtype).contiguous() if b is not None else None for b in (b1, b2, b3)]
     if any(b is not None and b.numel() != n for b, n in zip(bs, (N1, N2, N3))):
         raise ValueError("xg_sm100::mlp3: a bias does not match its layer's width")
@@ -354,14 +363,14 @@ def mlp3(x: torch.Tensor, w1: torch.Tensor, b1: Optional[torch.Tensor], w2: torc
     L = _lib.load()
     rc = L.xg_mlp3_bias_act(_ptr(x), _ptr(w1), _ptr(bs[0]), _ptr(w2), _ptr(bs[1]), _ptr(w3), _ptr(bs[2]), _ptr(out), M, K1, N1,
                             N2, N3, _row_stride(x), _row_stride(w1), _row_stride(w2), _row_stride(w3), N3, _lib.ACT_CODES[act1],
-                            _lib.ACT_CODES[act2], _lib.ACT_CODES[act3], _code(x.dtype), _stream(x))
+                            _lib.ACT_CODES[act2], _lib.ACT_CODES[act3], weights_kn, _code(x.dtype), _stream(x))
     _lib.check(rc, "xg_mlp3_bias_act")
     return out
 
 
 @mlp3.register_fake
-def _(x, w1, b1, w2, b2, w3, b3, act1, act2, act3):
-    return torch.empty((x.shape[0], w3.shape[0]), dtype=x.dtype, device=x.device)
+def _(x, w1, b1, w2, b2, w3, b3, act1, act2, act3, weights_kn=0):
+    return torch.empty((x.shape[0], w3.shape[1] if (weights_kn >> 2) & 1 else w3.shape[0]), dtype=x.dtype, device=x.device)
 
 
 @torch.library.custom_op(f"{NS}::dense_tower", mutates_args=(), device_types="cuda")
@@ -383,12 +392,13 @@ def dense_tower(x: torch.Tensor, weights: List[torch.Tensor], weight_trans: List
         # each, the rest layer by layer
         y, i = x, 0
         while i < n:
+            kn = lambda a, b: sum((0 if weight_trans[i + l] else 1) << l for l in range(a, b))  # noqa: E731
             if i + 2 < n and mlp3_eligible(M, dims[i], dims[i + 1], dims[i + 2], dims[i + 3], x.dtype, weight_trans[i:i + 3]):
                 y = mlp3(y, weights[i], biases[i], weights[i + 1], biases[i + 1], weights[i + 2], biases[i + 2],
-                         acts[i], acts[i + 1], acts[i + 2])
+                         acts[i], acts[i + 1], acts[i + 2], kn(0, 3))
                 i += 3
             elif i + 1 < n and mlp2_eligible(M, dims[i], dims[i + 1], dims[i + 2], x.dtype, weight_trans[i], weight_trans[i + 1]):
-                y = mlp2(y, weights[i], biases[i], weights[i + 1], biases[i + 1], acts[i], acts[i + 1])
+                y = mlp2(y, weights[i], biases[i], weights[i + 1], biases[i + 1], acts[i], acts[i + 1], kn(0, 2))
                 i += 2
             else:
                 y = dense(y, weights[i], weight_trans[i], biases[i], None, acts[i])
