@@ -339,6 +339,41 @@ def test_mlp_kn_weights(cuda_device, dtype):
     assert_parity(got, y2, f"mlp2 with [K, N] weights {dtype}")
 
 
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+def test_transposed_view_weights(cuda_device, dtype):
+    """Weights handed over as transposed views (w.T of a contiguous matrix, what F.linear(x, w.T) and x @ w.t() produce)
+    are read through their base in the other orientation: dense layers in both orientations, and the grouped launch of
+    the reference's combo test form (tests/mlu/test_combo_matmul.py:73-79: relu(F.linear(x_i, w_i.T)))."""
+    from tests.helpers import LaunchCounter
+    from xpu_graph_b200 import lib, ops  # noqa: F401
+    from xpu_graph_b200.modules import ComboDenseModule, DenseLayerModule
+
+    g = torch.Generator().manual_seed(45)
+    M, K, N = 200, 128, 72
+    x = torch.randn(M, K, generator=g).to(dtype)
+    w_kn = (torch.randn(K, N, generator=g) * K ** -0.5).to(dtype)   # contiguous [K, N]
+    w_nk = w_kn.t().contiguous()                                     # contiguous [N, K]
+    b = (0.1 * torch.randn(N, generator=g)).to(dtype)
+    want = ref_ops.dense(x, w_nk, True, b, "gelu")
+    xd, bd = x.to(cuda_device), b.to(cuda_device)
+    # [N, K] given as the transposed view of a contiguous [K, N] matrix, and the other way round
+    got = DenseLayerModule(False)(xd, w_kn.to(cuda_device).t(), True, bd, "gelu")
+    assert_parity(got, want, f"dense, weight = (K,N).T view {dtype}")
+    got = DenseLayerModule(False)(xd, w_nk.to(cuda_device).t(), False, bd, "gelu")
+    assert_parity(got, want, f"dense, weight = (N,K).T view {dtype}")
+    if dtype == torch.float32:
+        return
+    T = 6
+    xs = [torch.randn(M, K, generator=g).to(dtype) for _ in range(T)]
+    ws = [(torch.randn(K, N, generator=g) * K ** -0.5).to(dtype) for _ in range(T)]
+    with LaunchCounter() as c:
+        got = ComboDenseModule()([t.to(cuda_device) for t in xs], [w.to(cuda_device).t() for w in ws], [None] * T, "relu", True)
+    torch.cuda.synchronize()
+    assert lib.tc_status() == 0 and c.names == ["xg_gemm_group_bias_act"], c.names
+    for i in range(T):
+        assert_parity(got[i], ref_ops.dense(xs[i], ws[i], False, None, "relu"), f"combo member {i}, transposed-view weights")
+
+
 def test_mlp2_strided_input_and_limits(cuda_device):
     """A row-strided x (a column slice of a wider tensor) is read in place; shapes outside the kernel's limits are
     refused with XG_ERR_UNSUPPORTED, and the tower op then runs the layers one by one."""

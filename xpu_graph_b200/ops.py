@@ -215,6 +215,15 @@ def _mat(t: torch.Tensor) -> torch.Tensor:
     return t if t.stride(-1) == 1 else t.contiguous()
 
 
+def _weight_rows(w: torch.Tensor, weight_trans: bool):
+    """A 2-D weight with contiguous rows and the orientation flag that goes with it. A transposed view of a contiguous
+    matrix (``w.T``, what F.linear(x, w.T) or x @ w.t() hand over) is read through its base in the other orientation -
+    the kernels take both [N, K] and [K, N] - instead of being copied on every call."""
+    if w.dim() == 2 and w.stride(-1) != 1 and w.stride(0) == 1 and w.shape[0] > 1:
+        return w.t(), not weight_trans
+    return _mat(w), weight_trans
+
+
 # fp32 dense layers above this many FLOPs run on the bf16 tensor cores from three bf16 planes per operand
 # (fp32-grade results at several times the FMA rate); smaller ones stay on the FMA kernel, whose launch is cheaper.
 F32_TENSOR_MIN_FLOPS = int(os.environ.get("XG_F32_TENSOR_MIN_FLOPS", str(1 << 30)))
@@ -388,6 +397,8 @@ def dense_tower(x: torch.Tensor, weights: List[torch.Tensor], weight_trans: List
     M = x.shape[0]
     dims = [x.shape[1]] + [(w.shape[0] if t else w.shape[1]) for w, t in zip(weights, weight_trans)]
     if x.dtype != torch.float32:
+        rows = [_weight_rows(w, t) for w, t in zip(weights, weight_trans)]
+        weights, weight_trans = [r[0] for r in rows], [r[1] for r in rows]
         # 16-bit towers: runs of three or two neighbouring layers that fit the chained-layer kernel run as one launch
         # each, the rest layer by layer
         y, i = x, 0
@@ -446,7 +457,7 @@ def dense(x: torch.Tensor, weight: torch.Tensor, weight_trans: bool, bias: Optio
     if x.dim() != 2 or weight.dim() != 2:
         raise ValueError("xg_sm100::dense expects 2-D x and weight")
     x = _mat(x)
-    weight = _mat(weight)
+    weight, weight_trans = _weight_rows(weight, weight_trans)
     M, K = x.shape
     N = weight.shape[0] if weight_trans else weight.shape[1]
     if (weight.shape[1] if weight_trans else weight.shape[0]) != K:
@@ -537,7 +548,11 @@ def _combo_dense_grouped(inputs, weights, weight_trans: bool, biases, act: str) 
     x0, w0 = inputs[0], weights[0]
     if x0.dtype not in (torch.bfloat16, torch.float16) or x0.dim() != 2 or w0.dim() != 2:
         return None
-    xs, ws = [_mat(t) for t in inputs], [_mat(t) for t in weights]
+    xs = [_mat(t) for t in inputs]
+    rows = [_weight_rows(t, weight_trans) for t in weights]
+    if any(r[1] != rows[0][1] for r in rows):
+        return None
+    ws, weight_trans = [r[0] for r in rows], rows[0][1]
     M, K = xs[0].shape
     N = ws[0].shape[0] if weight_trans else ws[0].shape[1]
     lda, ldw = _row_stride(xs[0]), _row_stride(ws[0])

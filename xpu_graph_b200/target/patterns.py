@@ -1168,9 +1168,9 @@ COMBO_MIN_WIDTH = 4  # the reference's default width (utils/combo_utils.py:40-41
 
 class FusedComboDense(Pattern):
     """>= 4 independent dense layers of one shape, dtype, orientation and activation -> one ComboDenseModule call
-    (a batched launch) + unbind. The graph form of targets/mlu/combo_matmul.py:116-232, restricted to groups whose
-    operands are all defined before the group's first member, so that the combined node can take that member's
-    place without reordering the graph."""
+    (a grouped launch) + unbind. The graph form of targets/mlu/combo_matmul.py:116-232, restricted to groups whose
+    operands are all defined before the group's first member, or whose results are all used after its last member, so
+    that the combined node can take that member's place without reordering the graph."""
 
     _opt_level = OptLevel.level2
     _pattern_group = PatternGroup.GROUP2
@@ -1197,13 +1197,20 @@ class FusedComboDense(Pattern):
         for key, nodes in groups.items():
             if len(nodes) < COMBO_MIN_WIDTH:
                 continue
-            first = order[nodes[0]]
-            # every operand of every member precedes the first member: the members are then mutually independent too
+            first, last = order[nodes[0]], order[nodes[-1]]
+            # either every operand of every member precedes the first member (the combined node then takes that member's
+            # place), or every user of every member follows the last member (it takes the last member's place; the form of
+            # weights that are each produced right before their layer, e.g. F.linear(x_i, w_i.T)): the members are mutually
+            # independent in both cases
+            anchor = nodes[0]
             members = [n for n in nodes if all(not isinstance(a, fx.Node) or order[a] < first for a in n.args)]
+            if len(members) < COMBO_MIN_WIDTH:
+                anchor = nodes[-1]
+                members = [n for n in nodes if all(order[u] > last for u in n.users)]
             if len(members) < COMBO_MIN_WIDTH:
                 continue
             _ensure(gm, "xg_combo_dense", M.ComboDenseModule)
-            with gm.graph.inserting_before(nodes[0]):
+            with gm.graph.inserting_before(anchor):
                 new = gm.graph.call_module("xg_combo_dense", ([n.args[0] for n in members], [n.args[1] for n in members],
                                                               [n.args[3] for n in members], key[4], key[2]))
                 _fill_meta(gm, new)
