@@ -60,6 +60,29 @@ def register():
         return out
 
     k(ops.slice_cat)(slice_cat)
+
+    def slice_cat_partly_masked(src, starts, ends, masked, row_mask, zero_when):
+        parts = []
+        for s_, e_, m in zip(starts, ends, masked):
+            part = ref_ops.slice_cat(src, [(s_, e_)])
+            if m:
+                part = part.clone()
+                part[(row_mask.reshape(-1) != 0) == zero_when] = 0
+            parts.append(part)
+        return torch.cat(parts, dim=-1)
+
+    k(ops.slice_cat_partly_masked)(slice_cat_partly_masked)
+    def multi_slice_masked(src, starts, slice_len, masked, row_mask, zero_when):
+        parts = []
+        for s_, m in zip(starts, masked):
+            part = ref_ops.slice_cat(src, [(s_, s_ + slice_len)])
+            if m:
+                part = part.clone()
+                part[(row_mask.reshape(-1) != 0) == zero_when] = 0
+            parts.append(part)
+        return torch.stack(parts, dim=0)
+
+    k(ops.multi_slice_masked)(multi_slice_masked)
     k(ops.multi_slice)(lambda src, starts, slice_len: ref_ops.multi_slice(src, starts, slice_len))
 
     def slice_cat_multi(src, starts, ends, counts):

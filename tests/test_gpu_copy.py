@@ -86,6 +86,27 @@ def test_masked_slice_cat(cuda_device, dtype):
     assert_bit_exact(got, ref_ops.masked_slice_cat(src, mask, slices), "masked slice_cat")
 
 
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float16])
+def test_partly_masked_slice_cat_and_stack(cuda_device, dtype):
+    """Slices of one source where only some take the row mask, concatenated (MaskedSliceCatModule with flags) or stacked
+    along a new leading dim (MaskedSliceStackModule): bit-exact against slicing, masking and joining on CPU."""
+    from xpu_graph_b200.modules import MaskedSliceCatModule, MaskedSliceStackModule
+
+    src = _src(513, 1200, dtype)
+    g = torch.Generator().manual_seed(14)
+    mask = torch.rand(513, 1, generator=g) < 0.4
+    slices = [(0, 32), (700, 731), (64, 96), (1100, 1200), (5, 6)]
+    flags = [False, True, True, False, True]
+    want = torch.cat([torch.where(mask, torch.zeros((), dtype=dtype), src[:, a:b]) if f else src[:, a:b] for (a, b), f in zip(slices, flags)], dim=-1)
+    got = MaskedSliceCatModule()(src.to(cuda_device), mask.to(cuda_device), slices, flags)
+    assert_bit_exact(got, want, "partly masked slice_cat")
+    starts, L = [0, 1001, 37, 640], 24
+    sflags = [False, True, True, True]
+    want = torch.stack([torch.where(mask, torch.zeros((), dtype=dtype), src[:, a:a + L]) if f else src[:, a:a + L] for a, f in zip(starts, sflags)], dim=0)
+    got = MaskedSliceStackModule()(src.to(cuda_device), mask.to(cuda_device), starts, L, sflags)
+    assert_bit_exact(got, want, "partly masked slice stack")
+
+
 def test_cat_and_stack(cuda_device):
     from xpu_graph_b200.modules import CatLastDimModule
 

@@ -379,6 +379,35 @@ def test_masked_slice_cat(tgt, xlog):
     assert not any("where" in a or "slice" in a for a in atens), atens
 
 
+def test_masked_slice_cat_reference_test_forms(tgt, xlog):
+    """The two graphs of the reference's own test (tests/mlu/test_fuse_slice_where_cat.py:19-76, fp16, a 35149-wide
+    source): an unmasked slice followed by where-masked slices, concatenated along the last dim or stacked along a new
+    leading one, the unmasked slice being a second output. Each becomes one module call; the plain slice stays a view."""
+    g = torch.Generator().manual_seed(9)
+    B = 96
+    src = torch.randn(B, 35149, generator=g).to(torch.float16)
+    mask = (torch.rand(B, generator=g) < 0.5).unsqueeze(-1)
+
+    def cat_form(mask, src):
+        zeros = torch.zeros([B, 32], dtype=torch.float16)
+        first = src[:, 0:32]
+        rest = [src[:, a:a + 32] for a in (10118, 10579, 11032, 11445)]
+        return torch.cat([first] + [torch.where(mask, zeros, r) for r in rest], dim=-1), first
+
+    def stack_form(mask, src):
+        zeros = torch.zeros([B, 4], dtype=torch.float16)
+        first = src[:, 0:4]
+        rest = [src[:, a:a + 4] for a in (11984, 11562, 9782, 9727, 9745, 9763, 9773, 9805, 9822, 10283, 10736)]
+        return torch.stack([first] + [torch.where(mask, zeros, r) for r in rest], dim=0), first
+
+    for fn, module in ((cat_form, "xg_masked_slice_cat"), (stack_form, "xg_masked_slice_stack")):
+        want, got, mods, atens = _compile(tgt, fn, mask, src)
+        assert torch.equal(got[0], want[0]) and torch.equal(got[1], want[1])
+        assert mods == [module], (mods, atens)
+        assert not any("where" in a or "unbind" in a or "transpose" in a for a in atens), atens
+        torch._dynamo.reset()
+
+
 def test_slice_fusions_use_target_modules(tgt, xlog):
     g = torch.Generator().manual_seed(4)
     src = torch.randn(12, 200, generator=g)

@@ -240,10 +240,22 @@ class MaskedSliceCatModule(torch.nn.Module):
     """cat([where(mask[B,1], 0, x[:, s:e]) ...], -1) — the computation of the reference's
     fuse_slice_where_cat kernel (targets/mlu/triton_kernel/fused_slice_where_cat.py:12-73)."""
 
-    def forward(self, input_tensor, mask, slices):
+    def forward(self, input_tensor, mask, slices, masked=None):
+        """`masked`: optional flag per slice; slices flagged False are copied as they are (the form
+        cat([x[:, a:b], where(m, 0, x[:, c:d]), ...]) of the reference's test, tests/mlu/test_fuse_slice_where_cat.py:19-31)."""
         starts = [int(s) for s, _ in slices]
         ends = [int(e) for _, e in slices]
-        return _X.slice_cat(input_tensor, starts, ends, mask, True)
+        if masked is None or all(masked):
+            return _X.slice_cat(input_tensor, starts, ends, mask, True)
+        return _X.slice_cat_partly_masked(input_tensor, starts, ends, [bool(m) for m in masked], mask, True)
+
+
+class MaskedSliceStackModule(torch.nn.Module):
+    """stack([x[:, a:a+L], where(mask[B,1], 0, x[:, b:b+L]), ...], 0) -> [num, B, L]: forward(x, mask, starts, slice_len,
+    masked) with a flag per slice (the stack form of the reference's test, tests/mlu/test_fuse_slice_where_cat.py:34-76)."""
+
+    def forward(self, input_tensor, mask, starts, slice_len, masked):
+        return _X.multi_slice_masked(input_tensor, [int(s) for s in starts], int(slice_len), [bool(m) for m in masked], mask, True)
 
 
 class CatLastDimModule(torch.nn.Module):

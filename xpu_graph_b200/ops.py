@@ -738,6 +738,44 @@ def _(src, starts, ends, row_mask, zero_when):
     return torch.empty((src.shape[0], sum(e - s for s, e in segs)), dtype=src.dtype, device=src.device)
 
 
+@torch.library.custom_op(f"{NS}::slice_cat_partly_masked", mutates_args=(), device_types="cuda")
+def slice_cat_partly_masked(src: torch.Tensor, starts: List[int], ends: List[int], masked: List[bool], row_mask: torch.Tensor,
+                            zero_when: bool) -> torch.Tensor:
+    """slice_cat where the row mask applies to the slices flagged in `masked` only (cat([x[:, a:b], where(m, 0, x[:, c:d]),
+    ...], -1)): the masked and the unmasked slices are two passes of the segmented copy into one output buffer."""
+    if src.dim() != 2:
+        raise NotImplementedError("input must be 2d")
+    if len(masked) != len(starts):
+        raise ValueError("xg_sm100::slice_cat_partly_masked: one flag per slice")
+    if src.stride(1) != 1:
+        src = src.contiguous()
+    rows, width = src.shape
+    segs = _norm_slices(width, starts, ends)
+    total = sum(e - s for s, e in segs)
+    out = torch.empty((rows, total), dtype=src.dtype, device=src.device)
+    es = src.element_size()
+    off = 0
+    groups = {False: ([], [], []), True: ([], [], [])}
+    for (s, e), m in zip(segs, masked):
+        srcs, dsts, lens = groups[bool(m)]
+        srcs.append(src.data_ptr() + s * es)
+        dsts.append(out.data_ptr() + off * es)
+        lens.append((e - s) * es)
+        off += e - s
+    for m, (srcs, dsts, lens) in groups.items():
+        n = len(srcs)
+        if n:
+            _seg_copy(srcs, dsts, [_row_stride(src) * es] * n, [total * es] * n, lens, rows,
+                      _mask_bytes(row_mask, rows) if m else None, zero_when, src)
+    return out
+
+
+@slice_cat_partly_masked.register_fake
+def _(src, starts, ends, masked, row_mask, zero_when):
+    segs = _norm_slices(src.shape[1], starts, ends)
+    return torch.empty((src.shape[0], sum(e - s for s, e in segs)), dtype=src.dtype, device=src.device)
+
+
 def _checked_starts(width: int, starts: Sequence[int], slice_len: int) -> List[int]:
     """Slice starts with negative values wrapped; every slice [s, s + slice_len) has to lie inside the row. The
     reference derives slice_len as end - start of the raw aten.slice arguments (structure/fuse_slice.py:28), so a slice
@@ -774,6 +812,37 @@ def multi_slice(src: torch.Tensor, starts: List[int], slice_len: int) -> torch.T
 def _(src, starts, slice_len):
     _checked_starts(src.shape[-1], starts, slice_len)
     return torch.empty([len(starts)] + list(src.shape[:-1]) + [slice_len], dtype=src.dtype, device=src.device)
+
+
+@torch.library.custom_op(f"{NS}::multi_slice_masked", mutates_args=(), device_types="cuda")
+def multi_slice_masked(src: torch.Tensor, starts: List[int], slice_len: int, masked: List[bool], row_mask: torch.Tensor,
+                       zero_when: bool) -> torch.Tensor:
+    """multi_slice of a 2-D src where the slices flagged in `masked` are written as zeros in the rows where
+    (row_mask != 0) == zero_when: stack([x[:, a:a+L], where(m, 0, x[:, b:b+L]), ...], 0) -> [num, rows, L]."""
+    if src.dim() != 2:
+        raise NotImplementedError("input must be 2d")
+    if len(masked) != len(starts):
+        raise ValueError("xg_sm100::multi_slice_masked: one flag per slice")
+    starts = _checked_starts(src.shape[-1], starts, slice_len)
+    s2 = _rows_view(src)
+    rows = s2.shape[0]
+    num = len(starts)
+    out = torch.empty((num, rows, slice_len), dtype=src.dtype, device=src.device)
+    es = src.element_size()
+    for flag in (False, True):
+        ks = [k for k in range(num) if bool(masked[k]) == flag]
+        if ks:
+            n = len(ks)
+            _seg_copy([s2.data_ptr() + starts[k] * es for k in ks], [out.data_ptr() + k * rows * slice_len * es for k in ks],
+                      [_row_stride(s2) * es] * n, [slice_len * es] * n, [slice_len * es] * n, rows,
+                      _mask_bytes(row_mask, rows) if flag else None, zero_when, src)
+    return out
+
+
+@multi_slice_masked.register_fake
+def _(src, starts, slice_len, masked, row_mask, zero_when):
+    _checked_starts(src.shape[-1], starts, slice_len)
+    return torch.empty((len(starts), src.shape[0], slice_len), dtype=src.dtype, device=src.device)
 
 
 @torch.library.custom_op(f"{NS}::slice_cat_multi", mutates_args=(), device_types="cuda")

@@ -809,7 +809,9 @@ class FusedMaskedSliceCat(Pattern):
         where(mask, 0, fuse_slice_cat(src, slices))                                       or, for equal-length slices,
         cat(unbind(where(mask, 0, transpose(reshape(fuse_slice_cat(src, slices), [B, n, L]), 0, 1))), -1)
 
-    and both forms are matched here."""
+    and both forms are matched here; in the second one the members may stand between plain (unmasked) slices of the same
+    source, and may be stacked along a new leading dim instead of concatenated (-> MaskedSliceStackModule): the two
+    graphs of the reference's own test, tests/mlu/test_fuse_slice_where_cat.py:19-76."""
 
     _opt_level = OptLevel.level1
     _pattern_group = PatternGroup.GROUP2
@@ -826,17 +828,25 @@ class FusedMaskedSliceCat(Pattern):
 
     def _stacked_form(self, gm, node):
         """node = cat / CatLastDimModule over getitem(unbind(where(mask, 0, transpose(reshape(slice_cat))))) in order."""
+        stacked = False
         if _is(node, aten.cat.default):
             parts = node.args[0]
             dim = node.args[1] if len(node.args) > 1 else 0
             if dim not in (-1, 1):
                 return None
+        elif _is(node, aten.stack.default) and (len(node.args) == 1 or node.args[1] == 0):
+            parts, stacked = node.args[0], True  # the members side by side along a new leading dim instead
         elif _module_call(gm, node, M.CatLastDimModule) and len(node.args) == 1:
             parts = node.args[0]
         else:
             return None
-        if len(parts) < 2 or not all(_is(q, operator.getitem) and _only_user(q, node) for q in parts):
+        # the masked members are getitem(unbind(...), i) in order; plain slices of the same source (dim 1) may stand
+        # between them: they are copied unmasked (the form of tests/mlu/test_fuse_slice_where_cat.py:19-31)
+        items = [q for q in parts if _is(q, operator.getitem)]
+        plain = [q for q in parts if not _is(q, operator.getitem)]
+        if len(items) < 2 or not all(_only_user(q, node) for q in items):
             return None
+        parts_all, parts = parts, items
         ub = parts[0].args[0]
         if not (_is(ub, aten.unbind.int) and (len(ub.args) == 1 or ub.args[1] == 0) and len(ub.users) == len(parts)):
             return None
@@ -863,12 +873,34 @@ class FusedMaskedSliceCat(Pattern):
         others = [u for u in sc.users if u is not rs]
         if any(not (u.op == "call_method" and u.target == "size" and _only_user(u, rs)) for u in others):
             return None
-        return where.args[0], sc, [ub, where, tr, rs] + others
+        # the slices of the combined copy, in the order of the cat, with a flag per slice
+        src, width = sc.args[0], _val(sc.args[0]).shape[1] if isinstance(_val(sc.args[0]), torch.Tensor) else None
+        slices, masked = [], []
+        for q in parts_all:
+            if _is(q, operator.getitem):
+                slices.append(tuple(sc.args[1][q.args[1]]))
+                masked.append(True)
+                continue
+            if not (_is(q, aten.slice.Tensor) and q.args[0] is src and width is not None and len(q.args) >= 2 and q.args[1] in (1, -1)
+                    and (len(q.args) < 5 or q.args[4] == 1)):
+                return None
+            lo = q.args[2] if len(q.args) > 2 and q.args[2] is not None else 0
+            hi = q.args[3] if len(q.args) > 3 and q.args[3] is not None else width
+            if not (isinstance(lo, int) and isinstance(hi, int)):
+                return None
+            slices.append((lo, hi))
+            masked.append(False)
+        if stacked:
+            lens = {hi - lo for lo, hi in slices}
+            if len(lens) != 1 or min(lo for lo, _ in slices) < 0:
+                return None
+            return where.args[0], sc, [ub, where, tr, rs] + others, ("stack", [lo for lo, _ in slices], lens.pop(), masked)
+        return where.args[0], sc, [ub, where, tr, rs] + others, (slices, masked) if plain else None
 
     def process(self, gm: fx.GraphModule) -> bool:
         changed = False
         for node in list(gm.graph.nodes):
-            mask = sc = None
+            mask = sc = mixed = None
             dead = []
             if _is(node, aten.where.self) and len(node.args) == 3:
                 cand = node.args[2]
@@ -879,13 +911,19 @@ class FusedMaskedSliceCat(Pattern):
             else:
                 m = self._stacked_form(gm, node)
                 if m is not None:
-                    mask, sc, dead = m
-                    dead = list(node.args[0]) + dead
+                    mask, sc, dead, mixed = m
+                    dead = [q for q in node.args[0] if _is(q, operator.getitem)] + dead
             if sc is None:
                 continue
             _ensure(gm, "xg_masked_slice_cat", M.MaskedSliceCatModule)
             with gm.graph.inserting_before(node):
-                new = gm.graph.call_module("xg_masked_slice_cat", (sc.args[0], mask, sc.args[1]))
+                if mixed is not None and mixed[0] == "stack":
+                    _ensure(gm, "xg_masked_slice_stack", M.MaskedSliceStackModule)
+                    new = gm.graph.call_module("xg_masked_slice_stack", (sc.args[0], mask, mixed[1], mixed[2], mixed[3]))
+                elif mixed is None:
+                    new = gm.graph.call_module("xg_masked_slice_cat", (sc.args[0], mask, sc.args[1]))
+                else:
+                    new = gm.graph.call_module("xg_masked_slice_cat", (sc.args[0], mask, mixed[0], mixed[1]))
             _fill_meta(gm, new)
             node.replace_all_uses_with(new)
             gm.graph.erase_node(node)
