@@ -77,8 +77,9 @@ int xg_rmsnorm(const void* x, const void* residual, const void* weight, void* y,
                float eps, int dtype, int w_dtype, void* stream);
 
 /*
- * LayerNorm with optional fused residual add; weight and bias are both required, as in
- * passes/patterns/structure/custom_layernorm.py:25.
+ * LayerNorm with optional fused residual add; weight is required (as in
+ * passes/patterns/structure/custom_layernorm.py:25), bias may be null (layer_norm(..., bias=None), the configuration of
+ * the reference's own residual-add test, tests/mlu/test_fuse_addlayernorm.py:39-43).
  *   s = residual ? round_to_dtype(x + residual) : x
  *   y = to_dtype( (float(s) - mean) * rsqrt(var + eps) * float(weight) + float(bias) )
  * Replaces: passes/patterns/utils/default_replacements.py:28-36 (DefaultLayerNorm) as called by

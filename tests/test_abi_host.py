@@ -50,7 +50,7 @@ def test_argument_validation_without_gpu():
     assert L.xg_rmsnorm(p, None, p, p, None, 4, 8, 4, 0, 1e-6, lib.XG_BF16, lib.XG_BF16, None) == -1
     assert L.xg_rmsnorm(p, None, p, p, None, 4, 8, 8, 0, 1e-6, 7, 7, None) == -1
     assert L.xg_rmsnorm(p, None, p, p, p, 4, 8, 8, 0, 1e-6, lib.XG_BF16, lib.XG_BF16, None) == -1  # sum_out without residual
-    assert L.xg_layernorm(p, None, p, None, p, None, 4, 8, 8, 0, 1e-5, lib.XG_F32, lib.XG_F32, None) == -1  # bias required
+    assert L.xg_layernorm(p, None, None, None, p, None, 4, 8, 8, 0, 1e-5, lib.XG_F32, lib.XG_F32, None) == -1  # weight required (bias is not)
     assert L.xg_rope(p, p, p, p, 1, 1, 4, 7, 28, 28, 7, 28, 28, 7, lib.XG_F32, None) == -1  # odd head dim
     assert L.xg_swiglu(p, p, p, 4, 8, 4, 8, 8, lib.XG_F32, None) == -1
     assert L.xg_gemm_bias_act(p, p, None, None, p, 4, 4, 0, 4, 4, 4, 0, 1, 0, lib.XG_F32, None) == -1  # K == 0

@@ -39,6 +39,23 @@ def test_layer_norm(cuda_device, rows, hidden, dtype):
     assert_parity(got, ref_ops.layer_norm(x, w, b, 1e-5), f"layer_norm {rows}x{hidden} {dtype}")
 
 
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16, torch.float32])
+@pytest.mark.parametrize("rows,hidden", [(8, 1024), (33, 1000), (5, 8192)])
+def test_layer_norm_without_bias(cuda_device, rows, hidden, dtype):
+    """layer_norm(x, weight, bias=None), alone and behind a residual add with one and two outputs: the configuration of
+    the reference's residual-add test (tests/mlu/test_fuse_addlayernorm.py:39-43: [8, 1024], bias = None)."""
+    from xpu_graph_b200.modules import AddLayerNormModule, LayerNormModule
+
+    x, r, w, _ = _mk(rows, hidden, dtype, 6)
+    xd, rd, wd = (t.to(cuda_device) for t in (x, r, w))
+    assert_parity(LayerNormModule()(xd, wd, None, 1e-5), ref_ops.layer_norm(x, w, None, 1e-5), "layer_norm, no bias")
+    want_y, want_s = ref_ops.add_layer_norm(x, r, w, None, 1e-5)
+    assert_parity(AddLayerNormModule(False)(xd, rd, wd, None, 1e-5), want_y, "add_layer_norm, no bias")
+    y, s = AddLayerNormModule(True)(xd, rd, wd, None, 1e-5)
+    assert_parity(y, want_y, "add_layer_norm (2 outputs), no bias")
+    assert_bit_exact(s, want_s, "add_layer_norm sum, no bias")
+
+
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
 @pytest.mark.parametrize("rows,hidden", [(4, 64), (33, 1000), (64, 4096), (9, 8192), (3, 16384)])
 @pytest.mark.parametrize("store_sum", [False, True])

@@ -499,6 +499,29 @@ def test_combo_sum_after_multi_slice_cat(tgt, xlog):
     assert "combo_sum" in mods and not any("sum" in a for a in atens)
 
 
+def test_add_layer_norm_without_bias(tgt, xlog):
+    """The reference's residual-add LayerNorm test (tests/mlu/test_fuse_addlayernorm.py:17-43): torch.layer_norm with a
+    weight and bias=None on [8, 1024], the sum returned or not."""
+    g = torch.Generator().manual_seed(12)
+    x, r, w = torch.randn(8, 1024, generator=g), torch.randn(8, 1024, generator=g), torch.randn(1024, generator=g)
+
+    def fn0(inputs, residual, weight):
+        return torch.layer_norm(inputs + residual, normalized_shape=[1024], weight=weight, bias=None, eps=1e-5)
+
+    def fn1(inputs, residual, weight):
+        s = inputs + residual
+        return torch.layer_norm(s, normalized_shape=[1024], weight=weight, bias=None, eps=1e-5), s
+
+    want, got, mods, atens = _compile(tgt, fn0, x, r, w)
+    _same(got, want)
+    assert mods == ["xg_add_layer_norm_y"], (mods, atens)
+    torch._dynamo.reset()
+    want, got, mods, atens = _compile(tgt, fn1, x, r, w)
+    _same(got[0], want[0])
+    assert torch.equal(got[1], want[1])
+    assert mods == ["xg_add_layer_norm"], (mods, atens)
+
+
 def test_dense_tower(tgt, xlog):
     """Three chained fp32 Linear+ReLU layers, each large enough for the tensor-core path, collapse into one
     DenseTowerModule call; a small chain is left as separate dense layers."""

@@ -155,7 +155,12 @@ __global__ void __launch_bounds__((WPR == 1 ? 4 : WPR) * 32) norm_vec_kernel(con
             Vec16<T> o;
             if (LN) {
                 float bf[EPV];
-                load_coef<T>(p.b, p.w_is_f32, (int64_t)vi * EPV, bf);
+                if (p.b != nullptr) {  // LayerNorm without a bias (elementwise_affine with bias=None)
+                    load_coef<T>(p.b, p.w_is_f32, (int64_t)vi * EPV, bf);
+                } else {
+#pragma unroll
+                    for (int i = 0; i < EPV; ++i) bf[i] = 0.f;
+                }
 #pragma unroll
                 for (int i = 0; i < EPV; ++i)
                     o.v[i] = Cvt<T>::from_f((Cvt<T>::to_f(s[v].v[i]) - mean) * rstd * wf[i] + bf[i]);
@@ -214,8 +219,9 @@ __global__ void __launch_bounds__(128) norm_generic_kernel(const NormParams p) {
                                                         : Cvt<T>::to_f(reinterpret_cast<const T*>(p.w)[i]);
         float o;
         if (LN) {
-            const float bf = (p.w_is_f32 || sizeof(T) == 4) ? reinterpret_cast<const float*>(p.b)[i]
-                                                            : Cvt<T>::to_f(reinterpret_cast<const T*>(p.b)[i]);
+            const float bf = p.b == nullptr ? 0.f
+                             : ((p.w_is_f32 || sizeof(T) == 4) ? reinterpret_cast<const float*>(p.b)[i]
+                                                               : Cvt<T>::to_f(reinterpret_cast<const T*>(p.b)[i]));
             o = (sv - mean) * rstd * wf + bf;
         } else {
             o = sv * rstd * wf;
@@ -237,7 +243,7 @@ int launch_norm(const NormParams& p, cudaStream_t st, const char* name) {
     if (p.rows > 0x7fffffffLL) return fail(XG_ERR_TOO_LARGE, "%s: rows %lld exceed 2^31-1", name, (long long)p.rows);
     const bool w_f32 = p.w_is_f32 || sizeof(T) == 4;
     bool vec_ok = (p.hidden % EPV == 0) && aligned16(p.x) && (p.x_stride % EPV == 0) && aligned16(p.y) &&
-                  aligned16(p.w) && (!LN || aligned16(p.b)) &&
+                  aligned16(p.w) && (!LN || p.b == nullptr || aligned16(p.b)) &&
                   (!p.res || (aligned16(p.res) && p.res_stride % EPV == 0)) && (!p.sum_out || aligned16(p.sum_out));
     (void)w_f32;
     const int64_t nvec = p.hidden / EPV;
@@ -259,7 +265,7 @@ template <bool LN>
 int norm_entry(const char* name, const void* x, const void* residual, const void* weight, const void* bias, void* y,
                void* sum_out, int64_t rows, int64_t hidden, int64_t x_row_stride, int64_t res_row_stride, float eps,
                int dtype, int w_dtype, void* stream) {
-    if (!x || !weight || !y || (LN && !bias)) return fail(XG_ERR_INVALID_ARG, "%s: null x/weight/bias/y", name);
+    if (!x || !weight || !y) return fail(XG_ERR_INVALID_ARG, "%s: null x/weight/y", name);
     if (rows < 0 || hidden <= 0) return fail(XG_ERR_INVALID_ARG, "%s: bad extents rows=%lld hidden=%lld", name, (long long)rows, (long long)hidden);
     if (x_row_stride < hidden || (residual && res_row_stride < hidden))
         return fail(XG_ERR_INVALID_ARG, "%s: row stride smaller than hidden", name);

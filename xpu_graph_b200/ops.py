@@ -133,7 +133,7 @@ def _(x, residual, weight, eps):
 
 
 @torch.library.custom_op(f"{NS}::layer_norm", mutates_args=(), device_types="cuda")
-def layer_norm(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor, eps: float) -> torch.Tensor:
+def layer_norm(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor], eps: float) -> torch.Tensor:
     return _norm_call("ln", x, None, weight, bias, eps, False)
 
 
@@ -143,7 +143,7 @@ def _(x, weight, bias, eps):
 
 
 @torch.library.custom_op(f"{NS}::add_layer_norm", mutates_args=(), device_types="cuda")
-def add_layer_norm(x: torch.Tensor, residual: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor,
+def add_layer_norm(x: torch.Tensor, residual: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor],
                    eps: float) -> List[torch.Tensor]:
     y, s = _norm_call("ln", x, residual, weight, bias, eps, True)
     return [y, s]
@@ -155,7 +155,7 @@ def _(x, residual, weight, bias, eps):
 
 
 @torch.library.custom_op(f"{NS}::add_layer_norm_y", mutates_args=(), device_types="cuda")
-def add_layer_norm_y(x: torch.Tensor, residual: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor,
+def add_layer_norm_y(x: torch.Tensor, residual: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor],
                      eps: float) -> torch.Tensor:
     return _norm_call("ln", x, residual, weight, bias, eps, False)
 

@@ -104,8 +104,8 @@ class FusedNativeLayerNorm(Pattern):
                 continue
             x, shape, w, b, eps = node.args
             xv = _val(x)
-            if w is None or b is None or not _tensor_ok(xv) or xv.dim() < 1 or list(shape) != [xv.shape[-1]]:
-                continue
+            if w is None or not _tensor_ok(xv) or xv.dim() < 1 or list(shape) != [xv.shape[-1]]:
+                continue  # (a missing bias is fine: the kernel takes none)
             users = list(node.users)
             if not all(_is(u, operator.getitem) for u in users):
                 continue
