@@ -210,3 +210,28 @@ def test_reference_front_end_on_gpu(cuda_device):
             assert torch.equal(a, b)
         assert theirs.names and theirs.names == ours.names, (theirs.names, ours.names)
 
+
+def test_decomposed_attention_on_gpu(cuda_device):
+    """The decomposed attention graph of the reference's tests (tests/common/test_fuse_sdpa.py:14-25, fp16, 32 heads,
+    S = 38, E = 64, and a tensor-core shape) compiled for this target: one attention launch, no operand copies."""
+    import math
+
+    from oracle import ref_ops
+    from tests.helpers import LaunchCounter
+
+    def fn(query, key, value):
+        return torch.matmul(query, key.transpose(-2, -1)).div(math.sqrt(query.shape[-1])).softmax(dim=-1).matmul(value)
+
+    for B, H, S, E in ((2, 32, 38, 64), (2, 8, 256, 128)):
+        g = torch.Generator().manual_seed(14)
+        q, k, v = (torch.randn(B, H, S, E, generator=g).to(torch.float16) for _ in range(3))
+        compiled, got, mods, atens = _compile_run(fn, (q.to(cuda_device), k.to(cuda_device), v.to(cuda_device)))
+        assert mods == ["xg_sdpa"] and not any("clone" in a for a in atens), (mods, atens)
+        with LaunchCounter() as c:
+            with torch.no_grad():
+                got = compiled(q.to(cuda_device), k.to(cuda_device), v.to(cuda_device))
+        torch.cuda.synchronize()
+        assert c.names == ["xg_sdpa_fwd"], c.names
+        assert_parity(got, ref_ops.sdpa(q, k, v, None, None, False), f"decomposed attention {B}x{H}x{S}x{E}")
+        torch._dynamo.reset()
+

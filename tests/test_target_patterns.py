@@ -522,6 +522,25 @@ def test_add_layer_norm_without_bias(tgt, xlog):
     assert mods == ["xg_add_layer_norm"], (mods, atens)
 
 
+def test_decomposed_attention_operands_stay_views(tgt, xlog):
+    """matmul(q, k^T) / s -> softmax -> matmul(v) (the first form of the reference's attention tests,
+    tests/common/test_fuse_sdpa.py:14-25): FusedSDPA rewrites it with contiguous copies of q, k and v in front of the
+    attention call; the target replaces the copies by views, because its kernels address the operands by strides."""
+    import math
+
+    g = torch.Generator().manual_seed(13)
+    q, k, v = (torch.randn(2, 8, 38, 64, generator=g).to(torch.float16) for _ in range(3))
+
+    def fn(query, key, value):
+        return torch.matmul(query, key.transpose(-2, -1)).div(math.sqrt(64)).softmax(dim=-1).matmul(value)
+
+    want, got, mods, atens = _compile(tgt, fn, q, k, v)
+    _same(got, want, 5e-3)
+    assert mods == ["xg_sdpa"], mods
+    assert "Pattern.SdpaOperandViews changed graph" in xlog.text
+    assert not any("clone" in a for a in atens), atens
+
+
 def test_dense_tower(tgt, xlog):
     """Three chained fp32 Linear+ReLU layers, each large enough for the tensor-core path, collapse into one
     DenseTowerModule call; a small chain is left as separate dense layers."""

@@ -302,6 +302,45 @@ class FusedSdpa(Pattern):
         return changed
 
 
+class SdpaOperandViews(Pattern):
+    """The reference's FusedSDPA hands q, k, v to the attention call as  reshape(clone(x3, contiguous), [1, B*H, S, E])
+    (common/fuse_scaled_dot_product_attention.py:205-221): three materialised copies per call. The kernels behind
+    SDPAModule address q / k / v by strides, so a copy of a [B*H, S, E] operand whose last dim is contiguous is replaced
+    by unsqueeze(x3, 0), a view."""
+
+    _opt_level = OptLevel.level2
+    _pattern_group = PatternGroup.GROUP2
+
+    def process(self, gm: fx.GraphModule) -> bool:
+        changed = False
+        for node in list(gm.graph.nodes):
+            if not _module_call(gm, node, M.SDPAModule) or len(node.args) < 3:
+                continue
+            for i in range(3):
+                rs = node.args[i]
+                if not (_is(rs, *_RESHAPES) and _only_user(rs, node)):
+                    continue
+                cl = rs.args[0]
+                if not (_is(cl, aten.clone.default) and _only_user(cl, rs)):
+                    continue
+                x = cl.args[0]
+                xv, rv = _val(x), _val(rs)
+                if not (isinstance(xv, torch.Tensor) and isinstance(rv, torch.Tensor) and xv.dim() == 3 and rv.dim() == 4):
+                    continue
+                if not _static(xv.shape) or tuple(rv.shape) != (1,) + tuple(xv.shape) or xv.stride(-1) != 1:
+                    continue
+                if xv.dtype != torch.float32 and any(st % 8 for st in xv.stride()[:-1]):
+                    continue  # the tensor-core path wants 16-byte aligned rows: keep the copy
+                with gm.graph.inserting_before(node):
+                    view = gm.graph.call_function(aten.unsqueeze.default, (x, 0))
+                _fill_meta(gm, view)
+                node.replace_input_with(rs, view)
+                gm.graph.erase_node(rs)
+                gm.graph.erase_node(cl)
+                changed = True
+        return changed
+
+
 class FusedSdpaTensorScale(Pattern):
     """The reference's FusedSDPA keeps a tensor-valued softmax scale out of the aten call: at OptLevel.level2 it emits
     a ``SDPAWrappedScale`` module whose op reads the scalar on the host (default_replacements.py:39-55,
@@ -1338,7 +1377,7 @@ class FusedDenseTower(Pattern):
 
 
 ALL_PATTERNS = [FusedDenseTower, FusedComboDense, FusedSliceSumCat, FusedMulSumCat, FusedSumCat, FusedNativeLayerNorm,
-                FusedRmsNormLowered, FusedSdpa, FusedSdpaTensorScale, FusedRoPE, FusedEmbeddingStack, FusedSwiGLU,
+                FusedRmsNormLowered, FusedSdpa, FusedSdpaTensorScale, SdpaOperandViews, FusedRoPE, FusedEmbeddingStack, FusedSwiGLU,
                 FusedDenseResidual, FusedAddNorm, FusedCatLastDim, FusedDenseRope, FusedRowGather, GatherIndexRepeatToExpand,
                 FusedMaskedSliceCat]
 
