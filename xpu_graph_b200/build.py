@@ -25,7 +25,7 @@ SOURCES = [
     "gemm.cu",
     "gemm_tc.cu",
     "gemm_tc_ksplit.cu",
-    "gemm_mlp2.cu",
+    "gemm_mlp.cu",
     "gemm_f32.cu",
     "split_bf16x3.cu",
     "sdpa.cu",
