@@ -4,11 +4,10 @@
 // its share of the k-blocks with tcgen05.mma.cta_group::2 (each CTA loads 128 activation rows and 128 weight rows per
 // k-block, fp32 accumulators in TMEM), so every weight element enters exactly one SM once and the activations enter
 // S times fewer SMs than with independent 128-row CTAs. The S partial tiles are then added through distributed shared
-// memory: the tile's columns are dealt out to the pairs; each CTA copies the columns it does not own from TMEM into its
-// own (by then idle) pipeline buffers and hands them to their owners with one bulk shared-to-shared copy per owner
-// (cp.async.bulk.shared::cluster.shared::cta, completion counted in bytes on the owner's mbarrier), and the owner adds
-// the partials in split order (deterministic), applies bias / residual / activation and stores. No global scratch
-// memory, no second launch, no atomics.
+// memory: the tile's columns are dealt out to the pairs; each CTA sends the columns it does not own from TMEM through
+// registers straight into their owner's receive area (st.async to shared::cluster, 16 bytes per message, completion
+// counted in bytes on the owner's mbarrier), and the owner adds the partials in split order (deterministic), applies
+// bias / residual / activation and stores. No global scratch memory, no second launch, no atomics.
 //
 // Warp roles per CTA: warp 0 = TMA producer, warp 1 = MMA issuer (leader CTA of the pair only), warps 2..17 = epilogue
 // (a warp reads the 32 accumulator rows of its TMEM lane quadrant, 16 columns at a time; the four warps of a quadrant
@@ -71,11 +70,10 @@ __device__ __forceinline__ float act_of(float v, int act) {
 // chunks [lo, hi) of the tile's nch 32-column chunks are finished by pair s
 __device__ __forceinline__ int chunk_lo(int s, int S, int nch) { return (s * nch) / S; }
 
-// Bulk copy from this CTA's shared memory into a peer CTA's (both 16-byte aligned, size a multiple of 16); the bytes are
-// counted on the peer's mbarrier as they land. No multicast: one source, one destination.
-__device__ __forceinline__ void bulk_copy_to_peer(uint32_t peer_dst, uint32_t src, uint32_t bytes, uint32_t peer_bar) {
-    asm volatile("cp.async.bulk.shared::cluster.shared::cta.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-                 ::"r"(peer_dst), "r"(src), "r"(bytes), "r"(peer_bar)
+// 16 bytes from registers into a peer CTA's shared memory; the bytes are counted on the peer's mbarrier as they land.
+__device__ __forceinline__ void st_async_v4(uint32_t peer_dst, uint32_t a, uint32_t b, uint32_t c, uint32_t d, uint32_t peer_bar) {
+    asm volatile("st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.v4.b32 [%0], {%1, %2, %3, %4}, [%5];"
+                 ::"r"(peer_dst), "r"(a), "r"(b), "r"(c), "r"(d), "r"(peer_bar)
                  : "memory");
 }
 __device__ __forceinline__ void epilogue_bar_sync() { asm volatile("bar.sync 1, %0;" ::"n"(KS_EPI_WARPS * 32) : "memory"); }
@@ -246,7 +244,6 @@ gemm_tc_ksplit_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
         const int64_t row = (int64_t)mb * TILE + (int64_t)r * BM + row_in_cta;
         const uint32_t lane_field = (uint32_t)(quad * 32) << 16;
         const uint32_t recv_row = ptx::smem_u32(recv) + (uint32_t)(row_in_cta * 16);
-        const uint32_t stage_row = ptx::smem_u32(smem) + (uint32_t)(row_in_cta * 16);  // outgoing chunks reuse the pipeline buffers
         const int my_lo = chunk_lo(s, S, nch), my_hi = chunk_lo(s + 1, S, nch), mine = my_hi - my_lo;
         // the tile's bias row, once, while the main loop runs
         for (int i = (int)threadIdx.x - 64; i < TN; i += KS_EPI_WARPS * 32) {
@@ -257,36 +254,29 @@ gemm_tc_ksplit_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
         // All MMAs of this pair have completed: the accumulator is final and the pipeline buffers are idle.
         if (ok && S > 1) {
             ptx::tc_fence_after();
-            // ---- stage the chunks that other pairs finish. Staged list = all chunks outside [my_lo, my_hi), ascending,
-            //      so the chunks of one owner are contiguous here and in the owner's receive area. Work unit: 16 columns. ----
+            // ---- hand the chunks that other pairs finish to their owners, straight from registers (16 bytes per
+            //      message, counted on the owner's mbarrier). Work unit: 16 columns of this warp's 32 rows. ----
             const int n_units = 2 * (nch - mine);
 #pragma unroll 1
             for (int u = grp; u < n_units; u += GROUPS) {
                 const int j = u >> 1, half = u & 1;
                 const int c = j < my_lo ? j : j + mine;
+                int o = 0;
+                while (chunk_lo(o + 1, S, nch) <= c) ++o;  // the pair that finishes chunk c
+                const int lo = chunk_lo(o, S, nch), n_o = chunk_lo(o + 1, S, nch) - lo;
+                const int sender = s < o ? s : s - 1;      // this pair's slot among the owner's S - 1 senders
+                const uint32_t peer = (uint32_t)(2 * o) + r;
                 uint32_t v[16];
                 ptx::tmem_ld_32x16(tmem_base + lane_field + (uint32_t)(c * 32 + half * 16), v);
                 ptx::tmem_ld_wait();
-                const uint32_t d = stage_row + (uint32_t)(j * KS_CHUNK_BYTES + half * 4 * (BM * 16));
+                const uint32_t d = ptx::map_to_cta(recv_row + (uint32_t)((sender * n_o + (c - lo)) * KS_CHUNK_BYTES + half * 4 * (BM * 16)), peer);
+                const uint32_t pb = ptx::map_to_cta(ptx::smem_u32(recv_full), peer);
 #pragma unroll
                 for (int q = 0; q < 4; ++q)
-                    ptx::st_shared_v4(d + (uint32_t)(q * (BM * 16)), make_uint4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]));
+                    st_async_v4(d + (uint32_t)(q * (BM * 16)), v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3], pb);
             }
-            ptx::fence_proxy_async();  // the copies below read what was just written through the generic proxy
         }
         epilogue_bar_sync();  // reached by every epilogue thread, whatever `ok` says (also publishes bias_s)
-        if (ok && S > 1 && warp == 2 && ptx::elect_one()) {
-            for (int d = 1; d < S; ++d) {  // start with the next pair round the ring, so that the owners fill evenly
-                const int o = (s + d) % S;
-                const int lo = chunk_lo(o, S, nch), n_o = chunk_lo(o + 1, S, nch) - lo;
-                const int first = o < s ? lo : lo - mine;  // index of the owner's first chunk in the staged list
-                const int sender = s < o ? s : s - 1;      // this pair's slot among the owner's S - 1 senders
-                const uint32_t peer = (uint32_t)(2 * o) + r;
-                bulk_copy_to_peer(ptx::map_to_cta(ptx::smem_u32(recv) + (uint32_t)(sender * n_o * KS_CHUNK_BYTES), peer),
-                                  ptx::smem_u32(smem) + (uint32_t)(first * KS_CHUNK_BYTES), (uint32_t)(n_o * KS_CHUNK_BYTES),
-                                  ptx::map_to_cta(ptx::smem_u32(recv_full), peer));
-            }
-        }
         __syncwarp();
         // ---- finish the chunks this pair owns ----
         if (ok && S > 1) ok = __all_sync(0xffffffffu, ptx::mbar_wait_bounded(recv_full, 0, abort_flag));
