@@ -71,6 +71,7 @@ def test_dense_bf16_kn_weights(cuda_device, M, K, N, act):
 
 
 @pytest.mark.parametrize("M,K,N,act,with_res", [(64, 4096, 4096, "gelu", False), (32, 4096, 11008, "silu", False),
+                                                (16, 4096, 11008, "silu", False), (128, 4096, 2048, "gelu", False),
                                                 (128, 4096, 1000, "none", True), (100, 2048, 1002, "relu", True),
                                                 (16, 1024, 512, "gelu", True), (1, 4096, 4096, "none", False)])
 def test_dense_split_k(cuda_device, M, K, N, act, with_res):
@@ -79,7 +80,7 @@ def test_dense_split_k(cuda_device, M, K, N, act, with_res):
     from xpu_graph_b200 import lib
     from xpu_graph_b200.modules import DenseResidualModule
 
-    if (M, K, N) in ((64, 4096, 4096), (32, 4096, 11008), (1, 4096, 4096)):
+    if (M, K, N) in ((64, 4096, 4096), (16, 4096, 11008), (128, 4096, 2048), (1, 4096, 4096)):
         assert lib.load().xg_gemm_workspace_bytes(M, N, K, lib.XG_BF16) > 0, "shape expected to use split-K"
     x, w, b = _mk(M, K, N, torch.bfloat16, 28)
     g = torch.Generator().manual_seed(29)

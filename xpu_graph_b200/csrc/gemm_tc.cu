@@ -841,14 +841,26 @@ __global__ void __launch_bounds__(256) splitk_reduce_kernel(const GemmParams p) 
     const int ncol = (int)((p.N - col0) < 4 ? (p.N - col0) : 4);
     float acc[4] = {0.f, 0.f, 0.f, 0.f};
     const bool vec = (ncol == 4) && ((p.N & 3) == 0);
-    for (int s = 0; s < p.splits; ++s) {  // fixed order: deterministic
-        const float* src = p.split.partial + ((int64_t)s * p.M + row) * p.N + col0;
-        if (vec) {
-            const float4 f = *reinterpret_cast<const float4*>(src);
-            acc[0] += f.x; acc[1] += f.y; acc[2] += f.z; acc[3] += f.w;
-        } else {
-            for (int i = 0; i < ncol; ++i) acc[i] += src[i];
+    const float* src = p.split.partial + row * p.N + col0;
+    const int64_t plane = p.M * p.N;
+    int s = 0;
+    if (vec) {
+        // four planes in flight per thread (a dependent chain of single loads costs about 0.3 us per split); the
+        // additions stay in split order: deterministic
+        for (; s + 4 <= p.splits; s += 4) {
+            float4 f[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) f[j] = __ldcg(reinterpret_cast<const float4*>(src + (int64_t)(s + j) * plane));
+#pragma unroll
+            for (int j = 0; j < 4; ++j) { acc[0] += f[j].x; acc[1] += f[j].y; acc[2] += f[j].z; acc[3] += f[j].w; }
         }
+        for (; s < p.splits; ++s) {
+            const float4 f = __ldcg(reinterpret_cast<const float4*>(src + (int64_t)s * plane));
+            acc[0] += f.x; acc[1] += f.y; acc[2] += f.z; acc[3] += f.w;
+        }
+    } else {
+        for (; s < p.splits; ++s)
+            for (int i = 0; i < ncol; ++i) acc[i] += src[(int64_t)s * plane + i];
     }
     const T* bias = reinterpret_cast<const T*>(p.bias);
     const T* resid = reinterpret_cast<const T*>(p.residual);
@@ -1152,9 +1164,21 @@ bool use_cta_pairs(int64_t M, int64_t N, int out_bn) {
 }
 
 // Tile width and split-K factor for an [M, N, K] problem given `ws_bytes` of fp32 scratch (0 = none).
-// Without scratch: the widest tile that still gives every SM work. With scratch and a small M (the
-// weight-streaming regime, where a CTA's traffic is dominated by re-reading A once per n-tile): keep the
-// widest tile and split K so that (tiles x splits) fills the SMs in whole waves.
+// Larger M: the widest tile that still gives every SM work, no split. M <= 128 is the weight-streaming regime, where
+// what a CTA takes in through its SM decides: (128 + bn) rows of 128 bytes per k-block, and the activations again
+// for every column tile. There the plan is the cheapest of every (tile width, split) that runs as a single wave, by a
+// cost model in microseconds fitted to sweeps on B200 (K = 4096; M = 16..128; N = 512..11008; tile widths 64 / 128 /
+// 256; 1..16 splits; CUDA-graph replay):
+//   ingest  : 8.5 us per MB a CTA takes in (about 118 KB/us per SM), times the waves;
+//   tile    : 0.01 us per tile column (the epilogue of a wide tile is served by the same four warps);
+//   launch  : 2.5 us;
+//   a split : 4 us more (second launch, drain) and the fp32 partial sums written and read back: 0.13 us per MB while
+//             weights + partial sums stay within L2, 0.67 us per MB beyond that.
+// Measured examples (us; this plan / the previous one, which knew only 256-wide split tiles and took the narrowest
+// tile unsplit): 128 x 4096 x 4096 13.0 / 15.3; 64 x 4096 x 4096 11.1 / 14.2; 128 x 4096 x 2048 10.8 / 16.1;
+// 128 x 4096 x 11008 21.3 / 27.2; 64 x 4096 x 11008 19.9 / 27.0. At M = 256 a split through scratch loses to the
+// unsplit kernel (15.6 us vs 22.4 / 19.8 / 29.8 us for 2 / 4 / 8 splits at N = K = 4096); those shapes belong to the
+// cluster kernel, which reduces through shared memory.
 GemmPlan plan_gemm(int64_t M, int64_t N, int64_t K, int64_t ws_bytes, int sms) {
     GemmPlan pl;
     const int64_t mblk = (M + BM - 1) / BM;
@@ -1163,32 +1187,25 @@ GemmPlan plan_gemm(int64_t M, int64_t N, int64_t K, int64_t ws_bytes, int sms) {
     if (pl.bn == 128 && mblk * ((N + 127) / 128) < sms) pl.bn = 64;
     pl.splits = 1;
     const int64_t nkb = (K + BK - 1) / BK;
-    if (ws_bytes <= 0 || M > 128 || nkb < 8) return pl;  // measured: at M = 256 a split loses (see below)
-    // Small M is the weight-streaming regime. Two limits, both expressed in bytes one SM handles:
-    //   pull : what a CTA drags through its SM, (128 + bn) rows of 128 bytes per k-block, times the waves;
-    //   hbm  : the problem's DRAM traffic (weights + activations + the fp32 partial sums written and read
-    //          back by a split) divided over the SMs at the measured ratio of HBM to per-SM L2 bandwidth (~45x).
-    // A split also pays a second launch. Measured on B200: at M = 256 the partial sums cost more than the
-    // split saves (15.6 us unsplit vs 22.4 / 19.8 / 29.8 us for 2 / 4 / 8 splits at N = K = 4096, with the reduce pass
-    // launched programmatically), so only smaller M ends up split.
-    const int64_t tiles256 = mblk * ((N + 255) / 256);
-    const int64_t tiles_bn = mblk * ((N + pl.bn - 1) / pl.bn);
-    const double io_bytes = 2.0 * ((double)N * K + (double)M * K + (double)M * N);
-    const double ratio = 45.0, launch_cost = 0.4e6;
-    auto cost_of = [&](double pull, double partial_bytes, bool split) {
-        const double hbm = (io_bytes + partial_bytes) / ratio;
-        return (pull > hbm ? pull : hbm) + (split ? launch_cost : 0.0);
-    };
-    double best = cost_of((double)((tiles_bn + sms - 1) / sms) * (BM + pl.bn) * 128.0 * (double)nkb, 0.0, false) * 0.9;
-    for (int s = 2; s <= 16 && s * 4 <= nkb; ++s) {
-        if ((int64_t)s * M * N * 4 > ws_bytes) break;
-        const double waves = (double)((tiles256 * s + sms - 1) / sms);
-        const double pull = waves * (BM + 256) * 128.0 * ((double)nkb / s);
-        const double c = cost_of(pull, 2.0 * s * (double)M * N * 4.0, true);
-        if (c < best) {
-            best = c;
-            pl.bn = 256;
-            pl.splits = s;
+    if (M > 128 || nkb < 8) return pl;
+    const double w_mb = 2.0 * (double)N * (double)K / 1e6;
+    double best = 1e30;
+    for (int bn = 64; bn <= 256; bn *= 2) {
+        const int64_t tiles = mblk * ((N + bn - 1) / bn);
+        const double per_kblock_mb = (double)(BM + bn) * 128.0 / 1e6;
+        for (int s = 1; s <= 16; ++s) {
+            if (s > 1 && (s * 4 > nkb || (int64_t)s * M * N * 4 > ws_bytes || tiles * s > sms)) break;
+            const double waves = (double)((tiles * s + sms - 1) / sms);
+            double c = waves * (double)((nkb + s - 1) / s) * per_kblock_mb * 8.5 + 0.01 * bn + 2.5;
+            if (s > 1) {
+                const double partial_mb = 2.0 * s * (double)M * (double)N * 4.0 / 1e6;
+                c += 4.0 + partial_mb * (w_mb + partial_mb < 96.0 ? 0.13 : 0.67);
+            }
+            if (c < best) {
+                best = c;
+                pl.bn = bn;
+                pl.splits = s;
+            }
         }
     }
     return pl;
