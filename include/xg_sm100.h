@@ -238,16 +238,18 @@ int xg_mlp3_bias_act(const void* x, const void* w1, const void* b1, const void* 
                      int dtype, void* stream);
 
 /*
- * Grouped form: out[e] = act( A[e] @ W[e] + bias[e] ) for `count` problems of one shape [M, N, K] whose operands lie
- * wherever the caller has them: A, W, bias (nullable table, nullable entries) and out are host arrays of `count` device
- * pointers; one launch per 12 entries walks (entry, tile) work units with each entry's own tensor maps, so nothing
- * is stacked or copied. 16-bit dtypes; every A[e] / W[e] 16-byte aligned, lda / ldw multiples of 8 elements.
+ * Grouped form: out[e] = act( A[e] @ W[e] + bias[e] + residual[e] ) for `count` problems of one shape [M, N, K] whose
+ * operands lie wherever the caller has them: A, W, bias, residual (nullable tables, nullable entries; bias[e] a row of N,
+ * residual[e] an [M, N] matrix with row stride ldr) and out are host arrays of `count` device pointers, so nothing is
+ * stacked or copied. 16-bit dtypes: one launch per 12 entries walks (entry, tile) work units with each entry's own
+ * tensor maps; every A[e] / W[e] 16-byte aligned, lda / ldw multiples of 8 elements. fp32: one launch per 24 entries of
+ * the FMA kernels (true fp32, any alignment), the entry being the grid's third dimension.
  * Replaces: the grouped-GEMM form of targets/mlu/combo_matmul.py:87-113 (FusedCombineBmm.forward_groupgemm ->
  * torch.ops.torch_mlu.grouped_gemm), emitted by FusedCombineMatMul (:116-232).
  */
-int xg_gemm_group_bias_act(const void* const* A, const void* const* W, const void* const* bias, void* const* out,
-                           int64_t count, int64_t M, int64_t N, int64_t K, int64_t lda, int64_t ldw, int64_t ldc,
-                           int trans_b, int act, int dtype, void* stream);
+int xg_gemm_group_bias_act(const void* const* A, const void* const* W, const void* const* bias,
+                           const void* const* residual, void* const* out, int64_t count, int64_t M, int64_t N, int64_t K,
+                           int64_t lda, int64_t ldw, int64_t ldc, int64_t ldr, int trans_b, int act, int dtype, void* stream);
 
 /*
  * Dual GEMM with SwiGLU epilogue: out = silu(A @ Wg^T) * (A @ Wu^T); Wg, Wu: [N, K] (Linear layout).

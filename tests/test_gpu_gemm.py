@@ -566,23 +566,79 @@ def test_combo_dense(cuda_device, T, M, K, N, weight_trans, with_bias):
     assert_parity(got, want, f"combo_dense grouped T={T} {M}x{K}x{N}")
 
 
+@pytest.mark.parametrize("T,M,K,N,weight_trans,bias_kind", [(8, 5, 8, 7, False, "matrix"), (8, 5, 8, 7, False, "row"),
+                                                             (8, 5, 8, 7, True, "none"), (6, 40, 64, 48, True, "row"),
+                                                             (30, 33, 100, 70, True, "matrix"), (5, 300, 256, 520, False, "row"),
+                                                             (4, 1024, 192, 1024, True, "matrix")])
+def test_combo_dense_fp32(cuda_device, T, M, K, N, weight_trans, bias_kind):
+    """fp32 layers in one grouped launch of the FMA kernels (the entry is the grid's third dimension; 30 layers need two
+    launches of at most 24): the reference's own sizes (tests/mlu/test_combo_matmul.py:90-100: T = 8, 5 x 8 x 7, [K, N]
+    weights, full-matrix or row biases) and sizes that reach each of the three kernel choices, against fp64 math."""
+    from xpu_graph_b200.modules import ComboDenseModule
+
+    g = torch.Generator().manual_seed(34)
+    xs = [torch.randn(M, K, generator=g) for _ in range(T)]
+    ws = [0.05 * torch.randn(N, K, generator=g) for _ in range(T)]
+    if not weight_trans:
+        ws = [w.t().contiguous() for w in ws]
+    if bias_kind == "none":
+        bs = [None] * T
+    else:
+        bs = [0.05 * torch.randn((M, N) if bias_kind == "matrix" else (N,), generator=g) for _ in range(T)]
+    want = []
+    for x, w, b in zip(xs, ws, bs):
+        y = x.double() @ (w.double().t() if weight_trans else w.double())
+        want.append(torch.relu(y if b is None else y + b.double()).float())
+    with LaunchCounter() as calls:
+        got = ComboDenseModule()([x.to(cuda_device) for x in xs], [w.to(cuda_device) for w in ws],
+                                 [b.to(cuda_device) if b is not None else None for b in bs], "relu", weight_trans)
+    torch.cuda.synchronize()
+    assert calls.names == ["xg_gemm_group_bias_act"], calls.names
+    assert_parity(got, torch.stack(want), f"combo_dense fp32 grouped T={T} {M}x{K}x{N} {bias_kind}")
+
+
+def test_combo_dense_full_matrix_biases_16bit(cuda_device):
+    """Full [M, N] addends per layer (the addmm(bias, x, w) form of tests/mlu/test_combo_matmul.py:33-39) ride in the
+    grouped tensor-core kernel's epilogue as per-entry residuals; layers may mix them with none."""
+    from xpu_graph_b200 import lib
+    from xpu_graph_b200.modules import ComboDenseModule
+
+    g = torch.Generator().manual_seed(35)
+    T, M, K, N = 13, 130, 264, 200
+    xs = [torch.randn(M, K, generator=g).to(torch.bfloat16) for _ in range(T)]
+    ws = [(0.05 * torch.randn(N, K, generator=g)).to(torch.bfloat16) for _ in range(T)]
+    bs = [torch.randn(M, N, generator=g).to(torch.bfloat16) for _ in range(T)]
+    want = torch.stack([torch.relu(x.float() @ w.float().t() + b.float()) for x, w, b in zip(xs, ws, bs)]).to(torch.bfloat16)
+    with LaunchCounter() as calls:
+        got = ComboDenseModule()([x.to(cuda_device) for x in xs], [w.to(cuda_device) for w in ws], [b.to(cuda_device) for b in bs],
+                                 "relu", True)
+    torch.cuda.synchronize()
+    assert calls.names == ["xg_gemm_group_bias_act"] and lib.tc_status() == 0
+    assert_parity(got, want, "combo_dense bf16 with [M, N] addends", magnitude=torch.stack(bs))
+
+
 def test_combo_dense_fallback_to_the_batched_form(cuda_device):
-    """fp32 layers do not qualify for the grouped kernel: separate tensors are stacked, slabs of one buffer are used in
-    place, and the batched entry point runs them."""
+    """Layers the grouped kernels cannot address (16-bit rows that are not multiples of 16 bytes) go through the batched
+    entry point: separate tensors are stacked, slabs of one buffer are used in place."""
     from xpu_graph_b200 import ops
     from xpu_graph_b200.modules import ComboDenseModule
 
     g = torch.Generator().manual_seed(34)
     T, M, K, N = 4, 40, 64, 48
     xs = [torch.randn(M, K, generator=g) for _ in range(T)]
-    ws = [0.05 * torch.randn(N, K, generator=g) for _ in range(T)]
-    bs = [0.05 * torch.randn(N, generator=g) for _ in range(T)]
-    want = torch.stack([ref_ops.dense(x.double(), w.double(), True, b.double(), "relu").float() for x, w, b in zip(xs, ws, bs)])
     xcat = torch.stack(xs).to(cuda_device)
-    wcat = torch.stack(ws).to(cuda_device)
     assert ops._stack_or_view(list(xcat.unbind(0))).data_ptr() == xcat.data_ptr()  # no copy for slabs of one buffer
-    got = ComboDenseModule()(list(xcat.unbind(0)), list(wcat.unbind(0)), [b.to(cuda_device) for b in bs], "relu", True)
-    assert_parity(got, want, "combo_dense fp32 (batched form)")
+    xs16 = [x.to(torch.bfloat16) for x in xs]
+    ws16 = [(0.05 * torch.randn(N, K, generator=g)).to(torch.bfloat16) for _ in range(T)]
+    bs16 = [(0.05 * torch.randn(N, generator=g)).to(torch.bfloat16) for _ in range(T)]
+    want = torch.stack([ref_ops.dense(x, w, True, b, "relu") for x, w, b in zip(xs16, ws16, bs16)])
+    pad = torch.zeros(T, M, K + 4, dtype=torch.bfloat16, device=cuda_device)  # rows of 136 bytes: no tensor map for them
+    pad[:, :, :K] = torch.stack(xs16).to(cuda_device)
+    with LaunchCounter() as calls:
+        got = ComboDenseModule()([pad[i, :, :K] for i in range(T)], [w.to(cuda_device) for w in ws16],
+                                 [b.to(cuda_device) for b in bs16], "relu", True)
+    assert "xg_gemm_group_bias_act" not in calls.names, calls.names
+    assert_parity(got, want, "combo_dense (batched form)")
 
 
 @pytest.mark.parametrize("act", ["gelu", "silu"])

@@ -235,3 +235,38 @@ def test_decomposed_attention_on_gpu(cuda_device):
         assert_parity(got, ref_ops.sdpa(q, k, v, None, None, False), f"decomposed attention {B}x{H}x{S}x{E}")
         torch._dynamo.reset()
 
+
+
+def test_combo_matmul_forms_on_gpu(cuda_device):
+    """The reference's combo test at its own dtype and sizes (tests/mlu/test_combo_matmul.py:33-39, 57-79, 90-100: fp32,
+    eight 5 x 8 x 7 layers with full-matrix addends over one shared input, and relu(F.linear(x_i, w_i.T)) over eight
+    split inputs) compiled for this target: one grouped launch each, compared with fp64 math."""
+    from tests.helpers import LaunchCounter
+
+    T, M, K, N = 8, 5, 8, 7
+    g = torch.Generator().manual_seed(15)
+    shared, split = torch.randn(1, M, K, generator=g), torch.randn(T, M, K, generator=g)
+    ws = [torch.randn(K, N, generator=g) for _ in range(T)]
+    mats = [torch.randn(M, N, generator=g) for _ in range(T)]
+
+    def shared_bias_relu(x, *wb):
+        x = x.squeeze(0)
+        return tuple(torch.relu(x @ wi + bi) for wi, bi in zip(wb[:T], wb[T:]))
+
+    def split_linear_t(x, *w):
+        xs = [i.squeeze(0) for i in x.split(x.shape[0] // T, dim=0)]
+        return tuple(torch.relu(torch.nn.functional.linear(xi, wi.T)) for xi, wi in zip(xs, w))
+
+    for fn, args in ((shared_bias_relu, (shared, *ws, *mats)), (split_linear_t, (split, *ws))):
+        dev_args = tuple(a.to(cuda_device) for a in args)
+        compiled, got, mods, atens = _compile_run(fn, dev_args)
+        assert mods.count("xg_combo_dense") == 1 and "custom_dense_layer_replacement" not in mods, mods
+        with LaunchCounter() as c:
+            with torch.no_grad():
+                got = compiled(*dev_args)
+        torch.cuda.synchronize()
+        assert c.names == ["xg_gemm_group_bias_act"], c.names
+        want = fn(*(a.double() for a in args))
+        for o, w in zip(got, want):
+            assert_parity(o, w.float(), f"combo {fn.__name__}")
+        torch._dynamo.reset()

@@ -646,6 +646,49 @@ def test_combo_dense(tgt, xlog):
             assert "Pattern.FusedComboDense changed graph" in xlog.text and "custom_dense_layer_replacement" not in mods
 
 
+def test_combo_dense_reference_forms_fp32(tgt, xlog):
+    """The graphs of the reference's combo test at its own dtype and sizes (tests/mlu/test_combo_matmul.py:17-100:
+    fp32, T = 8, one shared or eight split inputs of 5 x 8, [K, N] weights of 8 x 7, no bias / a row of 7 / a full
+    5 x 7 addend per layer, with and without relu) end in one grouped call each."""
+    g = torch.Generator().manual_seed(12)
+    T, M, K, N = 8, 5, 8, 7
+    shared = torch.randn(1, M, K, generator=g)
+    split = torch.randn(T, M, K, generator=g)
+    ws = [torch.randn(K, N, generator=g) for _ in range(T)]
+    rows = [torch.randn(N, generator=g) for _ in range(T)]
+    mats = [torch.randn(M, N, generator=g) for _ in range(T)]
+
+    def shared_plain(x, *w):
+        x = x.squeeze(0)
+        return tuple(x @ wi for wi in w)
+
+    def shared_bias(x, *wb):
+        x = x.squeeze(0)
+        return tuple(x @ wi + bi for wi, bi in zip(wb[:T], wb[T:]))
+
+    def shared_bias_relu(x, *wb):
+        x = x.squeeze(0)
+        return tuple(torch.relu(x @ wi + bi) for wi, bi in zip(wb[:T], wb[T:]))
+
+    def split_relu(x, *w):
+        xs = [i.squeeze(0) for i in x.split(x.shape[0] // T, dim=0)]
+        return tuple(torch.relu(xi @ wi) for xi, wi in zip(xs, w))
+
+    def split_linear_t(x, *w):
+        xs = [i.squeeze(0) for i in x.split(x.shape[0] // T, dim=0)]
+        return tuple(torch.relu(torch.nn.functional.linear(xi, wi.T)) for xi, wi in zip(xs, w))
+
+    cases = [("fn0", shared_plain, (shared, *ws)), ("fn2", shared_bias, (shared, *ws, *mats)), ("fn4", shared_bias, (shared, *ws, *rows)),
+             ("fn5", shared_bias_relu, (shared, *ws, *mats)), ("fn6", split_relu, (split, *ws)), ("fn7", split_linear_t, (split, *ws))]
+    for name, fn, args in cases:
+        want, got, mods, atens = _compile(tgt, fn, *args)
+        for w, o in zip(want, got):
+            _same(o, w, 1e-5)
+        assert mods.count("xg_combo_dense") == 1 and "custom_dense_layer_replacement" not in mods, (name, mods)
+        assert not any(a in ("mm", "addmm", "matmul", "relu") for a in atens), (name, atens)
+        torch._dynamo.reset()
+
+
 def test_sum_cat_fusions(tgt, xlog):
     """slice -> sum -> cat, mul -> sum -> cat and sum -> cat along the last dim become one module call each
     (graph forms of targets/mlu/fuse_sum_cat.py and fuse_mul_sum_cat.py; the reference's tests

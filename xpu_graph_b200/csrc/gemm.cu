@@ -30,9 +30,12 @@ bool plan_ksplit(int64_t M, int64_t N, int64_t K, int dtype, int* S_out, int* tn
 int gemm_tc_ksplit_entry(const void* A, const void* W, const void* bias, const void* residual, void* out, int64_t M,
                          int64_t N, int64_t K, int64_t lda, int64_t ldw, int64_t ldc, int64_t ldr, int act, int dtype, int S,
                          int tn, cudaStream_t st);
-int gemm_group_entry(const void* const* A, const void* const* W, const void* const* bias, void* const* out, int64_t count,
-                     int64_t M, int64_t N, int64_t K, int64_t lda, int64_t ldw, int64_t ldc, int trans_b, int act, int dtype,
-                     cudaStream_t st);
+int gemm_group_entry(const void* const* A, const void* const* W, const void* const* bias, const void* const* residual,
+                     void* const* out, int64_t count, int64_t M, int64_t N, int64_t K, int64_t lda, int64_t ldw, int64_t ldc,
+                     int64_t ldr, int trans_b, int act, int dtype, cudaStream_t st);
+int gemm_f32_group_entry(const void* const* A, const void* const* W, const void* const* bias, const void* const* residual,
+                         void* const* out, int64_t count, int64_t M, int64_t N, int64_t K, int64_t lda, int64_t ldw,
+                         int64_t ldc, int64_t ldr, int trans_b, int act, cudaStream_t st);
 int read_tc_status(unsigned int* host_out, int reset);
 int read_sdpa_status(unsigned int* host_out, int reset);
 int read_ksplit_status(unsigned int* host_out, int reset);
@@ -141,18 +144,27 @@ extern "C" int xg_bgemm_bias_act(const void* A, const void* B, const void* bias,
     return XG_OK;
 }
 
-extern "C" int xg_gemm_group_bias_act(const void* const* A, const void* const* W, const void* const* bias, void* const* out,
-                                      int64_t count, int64_t M, int64_t N, int64_t K, int64_t lda, int64_t ldw, int64_t ldc,
-                                      int trans_b, int act, int dtype, void* stream) {
+extern "C" int xg_gemm_group_bias_act(const void* const* A, const void* const* W, const void* const* bias,
+                                      const void* const* residual, void* const* out, int64_t count, int64_t M, int64_t N,
+                                      int64_t K, int64_t lda, int64_t ldw, int64_t ldc, int64_t ldr, int trans_b, int act,
+                                      int dtype, void* stream) {
     using namespace xg;
     if (count < 0) return fail(XG_ERR_INVALID_ARG, "xg_gemm_group_bias_act: negative count");
     if (count == 0 || M == 0 || N == 0) return XG_OK;
     if (!A || !W || !out) return fail(XG_ERR_INVALID_ARG, "xg_gemm_group_bias_act: null pointer table");
     if (M < 0 || N < 0 || K <= 0) return fail(XG_ERR_INVALID_ARG, "xg_gemm_group_bias_act: bad extents");
-    if (dtype != XG_BF16 && dtype != XG_F16) return fail(XG_ERR_UNSUPPORTED, "xg_gemm_group_bias_act: 16-bit dtypes only");
+    if (dtype != XG_BF16 && dtype != XG_F16 && dtype != XG_F32) return fail(XG_ERR_UNSUPPORTED, "xg_gemm_group_bias_act: unsupported dtype %d", dtype);
     if (act < XG_ACT_NONE || act > XG_ACT_SIGMOID) return fail(XG_ERR_INVALID_ARG, "xg_gemm_group_bias_act: bad activation %d", act);
-    if (lda < K || ldc < N || ldw < (trans_b ? K : N)) return fail(XG_ERR_INVALID_ARG, "xg_gemm_group_bias_act: leading dimension too small");
-    return gemm_group_entry(A, W, bias, out, count, M, N, K, lda, ldw, ldc, trans_b, act, dtype, reinterpret_cast<cudaStream_t>(stream));
+    bool has_residual = false;
+    for (int64_t e = 0; residual && e < count; ++e) has_residual = has_residual || residual[e] != nullptr;
+    if (!has_residual) residual = nullptr;
+    if (lda < K || ldc < N || ldw < (trans_b ? K : N) || (has_residual && ldr < N))
+        return fail(XG_ERR_INVALID_ARG, "xg_gemm_group_bias_act: leading dimension too small");
+    if (dtype == XG_F32)
+        return gemm_f32_group_entry(A, W, bias, residual, out, count, M, N, K, lda, ldw, ldc, ldr, trans_b, act,
+                                    reinterpret_cast<cudaStream_t>(stream));
+    return gemm_group_entry(A, W, bias, residual, out, count, M, N, K, lda, ldw, ldc, ldr, trans_b, act, dtype,
+                            reinterpret_cast<cudaStream_t>(stream));
 }
 
 extern "C" int xg_gemm_swiglu(const void* A, const void* Wg, const void* Wu, void* out, int64_t M, int64_t N, int64_t K,

@@ -30,7 +30,7 @@ __device__ __forceinline__ float act_f32(float v, int act) {
 
 // 256 threads; thread (ty, tx) owns a TM x TN micro-tile; BM = 16*TM, BN = 16*TN.
 template <int TM, int TN, int BK>
-__global__ void __launch_bounds__(256) gemm_f32_kernel(const GemmF32Params p) {
+__device__ __forceinline__ void gemm_f32_tile(const GemmF32Params& p) {
     constexpr int BM = 16 * TM, BN = 16 * TN;
     __shared__ __align__(16) float As[2][BK][BM + 4];
     __shared__ __align__(16) float Bs[2][BK][BN + 4];
@@ -131,6 +131,38 @@ __global__ void __launch_bounds__(256) gemm_f32_kernel(const GemmF32Params p) {
     }
 }
 
+template <int TM, int TN, int BK>
+__global__ void __launch_bounds__(256) gemm_f32_kernel(const GemmF32Params p) {
+    gemm_f32_tile<TM, TN, BK>(p);
+}
+
+// Grouped form: blockIdx.z picks the entry; its five pointers come from a table in the kernel's parameter space, the
+// extents, strides and activation are shared by the group.
+constexpr int kF32GroupMax = 24;  // 24 x 5 pointers = 960 bytes of parameters
+struct GemmF32Group {
+    const float* A[kF32GroupMax];
+    const float* B[kF32GroupMax];
+    const float* bias[kF32GroupMax];
+    const float* residual[kF32GroupMax];
+    float* out[kF32GroupMax];
+};
+__device__ __forceinline__ GemmF32Params entry_params(const GemmF32Params& p, const GemmF32Group& g) {
+    GemmF32Params pe = p;
+    const int e = blockIdx.z;
+    pe.A = g.A[e];
+    pe.B = g.B[e];
+    pe.bias = g.bias[e];
+    pe.residual = g.residual[e];
+    pe.out = g.out[e];
+    return pe;
+}
+
+template <int TM, int TN, int BK>
+__global__ void __launch_bounds__(256) gemm_f32_group_kernel(const GemmF32Params p, const __grid_constant__ GemmF32Group g) {
+    const GemmF32Params pe = entry_params(p, g);
+    gemm_f32_tile<TM, TN, BK>(pe);
+}
+
 // Small problems (fewer 64 x 64 tiles than SMs) are latency-bound in the kernel above: every 16-wide k-tile costs a
 // round trip to L2. This variant gives each CTA a small output tile and the whole K-panel of both operands, 256 k at
 // a time, fetched with one burst of 16-byte asynchronous copies, so a k-chunk costs one round trip; the inner
@@ -147,7 +179,7 @@ __device__ __forceinline__ void cp_async16(void* smem_dst, const void* gsrc, boo
 }
 
 template <int TM, int TN>
-__global__ void __launch_bounds__(128) gemm_f32_panel_kernel(const GemmF32Params p) {
+__device__ __forceinline__ void gemm_f32_panel_tile(const GemmF32Params& p) {
     constexpr int BM = 8 * TM, BN = 16 * TN;
     extern __shared__ __align__(16) float panel[];
     float* As = panel;                      // [BM][kPanelPitch]
@@ -214,6 +246,32 @@ __global__ void __launch_bounds__(128) gemm_f32_panel_kernel(const GemmF32Params
 }
 
 template <int TM, int TN>
+__global__ void __launch_bounds__(128) gemm_f32_panel_kernel(const GemmF32Params p) {
+    gemm_f32_panel_tile<TM, TN>(p);
+}
+
+template <int TM, int TN>
+__global__ void __launch_bounds__(128) gemm_f32_panel_group_kernel(const GemmF32Params p, const __grid_constant__ GemmF32Group g) {
+    const GemmF32Params pe = entry_params(p, g);
+    gemm_f32_panel_tile<TM, TN>(pe);
+}
+
+template <int TM, int TN>
+int launch_panel_group(const GemmF32Params& p, const GemmF32Group& g, int count, cudaStream_t st) {
+    constexpr int BM = 8 * TM, BN = 16 * TN;
+    constexpr int smem = (BM + BN) * kPanelPitch * (int)sizeof(float);
+    auto kern = gemm_f32_panel_group_kernel<TM, TN>;
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) {
+        cudaGetLastError();
+        return fail(XG_ERR_LAUNCH, "xg_gemm_group_bias_act(f32): cannot reserve %d bytes of shared memory: %s", smem, cudaGetErrorString(e));
+    }
+    dim3 grid((unsigned)((p.N + BN - 1) / BN), (unsigned)((p.M + BM - 1) / BM), (unsigned)count);
+    kern<<<grid, 128, smem, st>>>(p, g);
+    return check_launch("xg_gemm_group_bias_act(f32)");
+}
+
+template <int TM, int TN>
 int launch_panel(const GemmF32Params& p, cudaStream_t st) {
     constexpr int BM = 8 * TM, BN = 16 * TN;
     constexpr int smem = (BM + BN) * kPanelPitch * (int)sizeof(float);
@@ -255,6 +313,50 @@ int gemm_f32_entry(const void* A, const void* B, const void* bias, const void* r
         gemm_f32_kernel<4, 4, 16><<<grid, 256, 0, st>>>(p);
     }
     return check_launch("xg_gemm_bias_act(f32)");
+}
+
+// out[e] = act(A[e] @ W[e] + bias[e] + residual[e]) for `count` fp32 problems of one shape; the operands stay where
+// they are (a pointer per entry). One launch per 24 entries; the kernel is chosen as for a single problem with `count`
+// times the tiles.
+int gemm_f32_group_entry(const void* const* A, const void* const* W, const void* const* bias, const void* const* residual,
+                         void* const* out, int64_t count, int64_t M, int64_t N, int64_t K, int64_t lda, int64_t ldw,
+                         int64_t ldc, int64_t ldr, int trans_b, int act, cudaStream_t st) {
+    if (M * N == 0) return XG_OK;
+    if ((M + 15) / 16 > 65535) return fail(XG_ERR_TOO_LARGE, "xg_gemm_group_bias_act(f32): M too large");
+    for (int64_t first = 0; first < count; first += kF32GroupMax) {
+        const int n = (int)((count - first) < kF32GroupMax ? (count - first) : kF32GroupMax);
+        GemmF32Group g;
+        bool aligned = true;
+        for (int e = 0; e < kF32GroupMax; ++e) {
+            const int64_t i = first + (e < n ? e : 0);  // unused slots repeat the first entry and are never read
+            if (!A[i] || !W[i] || !out[i])
+                return fail(XG_ERR_INVALID_ARG, "xg_gemm_group_bias_act: null pointer in entry %lld", (long long)i);
+            g.A[e] = reinterpret_cast<const float*>(A[i]);
+            g.B[e] = reinterpret_cast<const float*>(W[i]);
+            g.bias[e] = bias ? reinterpret_cast<const float*>(bias[i]) : nullptr;
+            g.residual[e] = residual ? reinterpret_cast<const float*>(residual[i]) : nullptr;
+            g.out[e] = reinterpret_cast<float*>(out[i]);
+            aligned = aligned && aligned16(A[i]) && aligned16(W[i]);
+        }
+        GemmF32Params p{nullptr, nullptr, nullptr, nullptr, nullptr, M, N, K, lda, ldw, ldc, ldr, trans_b, act};
+        const int64_t tiles64 = ((M + 63) / 64) * ((N + 63) / 64) * n;
+        const bool panel_ok = trans_b && K % 4 == 0 && lda % 4 == 0 && ldw % 4 == 0 && aligned;
+        int rc;
+        if (panel_ok && tiles64 < num_sms()) {
+            const int64_t tiles_32x64 = ((M + 31) / 32) * ((N + 63) / 64) * n;
+            rc = tiles_32x64 * 3 >= 2LL * num_sms() ? launch_panel_group<4, 4>(p, g, n, st) : launch_panel_group<2, 2>(p, g, n, st);
+        } else if (((M + 127) / 128) * ((N + 127) / 128) * n >= 2LL * num_sms()) {
+            dim3 grid((unsigned)((N + 127) / 128), (unsigned)((M + 127) / 128), (unsigned)n);
+            gemm_f32_group_kernel<8, 8, 16><<<grid, 256, 0, st>>>(p, g);
+            rc = check_launch("xg_gemm_group_bias_act(f32)");
+        } else {
+            dim3 grid((unsigned)((N + 63) / 64), (unsigned)((M + 63) / 64), (unsigned)n);
+            gemm_f32_group_kernel<4, 4, 16><<<grid, 256, 0, st>>>(p, g);
+            rc = check_launch("xg_gemm_group_bias_act(f32)");
+        }
+        if (rc != XG_OK) return rc;
+    }
+    return XG_OK;
 }
 
 }  // namespace xg

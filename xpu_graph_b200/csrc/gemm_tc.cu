@@ -914,12 +914,13 @@ int launch_gemm_tc(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorM
 // (a pointer per entry, no stacked copy). The persistent single-CTA kernel above, with the entry's tensor maps and
 // pointers taken from a table in the kernel's parameter space instead of a third tensor-map coordinate.
 // ---------------------------------------------------------------------------------------------------------
-constexpr int kGroupMax = 12;  // entries per launch: 12 x (2 tensor maps + 2 pointers) = 3264 bytes of parameters
+constexpr int kGroupMax = 12;  // entries per launch: 12 x (2 tensor maps + 3 pointers) = 3360 bytes of parameters
 struct GroupTable {
     CUtensorMap a[kGroupMax];
     CUtensorMap w[kGroupMax];
     void* out[kGroupMax];
     const void* bias[kGroupMax];
+    const void* resid[kGroupMax];
 };
 
 template <typename T, int BN, bool B_MN>
@@ -1055,6 +1056,7 @@ gemm_tc_group_kernel(const __grid_constant__ GroupTable tab, const GemmParams p,
             GemmParams pe = p;  // this entry's pointers; everything else is shared by the group
             pe.out = tab.out[entry];
             pe.bias = tab.bias[entry];
+            pe.residual = tab.resid[entry];
             const int64_t row = (int64_t)mb * BM + quad * 32 + lane;
             epilogue_tile<T, BN, false>(pe, tmem_base, acc, quad, row, row < p.M, nb, 0, 0);
             ptx::tc_fence_before();
@@ -1089,9 +1091,9 @@ int launch_gemm_group(const GroupTable& tab, const GemmParams& p, int count, cud
 }
 
 template <typename T>
-int gemm_group_dispatch(const void* const* A, const void* const* W, const void* const* bias, void* const* out, int64_t count,
-                        int64_t M, int64_t N, int64_t K, int64_t lda, int64_t ldw, int64_t ldc, int trans_b, int act,
-                        cudaStream_t st) {
+int gemm_group_dispatch(const void* const* A, const void* const* W, const void* const* bias, const void* const* residual,
+                        void* const* out, int64_t count, int64_t M, int64_t N, int64_t K, int64_t lda, int64_t ldw, int64_t ldc,
+                        int64_t ldr, int trans_b, int act, cudaStream_t st) {
     constexpr bool is_bf16 = std::is_same<T, __nv_bfloat16>::value;
     const int64_t mblk = (M + BM - 1) / BM;
     int bn = 256;
@@ -1101,7 +1103,7 @@ int gemm_group_dispatch(const void* const* A, const void* const* W, const void* 
     p.out = nullptr;
     p.bias = nullptr;
     p.residual = nullptr;
-    p.M = M; p.N = N; p.K = K; p.ldc = ldc; p.ldr = 0;
+    p.M = M; p.N = N; p.K = K; p.ldc = ldc; p.ldr = ldr;
     p.act = act;
     p.mode = kModePlain;
     p.split.partial = nullptr;
@@ -1126,7 +1128,8 @@ int gemm_group_dispatch(const void* const* A, const void* const* W, const void* 
                 return fail(XG_ERR_UNSUPPORTED, "xg_gemm_group_bias_act: tensor-map encoding failed for entry %lld", (long long)(first + e));
             tab.out[e] = o;
             tab.bias[e] = bias ? bias[first + e] : nullptr;
-            vec = vec && aligned16(o);
+            tab.resid[e] = residual ? residual[first + e] : nullptr;
+            vec = vec && aligned16(o) && (!tab.resid[e] || (ldr % 8 == 0 && aligned16(tab.resid[e])));
             bias_vec = bias_vec && (!tab.bias[e] || aligned16(tab.bias[e]));
         }
         for (int e = n; e < kGroupMax; ++e) {  // unused slots: valid descriptors, never dereferenced
@@ -1134,6 +1137,7 @@ int gemm_group_dispatch(const void* const* A, const void* const* W, const void* 
             tab.w[e] = tab.w[0];
             tab.out[e] = nullptr;
             tab.bias[e] = nullptr;
+            tab.resid[e] = nullptr;
         }
         p.vec_ok = vec ? 1 : 0;
         p.bias_vec_ok = bias_vec ? 1 : 0;
@@ -1412,17 +1416,17 @@ int bgemm_tc_entry(const void* A, const void* B, const void* bias, const void* r
 }
 
 // Grouped dense layers (one shape, a pointer per entry): see gemm_tc_group_kernel.
-int gemm_group_entry(const void* const* A, const void* const* W, const void* const* bias, void* const* out, int64_t count,
-                     int64_t M, int64_t N, int64_t K, int64_t lda, int64_t ldw, int64_t ldc, int trans_b, int act, int dtype,
-                     cudaStream_t st) {
+int gemm_group_entry(const void* const* A, const void* const* W, const void* const* bias, const void* const* residual,
+                     void* const* out, int64_t count, int64_t M, int64_t N, int64_t K, int64_t lda, int64_t ldw, int64_t ldc,
+                     int64_t ldr, int trans_b, int act, int dtype, cudaStream_t st) {
     if (lda % 8 != 0 || ldw % 8 != 0)
         return fail(XG_ERR_UNSUPPORTED, "xg_gemm_group_bias_act: row strides must be multiples of 8 elements");
     if (M > (int64_t)BM * 0x7fffff || N > (int64_t)64 * 0x7fffff || K > 0x7fffffff ||
         count * ((M + BM - 1) / BM) * ((N + 63) / 64) > 0x7fffffffLL)
         return fail(XG_ERR_TOO_LARGE, "xg_gemm_group_bias_act: extent too large");
     if (dtype == XG_BF16)
-        return gemm_group_dispatch<__nv_bfloat16>(A, W, bias, out, count, M, N, K, lda, ldw, ldc, trans_b, act, st);
-    return gemm_group_dispatch<__half>(A, W, bias, out, count, M, N, K, lda, ldw, ldc, trans_b, act, st);
+        return gemm_group_dispatch<__nv_bfloat16>(A, W, bias, residual, out, count, M, N, K, lda, ldw, ldc, ldr, trans_b, act, st);
+    return gemm_group_dispatch<__half>(A, W, bias, residual, out, count, M, N, K, lda, ldw, ldc, ldr, trans_b, act, st);
 }
 
 // ---- fp32 problems on the bf16 tensor cores ------------------------------------------------------------

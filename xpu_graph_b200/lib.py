@@ -55,8 +55,8 @@ SIGNATURES = {
     "xg_bgemm_bias_act": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64,
                                   c_int64, c_int64, c_int64, c_int64, c_int64, c_int64, c_int64, c_int64, c_int64,
                                   c_int, c_int, c_int, c_void_p]),
-    "xg_gemm_group_bias_act": (c_int, [_VPP, _VPP, _VPP, _VPP, c_int64, c_int64, c_int64, c_int64, c_int64, c_int64, c_int64,
-                                       c_int, c_int, c_int, c_void_p]),
+    "xg_gemm_group_bias_act": (c_int, [_VPP, _VPP, _VPP, _VPP, _VPP, c_int64, c_int64, c_int64, c_int64, c_int64, c_int64,
+                                       c_int64, c_int64, c_int, c_int, c_int, c_void_p]),
     "xg_mlp2_supported": (c_int, [c_int64, c_int64, c_int64, c_int64, c_int]),
     "xg_mlp3_supported": (c_int, [c_int64, c_int64, c_int64, c_int64, c_int64, c_int]),
     "xg_mlp3_bias_act": (c_int, [c_void_p] * 8 + [c_int64] * 10 + [c_int] * 5 + [c_void_p]),

@@ -523,9 +523,10 @@ def _(x, weight, weight_trans, bias, residual, act):
 @torch.library.custom_op(f"{NS}::combo_dense", mutates_args=(), device_types="cuda")
 def combo_dense(inputs: List[torch.Tensor], weights: List[torch.Tensor], weight_trans: bool,
                 biases: List[Optional[torch.Tensor]], act: str) -> torch.Tensor:
-    """T same-shape dense layers act(x_t @ W_t + b_t) in one launch; returns the stacked [T, M, N] result. 16-bit
-    operands are used in place through the grouped kernel (a pointer per layer, no stacking copy); anything else goes
-    through the batched form, for which operands that are not consecutive slabs of one buffer are stacked first."""
+    """T same-shape dense layers act(x_t @ W_t + b_t) in one launch; returns the stacked [T, M, N] result. Operands are
+    used in place through the grouped kernels (a pointer per layer, no stacking copy: tensor-core kernel for 16-bit,
+    FMA kernel for fp32); what those cannot address goes through the batched form, for which operands that are not
+    consecutive slabs of one buffer are stacked first. b_t: None, a row of N, or a full [M, N] addend."""
     T = len(inputs)
     if T == 0 or len(weights) != T or len(biases) != T:
         raise ValueError("xg_sm100::combo_dense: one input, weight and bias entry per layer")
@@ -534,20 +535,37 @@ def combo_dense(inputs: List[torch.Tensor], weights: List[torch.Tensor], weight_
         return grouped
     x = _stack_or_view(inputs)
     w = _stack_or_view(weights)
-    has_bias = biases[0] is not None
-    if any((b is not None) != has_bias for b in biases):
-        raise ValueError("xg_sm100::combo_dense: either every layer has a bias or none")
-    b = torch.stack([bi.reshape(1, -1) for bi in biases]) if has_bias else None  # [T, 1, N]
-    return batch_dense(x, w, weight_trans, b, None, act)
+    M = inputs[0].shape[0]
+    N = weights[0].shape[0] if weight_trans else weights[0].shape[1]
+    kinds = {_bias_kind(b, M, N) for b in biases}
+    if len(kinds) != 1:
+        raise ValueError("xg_sm100::combo_dense: the layers' biases must be of one kind (none, a row of N, or [M, N])")
+    kind = kinds.pop()
+    b = torch.stack([bi.reshape(1, -1) for bi in biases]) if kind == 1 else None  # [T, 1, N]
+    r = torch.stack([bi.reshape(M, N) for bi in biases]) if kind == 2 else None   # [T, M, N]
+    return batch_dense(x, w, weight_trans, b, r, act)
+
+
+def _bias_kind(b: Optional[torch.Tensor], M: int, N: int) -> int:
+    """0: none; 1: a per-column bias ([N] or [1, N]); 2: a full [M, N] addend (dense_layer_modules.py:22-57)."""
+    if b is None:
+        return 0
+    if b.numel() == N and (b.dim() == 1 or (b.dim() == 2 and b.shape[0] == 1)):
+        return 1
+    if b.dim() == 2 and tuple(b.shape) == (M, N):
+        return 2
+    raise ValueError(f"xg_sm100::combo_dense: bias of shape {tuple(b.shape)} for an [{M}, {N}] result")
 
 
 def _combo_dense_grouped(inputs, weights, weight_trans: bool, biases, act: str) -> Optional[torch.Tensor]:
     """The grouped launch: every layer's operands are used where they are (a pointer per entry), the results land side
-    by side in one [T, M, N] tensor. Returns None when the operands do not qualify (fp32, shapes that differ, rows a
-    tensor map cannot address), and the caller falls back to the stacked batched form."""
+    by side in one [T, M, N] tensor. A bias is a row of N or a full [M, N] addend, layer by layer. Returns None when
+    the operands do not qualify (shapes that differ; 16-bit rows a tensor map cannot address), and the caller falls back
+    to the stacked batched form."""
     x0, w0 = inputs[0], weights[0]
-    if x0.dtype not in (torch.bfloat16, torch.float16) or x0.dim() != 2 or w0.dim() != 2:
+    if x0.dtype not in (torch.bfloat16, torch.float16, torch.float32) or x0.dim() != 2 or w0.dim() != 2:
         return None
+    tc = x0.dtype != torch.float32
     xs = [_mat(t) for t in inputs]
     rows = [_weight_rows(t, weight_trans) for t in weights]
     if any(r[1] != rows[0][1] for r in rows):
@@ -558,19 +576,27 @@ def _combo_dense_grouped(inputs, weights, weight_trans: bool, biases, act: str) 
     lda, ldw = _row_stride(xs[0]), _row_stride(ws[0])
     for x, w in zip(xs, ws):
         if (x.shape != xs[0].shape or w.shape != ws[0].shape or x.dtype != x0.dtype or w.dtype != x0.dtype
-                or _row_stride(x) != lda or _row_stride(w) != ldw or x.data_ptr() % 16 or w.data_ptr() % 16):
+                or _row_stride(x) != lda or _row_stride(w) != ldw or (tc and (x.data_ptr() % 16 or w.data_ptr() % 16))):
             return None
-    if (ws[0].shape[1] if weight_trans else ws[0].shape[0]) != K or lda % 8 or ldw % 8:
+    if (ws[0].shape[1] if weight_trans else ws[0].shape[0]) != K or (tc and (lda % 8 or ldw % 8)):
         return None
-    bs = [None if b is None else b.reshape(-1).to(x0.dtype).contiguous() for b in biases]
-    if any(b is not None and b.numel() != N for b in bs):
-        return None
+    kinds = [_bias_kind(b, M, N) for b in biases]
+    bs = [b.reshape(-1).to(x0.dtype).contiguous() if k == 1 else None for b, k in zip(biases, kinds)]
+    rs = [_mat(b.to(x0.dtype)) if k == 2 else None for b, k in zip(biases, kinds)]
+    ldr = 0
+    if any(r is not None for r in rs):
+        strides = {_row_stride(r) for r in rs if r is not None}
+        if len(strides) != 1:
+            rs = [None if r is None else r.contiguous() for r in rs]
+            strides = {N}
+        ldr = strides.pop()
     out = torch.empty((len(xs), M, N), dtype=x0.dtype, device=x0.device)
     step = M * N * out.element_size()
     rc = _lib.load().xg_gemm_group_bias_act(
         _lib.ptr_array([x.data_ptr() for x in xs]), _lib.ptr_array([w.data_ptr() for w in ws]),
-        _lib.ptr_array([0 if b is None else b.data_ptr() for b in bs]), _lib.ptr_array([out.data_ptr() + i * step for i in range(len(xs))]),
-        len(xs), M, N, K, lda, ldw, N, 1 if weight_trans else 0, _lib.ACT_CODES[act], _code(x0.dtype), _stream(x0))
+        _lib.ptr_array([0 if b is None else b.data_ptr() for b in bs]), _lib.ptr_array([0 if r is None else r.data_ptr() for r in rs]),
+        _lib.ptr_array([out.data_ptr() + i * step for i in range(len(xs))]),
+        len(xs), M, N, K, lda, ldw, N, ldr, 1 if weight_trans else 0, _lib.ACT_CODES[act], _code(x0.dtype), _stream(x0))
     _lib.check(rc, "xg_gemm_group_bias_act")
     return out
 

@@ -1244,8 +1244,9 @@ COMBO_MIN_WIDTH = 4  # the reference's default width (utils/combo_utils.py:40-41
 
 
 class FusedComboDense(Pattern):
-    """>= 4 independent dense layers of one shape, dtype, orientation and activation -> one ComboDenseModule call
-    (a grouped launch) + unbind. The graph form of targets/mlu/combo_matmul.py:116-232, restricted to groups whose
+    """>= 4 independent dense layers of one shape, dtype, orientation, bias kind (none, a row, a full [M, N] addend) and
+    activation -> one ComboDenseModule call (a grouped launch: tensor-core kernel for 16-bit, FMA kernel for small fp32
+    members) + unbind. The graph form of targets/mlu/combo_matmul.py:116-232, restricted to groups whose
     operands are all defined before the group's first member, or whose results are all used after its last member, so
     that the combined node can take that member's place without reordering the graph."""
 
@@ -1253,6 +1254,8 @@ class FusedComboDense(Pattern):
     _pattern_group = PatternGroup.GROUP2
 
     def process(self, gm: fx.GraphModule) -> bool:
+        from .. import ops as _ops
+
         order = {n: i for i, n in enumerate(gm.graph.nodes)}
         groups = {}
         for n in gm.graph.nodes:
@@ -1262,13 +1265,25 @@ class FusedComboDense(Pattern):
             xv, wv, bv, v = _val(x), _val(w), _val(bias), _val(n)
             if not (_tensor_ok(xv, 2) and _tensor_ok(wv, 2) and _tensor_ok(v, 2) and _static(xv.shape) and _static(wv.shape)):
                 continue
-            if xv.dtype not in (torch.bfloat16, torch.float16) or wv.dtype != xv.dtype:
-                continue  # the batched launch is a 16-bit tensor-core path
-            if xv.shape[1] % 8 != 0 or wv.shape[1] % 8 != 0:
-                continue  # rows must be addressable by a tensor map
-            if bias is not None and not (isinstance(bv, torch.Tensor) and bv.numel() == v.shape[1] and bv.dim() <= 2 and bv.dtype == xv.dtype):
+            if xv.dtype not in (torch.bfloat16, torch.float16, torch.float32) or wv.dtype != xv.dtype:
                 continue
-            key = (tuple(xv.shape), tuple(wv.shape), bool(wt), bias is not None, act, xv.dtype)
+            if xv.dtype == torch.float32:
+                # the grouped fp32 launch is the FMA kernel; members large enough for the tensor-core path stay single
+                if 2 * xv.shape[0] * xv.shape[1] * v.shape[1] >= _ops.F32_TENSOR_MIN_FLOPS:
+                    continue
+            elif xv.shape[1] % 8 != 0 or wv.shape[1] % 8 != 0:
+                continue  # 16-bit rows must be addressable by a tensor map
+            kind = 0
+            if bias is not None:
+                if not (isinstance(bv, torch.Tensor) and bv.dtype == xv.dtype and _static(bv.shape)):
+                    continue
+                if bv.numel() == v.shape[1] and (bv.dim() == 1 or (bv.dim() == 2 and bv.shape[0] == 1)):
+                    kind = 1  # a row of N
+                elif bv.dim() == 2 and tuple(bv.shape) == tuple(v.shape):
+                    kind = 2  # a full [M, N] addend
+                else:
+                    continue
+            key = (tuple(xv.shape), tuple(wv.shape), bool(wt), kind, act, xv.dtype)
             groups.setdefault(key, []).append(n)
         changed = False
         for key, nodes in groups.items():
