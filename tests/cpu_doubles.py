@@ -142,4 +142,13 @@ def register():
         return torch.stack([dense(x, w, weight_trans, b, None, act) for x, w, b in zip(inputs, weights, biases)])
 
     k(ops.combo_dense)(combo_dense)
+
+    def combo_batch_dense(inputs, weights, weight_trans, biases, act):
+        outs = []
+        for x, w, b in zip(inputs, weights, biases):
+            y = torch.bmm(x, w.transpose(1, 2) if weight_trans else w)
+            outs.append(ref_ops._ACTS[act](y if b is None else y + b))
+        return torch.stack(outs)
+
+    k(ops.combo_batch_dense)(combo_batch_dense)
     _DONE = True

@@ -617,6 +617,38 @@ def test_combo_dense_full_matrix_biases_16bit(cuda_device):
     assert_parity(got, want, "combo_dense bf16 with [M, N] addends", magnitude=torch.stack(bs))
 
 
+@pytest.mark.parametrize("dtype,T,S,M,K,N,weight_trans,bias_kind", [
+    (torch.float32, 8, 3, 5, 6, 7, False, "full"), (torch.float32, 8, 3, 5, 6, 7, False, "none"),
+    (torch.float32, 5, 4, 33, 64, 48, True, "row"), (torch.bfloat16, 6, 4, 64, 128, 96, True, "full"),
+    (torch.bfloat16, 4, 5, 40, 64, 200, False, "row")])
+def test_combo_batch_dense(cuda_device, dtype, T, S, M, K, N, weight_trans, bias_kind):
+    """Lists of bmm in one grouped launch over the T * S products (a pointer per product; the shared input of the
+    reference's form, tests/mlu/test_combo_matmul.py:25-30 and 102-109, is read in place by every member), against
+    fp64 math."""
+    from xpu_graph_b200 import lib
+    from xpu_graph_b200.modules import ComboBatchDenseModule
+
+    g = torch.Generator().manual_seed(36)
+    x = torch.randn(S, M, K, generator=g).to(dtype)
+    ws = [(0.1 * torch.randn(S, N, K, generator=g)).to(dtype) for _ in range(T)]
+    if not weight_trans:
+        ws = [w.transpose(1, 2).contiguous() for w in ws]
+    shape = {"full": (S, M, N), "row": (S, 1, N)}.get(bias_kind)
+    bs = [torch.randn(shape, generator=g).to(dtype) if shape else None for _ in range(T)]
+    want = []
+    for w, b in zip(ws, bs):
+        y = torch.bmm(x.double(), w.double().transpose(1, 2) if weight_trans else w.double())
+        want.append(torch.relu(y if b is None else y + b.double()).to(dtype))
+    xd = x.to(cuda_device)
+    with LaunchCounter() as calls:
+        got = ComboBatchDenseModule()([xd] * T, [w.to(cuda_device) for w in ws],
+                                      [b.to(cuda_device) if b is not None else None for b in bs], "relu", weight_trans)
+    torch.cuda.synchronize()
+    assert set(calls.names) == {"xg_gemm_group_bias_act"} and lib.tc_status() == 0, calls.names
+    mag = torch.stack([b.broadcast_to((S, M, N)) for b in bs]) if shape else None
+    assert_parity(got, torch.stack(want), f"combo_batch_dense {dtype} T={T} S={S} {M}x{K}x{N} {bias_kind}", magnitude=mag)
+
+
 def test_combo_dense_fallback_to_the_batched_form(cuda_device):
     """Layers the grouped kernels cannot address (16-bit rows that are not multiples of 16 bytes) go through the batched
     entry point: separate tensors are stacked, slabs of one buffer are used in place."""

@@ -689,6 +689,30 @@ def test_combo_dense_reference_forms_fp32(tgt, xlog):
         torch._dynamo.reset()
 
 
+def test_combo_batch_dense_reference_forms(tgt, xlog):
+    """Lists of bmm over one shared input (tests/mlu/test_combo_matmul.py:25-30, 41-46, 102-109: fp32, T = 8, S = 3,
+    5 x 6 x 7, without and with full [S, M, K] addends) -> one grouped call over the T * S products."""
+    g = torch.Generator().manual_seed(13)
+    T, S, M, K, N = 8, 3, 5, 6, 7
+    x = torch.randn(S, M, K, generator=g)
+    ws = [torch.randn(S, K, N, generator=g) for _ in range(T)]
+    bs = [torch.randn(S, M, N, generator=g) for _ in range(T)]
+
+    def plain(x, *w):
+        return tuple(torch.bmm(x, wi) for wi in w)
+
+    def with_addend(x, *wb):
+        return tuple(x @ wi + bi for wi, bi in zip(wb[:T], wb[T:]))
+
+    for name, fn, args in (("fn1", plain, (x, *ws)), ("fn3", with_addend, (x, *ws, *bs))):
+        want, got, mods, atens = _compile(tgt, fn, *args)
+        for w, o in zip(want, got):
+            _same(o, w, 1e-5)
+        assert mods.count("xg_combo_batch_dense") == 1 and "custom_batch_dense_layer_replacement" not in mods, (name, mods)
+        assert not any(a in ("bmm", "baddbmm", "matmul") for a in atens), (name, atens)
+        torch._dynamo.reset()
+
+
 def test_sum_cat_fusions(tgt, xlog):
     """slice -> sum -> cat, mul -> sum -> cat and sum -> cat along the last dim become one module call each
     (graph forms of targets/mlu/fuse_sum_cat.py and fuse_mul_sum_cat.py; the reference's tests

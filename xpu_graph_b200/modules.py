@@ -310,6 +310,15 @@ class ComboDenseModule(torch.nn.Module):
         return _X.combo_dense(list(input_list), list(weight_list), bool(weight_trans), list(bias_list), str(act))
 
 
+class ComboBatchDenseModule(torch.nn.Module):
+    """Many same-shape batched dense layers (lists of bmm) in one grouped launch: forward(input_list, weight_list,
+    bias_list, act, weight_trans) -> [T, S, M, N] (callers unbind it). The place of FusedCombineBmm's stacked-bmm form,
+    targets/mlu/combo_matmul.py:22-86."""
+
+    def forward(self, input_list, weight_list, bias_list, act, weight_trans):
+        return _X.combo_batch_dense(list(input_list), list(weight_list), bool(weight_trans), list(bias_list), str(act))
+
+
 class DenseTowerModule(torch.nn.Module):
     """A chain of dense layers in one call: forward(x, weights, weight_trans, biases, acts) with one entry per layer.
     Stands where the reference fuses serial matmuls into one kernel (targets/mlu/fuse_densetower.py:272-316,

@@ -620,6 +620,38 @@ def _(inputs, weights, weight_trans, biases, act):
     return torch.empty((len(inputs), inputs[0].shape[0], N), dtype=inputs[0].dtype, device=inputs[0].device)
 
 
+@torch.library.custom_op(f"{NS}::combo_batch_dense", mutates_args=(), device_types="cuda")
+def combo_batch_dense(inputs: List[torch.Tensor], weights: List[torch.Tensor], weight_trans: bool,
+                      biases: List[Optional[torch.Tensor]], act: str) -> torch.Tensor:
+    """T same-shape batched dense layers act(bmm(x_t, W_t) + b_t), x_t [S, M, K], W_t [S, K, N] (or [S, N, K]), in one
+    grouped launch over the T * S matrix products (a pointer per product: batch entries of a member, also broadcast
+    ones, are addressed where they lie); returns [T, S, M, N]. b_t: None, a full [S, M, N] addend, or anything that
+    broadcasts to [S, 1, N]."""
+    T = len(inputs)
+    if T == 0 or len(weights) != T or len(biases) != T:
+        raise ValueError("xg_sm100::combo_batch_dense: one input, weight and bias entry per layer")
+    S, M, _ = inputs[0].shape
+    N = weights[0].shape[1] if weight_trans else weights[0].shape[2]
+    xs, ws, bs = [], [], []
+    for x, w, b in zip(inputs, weights, biases):
+        if x.dim() != 3 or w.dim() != 3 or x.shape[0] != S or w.shape[0] != S:
+            raise ValueError("xg_sm100::combo_batch_dense: every member is [S, M, K] x [S, K, N] with one S")
+        if b is not None:
+            b = b if tuple(b.shape) == (S, M, N) else b.broadcast_to((S, 1, N))
+        for i in range(S):
+            xs.append(x[i])
+            ws.append(w[i])
+            bs.append(None if b is None else b[i])
+    return combo_dense(xs, ws, weight_trans, bs, act).view(T, S, M, N)
+
+
+@combo_batch_dense.register_fake
+def _(inputs, weights, weight_trans, biases, act):
+    S, M, _ = inputs[0].shape
+    N = weights[0].shape[1] if weight_trans else weights[0].shape[2]
+    return torch.empty((len(inputs), S, M, N), dtype=inputs[0].dtype, device=inputs[0].device)
+
+
 @torch.library.custom_op(f"{NS}::dense_swiglu", mutates_args=(), device_types="cuda")
 def dense_swiglu(x: torch.Tensor, w_gate: torch.Tensor, w_up: torch.Tensor) -> torch.Tensor:
     """silu(x @ w_gate^T) * (x @ w_up^T); weights in Linear layout [N, K]."""

@@ -25,6 +25,7 @@ from .. import modules as M
 aten = torch.ops.aten
 INT64_MAX = 9223372036854775807
 DENSE_NAME = "custom_dense_layer_replacement"  # sub-module name used by structure/custom_denselayer.py:82
+BATCH_DENSE_NAME = "custom_batch_dense_layer_replacement"  # ... and by structure/custom_denselayer.py:108-115
 _RESHAPES = (aten.reshape.default, aten.view.default, aten._unsafe_view.default)
 
 
@@ -43,6 +44,13 @@ def _tensor_ok(v, dims: Optional[int] = None) -> bool:
     if v.dtype not in M._SUPPORTED or v.device.type not in M.ALLOWED_DEVICE_TYPES:
         return False
     return dims is None or v.dim() == dims
+
+
+def _broadcasts_to(shape, target) -> bool:
+    try:
+        return tuple(torch.broadcast_shapes(tuple(shape), tuple(target))) == tuple(target)
+    except RuntimeError:
+        return False
 
 
 def _static(shape) -> bool:
@@ -1244,48 +1252,57 @@ COMBO_MIN_WIDTH = 4  # the reference's default width (utils/combo_utils.py:40-41
 
 
 class FusedComboDense(Pattern):
-    """>= 4 independent dense layers of one shape, dtype, orientation, bias kind (none, a row, a full [M, N] addend) and
+    """>= 4 independent dense layers of one shape, dtype, orientation, bias kind (none, a row, a full addend) and
     activation -> one ComboDenseModule call (a grouped launch: tensor-core kernel for 16-bit, FMA kernel for small fp32
-    members) + unbind. The graph form of targets/mlu/combo_matmul.py:116-232, restricted to groups whose
-    operands are all defined before the group's first member, or whose results are all used after its last member, so
-    that the combined node can take that member's place without reordering the graph."""
+    members) + unbind; the same for batched dense layers (lists of bmm) -> ComboBatchDenseModule. The graph form of
+    targets/mlu/combo_matmul.py:116-232, restricted to groups whose operands are all defined before the group's first
+    member, or whose results are all used after its last member, so that the combined node can take that member's
+    place without reordering the graph."""
 
     _opt_level = OptLevel.level2
     _pattern_group = PatternGroup.GROUP2
 
     def process(self, gm: fx.GraphModule) -> bool:
+        return (self._combine(gm, M.DenseLayerModule, DENSE_NAME, 2, "xg_combo_dense", M.ComboDenseModule)
+                or self._combine(gm, M.BatchDenseLayerModule, BATCH_DENSE_NAME, 3, "xg_combo_batch_dense", M.ComboBatchDenseModule))
+
+    def _combine(self, gm, member_cls, member_name, rank, combo_name, combo_cls) -> bool:
         from .. import ops as _ops
 
         order = {n: i for i, n in enumerate(gm.graph.nodes)}
         groups = {}
         for n in gm.graph.nodes:
-            if not (_module_call(gm, n, M.DenseLayerModule) and n.target == DENSE_NAME and len(n.args) == 5):
+            if not (_module_call(gm, n, member_cls) and n.target == member_name and len(n.args) == 5):
                 continue
             x, w, wt, bias, act = n.args
             xv, wv, bv, v = _val(x), _val(w), _val(bias), _val(n)
-            if not (_tensor_ok(xv, 2) and _tensor_ok(wv, 2) and _tensor_ok(v, 2) and _static(xv.shape) and _static(wv.shape)):
+            if not (_tensor_ok(xv, rank) and _tensor_ok(wv, rank) and _tensor_ok(v, rank) and _static(xv.shape) and _static(wv.shape)):
                 continue
             if xv.dtype not in (torch.bfloat16, torch.float16, torch.float32) or wv.dtype != xv.dtype:
                 continue
+            if rank == 3 and xv.shape[0] != wv.shape[0]:
+                continue
+            rows, k, cols = v.shape[-2], xv.shape[-1], v.shape[-1]
             if xv.dtype == torch.float32:
                 # the grouped fp32 launch is the FMA kernel; members large enough for the tensor-core path stay single
-                if 2 * xv.shape[0] * xv.shape[1] * v.shape[1] >= _ops.F32_TENSOR_MIN_FLOPS:
+                if 2 * rows * k * cols >= _ops.F32_TENSOR_MIN_FLOPS:
                     continue
-            elif xv.shape[1] % 8 != 0 or wv.shape[1] % 8 != 0:
-                continue  # 16-bit rows must be addressable by a tensor map
+            elif k % 8 != 0 or wv.shape[-1] % 8 != 0 or (rank == 3 and (rows * k) % 8 != 0):
+                continue  # 16-bit rows (and the batch entries' first rows) must be addressable by a tensor map
             kind = 0
             if bias is not None:
                 if not (isinstance(bv, torch.Tensor) and bv.dtype == xv.dtype and _static(bv.shape)):
                     continue
-                if bv.numel() == v.shape[1] and (bv.dim() == 1 or (bv.dim() == 2 and bv.shape[0] == 1)):
+                if tuple(bv.shape) == tuple(v.shape) and rows > 1:
+                    kind = 2  # a full addend
+                elif bv.numel() == cols and rank == 2 and (bv.dim() == 1 or (bv.dim() == 2 and bv.shape[0] == 1)):
                     kind = 1  # a row of N
-                elif bv.dim() == 2 and tuple(bv.shape) == tuple(v.shape):
-                    kind = 2  # a full [M, N] addend
+                elif rank == 3 and _broadcasts_to(bv.shape, (v.shape[0], 1, cols)):
+                    kind = 1  # a row of N per batch entry
                 else:
                     continue
             key = (tuple(xv.shape), tuple(wv.shape), bool(wt), kind, act, xv.dtype)
             groups.setdefault(key, []).append(n)
-        changed = False
         for key, nodes in groups.items():
             if len(nodes) < COMBO_MIN_WIDTH:
                 continue
@@ -1301,10 +1318,10 @@ class FusedComboDense(Pattern):
                 members = [n for n in nodes if all(order[u] > last for u in n.users)]
             if len(members) < COMBO_MIN_WIDTH:
                 continue
-            _ensure(gm, "xg_combo_dense", M.ComboDenseModule)
+            _ensure(gm, combo_name, combo_cls)
             with gm.graph.inserting_before(anchor):
-                new = gm.graph.call_module("xg_combo_dense", ([n.args[0] for n in members], [n.args[1] for n in members],
-                                                              [n.args[3] for n in members], key[4], key[2]))
+                new = gm.graph.call_module(combo_name, ([n.args[0] for n in members], [n.args[1] for n in members],
+                                                        [n.args[3] for n in members], key[4], key[2]))
                 _fill_meta(gm, new)
                 parts = gm.graph.call_function(aten.unbind.int, (new,))
                 _fill_meta(gm, parts)
@@ -1315,7 +1332,7 @@ class FusedComboDense(Pattern):
             for n in members:
                 gm.graph.erase_node(n)
             return True  # one group per sweep: the node order used above is stale now; the pass manager calls again
-        return changed
+        return False
 
 
 # ---- chains of fp32 dense layers ---------------------------------------------------------------------------------
