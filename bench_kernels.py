@@ -139,7 +139,7 @@ def main(argv=None):
     ap.add_argument("case", choices=["sweep", "gemm_splitk", "gemm", "gemm_swiglu", "gemm_small_m", "add_rms_norm", "layer_norm", "sdpa", "rope", "swiglu",
                                      "gather", "slice_cat", "gemm_f32", "slice_sum_cat", "mul_sum_cat", "batch_dense", "graphs", "layer_gemms",
                                      "gemm_m256", "gemm_m64", "gemm_small_sweep", "layer_norm_small", "sdpa_full", "sdpa_simt", "gemm_f32_small",
-                                     "mlp2"])
+                                     "mlp2", "mlp_small"])
     ap.add_argument("--iters", type=int, default=3)
     args = ap.parse_args(argv)
     if args.case == "sweep":
@@ -271,6 +271,49 @@ def main(argv=None):
                                                 w3, True, b3, None, "none"))
             ms3 = _time_graphed(lambda: F_.linear(torch.relu(F_.linear(torch.relu(F_.linear(x, w1, b1)), w2, b2)), w3, b3))
             print(f"| {M} | {K1} -> {N1} -> {N2} -> {N3} | {ms * 1e3:.1f} | {ms2 * 1e3:.1f} | {ms3 * 1e3:.1f} | {4 * M * (N1 + N2) / 1e6:.1f} |")
+    elif args.case == "mlp_small":
+        # narrow towers with the weights resident in shared memory (one launch, FMA arithmetic) against one launch per
+        # layer of this library and eager torch, device time per call; and small fp32 / full-bias groups in one launch
+        import torch.nn.functional as F_
+
+        print("| dtype | rows | layer widths | one kernel (us) | one launch per layer (us) | eager torch (us) |")
+        print("|---|---:|---|---:|---:|---:|")
+        for dtype, M, dims in [(torch.float16, 16, (20, 32, 16, 1)), (torch.float32, 16384, (64, 32, 16, 1)),
+                               (torch.float32, 16384, (128, 64, 32)), (torch.bfloat16, 16384, (100, 64, 16)),
+                               (torch.float32, 65536, (26, 128, 64, 8))]:
+            x = rn(M, dims[0], dtype=dtype)
+            ws = [rn(dims[i + 1], dims[i], dtype=dtype, std=dims[i] ** -0.5) for i in range(len(dims) - 1)]
+            bs = [rn(dims[i + 1], dtype=dtype, std=0.1) for i in range(len(dims) - 1)]
+            acts = ["relu"] * (len(ws) - 1) + ["none"]
+
+            def layers(x=x, ws=ws, bs=bs, acts=acts):
+                y = x
+                for w, b, a in zip(ws, bs, acts):
+                    y = X.dense(y, w, True, b, None, a)
+                return y
+
+            def eager(x=x, ws=ws, bs=bs, acts=acts):
+                y = x
+                for w, b, a in zip(ws, bs, acts):
+                    y = F_.linear(y, w, b)
+                    y = torch.relu(y) if a == "relu" else y
+                return y
+
+            ms = _time_graphed(lambda: X.mlp_small(x, ws, bs, ",".join(acts), 0))
+            ms2 = _time_graphed(layers)
+            ms3 = _time_graphed(eager)
+            print(f"| {str(dtype)[6:]} | {M} | {' -> '.join(map(str, dims))} | {ms * 1e3:.1f} | {ms2 * 1e3:.1f} | {ms3 * 1e3:.1f} |")
+        print("| dtype | layers x (M x K x N) | bias | one grouped launch (us) | one launch per layer (us) | eager torch (us) |")
+        print("|---|---|---|---:|---:|---:|")
+        for dtype, T, M, K, N, full in [(torch.float32, 8, 5, 8, 7, True), (torch.float32, 16, 512, 64, 64, False),
+                                        (torch.bfloat16, 8, 512, 64, 64, True)]:
+            xs = [rn(M, K, dtype=dtype) for _ in range(T)]
+            ws = [rn(N, K, dtype=dtype, std=K ** -0.5) for _ in range(T)]
+            bs = [rn(M, N, dtype=dtype) if full else rn(N, dtype=dtype) for _ in range(T)]
+            ms = _time_graphed(lambda: X.combo_dense(xs, ws, True, bs, "relu"))
+            ms2 = _time_graphed(lambda: [X.dense(x, w, True, None if full else b, b if full else None, "relu") for x, w, b in zip(xs, ws, bs)])
+            ms3 = _time_graphed(lambda: [torch.relu(F_.linear(x, w) + b) for x, w, b in zip(xs, ws, bs)])
+            print(f"| {str(dtype)[6:]} | {T} x ({M} x {K} x {N}) | {'[M, N]' if full else '[N]'} | {ms * 1e3:.1f} | {ms2 * 1e3:.1f} | {ms3 * 1e3:.1f} |")
     elif args.case == "gemm_swiglu":
         M, K, N = 8192, 4096, 11008
         a, wg, wu = rn(M, K), rn(N, K, std=0.02), rn(N, K, std=0.02)

@@ -238,6 +238,22 @@ int xg_mlp3_bias_act(const void* x, const void* w1, const void* b1, const void* 
                      int dtype, void* stream);
 
 /*
+ * Small dense tower: 1..3 chained layers y = act_l(y @ W_l + b_l) whose widths (dims[0..layers]: the input width, then
+ * each layer's) are all <= 128 and whose weights together hold at most 24576 elements, as ONE kernel: every weight
+ * stays in shared memory for the whole launch and the hidden activations never leave the SM. fp32 / bf16 / f16, any
+ * row length or alignment (plain loads, FMA arithmetic with fp32 accumulation; fp32 towers are exact fp32); hidden
+ * activations are rounded to the tensors' dtype once per layer. w, bias (nullable table, nullable entries), ldw and
+ * act are host arrays with one entry per layer; bit l of weights_kn says that W_l is stored [K, N] instead of [N, K].
+ * xg_mlp_small_supported answers whether a tower qualifies (no device call).
+ * Replaces: the serial-matmul kernels of targets/mlu/fuse_densetower.py:272-316 at the sizes of their own condition
+ * "the weights fit on chip" (:66-77; tests/mlu/test_fuse_densetower.py:36-53 runs 16 rows of 20 -> 32 -> 16 -> 1 in fp16).
+ */
+int xg_mlp_small_supported(const int64_t* dims, int layers, int dtype);
+int xg_mlp_small_bias_act(const void* x, const void* const* w, const void* const* bias, void* out, int64_t M,
+                          const int64_t* dims, int layers, int64_t lda, const int64_t* ldw, int64_t ldc, const int* act,
+                          int weights_kn, int dtype, void* stream);
+
+/*
  * Grouped form: out[e] = act( A[e] @ W[e] + bias[e] + residual[e] ) for `count` problems of one shape [M, N, K] whose
  * operands lie wherever the caller has them: A, W, bias, residual (nullable tables, nullable entries; bias[e] a row of N,
  * residual[e] an [M, N] matrix with row stride ldr) and out are host arrays of `count` device pointers, so nothing is

@@ -135,6 +135,7 @@ def register():
             y = dense(y, w, not ((weights_kn >> l) & 1), b, None, a)
         return y
 
+    k(ops.mlp_small)(lambda x, weights, biases, act_names, weights_kn: mlp_chain(x, weights, biases, act_names.split(","), weights_kn))
     k(ops.mlp3)(lambda x, w1, b1, w2, b2, w3, b3, a1, a2, a3, weights_kn=0: mlp_chain(x, (w1, w2, w3), (b1, b2, b3), (a1, a2, a3), weights_kn))
     k(ops.mlp2)(lambda x, w1, b1, w2, b2, a1, a2, weights_kn=0: mlp_chain(x, (w1, w2), (b1, b2), (a1, a2), weights_kn))
 

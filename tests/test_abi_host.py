@@ -56,8 +56,18 @@ def test_argument_validation_without_gpu():
     assert L.xg_gemm_bias_act(p, p, None, None, p, 4, 4, 0, 4, 4, 4, 0, 1, 0, lib.XG_F32, None) == -1  # K == 0
     assert L.xg_gemm_bias_act(p, p, None, None, p, 4, 4, 8, 4, 8, 4, 0, 1, 0, lib.XG_F32, None) == -1  # lda < K
     assert L.xg_gemm_bias_act(p, p, None, None, p, 4, 4, 8, 8, 8, 4, 0, 1, 9, lib.XG_F32, None) == -1  # bad act
-    assert L.xg_gemm_bias_act(p, p, None, None, p, 8, 8, 8, 12, 8, 8, 0, 1, 0, lib.XG_BF16, None) == -2  # lda not 16-byte rows
+    # rows a tensor map cannot address: the cluster kernel refuses them (the plain entry runs them on the FMA kernel)
+    assert L.xg_gemm_bias_act_cluster(p, p, None, None, p, 8, 8, 8, 12, 8, 8, 0, 0, lib.XG_BF16, 1, 64, None) == -2
     assert "16-byte" in lib.last_error()
+    # small tower: limits answered without a device
+    dims_ok, dims_wide = lib.i64_array([20, 32, 16, 1]), lib.i64_array([20, 256, 16, 1])
+    assert L.xg_mlp_small_supported(dims_ok, 3, lib.XG_F16) == 1 and L.xg_mlp_small_supported(dims_wide, 3, lib.XG_F16) == 0
+    assert L.xg_mlp_small_supported(lib.i64_array([128, 128, 128, 128]), 3, lib.XG_F32) == 0  # 49152 weight elements
+    assert L.xg_mlp_small_supported(dims_ok, 4, lib.XG_F16) == 0
+    ws, ld, acts = lib.ptr_array([p.value] * 3), lib.i64_array([32, 16, 1]), (ctypes.c_int * 3)(1, 1, 0)
+    assert L.xg_mlp_small_bias_act(p, ws, None, p, 16, dims_wide, 3, 20, ld, 1, acts, 7, lib.XG_F16, None) == -2
+    assert L.xg_mlp_small_bias_act(None, ws, None, p, 16, dims_ok, 3, 20, ld, 1, acts, 7, lib.XG_F16, None) == -1
+    assert L.xg_mlp_small_bias_act(p, ws, None, p, 16, dims_ok, 3, 8, ld, 1, acts, 7, lib.XG_F16, None) == -1  # lda < K
     assert L.xg_gemm_swiglu(p, p, p, p, 8, 8, 8, 8, 8, 8, lib.XG_F32, None) == -2
     assert L.xg_sdpa_fwd(None, None, None, None, None, 1, 1, 1, 1, 8, None, None, None, None, None, 1.0, 0, lib.XG_BF16, None) == -1
     assert L.xg_gather_rows(None, None, 2, None, 2, 1, None, 1, None, 4, 8, 16, 4, None) == -1

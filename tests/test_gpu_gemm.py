@@ -617,6 +617,83 @@ def test_combo_dense_full_matrix_biases_16bit(cuda_device):
     assert_parity(got, want, "combo_dense bf16 with [M, N] addends", magnitude=torch.stack(bs))
 
 
+def _chain_reference(x, ws, bs, acts, kn, dtype):
+    """Layer by layer in fp64 with the hidden activation rounded to `dtype` once per layer (what the chained kernels do)."""
+    y = x.double()
+    for i, (w, b, a) in enumerate(zip(ws, bs, acts)):
+        y = y @ (w.double() if kn[i] else w.double().t())
+        if b is not None:
+            y = y + b.double()
+        y = ref_ops._ACTS[a](y.float()).double()
+        y = y.to(dtype).double()
+    return y.to(dtype)
+
+
+@pytest.mark.parametrize("dtype,M,dims,kn,acts", [
+    (torch.float16, 16, (20, 32, 16, 1), (True, True, True), ("relu", "relu", "none")),
+    (torch.float32, 1000, (64, 128, 32, 8), (False, False, False), ("relu", "gelu", "none")),
+    (torch.bfloat16, 4097, (100, 128, 64), (False, True), ("silu", "sigmoid")),
+    (torch.float32, 33, (7, 5, 3), (True, False), ("none", "relu")),
+    (torch.bfloat16, 300, (13, 50), (False,), ("gelu",)),
+    (torch.float32, 70000, (128, 128, 64), (False, False), ("relu", "none"))])
+def test_mlp_small(cuda_device, dtype, M, dims, kn, acts):
+    """One to three narrow layers with the weights resident in shared memory: the reference's own tower (16 rows of
+    20 -> 32 -> 16 -> 1 in fp16 with [K, N] weights, tests/mlu/test_fuse_densetower.py:36-53), both weight layouts,
+    widths that are no multiple of anything, the widest case the kernel takes, more row blocks than CTAs."""
+    from xpu_graph_b200 import ops  # noqa: F401  (registers the ops)
+
+    g = torch.Generator().manual_seed(37)
+    x = torch.randn(M, dims[0], generator=g).to(dtype)
+    ws, bs = [], []
+    for i in range(len(dims) - 1):
+        w = (torch.randn(dims[i + 1], dims[i], generator=g) * dims[i] ** -0.5).to(dtype)
+        ws.append(w.t().contiguous() if kn[i] else w)
+        bs.append(None if i == 1 else (0.3 * torch.randn(dims[i + 1], generator=g)).to(dtype))
+    want = _chain_reference(x, ws, bs, acts, kn, dtype)
+    kn_bits = sum(1 << i for i, f in enumerate(kn) if f)
+    with LaunchCounter() as calls:
+        got = torch.ops.xg_sm100.mlp_small(x.to(cuda_device), [w.to(cuda_device) for w in ws],
+                                           [b.to(cuda_device) if b is not None else None for b in bs], ",".join(acts), kn_bits)
+    torch.cuda.synchronize()
+    assert calls.names == ["xg_mlp_small_bias_act"], calls.names
+    assert_parity(got, want, f"mlp_small {dtype} M={M} {dims}")
+
+
+def test_dense_tower_module_takes_the_small_kernel(cuda_device):
+    """DenseTowerModule on the reference's tower: one launch, for fp16 as in its test and for fp32."""
+    from xpu_graph_b200.modules import DenseTowerModule
+
+    g = torch.Generator().manual_seed(38)
+    dims = (20, 32, 16, 1)
+    for dtype in (torch.float16, torch.float32):
+        x = torch.randn(16, dims[0], generator=g).to(dtype)
+        ws = [(torch.randn(dims[i], dims[i + 1], generator=g) * dims[i] ** -0.5).to(dtype) for i in range(3)]
+        bs = [torch.randn(dims[i + 1], generator=g).to(dtype) for i in range(3)]
+        acts = ["relu", "relu", "none"]
+        with LaunchCounter() as calls:
+            got = DenseTowerModule()(x.to(cuda_device), [w.to(cuda_device) for w in ws], [False] * 3, [b.to(cuda_device) for b in bs], acts)
+        torch.cuda.synchronize()
+        assert calls.names == ["xg_mlp_small_bias_act"], calls.names
+        assert_parity(got, _chain_reference(x, ws, bs, acts, (True, True, True), dtype), f"dense tower {dtype} {dims}")
+
+
+@pytest.mark.parametrize("M,K,N,weight_trans,act", [(128, 5897, 5897, True, "gelu"), (50, 444, 300, False, "relu"), (7, 20, 1, False, "none")])
+def test_dense_16bit_rows_no_tensor_map_addresses(cuda_device, M, K, N, weight_trans, act):
+    """16-bit dense layers whose rows are not multiples of 16 bytes (the sizes of tests/mlu/test_custom_denselayer.py run
+    in 16-bit: K = 5897, 444) run on the library's FMA kernel: bias, residual and activation fused as everywhere else."""
+    from xpu_graph_b200.modules import DenseLayerModule, can_fuse_custom_denselayer
+
+    x, w, b = _mk(M, K, N, torch.bfloat16, 39)
+    if not weight_trans:
+        w = w.t().contiguous()
+    assert can_fuse_custom_denselayer(x.to(cuda_device), w.to(cuda_device), weight_trans, b.to(cuda_device), act)
+    with LaunchCounter() as calls:
+        got = DenseLayerModule(False)(x.to(cuda_device), w.to(cuda_device), weight_trans, b.to(cuda_device), act)
+    torch.cuda.synchronize()
+    assert calls.names == ["xg_gemm_bias_act_ws"] or calls.names == ["xg_gemm_bias_act"], calls.names
+    assert_parity(got, ref_ops.dense(x, w, weight_trans, b, act), f"dense bf16 unaligned {M}x{K}x{N}")
+
+
 @pytest.mark.parametrize("dtype,T,S,M,K,N,weight_trans,bias_kind", [
     (torch.float32, 8, 3, 5, 6, 7, False, "full"), (torch.float32, 8, 3, 5, 6, 7, False, "none"),
     (torch.float32, 5, 4, 33, 64, 48, True, "row"), (torch.bfloat16, 6, 4, 64, 128, 96, True, "full"),

@@ -26,6 +26,7 @@ SOURCES = [
     "gemm_tc.cu",
     "gemm_tc_ksplit.cu",
     "gemm_mlp.cu",
+    "mlp_small.cu",
     "gemm_f32.cu",
     "split_bf16x3.cu",
     "sdpa.cu",

@@ -33,6 +33,9 @@ int gemm_tc_ksplit_entry(const void* A, const void* W, const void* bias, const v
 int gemm_group_entry(const void* const* A, const void* const* W, const void* const* bias, const void* const* residual,
                      void* const* out, int64_t count, int64_t M, int64_t N, int64_t K, int64_t lda, int64_t ldw, int64_t ldc,
                      int64_t ldr, int trans_b, int act, int dtype, cudaStream_t st);
+int gemm_simt16_entry(const void* A, const void* B, const void* bias, const void* residual, void* out, int64_t M, int64_t N,
+                      int64_t K, int64_t lda, int64_t ldb, int64_t ldc, int64_t ldr, int trans_b, int act, int dtype,
+                      cudaStream_t st);
 int gemm_f32_group_entry(const void* const* A, const void* const* W, const void* const* bias, const void* const* residual,
                          void* const* out, int64_t count, int64_t M, int64_t N, int64_t K, int64_t lda, int64_t ldw,
                          int64_t ldc, int64_t ldr, int trans_b, int act, cudaStream_t st);
@@ -65,6 +68,9 @@ extern "C" int xg_gemm_bias_act_ws(const void* A, const void* B, const void* bia
     if (workspace_bytes < 0) return fail(XG_ERR_INVALID_ARG, "xg_gemm_bias_act_ws: negative workspace size");
     cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
     if (dtype == XG_F32) return gemm_f32_entry(A, B, bias, residual, out, M, N, K, lda, ldb, ldc, ldr, trans_b, act, st);
+    // rows a tensor map cannot address (not multiples of 16 bytes from a 16-byte aligned base): the FMA kernel
+    if (lda % 8 != 0 || ldb % 8 != 0 || (reinterpret_cast<uintptr_t>(A) & 15u) || (reinterpret_cast<uintptr_t>(B) & 15u))
+        return gemm_simt16_entry(A, B, bias, residual, out, M, N, K, lda, ldb, ldc, ldr, trans_b, act, dtype, st);
     return gemm_tc_entry(A, B, bias, residual, out, M, N, K, lda, ldb, ldc, ldr, trans_b, act, dtype, workspace,
                          workspace_bytes, st);
 }

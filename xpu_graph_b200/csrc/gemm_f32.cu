@@ -1,18 +1,19 @@
 // True-fp32 dense layer (no TF32): out = act(A @ W + bias + residual) with FFMA accumulation.
 // Shared-memory tiled SIMT kernel; used for the fp32 graphs whose tolerance (1e-5 relative) rules out
-// tensor-core TF32. W is [K, N] (trans_b = 0) or [N, K] (trans_b = 1); both tiles are stored k-major
+// tensor-core TF32, and - with 16-bit elements converted on the way in and out, fp32 in between - for the 16-bit
+// shapes whose rows no tensor map can address (row lengths or base addresses that are not multiples of 16 bytes). W is [K, N] (trans_b = 0) or [N, K] (trans_b = 1); both tiles are stored k-major
 // in shared memory so the inner product reads float4 vectors without bank conflicts.
 #include "common.cuh"
 
 namespace xg {
 namespace {
 
-struct GemmF32Params {
-    const float* A;
-    const float* B;
-    const float* bias;
-    const float* residual;
-    float* out;
+struct GemmF32Params {  // element type: the kernel's template parameter
+    const void* A;
+    const void* B;
+    const void* bias;
+    const void* residual;
+    void* out;
     int64_t M, N, K, lda, ldb, ldc, ldr;
     int trans_b;
     int act;
@@ -29,9 +30,14 @@ __device__ __forceinline__ float act_f32(float v, int act) {
 }
 
 // 256 threads; thread (ty, tx) owns a TM x TN micro-tile; BM = 16*TM, BN = 16*TN.
-template <int TM, int TN, int BK>
+template <typename T, int TM, int TN, int BK>
 __device__ __forceinline__ void gemm_f32_tile(const GemmF32Params& p) {
     constexpr int BM = 16 * TM, BN = 16 * TN;
+    const T* __restrict__ gA = reinterpret_cast<const T*>(p.A);
+    const T* __restrict__ gB = reinterpret_cast<const T*>(p.B);
+    const T* gbias = reinterpret_cast<const T*>(p.bias);
+    const T* gres = reinterpret_cast<const T*>(p.residual);
+    T* gout = reinterpret_cast<T*>(p.out);
     __shared__ __align__(16) float As[2][BK][BM + 4];
     __shared__ __align__(16) float Bs[2][BK][BN + 4];
     const int tid = threadIdx.x;
@@ -54,7 +60,7 @@ __device__ __forceinline__ void gemm_f32_tile(const GemmF32Params& p) {
             const int idx = tid + e * 256;  // k fastest: consecutive threads read consecutive k of one row
             const int kk = idx % BK, mm = idx / BK;
             const int64_t gm = m0 + mm, gk = k0 + kk;
-            a_reg[e] = (gm < p.M && gk < p.K) ? p.A[gm * p.lda + gk] : 0.f;
+            a_reg[e] = (gm < p.M && gk < p.K) ? Cvt<T>::to_f(gA[gm * p.lda + gk]) : 0.f;
         }
 #pragma unroll
         for (int e = 0; e < B_ELEMS; ++e) {
@@ -62,11 +68,11 @@ __device__ __forceinline__ void gemm_f32_tile(const GemmF32Params& p) {
             if (p.trans_b) {  // W[N, K]: k fastest
                 const int kk = idx % BK, nn = idx / BK;
                 const int64_t gn = n0 + nn, gk = k0 + kk;
-                b_reg[e] = (gn < p.N && gk < p.K) ? p.B[gn * p.ldb + gk] : 0.f;
+                b_reg[e] = (gn < p.N && gk < p.K) ? Cvt<T>::to_f(gB[gn * p.ldb + gk]) : 0.f;
             } else {  // W[K, N]: n fastest
                 const int nn = idx % BN, kk = idx / BN;
                 const int64_t gn = n0 + nn, gk = k0 + kk;
-                b_reg[e] = (gn < p.N && gk < p.K) ? p.B[gk * p.ldb + gn] : 0.f;
+                b_reg[e] = (gn < p.N && gk < p.K) ? Cvt<T>::to_f(gB[gk * p.ldb + gn]) : 0.f;
             }
         }
     };
@@ -124,27 +130,27 @@ __device__ __forceinline__ void gemm_f32_tile(const GemmF32Params& p) {
             const int64_t gn = n0 + tx * TN + j;
             if (gn >= p.N) continue;
             float v = acc[i][j];
-            if (p.bias) v += p.bias[gn];
-            if (p.residual) v += p.residual[gm * p.ldr + gn];
-            p.out[gm * p.ldc + gn] = act_f32(v, p.act);
+            if (gbias) v += Cvt<T>::to_f(gbias[gn]);
+            if (gres) v += Cvt<T>::to_f(gres[gm * p.ldr + gn]);
+            gout[gm * p.ldc + gn] = Cvt<T>::from_f(act_f32(v, p.act));
         }
     }
 }
 
-template <int TM, int TN, int BK>
+template <typename T, int TM, int TN, int BK>
 __global__ void __launch_bounds__(256) gemm_f32_kernel(const GemmF32Params p) {
-    gemm_f32_tile<TM, TN, BK>(p);
+    gemm_f32_tile<T, TM, TN, BK>(p);
 }
 
 // Grouped form: blockIdx.z picks the entry; its five pointers come from a table in the kernel's parameter space, the
 // extents, strides and activation are shared by the group.
 constexpr int kF32GroupMax = 24;  // 24 x 5 pointers = 960 bytes of parameters
 struct GemmF32Group {
-    const float* A[kF32GroupMax];
-    const float* B[kF32GroupMax];
-    const float* bias[kF32GroupMax];
-    const float* residual[kF32GroupMax];
-    float* out[kF32GroupMax];
+    const void* A[kF32GroupMax];
+    const void* B[kF32GroupMax];
+    const void* bias[kF32GroupMax];
+    const void* residual[kF32GroupMax];
+    void* out[kF32GroupMax];
 };
 __device__ __forceinline__ GemmF32Params entry_params(const GemmF32Params& p, const GemmF32Group& g) {
     GemmF32Params pe = p;
@@ -157,10 +163,10 @@ __device__ __forceinline__ GemmF32Params entry_params(const GemmF32Params& p, co
     return pe;
 }
 
-template <int TM, int TN, int BK>
+template <typename T, int TM, int TN, int BK>
 __global__ void __launch_bounds__(256) gemm_f32_group_kernel(const GemmF32Params p, const __grid_constant__ GemmF32Group g) {
     const GemmF32Params pe = entry_params(p, g);
-    gemm_f32_tile<TM, TN, BK>(pe);
+    gemm_f32_tile<T, TM, TN, BK>(pe);
 }
 
 // Small problems (fewer 64 x 64 tiles than SMs) are latency-bound in the kernel above: every 16-wide k-tile costs a
@@ -200,12 +206,12 @@ __device__ __forceinline__ void gemm_f32_panel_tile(const GemmF32Params& p) {
         for (int idx = tid; idx < BM * vec_per_row; idx += 128) {
             const int r = idx / vec_per_row, v = idx - r * vec_per_row;
             const int64_t gm = m0 + r;
-            cp_async16(As + r * kPanelPitch + 4 * v, p.A + (gm < p.M ? gm : 0) * p.lda + k0 + 4 * v, gm < p.M);
+            cp_async16(As + r * kPanelPitch + 4 * v, reinterpret_cast<const float*>(p.A) + (gm < p.M ? gm : 0) * p.lda + k0 + 4 * v, gm < p.M);
         }
         for (int idx = tid; idx < BN * vec_per_row; idx += 128) {
             const int r = idx / vec_per_row, v = idx - r * vec_per_row;
             const int64_t gn = n0 + r;
-            cp_async16(Bs + r * kPanelPitch + 4 * v, p.B + (gn < p.N ? gn : 0) * p.ldb + k0 + 4 * v, gn < p.N);
+            cp_async16(Bs + r * kPanelPitch + 4 * v, reinterpret_cast<const float*>(p.B) + (gn < p.N ? gn : 0) * p.ldb + k0 + 4 * v, gn < p.N);
         }
         asm volatile("cp.async.commit_group;" ::: "memory");
         asm volatile("cp.async.wait_group 0;" ::: "memory");
@@ -238,9 +244,9 @@ __device__ __forceinline__ void gemm_f32_panel_tile(const GemmF32Params& p) {
             const int64_t gn = n0 + tx * TN + j;
             if (gn >= p.N) continue;
             float v = acc[i][j];
-            if (p.bias) v += p.bias[gn];
-            if (p.residual) v += p.residual[gm * p.ldr + gn];
-            p.out[gm * p.ldc + gn] = act_f32(v, p.act);
+            if (p.bias) v += reinterpret_cast<const float*>(p.bias)[gn];
+            if (p.residual) v += reinterpret_cast<const float*>(p.residual)[gm * p.ldr + gn];
+            reinterpret_cast<float*>(p.out)[gm * p.ldc + gn] = act_f32(v, p.act);
         }
     }
 }
@@ -291,9 +297,7 @@ int launch_panel(const GemmF32Params& p, cudaStream_t st) {
 int gemm_f32_entry(const void* A, const void* B, const void* bias, const void* residual, void* out, int64_t M, int64_t N,
                    int64_t K, int64_t lda, int64_t ldb, int64_t ldc, int64_t ldr, int trans_b, int act, cudaStream_t st) {
     if (M * N == 0) return XG_OK;
-    GemmF32Params p{reinterpret_cast<const float*>(A), reinterpret_cast<const float*>(B), reinterpret_cast<const float*>(bias),
-                    reinterpret_cast<const float*>(residual), reinterpret_cast<float*>(out), M, N, K, lda, ldb, ldc, ldr,
-                    trans_b, act};
+    GemmF32Params p{A, B, bias, residual, out, M, N, K, lda, ldb, ldc, ldr, trans_b, act};
     const int64_t tiles64 = ((M + 63) / 64) * ((N + 63) / 64);
     const bool panel_ok = trans_b && K % 4 == 0 && lda % 4 == 0 && ldb % 4 == 0 && aligned16(A) && aligned16(B) &&
                           (M + 15) / 16 <= 65535;
@@ -306,13 +310,34 @@ int gemm_f32_entry(const void* A, const void* B, const void* bias, const void* r
     if (big_tiles >= 2LL * num_sms()) {
         dim3 grid((unsigned)((N + 127) / 128), (unsigned)((M + 127) / 128));
         if ((M + 127) / 128 > 65535) return fail(XG_ERR_TOO_LARGE, "xg_gemm_bias_act(f32): M too large");
-        gemm_f32_kernel<8, 8, 16><<<grid, 256, 0, st>>>(p);
+        gemm_f32_kernel<float, 8, 8, 16><<<grid, 256, 0, st>>>(p);
     } else {
         dim3 grid((unsigned)((N + 63) / 64), (unsigned)((M + 63) / 64));
         if ((M + 63) / 64 > 65535) return fail(XG_ERR_TOO_LARGE, "xg_gemm_bias_act(f32): M too large");
-        gemm_f32_kernel<4, 4, 16><<<grid, 256, 0, st>>>(p);
+        gemm_f32_kernel<float, 4, 4, 16><<<grid, 256, 0, st>>>(p);
     }
     return check_launch("xg_gemm_bias_act(f32)");
+}
+
+// 16-bit operands the tensor-core kernels cannot address (rows or base addresses that are not multiples of 16 bytes):
+// the same tiled FMA kernel, elements converted on the way in and out, fp32 accumulation.
+int gemm_simt16_entry(const void* A, const void* B, const void* bias, const void* residual, void* out, int64_t M, int64_t N,
+                      int64_t K, int64_t lda, int64_t ldb, int64_t ldc, int64_t ldr, int trans_b, int act, int dtype,
+                      cudaStream_t st) {
+    if (M * N == 0) return XG_OK;
+    GemmF32Params p{A, B, bias, residual, out, M, N, K, lda, ldb, ldc, ldr, trans_b, act};
+    const bool big = ((M + 127) / 128) * ((N + 127) / 128) >= 2LL * num_sms();
+    const int64_t bm = big ? 128 : 64;
+    if ((M + bm - 1) / bm > 65535) return fail(XG_ERR_TOO_LARGE, "xg_gemm_bias_act: M too large for the unaligned 16-bit path");
+    dim3 grid((unsigned)((N + bm - 1) / bm), (unsigned)((M + bm - 1) / bm));
+    if (dtype == XG_BF16) {
+        if (big) gemm_f32_kernel<__nv_bfloat16, 8, 8, 16><<<grid, 256, 0, st>>>(p);
+        else gemm_f32_kernel<__nv_bfloat16, 4, 4, 16><<<grid, 256, 0, st>>>(p);
+    } else {
+        if (big) gemm_f32_kernel<__half, 8, 8, 16><<<grid, 256, 0, st>>>(p);
+        else gemm_f32_kernel<__half, 4, 4, 16><<<grid, 256, 0, st>>>(p);
+    }
+    return check_launch("xg_gemm_bias_act (16-bit, FMA path)");
 }
 
 // out[e] = act(A[e] @ W[e] + bias[e] + residual[e]) for `count` fp32 problems of one shape; the operands stay where
@@ -331,11 +356,11 @@ int gemm_f32_group_entry(const void* const* A, const void* const* W, const void*
             const int64_t i = first + (e < n ? e : 0);  // unused slots repeat the first entry and are never read
             if (!A[i] || !W[i] || !out[i])
                 return fail(XG_ERR_INVALID_ARG, "xg_gemm_group_bias_act: null pointer in entry %lld", (long long)i);
-            g.A[e] = reinterpret_cast<const float*>(A[i]);
-            g.B[e] = reinterpret_cast<const float*>(W[i]);
-            g.bias[e] = bias ? reinterpret_cast<const float*>(bias[i]) : nullptr;
-            g.residual[e] = residual ? reinterpret_cast<const float*>(residual[i]) : nullptr;
-            g.out[e] = reinterpret_cast<float*>(out[i]);
+            g.A[e] = A[i];
+            g.B[e] = W[i];
+            g.bias[e] = bias ? bias[i] : nullptr;
+            g.residual[e] = residual ? residual[i] : nullptr;
+            g.out[e] = out[i];
             aligned = aligned && aligned16(A[i]) && aligned16(W[i]);
         }
         GemmF32Params p{nullptr, nullptr, nullptr, nullptr, nullptr, M, N, K, lda, ldw, ldc, ldr, trans_b, act};
@@ -347,11 +372,11 @@ int gemm_f32_group_entry(const void* const* A, const void* const* W, const void*
             rc = tiles_32x64 * 3 >= 2LL * num_sms() ? launch_panel_group<4, 4>(p, g, n, st) : launch_panel_group<2, 2>(p, g, n, st);
         } else if (((M + 127) / 128) * ((N + 127) / 128) * n >= 2LL * num_sms()) {
             dim3 grid((unsigned)((N + 127) / 128), (unsigned)((M + 127) / 128), (unsigned)n);
-            gemm_f32_group_kernel<8, 8, 16><<<grid, 256, 0, st>>>(p, g);
+            gemm_f32_group_kernel<float, 8, 8, 16><<<grid, 256, 0, st>>>(p, g);
             rc = check_launch("xg_gemm_group_bias_act(f32)");
         } else {
             dim3 grid((unsigned)((N + 63) / 64), (unsigned)((M + 63) / 64), (unsigned)n);
-            gemm_f32_group_kernel<4, 4, 16><<<grid, 256, 0, st>>>(p, g);
+            gemm_f32_group_kernel<float, 4, 4, 16><<<grid, 256, 0, st>>>(p, g);
             rc = check_launch("xg_gemm_group_bias_act(f32)");
         }
         if (rc != XG_OK) return rc;

@@ -57,6 +57,9 @@ SIGNATURES = {
                                   c_int, c_int, c_int, c_void_p]),
     "xg_gemm_group_bias_act": (c_int, [_VPP, _VPP, _VPP, _VPP, _VPP, c_int64, c_int64, c_int64, c_int64, c_int64, c_int64,
                                        c_int64, c_int64, c_int, c_int, c_int, c_void_p]),
+    "xg_mlp_small_supported": (c_int, [_I64P, c_int, c_int]),
+    "xg_mlp_small_bias_act": (c_int, [c_void_p, _VPP, _VPP, c_void_p, c_int64, _I64P, c_int, c_int64, _I64P, c_int64,
+                                      POINTER(c_int), c_int, c_int, c_void_p]),
     "xg_mlp2_supported": (c_int, [c_int64, c_int64, c_int64, c_int64, c_int]),
     "xg_mlp3_supported": (c_int, [c_int64, c_int64, c_int64, c_int64, c_int64, c_int]),
     "xg_mlp3_bias_act": (c_int, [c_void_p] * 8 + [c_int64] * 10 + [c_int] * 5 + [c_void_p]),
@@ -143,7 +146,7 @@ def tc_status(reset: bool = True) -> int:
 # entry points that enqueue no kernel (queries and status reads)
 QUERY_ENTRY_POINTS = frozenset({"xg_version", "xg_device_arch_ok", "xg_last_error", "xg_tc_status", "xg_gemm_workspace_bytes",
                                 "xg_gemm_static_scratch_bytes", "xg_gemm_f32x3_padded_k", "xg_gemm_cluster_plan",
-                                "xg_mlp2_supported", "xg_mlp3_supported"})
+                                "xg_mlp2_supported", "xg_mlp3_supported", "xg_mlp_small_supported"})
 
 
 @contextlib.contextmanager

@@ -108,13 +108,7 @@ def can_fuse_custom_denselayer(inputs, weight, weight_trans, bias, act_str):
         return False
     if inputs.device.type not in ALLOWED_DEVICE_TYPES:
         return False
-    if inputs.dtype != torch.float32:
-        # tensor-core kernel: every TMA-read row must be a multiple of 16 bytes: K for the activations and
-        # [N, K] weights, N for weights given as [K, N]
-        if inputs.shape[1] % 8 != 0:
-            return False
-        if not weight_trans and weight.shape[1] % 8 != 0:
-            return False
+    # any extents: 16-bit rows a tensor map cannot address (not multiples of 16 bytes) run on the library's FMA kernel
     return True
 
 
@@ -324,7 +318,8 @@ class DenseTowerModule(torch.nn.Module):
     Stands where the reference fuses serial matmuls into one kernel (targets/mlu/fuse_densetower.py:272-316,
     triton_kernel/fused_serial_mm_2dot.py / _3dot.py). 16-bit towers: neighbouring narrow layers (N <= 256) run as one
     kernel per pair with the hidden activation kept on chip (xg_mlp2_bias_act). fp32 towers: the layers stay separate
-    tensor-core GEMMs and the activations travel between them as bf16 planes."""
+    tensor-core GEMMs and the activations travel between them as bf16 planes. Towers of any dtype whose widths are all
+    <= 128: runs of up to three layers in one kernel with the weights resident in shared memory (xg_mlp_small_bias_act)."""
 
     def forward(self, x, weights, weight_trans, biases, acts):
         return _X.dense_tower(x, list(weights), [bool(t) for t in weight_trans], list(biases), ",".join(str(a) for a in acts))

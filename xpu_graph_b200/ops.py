@@ -382,6 +382,73 @@ def _(x, w1, b1, w2, b2, w3, b3, act1, act2, act3, weights_kn=0):
     return torch.empty((x.shape[0], w3.shape[1] if (weights_kn >> 2) & 1 else w3.shape[0]), dtype=x.dtype, device=x.device)
 
 
+MLP_SMALL_MAX_DIM = 128
+MLP_SMALL_MAX_WEIGHTS = 24576
+
+
+def _small_run(dims: Sequence[int], i: int, n: int, dtype: torch.dtype, M: int) -> int:
+    """How many layers starting at layer i (at most three) run together on the weights-in-shared-memory kernel."""
+    for run in (3, 2):
+        if i + run <= n and mlp_small_worth_it(M, dims[i:i + run + 1], dtype):
+            return run
+    return 1
+
+
+def mlp_small_worth_it(M: int, dims: Sequence[int], dtype: torch.dtype) -> bool:
+    """The one-launch FMA tower is the faster form where a launch per layer is mostly launch and latency: few rows, or
+    very narrow layers. Measured on B200 (us, one kernel / a launch per layer): 16 rows of 20 -> 32 -> 16 -> 1 fp16
+    8.3 / 26.5; 16384 rows of 64 -> 32 -> 16 -> 1 fp32 20.5 / 21.7; 16384 rows of 128 -> 64 -> 32 fp32 43.5 / 24.6."""
+    if not mlp_small_eligible(dims, dtype):
+        return False
+    weights = sum(((dims[i] + 3) // 4 * 4) * dims[i + 1] for i in range(len(dims) - 1))
+    return M <= 2048 or weights <= 4096
+
+
+def mlp_small_eligible(dims: Sequence[int], dtype: torch.dtype) -> bool:
+    """A tower [K0 -> N1 -> ... ] of one to three layers fits the weights-in-shared-memory kernel (the limits of
+    xg_mlp_small_supported: every width <= 128, at most 24576 weight elements with K padded to a multiple of 4)."""
+    n = len(dims) - 1
+    if dtype not in (torch.float32, torch.bfloat16, torch.float16) or not 1 <= n <= 3:
+        return False
+    if any(d < 1 or d > MLP_SMALL_MAX_DIM for d in dims):
+        return False
+    return sum(((dims[i] + 3) // 4 * 4) * dims[i + 1] for i in range(n)) <= MLP_SMALL_MAX_WEIGHTS
+
+
+@torch.library.custom_op(f"{NS}::mlp_small", mutates_args=(), device_types="cuda")
+def mlp_small(x: torch.Tensor, weights: List[torch.Tensor], biases: List[Optional[torch.Tensor]], act_names: str,
+              weights_kn: int) -> torch.Tensor:
+    """One to three chained narrow dense layers in one launch with every weight resident in shared memory (FMA
+    arithmetic, fp32 accumulation, any row length); weight l is [N, K] unless bit l of weights_kn says [K, N]."""
+    acts = act_names.split(",")
+    n = len(weights)
+    if x.dim() != 2 or len(biases) != n or len(acts) != n or any(w.dim() != 2 for w in weights):
+        raise ValueError("xg_sm100::mlp_small expects a 2-D x and one 2-D weight, bias and activation per layer")
+    x = _mat(x)
+    ws = [_mat(w) for w in weights]
+    dims = [x.shape[1]] + _mlp_dims(x, ws, weights_kn, "mlp_small")
+    bs = [None if b is None else b.reshape(-1).to(x.dtype).contiguous() for b in biases]
+    if any(b is not None and b.numel() != dims[i + 1] for i, b in enumerate(bs)):
+        raise ValueError("xg_sm100::mlp_small: a bias does not match its layer's width")
+    M = x.shape[0]
+    out = torch.empty((M, dims[-1]), dtype=x.dtype, device=x.device)
+    if M == 0:
+        return out
+    rc = _lib.load().xg_mlp_small_bias_act(
+        _ptr(x), _lib.ptr_array([w.data_ptr() for w in ws]), _lib.ptr_array([0 if b is None else b.data_ptr() for b in bs]),
+        _ptr(out), M, _lib.i64_array(dims), n, _row_stride(x), _lib.i64_array([_row_stride(w) for w in ws]), dims[-1],
+        (ctypes.c_int * n)(*[_lib.ACT_CODES[a] for a in acts]), weights_kn, _code(x.dtype), _stream(x))
+    _lib.check(rc, "xg_mlp_small_bias_act")
+    return out
+
+
+@mlp_small.register_fake
+def _(x, weights, biases, act_names, weights_kn):
+    w = weights[-1]
+    last = len(weights) - 1
+    return torch.empty((x.shape[0], w.shape[1] if (weights_kn >> last) & 1 else w.shape[0]), dtype=x.dtype, device=x.device)
+
+
 @torch.library.custom_op(f"{NS}::dense_tower", mutates_args=(), device_types="cuda")
 def dense_tower(x: torch.Tensor, weights: List[torch.Tensor], weight_trans: List[bool], biases: List[Optional[torch.Tensor]],
                 act_names: str) -> torch.Tensor:
@@ -412,13 +479,25 @@ def dense_tower(x: torch.Tensor, weights: List[torch.Tensor], weight_trans: List
                 y = mlp2(y, weights[i], biases[i], weights[i + 1], biases[i + 1], acts[i], acts[i + 1], kn(0, 2))
                 i += 2
             else:
-                y = dense(y, weights[i], weight_trans[i], biases[i], None, acts[i])
-                i += 1
+                run = _small_run(dims, i, n, x.dtype, M)
+                if run >= 2:  # narrow layers no tensor map addresses (or too narrow for a tile): weights in shared memory
+                    y = mlp_small(y, weights[i:i + run], biases[i:i + run], ",".join(acts[i:i + run]), kn(0, run))
+                    i += run
+                else:
+                    y = dense(y, weights[i], weight_trans[i], biases[i], None, acts[i])
+                    i += 1
         return y
     if not dense_tower_eligible(M, dims):
-        y = x
-        for i in range(n):
-            y = dense(y, weights[i], weight_trans[i], biases[i], None, acts[i])
+        y, i = x, 0
+        while i < n:
+            run = _small_run(dims, i, n, x.dtype, M)
+            if run >= 2:
+                kn_bits = sum((0 if weight_trans[i + l] else 1) << l for l in range(run))
+                y = mlp_small(y, weights[i:i + run], biases[i:i + run], ",".join(acts[i:i + run]), kn_bits)
+                i += run
+            else:
+                y = dense(y, weights[i], weight_trans[i], biases[i], None, acts[i])
+                i += 1
         return y
     L = _lib.load()
     x = _mat(x)

@@ -1340,7 +1340,8 @@ class FusedDenseTower(Pattern):
     """dense(dense(dense(x))), each inner result used only by the next layer -> DenseTowerModule. fp32 chains of any
     depth >= 2 when every layer is large enough for the tensor-core path (ops.dense_tower_eligible); 16-bit chains when
     at least one pair of neighbouring layers fits the two-layer kernel (ops.mlp2_eligible: narrow layers whose hidden
-    activation then never leaves the SM). The graph form of targets/mlu/fuse_densetower.py:272-316
+    activation then never leaves the SM); chains of any dtype when a pair of neighbours is narrow enough for the
+    weights-in-shared-memory kernel and the rows are few or the layers very narrow (ops.mlp_small_worth_it). The graph form of targets/mlu/fuse_densetower.py:272-316
     (FusedDenseTower2 / 3)."""
 
     _opt_level = OptLevel.level2
@@ -1367,8 +1368,10 @@ class FusedDenseTower(Pattern):
             rows = _val(x).shape[0]
             dims = [_val(x).shape[1]] + [_val(n).shape[1] for n in chain]
             dtype = _val(chain[0]).dtype
+            # narrow neighbours whose weights fit in shared memory together (any dtype, any row length)
+            small = any(_ops.mlp_small_worth_it(rows, dims[i:i + 3], dtype) for i in range(len(chain) - 1))
             if dtype == torch.float32:
-                return _ops.dense_tower_eligible(rows, dims)
+                return small or _ops.dense_tower_eligible(rows, dims)
             # four or more independent layers of one shape are FusedComboDense's (one grouped launch for all of them)
             head = chain[0]
             alike = [m for m in gm.graph.nodes
@@ -1376,8 +1379,8 @@ class FusedDenseTower(Pattern):
                      and _val(m.args[1]).shape == _val(head.args[1]).shape and _val(m.args[0]).shape == _val(x).shape]
             if len(alike) >= 4:
                 return False
-            return any(_ops.mlp2_eligible(rows, dims[i], dims[i + 1], dims[i + 2], dtype, chain[i].args[2], chain[i + 1].args[2])
-                       for i in range(len(chain) - 1))
+            return small or any(_ops.mlp2_eligible(rows, dims[i], dims[i + 1], dims[i + 2], dtype, chain[i].args[2], chain[i + 1].args[2])
+                                for i in range(len(chain) - 1))
 
         changed = False
         for tail in reversed(list(gm.graph.nodes)):
