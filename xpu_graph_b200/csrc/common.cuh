@@ -58,6 +58,21 @@ struct Cvt<__half> {
     static __device__ __forceinline__ __half from_f(float v) { return __float2half_rn(v); }
 };
 
+// GELU (erf form) for epilogues whose result is rounded to a 16-bit type: erfc from Abramowitz & Stegun 7.1.26
+// (absolute error <= 1.5e-7, against a 16-bit rounding step of 2^-9 or 2^-11 relative), one reciprocal, one exp2 and
+// five FMAs instead of erff's branches; for v < 0 the factor 1 + erf is the formula's erfc term itself, so the tail
+// does not cancel. fp32 outputs keep erff.
+__device__ __forceinline__ float gelu_erf_16bit(float v) {
+    const float x = fabsf(v) * 0.70710678118654752f;
+    const float t = __fdividef(1.0f, fmaf(0.3275911f, x, 1.0f));
+    float poly = fmaf(1.061405429f, t, -1.453152027f);
+    poly = fmaf(poly, t, 1.421413741f);
+    poly = fmaf(poly, t, -0.284496736f);
+    poly = fmaf(poly, t, 0.254829592f);
+    const float e = poly * t * __expf(-x * x);  // erfc(|v| / sqrt(2))
+    return 0.5f * v * (v >= 0.f ? 2.0f - e : e);
+}
+
 // 16-byte vector of T (4 floats or 8 half-precision values).
 template <typename T>
 struct alignas(16) Vec16 {

@@ -61,7 +61,7 @@ static_assert(sizeof(MlpParams) <= 128, "the scalar parameters stay within 128 b
 
 __device__ __forceinline__ float apply_act(float v, int act) {
     switch (act) {
-        case XG_ACT_GELU: return 0.5f * v * (1.0f + erff(v * 0.70710678118654752f));
+        case XG_ACT_GELU: return gelu_erf_16bit(v);  // results of this file are always rounded to a 16-bit type
         case XG_ACT_RELU: return v > 0.f ? v : 0.f;
         case XG_ACT_SILU: return __fdividef(v, 1.0f + __expf(-v));
         case XG_ACT_SIGMOID: return __fdividef(1.0f, 1.0f + __expf(-v));

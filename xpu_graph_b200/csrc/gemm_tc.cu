@@ -213,6 +213,13 @@ __device__ __forceinline__ float apply_act(float v, int act) {
     }
 }
 
+// ... for results that are rounded to a 16-bit type
+template <typename T>
+__device__ __forceinline__ float apply_act_out(float v, int act) {
+    if (sizeof(T) == 2 && act == XG_ACT_GELU) return gelu_erf_16bit(v);
+    return apply_act(v, act);
+}
+
 __device__ __forceinline__ void tile_coords(int t, int num_m, int num_n, int& mb, int& nb) {
     const int per_group = GROUP_M * num_n;
     const int g = t / per_group;
@@ -397,7 +404,7 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams& p, uint32_t tmem
                 for (int i = 0; i < 32; i += 8) {
                     Vec16<T> ov;
 #pragma unroll
-                    for (int j = 0; j < 8; ++j) ov.v[j] = Cvt<T>::from_f(apply_act(v[i + j], p.act));
+                    for (int j = 0; j < 8; ++j) ov.v[j] = Cvt<T>::from_f(apply_act_out<T>(v[i + j], p.act));
                     st16(orow + i, ov);
                 }
             } else {
@@ -406,7 +413,7 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams& p, uint32_t tmem
                     if (col0 + i < p.N) {
                         float a = v[i];
                         if (resid != nullptr) a += Cvt<T>::to_f(resid[row * p.ldr + col0 + i]);
-                        out[row * p.ldc + col0 + i] = Cvt<T>::from_f(apply_act(a, p.act));
+                        out[row * p.ldc + col0 + i] = Cvt<T>::from_f(apply_act_out<T>(a, p.act));
                     }
                 }
             }
@@ -869,7 +876,7 @@ __global__ void __launch_bounds__(256) splitk_reduce_kernel(const GemmParams p) 
         float v = acc[i];
         if (bias) v += Cvt<T>::to_f(bias[col0 + i]);
         if (resid) v += Cvt<T>::to_f(resid[row * p.ldr + col0 + i]);
-        out[row * p.ldc + col0 + i] = Cvt<T>::from_f(apply_act(v, p.act));
+        out[row * p.ldc + col0 + i] = Cvt<T>::from_f(apply_act_out<T>(v, p.act));
     }
 }
 

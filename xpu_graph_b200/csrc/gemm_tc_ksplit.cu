@@ -59,7 +59,7 @@ static_assert(sizeof(KsplitParams) <= 128, "keep the kernel parameter block with
 
 __device__ __forceinline__ float act_of(float v, int act) {
     switch (act) {
-        case XG_ACT_GELU: return 0.5f * v * (1.0f + erff(v * 0.70710678118654752f));
+        case XG_ACT_GELU: return gelu_erf_16bit(v);  // results of this file are always rounded to a 16-bit type
         case XG_ACT_RELU: return v > 0.f ? v : 0.f;
         case XG_ACT_SILU: return __fdividef(v, 1.0f + __expf(-v));
         case XG_ACT_SIGMOID: return __fdividef(1.0f, 1.0f + __expf(-v));
@@ -282,14 +282,11 @@ gemm_tc_ksplit_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
         if (ok && S > 1) ok = __all_sync(0xffffffffu, ptx::mbar_wait_bounded(recv_full, 0, abort_flag));
         if (ok) {
             ptx::tc_fence_after();
-#pragma unroll 1
-            for (int u = grp; u < 2 * mine; u += GROUPS) {
-                const int cl = u >> 1, half = u & 1;  // chunk within this pair's share, 16-column half
-                const int64_t col0 = (int64_t)nb * TN + (my_lo + cl) * 32 + half * 16;
-                if (col0 >= p.N) break;  // warp-uniform; later units of this warp lie further right
-                uint32_t own[16];
-                ptx::tmem_ld_32x16(tmem_base + lane_field + (uint32_t)((my_lo + cl) * 32 + half * 16), own);
-                ptx::tmem_ld_wait();
+            // unit u = 16 columns: chunk u >> 1 of this pair's share, half u & 1
+            auto unit_col0 = [&](int u) { return (int64_t)nb * TN + (my_lo + (u >> 1)) * 32 + (u & 1) * 16; };
+            auto unit_taddr = [&](int u) { return tmem_base + lane_field + (uint32_t)((my_lo + (u >> 1)) * 32 + (u & 1) * 16); };
+            auto finish_unit = [&](int u, const uint32_t (&own)[16]) {
+                const int cl = u >> 1, half = u & 1;
                 float v[16];
 #pragma unroll
                 for (int e = 0; e < 16; ++e) v[e] = 0.f;
@@ -311,7 +308,21 @@ gemm_tc_ksplit_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
                         }
                     }
                 }
-                store_cols16<T>(p, v, bias_s + (my_lo + cl) * 32 + half * 16, row, row < p.M, col0);
+                store_cols16<T>(p, v, bias_s + (my_lo + cl) * 32 + half * 16, row, row < p.M, unit_col0(u));
+            };
+            // two units per round: both accumulator reads are in flight before either is used (a round is mostly the
+            // latency of the TMEM read and of the stores, so a warp with three units to finish pays for two rounds, not three)
+#pragma unroll 1
+            for (int u = grp; u < 2 * mine; u += 2 * GROUPS) {
+                if (unit_col0(u) >= p.N) break;  // warp-uniform; later units of this warp lie further right
+                const int u2 = u + GROUPS;
+                const bool second = u2 < 2 * mine && unit_col0(u2) < p.N;
+                uint32_t own[16], own2[16];
+                ptx::tmem_ld_32x16(unit_taddr(u), own);
+                if (second) ptx::tmem_ld_32x16(unit_taddr(u2), own2);
+                ptx::tmem_ld_wait();
+                finish_unit(u, own);
+                if (second) finish_unit(u2, own2);
             }
         }
         if (!ok && lane == 0) atomicOr(&g_ksplit_status[0], 4u);
