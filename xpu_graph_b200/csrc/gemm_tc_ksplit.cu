@@ -440,7 +440,8 @@ bool ksplit_shape_ok(int S, int tn, int64_t nkb) {
 // about 45 KB/us per CTA and 0.5 us of synchronisation. The alternative - independent 128-row CTAs - streams at
 // about 127 KB/us per SM plus 3 us. The cluster kernel runs when it comes out at least 10 % ahead, which for
 // K = 4096 means 128 < M <= 512 at N = 4096 (13.3 vs 15.7 us at M = 256, 19.6 vs 26.9 us at M = 512) and M <= 256 at
-// N = 11008 (22.3 vs 36.3 us). Smaller M stays with split-K through scratch, which is ahead there.
+// N = 11008 (22.3 vs 36.3 us), and shapes with between one and two waves of 256 x 256 tiles (512 x 11008: 43 vs
+// 51 us for the pair kernel). Smaller M stays with split-K through scratch, which is ahead there.
 bool plan_ksplit(int64_t M, int64_t N, int64_t K, int dtype, int* S_out, int* tn_out) {
     static const int forced_s = []() {
         const char* e = getenv("XG_GEMM_KSPLIT");
@@ -462,7 +463,8 @@ bool plan_ksplit(int64_t M, int64_t N, int64_t K, int dtype, int* S_out, int* tn
     }
     if (M <= 128 || nkb < 8) return false;  // small M: split-K through scratch is ahead; short K: nothing to stream
     const int sms = num_sms();
-    if (mblk * ((N + 255) / 256) >= sms / 2) return false;  // enough 256 x 256 tiles for the persistent pair kernel
+    const int64_t tiles256 = mblk * ((N + 255) / 256);
+    if (tiles256 >= sms) return false;  // two full waves or more of 256 x 256 tiles: the persistent pair kernel's regime
     auto per_kblock = [](double kib, int tn) {
         const double load = 0.0142 * kib - 0.124, mma = tn / 256.0 * 0.26;
         const double t = load > mma ? load : mma;
@@ -492,7 +494,13 @@ bool plan_ksplit(int64_t M, int64_t N, int64_t K, int dtype, int* S_out, int* tn
     if (mblk128 * ((N + 255) / 256) < sms) bn = 128;
     if (bn == 128 && mblk128 * ((N + 127) / 128) < sms) bn = 64;
     const int64_t ctas = mblk128 * ((N + bn - 1) / bn);
-    const double other = (double)((ctas + sms - 1) / sms) * (double)nkb * (16.0 + bn * 0.125) / 127.0 + 3.0;
+    double other = (double)((ctas + sms - 1) / sms) * (double)nkb * (16.0 + bn * 0.125) / 127.0 + 3.0;
+    if (tiles256 >= sms / 2) {
+        // between one and two waves of 256 x 256 tiles the dispatcher would take the persistent pair kernel, whose last
+        // wave is mostly empty (86 tiles on 74 pairs: 51 us at 512 x 4096 x 11008 against 43 us for 138 tiles of 160 columns)
+        const double pair = (double)((tiles256 + sms / 2 - 1) / (sms / 2)) * ((double)nkb * per_kblock(32.0, 256) + 3.6);
+        if (pair < other) other = pair;
+    }
     if (best > 0.9 * other) return false;
     *S_out = best_s;
     *tn_out = best_tn;
