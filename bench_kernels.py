@@ -94,7 +94,9 @@ def sweep():
     for (M, K, N) in W.GEMM_SWEEP:
         a, w, b = W.make_gemm_inputs(M, K, N, device=dev)
         for act in ("gelu", "silu"):
-            ms = _time_graphed(lambda: X.dense(a, w, True, b, None, act), reps=5)
+            # 20 calls per graph for the cells of a few microseconds (the gap between graph replays would be 5-10 % of a
+            # 5-call graph there), 5 for the long ones
+            ms = _time_graphed(lambda: X.dense(a, w, True, b, None, act), reps=20 if M <= 256 else 5)
             tf = 2 * M * N * K / ms / 1e9
             gbs = 2 * (M * K + N * K + M * N) / ms / 1e6
             print(f"| {M} | {K} | {N} | bias+{act} | {ms * 1e3:.1f} | {tf:.0f} | {tf / peaks['bf16_tflops']:.2f} | {gbs:.0f} |")
