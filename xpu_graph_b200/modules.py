@@ -70,6 +70,9 @@ class AddLayerNormModule(torch.nn.Module):
 
 
 # ---- dense layers --------------------------------------------------------------------------
+UNALIGNED_16BIT_MAX_FLOPS = 1 << 26
+
+
 class DenseLayerModule(torch.nn.Module):
     """CustomDenseLayer target (structure/custom_denselayer.py:80-88):
     ``M(fast_act)``; forward(inputs, weight, weight_trans, bias, act). Bias handling follows
@@ -108,7 +111,19 @@ def can_fuse_custom_denselayer(inputs, weight, weight_trans, bias, act_str):
         return False
     if inputs.device.type not in ALLOWED_DEVICE_TYPES:
         return False
-    # any extents: 16-bit rows a tensor map cannot address (not multiples of 16 bytes) run on the library's FMA kernel
+    if inputs.dtype != torch.float32:
+        # 16-bit rows a tensor map cannot address (not multiples of 16 bytes: K for the activations and [N, K] weights,
+        # N for weights given as [K, N]) run on the library's FMA kernel. That wins while the layer is mostly launches
+        # (one fused launch against matmul + add + activation); beyond about 64 MFLOP the vendor matmul is the faster
+        # home for such a shape, and the layer is left to it.
+        unaligned = inputs.shape[1] % 8 != 0 or (not weight_trans and weight.shape[1] % 8 != 0)
+        if unaligned:
+            try:
+                flops = 2 * int(inputs.shape[0]) * int(weight.shape[0]) * int(weight.shape[1])
+            except (TypeError, RuntimeError):  # symbolic extents: size unknown at compile time
+                return False
+            if flops > UNALIGNED_16BIT_MAX_FLOPS:
+                return False
     return True
 
 
