@@ -115,9 +115,10 @@ int xg_swiglu(const void* gate, const void* up, void* out, int64_t rows, int64_t
 /*
  * out[M,N] = act( A[M,K] @ W + bias + residual ),  W = B[K,N] (trans_b = 0) or B[N,K]^T (trans_b = 1).
  * bias: nullable [N]; residual: nullable [M,N] with row stride ldr (the "2-D bias" / beta = 1 form);
- * act: XG_ACT_*. dtype XG_BF16 / XG_F16: tensor-core path (tcgen05, fp32 accumulate; A and B must be
- * 16-byte aligned with row strides that are multiples of 8 elements, else XG_ERR_UNSUPPORTED);
- * dtype XG_F32: true fp32 FMA path (no TF32).
+ * act: XG_ACT_*. dtype XG_BF16 / XG_F16: tensor-core path (tcgen05, fp32 accumulate) when A and B are
+ * 16-byte aligned with row strides that are multiples of 8 elements; other 16-bit operands run on the
+ * FMA kernel (elements converted on the way in and out, fp32 accumulate) - correct for any extents, meant
+ * for small layers. dtype XG_F32: true fp32 FMA path (no TF32).
  * Replaces: targets/mlu/structure_replacements/dense_layer_modules.py:9-57 (DenseLayerModule →
  * torch_mlu_ops.matmul) as called by passes/patterns/structure/custom_denselayer.py:80-88.
  */
