@@ -90,8 +90,8 @@ template <typename T>
 __global__ void __launch_bounds__(MS_THREADS) mlp_small_kernel(const MlpSmallParams p) {
     extern __shared__ __align__(16) float ms_smem[];
     // [weights of layer 0 | 1 | 2: Kp x N each, rows k >= K zero][biases][activation buffer A][activation buffer B]
-    float* w_s[3];
-    float* b_s[3];
+    float* w_s[3] = {ms_smem, ms_smem, ms_smem};
+    float* b_s[3] = {ms_smem, ms_smem, ms_smem};
     float* cur = ms_smem;
     int max_dim = p.dims[0];
     for (int l = 0; l < p.layers; ++l) {
@@ -108,33 +108,52 @@ __global__ void __launch_bounds__(MS_THREADS) mlp_small_kernel(const MlpSmallPar
     float* act_b = cur + MS_ROWS * pitch;
     const int tid = threadIdx.x;
 
-    // Loads go out in batches of MS_BATCH per thread before any of them is used: one trip to memory per batch instead of
-    // one per element (a CTA that serves 16 rows spends its whole life in these loops).
-    for (int l = 0; l < p.layers; ++l) {
-        const int K = p.dims[l], N = p.dims[l + 1], Kp = ms_pad4(K);
-        const T* __restrict__ w = reinterpret_cast<const T*>(p.w[l]);
-        const bool kn = (p.w_kn >> l) & 1;
-        const int64_t ldw = p.ldw[l];
-        const int total = Kp * N;
-        for (int base = tid; base < total; base += MS_BATCH * MS_THREADS) {
-            float v[MS_BATCH];
-            int dst[MS_BATCH];
+    // Filling shared memory. A CTA that serves 16 rows spends its life waiting on memory, so the loads of ALL layers'
+    // weights and biases (MS_BATCH elements per thread and layer) go out before any of them is used: one trip to memory
+    // per pass over the three layers instead of one per layer and batch.
+    {
+        int totals[3], max_total = 0;
 #pragma unroll
-            for (int u = 0; u < MS_BATCH; ++u) {
-                const int idx = base + u * MS_THREADS;
-                // consecutive threads read consecutive elements of the stored rows
-                int k, n;
-                if (kn) { k = idx / N; n = idx - k * N; }
-                else { n = idx / Kp; k = idx - n * Kp; }
-                dst[u] = idx < total ? k * N + n : -1;
-                v[u] = (idx < total && k < K) ? Cvt<T>::to_f(kn ? w[(int64_t)k * ldw + n] : w[(int64_t)n * ldw + k]) : 0.f;
+        for (int l = 0; l < 3; ++l) {
+            totals[l] = l < p.layers ? ms_pad4(p.dims[l]) * p.dims[l + 1] : 0;
+            if (totals[l] > max_total) max_total = totals[l];
+        }
+        for (int base = tid; base < max_total; base += MS_BATCH * MS_THREADS) {
+            float v[3][MS_BATCH];
+            int dst[3][MS_BATCH];
+#pragma unroll
+            for (int l = 0; l < 3; ++l) {
+                const bool used = l < p.layers;  // unused layers: extents that divide, nothing loaded or stored
+                const int K = used ? p.dims[l] : 4, N = used ? p.dims[l + 1] : 1, Kp = ms_pad4(K);
+                const T* __restrict__ w = reinterpret_cast<const T*>(p.w[l]);
+                const bool kn = (p.w_kn >> l) & 1;
+                const int64_t ldw = p.ldw[l];
+#pragma unroll
+                for (int u = 0; u < MS_BATCH; ++u) {
+                    const int idx = base + u * MS_THREADS;
+                    // consecutive threads read consecutive elements of the stored rows
+                    int k, n;
+                    if (kn) { k = idx / N; n = idx - k * N; }
+                    else { n = idx / Kp; k = idx - n * Kp; }
+                    const bool in = idx < totals[l];
+                    dst[l][u] = in ? k * N + n : -1;
+                    v[l][u] = (in && k < K) ? Cvt<T>::to_f(kn ? w[(int64_t)k * ldw + n] : w[(int64_t)n * ldw + k]) : 0.f;
+                }
+            }
+            float bv[3];
+#pragma unroll
+            for (int l = 0; l < 3; ++l) {  // the biases ride in the first pass (widths <= 128 < MS_THREADS)
+                const T* b = reinterpret_cast<const T*>(p.bias[l]);
+                bv[l] = (base == tid && l < p.layers && b != nullptr && tid < p.dims[l + 1]) ? Cvt<T>::to_f(b[tid]) : 0.f;
             }
 #pragma unroll
-            for (int u = 0; u < MS_BATCH; ++u)
-                if (dst[u] >= 0) w_s[l][dst[u]] = v[u];
+            for (int l = 0; l < 3; ++l) {
+#pragma unroll
+                for (int u = 0; u < MS_BATCH; ++u)
+                    if (dst[l][u] >= 0) w_s[l][dst[l][u]] = v[l][u];
+                if (base == tid && l < p.layers && tid < p.dims[l + 1]) b_s[l][tid] = bv[l];
+            }
         }
-        const T* b = reinterpret_cast<const T*>(p.bias[l]);
-        for (int n = tid; n < N; n += MS_THREADS) b_s[l][n] = b ? Cvt<T>::to_f(b[n]) : 0.f;
     }
 
     const T* __restrict__ x = reinterpret_cast<const T*>(p.x);
