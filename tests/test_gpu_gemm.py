@@ -677,7 +677,8 @@ def test_dense_tower_module_takes_the_small_kernel(cuda_device):
         assert_parity(got, _chain_reference(x, ws, bs, acts, (True, True, True), dtype), f"dense tower {dtype} {dims}")
 
 
-@pytest.mark.parametrize("M,K,N,weight_trans,act", [(128, 5897, 5897, True, "gelu"), (50, 444, 300, False, "relu"), (7, 20, 1, False, "none")])
+@pytest.mark.parametrize("M,K,N,weight_trans,act", [(128, 5897, 5897, True, "gelu"), (50, 444, 300, False, "relu"), (7, 20, 1, False, "none"),
+                                                    (2048, 100, 2564, True, "silu"), (2100, 36, 2564, False, "none")])
 def test_dense_16bit_rows_no_tensor_map_addresses(cuda_device, M, K, N, weight_trans, act):
     """16-bit dense layers whose rows are not multiples of 16 bytes (the sizes of tests/mlu/test_custom_denselayer.py run
     in 16-bit: K = 5897, 444) run on the library's FMA kernel: bias, residual and activation fused as everywhere else."""
