@@ -569,11 +569,13 @@ def test_combo_dense(cuda_device, T, M, K, N, weight_trans, with_bias):
 @pytest.mark.parametrize("T,M,K,N,weight_trans,bias_kind", [(8, 5, 8, 7, False, "matrix"), (8, 5, 8, 7, False, "row"),
                                                              (8, 5, 8, 7, True, "none"), (6, 40, 64, 48, True, "row"),
                                                              (30, 33, 100, 70, True, "matrix"), (5, 300, 256, 520, False, "row"),
-                                                             (4, 1024, 192, 1024, True, "matrix")])
+                                                             (4, 1024, 192, 1024, True, "matrix"), (8, 256, 64, 256, True, "row"),
+                                                             (5, 1024, 64, 1100, False, "matrix")])
 def test_combo_dense_fp32(cuda_device, T, M, K, N, weight_trans, bias_kind):
     """fp32 layers in one grouped launch of the FMA kernels (the entry is the grid's third dimension; 30 layers need two
     launches of at most 24): the reference's own sizes (tests/mlu/test_combo_matmul.py:90-100: T = 8, 5 x 8 x 7, [K, N]
-    weights, full-matrix or row biases) and sizes that reach each of the three kernel choices, against fp64 math."""
+    weights, full-matrix or row biases) and sizes that reach each of the four kernel choices (two panel tiles, two tiled
+    kernels), against fp64 math."""
     from xpu_graph_b200.modules import ComboDenseModule
 
     g = torch.Generator().manual_seed(34)
