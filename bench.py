@@ -533,42 +533,43 @@ def run_ours(args) -> dict | None:
     # Inside the step it runs right after 4 ms of dense layers at the power cap and inherits their clock (and a GPU that
     # has just run such steps for seconds keeps that clock for a while: timed after the benchmark the same launch reads
     # 0.30-0.35 ms); this figure is the same launch timed back to back on its own, so that kernel and clock can be told apart.
-    hd = HIDDEN // HEADS
-    qkv = [torch.randn(per_gpu, SEQ, HEADS, hd, device=dev, dtype=torch.bfloat16).transpose(1, 2) for _ in range(3)]
+    attn_alone = None
+    if not args.no_attention_alone:
+        hd = HIDDEN // HEADS
+        qkv = [torch.randn(per_gpu, SEQ, HEADS, hd, device=dev, dtype=torch.bfloat16).transpose(1, 2) for _ in range(3)]
 
-    def attention_alone():
-        return torch.ops.xg_sm100.sdpa(qkv[0], qkv[1], qkv[2], None, hd ** -0.5, True)
+        def attention_alone():
+            return torch.ops.xg_sm100.sdpa(qkv[0], qkv[1], qkv[2], None, hd ** -0.5, True)
 
-    # (replayed from a CUDA graph: launched from Python one by one, the host - three tensor maps and an op dispatch per
-    # call - is slower than this kernel)
-    reps, replays = 8, 9
-    attention_alone()
-    torch.cuda.synchronize()
-    side = torch.cuda.Stream(dev)
-    side.wait_stream(stream)
-    graph = torch.cuda.CUDAGraph()
-    with torch.cuda.graph(graph, stream=side):
-        for _ in range(reps):
-            attention_alone()
-    stream.wait_stream(side)
-    for _ in range(replays):  # warm-up: the clock takes some milliseconds to come back up after the host-side capture
-        graph.replay()
-    torch.cuda.synchronize()
-    marks = [torch.cuda.Event(enable_timing=True) for _ in range(replays + 1)]
-    marks[0].record(stream)
-    for i in range(replays):
-        graph.replay()
-        marks[i + 1].record(stream)
-    torch.cuda.synchronize()
-    per_replay = [marks[i].elapsed_time(marks[i + 1]) / reps for i in range(replays)]
-    alone_ms = sorted(per_replay)[replays // 2]
-    alone = 2.0 * per_gpu * HEADS * SEQ * SEQ * hd / (alone_ms * 1e-3) / 1e12  # causal: half of 4 B H S^2 D
-    attn_alone = {"ms_per_launch": alone_ms, "achieved": alone, "launches": reps * replays,
-                  "ms_per_launch_by_replay": [round(t, 4) for t in per_replay],
-                  "note": "same launch replayed back to back from a CUDA graph before the timed steps; median replay"}
-    del graph
-    del qkv
-
+        # (replayed from a CUDA graph: launched from Python one by one, the host - three tensor maps and an op dispatch per
+        # call - is slower than this kernel)
+        reps, replays = 8, 9
+        attention_alone()
+        torch.cuda.synchronize()
+        side = torch.cuda.Stream(dev)
+        side.wait_stream(stream)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=side):
+            for _ in range(reps):
+                attention_alone()
+        stream.wait_stream(side)
+        for _ in range(replays):  # warm-up: the clock takes some milliseconds to come back up after the host-side capture
+            graph.replay()
+        torch.cuda.synchronize()
+        marks = [torch.cuda.Event(enable_timing=True) for _ in range(replays + 1)]
+        marks[0].record(stream)
+        for i in range(replays):
+            graph.replay()
+            marks[i + 1].record(stream)
+        torch.cuda.synchronize()
+        per_replay = [marks[i].elapsed_time(marks[i + 1]) / reps for i in range(replays)]
+        alone_ms = sorted(per_replay)[replays // 2]
+        alone = 2.0 * per_gpu * HEADS * SEQ * SEQ * hd / (alone_ms * 1e-3) / 1e12  # causal: half of 4 B H S^2 D
+        attn_alone = {"ms_per_launch": alone_ms, "achieved": alone, "launches": reps * replays,
+                      "ms_per_launch_by_replay": [round(t, 4) for t in per_replay],
+                      "note": "same launch replayed back to back from a CUDA graph before the timed steps; median replay"}
+        del graph
+        del qkv
 
     # ---- device-resident throughput -------------------------------------------------------
     for _ in range(warmup):
@@ -621,8 +622,9 @@ def run_ours(args) -> dict | None:
     e2e = {"value": world * per_gpu / (e2e_ms * 1e-3), "unit": UNIT, "h2d_bytes_per_step": nbytes, "d2h_bytes_per_step": nbytes,
            "ms_per_step": e2e_ms, "overlap": "3-stream pipeline: H2D(i+1) | compute(i) | D2H(i-1)"}
 
-    attn_alone["frac_burst"] = attn_alone["achieved"] / roofline_attn["peak_burst"]
-    roofline_attn["alone"] = attn_alone
+    if attn_alone is not None:
+        attn_alone["frac_burst"] = attn_alone["achieved"] / roofline_attn["peak_burst"]
+        roofline_attn["alone"] = attn_alone
 
     status = lib.tc_status()
     if status != 0:
@@ -661,6 +663,8 @@ def main():
     ap.add_argument("--global-batch", type=int, default=0,
                     help="strong scaling: split this many samples per step over the GPUs (default: 8 samples per GPU, weak scaling)")
     ap.add_argument("--no-xpu-graph", action="store_true", help="time the assembled op sequence even if xpu_graph is importable")
+    ap.add_argument("--no-attention-alone", action="store_true",
+                    help="skip the stand-alone timing of the attention launch (144 extra launches; for launch-list captures)")
     ap.add_argument("--copy-only", choices=["both", "h2d", "d2h"], default=None,
                     help="no compute: only the pinned host <-> device copies of the end-to-end leg")
     args = ap.parse_args()
