@@ -171,3 +171,26 @@ def test_weight_plane_cache_key_with_untracked_tensors():
     ops.invalidate_weight_planes(w)
     assert not hasattr(w, "_xg_bf16_planes")
     ops.invalidate_weight_planes(w)  # idempotent
+
+
+def test_small_m_plan_and_tower_routing_without_gpu():
+    """Host-side decisions that need no device: the split-K plan of dense layers with M <= 128 (scratch size = splits x
+    M x N x 4 bytes; the measured best choices of the sweep it was fitted to) and the routing of narrow towers."""
+    import torch
+
+    from xpu_graph_b200 import ops
+
+    L = lib.load()
+    splits = lambda M, N, K: L.xg_gemm_workspace_bytes(M, N, K, lib.XG_BF16) // (M * N * 4)  # noqa: E731
+    assert [splits(M, 4096, 4096) for M in (16, 64, 128)] == [4, 4, 4]      # 128-wide tiles x 4 splits = 128 CTAs
+    assert splits(128, 2048, 4096) == 4 and splits(128, 1024, 4096) == 8    # 64-wide tiles for narrow outputs
+    assert splits(16, 11008, 4096) == 3                                     # 43 tiles of 256 x 3 = 129 CTAs
+    assert splits(128, 11008, 4096) == 0 and splits(64, 11008, 4096) == 0   # 86 tiles of 128, unsplit: partial sums would leave L2
+    assert splits(256, 4096, 4096) == 0 and splits(4096, 4096, 4096) == 0   # the cluster / pair kernels need none
+    # narrow towers: every width <= 128 and <= 24576 weight elements fit the kernel; it is used for few rows or tiny layers
+    assert ops.mlp_small_eligible((20, 32, 16, 1), torch.float16) and not ops.mlp_small_eligible((20, 256, 16), torch.float16)
+    assert not ops.mlp_small_eligible((128, 128, 128, 128), torch.float32)
+    assert ops.mlp_small_worth_it(16, (20, 32, 16, 1), torch.float16) and ops.mlp_small_worth_it(16384, (64, 32, 16, 1), torch.float32)
+    assert not ops.mlp_small_worth_it(16384, (128, 64, 32), torch.float32) and ops.mlp_small_worth_it(2048, (128, 64, 32), torch.float32)
+    assert ops._small_run((20, 32, 16, 1), 0, 3, torch.float16, 16) == 3 and ops._small_run((512, 32, 16, 1), 0, 3, torch.float16, 16) == 1
+    assert ops._small_run((512, 32, 16, 1), 1, 3, torch.float16, 16) == 2
