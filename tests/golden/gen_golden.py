@@ -15,6 +15,10 @@ What is recorded (inputs and outputs, all seeded, all small):
       - slice + cat graphs incl. the INT64_MAX / negative-end cases of tests/mlu/test_fuse_slice_cat.py:293-323,
       - multi-slice + stack, embedding + where + stack, RoPE and SwiGLU chains,
       - the three benchmark graphs at reduced size (encoder block, Llama-style layer, recsys graph).
+`python tests/golden/gen_golden.py v4` writes tests/golden/golden_v4.pt: the graph forms of the reference's combo
+and dense-tower tests at their own sizes (tests/mlu/test_combo_matmul.py:17-109, test_fuse_densetower.py:17-53: eight
+layers of 5 x 8 x 7 in fp32 over a shared or split input with no bias, a row or a full [M, N] addend; lists of bmm;
+16 rows of 20 -> 32 -> 16 -> 1 in fp16 with [K, N] weights) and a bf16 layer whose rows no tensor map addresses;
 `python tests/golden/gen_golden.py v3` writes tests/golden/golden_v3.pt (16-bit towers of narrow dense layers);
 `python tests/golden/gen_golden.py v2` writes tests/golden/golden_v2.pt the same way: slice -> sum -> cat,
 mul -> sum -> cat and sum -> cat graphs (targets/mlu/fuse_sum_cat.py, fuse_mul_sum_cat.py), a chain of three dense
@@ -270,10 +274,90 @@ def main_v3():
     print(f"wrote {out}: {len(G)} cases, {os.path.getsize(out) / 1024:.0f} KiB")
 
 
+def main_v4():
+    """Fourth fixture file: see the module docstring."""
+    G = {}
+    g = torch.Generator().manual_seed(4321)
+
+    def rn(*shape, dtype=torch.float32, std=1.0):
+        return (torch.randn(*shape, generator=g) * std).to(dtype)
+
+    T, M, K, N = 8, 5, 8, 7
+    shared, split = rn(1, M, K), rn(T, M, K)
+    ws = [rn(K, N) for _ in range(T)]
+    rows, mats = [rn(N) for _ in range(T)], [rn(M, N) for _ in range(T)]
+
+    def shared_plain(x, *w):
+        x = x.squeeze(0)
+        return tuple(x @ wi for wi in w)
+
+    def shared_bias(x, *wb):
+        x = x.squeeze(0)
+        return tuple(x @ wi + bi for wi, bi in zip(wb[:T], wb[T:]))
+
+    def shared_bias_relu(x, *wb):
+        x = x.squeeze(0)
+        return tuple(torch.relu(x @ wi + bi) for wi, bi in zip(wb[:T], wb[T:]))
+
+    def split_linear_t(x, *w):
+        xs = [i.squeeze(0) for i in x.split(x.shape[0] // T, dim=0)]
+        return tuple(torch.relu(F.linear(xi, wi.T)) for xi, wi in zip(xs, w))
+
+    G["combo_plain"] = dict(x=shared, ws=ws, bs=[None] * T, act="none", shared=True, y=list(run_ref(shared_plain, shared, *ws)))
+    G["combo_matrix_bias"] = dict(x=shared, ws=ws, bs=mats, act="none", shared=True, y=list(run_ref(shared_bias, shared, *ws, *mats)))
+    G["combo_row_bias"] = dict(x=shared, ws=ws, bs=rows, act="none", shared=True, y=list(run_ref(shared_bias, shared, *ws, *rows)))
+    G["combo_matrix_bias_relu"] = dict(x=shared, ws=ws, bs=mats, act="relu", shared=True, y=list(run_ref(shared_bias_relu, shared, *ws, *mats)))
+    G["combo_split_linear_t"] = dict(x=split, ws=ws, bs=[None] * T, act="relu", shared=False, y=list(run_ref(split_linear_t, split, *ws)))
+
+    S, Mb, Kb, Nb = 3, 5, 6, 7
+    xb = rn(S, Mb, Kb)
+    wbs = [rn(S, Kb, Nb) for _ in range(T)]
+    bbs = [rn(S, Mb, Nb) for _ in range(T)]
+
+    def bmm_plain(x, *w):
+        return tuple(torch.bmm(x, wi) for wi in w)
+
+    def bmm_addend(x, *wb):
+        return tuple(x @ wi + bi for wi, bi in zip(wb[:T], wb[T:]))
+
+    G["combo_bmm_plain"] = dict(x=xb, ws=wbs, bs=[None] * T, y=list(run_ref(bmm_plain, xb, *wbs)))
+    G["combo_bmm_addend"] = dict(x=xb, ws=wbs, bs=bbs, y=list(run_ref(bmm_addend, xb, *wbs, *bbs)))
+
+    dims = (20, 32, 16, 1)
+    x = rn(16, dims[0], dtype=torch.float16)
+    tw = [rn(dims[i], dims[i + 1], dtype=torch.float16, std=dims[i] ** -0.5) for i in range(3)]
+    tb = [rn(dims[i + 1], dtype=torch.float16) for i in range(3)]
+
+    def tower(x, w1, w2, w3, b1, b2, b3):
+        out = F.relu(torch.matmul(x, w1) + b1)
+        out = F.relu(torch.matmul(out, w2) + b2)
+        return torch.matmul(out, w3) + b3
+
+    G["tower_kn_f16"] = dict(x=x, ws=tw, bs=tb, acts=["relu", "relu", "none"], y=run_ref(tower, x, *tw, *tb))
+
+    xa, wa, ba = rn(50, 444, dtype=torch.bfloat16), rn(300, 444, dtype=torch.bfloat16, std=444 ** -0.5), rn(300, dtype=torch.bfloat16)
+    G["dense_unaligned_bf16"] = dict(x=xa, w=wa, b=ba, act="gelu", y=run_ref(lambda x, w, b: F.gelu(F.linear(x, w, b)), xa, wa, ba))
+
+    def compact(o):
+        if isinstance(o, torch.Tensor):
+            return o.detach().clone().contiguous()
+        if isinstance(o, dict):
+            return {k: compact(v) for k, v in o.items()}
+        if isinstance(o, (list, tuple)):
+            return type(o)(compact(v) for v in o)
+        return o
+
+    out = os.path.join(HERE, "golden_v4.pt")
+    torch.save(compact(G), out)
+    print(f"wrote {out}: {len(G)} cases, {os.path.getsize(out) / 1024:.0f} KiB")
+
+
 if __name__ == "__main__":
     if len(sys.argv) > 1 and sys.argv[1] == "v2":
         main_v2()
     elif len(sys.argv) > 1 and sys.argv[1] == "v3":
         main_v3()
+    elif len(sys.argv) > 1 and sys.argv[1] == "v4":
+        main_v4()
     else:
         main()

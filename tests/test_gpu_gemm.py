@@ -312,6 +312,42 @@ def test_mlp_against_reference_fixtures(cuda_device, name, tag):
     assert_parity(got, c["y"], f"chained-layer kernel vs reference fixture ({name}, {tag})")
 
 
+def test_grouped_tower_and_unaligned_kernels_against_reference_fixtures(cuda_device):
+    """The grouped fp32 launches, the batched-list form, the weights-in-shared-memory tower and the 16-bit FMA path on
+    the inputs of tests/golden/golden_v4.pt (the reference's combo and dense-tower test graphs at their own sizes) vs
+    the outputs the reference pipeline recorded for them; one launch each."""
+    import os
+
+    from tests.helpers import LaunchCounter
+    from xpu_graph_b200.modules import ComboBatchDenseModule, ComboDenseModule, DenseLayerModule, DenseTowerModule
+
+    G4 = torch.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "golden_v4.pt"))
+    dev = lambda t: None if t is None else t.to(cuda_device)  # noqa: E731
+    for name in ("combo_plain", "combo_matrix_bias", "combo_row_bias", "combo_matrix_bias_relu", "combo_split_linear_t"):
+        c = G4[name]
+        x = dev(c["x"])
+        xs = [x[0]] * len(c["ws"]) if c["shared"] else list(x.unbind(0))
+        with LaunchCounter() as launches:
+            got = ComboDenseModule()(xs, [dev(w) for w in c["ws"]], [dev(b) for b in c["bs"]], c["act"], False)
+        assert launches.names == ["xg_gemm_group_bias_act"], (name, launches.names)
+        assert_parity(got, torch.stack(list(c["y"])), f"{name} vs reference fixture")
+    for name in ("combo_bmm_plain", "combo_bmm_addend"):
+        c = G4[name]
+        with LaunchCounter() as launches:
+            got = ComboBatchDenseModule()([dev(c["x"])] * len(c["ws"]), [dev(w) for w in c["ws"]], [dev(b) for b in c["bs"]], "none", False)
+        assert launches.names == ["xg_gemm_group_bias_act"], (name, launches.names)
+        assert_parity(got, torch.stack(list(c["y"])), f"{name} vs reference fixture")
+    c = G4["tower_kn_f16"]
+    with LaunchCounter() as launches:
+        got = DenseTowerModule()(dev(c["x"]), [dev(w) for w in c["ws"]], [False] * 3, [dev(b) for b in c["bs"]], c["acts"])
+    assert launches.names == ["xg_mlp_small_bias_act"], launches.names
+    assert_parity(got, c["y"], "narrow tower vs reference fixture")
+    c = G4["dense_unaligned_bf16"]
+    got = DenseLayerModule(False)(dev(c["x"]), dev(c["w"]), True, dev(c["b"]), c["act"])
+    torch.cuda.synchronize()
+    assert_parity(got, c["y"], "bf16 layer with K = 444 vs reference fixture")
+
+
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
 def test_mlp_kn_weights(cuda_device, dtype):
     """Weights stored [K, N] (the operand of torch.matmul(x, W), the form of the reference's dense-tower test) are

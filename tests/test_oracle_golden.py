@@ -166,3 +166,28 @@ def test_narrow_towers(name, tag):
         y = ref_ops.dense(y, w, True, b, a)
     _close(y, c["y"], f"tower {name} {tag}")
 
+
+
+GOLDEN4 = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "golden_v4.pt")
+
+
+def test_combo_tower_and_unaligned_forms():
+    """The reference's combo and dense-tower test graphs at their own sizes, and a bf16 layer with 888-byte rows, as the
+    reference pipeline computes them (golden_v4.pt): the oracle's per-layer functions reproduce them."""
+    G4 = torch.load(GOLDEN4)
+    for name in ("combo_plain", "combo_matrix_bias", "combo_row_bias", "combo_matrix_bias_relu", "combo_split_linear_t"):
+        c = G4[name]
+        xs = [c["x"][0]] * len(c["ws"]) if c["shared"] else list(c["x"].unbind(0))
+        for x, w, b, want in zip(xs, c["ws"], c["bs"], c["y"]):
+            _close(ref_ops.dense(x, w, False, b, c["act"]), want, name)
+    for name in ("combo_bmm_plain", "combo_bmm_addend"):
+        c = G4[name]
+        for w, b, want in zip(c["ws"], c["bs"], c["y"]):
+            _close(ref_ops.batch_dense(c["x"], w, False, b, "none"), want, name)
+    c = G4["tower_kn_f16"]
+    y = c["x"]
+    for w, b, a in zip(c["ws"], c["bs"], c["acts"]):
+        y = ref_ops.dense(y, w, False, b, a)
+    _close(y, c["y"], "tower with [K, N] weights, fp16")
+    c = G4["dense_unaligned_bf16"]
+    _close(ref_ops.dense(c["x"], c["w"], True, c["b"], c["act"]), c["y"], "bf16 layer with K = 444")
