@@ -270,3 +270,39 @@ def test_combo_matmul_forms_on_gpu(cuda_device):
         for o, w in zip(got, want):
             assert_parity(o, w.float(), f"combo {fn.__name__}")
         torch._dynamo.reset()
+
+
+def test_dynamic_batch_on_gpu(cuda_device):
+    """One compilation with a symbolic batch dimension (mark_dynamic) serves several batch sizes on the GPU: the grouped
+    launch, the narrow tower and the residual-add LayerNorm run with the actual row count of each call."""
+    from tests.helpers import LaunchCounter
+    from xpu_graph_b200 import target
+
+    torch.manual_seed(16)
+
+    class Towers(torch.nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.layers = torch.nn.ModuleList(torch.nn.Linear(64, 48) for _ in range(5))
+            self.chain = torch.nn.Sequential(torch.nn.Linear(20, 32), torch.nn.ReLU(), torch.nn.Linear(32, 16), torch.nn.ReLU(),
+                                             torch.nn.Linear(16, 1))
+            self.ln = torch.nn.LayerNorm(64)
+
+        def forward(self, x, z, r):
+            return tuple(torch.relu(layer(x)) for layer in self.layers) + (self.chain(z), self.ln(x + r))
+
+    model = Towers().eval().to(cuda_device)
+    compiled = torch.compile(model, backend=target.backend(target.make_config()), dynamic=None)
+    for m in (6, 50, 300):
+        args = (torch.randn(m, 64, device=cuda_device), torch.randn(m, 20, device=cuda_device), torch.randn(m, 64, device=cuda_device))
+        for a in args:
+            torch._dynamo.mark_dynamic(a, 0)
+        with torch.no_grad():
+            with LaunchCounter() as c:
+                got = compiled(*args)
+            want = model.double()(*(a.double() for a in args))
+            model.float()
+        torch.cuda.synchronize()
+        assert sorted(c.names) == sorted(["xg_gemm_group_bias_act", "xg_mlp_small_bias_act", "xg_layernorm"]), c.names
+        for o, w in zip(got, want):
+            assert_parity(o, w.float(), f"dynamic batch {m}")

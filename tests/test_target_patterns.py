@@ -717,6 +717,62 @@ def test_combo_batch_dense_reference_forms(tgt, xlog):
         torch._dynamo.reset()
 
 
+def test_dynamic_batch_keeps_the_fusions(tgt):
+    """A symbolic row count (torch._dynamo.mark_dynamic on the batch dimension, parameters static - the way the reference's
+    tests compile with dynamic=True) does not cost the grouped launch, the dense tower or the residual-add norm: one
+    compilation serves three batch sizes and ends in the same modules as the static graph."""
+    torch.manual_seed(14)
+
+    class Towers(torch.nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.layers = torch.nn.ModuleList(torch.nn.Linear(64, 48) for _ in range(5))
+
+        def forward(self, x):
+            return tuple(torch.relu(layer(x)) for layer in self.layers)
+
+    class Chain(torch.nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.a, self.b, self.c = torch.nn.Linear(20, 32), torch.nn.Linear(32, 16), torch.nn.Linear(16, 1)
+
+        def forward(self, x):
+            return self.c(torch.relu(self.b(torch.relu(self.a(x)))))
+
+    class AddNorm(torch.nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.ln = torch.nn.LayerNorm(64)
+
+        def forward(self, x, r):
+            return self.ln(x + r)
+
+    cases = ((Towers().eval(), lambda m: (torch.randn(m, 64),), ["xg_combo_dense"]),
+             (Chain().eval(), lambda m: (torch.randn(m, 20),), ["xg_dense_tower"]),
+             (AddNorm().eval(), lambda m: (torch.randn(m, 64), torch.randn(m, 64)), ["xg_add_layer_norm_y"]))
+    for mod, make, expect in cases:
+        torch._dynamo.reset()
+        cap, graphs = {}, []
+        inner = tgt.backend(tgt.make_config(), capture=cap)
+
+        def counting(gm, example_inputs, inner=inner, graphs=graphs):
+            graphs.append(1)
+            return inner(gm, example_inputs)
+
+        compiled = torch.compile(mod, backend=counting, dynamic=None)
+        for m in (5, 9, 13):
+            args = make(m)
+            for a in args:
+                torch._dynamo.mark_dynamic(a, 0)
+            with torch.no_grad():
+                got, want = compiled(*args), mod(*args)
+            for o, w in zip(got if isinstance(got, tuple) else (got,), want if isinstance(want, tuple) else (want,)):
+                _same(o, w, 1e-5)
+        assert [n.target for n in cap["gm"].graph.nodes if n.op == "call_module"] == expect
+        assert len(graphs) == 1, "one compilation for all three batch sizes"
+    torch._dynamo.reset()
+
+
 def test_sum_cat_fusions(tgt, xlog):
     """slice -> sum -> cat, mul -> sum -> cat and sum -> cat along the last dim become one module call each
     (graph forms of targets/mlu/fuse_sum_cat.py and fuse_mul_sum_cat.py; the reference's tests

@@ -57,6 +57,27 @@ def _static(shape) -> bool:
     return all(isinstance(s, int) for s in shape)
 
 
+def _static_but_rows(shape) -> bool:
+    """Every extent but the first is a plain int; the first (the row / batch count) may be symbolic (dynamic=True)."""
+    return len(shape) >= 1 and _static(tuple(shape)[1:]) and (isinstance(shape[0], int) or isinstance(shape[0], torch.SymInt))
+
+
+def _rows_hint(n) -> int:
+    """A row count as a number: itself, or the example value a symbolic one was traced with (0 if it has none)."""
+    if isinstance(n, int):
+        return n
+    from torch.fx.experimental import symbolic_shapes as ss
+
+    if hasattr(ss, "size_hint"):  # the name on current releases; hint_int is its older spelling
+        return int(ss.size_hint(n, fallback=0))
+    return int(ss.hint_int(n)) if ss.has_hint(n) else 0
+
+
+def _shape_key(shape) -> tuple:
+    """Hashable stand-in for a shape that may hold symbolic extents (equal expressions give equal keys)."""
+    return tuple(s if isinstance(s, int) else str(s) for s in shape)
+
+
 def _only_user(node: fx.Node, user: fx.Node) -> bool:
     return len(node.users) == 1 and next(iter(node.users)) is user
 
@@ -1276,7 +1297,9 @@ class FusedComboDense(Pattern):
                 continue
             x, w, wt, bias, act = n.args
             xv, wv, bv, v = _val(x), _val(w), _val(bias), _val(n)
-            if not (_tensor_ok(xv, rank) and _tensor_ok(wv, rank) and _tensor_ok(v, rank) and _static(xv.shape) and _static(wv.shape)):
+            # (2-D members may have a symbolic row count, the same expression in all of them; batched ones are static)
+            x_ok = _static_but_rows(xv.shape) if (rank == 2 and isinstance(xv, torch.Tensor)) else _static(xv.shape) if isinstance(xv, torch.Tensor) else False
+            if not (_tensor_ok(xv, rank) and _tensor_ok(wv, rank) and _tensor_ok(v, rank) and x_ok and _static(wv.shape)):
                 continue
             if xv.dtype not in (torch.bfloat16, torch.float16, torch.float32) or wv.dtype != xv.dtype:
                 continue
@@ -1285,15 +1308,15 @@ class FusedComboDense(Pattern):
             rows, k, cols = v.shape[-2], xv.shape[-1], v.shape[-1]
             if xv.dtype == torch.float32:
                 # the grouped fp32 launch is the FMA kernel; members large enough for the tensor-core path stay single
-                if 2 * rows * k * cols >= _ops.F32_TENSOR_MIN_FLOPS:
+                if 2 * _rows_hint(rows) * k * cols >= _ops.F32_TENSOR_MIN_FLOPS:
                     continue
-            elif k % 8 != 0 or wv.shape[-1] % 8 != 0 or (rank == 3 and (rows * k) % 8 != 0):
+            elif k % 8 != 0 or wv.shape[-1] % 8 != 0 or (rank == 3 and (rows * k) % 8 != 0):  # (rank 3: static extents)
                 continue  # 16-bit rows (and the batch entries' first rows) must be addressable by a tensor map
             kind = 0
             if bias is not None:
-                if not (isinstance(bv, torch.Tensor) and bv.dtype == xv.dtype and _static(bv.shape)):
+                if not (isinstance(bv, torch.Tensor) and bv.dtype == xv.dtype and (_static(bv.shape) or (rank == 2 and bv.dim() == 2 and _static_but_rows(bv.shape)))):
                     continue
-                if tuple(bv.shape) == tuple(v.shape) and rows > 1:
+                if _shape_key(bv.shape) == _shape_key(v.shape) and _shape_key(v.shape)[-2] != 1:
                     kind = 2  # a full addend
                 elif bv.numel() == cols and rank == 2 and (bv.dim() == 1 or (bv.dim() == 2 and bv.shape[0] == 1)):
                     kind = 1  # a row of N
@@ -1301,7 +1324,7 @@ class FusedComboDense(Pattern):
                     kind = 1  # a row of N per batch entry
                 else:
                     continue
-            key = (tuple(xv.shape), tuple(wv.shape), bool(wt), kind, act, xv.dtype)
+            key = (_shape_key(xv.shape), tuple(wv.shape), bool(wt), kind, act, xv.dtype)
             groups.setdefault(key, []).append(n)
         for key, nodes in groups.items():
             if len(nodes) < COMBO_MIN_WIDTH:
@@ -1354,8 +1377,8 @@ class FusedDenseTower(Pattern):
             if not (_module_call(gm, n, M.DenseLayerModule) and n.target == DENSE_NAME and len(n.args) == 5):
                 return False
             v, xv, bv = _val(n), _val(n.args[0]), _val(n.args[3])
-            if not (_tensor_ok(v, 2) and _tensor_ok(xv, 2) and _static(v.shape) and _static(xv.shape)):
-                return False
+            if not (_tensor_ok(v, 2) and _tensor_ok(xv, 2) and _static_but_rows(v.shape) and _static_but_rows(xv.shape)):
+                return False  # (the row count may be symbolic: the op chooses its kernels from the actual one)
             if v.dtype not in (torch.float32, torch.bfloat16, torch.float16) or xv.dtype != v.dtype:
                 return False
             if dtype is not None and v.dtype != dtype:
@@ -1365,7 +1388,7 @@ class FusedDenseTower(Pattern):
             return n.args[3] is None or (isinstance(bv, torch.Tensor) and bv.dim() == 1 and bv.numel() == v.shape[1])
 
         def worth_it(x, chain):
-            rows = _val(x).shape[0]
+            rows = _rows_hint(_val(x).shape[0])
             dims = [_val(x).shape[1]] + [_val(n).shape[1] for n in chain]
             dtype = _val(chain[0]).dtype
             # narrow neighbours whose weights fit in shared memory together (any dtype, any row length)
@@ -1376,7 +1399,8 @@ class FusedDenseTower(Pattern):
             head = chain[0]
             alike = [m for m in gm.graph.nodes
                      if is_dense(m, dtype) and m.args[2] == head.args[2] and m.args[4] == head.args[4]
-                     and _val(m.args[1]).shape == _val(head.args[1]).shape and _val(m.args[0]).shape == _val(x).shape]
+                     and _val(m.args[1]).shape == _val(head.args[1]).shape
+                     and _shape_key(_val(m.args[0]).shape) == _shape_key(_val(x).shape)]
             if len(alike) >= 4:
                 return False
             return small or any(_ops.mlp2_eligible(rows, dims[i], dims[i + 1], dims[i + 2], dtype, chain[i].args[2], chain[i + 1].args[2])
