@@ -306,3 +306,29 @@ def test_dynamic_batch_on_gpu(cuda_device):
         assert sorted(c.names) == sorted(["xg_gemm_group_bias_act", "xg_mlp_small_bias_act", "xg_layernorm"]), c.names
         for o, w in zip(got, want):
             assert_parity(o, w.float(), f"dynamic batch {m}")
+
+
+def test_dynamic_batch_recsys_graph_on_gpu(cuda_device):
+    """The recsys graph compiled once with a symbolic batch dimension and run at two batch sizes on the GPU: lookups +
+    mask + stack, slice-cat, the concatenation and the dense layers run fused, results equal eager CUDA."""
+    from tests.helpers import LaunchCounter
+    from xpu_graph_b200 import target
+    from xpu_graph_b200.workloads import make_recsys
+
+    model = None
+    compiled = None
+    for batch in (512, 1536):
+        m, inputs = make_recsys(seed=5, batch=batch)
+        if model is None:
+            model = m.to(cuda_device)
+            compiled = torch.compile(model, backend=target.backend(target.make_config()), dynamic=None)
+        args = tuple(t.to(cuda_device) for t in inputs)
+        for a in args:
+            torch._dynamo.mark_dynamic(a, 0)
+        with torch.no_grad():
+            with LaunchCounter() as c:
+                got = compiled(*args)
+            want = model(*args)
+        torch.cuda.synchronize()
+        assert "xg_gather_rows" in c.names and "xg_seg_copy" in c.names, c.names
+        assert_parity(got, want, f"recsys graph, dynamic batch {batch}")

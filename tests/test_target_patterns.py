@@ -773,6 +773,34 @@ def test_dynamic_batch_keeps_the_fusions(tgt):
     torch._dynamo.reset()
 
 
+def test_dynamic_batch_on_the_benchmark_graphs(tgt):
+    """The recsys graph and the Llama-style layer (reduced sizes) compiled with a symbolic batch dimension: same results
+    as eager; the recsys graph ends in the same modules as its static compilation (lookups + mask + stack, slice-cat, the
+    concatenation, three dense layers), the layer keeps its norms, RoPE and attention modules."""
+    from xpu_graph_b200.workloads import make_llama_layer, make_recsys
+
+    def run(model, inputs, dynamic_args):
+        torch._dynamo.reset()
+        cap = {}
+        compiled = torch.compile(model, backend=tgt.backend(tgt.make_config(), capture=cap), dynamic=None)
+        args = tuple(t.clone() for t in inputs)
+        for i in dynamic_args:
+            torch._dynamo.mark_dynamic(args[i], 0)
+        with torch.no_grad():
+            got, want = compiled(*args), model(*args)
+        for o, w in zip(got if isinstance(got, (tuple, list)) else (got,), want if isinstance(want, (tuple, list)) else (want,)):
+            _same(o, w, 1e-5)
+        return [n.target for n in cap["gm"].graph.nodes if n.op == "call_module"]
+
+    model, inputs = make_recsys(seed=5, batch=64)
+    mods = run(model, inputs, range(len(inputs)))
+    assert mods == ["xg_gather_stack", "fuse_slice_cat", "xg_cat_lastdim"] + ["custom_dense_layer_replacement"] * 3, mods
+    layer, (x, cos, sin) = make_llama_layer(seed=3, batch=2, seq=64, hidden=256, heads=4, ffn=512)
+    mods = run(layer.float(), (x.float(), cos.float(), sin.float()), [0])
+    assert mods.count("xg_rope") == 2 and "xg_sdpa" in mods and "custom_rms_norm" in mods and "xg_add_rms_norm" in mods, mods
+    torch._dynamo.reset()
+
+
 def test_sum_cat_fusions(tgt, xlog):
     """slice -> sum -> cat, mul -> sum -> cat and sum -> cat along the last dim become one module call each
     (graph forms of targets/mlu/fuse_sum_cat.py and fuse_mul_sum_cat.py; the reference's tests

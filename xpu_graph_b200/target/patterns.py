@@ -430,7 +430,7 @@ class FusedRoPE(Pattern):
             return None
         x = hi.args[0]
         xv = _val(x)
-        if not _tensor_ok(xv, 4) or not _static(xv.shape):
+        if not _tensor_ok(xv, 4) or not _static_but_rows(xv.shape):  # (the batch extent may be symbolic)
             return None
         D = xv.shape[-1]
         if D % 2 or dim not in (-1, 3):
@@ -779,7 +779,8 @@ class FusedEmbeddingStack(Pattern):
                 new = gm.graph.call_module("xg_gather_stack", (list(tables), idx, mask, True))
                 _fill_meta(gm, new)
                 B = _val(idx).shape[0]
-                out = gm.graph.call_function(aten.reshape.default, (new, [B, F, D]))
+                # (a symbolic batch size must not be written into the graph as a literal: let reshape infer it)
+                out = gm.graph.call_function(aten.reshape.default, (new, [B if isinstance(B, int) else -1, F, D]))
                 _fill_meta(gm, out)
                 if layout == "fbd":
                     out = gm.graph.call_function(aten.transpose.int, (out, 0, 1))
@@ -1068,8 +1069,9 @@ class FusedCatLastDim(Pattern):
                 continue
             if any(_is(p, aten.slice.Tensor) for p in parts):
                 continue  # leave slices to the slice-cat fusion
-            if not all(v.dim() == nd and v.dtype == vals[0].dtype and v.shape[:-1] == vals[0].shape[:-1]
-                       and v.device.type in M.ALLOWED_DEVICE_TYPES and _static(v.shape) for v in vals):
+            # (the leading extent may be symbolic - a dynamic batch - as long as it is the same expression in every part)
+            if not all(v.dim() == nd and v.dtype == vals[0].dtype and _shape_key(v.shape[:-1]) == _shape_key(vals[0].shape[:-1])
+                       and v.device.type in M.ALLOWED_DEVICE_TYPES and _static_but_rows(v.shape) for v in vals):
                 continue
             _ensure(gm, "xg_cat_lastdim", M.CatLastDimModule)
             with gm.graph.inserting_before(node):
