@@ -332,3 +332,29 @@ def test_dynamic_batch_recsys_graph_on_gpu(cuda_device):
         torch.cuda.synchronize()
         assert "xg_gather_rows" in c.names and "xg_seg_copy" in c.names, c.names
         assert_parity(got, want, f"recsys graph, dynamic batch {batch}")
+
+
+def test_dynamic_batch_llama_layer_on_gpu(cuda_device):
+    """The Llama-style layer (bf16, reduced size) compiled once with a symbolic batch dimension and run at two batch
+    sizes: eleven launches per call (RoPE as its own kernel, the residual adds in the projections' epilogues, the dual
+    GEMM with SwiGLU), results within the 16-bit bar of eager CUDA."""
+    from tests.helpers import LaunchCounter
+    from xpu_graph_b200 import lib, target
+    from xpu_graph_b200.workloads import make_llama_layer
+
+    layer, (x, cos, sin) = make_llama_layer(seed=3, batch=2, seq=320, hidden=512, heads=4, ffn=1376)
+    layer = layer.to(cuda_device)
+    cos, sin = cos.to(cuda_device), sin.to(cuda_device)
+    compiled = torch.compile(layer, backend=target.backend(target.make_config()), dynamic=None)
+    g = torch.Generator().manual_seed(17)
+    for batch in (2, 5):
+        xb = torch.randn(batch, 320, 512, generator=g).to(torch.bfloat16).to(cuda_device)
+        torch._dynamo.mark_dynamic(xb, 0)
+        with torch.no_grad():
+            with LaunchCounter() as c:
+                got = compiled(xb, cos, sin)
+            want = layer(xb, cos, sin)
+        torch.cuda.synchronize()
+        assert lib.tc_status() == 0
+        assert len(c.names) == 11 and c.names.count("xg_rope") == 2 and "xg_gemm_swiglu" in c.names, c.names
+        assert_parity(got, want, f"Llama layer, dynamic batch {batch}", magnitude=xb)

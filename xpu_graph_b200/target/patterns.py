@@ -596,20 +596,32 @@ class FusedDenseResidual(Pattern):
                 if act != "none" or not (_tensor_ok(dv, 2) and _tensor_ok(ov) and isinstance(av, torch.Tensor)):
                     continue
                 Mr, N = dv.shape
-                if not _static(dv.shape) or not _static(ov.shape) or ov.dtype != dv.dtype or ov.dim() < 1:
+                if ov.dtype != dv.dtype or ov.dim() < 1 or not isinstance(N, int):
                     continue
-                if ov.numel() != Mr * N or ov.shape[-1] != N or av.numel() != Mr * N:
-                    continue
+                if _static(dv.shape) and _static(ov.shape):
+                    if ov.numel() != Mr * N or ov.shape[-1] != N or av.numel() != Mr * N:
+                        continue
+                    back = None if list(av.shape) == [Mr, N] else list(av.shape)
+                else:
+                    # symbolic extents (a dynamic batch): the addend must have the sum's shape expression for expression,
+                    # ending in N; the way back to that shape is the size list of the reshape the dense output went through
+                    if ov.shape[-1] != N or _shape_key(ov.shape) != _shape_key(av.shape):
+                        continue
+                    if via is None and _shape_key(av.shape) != _shape_key(dv.shape):
+                        continue
+                    if via is not None and _shape_key(_val(via).shape) != _shape_key(av.shape):
+                        continue
+                    back = None if via is None else list(via.args[1])
                 if bias is not None and not (isinstance(bv, torch.Tensor) and bv.numel() == N and bv.dim() <= 2):
                     continue
                 _ensure(gm, "xg_dense_residual", M.DenseResidualModule)
                 with gm.graph.inserting_before(node):
-                    r2 = other if ov.dim() == 2 else gm.graph.call_function(aten.reshape.default, (other, [Mr, N]))
+                    r2 = other if ov.dim() == 2 else gm.graph.call_function(aten.reshape.default, (other, [-1, N]))
                     if r2 is not other:
                         _fill_meta(gm, r2)
                     new = gm.graph.call_module("xg_dense_residual", (x, w, wt, bias, r2, "none"))
                     _fill_meta(gm, new)
-                    out = new if list(av.shape) == [Mr, N] else gm.graph.call_function(aten.reshape.default, (new, list(av.shape)))
+                    out = new if back is None else gm.graph.call_function(aten.reshape.default, (new, back))
                     if out is not new:
                         _fill_meta(gm, out)
                 node.replace_all_uses_with(out)
