@@ -799,6 +799,18 @@ def test_dynamic_batch_on_the_benchmark_graphs(tgt):
     mods = run(layer.float(), (x.float(), cos.float(), sin.float()), [0])
     assert mods.count("xg_rope") == 2 and "xg_sdpa" in mods and mods.count("custom_rms_norm") == 2, mods
     assert mods.count("xg_dense_residual") == 2, mods  # both residual adds ride in their projection's epilogue
+    # in bf16 (the benchmark's dtype) the symbolic batch costs nothing: the same nine modules as the static graph
+    layer16, (x16, cos16, sin16) = make_llama_layer(seed=3, batch=2, seq=64, hidden=256, heads=4, ffn=512)
+    torch._dynamo.reset()
+    cap = {}
+    compiled = torch.compile(layer16, backend=tgt.backend(tgt.make_config(), capture=cap), dynamic=None)
+    xd = x16.clone()
+    torch._dynamo.mark_dynamic(xd, 0)
+    with torch.no_grad():
+        compiled(xd, cos16, sin16)
+    mods = [n.target for n in cap["gm"].graph.nodes if n.op == "call_module"]
+    assert mods == ["custom_rms_norm", "custom_dense_layer_replacement", "xg_dense_rope", "xg_dense_rope", "xg_sdpa", "xg_dense_residual",
+                    "custom_rms_norm", "xg_dense_swiglu", "xg_dense_residual"], mods
     torch._dynamo.reset()
 
 

@@ -175,7 +175,8 @@ class DenseSwiGLUModule(torch.nn.Module):
 class DenseRopeModule(torch.nn.Module):
     """q/k projection with the rotary embedding applied in the GEMM epilogue:
     forward(inputs [B*S, K], weight [H*D, K], cos, sin, B, S, H, D) -> [B, H, S, D] (a view of the [B, S, H*D]
-    result, i.e. exactly what reshape + transpose + RopeModule returned)."""
+    result, i.e. exactly what reshape + transpose + RopeModule returned). B = -1: inferred from the rows (a graph
+    compiled with a symbolic batch size)."""
 
     def forward(self, inputs, weight, cos, sin, B, S, H, D):
         y = _X.dense_rope(inputs, weight, cos, sin, int(S), int(D))

@@ -1041,11 +1041,21 @@ class FusedDenseRope(Pattern):
             xv, rv = _val(x), _val(rs)
             if not (wt and bias is None and act == "none" and _tensor_ok(xv, 2) and isinstance(rv, torch.Tensor)):
                 continue
-            if xv.dtype not in (torch.bfloat16, torch.float16) or rv.dim() != 4 or not _static(rv.shape):
+            if xv.dtype not in (torch.bfloat16, torch.float16) or rv.dim() != 4 or not _static_but_rows(rv.shape):
                 continue
             B, S, H, D = rv.shape
-            if D not in (64, 128) or xv.shape[0] != B * S or xv.shape[1] % 8 != 0:
+            if D not in (64, 128) or xv.shape[1] % 8 != 0:
                 continue
+            if isinstance(B, int) and isinstance(xv.shape[0], int):
+                if xv.shape[0] != B * S:
+                    continue
+            else:
+                # a symbolic batch: the rows must be B * S as expressions; the module infers B (view(-1, S, H, D))
+                from torch.fx.experimental.symbolic_shapes import statically_known_true
+
+                if not statically_known_true(xv.shape[0] == B * S):
+                    continue
+                B = -1
             _ensure(gm, "xg_dense_rope", M.DenseRopeModule)
             with gm.graph.inserting_before(node):
                 new = gm.graph.call_module("xg_dense_rope", (x, w, cos, sin, B, S, H, D))
