@@ -774,7 +774,7 @@ def test_dynamic_batch_keeps_the_fusions(tgt):
 
 
 def test_dynamic_batch_on_the_benchmark_graphs(tgt):
-    """The recsys graph and the Llama-style layer (reduced sizes) compiled with a symbolic batch dimension: same results
+    """The recsys graph, the encoder block and the Llama-style layer (reduced sizes) compiled with a symbolic batch dimension: same results
     as eager; the recsys graph ends in the same modules as its static compilation (lookups + mask + stack, slice-cat, the
     concatenation, three dense layers), the layer keeps its norms, RoPE, attention and residual-in-epilogue modules."""
     from xpu_graph_b200.workloads import make_llama_layer, make_recsys
@@ -799,6 +799,13 @@ def test_dynamic_batch_on_the_benchmark_graphs(tgt):
     mods = run(layer.float(), (x.float(), cos.float(), sin.float()), [0])
     assert mods.count("xg_rope") == 2 and "xg_sdpa" in mods and mods.count("custom_rms_norm") == 2, mods
     assert mods.count("xg_dense_residual") == 2, mods  # both residual adds ride in their projection's epilogue
+    from xpu_graph_b200.workloads import make_encoder
+
+    made = make_encoder(seed=1, batch=2, seq=32)
+    enc, enc_in = made[0], made[1] if isinstance(made[1], (tuple, list)) else (made[1],)
+    mods = run(enc, enc_in, range(len(enc_in)))
+    assert mods == ["xg_layer_norm", "custom_dense_layer_replacement", "xg_sdpa", "xg_dense_residual", "xg_layer_norm",
+                    "custom_dense_layer_replacement", "xg_dense_residual"], mods  # as the static encoder block
     # in bf16 (the benchmark's dtype) the symbolic batch costs nothing: the same nine modules as the static graph
     layer16, (x16, cos16, sin16) = make_llama_layer(seed=3, batch=2, seq=64, hidden=256, heads=4, ffn=512)
     torch._dynamo.reset()
