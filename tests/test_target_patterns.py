@@ -773,6 +773,38 @@ def test_dynamic_batch_keeps_the_fusions(tgt):
     torch._dynamo.reset()
 
 
+def test_automatic_dynamic_batch(tgt):
+    """The reference's own dynamic-shape test style (tests/common/test_dynamic_shape.py:17-31: dynamic=None, the batch size
+    walking up and down): the first call compiles a static graph, the second a symbolic one, both with the grouped launch
+    and the add + LayerNorm module, and every result equals eager."""
+    torch.manual_seed(15)
+
+    class Block(torch.nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.layers = torch.nn.ModuleList(torch.nn.Linear(16, 24) for _ in range(4))
+            self.ln = torch.nn.LayerNorm(16)
+
+        def forward(self, x, r):
+            h = self.ln(x + r)
+            return tuple(torch.relu(layer(h)) for layer in self.layers)
+
+    model = Block().eval()
+    torch._dynamo.reset()
+    cap = {}
+    compiled = torch.compile(model, backend=tgt.backend(tgt.make_config(), capture=cap), dynamic=None)
+    seen = []
+    for bs in list(range(2, 7)) + list(range(7, 2, -1)):
+        x, r = torch.randn(bs, 16), torch.randn(bs, 16)
+        with torch.no_grad():
+            got, want = compiled(x, r), model(x, r)
+        for o, w in zip(got, want):
+            _same(o, w, 1e-5)
+        seen.append([n.target for n in cap["gm"].graph.nodes if n.op == "call_module"])
+    assert all(m == ["xg_add_layer_norm_y", "xg_combo_dense"] for m in seen), seen
+    torch._dynamo.reset()
+
+
 def test_dynamic_batch_on_the_benchmark_graphs(tgt):
     """The recsys graph, the encoder block and the Llama-style layer (reduced sizes) compiled with a symbolic batch dimension: same results
     as eager; the recsys graph ends in the same modules as its static compilation (lookups + mask + stack, slice-cat, the
