@@ -773,6 +773,32 @@ def test_dynamic_batch_keeps_the_fusions(tgt):
     torch._dynamo.reset()
 
 
+def test_dynamic_batch_row_sums(tgt):
+    """slice -> sum -> cat and sum -> cat with a symbolic batch dimension: one module call each, as in the static graph."""
+    def fn(x, y0, y1, y2):
+        s = torch.cat([x[:, 0:10, :].sum(dim=1), x[:, 0:25, :].sum(dim=1), x[:, 8:40, :].sum(dim=1)], dim=-1)
+        t = torch.cat([y0.sum(dim=1), y1.sum(dim=1), y2.sum(dim=1)], dim=-1)
+        return s, t
+
+    torch._dynamo.reset()
+    cap = {}
+    compiled = torch.compile(fn, backend=tgt.backend(tgt.make_config(), capture=cap), dynamic=None)
+    g = torch.Generator().manual_seed(16)
+    for b in (6, 9, 4):
+        args = (torch.randn(b, 40, 16, generator=g), torch.randn(b, 3, 8, generator=g), torch.randn(b, 7, 8, generator=g),
+                torch.randn(b, 4, 8, generator=g))
+        for a in args:
+            torch._dynamo.mark_dynamic(a, 0)
+        with torch.no_grad():
+            got, want = compiled(*args), fn(*args)
+        for o, w in zip(got, want):
+            _same(o, w, 1e-5)
+    mods = [n.target for n in cap["gm"].graph.nodes if n.op == "call_module"]
+    assert mods == ["xg_slice_sum_cat_0", "xg_sum_cat"], mods
+    assert not [n for n in cap["gm"].graph.nodes if n.op == "call_function"]
+    torch._dynamo.reset()
+
+
 def test_automatic_dynamic_batch(tgt):
     """The reference's own dynamic-shape test style (tests/common/test_dynamic_shape.py:17-31: dynamic=None, the batch size
     walking up and down): the first call compiles a static graph, the second a symbolic one, both with the grouped launch

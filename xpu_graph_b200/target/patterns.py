@@ -1111,7 +1111,7 @@ def _sum_dim1(node) -> bool:
     if not _is(node, aten.sum.dim_IntList) or len(node.args) < 2 or len(node.args) > 2 or node.kwargs:
         return False
     v = _val(node.args[0])
-    return list(node.args[1]) == [1] and _tensor_ok(v, 3) and _static(v.shape)
+    return list(node.args[1]) == [1] and _tensor_ok(v, 3) and _static_but_rows(v.shape)  # (the batch may be symbolic)
 
 
 def _replace_run(gm: fx.GraphModule, cat: fx.Node, lo: int, hi: int, new: fx.Node) -> None:
@@ -1171,7 +1171,7 @@ class FusedSliceSumCat(Pattern):
                 if not (isinstance(sl.args[2], int) and isinstance(sl.args[3], int)):
                     return None
                 v = _val(sl.args[0])
-                return sl.args[0] if _tensor_ok(v, 3) and _static(v.shape) else None
+                return sl.args[0] if _tensor_ok(v, 3) and _static_but_rows(v.shape) else None
 
             i = 0
             while i < len(parts):
@@ -1212,7 +1212,7 @@ class FusedSumCat(Pattern):
                 if not (_sum_dim1(q) and _only_user(q, cat)) or _is(q.args[0], aten.slice.Tensor, aten.mul.Tensor):
                     return False
                 v = _val(q.args[0])
-                return ref is None or (v.shape[0] == ref.shape[0] and v.shape[2] == ref.shape[2] and v.dtype == ref.dtype)
+                return ref is None or (_shape_key(v.shape[:1]) == _shape_key(ref.shape[:1]) and v.shape[2] == ref.shape[2] and v.dtype == ref.dtype)
 
             i = 0
             while i < len(parts):
