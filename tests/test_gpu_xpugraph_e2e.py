@@ -358,3 +358,29 @@ def test_dynamic_batch_llama_layer_on_gpu(cuda_device):
         assert lib.tc_status() == 0
         assert len(c.names) == 9 and c.names.count("xg_gemm_rope") == 2 and "xg_gemm_swiglu" in c.names, c.names
         assert_parity(got, want, f"Llama layer, dynamic batch {batch}", magnitude=xb)
+
+
+def test_dynamic_batch_row_sums_on_gpu(cuda_device):
+    """slice -> sum -> cat and sum -> cat compiled once with a symbolic batch dimension, run at three batch sizes on the GPU."""
+    from tests.helpers import LaunchCounter
+    from xpu_graph_b200 import target
+
+    def fn(x, y0, y1, y2):
+        s = torch.cat([x[:, 0:10, :].sum(dim=1), x[:, 0:25, :].sum(dim=1), x[:, 8:40, :].sum(dim=1)], dim=-1)
+        t = torch.cat([y0.sum(dim=1), y1.sum(dim=1), y2.sum(dim=1)], dim=-1)
+        return s, t
+
+    compiled = torch.compile(fn, backend=target.backend(target.make_config()), dynamic=None)
+    g = torch.Generator().manual_seed(18)
+    for b in (6, 200, 33):
+        args = tuple(torch.randn(b, r, c, generator=g).to(cuda_device) for r, c in ((40, 16), (3, 8), (7, 8), (4, 8)))
+        for a in args:
+            torch._dynamo.mark_dynamic(a, 0)
+        with torch.no_grad():
+            with LaunchCounter() as c:
+                got = compiled(*args)
+            want = fn(*(a.double() for a in args))
+        torch.cuda.synchronize()
+        assert c.names == ["xg_rowsum_cat", "xg_rowsum_cat"], c.names
+        for o, w in zip(got, want):
+            assert_parity(o, w.float(), f"row sums, dynamic batch {b}")
