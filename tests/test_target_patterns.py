@@ -799,6 +799,37 @@ def test_dynamic_batch_row_sums(tgt):
     torch._dynamo.reset()
 
 
+def test_dynamic_batch_row_gathers(tgt):
+    """The three single-lookup forms (embedding, table[idx] with negative indices, index_select) with a symbolic number
+    of lookups: one RowGatherModule call each, as in the static graph."""
+    torch.manual_seed(17)
+
+    class Lookups(torch.nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.emb = torch.nn.Embedding(1000, 32)
+            self.table = torch.nn.Parameter(torch.randn(500, 16))
+
+        def forward(self, i, j, k):
+            return self.emb(i), self.table[j], torch.index_select(self.table, 0, k)
+
+    model = Lookups().eval()
+    torch._dynamo.reset()
+    cap = {}
+    compiled = torch.compile(model, backend=tgt.backend(tgt.make_config(), capture=cap), dynamic=None)
+    for b in (7, 19, 4):
+        i, j, k = torch.randint(0, 1000, (b, 3)), torch.randint(-500, 500, (b,)), torch.randint(0, 500, (b,))
+        for t in (i, j, k):
+            torch._dynamo.mark_dynamic(t, 0)
+        with torch.no_grad():
+            got, want = compiled(i, j, k), model(i, j, k)
+        for o, w in zip(got, want):
+            assert torch.equal(o, w)
+    mods = [n.target for n in cap["gm"].graph.nodes if n.op == "call_module"]
+    assert mods == ["xg_row_gather", "xg_row_gather_wrap", "xg_row_gather"], mods
+    torch._dynamo.reset()
+
+
 def test_automatic_dynamic_batch(tgt):
     """The reference's own dynamic-shape test style (tests/common/test_dynamic_shape.py:17-31: dynamic=None, the batch size
     walking up and down): the first call compiles a static graph, the second a symbolic one, both with the grouped launch

@@ -836,7 +836,8 @@ class FusedRowGather(Pattern):
             tv, iv = _val(table), _val(idx)
             if not (_tensor_ok(tv, 2) and isinstance(iv, torch.Tensor) and iv.dtype in (torch.int64, torch.int32)):
                 continue
-            if not (_static(tv.shape) and _static(iv.shape)) or iv.dim() < 1 or iv.device.type not in M.ALLOWED_DEVICE_TYPES:
+            # (the index tensor's extents may be symbolic - a dynamic batch of lookups; the module reads them at run time)
+            if not _static(tv.shape) or iv.dim() < 1 or iv.device.type not in M.ALLOWED_DEVICE_TYPES:
                 continue
             name = _ensure(gm, "xg_row_gather_wrap" if wrap else "xg_row_gather", lambda: M.RowGatherModule(wrap))
             with gm.graph.inserting_before(node):
