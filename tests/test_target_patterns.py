@@ -774,7 +774,8 @@ def test_dynamic_batch_keeps_the_fusions(tgt):
 
 
 def test_dynamic_batch_row_sums(tgt):
-    """slice -> sum -> cat and sum -> cat with a symbolic batch dimension: one module call each, as in the static graph."""
+    """slice -> sum -> cat, sum -> cat and mul -> sum -> cat with a symbolic batch dimension: one module call each, as in
+    the static graph."""
     def fn(x, y0, y1, y2):
         s = torch.cat([x[:, 0:10, :].sum(dim=1), x[:, 0:25, :].sum(dim=1), x[:, 8:40, :].sum(dim=1)], dim=-1)
         t = torch.cat([y0.sum(dim=1), y1.sum(dim=1), y2.sum(dim=1)], dim=-1)
@@ -796,6 +797,21 @@ def test_dynamic_batch_row_sums(tgt):
     mods = [n.target for n in cap["gm"].graph.nodes if n.op == "call_module"]
     assert mods == ["xg_slice_sum_cat_0", "xg_sum_cat"], mods
     assert not [n for n in cap["gm"].graph.nodes if n.op == "call_function"]
+
+    def products(a0, a1, a2, b0, b1, b2):  # the middle pair's second operand broadcasts over the batch
+        return torch.cat([(a0 * b0).sum(dim=1), (a1 * b1).sum(dim=1), (a2 * b2).sum(dim=1)], dim=-1)
+
+    torch._dynamo.reset()
+    cap = {}
+    compiled = torch.compile(products, backend=tgt.backend(tgt.make_config(), capture=cap), dynamic=None)
+    for b in (6, 9, 4):
+        a = [torch.randn(b, 5, 8, generator=g) for _ in range(3)]
+        bb = [torch.randn(1 if i == 1 else b, 5, 8, generator=g) for i in range(3)]
+        for t in a + [bb[0], bb[2]]:
+            torch._dynamo.mark_dynamic(t, 0)
+        with torch.no_grad():
+            _same(compiled(*a, *bb), products(*a, *bb), 1e-5)
+    assert [n.target for n in cap["gm"].graph.nodes if n.op == "call_module"] == ["xg_mul_sum_cat"]
     torch._dynamo.reset()
 
 

@@ -1239,10 +1239,20 @@ class FusedSumCat(Pattern):
 
 class FusedMulSumCat(Pattern):
     """cat([(a_k * b_k).sum(1) ...], -1) -> MulSumCatModule (the graph form of targets/mlu/fuse_mul_sum_cat.py:53-123);
-    a_k / b_k are [B or 1, R, C] tensors of one shape apart from the batch."""
+    a_k / b_k are [B or 1, R, C] tensors of one shape apart from the batch (B may be symbolic)."""
 
     _opt_level = OptLevel.level2
     _pattern_group = PatternGroup.GROUP0
+
+    @staticmethod
+    def _common_batch(a0, b0):
+        """The batch extent two operands broadcast to: both equal (as numbers or as symbolic expressions), or one is 1."""
+        one = lambda d: isinstance(d, int) and d == 1  # noqa: E731
+        if one(a0):
+            return b0
+        if one(b0) or _shape_key((a0,)) == _shape_key((b0,)):
+            return a0
+        return None
 
     def process(self, gm: fx.GraphModule) -> bool:
         changed = False
@@ -1258,14 +1268,14 @@ class FusedMulSumCat(Pattern):
                 if not (_is(mul, aten.mul.Tensor) and _only_user(mul, q)):
                     return False
                 va, vb = _val(mul.args[0]), _val(mul.args[1])
-                if not (_tensor_ok(va, 3) and _tensor_ok(vb, 3) and _static(va.shape) and _static(vb.shape)):
+                if not (_tensor_ok(va, 3) and _tensor_ok(vb, 3) and _static_but_rows(va.shape) and _static_but_rows(vb.shape)):
                     return False
                 if va.shape[1:] != vb.shape[1:] or va.dtype != vb.dtype:
                     return False
-                batch = max(va.shape[0], vb.shape[0])
-                if va.shape[0] not in (1, batch) or vb.shape[0] not in (1, batch):
+                batch = self._common_batch(va.shape[0], vb.shape[0])
+                if batch is None:
                     return False
-                return ref is None or (batch == ref[0] and va.shape[2] == ref[1] and va.dtype == ref[2])
+                return ref is None or (_shape_key((batch,)) == _shape_key((ref[0],)) and va.shape[2] == ref[1] and va.dtype == ref[2])
 
             i = 0
             while i < len(parts):
@@ -1273,7 +1283,7 @@ class FusedMulSumCat(Pattern):
                     i += 1
                     continue
                 va, vb = (_val(a) for a in parts[i].args[0].args[:2])
-                ref = (max(va.shape[0], vb.shape[0]), va.shape[2], va.dtype)
+                ref = (self._common_batch(va.shape[0], vb.shape[0]), va.shape[2], va.dtype)
                 j = i
                 while j + 1 < len(parts) and ok(parts[j + 1], ref):
                     j += 1
